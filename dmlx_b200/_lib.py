@@ -1,0 +1,188 @@
+"""ctypes binding of libdmlx_b200.so — the same C header a Zig host binds with @cImport.
+
+The library is the product: importing this module fails loudly when it has not been built
+(`python -m dmlx_b200.build`); there is no Python or CPU fallback behind it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libdmlx_b200.so")
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: build it with `python -m dmlx_b200.build` "
+        "(there is no fallback implementation)"
+    )
+
+lib = C.CDLL(LIB_PATH)
+
+u64, u32, i32, f32 = C.c_uint64, C.c_uint32, C.c_int32, C.c_float
+vp = C.c_void_p
+P = C.POINTER
+
+
+class PackDesc(C.Structure):
+    _fields_ = [("seq_slot", i32), ("count", i32), ("base_pos", i32), ("src_offset", i32)]
+
+
+class TokenOutput(C.Structure):
+    _fields_ = [("request_id", u64), ("token", u32), ("_pad", u32)]
+
+
+class KvConfig(C.Structure):
+    _fields_ = [(n, i32) for n in (
+        "n_layers", "n_kv_heads", "head_dim", "page_size", "n_pages", "max_seqs", "max_pages_per_seq",
+        "kv_dtype", "max_rows", "n_q_heads", "attn_scratch_chunks")]
+
+
+# status codes (include/dmlx_b200.h)
+OK = 0
+ERR_INSUFFICIENT_BLOCKS = 1
+ERR_INVALID_BLOCK_ID = 2
+ERR_PAGE_POOL_EXHAUSTED = 3
+ERR_INVALID_QUANT_BITS = 4
+ERR_INVALID_BATCH_INDEX = 5
+ERR_INVALID_ARGUMENT = 6
+ERR_CUDA = 7
+ERR_NO_DEVICE = 8
+ERR_UNSUPPORTED = 9
+ERR_CAPACITY = 10
+ERR_DEVICE_FLAGGED = 11
+
+
+def _sig(name, restype, *argtypes):
+    fn = getattr(lib, name)
+    fn.restype = restype
+    fn.argtypes = list(argtypes)
+    return fn
+
+
+_sig("b200_status_name", C.c_char_p, i32)
+_sig("b200_last_error", C.c_char_p)
+_sig("b200_version", i32)
+_sig("b200_device_available", i32)
+
+# block manager
+_sig("b200_bm_create", vp, u64)
+_sig("b200_bm_destroy", None, vp)
+_sig("b200_bm_can_allocate", i32, vp, u64)
+_sig("b200_bm_allocate_blocks", i32, vp, u64, u64, P(u64))
+_sig("b200_bm_free_blocks", None, vp, u64)
+_sig("b200_bm_copy_on_write", i32, vp, u64, P(u64))
+_sig("b200_bm_free_count", u64, vp)
+_sig("b200_bm_used_count", u64, vp)
+_sig("b200_bm_total_blocks", u64, vp)
+_sig("b200_hash_block", u64, u64, P(u32), u64)
+_sig("b200_bm_find_cached_prefix", i32, vp, P(u32), u64, u64, P(u64), u64, P(u64))
+_sig("b200_bm_register_block_hash", i32, vp, u64, u64)
+_sig("b200_bm_get_ref", u64, vp, u64)
+_sig("b200_bm_set_ref", None, vp, u64, u64)
+_sig("b200_bm_is_used", i32, vp, u64)
+_sig("b200_bm_get_tokens_used", u64, vp, u64)
+_sig("b200_bm_set_tokens_used", None, vp, u64, u64)
+_sig("b200_bm_share", None, vp, u64, u64)
+_sig("b200_bm_blocks_of", u64, vp, u64, P(u64), u64)
+
+# request
+_sig("b200_request_create", vp, u64, P(u32), u64, u64, P(u32), u64)
+_sig("b200_request_destroy", None, vp)
+_sig("b200_request_id", u64, vp)
+_sig("b200_request_state", i32, vp)
+_sig("b200_request_prefill_offset", u64, vp)
+_sig("b200_request_prompt_len", u64, vp)
+_sig("b200_request_seq_len", u64, vp)
+_sig("b200_request_is_stop_token", i32, vp, u32)
+_sig("b200_request_has_pending_prefill", i32, vp)
+_sig("b200_request_current_prefill_chunk_len", u64, vp, u64)
+_sig("b200_request_generated", u64, vp, P(u32), u64)
+_sig("b200_request_block_ids", u64, vp, P(u64), u64)
+_sig("b200_request_force_state", None, vp, i32, u64, P(u32), u64)
+_sig("b200_request_kv_slot", i32, vp)
+
+# scheduler-side block manager + scheduler
+_sig("b200_sched_bm_create", vp, u64)
+_sig("b200_sched_bm_create_with_real", vp, vp)
+_sig("b200_sched_bm_create_with_kv", vp, vp)
+_sig("b200_sched_bm_destroy", None, vp)
+_sig("b200_sched_bm_can_allocate", i32, vp, u64)
+_sig("b200_sched_bm_free_count", u64, vp)
+_sig("b200_sched_bm_total_blocks", u64, vp)
+_sig("b200_sched_bm_used_blocks", u64, vp)
+_sig("b200_scheduler_create", vp, vp, u64)
+_sig("b200_scheduler_destroy", None, vp)
+_sig("b200_scheduler_add_request", i32, vp, vp)
+_sig("b200_scheduler_schedule", i32, vp, P(vp), P(u64), P(vp), P(u64), u64, P(u64))
+_sig("b200_scheduler_postprocess", i32, vp, P(TokenOutput), u64)
+_sig("b200_scheduler_active_count", u64, vp)
+_sig("b200_scheduler_waiting_count", u64, vp)
+_sig("b200_scheduler_running_count", u64, vp)
+
+# batch builder
+_sig("b200_batch_build", i32, P(vp), u64, P(vp), u64, i32, u64, P(u32), P(i32), P(i32), u64, P(i32), P(u64), P(u64))
+_sig("b200_is_attending", i32, P(i32), u64, u64, u64)
+_sig("b200_batch_mask", i32, P(i32), u64, P(f32), u64)
+_sig("b200_greedy_host", u32, P(f32), u64)
+
+# device layer
+_sig("b200_pack_batch", i32, vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp)
+_sig("b200_kv_create", i32, P(KvConfig), P(vp))
+_sig("b200_kv_destroy", None, vp)
+_sig("b200_kv_dims", i32, vp, P(i32), P(i32))
+_sig("b200_kv_reset", i32, vp)
+_sig("b200_kv_set_free_order", i32, vp, P(i32), i32)
+_sig("b200_kv_free_count", i32, vp, P(i32))
+_sig("b200_kv_alloc", i32, vp, i32, i32, P(i32))
+_sig("b200_kv_release", i32, vp, P(i32), i32)
+_sig("b200_kv_fork", i32, vp, i32, i32, i32)
+_sig("b200_kv_rollback", i32, vp, i32, i32)
+_sig("b200_kv_filter", i32, vp, P(i32), i32)
+_sig("b200_kv_reserve", i32, vp, vp, i32, vp)
+_sig("b200_kv_append", i32, vp, i32, vp, vp, i32, vp)
+_sig("b200_kv_seq_len", i32, vp, i32, P(i32))
+_sig("b200_kv_current_len", i32, vp, P(i32))
+_sig("b200_kv_block_table", i32, vp, i32, P(i32), i32, P(i32))
+_sig("b200_kv_ref_counts", i32, vp, P(i32), i32)
+_sig("b200_kv_error_word", i32, vp, P(i32))
+_sig("b200_kv_gather", i32, vp, i32, i32, vp, vp, i32, vp)
+_sig("b200_kv_page_raw", i32, vp, i32, i32, vp, vp, P(f32), P(f32))
+_sig("b200_paged_attn_decode", i32, vp, i32, vp, vp, vp, i32, vp, vp)
+_sig("b200_set_attn_pages_per_chunk", None, i32)
+_sig("b200_rmsnorm", i32, vp, vp, vp, i32, i32, f32, vp)
+_sig("b200_rope", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp)
+_sig("b200_embed_gather", i32, vp, vp, vp, i32, i32, vp)
+_sig("b200_argmax", i32, vp, i32, i32, vp, vp)
+_sig("b200_qweight_create", i32, i32, i32, i32, i32, vp, vp, vp, P(vp))
+_sig("b200_qweight_destroy", None, vp)
+_sig("b200_qmm", i32, vp, vp, i32, vp, i32, vp, f32, i32, vp)
+
+
+class B200Error(RuntimeError):
+    def __init__(self, status: int):
+        self.status = status
+        name = lib.b200_status_name(status).decode()
+        msg = lib.b200_last_error().decode()
+        super().__init__(f"{name}: {msg}")
+
+
+class InsufficientBlocks(B200Error):
+    pass
+
+
+class InvalidBlockId(B200Error):
+    pass
+
+
+class InvalidBatchIndex(B200Error):
+    pass
+
+
+_ERR_CLASS = {ERR_INSUFFICIENT_BLOCKS: InsufficientBlocks, ERR_INVALID_BLOCK_ID: InvalidBlockId,
+              ERR_INVALID_BATCH_INDEX: InvalidBatchIndex}
+
+
+def check(status: int) -> None:
+    if status != OK:
+        raise _ERR_CLASS.get(status, B200Error)(status)

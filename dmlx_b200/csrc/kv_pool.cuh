@@ -1,0 +1,41 @@
+// Shared definitions of the device page pool (see kv_pool.cu for the layout).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "dmlx_b200.h"
+
+enum { ST_FREE_TOP = 0, ST_ERR = 1, ST_N_TOUCH = 2, ST_N_COW = 3, ST_ATTN_ERR = 4 };
+
+// Plain-old-data view of the pool, passed to kernels by value.
+struct KvDev {
+  void* k_pool = nullptr;
+  void* v_pool = nullptr;
+  float* k_scale = nullptr;
+  float* v_scale = nullptr;
+  int* free_stack = nullptr;
+  int* ref_count = nullptr;
+  int* tokens_used = nullptr;
+  int* block_table = nullptr;
+  int* seq_pages = nullptr;
+  int* seq_len = nullptr;
+  int* state = nullptr;
+  int4* touch_list = nullptr;  // {page, first packed row, rows, first slot in page}
+  int2* cow_list = nullptr;    // {source page, private copy}
+  int n_layers = 0, n_kv_heads = 0, head_dim = 0, page_size = 0, n_pages = 0, max_seqs = 0, max_pages_per_seq = 0;
+  int elem_bytes = 2;
+  int max_touch = 0;
+};
+
+struct b200_kv {
+  b200_kv_config cfg;
+  KvDev dev;
+  int* d_admin_in = nullptr;
+  int* d_admin_out = nullptr;
+  int admin_cap = 0;
+  // split-K attention scratch
+  int* d_chunk_start = nullptr;  // [max_rows + 2]
+  float* d_part_o = nullptr;     // [max_chunks][n_q_heads][head_dim]
+  float* d_part_ml = nullptr;    // [max_chunks][n_q_heads][2]  (running max in log2 units, sum)
+  int max_chunks = 0;
+};

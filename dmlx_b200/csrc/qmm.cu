@@ -1,0 +1,539 @@
+// Dequant-fused quantised matmul  y[T,N] = x[T,K] . dequant(W[N,K])^T  for affine int4 (group 64)
+// and MXFP4 (E2M1, one E8M0 scale per 32) weights.
+//
+// Weight layout in HBM ("blocks"): weights are repacked once into tiles of 128 output rows x 64
+// input columns; the block of tile (nt, kc) is contiguous:
+//     plane 0: 128 rows x 16 B   (nibbles of columns  0..31 of the chunk)
+//     plane 1: 128 rows x 16 B   (nibbles of columns 32..63)
+//     affine: 128 bf16 scales, 128 bf16 biases (one group of 64 = one chunk)        -> 4608 B
+//     mxfp4 : 128 x 2 E8M0 bytes (one per plane)                                    -> 4352 B
+// so a CTA streams its weights as whole blocks (one bulk copy per chunk, or fully coalesced
+// 16-byte loads in the GEMV kernel).  Within a 32-bit word holding columns 8w..8w+7, nibble
+// position p stores column 2p (p < 4) or 2(p-4)+1, so that (word >> 4i) & 0x000F000F yields the
+// adjacent column pair (2i, 2i+1) in the two halves of a bf16x2 register.
+//
+// Two kernels share the layout, the split-K scratch and the epilogue:
+//   * qmm_simt_kernel : bandwidth-bound GEMV for a handful of rows, f32 FMAs on CUDA cores.
+//   * qmm_tc_kernel   : "swap-AB" tcgen05 GEMM.  The 128 weight rows are the MMA M dimension, the
+//     packed tokens (16..256 per tile) the N dimension, so small and large batches both map to
+//     dense tensor-core tiles.  Per 64-column chunk: warp 4 issues one bulk copy for the weight
+//     block and one 2-D TMA load (128B swizzle) for the activation tile; warps 0-3 dequantise the
+//     block to bf16 into a 128B-swizzled K-major tile (1 row per thread); warp 5 issues 4
+//     tcgen05.mma (M128 x N x K16) accumulating in tensor memory and commits to free the stage.
+//     After the last chunk warps 0-3 read the accumulator with tcgen05.ld.
+// Split-K partials go to an f32 scratch; the last CTA to arrive for an output tile sums them in
+// split order (deterministic), applies the epilogue and writes bf16.  No CTA waits on another.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <algorithm>
+#include <cstring>
+#include <vector>
+
+#include "common.h"
+#include "ptx.cuh"
+#include "qmm.cuh"
+
+namespace {
+
+constexpr int kTileN = 128;
+constexpr int kChunkK = 64;
+constexpr int kPlaneBytes = kTileN * 16;
+
+__host__ __device__ constexpr int block_bytes(int mode) { return mode == B200_Q_AFFINE4_G64 ? 4608 : 4352; }
+
+// ---- dequantisation of one 32-bit word (8 columns) to 8 bf16 -----------------------------------
+template <int MODE>
+__device__ __forceinline__ uint4 dequant_word(uint32_t word, __nv_bfloat162 s2, __nv_bfloat162 b2) {
+  uint32_t out[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t t = (word >> (4 * i)) & 0x000F000Fu;
+    __nv_bfloat162 r;
+    if (MODE == B200_Q_AFFINE4_G64) {
+      // 0x4300 | q is the bf16 128+q; subtracting 128 leaves q exactly, then one fused q*s+b.
+      uint32_t u = t | 0x43004300u;
+      const uint32_t c128 = 0x43004300u;
+      __nv_bfloat162 q = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), *reinterpret_cast<const __nv_bfloat162*>(&c128));
+      r = __hfma2(q, s2, b2);
+    } else {
+      // sign | (e,m) << 6 is the E2M1 value times 2^-126 (exact, subnormals included); two exact
+      // power-of-two multiplies bring it to value * 2^(scale-127).
+      uint32_t u = ((t & 0x00080008u) << 12) | ((t & 0x00070007u) << 6);
+      const uint32_t c64 = 0x5F805F80u;  // 2^64
+      r = __hmul2(__hmul2(*reinterpret_cast<__nv_bfloat162*>(&u), *reinterpret_cast<const __nv_bfloat162*>(&c64)), s2);
+    }
+    out[i] = *reinterpret_cast<uint32_t*>(&r);
+  }
+  return make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+// Per-row dequant parameters for one plane of a block.
+template <int MODE>
+__device__ __forceinline__ void row_params(const unsigned char* blk, int r, int plane, __nv_bfloat162& s2, __nv_bfloat162& b2) {
+  if (MODE == B200_Q_AFFINE4_G64) {
+    const __nv_bfloat16* sc = reinterpret_cast<const __nv_bfloat16*>(blk + 2 * kPlaneBytes);
+    s2 = __bfloat162bfloat162(sc[r]);
+    b2 = __bfloat162bfloat162(sc[kTileN + r]);
+  } else {
+    uint32_t se = blk[2 * kPlaneBytes + r * 2 + plane];
+    se = se > 192u ? 192u : se;
+    uint32_t bits = (se + 62u) << 7;  // bf16 2^(se-65)
+    bits |= bits << 16;
+    s2 = *reinterpret_cast<__nv_bfloat162*>(&bits);
+    b2 = s2;
+  }
+}
+
+// ---- split-K finish: the last CTA of a tile reduces, applies the epilogue, writes bf16 ----------
+__device__ void qmm_finish_tile(const QmmArgs& a, int tile_id, int nt, int t0, int split_count) {
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int prev = atomicAdd(&a.counters[tile_id], 1);
+    s_last = (prev == split_count - 1);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* base = a.ws + (size_t)tile_id * split_count * a.tn * kTileN;
+  const int n0 = nt * kTileN;
+  if (a.epilogue == B200_EPI_SWIGLU) {
+    const int n_out = a.n / 2;
+    for (int idx = threadIdx.x; idx < a.tn * (kTileN / 2); idx += blockDim.x) {
+      const int t = idx / (kTileN / 2), rp = idx % (kTileN / 2);
+      const int token = t0 + t, n = n0 + 2 * rp;
+      if (token >= a.rows || n >= a.n) continue;
+      float g = 0.f, u = 0.f;
+      for (int s = 0; s < split_count; ++s) {
+        const float* p = base + ((size_t)s * a.tn + t) * kTileN + 2 * rp;
+        g += p[0];
+        u += p[1];
+      }
+      if (a.swiglu_limit > 0.f) {
+        g = fminf(g, a.swiglu_limit);
+        u = fminf(fmaxf(u, -a.swiglu_limit), a.swiglu_limit);
+      }
+      const float act = g / (1.0f + __expf(-g)) * u;
+      a.y[(size_t)a.row_base_out(token) * n_out + n / 2] = __float2bfloat16(act * a.row_scale(token));
+    }
+  } else {
+    for (int idx = threadIdx.x; idx < a.tn * kTileN; idx += blockDim.x) {
+      const int t = idx / kTileN, r = idx % kTileN;
+      const int token = t0 + t, n = n0 + r;
+      if (token >= a.rows || n >= a.n) continue;
+      float acc = 0.f;
+      for (int s = 0; s < split_count; ++s) acc += base[((size_t)s * a.tn + t) * kTileN + r];
+      const size_t o = (size_t)a.row_base_out(token) * a.n + n;
+      if (a.epilogue == B200_EPI_RESIDUAL) acc += __bfloat162float(a.residual[o]);
+      a.y[o] = __float2bfloat16(acc * a.row_scale(token));
+    }
+  }
+  if (threadIdx.x == 0) a.counters[tile_id] = 0;
+}
+
+// ---- GEMV kernel ---------------------------------------------------------------------------------
+template <int MODE, int TT>
+__global__ void __launch_bounds__(kTileN) qmm_simt_kernel(QmmArgs a) {
+  __shared__ __align__(16) float xs[TT][kChunkK];
+  const int nt = blockIdx.x, split = blockIdx.y, tt = blockIdx.z;
+  const int r = threadIdx.x, t0 = tt * TT;
+  const int kc0 = split * a.chunks_per_split, kc1 = min(kc0 + a.chunks_per_split, a.kc);
+  float acc[TT];
+#pragma unroll
+  for (int t = 0; t < TT; ++t) acc[t] = 0.f;
+  constexpr int BB = block_bytes(MODE);
+  for (int kc = kc0; kc < kc1; ++kc) {
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < TT * kChunkK; idx += blockDim.x) {
+      const int t = idx / kChunkK, j = idx % kChunkK;
+      xs[t][j] = (t0 + t < a.rows) ? __bfloat162float(a.x[(size_t)(t0 + t) * a.k + kc * kChunkK + j]) : 0.f;
+    }
+    __syncthreads();
+    const unsigned char* blk = a.blocks + ((size_t)nt * a.kc + kc) * BB;
+#pragma unroll
+    for (int plane = 0; plane < 2; ++plane) {
+      const uint4 raw = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[r];
+      __nv_bfloat162 s2, b2;
+      row_params<MODE>(blk, r, plane, s2, b2);
+      const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint4 d = dequant_word<MODE>(words[w], s2, b2);
+        const uint32_t dd[4] = {d.x, d.y, d.z, d.w};
+        float wf[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { wf[2 * i] = ptx::bf16_lo(dd[i]); wf[2 * i + 1] = ptx::bf16_hi(dd[i]); }
+        const int col = plane * 32 + w * 8;
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+          const float4 x0 = *reinterpret_cast<const float4*>(&xs[t][col]);
+          const float4 x1 = *reinterpret_cast<const float4*>(&xs[t][col + 4]);
+          acc[t] = fmaf(wf[0], x0.x, acc[t]); acc[t] = fmaf(wf[1], x0.y, acc[t]);
+          acc[t] = fmaf(wf[2], x0.z, acc[t]); acc[t] = fmaf(wf[3], x0.w, acc[t]);
+          acc[t] = fmaf(wf[4], x1.x, acc[t]); acc[t] = fmaf(wf[5], x1.y, acc[t]);
+          acc[t] = fmaf(wf[6], x1.z, acc[t]); acc[t] = fmaf(wf[7], x1.w, acc[t]);
+        }
+      }
+    }
+  }
+  const int tile_id = nt * gridDim.z + tt;
+  float* wsp = a.ws + ((size_t)tile_id * gridDim.y + split) * a.tn * kTileN;
+#pragma unroll
+  for (int t = 0; t < TT; ++t) wsp[(size_t)t * kTileN + r] = acc[t];
+  qmm_finish_tile(a, tile_id, nt, t0, gridDim.y);
+}
+
+// ---- tcgen05 kernel ------------------------------------------------------------------------------
+constexpr int kTcThreads = 192;
+constexpr int kRawStride = 5120;  // weight block padded to a multiple of 1024
+
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+          ptx::smem_u32(dst)),
+      "l"(map), "r"(x), "r"(y), "r"(ptx::smem_u32(bar))
+      : "memory");
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_constant__ CUtensorMap xmap, QmmArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  // 1024-byte alignment: the 128B swizzle pattern is a function of the shared-memory address.
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int tn = a.tn, stages = a.stages;
+  const int stage_stride = kTileN * 128 + tn * 128 + kRawStride;
+  auto a_tile = [&](int s) { return smem + (size_t)s * stage_stride; };
+  auto x_tile = [&](int s) { return smem + (size_t)s * stage_stride + kTileN * 128; };
+  auto raw_blk = [&](int s) { return smem + (size_t)s * stage_stride + kTileN * 128 + tn * 128; };
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_stride);
+  uint64_t* loaded = bars;
+  uint64_t* a_ready = bars + stages;
+  uint64_t* mma_done = bars + 2 * stages;
+  uint64_t* accum_ready = bars + 3 * stages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * stages + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nt = blockIdx.x, split = blockIdx.y, tt = blockIdx.z;
+  const int t0 = tt * tn;
+  const int kc0 = split * a.chunks_per_split, kc1 = min(kc0 + a.chunks_per_split, a.kc);
+  const int n_chunks = kc1 - kc0;
+  constexpr int BB = block_bytes(MODE);
+  uint32_t ncols = 32;
+  while (ncols < (uint32_t)tn) ncols <<= 1;
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(&loaded[s], 1);
+      ptx::mbar_init(&a_ready[s], kTileN);
+      ptx::mbar_init(&mma_done[s], 1);
+    }
+    ptx::mbar_init(accum_ready, 1);
+    ptx::mbar_fence_init();
+  }
+  if (warp == 5) {
+    ptx::tmem_alloc(tmem_slot, ncols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      for (int i = 0; i < n_chunks && ok; ++i) {
+        const int s = i % stages;
+        ok = ptx::mbar_wait(&mma_done[s], ((i / stages) & 1) ^ 1);
+        if (!ok) break;
+        ptx::mbar_expect_tx(&loaded[s], BB + tn * 128);
+        ptx::bulk_g2s(raw_blk(s), a.blocks + ((size_t)nt * a.kc + kc0 + i) * BB, BB, &loaded[s]);
+        tma_load_2d(x_tile(s), &xmap, (kc0 + i) * kChunkK, a.x_row0 + t0, &loaded[s]);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t idesc = ptx::umma_idesc_bf16(kTileN, tn);
+      for (int i = 0; i < n_chunks && ok; ++i) {
+        const int s = i % stages;
+        ok = ptx::mbar_wait(&loaded[s], (i / stages) & 1) && ptx::mbar_wait(&a_ready[s], (i / stages) & 1);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint64_t da = ptx::umma_desc_k_sw128(ptx::smem_u32(a_tile(s)));
+        const uint64_t db = ptx::umma_desc_k_sw128(ptx::smem_u32(x_tile(s)));
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)  // 4 x K16 per 64-column chunk; +32 bytes = +2 in 16-byte units
+          ptx::umma_bf16(tmem_base, da + 2 * k4, db + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+        ptx::umma_commit(&mma_done[s]);
+      }
+      if (ok) ptx::umma_commit(accum_ready);
+    }
+  } else {
+    // ---- dequantise: thread r owns weight row r of the tile ----
+    const int r = tid;
+    for (int i = 0; i < n_chunks && ok; ++i) {
+      const int s = i % stages;
+      ok = ptx::mbar_wait(&loaded[s], (i / stages) & 1);
+      if (!ok) break;
+      const unsigned char* blk = raw_blk(s);
+      unsigned char* arow = a_tile(s) + r * 128;
+#pragma unroll
+      for (int plane = 0; plane < 2; ++plane) {
+        const uint4 raw = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[r];
+        __nv_bfloat162 s2, b2;
+        row_params<MODE>(blk, r, plane, s2, b2);
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const int chunk16 = plane * 4 + w;  // 16-byte chunk index within the 128-byte row
+          *reinterpret_cast<uint4*>(arow + ((chunk16 ^ (r & 7)) << 4)) = dequant_word<MODE>(words[w], s2, b2);
+        }
+      }
+      ptx::fence_proxy_async_smem();
+      ptx::mbar_arrive(&a_ready[s]);
+    }
+    // ---- accumulator -> f32 partial tile in scratch ----
+    if (ok) ok = ptx::mbar_wait(accum_ready, 0);
+    if (ok) {
+      ptx::tc_fence_after_sync();
+      const int tile_id = nt * gridDim.z + tt;
+      float* wsp = a.ws + ((size_t)tile_id * gridDim.y + split) * tn * kTileN;
+      for (int c0 = 0; c0 < tn; c0 += 32) {
+        uint32_t v[32];
+        ptx::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+        ptx::tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (c0 + j < tn) wsp[(size_t)(c0 + j) * kTileN + warp * 32 + lane] = __uint_as_float(v[j]);
+      }
+    }
+  }
+  if (!ok) atomicExch(a.err, B200_ERR_DEVICE_FLAGGED);
+  ptx::tc_fence_before_sync();
+  const int any_bad = __syncthreads_or(!ok);
+  if (warp == 5) ptx::tmem_dealloc(tmem_base, ncols);
+  if (any_bad) return;
+  qmm_finish_tile(a, nt * gridDim.z + tt, nt, t0, gridDim.y);
+}
+
+// ---- host-side state -------------------------------------------------------------------------------
+float* g_ws = nullptr;
+size_t g_ws_bytes = 0;
+int* g_counters = nullptr;
+int g_counters_n = 0;
+int* g_err = nullptr;
+int g_sms = 0;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+b200_status ensure_state(size_t ws_bytes, int n_counters) {
+  if (!g_err) {
+    B200_CUDA_TRY(cudaMalloc((void**)&g_err, sizeof(int)));
+    B200_CUDA_TRY(cudaMemset(g_err, 0, sizeof(int)));
+    int dev = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev));
+  }
+  if (ws_bytes > g_ws_bytes) {
+    B200_CUDA_TRY(cudaDeviceSynchronize());
+    if (g_ws) cudaFree(g_ws);
+    g_ws = nullptr;
+    size_t want = std::max(ws_bytes, (size_t)64 << 20);
+    B200_CUDA_TRY(cudaMalloc((void**)&g_ws, want));
+    g_ws_bytes = want;
+  }
+  if (n_counters > g_counters_n) {
+    B200_CUDA_TRY(cudaDeviceSynchronize());
+    if (g_counters) cudaFree(g_counters);
+    g_counters = nullptr;
+    int want = std::max(n_counters, 1 << 16);
+    B200_CUDA_TRY(cudaMalloc((void**)&g_counters, sizeof(int) * want));
+    B200_CUDA_TRY(cudaMemset(g_counters, 0, sizeof(int) * want));
+    g_counters_n = want;
+  }
+  return B200_OK;
+}
+
+b200_status make_x_map(CUtensorMap* map, const void* x, int rows, int k, int box_rows) {
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    B200_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (!fn || q != cudaDriverEntryPointSuccess) {
+      b200_set_error("cuTensorMapEncodeTiled is not available from the driver");
+      return B200_ERR_CUDA;
+    }
+    g_encode = (EncodeTiledFn)fn;
+  }
+  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)k * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kChunkK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    b200_set_error("cuTensorMapEncodeTiled failed (%d) for x[%d,%d]", (int)r, rows, k);
+    return B200_ERR_CUDA;
+  }
+  return B200_OK;
+}
+
+int pick_splits(int tiles, int kc, int sms) {
+  // Enough CTAs to fill the machine about twice, but at least 4 chunks per split.
+  int want = (2 * sms + tiles - 1) / tiles;
+  int max_s = std::max(1, kc / 4);
+  return std::max(1, std::min(want, max_s));
+}
+
+}  // namespace
+
+// ---- repacking ---------------------------------------------------------------------------------------
+static inline int nibble_pos_to_col(int p) { return p < 4 ? 2 * p : 2 * (p - 4) + 1; }
+
+extern "C" b200_status b200_qweight_create(int32_t mode, int32_t n_experts, int32_t n, int32_t k, const void* h_packed,
+                                           const void* h_scales, const void* h_biases, b200_qweight** out) {
+  *out = nullptr;
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (mode != B200_Q_AFFINE4_G64 && mode != B200_Q_MXFP4_G32) { b200_set_error("unknown quantisation mode %d", mode); return B200_ERR_INVALID_QUANT_BITS; }
+  if (n_experts <= 0 || n <= 0 || k <= 0 || k % kChunkK != 0) { b200_set_error("qweight: K must be a positive multiple of 64"); return B200_ERR_INVALID_ARGUMENT; }
+  if (mode == B200_Q_AFFINE4_G64 && !h_biases) { b200_set_error("affine weights need biases"); return B200_ERR_INVALID_ARGUMENT; }
+  const int nt = (n + kTileN - 1) / kTileN, kc = k / kChunkK, bb = block_bytes(mode);
+  const size_t total = (size_t)n_experts * nt * kc * bb;
+  std::vector<unsigned char> host(total, 0);
+  for (int e = 0; e < n_experts; ++e)
+    for (int t = 0; t < nt; ++t)
+      for (int c = 0; c < kc; ++c) {
+        unsigned char* blk = host.data() + (((size_t)e * nt + t) * kc + c) * bb;
+        for (int r = 0; r < kTileN; ++r) {
+          const int row = t * kTileN + r;
+          if (row >= n) {
+            if (mode == B200_Q_MXFP4_G32) { blk[2 * kPlaneBytes + r * 2] = 127; blk[2 * kPlaneBytes + r * 2 + 1] = 127; }
+            continue;  // zero nibbles, zero scale/bias (affine) -> zero weights
+          }
+          const size_t grow = (size_t)e * n + row;
+          for (int plane = 0; plane < 2; ++plane)
+            for (int w = 0; w < 4; ++w) {
+              uint32_t word = 0;
+              for (int p = 0; p < 8; ++p) {
+                const int col = c * kChunkK + plane * 32 + w * 8 + nibble_pos_to_col(p);
+                uint32_t nib;
+                if (mode == B200_Q_AFFINE4_G64) {
+                  const uint32_t src = ((const uint32_t*)h_packed)[grow * (k / 8) + col / 8];
+                  nib = (src >> (4 * (col % 8))) & 0xF;
+                } else {
+                  const uint8_t src = ((const uint8_t*)h_packed)[grow * (k / 2) + col / 2];
+                  nib = (col & 1) ? (src >> 4) & 0xF : src & 0xF;
+                }
+                word |= nib << (4 * p);
+              }
+              std::memcpy(blk + plane * kPlaneBytes + r * 16 + w * 4, &word, 4);
+            }
+          if (mode == B200_Q_AFFINE4_G64) {
+            uint16_t* sc = (uint16_t*)(blk + 2 * kPlaneBytes);
+            sc[r] = ((const uint16_t*)h_scales)[grow * (k / 64) + c];
+            sc[kTileN + r] = ((const uint16_t*)h_biases)[grow * (k / 64) + c];
+          } else {
+            blk[2 * kPlaneBytes + r * 2] = ((const uint8_t*)h_scales)[grow * (k / 32) + c * 2];
+            blk[2 * kPlaneBytes + r * 2 + 1] = ((const uint8_t*)h_scales)[grow * (k / 32) + c * 2 + 1];
+          }
+        }
+      }
+  auto* w = new b200_qweight();
+  w->mode = mode; w->n_experts = n_experts; w->n = n; w->k = k; w->nt = nt; w->kc = kc; w->block_bytes = bb;
+  cudaError_t e = cudaMalloc((void**)&w->d_blocks, total);
+  if (e != cudaSuccess) { b200_set_error("cudaMalloc(%zu) failed: %s", total, cudaGetErrorString(e)); delete w; return B200_ERR_CUDA; }
+  e = cudaMemcpy(w->d_blocks, host.data(), total, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) { b200_set_error("weight upload failed: %s", cudaGetErrorString(e)); cudaFree(w->d_blocks); delete w; return B200_ERR_CUDA; }
+  *out = w;
+  return B200_OK;
+}
+
+extern "C" void b200_qweight_destroy(b200_qweight* w) {
+  if (!w) return;
+  if (w->d_blocks) cudaFree(w->d_blocks);
+  delete w;
+}
+
+// ---- launch -------------------------------------------------------------------------------------------
+template <int MODE>
+static b200_status launch_simt(QmmArgs& a, int rows, cudaStream_t s) {
+  constexpr int TT = 4;
+  a.tn = TT;
+  const int tts = (rows + TT - 1) / TT;
+  const int tiles = a.nt * tts;
+  const int splits0 = pick_splits(tiles, a.kc, g_sms ? g_sms : 148);
+  a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
+  const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
+  b200_status st = ensure_state((size_t)tiles * splits * TT * kTileN * sizeof(float), tiles);
+  if (st != B200_OK) return st;
+  a.ws = g_ws; a.counters = g_counters; a.err = g_err;
+  qmm_simt_kernel<MODE, TT><<<dim3(a.nt, splits, tts), kTileN, 0, s>>>(a);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+template <int MODE>
+static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
+  const int tn = std::min(256, ((rows + 15) / 16) * 16);
+  a.tn = tn;
+  const int tts = (rows + tn - 1) / tn;
+  const int tiles = a.nt * tts;
+  b200_status st = ensure_state(0, 0);
+  if (st != B200_OK) return st;
+  const int splits0 = pick_splits(tiles, a.kc, g_sms);
+  a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
+  const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
+  st = ensure_state((size_t)tiles * splits * tn * kTileN * sizeof(float), tiles);
+  if (st != B200_OK) return st;
+  a.ws = g_ws; a.counters = g_counters; a.err = g_err;
+  const int stage_stride = kTileN * 128 + tn * 128 + kRawStride;
+  a.stages = std::max(2, std::min(6, (200 * 1024) / stage_stride));
+  const size_t smem = (size_t)a.stages * stage_stride + 1024 /*alignment slack*/ + 8 * (3 * a.stages + 2) + 16;
+  static size_t configured[2] = {0, 0};
+  if (configured[MODE] < smem) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(qmm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    configured[MODE] = 227 * 1024;
+  }
+  CUtensorMap xmap;
+  st = make_x_map(&xmap, a.x, rows, a.k, tn);
+  if (st != B200_OK) return st;
+  a.x_row0 = 0;
+  qmm_tc_kernel<MODE><<<dim3(a.nt, splits, tts), kTcThreads, smem, s>>>(xmap, a);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
+                                const void* d_residual, float swiglu_limit, int32_t path, void* stream) {
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (rows <= 0) return B200_OK;
+  if (w->n_experts != 1) { b200_set_error("qmm: stacked expert weights go through the grouped entry point"); return B200_ERR_INVALID_ARGUMENT; }
+  if (epilogue == B200_EPI_RESIDUAL && !d_residual) { b200_set_error("qmm: residual epilogue without a residual"); return B200_ERR_INVALID_ARGUMENT; }
+  if (epilogue == B200_EPI_SWIGLU && (w->n % 2) != 0) { b200_set_error("qmm: SwiGLU needs an even N"); return B200_ERR_INVALID_ARGUMENT; }
+  if (path == B200_QMM_AUTO) path = rows <= 2 ? B200_QMM_SIMT : B200_QMM_TCGEN05;
+  QmmArgs a{};
+  a.blocks = w->d_blocks; a.x = (const __nv_bfloat16*)d_x; a.y = (__nv_bfloat16*)d_y;
+  a.residual = (const __nv_bfloat16*)d_residual;
+  a.rows = rows; a.n = w->n; a.k = w->k; a.nt = w->nt; a.kc = w->kc; a.epilogue = epilogue; a.swiglu_limit = swiglu_limit;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (path == B200_QMM_SIMT)
+    return w->mode == B200_Q_AFFINE4_G64 ? launch_simt<B200_Q_AFFINE4_G64>(a, rows, s) : launch_simt<B200_Q_MXFP4_G32>(a, rows, s);
+  return w->mode == B200_Q_AFFINE4_G64 ? launch_tc<B200_Q_AFFINE4_G64>(a, rows, s) : launch_tc<B200_Q_MXFP4_G32>(a, rows, s);
+}
+
+// Reads and clears the matmul kernels' error word (a bounded wait that ran out).
+extern "C" b200_status b200_qmm_error_word(int32_t* out) {
+  *out = 0;
+  if (!g_err) return B200_OK;
+  B200_CUDA_TRY(cudaMemcpy(out, g_err, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*out != 0) B200_CUDA_TRY(cudaMemset(g_err, 0, sizeof(int)));
+  return B200_OK;
+}

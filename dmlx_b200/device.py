@@ -1,0 +1,254 @@
+"""Device-side Python surface: torch tensors carry device memory and streams, every operation
+is a call into libdmlx_b200 through the C-ABI.  There is no torch or CPU implementation behind
+these calls — without the library or without a GPU they raise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from . import _lib
+from ._lib import KvConfig, PackDesc, lib
+
+KV_BF16, KV_FP8_E4M3 = 0, 1
+Q_AFFINE4_G64, Q_MXFP4_G32 = 0, 1
+EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+QMM_AUTO, QMM_SIMT, QMM_TCGEN05 = 0, 1, 2
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    if t is None:
+        return None
+    assert t.is_cuda and t.is_contiguous(), "device tensors must be contiguous CUDA tensors"
+    return t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def pack_desc_array(descs: Sequence[Sequence[int]]) -> torch.Tensor:
+    """[(seq_slot, count, base_pos, src_offset)] -> pinned int32 [R,4] host tensor."""
+    a = torch.tensor(list(descs), dtype=torch.int32).reshape(-1, 4)
+    return a.pin_memory() if torch.cuda.is_available() else a
+
+
+class PackedBatch:
+    """Device-resident result of pack_batch (the ragged stand-in for BatchResult)."""
+
+    def __init__(self, n_req: int, total_rows: int, device):
+        i32 = dict(dtype=torch.int32, device=device)
+        self.n_req, self.total_rows = n_req, total_rows
+        self.cu_seqlens = torch.empty(n_req + 1, **i32)
+        self.token_ids = torch.empty(max(total_rows, 1), dtype=torch.int32, device=device)  # u32 payload
+        self.position_ids = torch.empty(max(total_rows, 1), **i32)
+        self.row_to_req = torch.empty(max(total_rows, 1), **i32)
+        self.row_seq = torch.empty(max(total_rows, 1), **i32)
+        self.row_ctx = torch.empty(max(total_rows, 1), **i32)
+        self.last_row = torch.empty(max(n_req, 1), **i32)
+
+
+def pack_batch(d_desc: torch.Tensor, total_rows: int, prefill_tokens: Optional[torch.Tensor],
+               last_token: Optional[torch.Tensor], out: Optional[PackedBatch] = None) -> PackedBatch:
+    """b200_pack_batch: builds cu_seqlens / positions / flat tokens on the GPU."""
+    n_req = d_desc.shape[0]
+    out = out or PackedBatch(n_req, total_rows, d_desc.device)
+    _lib.check(lib.b200_pack_batch(_ptr(d_desc), n_req, _ptr(prefill_tokens), _ptr(last_token),
+                                   _ptr(out.cu_seqlens), _ptr(out.token_ids), _ptr(out.position_ids),
+                                   _ptr(out.row_to_req), _ptr(out.row_seq), _ptr(out.row_ctx), _ptr(out.last_row),
+                                   total_rows, _stream()))
+    return out
+
+
+class PagedKVCache:
+    """The Paged KVCacheStrategy on a device page pool (src/kvcache/paged.zig:305-1139).
+
+    updateAndFetch becomes reserve() + append(): pages are written in place and attention reads
+    them in place; gather() returns the contiguous view for tests.
+    """
+
+    def __init__(self, n_layers: int, n_kv_heads: int, head_dim: int, n_pages: int, max_seqs: int,
+                 max_pages_per_seq: int, n_q_heads: int, max_rows: int = 4096, kv_dtype: int = KV_BF16,
+                 page_size: int = 32, attn_scratch_chunks: int = 0):
+        cfg = KvConfig(n_layers, n_kv_heads, head_dim, page_size, n_pages, max_seqs, max_pages_per_seq, kv_dtype,
+                       max_rows, n_q_heads, attn_scratch_chunks)
+        h = C.c_void_p()
+        _lib.check(lib.b200_kv_create(C.byref(cfg), C.byref(h)))
+        self._h = h.value
+        self.cfg = cfg
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib.b200_kv_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    # -- allocator surface --
+    def reset(self):
+        _lib.check(lib.b200_kv_reset(self._h))
+
+    def set_free_order(self, ids: Sequence[int]):
+        arr = (C.c_int32 * len(ids))(*ids)
+        _lib.check(lib.b200_kv_set_free_order(self._h, arr, len(ids)))
+
+    def free_count(self) -> int:
+        out = C.c_int32()
+        _lib.check(lib.b200_kv_free_count(self._h, C.byref(out)))
+        return out.value
+
+    def alloc(self, seq: int, n: int) -> List[int]:
+        out = (C.c_int32 * max(n, 1))()
+        _lib.check(lib.b200_kv_alloc(self._h, seq, n, out))
+        return [out[i] for i in range(n)]
+
+    def release(self, seqs: Sequence[int]):
+        arr = (C.c_int32 * max(len(seqs), 1))(*seqs)
+        _lib.check(lib.b200_kv_release(self._h, arr, len(seqs)))
+
+    def fork(self, src: int, dst: int, n_tokens: int):
+        _lib.check(lib.b200_kv_fork(self._h, src, dst, n_tokens))
+
+    def rollback(self, seq: int, to_len: int):
+        _lib.check(lib.b200_kv_rollback(self._h, seq, to_len))
+
+    def filter(self, keep: Sequence[int]):
+        arr = (C.c_int32 * max(len(keep), 1))(*keep)
+        _lib.check(lib.b200_kv_filter(self._h, arr, len(keep)))
+
+    # -- step surface --
+    def reserve(self, d_desc: torch.Tensor):
+        _lib.check(lib.b200_kv_reserve(self._h, _ptr(d_desc), d_desc.shape[0], _stream()))
+
+    def append(self, layer: int, k_rows: torch.Tensor, v_rows: torch.Tensor):
+        assert k_rows.dtype == torch.bfloat16 and v_rows.dtype == torch.bfloat16
+        _lib.check(lib.b200_kv_append(self._h, layer, _ptr(k_rows), _ptr(v_rows), k_rows.shape[0], _stream()))
+
+    def attention(self, layer: int, q: torch.Tensor, row_seq: torch.Tensor, row_ctx: torch.Tensor,
+                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """b200_paged_attn_decode. q: [T, Hq, D] bf16."""
+        out = out if out is not None else torch.empty_like(q)
+        _lib.check(lib.b200_paged_attn_decode(self._h, layer, _ptr(q), _ptr(row_seq), _ptr(row_ctx), q.shape[0],
+                                              _ptr(out), _stream()))
+        return out
+
+    # -- introspection --
+    def seq_len(self, seq: int) -> int:
+        out = C.c_int32()
+        _lib.check(lib.b200_kv_seq_len(self._h, seq, C.byref(out)))
+        return out.value
+
+    def current_len(self) -> int:
+        out = C.c_int32()
+        _lib.check(lib.b200_kv_current_len(self._h, C.byref(out)))
+        return out.value
+
+    def block_table(self, seq: int) -> List[int]:
+        cap = self.cfg.max_pages_per_seq
+        out = (C.c_int32 * cap)()
+        n = C.c_int32()
+        _lib.check(lib.b200_kv_block_table(self._h, seq, out, cap, C.byref(n)))
+        return [out[i] for i in range(n.value)]
+
+    def ref_counts(self) -> np.ndarray:
+        out = np.zeros(self.cfg.n_pages, np.int32)
+        _lib.check(lib.b200_kv_ref_counts(self._h, out.ctypes.data_as(C.POINTER(C.c_int32)), out.size))
+        return out
+
+    def error_word(self) -> int:
+        out = C.c_int32()
+        _lib.check(lib.b200_kv_error_word(self._h, C.byref(out)))
+        return out.value
+
+    def gather(self, layer: int, seq: int):
+        n = self.seq_len(seq)
+        shape = (max(n, 1), self.cfg.n_kv_heads, self.cfg.head_dim)
+        k = torch.empty(shape, dtype=torch.bfloat16, device="cuda")
+        v = torch.empty_like(k)
+        _lib.check(lib.b200_kv_gather(self._h, layer, seq, _ptr(k), _ptr(v), n, _stream()))
+        return k[:n], v[:n]
+
+    def page_raw(self, layer: int, page: int):
+        c = self.cfg
+        eb = 2 if c.kv_dtype == KV_BF16 else 1
+        nbytes = c.n_kv_heads * c.page_size * c.head_dim * eb
+        k, v = np.zeros(nbytes, np.uint8), np.zeros(nbytes, np.uint8)
+        ks, vs = np.zeros(c.n_kv_heads, np.float32), np.zeros(c.n_kv_heads, np.float32)
+        _lib.check(lib.b200_kv_page_raw(self._h, layer, page, k.ctypes.data, v.ctypes.data,
+                                        ks.ctypes.data_as(C.POINTER(C.c_float)), vs.ctypes.data_as(C.POINTER(C.c_float))))
+        shape = (c.n_kv_heads, c.page_size, c.head_dim)
+        if eb == 2:
+            return k.view(np.uint16).reshape(shape), v.view(np.uint16).reshape(shape), ks, vs
+        return k.reshape(shape), v.reshape(shape), ks, vs
+
+
+def set_attn_pages_per_chunk(n: int):
+    lib.b200_set_attn_pages_per_chunk(n)
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    out = out if out is not None else torch.empty_like(x)
+    _lib.check(lib.b200_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), x.shape[0], x.shape[1], eps, _stream()))
+    return out
+
+
+def rope_(q: torch.Tensor, k: torch.Tensor, positions: torch.Tensor, n_q_heads: int, n_kv_heads: int, head_dim: int,
+          theta: float = 10000.0, q_stride: Optional[int] = None, k_stride: Optional[int] = None):
+    """In-place RoPE on q [T, Hq*D] and k [T, Hkv*D] rows (strides in elements)."""
+    rows = positions.shape[0]
+    q_stride = q_stride if q_stride is not None else n_q_heads * head_dim
+    k_stride = k_stride if k_stride is not None else n_kv_heads * head_dim
+    _lib.check(lib.b200_rope(q.data_ptr(), k.data_ptr(), _ptr(positions), rows, n_q_heads, n_kv_heads, head_dim,
+                             q_stride, k_stride, theta, _stream()))
+
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    rows = ids.shape[0]
+    out = out if out is not None else torch.empty((rows, table.shape[1]), dtype=torch.bfloat16, device=table.device)
+    _lib.check(lib.b200_embed_gather(_ptr(table), _ptr(ids), _ptr(out), rows, table.shape[1], _stream()))
+    return out
+
+
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    out = out if out is not None else torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+    _lib.check(lib.b200_argmax(_ptr(logits), logits.shape[0], logits.shape[1], _ptr(out), _stream()))
+    return out
+
+
+class QWeight:
+    """A quantised weight repacked into the library's tile-major device layout."""
+
+    def __init__(self, mode: int, packed: np.ndarray, scales: np.ndarray, biases: Optional[np.ndarray], n: int, k: int,
+                 n_experts: int = 1):
+        packed = np.ascontiguousarray(packed)
+        scales = np.ascontiguousarray(scales)
+        biases = np.ascontiguousarray(biases) if biases is not None else None
+        h = C.c_void_p()
+        _lib.check(lib.b200_qweight_create(mode, n_experts, n, k, packed.ctypes.data, scales.ctypes.data,
+                                           biases.ctypes.data if biases is not None else None, C.byref(h)))
+        self._h, self.mode, self.n, self.k, self.n_experts = h.value, mode, n, k, n_experts
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            lib.b200_qweight_destroy(self._h)
+            self._h = None
+
+
+def qmm(w: QWeight, x: torch.Tensor, epilogue: int = EPI_NONE, residual: Optional[torch.Tensor] = None,
+        swiglu_limit: float = 0.0, path: int = QMM_AUTO, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """b200_qmm: y = x . dequant(W)^T with a fused epilogue."""
+    rows = x.shape[0]
+    n_out = w.n // 2 if epilogue == EPI_SWIGLU else w.n
+    out = out if out is not None else torch.empty((rows, n_out), dtype=torch.bfloat16, device=x.device)
+    _lib.check(lib.b200_qmm(w._h, _ptr(x), rows, _ptr(out), epilogue, _ptr(residual), swiglu_limit, path, _stream()))
+    return out
+
+
+def qmm_error_word() -> int:
+    out = C.c_int32()
+    _lib.check(lib.b200_qmm_error_word(C.byref(out)))
+    return out.value

@@ -1,0 +1,295 @@
+/*
+ * dmlx_b200.h — C-ABI of the B200-native continuous-batching decode path.
+ *
+ * Plain C99: fixed-width integers, opaque handles, caller-allocated out-arrays with explicit
+ * capacities, no callbacks.  Bound from Zig with @cImport, from C/C++ directly and from Python
+ * with ctypes.  Every entry point names the reference interface it stands in for (path within the
+ * reference project : line).
+ *
+ * Conventions
+ *  - Every function that can fail returns a b200_status; b200_last_error() gives a message for
+ *    the calling thread's last failure.
+ *  - A context (kv pool, model, scheduler ...) is single-owner and not thread-safe, one per GPU per
+ *    process, like the reference's single engine thread.
+ *  - Device pointers are plain `void*`/typed pointers to memory on the current CUDA device; streams
+ *    are passed as `void*` (a cudaStream_t; NULL = the default stream).
+ *  - Conditions detected inside a kernel (pool exhausted, bad index) are reported through an error
+ *    word read after the step (b200_kv_error_word); kernels never trap.
+ *  - There is no CPU fallback: compute entry points return B200_ERR_NO_DEVICE without a GPU.
+ */
+#ifndef DMLX_B200_H
+#define DMLX_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------ */
+/* Status codes: the reference's Zig error set for this path, one to one.                      */
+/* ------------------------------------------------------------------------------------------ */
+typedef int32_t b200_status;
+enum {
+  B200_OK = 0,
+  B200_ERR_INSUFFICIENT_BLOCKS = 1, /* src/kvcache/paged.zig:109,174; src/scheduler.zig:64 */
+  B200_ERR_INVALID_BLOCK_ID = 2,    /* src/kvcache/paged.zig:168,269 */
+  B200_ERR_PAGE_POOL_EXHAUSTED = 3, /* src/kvcache/paged.zig:427 */
+  B200_ERR_INVALID_QUANT_BITS = 4,  /* src/kvcache/paged.zig:355 */
+  B200_ERR_INVALID_BATCH_INDEX = 5, /* src/kvcache/paged.zig:904 */
+  B200_ERR_INVALID_ARGUMENT = 6,
+  B200_ERR_CUDA = 7,
+  B200_ERR_NO_DEVICE = 8,
+  B200_ERR_UNSUPPORTED = 9,         /* src/kvcache/interface.zig:119,136 (FilterNotSupported ...) */
+  B200_ERR_CAPACITY = 10,           /* out-array too small / src/kvcache/quantized.zig:135 CacheOverflow */
+  B200_ERR_DEVICE_FLAGGED = 11      /* a kernel set the error word; see b200_kv_error_word */
+};
+const char* b200_status_name(b200_status s);
+const char* b200_last_error(void);
+/* Library version, and 1 if a CUDA device is usable by this process. */
+int32_t b200_version(void);
+int32_t b200_device_available(void);
+
+/* ========================================================================================== */
+/* HOST LAYER (no GPU needed)                                                                  */
+/* ========================================================================================== */
+
+/* ---- paged.BlockManager: src/kvcache/paged.zig:44-273 ------------------------------------ */
+typedef struct b200_block_manager b200_block_manager;
+b200_block_manager* b200_bm_create(uint64_t total_blocks);                       /* :53-84  init */
+void b200_bm_destroy(b200_block_manager* bm);                                    /* :86-99  deinit */
+int32_t b200_bm_can_allocate(const b200_block_manager* bm, uint64_t n);          /* :102-104 */
+b200_status b200_bm_allocate_blocks(b200_block_manager* bm, uint64_t req_id, uint64_t n,
+                                    uint64_t* out_ids);                          /* :108-137 */
+void b200_bm_free_blocks(b200_block_manager* bm, uint64_t req_id);               /* :142-162 */
+b200_status b200_bm_copy_on_write(b200_block_manager* bm, uint64_t block_id,
+                                  uint64_t* out_id);                             /* :167-206 */
+uint64_t b200_bm_free_count(const b200_block_manager* bm);                       /* :209-211 */
+uint64_t b200_bm_used_count(const b200_block_manager* bm);                       /* :214-216 */
+uint64_t b200_bm_total_blocks(const b200_block_manager* bm);
+uint64_t b200_hash_block(uint64_t prev_hash, const uint32_t* token_ids, uint64_t n); /* :224-230 */
+b200_status b200_bm_find_cached_prefix(b200_block_manager* bm, const uint32_t* token_ids,
+                                       uint64_t n_tokens, uint64_t block_size, uint64_t* out_ids,
+                                       uint64_t cap, uint64_t* out_n);           /* :234-265 */
+b200_status b200_bm_register_block_hash(b200_block_manager* bm, uint64_t block_id,
+                                        uint64_t hash);                          /* :268-272 */
+/* Field access on block_pool.items[i] / req_to_blocks (the reference's tests write these). */
+uint64_t b200_bm_get_ref(const b200_block_manager* bm, uint64_t block_id);       /* :34 ref_count */
+void b200_bm_set_ref(b200_block_manager* bm, uint64_t block_id, uint64_t n);
+int32_t b200_bm_is_used(const b200_block_manager* bm, uint64_t block_id);        /* :33 used */
+uint64_t b200_bm_get_tokens_used(const b200_block_manager* bm, uint64_t block_id); /* :37 */
+void b200_bm_set_tokens_used(b200_block_manager* bm, uint64_t block_id, uint64_t n);
+void b200_bm_share(b200_block_manager* bm, uint64_t req_id, uint64_t block_id);  /* :48 req_to_blocks */
+uint64_t b200_bm_blocks_of(const b200_block_manager* bm, uint64_t req_id, uint64_t* out_ids,
+                           uint64_t cap);
+
+/* ---- Request: src/scheduler.zig:101-187 --------------------------------------------------- */
+enum { B200_REQ_WAITING = 0, B200_REQ_PREFILLING = 1, B200_REQ_DECODING = 2, B200_REQ_DONE = 3 };
+typedef struct b200_request b200_request;
+b200_request* b200_request_create(uint64_t id, const uint32_t* prompt, uint64_t n_prompt,
+                                  uint64_t max_tokens, const uint32_t* stop_tokens,
+                                  uint64_t n_stop);                              /* :123-142 init */
+void b200_request_destroy(b200_request* r);                                      /* :144-147 */
+uint64_t b200_request_id(const b200_request* r);
+int32_t b200_request_state(const b200_request* r);                               /* :112 */
+uint64_t b200_request_prefill_offset(const b200_request* r);                     /* :116 */
+uint64_t b200_request_prompt_len(const b200_request* r);
+uint64_t b200_request_seq_len(const b200_request* r);                            /* :165-167 */
+int32_t b200_request_is_stop_token(const b200_request* r, uint32_t token);       /* :170-175 */
+int32_t b200_request_has_pending_prefill(const b200_request* r);                 /* :178-180 */
+uint64_t b200_request_current_prefill_chunk_len(const b200_request* r, uint64_t max_prefill_tokens); /* :183-186 */
+uint64_t b200_request_generated(const b200_request* r, uint32_t* out, uint64_t cap); /* :111 */
+uint64_t b200_request_block_ids(const b200_request* r, uint64_t* out, uint64_t cap); /* :113 */
+/* The reference's tests construct mid-flight requests by writing the fields. */
+void b200_request_force_state(b200_request* r, int32_t state, uint64_t prefill_offset,
+                              const uint32_t* generated, uint64_t n_generated);
+/* Sequence slot in a device KV pool bound to this request (-1 when none). */
+int32_t b200_request_kv_slot(const b200_request* r);
+
+/* ---- scheduler-side BlockManager: src/scheduler.zig:22-95 --------------------------------- */
+typedef struct b200_sched_bm b200_sched_bm;
+typedef struct b200_kv b200_kv;
+b200_sched_bm* b200_sched_bm_create(uint64_t total_blocks);                      /* :28-34 init */
+b200_sched_bm* b200_sched_bm_create_with_real(b200_block_manager* real);         /* :37-43 initWithReal */
+/* initWithReal against the device page pool: admission takes one page of the pool for a new
+ * sequence slot, completion releases the sequence. */
+b200_sched_bm* b200_sched_bm_create_with_kv(b200_kv* kv);
+void b200_sched_bm_destroy(b200_sched_bm* bm);
+int32_t b200_sched_bm_can_allocate(const b200_sched_bm* bm, uint64_t n);         /* :46-51 */
+uint64_t b200_sched_bm_free_count(const b200_sched_bm* bm);                      /* :89-94 */
+uint64_t b200_sched_bm_total_blocks(const b200_sched_bm* bm);
+uint64_t b200_sched_bm_used_blocks(const b200_sched_bm* bm);
+
+/* ---- Scheduler: src/scheduler.zig:222-387 -------------------------------------------------- */
+typedef struct b200_scheduler b200_scheduler;
+typedef struct b200_token_output { uint64_t request_id; uint32_t token; uint32_t _pad; } b200_token_output; /* :193-196 */
+b200_scheduler* b200_scheduler_create(b200_sched_bm* bm, uint64_t max_prefill_tokens); /* :231-244 */
+void b200_scheduler_destroy(b200_scheduler* s);                                  /* :246-249 */
+b200_status b200_scheduler_add_request(b200_scheduler* s, b200_request* r);      /* :252-255 */
+/* schedule(): fills caller arrays of capacity `cap` each (ScheduleResult, :202-216, :267-315). */
+b200_status b200_scheduler_schedule(b200_scheduler* s, b200_request** prefill_out,
+                                    uint64_t* n_prefill, b200_request** decode_out,
+                                    uint64_t* n_decode, uint64_t cap, uint64_t* blocks_needed);
+b200_status b200_scheduler_postprocess(b200_scheduler* s, const b200_token_output* outputs,
+                                       uint64_t n);                              /* :328-381 */
+uint64_t b200_scheduler_active_count(const b200_scheduler* s);                   /* :384-386 */
+uint64_t b200_scheduler_waiting_count(const b200_scheduler* s);
+uint64_t b200_scheduler_running_count(const b200_scheduler* s);
+
+/* ---- batch_builder: src/batch_builder.zig:24-42, 47-83, 90-214, 253-256 ------------------- */
+/* Host build of the flat batch (prefill requests first, then decode).  `chunked` = 0 reproduces
+ * the reference (a prefilling request contributes all remaining prompt tokens, :50-66); 1 caps it
+ * at its current chunk (src/scheduler.zig:183-186).  The T x T mask is not materialised: it is a
+ * function of cu_seqlens (b200_is_attending); b200_batch_mask writes it out for parity checks. */
+b200_status b200_batch_build(b200_request* const* prefill, uint64_t n_prefill,
+                             b200_request* const* decode, uint64_t n_decode, int32_t chunked,
+                             uint64_t max_prefill_tokens, uint32_t* tokens, int32_t* positions,
+                             int32_t* row_to_req, uint64_t cap_tokens, int32_t* cu_seqlens,
+                             uint64_t* total_tokens, uint64_t* num_requests);
+int32_t b200_is_attending(const int32_t* cu_seqlens, uint64_t num_requests, uint64_t row,
+                          uint64_t col);                                         /* :253-256 */
+b200_status b200_batch_mask(const int32_t* cu_seqlens, uint64_t num_requests, float* mask,
+                            uint64_t total_tokens);                              /* :138-177 */
+/* Greedy sampler on a host logits row: first strict maximum (src/sampling.zig:22-39). */
+uint32_t b200_greedy_host(const float* logits, uint64_t n);
+
+/* ========================================================================================== */
+/* DEVICE LAYER                                                                                */
+/* ========================================================================================== */
+
+/* ---- ragged batch packing on the GPU (replaces src/batch_builder.zig:122-205) ------------- */
+/* One descriptor per request, in batch order. */
+typedef struct b200_pack_desc {
+  int32_t seq_slot;   /* sequence slot in the KV pool */
+  int32_t count;      /* rows this request contributes (prefill chunk length, or 1) */
+  int32_t base_pos;   /* position of its first row (src/batch_builder.zig:159-163) */
+  int32_t src_offset; /* >= 0: offset into `prefill_tokens`; < 0: take last_token[seq_slot] */
+} b200_pack_desc;
+/* Exclusive prefix sum of counts -> cu_seqlens[R+1]; token_ids[T]; position_ids[T];
+ * row_to_req[T]; row_seq[T] (slot per row); row_ctx[T] (= position + 1, the causal context of the
+ * row); last_row[R] (row whose logits are sampled).  All pointers are device pointers. */
+b200_status b200_pack_batch(const b200_pack_desc* d_desc, int32_t n_req,
+                            const uint32_t* d_prefill_tokens, const uint32_t* d_last_token,
+                            int32_t* d_cu_seqlens, uint32_t* d_token_ids, int32_t* d_position_ids,
+                            int32_t* d_row_to_req, int32_t* d_row_seq, int32_t* d_row_ctx,
+                            int32_t* d_last_row, int32_t total_rows, void* stream);
+
+/* ---- Paged KV strategy on a device page pool ----------------------------------------------- */
+/* Stands in for PagedKVCache (src/kvcache/paged.zig:305-1139) behind the KVCacheStrategy vtable
+ * (src/kvcache/interface.zig:31-77), with the page allocator of paged.BlockManager (:44-206)
+ * whose free stack, ref-counts and page tables live in device memory. */
+enum { B200_KV_BF16 = 0, B200_KV_FP8_E4M3 = 1 };
+typedef struct b200_kv_config {
+  int32_t n_layers;
+  int32_t n_kv_heads;        /* LayerConfig.num_kv_heads  src/kvcache/interface.zig:162-169 */
+  int32_t head_dim;          /* LayerConfig.head_dim */
+  int32_t page_size;         /* must be 32: src/kvcache/paged.zig:24 */
+  int32_t n_pages;           /* pool size (BlockManager.total_blocks) */
+  int32_t max_seqs;          /* sequence slots (LayerConfig.batch_size) */
+  int32_t max_pages_per_seq; /* ceil(LayerConfig.max_seq_len / page_size) */
+  int32_t kv_dtype;          /* B200_KV_BF16 | B200_KV_FP8_E4M3 (one f32 scale per page and kv head) */
+  int32_t max_rows;          /* largest packed batch (rows) a step may carry */
+  int32_t n_q_heads;         /* LayerConfig.num_heads (sizes the split-K scratch) */
+  int32_t attn_scratch_chunks; /* split-K partial slots; 0 = n_pages/4 + max_rows + 8 */
+} b200_kv_config;
+b200_status b200_kv_create(const b200_kv_config* cfg, b200_kv** out);            /* :342-411 init, :1141-1186 factories */
+void b200_kv_destroy(b200_kv* kv);                                               /* :1111-1138 deinit */
+/* Pool size and number of sequence slots of a pool. */
+b200_status b200_kv_dims(const b200_kv* kv, int32_t* n_pages, int32_t* max_seqs);
+b200_status b200_kv_reset(b200_kv* kv);                                          /* :851-862 reset */
+/* Install the order in which free pages will be popped (ids[0] first).  Default: 0,1,2,... */
+b200_status b200_kv_set_free_order(b200_kv* kv, const int32_t* ids, int32_t n);
+b200_status b200_kv_free_count(b200_kv* kv, int32_t* out);                       /* BlockManager.freeCount :209 */
+/* allocateBlocks for one sequence slot (synchronous; used at admission). */
+b200_status b200_kv_alloc(b200_kv* kv, int32_t seq, int32_t n, int32_t* out_ids); /* :108-137 */
+/* freeBlocks for `n` sequence slots, in order. */
+b200_status b200_kv_release(b200_kv* kv, const int32_t* seqs, int32_t n);        /* :142-162 */
+/* Share the pages covering the first n_tokens of `src` with the empty slot `dst` (ref_count += 1,
+ * the effect of findCachedPrefix :247-256). */
+b200_status b200_kv_fork(b200_kv* kv, int32_t src, int32_t dst, int32_t n_tokens);
+b200_status b200_kv_rollback(b200_kv* kv, int32_t seq, int32_t to_len);          /* :864-877 */
+/* filter: keep only the listed slots, release the rest (:879-945). */
+b200_status b200_kv_filter(b200_kv* kv, const int32_t* keep, int32_t n_keep);
+/* Step part 1 (device, asynchronous): grow page tables for a packed batch — per request, in
+ * order: copy-on-write of a shared partially-filled last page (:167-206), then
+ * ceil((len+count)/32) - held new pages (:525-531) — and build the page-touch work list for
+ * append; the queued copy-on-write page copies (:186-200) are applied to every layer before it
+ * returns control to the stream.  d_desc is the same array given to b200_pack_batch; a sequence
+ * slot may appear at most once per step and n_req <= 4096. */
+b200_status b200_kv_reserve(b200_kv* kv, const b200_pack_desc* d_desc, int32_t n_req, void* stream);
+/* Step part 2: write K/V rows [T, n_kv_heads, head_dim] (bf16) of one layer into their pages
+ * (:533-637).  K rows are expected already rotated, as updateAndFetch receives them. */
+b200_status b200_kv_append(b200_kv* kv, int32_t layer, const void* d_k_rows, const void* d_v_rows,
+                           int32_t total_rows, void* stream);
+/* Introspection for bit-exact checks (synchronous). */
+b200_status b200_kv_seq_len(b200_kv* kv, int32_t seq, int32_t* out_len);         /* :485-488 */
+b200_status b200_kv_current_len(b200_kv* kv, int32_t* out_len);                  /* :842-849 currentLen */
+b200_status b200_kv_block_table(b200_kv* kv, int32_t seq, int32_t* out_ids, int32_t cap,
+                                int32_t* out_n_pages);
+b200_status b200_kv_ref_counts(b200_kv* kv, int32_t* out, int32_t cap);
+/* Reads and clears the device error word: 0, or a b200_status set by a kernel. */
+b200_status b200_kv_error_word(b200_kv* kv, int32_t* out);
+/* Tests only: the contiguous [len, n_kv_heads, head_dim] bf16 view updateAndFetch would return
+ * (:705-802); FP8 pages are dequantised. */
+b200_status b200_kv_gather(b200_kv* kv, int32_t layer, int32_t seq, void* d_k_out, void* d_v_out,
+                           int32_t cap_rows, void* stream);
+/* Raw E4M3 codes and scales of one page (FP8 pools; bit-exact checks). */
+b200_status b200_kv_page_raw(b200_kv* kv, int32_t layer, int32_t page, void* h_k, void* h_v,
+                             float* h_k_scales, float* h_v_scales);
+
+/* ---- split-K GQA paged-attention decode ----------------------------------------------------- */
+/* Replaces gather + repeatHeads + softmax(QK^T/sqrt(D))V (src/kvcache/paged.zig:705-802,
+ * src/models/llama.zig:231-270,303-323).  q, out: [T, n_q_heads, head_dim] bf16; row r attends to
+ * the first d_row_ctx[r] cached tokens of slot d_row_seq[r]. */
+b200_status b200_paged_attn_decode(b200_kv* kv, int32_t layer, const void* d_q,
+                                   const int32_t* d_row_seq, const int32_t* d_row_ctx,
+                                   int32_t total_rows, void* d_out, void* stream);
+
+/* Tuning hook with no reference counterpart: pages per split-K chunk (4..32, default 8). */
+void b200_set_attn_pages_per_chunk(int32_t n);
+
+/* ---- elementwise pieces of the layer (src/models/llama.zig) -------------------------------- */
+b200_status b200_rmsnorm(const void* d_x, const void* d_weight, void* d_out, int32_t rows,
+                         int32_t hidden, float eps, void* stream);                /* :462,473,592 */
+/* In-place non-traditional RoPE on q [T,Hq,D] and k [T,Hkv,D] with per-row positions (:213-215). */
+b200_status b200_rope(void* d_q, void* d_k, const int32_t* d_positions, int32_t rows,
+                      int32_t n_q_heads, int32_t n_kv_heads, int32_t head_dim, int32_t q_stride,
+                      int32_t k_stride, float theta, void* stream);
+b200_status b200_embed_gather(const void* d_table, const uint32_t* d_ids, void* d_out, int32_t rows,
+                              int32_t hidden, void* stream);                      /* :566 */
+/* Greedy: first strict maximum per row of bf16 logits [rows, vocab] (src/sampling.zig:22-39). */
+b200_status b200_argmax(const void* d_logits, int32_t rows, int32_t vocab, uint32_t* d_out,
+                        void* stream);
+
+/* ---- dequant-fused quantised matmul --------------------------------------------------------- */
+/* y[T,N] = x[T,K] . dequant(W[N,K])^T  (quantizedMatmul call sites src/models/llama.zig:127,367,596;
+ * gatherQmm src/models/deepseek_v4.zig:976).  Weights are repacked once into a tile-major device
+ * layout; the handle owns that memory. */
+enum { B200_Q_AFFINE4_G64 = 0, B200_Q_MXFP4_G32 = 1 };
+typedef struct b200_qweight b200_qweight;
+/* affine: packed uint32 [N, K/8] (8 nibbles per word, least significant first), scales and biases
+ * bf16 [N, K/64]  (src/kvcache/paged.zig:358,1199-1208; src/models/llama_loader.zig:262-279).
+ * mxfp4: packed uint8 [N, K/2] (low nibble = even element), E8M0 scales uint8 [N, K/32], no
+ * biases (src/models/deepseek_v4_loader.zig:121-122,839-920).  Host pointers.
+ * n_experts > 1 stacks [E, N, K] for grouped use. */
+b200_status b200_qweight_create(int32_t mode, int32_t n_experts, int32_t n, int32_t k,
+                                const void* h_packed, const void* h_scales, const void* h_biases,
+                                b200_qweight** out);
+void b200_qweight_destroy(b200_qweight* w);
+enum { B200_EPI_NONE = 0, B200_EPI_RESIDUAL = 1, B200_EPI_SWIGLU = 2 };
+enum { B200_QMM_AUTO = 0, B200_QMM_SIMT = 1, B200_QMM_TCGEN05 = 2 };
+/* epilogue NONE: y = xW^T.  RESIDUAL: y = residual + xW^T.  SWIGLU: W holds gate and up rows
+ * interleaved (row 2i = gate_i, 2i+1 = up_i); y[T, N/2] = silu(min(g,L)) * clip(u,+-L) with
+ * L = swiglu_limit (0 = unclipped)  (src/models/llama.zig:396-415; deepseek_v4.zig:947-966). */
+b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y,
+                     int32_t epilogue, const void* d_residual, float swiglu_limit, int32_t path,
+                     void* stream);
+
+/* Reads and clears the matmul kernels' error word (set when a bounded wait ran out). */
+b200_status b200_qmm_error_word(int32_t* out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DMLX_B200_H */

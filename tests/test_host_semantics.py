@@ -352,7 +352,7 @@ def test_scheduler_with_real_block_manager(H):  # scheduler.zig:37-43 initWithRe
     s.postprocess([(1, 5), (2, 6)])
     assert real.free_count() == 2
     res = s.schedule()
-    assert [r.id for r in res.prefill_requests] == [3] and list(reqs[2].block_ids) == [0]
+    assert [r.id for r in res.prefill_requests] == [3] and list(reqs[2].block_ids) == [1]  # LIFO: last freed first
 
 
 def test_greedy_first_strict_max(H):  # sampling.zig:22-39
