@@ -1,0 +1,130 @@
+"""GPU parity: split-K GQA paged-attention decode against the per-request oracle
+(softmax(q k^T / sqrt(D)) v over the request's own cached rows, src/models/llama.zig:231-270).
+
+Tolerance (bf16 outputs): max |diff| / max |ref| <= 2e-2 and cosine >= 0.9995."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_math
+
+pytestmark = pytest.mark.gpu
+
+REL_TOL, COS_TOL = 2e-2, 0.9995
+
+
+def _close(got, want):
+    g, w = got.astype(np.float64).reshape(-1), want.astype(np.float64).reshape(-1)
+    rel = np.abs(g - w).max() / max(np.abs(w).max(), 1e-30)
+    cos = g @ w / (np.linalg.norm(g) * np.linalg.norm(w) + 1e-30)
+    return rel, cos
+
+
+def _run_case(ctxs, hq, hkv, d, kv_dtype, seed, scatter=True, pages_per_chunk=8):
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(seed)
+    n = len(ctxs)
+    pages = sum(-(-c // 32) for c in ctxs)
+    n_pages = int(pages * 1.25) + 2
+    kv = dev.PagedKVCache(1, hkv, d, n_pages, n, max(-(-max(ctxs) // 32), 1), hq, max_rows=max(sum(ctxs), n, 1),
+                          kv_dtype=kv_dtype)
+    dev.set_attn_pages_per_chunk(pages_per_chunk)
+    if scatter:
+        kv.set_free_order(rng.permutation(n_pages).tolist())
+    k = ref_math.bf16_round(rng.normal(0, 1, (sum(ctxs), hkv, d)).astype(np.float32))
+    v = ref_math.bf16_round(rng.normal(0, 1, (sum(ctxs), hkv, d)).astype(np.float32))
+    q = ref_math.bf16_round((rng.normal(0, 1, (n, hq, d)) / np.sqrt(d)).astype(np.float32) * np.sqrt(d))
+    desc = dev.pack_desc_array([(s, c, 0, -1) for s, c in enumerate(ctxs)]).cuda()
+    kv.reserve(desc)
+    kv.append(0, torch.tensor(k, device="cuda").bfloat16(), torch.tensor(v, device="cuda").bfloat16())
+    row_seq = torch.arange(n, dtype=torch.int32, device="cuda")
+    row_ctx = torch.tensor(ctxs, dtype=torch.int32, device="cuda")
+    out = kv.attention(0, torch.tensor(q, device="cuda").bfloat16(), row_seq, row_ctx)
+    torch.cuda.synchronize()
+    assert kv.error_word() == 0
+    got = out.float().cpu().numpy()
+    if kv_dtype == dev.KV_FP8_E4M3:
+        # the oracle for FP8 pools reads what the pool holds: decode(codes) * scale
+        kk, vv = [], []
+        for s in range(n):
+            a, b = kv.gather(0, s)
+            kk.append(a.float().cpu().numpy())
+            vv.append(b.float().cpu().numpy())
+        k_eff, v_eff = np.concatenate(kk) if sum(ctxs) else k, np.concatenate(vv) if sum(ctxs) else v
+    else:
+        k_eff, v_eff = k, v
+    off = 0
+    want = np.zeros_like(got)
+    for s, c in enumerate(ctxs):
+        if c > 0:
+            want[s] = ref_math.gqa_attention_decode(q[s], k_eff[off : off + c], v_eff[off : off + c])
+        off += c
+    kv.close()
+    return got, want, (k, v, q)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("kv_dtype", [0, 1])
+def test_ragged_contexts(d, kv_dtype):
+    ctxs = [1, 31, 32, 33, 64, 65, 200, 257, 700, 5, 1023, 96]
+    hq, hkv = (8, 2) if d == 64 else (32, 8)
+    got, want, _ = _run_case(ctxs, hq, hkv, d, kv_dtype, seed=7 + d + kv_dtype)
+    rel, cos = _close(got, want)
+    assert rel <= REL_TOL and cos >= COS_TOL, (rel, cos)
+    for s in range(len(ctxs)):  # every row on its own, so a short context cannot hide behind a long one
+        r, c = _close(got[s], want[s])
+        assert r <= REL_TOL and c >= COS_TOL, (s, ctxs[s], r, c)
+
+
+def test_fp8_close_to_bf16_oracle():
+    """FP8 pools against the bf16 (unquantised) oracle: the quantisation error itself stays inside
+    the tolerance the north-star states for bf16 outputs."""
+    from dmlx_b200 import device as dev
+
+    ctxs = [300, 1024, 77]
+    got, _, (k, v, q) = _run_case(ctxs, 32, 8, 128, dev.KV_FP8_E4M3, seed=99)
+    off = 0
+    for s, c in enumerate(ctxs):
+        want = ref_math.gqa_attention_decode(q[s], k[off : off + c], v[off : off + c])
+        rel, cos = _close(got[s], want)
+        assert rel <= 6e-2 and cos >= 0.998, (s, rel, cos)  # E4M3 carries 3 mantissa bits
+        off += c
+
+
+@pytest.mark.parametrize("ppc", [4, 8, 32])
+def test_split_sizes_agree(ppc):
+    got, want, _ = _run_case([2000, 40, 513], 32, 8, 128, 0, seed=5, pages_per_chunk=ppc)
+    rel, cos = _close(got, want)
+    assert rel <= REL_TOL and cos >= COS_TOL
+
+
+def test_empty_context_row_is_zero():
+    got, want, _ = _run_case([0, 40], 8, 2, 64, 0, seed=3)
+    assert np.all(got[0] == 0)
+    rel, cos = _close(got[1], want[1])
+    assert rel <= REL_TOL and cos >= COS_TOL
+
+
+def test_prefill_rows_as_causal_decode_rows():
+    """A prefill chunk is served by giving each row its causal context (position + 1): row r of a
+    request sees only its first r+1 tokens — the block-diagonal causal mask of
+    src/batch_builder.zig:168-177 without materialising it."""
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(21)
+    hq, hkv, d, n_tok = 8, 2, 64, 70
+    kv = dev.PagedKVCache(1, hkv, d, 8, 1, 4, hq, max_rows=128, attn_scratch_chunks=256)
+    k = ref_math.bf16_round(rng.normal(0, 1, (n_tok, hkv, d)).astype(np.float32))
+    v = ref_math.bf16_round(rng.normal(0, 1, (n_tok, hkv, d)).astype(np.float32))
+    q = ref_math.bf16_round(rng.normal(0, 1, (n_tok, hq, d)).astype(np.float32))
+    kv.reserve(dev.pack_desc_array([(0, n_tok, 0, -1)]).cuda())
+    kv.append(0, torch.tensor(k, device="cuda").bfloat16(), torch.tensor(v, device="cuda").bfloat16())
+    row_seq = torch.zeros(n_tok, dtype=torch.int32, device="cuda")
+    row_ctx = torch.arange(1, n_tok + 1, dtype=torch.int32, device="cuda")
+    got = kv.attention(0, torch.tensor(q, device="cuda").bfloat16(), row_seq, row_ctx).float().cpu().numpy()
+    assert kv.error_word() == 0
+    for r in range(n_tok):
+        want = ref_math.gqa_attention_decode(q[r], k[: r + 1], v[: r + 1])
+        rel, cos = _close(got[r], want)
+        assert rel <= REL_TOL and cos >= COS_TOL, (r, rel, cos)

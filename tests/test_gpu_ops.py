@@ -1,0 +1,182 @@
+"""GPU parity: row-wise ops and the dequant-fused quantised matmuls against the CPU oracle.
+
+bf16 tolerance: max |diff| / max |ref| <= 2e-2 and cosine >= 0.9995 (tighter where the op allows)."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_host, ref_math
+
+pytestmark = pytest.mark.gpu
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def _load(name):
+    meta = json.load(open(os.path.join(G, name + ".bin.json")))
+    dt = {"float32": "<f4", "int32": "<i4"}[meta["dtype"]]
+    return np.fromfile(os.path.join(G, name + ".bin"), dtype=dt).reshape(meta["shape"])
+
+
+def _close(got, want):
+    g, w = np.asarray(got, np.float64).reshape(-1), np.asarray(want, np.float64).reshape(-1)
+    rel = np.abs(g - w).max() / max(np.abs(w).max(), 1e-30)
+    cos = g @ w / (np.linalg.norm(g) * np.linalg.norm(w) + 1e-30)
+    return rel, cos
+
+
+def _bf(x):
+    return torch.tensor(np.asarray(x, np.float32), device="cuda").bfloat16()
+
+
+def test_rmsnorm_golden_and_random():
+    from dmlx_b200 import device as dev
+
+    x = _load("rmsnorm_input").reshape(-1, 8)  # reference KAT (tests/generate_golden.py:62-72), bf16 I/O
+    got = dev.rmsnorm(_bf(x), _bf(np.ones(8)), 1e-5).float().cpu().numpy()
+    rel, cos = _close(got, _load("rmsnorm_output").reshape(-1, 8))
+    assert rel <= 1e-2 and cos >= 0.9999
+    rng = np.random.default_rng(1)
+    x = ref_math.bf16_round(rng.normal(0, 2, (37, 4096)))
+    w = ref_math.bf16_round(rng.normal(1, 0.1, 4096))
+    got = dev.rmsnorm(_bf(x), _bf(w), 1e-5).float().cpu().numpy()
+    rel, cos = _close(got, ref_math.rms_norm(x, w, 1e-5))
+    assert rel <= 1e-2 and cos >= 0.99999
+
+
+def test_rope_golden_and_positions():
+    from dmlx_b200 import device as dev
+
+    x = _load("rope_input")  # (1,2,4,8): 2 heads, positions 0..3 (tests/generate_golden.py:75-83)
+    rows = np.ascontiguousarray(x[0].transpose(1, 0, 2)).reshape(4, 16)  # [S, H*D]
+    q = _bf(rows)
+    k = _bf(rows[:, :8])
+    dev.rope_(q, k, torch.arange(4, dtype=torch.int32, device="cuda"), 2, 1, 8)
+    want = _load("rope_output")[0].transpose(1, 0, 2).reshape(4, 16)
+    rel, cos = _close(q.float().cpu().numpy(), want)
+    assert rel <= 1e-2 and cos >= 0.9999
+    rel, cos = _close(k.float().cpu().numpy(), want[:, :8])
+    assert rel <= 1e-2 and cos >= 0.9999
+    rng = np.random.default_rng(2)
+    pos = rng.integers(0, 32768, 19).astype(np.int32)
+    xq = ref_math.bf16_round(rng.normal(0, 1, (19, 32, 128)))
+    xk = ref_math.bf16_round(rng.normal(0, 1, (19, 8, 128)))
+    q, k = _bf(xq.reshape(19, -1)), _bf(xk.reshape(19, -1))
+    dev.rope_(q, k, torch.tensor(pos, device="cuda"), 32, 8, 128, theta=10000.0)
+    wq = ref_math.rope(xq.transpose(1, 0, 2), pos).transpose(1, 0, 2)
+    wk = ref_math.rope(xk.transpose(1, 0, 2), pos).transpose(1, 0, 2)
+    for got, want in ((q, wq), (k, wk)):
+        rel, cos = _close(got.float().cpu().numpy(), want.reshape(19, -1))
+        assert rel <= 1e-2 and cos >= 0.9999
+
+
+def test_embedding_golden():
+    from dmlx_b200 import device as dev
+
+    w = np.zeros((8, 8), np.float32)
+    w[:, :4] = _load("embedding_weight")  # hidden padded to the 16-byte vector the kernel moves
+    ids = torch.tensor(_load("embedding_indices"), dtype=torch.int32, device="cuda")
+    got = dev.embed_gather(_bf(w), ids).float().cpu().numpy()[:, :4]
+    assert np.array_equal(got, ref_math.bf16_round(_load("embedding_output")))
+
+
+def test_argmax_first_strict_max():
+    """Ties resolve to the smaller index (src/sampling.zig:30-36)."""
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(3)
+    logits = ref_math.bf16_round(rng.normal(0, 1, (9, 32000)))
+    logits[0, 777] = logits[0, 31000] = 9.0
+    logits[1, 0] = 9.0
+    logits[2, 31999] = 9.0
+    got = dev.argmax(_bf(logits)).cpu().numpy()
+    assert got.tolist() == [ref_host.greedy(r) for r in logits]
+    assert got[0] == 777
+
+
+def _affine_weight(rng, n, k):
+    w = rng.normal(0, 0.02, (n, k)).astype(np.float32)
+    packed, s, b = ref_math.quantize_affine4(w)
+    to_bits = lambda a: (a.astype(np.float32).view(np.uint32) >> 16).astype(np.uint16)  # exact: already bf16 values
+    return packed, s, b, to_bits(s), to_bits(b)
+
+
+def _mxfp4_weight(rng, n, k):
+    packed = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    scales = rng.integers(118, 124, (n, k // 32), dtype=np.uint8)
+    return packed, scales
+
+
+@pytest.mark.parametrize("path", [1, 2])  # SIMT GEMV, tcgen05
+@pytest.mark.parametrize("rows,n,k", [(1, 256, 512), (3, 384, 1408), (16, 768, 512), (33, 128, 4096), (130, 512, 1024)])
+def test_qmm_affine4(path, rows, n, k):
+    from dmlx_b200 import device as dev
+
+    if path == 1 and rows > 16:
+        pytest.skip("the GEMV kernel is the small-batch path")
+    rng = np.random.default_rng(rows * 1000 + n + k)
+    packed, s, b, sb, bb = _affine_weight(rng, n, k)
+    w = dev.QWeight(dev.Q_AFFINE4_G64, packed, sb, bb, n, k)
+    x = ref_math.bf16_round(rng.normal(0, 1, (rows, k)))
+    got = dev.qmm(w, _bf(x), path=path).float().cpu().numpy()
+    assert dev.qmm_error_word() == 0
+    want = ref_math.qmm(x, ref_math.dequantize_affine4(packed, s, b))
+    rel, cos = _close(got, want)
+    assert rel <= 2e-2 and cos >= 0.9995, (rel, cos)
+
+
+@pytest.mark.parametrize("path", [1, 2])
+@pytest.mark.parametrize("rows,n,k", [(2, 256, 512), (24, 384, 2048), (100, 256, 4096)])
+def test_qmm_mxfp4(path, rows, n, k):
+    from dmlx_b200 import device as dev
+
+    if path == 1 and rows > 16:
+        pytest.skip("the GEMV kernel is the small-batch path")
+    rng = np.random.default_rng(rows + n + k)
+    packed, scales = _mxfp4_weight(rng, n, k)
+    w = dev.QWeight(dev.Q_MXFP4_G32, packed, scales, None, n, k)
+    x = ref_math.bf16_round(rng.normal(0, 1, (rows, k)))
+    got = dev.qmm(w, _bf(x), path=path).float().cpu().numpy()
+    assert dev.qmm_error_word() == 0
+    want = ref_math.qmm(x, ref_math.dequantize_mxfp4(packed, scales))
+    rel, cos = _close(got, want)
+    assert rel <= 2e-2 and cos >= 0.9995, (rel, cos)
+
+
+@pytest.mark.parametrize("path", [1, 2])
+def test_qmm_epilogues(path):
+    """Residual add (src/models/llama.zig:466,477) and SwiGLU over interleaved gate/up rows
+    (src/models/llama.zig:396-415; clipped form src/models/deepseek_v4.zig:947-966)."""
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(77)
+    rows, n, k = 5, 256, 512
+    packed, s, b, sb, bb = _affine_weight(rng, n, k)
+    w = dev.QWeight(dev.Q_AFFINE4_G64, packed, sb, bb, n, k)
+    x = ref_math.bf16_round(rng.normal(0, 1, (rows, k)))
+    res = ref_math.bf16_round(rng.normal(0, 1, (rows, n)))
+    base = ref_math.qmm(x, ref_math.dequantize_affine4(packed, s, b))
+    got = dev.qmm(w, _bf(x), dev.EPI_RESIDUAL, residual=_bf(res), path=path).float().cpu().numpy()
+    rel, cos = _close(got, base + res)
+    assert rel <= 2e-2 and cos >= 0.9995
+    for limit in (0.0, 0.05):
+        got = dev.qmm(w, _bf(x), dev.EPI_SWIGLU, swiglu_limit=limit, path=path).float().cpu().numpy()
+        want = ref_math.limited_swiglu(base[:, 0::2].astype(np.float64), base[:, 1::2].astype(np.float64), limit)
+        rel, cos = _close(got, want)
+        assert got.shape == (rows, n // 2) and rel <= 2e-2 and cos >= 0.9995, (limit, rel, cos)
+
+
+def test_qmm_paths_agree_and_are_deterministic():
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(5)
+    rows, n, k = 8, 512, 2048
+    packed, s, b, sb, bb = _affine_weight(rng, n, k)
+    w = dev.QWeight(dev.Q_AFFINE4_G64, packed, sb, bb, n, k)
+    x = _bf(ref_math.bf16_round(rng.normal(0, 1, (rows, k))))
+    a1, a2 = dev.qmm(w, x, path=2), dev.qmm(w, x, path=2)
+    assert torch.equal(a1, a2)  # split-K partials are summed in a fixed order
+    rel, cos = _close(dev.qmm(w, x, path=1).float().cpu().numpy(), a1.float().cpu().numpy())
+    assert rel <= 1e-2 and cos >= 0.9999

@@ -1,0 +1,244 @@
+"""GPU parity: ragged packing and the device page pool, bit-exact against the integer oracle.
+
+All calls go through the C-ABI (dmlx_b200.device is a ctypes shim)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_host, ref_math
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    from dmlx_b200 import device
+
+    return device
+
+
+def _desc(dev, rows):
+    return dev.pack_desc_array(rows).cuda(non_blocking=True)
+
+
+def test_pack_matches_batch_builder():
+    """cu_seqlens / positions / tokens equal batch_builder.build on the same schedule
+    (src/batch_builder.zig:90-214); 50 random mixed prefill+decode schedules."""
+    dev = _dev()
+    rng = np.random.default_rng(101)
+    for _ in range(50):
+        n_pre, n_dec = int(rng.integers(0, 5)), int(rng.integers(0, 9))
+        if n_pre + n_dec == 0:
+            n_dec = 1
+        pre, dec, descs, flat = [], [], [], []
+        last_token = np.zeros(64, np.uint32)
+        slot = 0
+        for i in range(n_pre):
+            prompt = rng.integers(0, 32000, int(rng.integers(1, 40))).tolist()
+            off = int(rng.integers(0, len(prompt)))
+            r = ref_host.Request(i, prompt, 10)
+            r.force_state(ref_host.PREFILLING, off, [])
+            pre.append(r)
+            descs.append((slot, len(prompt) - off, off, len(flat)))
+            flat.extend(prompt[off:])
+            slot += 1
+        for i in range(n_dec):
+            prompt = rng.integers(0, 32000, int(rng.integers(1, 40))).tolist()
+            gen = rng.integers(0, 32000, int(rng.integers(1, 6))).tolist()
+            r = ref_host.Request(100 + i, prompt, 10)
+            r.force_state(ref_host.DECODING, len(prompt), gen)
+            dec.append(r)
+            last_token[slot] = gen[-1]
+            descs.append((slot, 1, len(prompt) + len(gen) - 1, -1))
+            slot += 1
+        want = ref_host.build_batch(ref_host.ScheduleResult(pre, dec, 0), with_mask=False)
+        d_flat = torch.tensor(np.array(flat + [0], np.int64).astype(np.int32), device="cuda")
+        d_last = torch.tensor(last_token.astype(np.int32), device="cuda")
+        got = dev.pack_batch(_desc(dev, descs), want.total_tokens, d_flat, d_last)
+        t = want.total_tokens
+        assert got.cu_seqlens.cpu().numpy().tolist() == want.cu_seqlens.tolist()
+        assert got.token_ids[:t].cpu().numpy().astype(np.uint32).tolist() == want.batched_tokens.tolist()
+        assert got.position_ids[:t].cpu().numpy().tolist() == want.position_ids.tolist()
+        assert got.row_to_req[:t].cpu().numpy().tolist() == want.row_to_req.tolist()
+        assert got.row_ctx[:t].cpu().numpy().tolist() == (want.position_ids + 1).tolist()
+        assert got.last_row.cpu().numpy()[: len(descs)].tolist() == (want.cu_seqlens[1:] - 1).tolist()
+
+
+def _check_tables(kv, ref, n_seqs):
+    assert kv.free_count() == ref.free_count()
+    for s in range(n_seqs):
+        assert kv.block_table(s) == ref.tables[s], f"seq {s}"
+        assert kv.seq_len(s) == ref.lens[s]
+    assert kv.ref_counts().tolist() == ref.ref
+
+
+def test_pool_random_workload_bit_exact():
+    """Block tables, ref-counts and free count follow the LIFO allocator of paged.BlockManager
+    (src/kvcache/paged.zig:61-73,116-118,142-162,167-206) through random multi-step workloads with
+    growth, release, prefix fork + copy-on-write and rollback."""
+    dev = _dev()
+    rng = np.random.default_rng(202)
+    for trial in range(6):
+        n_pages, n_seqs = int(rng.integers(40, 200)), 12
+        kv = dev.PagedKVCache(1, 2, 64, n_pages, n_seqs, 64, 8, max_rows=4096)
+        ref = ref_host.PagedKVTables(n_pages, n_seqs)
+        if trial % 2 == 1:  # scattered pool: random pop order
+            order = rng.permutation(n_pages).tolist()
+            kv.set_free_order(order)
+            ref.free = order[::-1]
+        live = set()
+        for step in range(60):
+            op = rng.random()
+            if op < 0.55:
+                seqs = [s for s in rng.permutation(n_seqs)[: int(rng.integers(1, 7))].tolist()]
+                counts = [int(rng.integers(1, 70)) if s not in live else int(rng.integers(1, 4)) for s in seqs]
+                counts = [min(c, 64 * 32 - ref.lens[s]) for s, c in zip(seqs, counts)]
+                try:
+                    ref.reserve(seqs, counts)
+                    expect_err = 0
+                except ref_host.InsufficientBlocks:
+                    expect_err = 1
+                kv.reserve(_desc(dev, [(s, c, 0, -1) for s, c in zip(seqs, counts)]))
+                assert kv.error_word() == expect_err
+                if not expect_err:
+                    live.update(seqs)
+            elif op < 0.7 and live:
+                s = int(rng.choice(sorted(live)))
+                ref.release(s)
+                kv.release([s])
+                live.discard(s)
+            elif op < 0.85 and live:
+                free_slots = [s for s in range(n_seqs) if s not in live and not ref.tables[s]]
+                src = int(rng.choice(sorted(live)))
+                if free_slots and ref.lens[src] > 0:
+                    dst, nt = free_slots[0], int(rng.integers(1, ref.lens[src] + 1))
+                    ref.fork(src, dst, nt)
+                    kv.fork(src, dst, nt)
+                    live.add(dst)
+            elif live:
+                s = int(rng.choice(sorted(live)))
+                to = int(rng.integers(0, ref.lens[s] + 1))
+                ref.rollback(s, to)
+                kv.rollback(s, to)
+            _check_tables(kv, ref, n_seqs)
+        kv.close()
+
+
+def test_cow_two_sharers_same_step():
+    """Two sequences that share a partially filled page and both append in one step: the first
+    (in batch order) takes a private copy, the second keeps the original (paged.zig:167-206)."""
+    dev = _dev()
+    kv = dev.PagedKVCache(2, 2, 64, 16, 4, 8, 8)
+    ref = ref_host.PagedKVTables(16, 4)
+    rows = torch.randn(40, 2, 64, device="cuda").bfloat16()
+    for layer in range(2):
+        pass
+    kv.reserve(_desc(dev, [(0, 40, 0, -1)]))
+    for layer in range(2):
+        kv.append(layer, rows, rows * 2)
+    ref.reserve([0], [40])
+    kv.fork(0, 1, 40)
+    ref.fork(0, 1, 40)
+    new = torch.randn(2, 2, 64, device="cuda").bfloat16()
+    kv.reserve(_desc(dev, [(0, 1, 40, -1), (1, 1, 40, -1)]))
+    for layer in range(2):
+        kv.append(layer, new, new)
+    ref.reserve([0, 1], [1, 1])
+    assert kv.error_word() == 0
+    _check_tables(kv, ref, 4)
+    assert ref.cow_log == [(1, 2)]
+    for layer in range(2):
+        k0, v0 = kv.gather(layer, 0)
+        k1, v1 = kv.gather(layer, 1)
+        assert torch.equal(k0[:40], rows) and torch.equal(k1[:40], rows)  # the copy carried the data
+        assert torch.equal(v0[:40], rows * 2) and torch.equal(v1[:40], rows * 2)
+        assert torch.equal(k0[40], new[0]) and torch.equal(k1[40], new[1])
+
+
+def test_append_gather_roundtrip_bf16():
+    """append then gather returns exactly the rows written, in order (updateAndFetch's contiguous
+    view, src/kvcache/paged.zig:533-637,705-802), for ragged multi-request steps over a scattered pool."""
+    dev = _dev()
+    rng = np.random.default_rng(303)
+    kv = dev.PagedKVCache(2, 2, 128, 64, 4, 16, 8)
+    kv.set_free_order(rng.permutation(64).tolist())
+    want = {s: [] for s in range(4)}
+    for step in range(5):
+        seqs = [0, 1, 2, 3][: int(rng.integers(1, 5))]
+        counts = [int(rng.integers(1, 45)) for _ in seqs]
+        total = sum(counts)
+        base = [kv.seq_len(s) for s in seqs]
+        kv.reserve(_desc(dev, [(s, c, b, -1) for s, c, b in zip(seqs, counts, base)]))
+        k = torch.randn(total, 2, 128, device="cuda").bfloat16()
+        v = torch.randn(total, 2, 128, device="cuda").bfloat16()
+        for layer in range(2):
+            kv.append(layer, k + layer, v - layer)
+        off = 0
+        for s, c in zip(seqs, counts):
+            want[s].append((k[off : off + c], v[off : off + c]))
+            off += c
+    assert kv.error_word() == 0
+    for s in range(4):
+        if not want[s]:
+            continue
+        kw = torch.cat([a for a, _ in want[s]])
+        vw = torch.cat([b for _, b in want[s]])
+        for layer in range(2):
+            kg, vg = kv.gather(layer, s)
+            assert torch.equal(kg, (kw + layer).bfloat16()) and torch.equal(vg, (vw - layer).bfloat16())
+
+
+def test_fp8_pages_bit_exact():
+    """E4M3 codes and per-(page, head) scales equal the oracle's definition, including the
+    re-encode when a later append raises the page scale."""
+    dev = _dev()
+    rng = np.random.default_rng(404)
+    H, D = 2, 64
+    kv = dev.PagedKVCache(1, H, D, 8, 1, 8, 8, kv_dtype=dev.KV_FP8_E4M3)
+    pages_k = {}
+    n = 0
+    for step, cnt in enumerate([5, 1, 1, 30, 1, 20]):
+        rows = rng.normal(0, 1, (cnt, H, D)).astype(np.float32)
+        if step == 2:
+            rows *= 6.0  # forces a rescale of the first page
+        rows = ref_math.bf16_round(rows)
+        kv.reserve(_desc(dev, [(0, cnt, n, -1)]))
+        t = torch.tensor(rows, device="cuda").bfloat16()
+        kv.append(0, t, t * 0.5)
+        for i in range(cnt):
+            p, slot = (n + i) // 32, (n + i) % 32
+            for h in range(H):
+                q, sc, filled = pages_k.get((p, h), (np.zeros((32, D), np.uint8), 0.0, 0))
+                pages_k[(p, h)] = (q, sc, filled)
+        # oracle: apply per page touched, as the kernel does (one touch = rows of this step in that page)
+        pos = n
+        while pos < n + cnt:
+            p = pos // 32
+            hi = min((p + 1) * 32, n + cnt)
+            for h in range(H):
+                q, sc, filled = pages_k[(p, h)]
+                q2, sc2 = ref_math.fp8_page_append(q, sc, filled, rows[pos - n : hi - n, h, :])
+                pages_k[(p, h)] = (q2, sc2, filled + hi - pos)
+            pos = hi
+        n += cnt
+    table = kv.block_table(0)
+    for (p, h), (q, sc, filled) in pages_k.items():
+        k_raw, v_raw, ks, vs = kv.page_raw(0, table[p])
+        assert np.float32(ks[h]) == np.float32(sc), (p, h)
+        assert np.array_equal(k_raw[h][:filled], q[:filled]), (p, h)
+    kg, _ = kv.gather(0, 0)
+    assert kg.shape[0] == n
+
+
+def test_pool_exhaustion_is_flagged_not_trapped():
+    """InsufficientBlocks surfaces through the error word and leaves the pool untouched
+    (error.InsufficientBlocks, src/kvcache/paged.zig:109)."""
+    dev = _dev()
+    kv = dev.PagedKVCache(1, 2, 64, 4, 2, 8, 8)
+    kv.reserve(_desc(dev, [(0, 100, 0, -1)]))
+    kv.reserve(_desc(dev, [(1, 64, 0, -1)]))
+    assert kv.error_word() == 1
+    assert kv.free_count() == 0 and kv.seq_len(1) == 0 and kv.block_table(1) == []
+    with pytest.raises(Exception):
+        kv.alloc(1, 1)
+    kv.reserve(_desc(dev, [(7, 1, 0, -1)]))  # bad slot
+    assert kv.error_word() == 5
