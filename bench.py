@@ -64,7 +64,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-i", str(self.index), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+                                          "-i", str(self.index), "-lms", "50"], stdout=subprocess.PIPE, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except Exception:
             self.proc = None
@@ -95,9 +95,9 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def build_c2(dev, torch, seed: int, fp8: bool):
+def build_c2(dev, torch, seed: int, fp8: bool, n_seq: int = 64):
     """Fills a scattered page pool with the config-2 contexts; returns the pool and the step inputs."""
-    ctxs = c2_contexts(seed)
+    ctxs = c2_contexts(seed, n_seq)
     rng = np.random.default_rng(seed + 1)
     pages = int((-(-ctxs // PAGE)).sum())
     n_pages = int(np.ceil(pages * 1.25))
@@ -169,11 +169,18 @@ def run_reference(args, rank: int):
     seed = 1234
     ctxs = c2_contexts(seed)
     g = torch.Generator().manual_seed(seed)
-    sample = 8
+    q = (torch.randn((len(ctxs), HQ, D), generator=g) / np.sqrt(D)).bfloat16()
+    # Calibrate on the first sequence, then take as many leading sequences as fit ~120 s overall.
+    c0 = int(ctxs[0])
+    k0 = torch.randn((c0, HKV, D), generator=g).bfloat16()
+    _, dt0 = cpu_baseline_c2(ctxs, None, k0, k0, q, 1, min_time=0.0, warm=True)
+    per_token = dt0 / c0
+    budget_tokens = 120.0 / max(args.steps + args.warmup, 1) / per_token
+    sample = int(np.searchsorted(np.cumsum(ctxs), budget_tokens, side="right"))
+    sample = max(1, min(sample, 8))
     total = int(ctxs[:sample].sum())
     k = torch.randn((total, HKV, D), generator=g).bfloat16()
     v = torch.randn((total, HKV, D), generator=g).bfloat16()
-    q = (torch.randn((len(ctxs), HQ, D), generator=g) / np.sqrt(D)).bfloat16()
     cb, dt = None, None
     times = []
     for i in range(args.warmup + args.steps):
@@ -187,7 +194,7 @@ def run_reference(args, rank: int):
         "impl": "reference", "metric": "decode tokens/sec (ragged continuous batch)", "value": val,
         "unit": "decode tokens/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
-        "data": "synthetic", "config": {"workload": args.workload, "note": "bounded sample: 8 of 64 sequences per step"},
+        "data": "synthetic", "config": {"workload": args.workload, "note": f"bounded sample: first {sample} of 64 sequences per step"},
         "cpu_baseline": cb, "e2e": {"value": val, "unit": "decode tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
@@ -195,12 +202,15 @@ def run_reference(args, rank: int):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="paged_attn_bf16")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--seqs", type=int, default=64, help="sequences per GPU (64 = the configuration; fewer for profiling)")
     args = ap.parse_args()
+    if args.steps is None:
+        args.steps = 10 if args.impl == "reference" else 500
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -219,7 +229,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     fp8 = args.workload.endswith("fp8")
-    kv, ctxs, q, (k_rows, v_rows) = build_c2(dev, torch, 1234 + rank, fp8)
+    kv, ctxs, q, (k_rows, v_rows) = build_c2(dev, torch, 1234 + rank, fp8, args.seqs)
     n_seq = len(ctxs)
     row_seq = torch.arange(n_seq, dtype=torch.int32, device="cuda")
     row_ctx = torch.tensor(ctxs, dtype=torch.int32, device="cuda")
@@ -232,12 +242,12 @@ def main():
         torch.cuda.synchronize()
 
     # ---- device-resident timing: one step = one attention decode over all sequences ----
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a moment to start: it samples from warm-up to the end of the run
     for _ in range(W):
         kv.attention(0, q, row_seq, row_ctx, out)
     barrier()
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     barrier()
     t_all0 = torch.cuda.Event(enable_timing=True)
@@ -249,7 +259,6 @@ def main():
         b.record()
     t_all1.record()
     barrier()
-    clocks = sampler.stop() if rank == 0 else None
     total_ms = t_all0.elapsed_time(t_all1)
     kern_ms = float(np.mean([a.elapsed_time(b) for a, b in evs]))
     assert kv.error_word() == 0
@@ -277,6 +286,7 @@ def main():
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
 
     if world > 1:
         t = torch.tensor([total_ms, e2e_ms, kern_ms], device="cuda", dtype=torch.float64)

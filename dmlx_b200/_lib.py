@@ -150,6 +150,7 @@ _sig("b200_kv_gather", i32, vp, i32, i32, vp, vp, i32, vp)
 _sig("b200_kv_page_raw", i32, vp, i32, i32, vp, vp, P(f32), P(f32))
 _sig("b200_paged_attn_decode", i32, vp, i32, vp, vp, vp, i32, vp, vp)
 _sig("b200_set_attn_pages_per_chunk", None, i32)
+_sig("b200_set_attn_path", None, i32)
 _sig("b200_rmsnorm", i32, vp, vp, vp, i32, i32, f32, vp)
 _sig("b200_rope", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp)
 _sig("b200_embed_gather", i32, vp, vp, vp, i32, i32, vp)

@@ -20,6 +20,7 @@
 
 #include "common.h"
 #include "kv_pool.cuh"
+#include "tma.cuh"
 
 static int g_device_state = -1;  // -1 unknown, 0 none, 1 ok
 
@@ -501,6 +502,19 @@ b200_status b200_kv_create(const b200_kv_config* c, b200_kv** out) {
   KV_ALLOC(kv->d_part_ml, sizeof(float) * (size_t)kv->max_chunks * c->n_q_heads * 2);
 #undef KV_ALLOC
   cudaMemset(d.block_table, 0, sizeof(int) * (size_t)c->max_seqs * c->max_pages_per_seq);
+  // Pages start zeroed so that slots never written hold finite values: attention multiplies
+  // masked slots by a zero weight instead of branching around them.
+  cudaMemset(d.k_pool, 0, pool_bytes);
+  cudaMemset(d.v_pool, 0, pool_bytes);
+  if (d.elem_bytes == 2) {
+    const uint64_t rows_per_layer = (uint64_t)c->n_pages * c->n_kv_heads * c->page_size;
+    const uint64_t dims[3] = {(uint64_t)c->head_dim, rows_per_layer, (uint64_t)c->n_layers};
+    const uint64_t strides[2] = {(uint64_t)c->head_dim * 2, rows_per_layer * c->head_dim * 2};
+    const uint32_t box[3] = {64, 32, 1};
+    st = b200_make_tensor_map(&kv->kmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d.k_pool, dims, strides, box);
+    if (st == B200_OK) st = b200_make_tensor_map(&kv->vmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d.v_pool, dims, strides, box);
+    if (st != B200_OK) { b200_kv_destroy(kv); return st; }
+  }
   st = b200_kv_reset(kv);
   if (st != B200_OK) { b200_kv_destroy(kv); return st; }
   *out = kv;

@@ -1,5 +1,6 @@
 // Shared definitions of the device page pool (see kv_pool.cu for the layout).
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -38,4 +39,6 @@ struct b200_kv {
   float* d_part_o = nullptr;     // [max_chunks][n_q_heads][head_dim]
   float* d_part_ml = nullptr;    // [max_chunks][n_q_heads][2]  (running max in log2 units, sum)
   int max_chunks = 0;
+  // 3-D tensor maps over the bf16 pools: [layer][page*kv_head*32 rows][head_dim], box 64 x 32 x 1
+  CUtensorMap kmap, vmap;
 };

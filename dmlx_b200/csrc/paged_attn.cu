@@ -22,6 +22,7 @@
 #include "common.h"
 #include "kv_pool.cuh"
 #include "ptx.cuh"
+#include "tma.cuh"
 
 namespace {
 
@@ -112,6 +113,44 @@ __device__ __forceinline__ Item decode_item(const AttnArgs& a, int item) {
   it.page_begin = c * a.pages_per_chunk;
   it.page_end = min(it.page_begin + a.pages_per_chunk, npages);
   return it;
+}
+
+// One token row segment of a staged tile -> VEC floats (lane l16 owns dims [l16*VEC, l16*VEC+VEC)).
+template <int D, bool FP8>
+__device__ __forceinline__ void load_row(const unsigned char* tile, int tok, int l16, float (&f)[D / 16]) {
+  constexpr int VEC = D / 16;
+  if constexpr (FP8) {
+    const unsigned char* p = tile + tok * D + l16 * VEC;
+    if constexpr (VEC == 8) {
+      const uint2 w = *reinterpret_cast<const uint2*>(p);
+      const uint32_t ww[2] = {w.x, w.y};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_fp8x2_storage_t pr = (__nv_fp8x2_storage_t)((ww[i >> 1] >> (16 * (i & 1))) & 0xFFFFu);
+        const float2 fv = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(pr, __NV_E4M3)));
+        f[2 * i] = fv.x; f[2 * i + 1] = fv.y;
+      }
+    } else {
+      const uint32_t w = *reinterpret_cast<const uint32_t*>(p);
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const __nv_fp8x2_storage_t pr = (__nv_fp8x2_storage_t)((w >> (16 * i)) & 0xFFFFu);
+        const float2 fv = __half22float2(__half2(__nv_cvt_fp8x2_to_halfraw2(pr, __NV_E4M3)));
+        f[2 * i] = fv.x; f[2 * i + 1] = fv.y;
+      }
+    }
+  } else {
+    const unsigned char* p = tile + (tok * D + l16 * VEC) * 2;
+    if constexpr (VEC == 8) {
+      const uint4 w = *reinterpret_cast<const uint4*>(p);
+      const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { f[2 * i] = ptx::bf16_lo(ww[i]); f[2 * i + 1] = ptx::bf16_hi(ww[i]); }
+    } else {
+      const uint2 w = *reinterpret_cast<const uint2*>(p);
+      f[0] = ptx::bf16_lo(w.x); f[1] = ptx::bf16_hi(w.x); f[2] = ptx::bf16_lo(w.y); f[3] = ptx::bf16_hi(w.y);
+    }
+  }
 }
 
 template <int D, bool FP8>
@@ -215,10 +254,13 @@ __global__ void __launch_bounds__(kAttnThreads, 3) paged_attn_kernel(AttnArgs a)
 #pragma unroll
       for (int i = 0; i < VEC; ++i) q[h][i] = __bfloat162float(qp[i]) * a.scale_log2;
     }
-    float m[kGroup], l[kGroup], o[kGroup][VEC];
+    // Running softmax state of this lane's own head (head = l16 >> 2; the 4 lanes of a
+    // (half-warp, head) group hold the same value); accumulators for all 4 heads x VEC dims.
+    const int myh = l16 >> 2;
+    const bool b3 = (l16 & 8) != 0, b2 = (l16 & 4) != 0;
+    float m_run = -1e30f, l_run = 0.f, o[kGroup][VEC];
 #pragma unroll
     for (int h = 0; h < kGroup; ++h) {
-      m[h] = -1e30f; l[h] = 0.f;
 #pragma unroll
       for (int i = 0; i < VEC; ++i) o[h][i] = 0.f;
     }
@@ -233,64 +275,68 @@ __global__ void __launch_bounds__(kAttnThreads, 3) paged_attn_kernel(AttnArgs a)
       float ks = 1.f, vs = 1.f;
       if (FP8) { ks = stage_scale[s * 2]; vs = stage_scale[s * 2 + 1]; }
       const int tok0 = pg * 32;
+      const bool partial_page = tok0 + 32 > it.ctx;  // uniform across the CTA
+
+      // ---- phase 1: scores of this warp's 8 tokens (4 passes x 2 half-warps) ----
+      float sreg[4];
 #pragma unroll
       for (int pass = 0; pass < 4; ++pass) {
         const int tok = warp * 8 + pass * 2 + half;
-        float kf[VEC], vf[VEC];
-        if constexpr (FP8) {
-          // VEC bytes per lane
-          const unsigned char* kp = kt + tok * D + l16 * VEC;
-          const unsigned char* vp = vt + tok * D + l16 * VEC;
-#pragma unroll
-          for (int i = 0; i < VEC; i += 2) {
-            __half2_raw hk = __nv_cvt_fp8x2_to_halfraw2(*reinterpret_cast<const __nv_fp8x2_storage_t*>(kp + i), __NV_E4M3);
-            __half2_raw hv = __nv_cvt_fp8x2_to_halfraw2(*reinterpret_cast<const __nv_fp8x2_storage_t*>(vp + i), __NV_E4M3);
-            float2 fk = __half22float2(__half2(hk)), fv = __half22float2(__half2(hv));
-            kf[i] = fk.x; kf[i + 1] = fk.y; vf[i] = fv.x; vf[i + 1] = fv.y;
-          }
-        } else {
-          const uint32_t* kp = reinterpret_cast<const uint32_t*>(kt + (tok * D + l16 * VEC) * 2);
-          const uint32_t* vp = reinterpret_cast<const uint32_t*>(vt + (tok * D + l16 * VEC) * 2);
-          if constexpr (VEC == 8) {
-            const uint4 kw = *reinterpret_cast<const uint4*>(kp), vw = *reinterpret_cast<const uint4*>(vp);
-            const uint32_t kk[4] = {kw.x, kw.y, kw.z, kw.w}, vv[4] = {vw.x, vw.y, vw.z, vw.w};
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              kf[2 * i] = ptx::bf16_lo(kk[i]); kf[2 * i + 1] = ptx::bf16_hi(kk[i]);
-              vf[2 * i] = ptx::bf16_lo(vv[i]); vf[2 * i + 1] = ptx::bf16_hi(vv[i]);
-            }
-          } else {
-            const uint2 kw = *reinterpret_cast<const uint2*>(kp), vw = *reinterpret_cast<const uint2*>(vp);
-            kf[0] = ptx::bf16_lo(kw.x); kf[1] = ptx::bf16_hi(kw.x); kf[2] = ptx::bf16_lo(kw.y); kf[3] = ptx::bf16_hi(kw.y);
-            vf[0] = ptx::bf16_lo(vw.x); vf[1] = ptx::bf16_hi(vw.x); vf[2] = ptx::bf16_lo(vw.y); vf[3] = ptx::bf16_hi(vw.y);
-          }
-        }
-        float sc[kGroup];
+        float kf[VEC];
+        load_row<D, FP8>(kt, tok, l16, kf);
+        float part[kGroup];
 #pragma unroll
         for (int h = 0; h < kGroup; ++h) {
           float acc = 0.f;
 #pragma unroll
           for (int i = 0; i < VEC; ++i) acc = fmaf(q[h][i], kf[i], acc);
-          sc[h] = acc;
+          part[h] = acc;
         }
+        // Transposed butterfly over the 16 lanes of the half-warp: 5 shuffles leave each lane
+        // with the full dot product of head (l16 >> 2).
+        const float r0 = __shfl_xor_sync(0xffffffffu, b3 ? part[0] : part[2], 8);
+        const float r1 = __shfl_xor_sync(0xffffffffu, b3 ? part[1] : part[3], 8);
+        const float a0 = (b3 ? part[2] : part[0]) + r0;
+        const float a1 = (b3 ? part[3] : part[1]) + r1;
+        float sc = (b2 ? a1 : a0) + __shfl_xor_sync(0xffffffffu, b2 ? a0 : a1, 4);
+        sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+        sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+        sreg[pass] = (tok0 + tok < it.ctx) ? sc * ks : -1e30f;
+      }
+      // ---- one rescale per page ----
+      const float mx = fmaxf(fmaxf(sreg[0], sreg[1]), fmaxf(sreg[2], sreg[3]));
+      const float m_new = fmaxf(m_run, mx);
+      const float corr = exp2f(m_run - m_new);
+      float p[4], psum = 0.f;
 #pragma unroll
-        for (int off = 8; off > 0; off >>= 1) {
+      for (int pass = 0; pass < 4; ++pass) {
+        p[pass] = sreg[pass] > -1e29f ? exp2f(sreg[pass] - m_new) : 0.f;
+        psum += p[pass];
+      }
+      l_run = l_run * corr + psum;
+      m_run = m_new;
 #pragma unroll
-          for (int h = 0; h < kGroup; ++h) sc[h] += __shfl_xor_sync(0xffffffffu, sc[h], off);
+      for (int h = 0; h < kGroup; ++h) {
+        const float ch = __shfl_sync(0xffffffffu, corr, (lane & 16) + h * 4);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) o[h][i] *= ch;
+      }
+      // ---- phase 2: o += p * v ----
+#pragma unroll
+      for (int pass = 0; pass < 4; ++pass) {
+        const int tok = warp * 8 + pass * 2 + half;
+        float vf[VEC];
+        load_row<D, FP8>(vt, tok, l16, vf);
+        if (partial_page && tok0 + tok >= it.ctx) {  // unused slots of a page may hold anything
+#pragma unroll
+          for (int i = 0; i < VEC; ++i) vf[i] = 0.f;
         }
-        if (tok0 + tok < it.ctx) {  // uniform per half-warp
+        const float pw = p[pass] * vs;
 #pragma unroll
-          for (int h = 0; h < kGroup; ++h) {
-            const float sv = sc[h] * ks;
-            const float m_new = fmaxf(m[h], sv);
-            const float corr = exp2f(m[h] - m_new);
-            const float p = exp2f(sv - m_new);
-            l[h] = l[h] * corr + p;
-            m[h] = m_new;
-            const float pv = p * vs;
+        for (int h = 0; h < kGroup; ++h) {
+          const float ph = __shfl_sync(0xffffffffu, pw, (lane & 16) + h * 4);
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) o[h][i] = fmaf(o[h][i], corr, pv * vf[i]);
-          }
+          for (int i = 0; i < VEC; ++i) o[h][i] = fmaf(ph, vf[i], o[h][i]);
         }
       }
       __syncwarp();
@@ -300,27 +346,31 @@ __global__ void __launch_bounds__(kAttnThreads, 3) paged_attn_kernel(AttnArgs a)
     if (__syncthreads_or(!alive)) { alive = false; break; }
 
     // ---- merge the two half-warps (same dims, different tokens) ----
+    {
+      const float m_o = __shfl_xor_sync(0xffffffffu, m_run, 16);
+      const float l_o = __shfl_xor_sync(0xffffffffu, l_run, 16);
+      const float m_new = fmaxf(m_run, m_o);
+      const float ca = exp2f(m_run - m_new), cb = exp2f(m_o - m_new);
+      l_run = l_run * ca + l_o * cb;
+      m_run = m_new;
 #pragma unroll
-    for (int h = 0; h < kGroup; ++h) {
-      const float m_o = __shfl_xor_sync(0xffffffffu, m[h], 16);
-      const float l_o = __shfl_xor_sync(0xffffffffu, l[h], 16);
-      const float m_new = fmaxf(m[h], m_o);
-      const float ca = exp2f(m[h] - m_new), cb = exp2f(m_o - m_new);
-      l[h] = l[h] * ca + l_o * cb;
+      for (int h = 0; h < kGroup; ++h) {
+        const float cah = __shfl_sync(0xffffffffu, ca, (lane & 16) + h * 4);
+        const float cbh = __shfl_sync(0xffffffffu, cb, (lane & 16) + h * 4);
 #pragma unroll
-      for (int i = 0; i < VEC; ++i) {
-        const float o_o = __shfl_xor_sync(0xffffffffu, o[h][i], 16);
-        o[h][i] = o[h][i] * ca + o_o * cb;
+        for (int i = 0; i < VEC; ++i) {
+          const float o_o = __shfl_xor_sync(0xffffffffu, o[h][i], 16);
+          o[h][i] = o[h][i] * cah + o_o * cbh;
+        }
       }
-      m[h] = m_new;
     }
     if (half == 0) {
 #pragma unroll
       for (int h = 0; h < kGroup; ++h) {
 #pragma unroll
         for (int i = 0; i < VEC; ++i) red_o[(warp * kGroup + h) * D + l16 * VEC + i] = o[h][i];
-        if (l16 == 0) { red_ml[(warp * kGroup + h) * 2] = m[h]; red_ml[(warp * kGroup + h) * 2 + 1] = l[h]; }
       }
+      if ((l16 & 3) == 0) { red_ml[(warp * kGroup + myh) * 2] = m_run; red_ml[(warp * kGroup + myh) * 2 + 1] = l_run; }
     }
     __syncthreads();
     // ---- merge the 4 warps; thread -> (head, DV dims) ----
@@ -349,29 +399,225 @@ __global__ void __launch_bounds__(kAttnThreads, 3) paged_attn_kernel(AttnArgs a)
   if (!alive && tid == 0) atomicExch(err, B200_ERR_DEVICE_FLAGGED);
 }
 
-// One warp per (row, query head): merge the row's chunks and write bf16.
+
+// ---------------------------------------------------------------------------------------------
+// bf16 pools: tensor-core variant.
+//
+// The CUDA-core kernel above is bound by instruction issue, not by HBM (an FP8 pool moves half the
+// bytes in the same time).  Here every warp is an independent worker: it owns a private ring of
+// kMmaStages page slots, walks its own (chunk, kv head) items, and there is no CTA-wide barrier in
+// the main loop.  Lane 0 stages a page's K and V tiles with tiled TMA loads through 3-D tensor
+// maps over the pool ([layer][page*head*32 rows][head_dim], box 64 x 32, 128B swizzle), so
+// ldmatrix reads them without bank conflicts.  S = Q K^T and O += P V run on mma.sync m16n8k16
+// (bf16 in, f32 out) with the group's query heads as the 16-row M dimension (rows >= group size
+// are zero), the FlashAttention-2 register reuse turns the score fragments into the P operand,
+// and softmax is online per page.  Instructions per staged byte drop by about 8x.
+constexpr int kMmaWarps = 4;
+constexpr int kMmaStages = 3;
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// D(16x8,f32) += A(16x16,bf16; rows 8..15 are zero: a1 = a3 = 0) * B(16x8,bf16)
+__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  const uint32_t z = 0u;
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
 template <int D>
-__global__ void attn_combine_kernel(AttnArgs a, __nv_bfloat16* __restrict__ out) {
-  constexpr int DV = D / 32;
-  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp_global >= a.total_rows * a.n_q_heads || a.d.state[ST_ATTN_ERR] != 0) return;
-  const int row = warp_global / a.n_q_heads, qh = warp_global - row * a.n_q_heads;
+__global__ void __launch_bounds__(kMmaWarps * 32, 1)
+    paged_attn_mma_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, AttnArgs a) {
+  constexpr int BOXES = D / 64;     // 128-byte wide TMA boxes per tile
+  constexpr int TILE = 32 * D * 2;  // bytes of one K or V tile
+  constexpr int KS = D / 16;        // k-steps of Q K^T
+  constexpr int NO = D / 8;         // n-tiles of the output
+
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  unsigned char* my_tiles = smem + (size_t)warp * kMmaStages * 2 * TILE;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kMmaWarps * kMmaStages * 2 * TILE) + warp * kMmaStages;
+  const int H = a.d.n_kv_heads, G = a.n_q_heads / H;
+  const int n_items = a.chunk_start[a.total_rows] * H;
+  const int worker = blockIdx.x * kMmaWarps + warp, n_workers = gridDim.x * kMmaWarps;
+
+  if (lane == 0) {
+    for (int s = 0; s < kMmaStages; ++s) ptx::mbar_init(&full_bar[s], 1);
+    ptx::mbar_fence_init();
+  }
+  __syncwarp();
+
+  // ---- producer cursor (all lanes track it; lane 0 issues) ----
+  int p_item = worker, p_page = 0, p_end = 0, p_begin = 0, p_head = 0, p_pid = 0;
+  uint32_t prod_n = 0;
+  auto producer_enter_item = [&]() {
+    if (p_item < n_items) {
+      const Item it = decode_item(a, p_item);
+      p_begin = it.page_begin; p_page = it.page_begin; p_end = it.page_end; p_head = it.head;
+      const int pg = it.page_begin + lane;
+      if (pg < it.page_end) p_pid = a.d.block_table[(size_t)it.seq * a.d.max_pages_per_seq + pg];
+    }
+  };
+  auto produce_one = [&]() {
+    if (p_item >= n_items) return;
+    const int pid = __shfl_sync(0xffffffffu, p_pid, p_page - p_begin);
+    const uint32_t s = prod_n % kMmaStages;
+    if (lane == 0) {
+      ptx::fence_proxy_async_smem();
+      unsigned char* kd = my_tiles + (size_t)s * 2 * TILE;
+      const int row0 = (pid * H + p_head) * 32;
+      ptx::mbar_expect_tx(&full_bar[s], 2 * TILE);
+#pragma unroll
+      for (int b = 0; b < BOXES; ++b) {
+        ptx::tma_load_3d(kd + b * 4096, &kmap, b * 64, row0, a.layer, &full_bar[s]);
+        ptx::tma_load_3d(kd + TILE + b * 4096, &vmap, b * 64, row0, a.layer, &full_bar[s]);
+      }
+    }
+    prod_n += 1;
+    p_page += 1;
+    if (p_page >= p_end) {
+      p_item += n_workers;
+      producer_enter_item();
+    }
+  };
+  producer_enter_item();
+  for (int i = 0; i < kMmaStages; ++i) produce_one();
+
+  bool alive = true;
+  uint32_t cons_n = 0;
+  // per-lane ldmatrix row/chunk selectors
+  const int ld_r = lane & 7, ld_m = lane >> 3;
+  for (int item = worker; item < n_items && alive; item += n_workers) {
+    const Item it = decode_item(a, item);
+    // Q fragments: row g = query head g of the group (zero beyond the group size).
+    uint32_t qa0[KS], qa2[KS];
+    {
+      const uint32_t* qrow = reinterpret_cast<const uint32_t*>(a.q + ((size_t)it.row * a.n_q_heads + it.head * G + (g < G ? g : 0)) * D);
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        qa0[ks] = g < G ? qrow[ks * 8 + t] : 0u;
+        qa2[ks] = g < G ? qrow[ks * 8 + 4 + t] : 0u;
+      }
+    }
+    float o[NO][4];
+#pragma unroll
+    for (int j = 0; j < NO; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float m_run = -1e30f, l_run = 0.f;
+
+    for (int pg = it.page_begin; pg < it.page_end; ++pg) {
+      const uint32_t s = cons_n % kMmaStages;
+      alive = ptx::mbar_wait(&full_bar[s], (cons_n / kMmaStages) & 1u);
+      if (!alive) break;
+      const uint32_t kbase = ptx::smem_u32(my_tiles + (size_t)s * 2 * TILE), vbase = kbase + TILE;
+      // ---- S = Q K^T : 4 n-tiles of 8 tokens ----
+      float sc[4][4];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+#pragma unroll
+      for (int kk = 0; kk < KS / 2; ++kk) {
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          const int row = nt * 8 + ld_r, cc = 4 * kk + ld_m;  // 16-byte chunk index along head_dim
+          uint32_t b[4];
+          ldsm_x4(kbase + (cc >> 3) * 4096 + row * 128 + (((cc & 7) ^ (row & 7)) << 4), b);
+          mma_bf16_16816(sc[nt], qa0[2 * kk], qa2[2 * kk], b[0], b[1]);
+          mma_bf16_16816(sc[nt], qa0[2 * kk + 1], qa2[2 * kk + 1], b[2], b[3]);
+        }
+      }
+      // ---- online softmax on row g (lanes of a quad share the row) ----
+      const int tok0 = pg * 32;
+      float mx = -1e30f;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const bool valid = tok0 + nt * 8 + 2 * t + e < it.ctx;
+          sc[nt][e] = valid ? sc[nt][e] * a.scale_log2 : -1e30f;
+          mx = fmaxf(mx, sc[nt][e]);
+        }
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);
+      const float corr = exp2f(m_run - m_new);
+      float psum = 0.f;
+      uint32_t pa0[2], pa2[2];
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt) {
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float sv = sc[2 * kt + (e >> 1)][e & 1];
+          pv[e] = sv > -1e29f ? exp2f(sv - m_new) : 0.f;
+          psum += pv[e];
+        }
+        pa0[kt] = pack_bf16(pv[0], pv[1]);
+        pa2[kt] = pack_bf16(pv[2], pv[3]);
+      }
+      l_run = l_run * corr + psum;
+      m_run = m_new;
+      if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+        for (int j = 0; j < NO; ++j) { o[j][0] *= corr; o[j][1] *= corr; }
+      }
+      // ---- O += P V ----
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt) {
+#pragma unroll
+        for (int jj = 0; jj < NO / 2; ++jj) {
+          const int row = kt * 16 + (ld_m & 1) * 8 + ld_r, cc = 2 * jj + (ld_m >> 1);
+          uint32_t b[4];
+          ldsm_x4_trans(vbase + (cc >> 3) * 4096 + row * 128 + (((cc & 7) ^ (row & 7)) << 4), b);
+          mma_bf16_16816(o[2 * jj], pa0[kt], pa2[kt], b[0], b[1]);
+          mma_bf16_16816(o[2 * jj + 1], pa0[kt], pa2[kt], b[2], b[3]);
+        }
+      }
+      __syncwarp();
+      cons_n += 1;
+      produce_one();  // refill the slot just drained: kMmaStages - 1 pages stay in flight while one is computed
+    }
+    if (!alive) break;
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (g < G) {
+      const size_t pidx = (size_t)it.chunk * a.n_q_heads + it.head * G + g;
+#pragma unroll
+      for (int j = 0; j < NO; ++j)
+        *reinterpret_cast<float2*>(a.part_o + pidx * D + j * 8 + 2 * t) = make_float2(o[j][0], o[j][1]);
+      if (t == 0) { a.part_ml[pidx * 2] = m_run; a.part_ml[pidx * 2 + 1] = l_run; }
+    }
+  }
+  if (!alive && lane == 0) atomicExch(a.d.state + ST_ATTN_ERR, B200_ERR_DEVICE_FLAGGED);
+}
+
+// D threads per (row, query head): merge the row's chunks and write bf16.
+template <int D>
+__global__ void __launch_bounds__(D) attn_combine_kernel(AttnArgs a, __nv_bfloat16* __restrict__ out) {
+  const int row = blockIdx.x / a.n_q_heads, qh = blockIdx.x - row * a.n_q_heads, d = threadIdx.x;
+  if (a.d.state[ST_ATTN_ERR] != 0) return;
   const int c0 = a.chunk_start[row], c1 = a.chunk_start[row + 1];
   float mm = -1e30f;
   for (int c = c0; c < c1; ++c) mm = fmaxf(mm, a.part_ml[((size_t)c * a.n_q_heads + qh) * 2]);
-  float ll = 0.f, acc[DV];
-#pragma unroll
-  for (int i = 0; i < DV; ++i) acc[i] = 0.f;
+  float ll = 0.f, acc = 0.f;
+#pragma unroll 4
   for (int c = c0; c < c1; ++c) {
     const size_t pidx = (size_t)c * a.n_q_heads + qh;
     const float w = exp2f(a.part_ml[pidx * 2] - mm);
     ll += a.part_ml[pidx * 2 + 1] * w;
-#pragma unroll
-    for (int i = 0; i < DV; ++i) acc[i] += a.part_o[pidx * D + lane * DV + i] * w;
+    acc += a.part_o[pidx * D + d] * w;
   }
-  const float inv = ll > 0.f ? 1.0f / ll : 0.f;
-#pragma unroll
-  for (int i = 0; i < DV; ++i) out[((size_t)row * a.n_q_heads + qh) * D + lane * DV + i] = __float2bfloat16(acc[i] * inv);
+  out[((size_t)row * a.n_q_heads + qh) * D + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
 }
 
 template <int D, bool FP8>
@@ -390,8 +636,24 @@ b200_status launch_attn(const AttnArgs& a, void* d_out, int grid, cudaStream_t s
   }
   paged_attn_kernel<D, FP8><<<grid, kAttnThreads, smem, s>>>(a);
   B200_LAUNCH_CHECK();
-  int warps = a.total_rows * a.n_q_heads;
-  attn_combine_kernel<D><<<(warps * 32 + 255) / 256, 256, 0, s>>>(a, (__nv_bfloat16*)d_out);
+  attn_combine_kernel<D><<<a.total_rows * a.n_q_heads, D, 0, s>>>(a, (__nv_bfloat16*)d_out);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+template <int D>
+b200_status launch_attn_mma(const b200_kv* kv, const AttnArgs& a, void* d_out, int sms, cudaStream_t s) {
+  constexpr int TILE = 32 * D * 2;
+  const size_t smem = (size_t)kMmaWarps * kMmaStages * 2 * TILE + 1024 + sizeof(uint64_t) * kMmaWarps * kMmaStages;
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(paged_attn_mma_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  const int ctas_per_sm = smem <= 100 * 1024 ? 2 : 1;
+  paged_attn_mma_kernel<D><<<sms * ctas_per_sm, kMmaWarps * 32, smem, s>>>(kv->kmap, kv->vmap, a);
+  B200_LAUNCH_CHECK();
+  attn_combine_kernel<D><<<a.total_rows * a.n_q_heads, D, 0, s>>>(a, (__nv_bfloat16*)d_out);
   B200_LAUNCH_CHECK();
   return B200_OK;
 }
@@ -400,9 +662,13 @@ int g_sm_count = 0;
 
 }  // namespace
 
+extern int b200_attn_pages_per_chunk;
+extern int b200_attn_path;
+
 // Pages per chunk chosen so that the persistent grid sees several items per CTA without making
 // the per-item partials a visible share of the traffic.
 int b200_attn_pages_per_chunk = 8;
+int b200_attn_path = 0;  // 0 = automatic, 1 = CUDA-core kernel, 2 = tensor-core kernel
 
 extern "C" b200_status b200_paged_attn_decode(b200_kv* kv, int32_t layer, const void* d_q, const int32_t* d_row_seq,
                                               const int32_t* d_row_ctx, int32_t total_rows, void* d_out, void* stream) {
@@ -410,8 +676,10 @@ extern "C" b200_status b200_paged_attn_decode(b200_kv* kv, int32_t layer, const 
   if (st != B200_OK) return st;
   const b200_kv_config& c = kv->cfg;
   if (layer < 0 || layer >= c.n_layers) { b200_set_error("attention: layer %d out of range", layer); return B200_ERR_INVALID_ARGUMENT; }
-  if (c.n_q_heads != c.n_kv_heads * kGroup) {
-    b200_set_error("attention: only a GQA group of %d query heads per kv head is built (got %d/%d)", kGroup, c.n_q_heads, c.n_kv_heads);
+  const bool fp8 = c.kv_dtype == B200_KV_FP8_E4M3;
+  const bool use_mma = !fp8 && b200_attn_path != 1 && c.n_q_heads / c.n_kv_heads <= 8;  // MMA rows 0..7 carry the group's heads
+  if (!use_mma && c.n_q_heads != c.n_kv_heads * kGroup) {
+    b200_set_error("attention: the CUDA-core kernel is built for a GQA group of %d query heads per kv head (got %d/%d)", kGroup, c.n_q_heads, c.n_kv_heads);
     return B200_ERR_UNSUPPORTED;
   }
   if (total_rows <= 0) return B200_OK;
@@ -433,11 +701,13 @@ extern "C" b200_status b200_paged_attn_decode(b200_kv* kv, int32_t layer, const 
   attn_plan_kernel<<<1, 1024, 0, s>>>(d_row_ctx, total_rows, c.page_size, ppc, kv->d_chunk_start, kv->max_chunks,
                                       kv->dev.state + ST_ATTN_ERR);
   B200_LAUNCH_CHECK();
+  if (use_mma) return c.head_dim == 128 ? launch_attn_mma<128>(kv, a, d_out, g_sm_count, s) : launch_attn_mma<64>(kv, a, d_out, g_sm_count, s);
   const int grid = g_sm_count * 3;
-  const bool fp8 = c.kv_dtype == B200_KV_FP8_E4M3;
   if (c.head_dim == 128) return fp8 ? launch_attn<128, true>(a, d_out, grid, s) : launch_attn<128, false>(a, d_out, grid, s);
   return fp8 ? launch_attn<64, true>(a, d_out, grid, s) : launch_attn<64, false>(a, d_out, grid, s);
 }
 
 // Tuning hook (not part of the reference surface): pages per split-K chunk, 4..32.
 extern "C" void b200_set_attn_pages_per_chunk(int32_t n) { b200_attn_pages_per_chunk = n; }
+// Tuning hook: 0 = automatic (tensor-core kernel for bf16 pools), 1 = force the CUDA-core kernel.
+extern "C" void b200_set_attn_path(int32_t p) { b200_attn_path = p; }

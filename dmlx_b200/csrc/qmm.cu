@@ -33,6 +33,7 @@
 #include "common.h"
 #include "ptx.cuh"
 #include "qmm.cuh"
+#include "tma.cuh"
 
 namespace {
 
@@ -189,14 +190,6 @@ __global__ void __launch_bounds__(kTileN) qmm_simt_kernel(QmmArgs a) {
 constexpr int kTcThreads = 192;
 constexpr int kRawStride = 5120;  // weight block padded to a multiple of 1024
 
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-          ptx::smem_u32(dst)),
-      "l"(map), "r"(x), "r"(y), "r"(ptx::smem_u32(bar))
-      : "memory");
-}
-
 template <int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_constant__ CUtensorMap xmap, QmmArgs a) {
   extern __shared__ unsigned char smem_raw[];
@@ -250,7 +243,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
         if (!ok) break;
         ptx::mbar_expect_tx(&loaded[s], BB + tn * 128);
         ptx::bulk_g2s(raw_blk(s), a.blocks + ((size_t)nt * a.kc + kc0 + i) * BB, BB, &loaded[s]);
-        tma_load_2d(x_tile(s), &xmap, (kc0 + i) * kChunkK, a.x_row0 + t0, &loaded[s]);
+        ptx::tma_load_2d(x_tile(s), &xmap, (kc0 + i) * kChunkK, a.x_row0 + t0, &loaded[s]);
       }
     }
   } else if (warp == 5) {
@@ -326,11 +319,6 @@ int g_counters_n = 0;
 int* g_err = nullptr;
 int g_sms = 0;
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn g_encode = nullptr;
-
 b200_status ensure_state(size_t ws_bytes, int n_counters) {
   if (!g_err) {
     B200_CUDA_TRY(cudaMalloc((void**)&g_err, sizeof(int)));
@@ -360,28 +348,10 @@ b200_status ensure_state(size_t ws_bytes, int n_counters) {
 }
 
 b200_status make_x_map(CUtensorMap* map, const void* x, int rows, int k, int box_rows) {
-  if (!g_encode) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    B200_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
-    if (!fn || q != cudaDriverEntryPointSuccess) {
-      b200_set_error("cuTensorMapEncodeTiled is not available from the driver");
-      return B200_ERR_CUDA;
-    }
-    g_encode = (EncodeTiledFn)fn;
-  }
-  cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)k * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kChunkK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) {
-    b200_set_error("cuTensorMapEncodeTiled failed (%d) for x[%d,%d]", (int)r, rows, k);
-    return B200_ERR_CUDA;
-  }
-  return B200_OK;
+  const uint64_t dims[2] = {(uint64_t)k, (uint64_t)rows};
+  const uint64_t strides[1] = {(uint64_t)k * 2};
+  const uint32_t box[2] = {(uint32_t)kChunkK, (uint32_t)box_rows};
+  return b200_make_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box);
 }
 
 int pick_splits(int tiles, int kc, int sms) {
@@ -494,12 +464,23 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
   if (st != B200_OK) return st;
   a.ws = g_ws; a.counters = g_counters; a.err = g_err;
   const int stage_stride = kTileN * 128 + tn * 128 + kRawStride;
-  a.stages = std::max(2, std::min(6, (200 * 1024) / stage_stride));
-  const size_t smem = (size_t)a.stages * stage_stride + 1024 /*alignment slack*/ + 8 * (3 * a.stages + 2) + 16;
-  static size_t configured[2] = {0, 0};
-  if (configured[MODE] < smem) {
-    B200_CUDA_TRY(cudaFuncSetAttribute(qmm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    configured[MODE] = 227 * 1024;
+  static int smem_budget[2] = {0, 0};  // opt-in dynamic shared memory available to this kernel
+  if (smem_budget[MODE] == 0) {
+    int dev = 0, optin = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    cudaFuncAttributes fa;
+    B200_CUDA_TRY(cudaFuncGetAttributes(&fa, qmm_tc_kernel<MODE>));
+    const int budget = optin - (int)fa.sharedSizeBytes;
+    B200_CUDA_TRY(cudaFuncSetAttribute(qmm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget));
+    smem_budget[MODE] = budget;
+  }
+  const int fixed = 1024 /*alignment slack*/ + 8 * (3 * 8 + 2) + 16;
+  a.stages = std::max(2, std::min(6, (std::min(smem_budget[MODE], 200 * 1024) - fixed) / stage_stride));
+  const size_t smem = (size_t)a.stages * stage_stride + fixed;
+  if ((int)smem > smem_budget[MODE]) {
+    b200_set_error("qmm: %zu bytes of shared memory needed, %d available", smem, smem_budget[MODE]);
+    return B200_ERR_CAPACITY;
   }
   CUtensorMap xmap;
   st = make_x_map(&xmap, a.x, rows, a.k, tn);

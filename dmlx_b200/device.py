@@ -190,6 +190,11 @@ def set_attn_pages_per_chunk(n: int):
     lib.b200_set_attn_pages_per_chunk(n)
 
 
+def set_attn_path(path: int):
+    """0 = automatic (tensor-core kernel for bf16 pools), 1 = force the CUDA-core kernel."""
+    lib.b200_set_attn_path(path)
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     out = out if out is not None else torch.empty_like(x)
     _lib.check(lib.b200_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), x.shape[0], x.shape[1], eps, _stream()))

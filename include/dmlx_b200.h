@@ -248,6 +248,8 @@ b200_status b200_paged_attn_decode(b200_kv* kv, int32_t layer, const void* d_q,
 
 /* Tuning hook with no reference counterpart: pages per split-K chunk (4..32, default 8). */
 void b200_set_attn_pages_per_chunk(int32_t n);
+/* Tuning hook: 0 = automatic (tensor-core kernel for bf16 pools), 1 = force the CUDA-core kernel. */
+void b200_set_attn_path(int32_t path);
 
 /* ---- elementwise pieces of the layer (src/models/llama.zig) -------------------------------- */
 b200_status b200_rmsnorm(const void* d_x, const void* d_weight, void* d_out, int32_t rows,

@@ -20,7 +20,7 @@ def _close(got, want):
     return rel, cos
 
 
-def _run_case(ctxs, hq, hkv, d, kv_dtype, seed, scatter=True, pages_per_chunk=8):
+def _run_case(ctxs, hq, hkv, d, kv_dtype, seed, scatter=True, pages_per_chunk=8, path=0):
     from dmlx_b200 import device as dev
 
     rng = np.random.default_rng(seed)
@@ -30,6 +30,7 @@ def _run_case(ctxs, hq, hkv, d, kv_dtype, seed, scatter=True, pages_per_chunk=8)
     kv = dev.PagedKVCache(1, hkv, d, n_pages, n, max(-(-max(ctxs) // 32), 1), hq, max_rows=max(sum(ctxs), n, 1),
                           kv_dtype=kv_dtype)
     dev.set_attn_pages_per_chunk(pages_per_chunk)
+    dev.set_attn_path(path)
     if scatter:
         kv.set_free_order(rng.permutation(n_pages).tolist())
     k = ref_math.bf16_round(rng.normal(0, 1, (sum(ctxs), hkv, d)).astype(np.float32))
@@ -61,15 +62,17 @@ def _run_case(ctxs, hq, hkv, d, kv_dtype, seed, scatter=True, pages_per_chunk=8)
             want[s] = ref_math.gqa_attention_decode(q[s], k_eff[off : off + c], v_eff[off : off + c])
         off += c
     kv.close()
+    dev.set_attn_path(0)
+    dev.set_attn_pages_per_chunk(8)
     return got, want, (k, v, q)
 
 
 @pytest.mark.parametrize("d", [64, 128])
-@pytest.mark.parametrize("kv_dtype", [0, 1])
-def test_ragged_contexts(d, kv_dtype):
+@pytest.mark.parametrize("kv_dtype,path", [(0, 0), (0, 1), (1, 0)])  # bf16 tensor-core, bf16 CUDA-core, FP8
+def test_ragged_contexts(d, kv_dtype, path):
     ctxs = [1, 31, 32, 33, 64, 65, 200, 257, 700, 5, 1023, 96]
     hq, hkv = (8, 2) if d == 64 else (32, 8)
-    got, want, _ = _run_case(ctxs, hq, hkv, d, kv_dtype, seed=7 + d + kv_dtype)
+    got, want, _ = _run_case(ctxs, hq, hkv, d, kv_dtype, seed=7 + d + kv_dtype, path=path)
     rel, cos = _close(got, want)
     assert rel <= REL_TOL and cos >= COS_TOL, (rel, cos)
     for s in range(len(ctxs)):  # every row on its own, so a short context cannot hide behind a long one
@@ -93,10 +96,19 @@ def test_fp8_close_to_bf16_oracle():
 
 
 @pytest.mark.parametrize("ppc", [4, 8, 32])
-def test_split_sizes_agree(ppc):
-    got, want, _ = _run_case([2000, 40, 513], 32, 8, 128, 0, seed=5, pages_per_chunk=ppc)
+@pytest.mark.parametrize("path", [0, 1])
+def test_split_sizes_agree(ppc, path):
+    got, want, _ = _run_case([2000, 40, 513], 32, 8, 128, 0, seed=5, pages_per_chunk=ppc, path=path)
     rel, cos = _close(got, want)
     assert rel <= REL_TOL and cos >= COS_TOL
+
+
+def test_gqa_group_sizes_tensor_core_path():
+    """The tensor-core kernel takes the group's query heads as MMA rows: groups of 1, 2 and 8."""
+    for hq, hkv in ((2, 2), (4, 2), (16, 2)):
+        got, want, _ = _run_case([130, 31, 64], hq, hkv, 128, 0, seed=hq)
+        rel, cos = _close(got, want)
+        assert rel <= REL_TOL and cos >= COS_TOL, (hq, hkv, rel, cos)
 
 
 def test_empty_context_row_is_zero():

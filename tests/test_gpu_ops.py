@@ -161,7 +161,7 @@ def test_qmm_epilogues(path):
     got = dev.qmm(w, _bf(x), dev.EPI_RESIDUAL, residual=_bf(res), path=path).float().cpu().numpy()
     rel, cos = _close(got, base + res)
     assert rel <= 2e-2 and cos >= 0.9995
-    for limit in (0.0, 0.05):
+    for limit in (0.0, 0.5):
         got = dev.qmm(w, _bf(x), dev.EPI_SWIGLU, swiglu_limit=limit, path=path).float().cpu().numpy()
         want = ref_math.limited_swiglu(base[:, 0::2].astype(np.float64), base[:, 1::2].astype(np.float64), limit)
         rel, cos = _close(got, want)
