@@ -4,6 +4,12 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
 Prints ONE JSON line (rank 0).  Workloads (BASELINE.json `configs`, synthetic seeded inputs):
+  llama8b_int4 (default) : config 3, the Llama-3-8B-shaped int4 continuous-batching decode step at a
+      fixed live-batch snapshot — 256 requests in flight, each with its lognormal prompt
+      (mean 1024, sigma 0.6, clipped 32..8192) plus a uniform share of its 128..1024 output tokens
+      already generated; weights affine 4-bit group 64 (random codes), paged bf16 KV in 32-token
+      pages.  One step = one decode token for each of the 256 requests through all 32 layers,
+      lm_head and greedy argmax.
   paged_attn_bf16 / paged_attn_fp8 : config 2, the paged-attention decode microbench — 64
       sequences, contexts log-uniform 128..32768, 32 query / 8 KV heads, head_dim 128, 32-token
       pages scattered by a random permutation over a pool of 1.25x the pages in use.
@@ -159,10 +165,247 @@ def cpu_baseline_c2(ctxs, kv, k_rows, v_rows, q, sample: int = 8, min_time: floa
                       f"{reps} repetitions; gather+repeat+dense attention as the reference does per step"}, dt
 
 
+
+# ---------------------------------------------------------------------------------------------
+# config 3: Llama-3-8B-shaped int4 decode step
+# ---------------------------------------------------------------------------------------------
+L8 = dict(n_layers=32, hidden=4096, n_heads=32, n_kv_heads=8, head_dim=128, ffn=14336, vocab=128256)
+
+
+def c3_snapshot(seed: int, n_req: int = 256):
+    """Context length of every live request: prompt + tokens generated so far."""
+    rng = np.random.default_rng(seed)
+    sigma = 0.6
+    mu = np.log(1024.0) - sigma * sigma / 2  # lognormal with mean 1024
+    prompt = np.clip(np.rint(rng.lognormal(mu, sigma, n_req)), 32, 8192).astype(np.int64)
+    out_len = rng.integers(128, 1025, n_req)
+    done = (rng.random(n_req) * out_len).astype(np.int64)
+    return prompt + done
+
+
+def llama_weight_bytes(c) -> float:
+    qkv = (c["n_heads"] + 2 * c["n_kv_heads"]) * c["head_dim"]
+    per_layer = c["hidden"] * (qkv + c["n_heads"] * c["head_dim"]) + 3 * c["hidden"] * c["ffn"]
+    return 0.5625 * (c["n_layers"] * per_layer + c["vocab"] * c["hidden"])
+
+
+def run_llama(args, rank, world, local):
+    import torch
+    import torch.distributed as dist
+
+    from dmlx_b200 import device as dev
+
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    c = dict(L8)
+    if args.layers:
+        c["n_layers"] = args.layers
+    n_req = args.seqs if args.seqs != 64 else 256
+    K, W = args.steps, max(args.warmup, 3)
+    ctxs = c3_snapshot(4321 + rank, n_req)
+    grow = 2 * (K + W) + 8
+    n_pages = int((-(-(ctxs + grow) // PAGE)).sum() * 1.1) + 16
+    kv = dev.PagedKVCache(c["n_layers"], c["n_kv_heads"], c["head_dim"], n_pages, n_req,
+                          int(-(-(ctxs.max() + grow) // PAGE)), c["n_heads"], max_rows=max(n_req, 16))
+    rng = np.random.default_rng(99 + rank)
+    kv.set_free_order(rng.permutation(n_pages).tolist())
+    model = dev.LlamaModel(c["n_layers"], c["hidden"], c["n_heads"], c["n_kv_heads"], c["head_dim"], c["ffn"], c["vocab"],
+                           max_rows=max(n_req, 16), max_reqs=n_req, max_seqs=n_req, rms_eps=1e-5, rope_theta=500000.0)
+    model.random_init(dev.Q_AFFINE4_G64, seed=7 + rank)
+    # live-batch snapshot: every request already holds `ctx` cached tokens in every layer
+    kv.reserve(dev.pack_desc_array([(s, int(n), 0, -1) for s, n in enumerate(ctxs)]).cuda())
+    g = torch.Generator(device="cuda").manual_seed(5 + rank)
+    total = int(ctxs.sum())
+    krows = torch.randn((total, c["n_kv_heads"], c["head_dim"]), generator=g, device="cuda").bfloat16()
+    vrows = torch.randn((total, c["n_kv_heads"], c["head_dim"]), generator=g, device="cuda").bfloat16()
+    for layer in range(c["n_layers"]):
+        kv.append(layer, krows, vrows)
+    torch.cuda.synchronize()
+    assert kv.error_word() == 0
+    del krows, vrows
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    lens = ctxs.copy()
+
+    def host_descs():
+        return [(s, 1, int(lens[s]), -1) for s in range(n_req)]
+
+    def device_descs(n_steps):
+        a = np.zeros((n_steps, n_req, 4), np.int32)
+        for i in range(n_steps):
+            a[i, :, 0] = np.arange(n_req)
+            a[i, :, 1] = 1
+            a[i, :, 2] = lens + i
+            a[i, :, 3] = -1
+        return torch.tensor(a, device="cuda")
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    # ---- device-resident: descriptors already in HBM, no host copies in the timed region ----
+    d = device_descs(W + K)
+    for i in range(W):
+        model.forward_device(kv, d[i], n_req)
+    barrier()
+    launches0 = model.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(W, W + K):
+        model.forward_device(kv, d[i], n_req)
+    e1.record()
+    barrier()
+    total_ms = e0.elapsed_time(e1)
+    launches = model.launch_count() - launches0
+    lens += W + K
+    assert kv.error_word() == 0 and dev.qmm_error_word() == 0
+    # ---- the same steps with per-kernel CUDA events (roofline of the dominant kernel) ----
+    P = min(K, 10)
+    d = device_descs(P)
+    model.profile_enable(True)
+    for i in range(P):
+        model.forward_device(kv, d[i], n_req)
+    prof = model.profile_collect()
+    model.profile_enable(False)
+    live_tokens = float(lens.sum() + n_req * (P + 1) / 2.0)
+    lens += P
+    # ---- end to end: host descriptors in, host tokens out, every step ----
+    for _ in range(2):
+        model.step(kv, host_descs())
+        lens += 1
+    barrier()
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    E = min(K, 20)
+    t0.record()
+    for _ in range(E):
+        toks, free = model.step(kv, host_descs())
+        lens += 1
+    t1.record()
+    barrier()
+    e2e_ms = t0.elapsed_time(t1) / E
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([total_ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms = t.tolist()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    ms_per_step = total_ms / K
+    peak, peak_kind = load_peaks()
+    attn_ms, attn_calls = prof["attention"]
+    mm_ms, mm_calls = prof["matmul"]
+    kv_bytes_per_call = 2 * c["n_kv_heads"] * c["head_dim"] * 2 * live_tokens + n_req * 2 * c["n_heads"] * c["head_dim"] * 2 \
+        + 4 * float((-(-lens // PAGE)).sum())
+    attn_launch_ms = attn_ms / max(attn_calls, 1)
+    achieved = kv_bytes_per_call / (attn_launch_ms * 1e-3) / 1e9
+    wbytes = llama_weight_bytes(c)
+    result = {
+        "metric": "decode tokens/sec (ragged continuous batch)",
+        "value": n_req * world / (ms_per_step * 1e-3), "unit": "decode tokens/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int4 affine g64 weights, bf16 activations and KV, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "llama8b_int4 decode step at a 256-request live-batch snapshot" if n_req == 256 and not args.layers
+                   else f"llama8b_int4 reduced ({c['n_layers']} layers, {n_req} requests)",
+                   "requests_per_gpu": n_req, "layers": c["n_layers"], "hidden": c["hidden"], "q_heads": c["n_heads"],
+                   "kv_heads": c["n_kv_heads"], "head_dim": c["head_dim"], "ffn": c["ffn"], "vocab": c["vocab"],
+                   "cached_tokens_per_gpu": int(lens.sum()), "prompt": "lognormal mean 1024 sigma 0.6 clip 32..8192",
+                   "page_tokens": PAGE, "l2": f"inputs larger than L2 ({(wbytes + 32 * kv_bytes_per_call) / 1e9:.1f} GB read per step)",
+                   "parallelism": f"dp{world}"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                     "peak_kind": f"of {peak_kind}", "traffic": None, "frac_of_8TBs": achieved / 8000.0,
+                     "kernel": "paged_attn_mma_kernel (+plan, +combine), one launch per layer",
+                     "algorithmic_bytes_per_launch": kv_bytes_per_call, "kernel_ms": attn_launch_ms,
+                     "step_breakdown_ms": {k: v[0] / P for k, v in prof.items()},
+                     "matmul": {"ms_per_step": mm_ms / P, "weight_GBs": wbytes / (mm_ms / P * 1e-3) / 1e9,
+                                "tflops": 2.0 * n_req * wbytes / 0.5625 / (mm_ms / P * 1e-3) / 1e12}},
+        "e2e": {"value": n_req * world / (e2e_ms * 1e-3), "unit": "decode tokens/s",
+                "h2d_bytes_per_step": 16 * n_req, "d2h_bytes_per_step": 4 * n_req + 36},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+    }
+    traffic_file = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(traffic_file):
+        result["roofline"]["traffic"] = json.load(open(traffic_file)).get("llama8b_int4")
+    if not args.no_cpu_baseline:
+        result["cpu_baseline"] = cpu_baseline_c3(c, n_req)
+    print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_baseline_c3(c, n_req, sample_req: int = 16, seed: int = 4321):
+    """One decode step of the reference's structure on the host, bounded: ONE layer for the first
+    `sample_req` requests of the snapshot (gather + repeat + dense attention, then the four int4
+    matmuls of the layer), extrapolated to 32 layers + lm_head by parameter count."""
+    from oracle import ref_c
+
+    ctxs = c3_snapshot(seed, n_req)[:sample_req]
+    rng = np.random.default_rng(0)
+    hq, hkv, d, hid, ffn = c["n_heads"], c["n_kv_heads"], c["head_dim"], c["hidden"], c["ffn"]
+    pages = -(-ctxs // PAGE)
+    kp = rng.integers(0, 2 ** 16, (int(pages.sum()), hkv, PAGE, d), dtype=np.uint16) & 0xBF7F
+    table = np.zeros((sample_req, int(pages.max())), np.int32)
+    nxt = 0
+    for s in range(sample_req):
+        table[s, :pages[s]] = np.arange(nxt, nxt + pages[s])
+        nxt += pages[s]
+    q = rng.normal(0, 1, (sample_req, hq, d)).astype(np.float32)
+    x = rng.normal(0, 1, (sample_req, hid)).astype(np.float32)
+
+    def qw(n, k):
+        return (rng.integers(0, 2 ** 32, (n, k // 8), dtype=np.uint32), np.full((n, k // 64), 0.005, np.float32),
+                np.full((n, k // 64), -0.04, np.float32))
+
+    wqkv, wo, wgu, wdn = qw((hq + 2 * hkv) * d, hid), qw(hid, hq * d), qw(2 * ffn, hid), qw(hid, ffn)
+    xf = rng.normal(0, 1, (sample_req, ffn)).astype(np.float32)
+    t0 = time.perf_counter()
+    ref_c.qmm_affine4(*wqkv, x)
+    ref_c.paged_attention_decode(kp, kp, table, ctxs.astype(np.int32), hq, hkv, d, q)
+    ref_c.qmm_affine4(*wo, x)
+    ref_c.qmm_affine4(*wgu, x)
+    ref_c.qmm_affine4(*wdn, xf)
+    t_layer = time.perf_counter() - t0
+    per_layer_params = hid * ((hq + 2 * hkv) * d + hq * d) + 3 * hid * ffn
+    t_step = t_layer * (c["n_layers"] + c["vocab"] * hid / per_layer_params * 0.5)
+    return {"value": sample_req / t_step, "unit": "decode tokens/s", "cores": ref_c.num_threads(), "kind": "port",
+            "sample": f"one layer for the first {sample_req} of {n_req} requests ({int(ctxs.sum())} cached tokens), "
+                      f"extrapolated to {c['n_layers']} layers + lm_head; {t_layer:.2f} s measured"}
+
+
 def run_reference(args, rank: int):
     """--impl reference: the reference's own algorithm for the path on the host cores.  The
     reference itself (Zig + MLX) cannot be built here, so the timed code is the oracle's C twin."""
     if rank != 0:
+        return
+    if args.workload.startswith("llama"):
+        times, cb = [], None
+        for i in range(args.warmup + args.steps):
+            cb = cpu_baseline_c3(dict(L8), 256, sample_req=8)
+            if i >= args.warmup:
+                times.append(8 / cb["value"])
+            if sum(times) > 150.0:
+                break
+        ms = float(np.mean(times) * 1e3)
+        val = 8 / (ms / 1e3)
+        cb["value"] = val
+        print(json.dumps({
+            "impl": "reference", "metric": "decode tokens/sec (ragged continuous batch)", "value": val,
+            "unit": "decode tokens/s", "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "llama8b_int4 decode step at a 256-request live-batch snapshot",
+                       "note": "bounded sample per step: one layer for 8 of 256 requests, extrapolated to the full stack"},
+            "cpu_baseline": cb,
+            "e2e": {"value": val, "unit": "decode tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }))
         return
     import torch
 
@@ -205,12 +448,13 @@ def main():
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--workload", default="paged_attn_bf16")
+    ap.add_argument("--workload", default="llama8b_int4")
+    ap.add_argument("--layers", type=int, default=0, help="llama8b_int4 only: fewer layers (profiling / smoke runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--seqs", type=int, default=64, help="sequences per GPU (64 = the configuration; fewer for profiling)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = 10 if args.impl == "reference" else 500
+        args.steps = 10 if args.impl == "reference" else (50 if args.workload.startswith("llama") else 500)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -225,6 +469,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the product has no CPU path)")
+    if args.workload.startswith("llama"):
+        run_llama(args, rank, world, local)
+        return
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))

@@ -156,8 +156,31 @@ _sig("b200_rope", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp)
 _sig("b200_embed_gather", i32, vp, vp, vp, i32, i32, vp)
 _sig("b200_argmax", i32, vp, i32, i32, vp, vp)
 _sig("b200_qweight_create", i32, i32, i32, i32, i32, vp, vp, vp, P(vp))
+_sig("b200_qweight_random", i32, i32, i32, i32, i32, u32, P(vp))
 _sig("b200_qweight_destroy", None, vp)
 _sig("b200_qmm", i32, vp, vp, i32, vp, i32, vp, f32, i32, vp)
+
+
+class LlamaConfig(C.Structure):
+    _fields_ = [(n, i32) for n in ("n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "ffn", "vocab", "max_rows",
+                                   "max_reqs", "max_seqs")] + [("rms_eps", f32), ("rope_theta", f32)]
+
+
+_sig("b200_qmm_error_word", i32, P(i32))
+_sig("b200_llama_create", i32, P(LlamaConfig), P(vp))
+_sig("b200_llama_destroy", None, vp)
+_sig("b200_llama_set_linear", i32, vp, i32, i32, i32, vp, vp, vp)
+_sig("b200_llama_set_embedding", i32, vp, vp)
+_sig("b200_llama_set_norm", i32, vp, i32, i32, vp)
+_sig("b200_llama_finalize", i32, vp)
+_sig("b200_llama_random_init", i32, vp, i32, u32)
+_sig("b200_llama_step", i32, vp, vp, vp, i32, vp, i32, vp, P(i32), vp)
+_sig("b200_llama_forward", i32, vp, vp, vp, i32, i32, vp, vp)
+_sig("b200_llama_device_buffers", None, vp, P(vp), P(vp), P(vp))
+_sig("b200_llama_last_logits", i32, vp, vp, i32)
+_sig("b200_llama_launch_count", C.c_int64, vp)
+_sig("b200_llama_profile_enable", None, vp, i32)
+_sig("b200_llama_profile_collect", i32, vp, P(C.c_double), P(C.c_int64))
 
 
 class B200Error(RuntimeError):

@@ -120,7 +120,39 @@ __global__ void argmax_kernel(const __nv_bfloat16* __restrict__ logits, int voca
   }
 }
 
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ idx,
+                                   __nv_bfloat16* __restrict__ dst, int hidden) {
+  const int row = blockIdx.x;
+  const int s = max(idx[row], 0);
+  const uint4* sp = reinterpret_cast<const uint4*>(src + (size_t)s * hidden);
+  uint4* dp = reinterpret_cast<uint4*>(dst + (size_t)row * hidden);
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dp[i] = sp[i];
+}
+
+__global__ void scatter_tokens_kernel(const uint32_t* __restrict__ next, const b200_pack_desc* __restrict__ desc,
+                                      uint32_t* __restrict__ last_token, int n_req) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n_req && desc[i].count > 0) last_token[desc[i].seq_slot] = next[i];
+}
+
 }  // namespace
+
+// Rows idx[r] of src -> row r of dst (the last position of every request, src/generation.zig:124-131).
+b200_status b200_gather_rows(const void* d_src, const int32_t* d_idx, void* d_dst, int32_t rows, int32_t hidden, void* stream) {
+  if (rows <= 0) return B200_OK;
+  gather_rows_kernel<<<rows, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)d_src, d_idx, (__nv_bfloat16*)d_dst, hidden);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+// The sampled token of request i becomes the next decode input of its sequence slot.
+b200_status b200_scatter_tokens(const uint32_t* d_next, const b200_pack_desc* d_desc, uint32_t* d_last_token, int32_t n_req,
+                                void* stream) {
+  if (n_req <= 0) return B200_OK;
+  scatter_tokens_kernel<<<(n_req + 127) / 128, 128, 0, (cudaStream_t)stream>>>(d_next, d_desc, d_last_token, n_req);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
 
 extern "C" {
 

@@ -253,7 +253,7 @@ __global__ void cow_copy_kernel(KvDev d) {
 
 // bf16 append: one CTA per (page touch, kv head) copies rows into the page tile.
 __global__ void append_bf16_kernel(KvDev d, int layer, const __nv_bfloat16* __restrict__ k_rows,
-                                   const __nv_bfloat16* __restrict__ v_rows) {
+                                   const __nv_bfloat16* __restrict__ v_rows, int k_stride, int v_stride) {
   const int n_touch = d.state[ST_N_TOUCH];
   const int head = blockIdx.y, D = d.head_dim, H = d.n_kv_heads;
   const int vec_per_row = D / 8;
@@ -264,9 +264,8 @@ __global__ void append_bf16_kernel(KvDev d, int layer, const __nv_bfloat16* __re
     uint4* vd = (uint4*)((__nv_bfloat16*)d.v_pool + tile + (size_t)tc.w * D);
     for (int i = threadIdx.x; i < tc.z * vec_per_row; i += blockDim.x) {
       int r = i / vec_per_row, c = i % vec_per_row;
-      size_t src = ((size_t)(tc.y + r) * H + head) * D;
-      kd[r * vec_per_row + c] = ((const uint4*)(k_rows + src))[c];
-      vd[r * vec_per_row + c] = ((const uint4*)(v_rows + src))[c];
+      kd[r * vec_per_row + c] = ((const uint4*)(k_rows + (size_t)(tc.y + r) * k_stride + head * D))[c];
+      vd[r * vec_per_row + c] = ((const uint4*)(v_rows + (size_t)(tc.y + r) * v_stride + head * D))[c];
     }
   }
 }
@@ -282,13 +281,14 @@ __device__ __forceinline__ float from_e4m3(unsigned char b) {
 // FP8 append: per (touch, head, K|V): new scale = max(old, amax(new rows)/448); when it grows the
 // rows already in the tile are re-encoded at the new scale; then the new rows are encoded.
 __global__ void append_fp8_kernel(KvDev d, int layer, const __nv_bfloat16* __restrict__ k_rows,
-                                  const __nv_bfloat16* __restrict__ v_rows) {
+                                  const __nv_bfloat16* __restrict__ v_rows, int k_stride, int v_stride) {
   __shared__ float s_red[32];
   __shared__ float s_scale[2];
   const int n_touch = d.state[ST_N_TOUCH];
   const int head = blockIdx.y, D = d.head_dim, H = d.n_kv_heads;
   const int is_v = blockIdx.z;
   const __nv_bfloat16* rows = is_v ? v_rows : k_rows;
+  const int stride = is_v ? v_stride : k_stride;
   unsigned char* pool = (unsigned char*)(is_v ? d.v_pool : d.k_pool);
   float* scales = is_v ? d.v_scale : d.k_scale;
   for (int t = blockIdx.x; t < n_touch; t += gridDim.x) {
@@ -298,7 +298,7 @@ __global__ void append_fp8_kernel(KvDev d, int layer, const __nv_bfloat16* __res
     float amax = 0.f;
     for (int i = threadIdx.x; i < tc.z * D; i += blockDim.x) {
       int r = i / D, c = i % D;
-      amax = fmaxf(amax, fabsf(__bfloat162float(rows[((size_t)(tc.y + r) * H + head) * D + c])));
+      amax = fmaxf(amax, fabsf(__bfloat162float(rows[(size_t)(tc.y + r) * stride + head * D + c])));
     }
     for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     if ((threadIdx.x & 31) == 0) s_red[threadIdx.x >> 5] = amax;
@@ -321,7 +321,7 @@ __global__ void append_fp8_kernel(KvDev d, int layer, const __nv_bfloat16* __res
     const float inv = 1.0f / s_new;
     for (int i = threadIdx.x; i < tc.z * D; i += blockDim.x) {
       int r = i / D, c = i % D;
-      float x = __bfloat162float(rows[((size_t)(tc.y + r) * H + head) * D + c]);
+      float x = __bfloat162float(rows[(size_t)(tc.y + r) * stride + head * D + c]);
       tile[(size_t)(tc.w + r) * D + c] = to_e4m3(x * inv);
     }
     if (threadIdx.x == 0) scales[tile_idx] = s_new;
@@ -465,7 +465,7 @@ b200_status b200_kv_create(const b200_kv_config* c, b200_kv** out) {
   d.n_layers = c->n_layers; d.n_kv_heads = c->n_kv_heads; d.head_dim = c->head_dim; d.page_size = c->page_size;
   d.n_pages = c->n_pages; d.max_seqs = c->max_seqs; d.max_pages_per_seq = c->max_pages_per_seq;
   d.elem_bytes = c->kv_dtype == B200_KV_BF16 ? 2 : 1;
-  d.max_touch = c->max_rows;
+  d.max_touch = std::max(c->max_rows, c->n_pages + c->max_seqs);  // a bulk fill may touch every page
   size_t pool_bytes = (size_t)c->n_layers * c->n_pages * c->n_kv_heads * c->page_size * c->head_dim * d.elem_bytes;
   size_t n_tiles = (size_t)c->n_layers * c->n_pages * c->n_kv_heads;
 #define KV_ALLOC(ptr, bytes)                                            \
@@ -597,20 +597,30 @@ b200_status b200_kv_reserve(b200_kv* kv, const b200_pack_desc* d_desc, int32_t n
 
 b200_status b200_kv_append(b200_kv* kv, int32_t layer, const void* d_k_rows, const void* d_v_rows,
                            int32_t total_rows, void* stream) {
+  const int stride = kv->cfg.n_kv_heads * kv->cfg.head_dim;
+  return b200_kv_append_strided(kv, layer, d_k_rows, d_v_rows, stride, stride, total_rows, stream);
+}
+
+}  // extern "C"
+
+b200_status b200_kv_append_strided(b200_kv* kv, int32_t layer, const void* d_k_rows, const void* d_v_rows,
+                                   int32_t k_stride, int32_t v_stride, int32_t total_rows, void* stream) {
   if (layer < 0 || layer >= kv->cfg.n_layers) { b200_set_error("append: layer %d out of range", layer); return B200_ERR_INVALID_ARGUMENT; }
   if (total_rows <= 0) return B200_OK;
   cudaStream_t s = (cudaStream_t)stream;
   int gx = std::min(total_rows, 2048);
   if (kv->cfg.kv_dtype == B200_KV_BF16) {
     append_bf16_kernel<<<dim3(gx, kv->cfg.n_kv_heads), 128, 0, s>>>(kv->dev, layer, (const __nv_bfloat16*)d_k_rows,
-                                                                    (const __nv_bfloat16*)d_v_rows);
+                                                                    (const __nv_bfloat16*)d_v_rows, k_stride, v_stride);
   } else {
     append_fp8_kernel<<<dim3(gx, kv->cfg.n_kv_heads, 2), 128, 0, s>>>(kv->dev, layer, (const __nv_bfloat16*)d_k_rows,
-                                                                      (const __nv_bfloat16*)d_v_rows);
+                                                                      (const __nv_bfloat16*)d_v_rows, k_stride, v_stride);
   }
   B200_LAUNCH_CHECK();
   return B200_OK;
 }
+
+extern "C" {
 
 b200_status b200_kv_seq_len(b200_kv* kv, int32_t seq, int32_t* out_len) {
   if (seq < 0 || seq >= kv->cfg.max_seqs) { b200_set_error("slot %d out of range", seq); return B200_ERR_INVALID_BATCH_INDEX; }

@@ -42,3 +42,11 @@ struct b200_kv {
   // 3-D tensor maps over the bf16 pools: [layer][page*kv_head*32 rows][head_dim], box 64 x 32 x 1
   CUtensorMap kmap, vmap;
 };
+
+// Internal variants with explicit row strides (elements), used when q/k/v live inside a fused
+// projection output.
+b200_status b200_kv_append_strided(b200_kv* kv, int32_t layer, const void* d_k_rows, const void* d_v_rows,
+                                   int32_t k_stride, int32_t v_stride, int32_t total_rows, void* stream);
+b200_status b200_paged_attn_decode_strided(b200_kv* kv, int32_t layer, const void* d_q, int32_t q_stride,
+                                           const int32_t* d_row_seq, const int32_t* d_row_ctx, int32_t total_rows,
+                                           void* d_out, void* stream);

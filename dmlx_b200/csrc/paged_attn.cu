@@ -35,6 +35,7 @@ struct AttnArgs {
   KvDev d;
   int layer;
   const __nv_bfloat16* q;
+  int q_stride;  // elements between consecutive query rows
   const int* row_seq;
   const int* row_ctx;
   const int* chunk_start;  // [T+1]
@@ -250,7 +251,7 @@ __global__ void __launch_bounds__(kAttnThreads, 3) paged_attn_kernel(AttnArgs a)
     float q[kGroup][VEC];
 #pragma unroll
     for (int h = 0; h < kGroup; ++h) {
-      const __nv_bfloat16* qp = a.q + ((size_t)it.row * a.n_q_heads + it.head * kGroup + h) * D + l16 * VEC;
+      const __nv_bfloat16* qp = a.q + (size_t)it.row * a.q_stride + (it.head * kGroup + h) * D + l16 * VEC;
 #pragma unroll
       for (int i = 0; i < VEC; ++i) q[h][i] = __bfloat162float(qp[i]) * a.scale_log2;
     }
@@ -503,7 +504,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1)
     // Q fragments: row g = query head g of the group (zero beyond the group size).
     uint32_t qa0[KS], qa2[KS];
     {
-      const uint32_t* qrow = reinterpret_cast<const uint32_t*>(a.q + ((size_t)it.row * a.n_q_heads + it.head * G + (g < G ? g : 0)) * D);
+      const uint32_t* qrow = reinterpret_cast<const uint32_t*>(a.q + (size_t)it.row * a.q_stride + (it.head * G + (g < G ? g : 0)) * D);
 #pragma unroll
       for (int ks = 0; ks < KS; ++ks) {
         qa0[ks] = g < G ? qrow[ks * 8 + t] : 0u;
@@ -672,6 +673,13 @@ int b200_attn_path = 0;  // 0 = automatic, 1 = CUDA-core kernel, 2 = tensor-core
 
 extern "C" b200_status b200_paged_attn_decode(b200_kv* kv, int32_t layer, const void* d_q, const int32_t* d_row_seq,
                                               const int32_t* d_row_ctx, int32_t total_rows, void* d_out, void* stream) {
+  return b200_paged_attn_decode_strided(kv, layer, d_q, kv->cfg.n_q_heads * kv->cfg.head_dim, d_row_seq, d_row_ctx,
+                                        total_rows, d_out, stream);
+}
+
+b200_status b200_paged_attn_decode_strided(b200_kv* kv, int32_t layer, const void* d_q, int32_t q_stride,
+                                           const int32_t* d_row_seq, const int32_t* d_row_ctx, int32_t total_rows,
+                                           void* d_out, void* stream) {
   b200_status st = b200_require_device();
   if (st != B200_OK) return st;
   const b200_kv_config& c = kv->cfg;
@@ -694,7 +702,7 @@ extern "C" b200_status b200_paged_attn_decode(b200_kv* kv, int32_t layer, const 
   // scratch bound: chunks <= pages/ppc + rows; kv->max_chunks was sized for ppc >= 4
   if (ppc < 4) ppc = 4;
   AttnArgs a;
-  a.d = kv->dev; a.layer = layer; a.q = (const __nv_bfloat16*)d_q; a.row_seq = d_row_seq; a.row_ctx = d_row_ctx;
+  a.d = kv->dev; a.layer = layer; a.q = (const __nv_bfloat16*)d_q; a.q_stride = q_stride; a.row_seq = d_row_seq; a.row_ctx = d_row_ctx;
   a.chunk_start = kv->d_chunk_start; a.total_rows = total_rows; a.n_q_heads = c.n_q_heads; a.pages_per_chunk = ppc;
   a.part_o = kv->d_part_o; a.part_ml = kv->d_part_ml;
   a.scale_log2 = 1.4426950408889634f / sqrtf((float)c.head_dim);

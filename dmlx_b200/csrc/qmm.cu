@@ -41,7 +41,9 @@ constexpr int kTileN = 128;
 constexpr int kChunkK = 64;
 constexpr int kPlaneBytes = kTileN * 16;
 
-__host__ __device__ constexpr int block_bytes(int mode) { return mode == B200_Q_AFFINE4_G64 ? 4608 : 4352; }
+__host__ __device__ constexpr int block_bytes(int mode) {
+  return mode == B200_Q_AFFINE4_G64 ? 4608 : (mode == B200_Q_MXFP4_G32 ? 4352 : kTileN * 128);
+}
 
 // ---- dequantisation of one 32-bit word (8 columns) to 8 bf16 -----------------------------------
 template <int MODE>
@@ -153,6 +155,22 @@ __global__ void __launch_bounds__(kTileN) qmm_simt_kernel(QmmArgs a) {
     }
     __syncthreads();
     const unsigned char* blk = a.blocks + ((size_t)nt * a.kc + kc) * BB;
+    if constexpr (MODE == B200_Q_BF16) {
+      // dense bf16 block: row r is 128 bytes, 16-byte chunk c stored at position c ^ (r & 7)
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint4 d = *reinterpret_cast<const uint4*>(blk + r * 128 + ((c ^ (r & 7)) << 4));
+        const uint32_t dd[4] = {d.x, d.y, d.z, d.w};
+        float wf[8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { wf[2 * i] = ptx::bf16_lo(dd[i]); wf[2 * i + 1] = ptx::bf16_hi(dd[i]); }
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) acc[t] = fmaf(wf[i], xs[t][c * 8 + i], acc[t]);
+        }
+      }
+    } else {
 #pragma unroll
     for (int plane = 0; plane < 2; ++plane) {
       const uint4 raw = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[r];
@@ -177,6 +195,7 @@ __global__ void __launch_bounds__(kTileN) qmm_simt_kernel(QmmArgs a) {
           acc[t] = fmaf(wf[6], x1.z, acc[t]); acc[t] = fmaf(wf[7], x1.w, acc[t]);
         }
       }
+    }
     }
   }
   const int tile_id = nt * gridDim.z + tt;
@@ -242,7 +261,9 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
         ok = ptx::mbar_wait(&mma_done[s], ((i / stages) & 1) ^ 1);
         if (!ok) break;
         ptx::mbar_expect_tx(&loaded[s], BB + tn * 128);
-        ptx::bulk_g2s(raw_blk(s), a.blocks + ((size_t)nt * a.kc + kc0 + i) * BB, BB, &loaded[s]);
+        // dense bf16 blocks are stored in the swizzled K-major layout and land in the MMA tile directly
+        ptx::bulk_g2s(MODE == B200_Q_BF16 ? a_tile(s) : raw_blk(s), a.blocks + ((size_t)nt * a.kc + kc0 + i) * BB, BB,
+                      &loaded[s]);
         ptx::tma_load_2d(x_tile(s), &xmap, (kc0 + i) * kChunkK, a.x_row0 + t0, &loaded[s]);
       }
     }
@@ -273,7 +294,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
       const unsigned char* blk = raw_blk(s);
       unsigned char* arow = a_tile(s) + r * 128;
 #pragma unroll
-      for (int plane = 0; plane < 2; ++plane) {
+      for (int plane = 0; plane < (MODE == B200_Q_BF16 ? 0 : 2); ++plane) {
         const uint4 raw = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[r];
         __nv_bfloat162 s2, b2;
         row_params<MODE>(blk, r, plane, s2, b2);
@@ -371,7 +392,7 @@ extern "C" b200_status b200_qweight_create(int32_t mode, int32_t n_experts, int3
   *out = nullptr;
   b200_status st = b200_require_device();
   if (st != B200_OK) return st;
-  if (mode != B200_Q_AFFINE4_G64 && mode != B200_Q_MXFP4_G32) { b200_set_error("unknown quantisation mode %d", mode); return B200_ERR_INVALID_QUANT_BITS; }
+  if (mode != B200_Q_AFFINE4_G64 && mode != B200_Q_MXFP4_G32 && mode != B200_Q_BF16) { b200_set_error("unknown quantisation mode %d", mode); return B200_ERR_INVALID_QUANT_BITS; }
   if (n_experts <= 0 || n <= 0 || k <= 0 || k % kChunkK != 0) { b200_set_error("qweight: K must be a positive multiple of 64"); return B200_ERR_INVALID_ARGUMENT; }
   if (mode == B200_Q_AFFINE4_G64 && !h_biases) { b200_set_error("affine weights need biases"); return B200_ERR_INVALID_ARGUMENT; }
   const int nt = (n + kTileN - 1) / kTileN, kc = k / kChunkK, bb = block_bytes(mode);
@@ -388,6 +409,11 @@ extern "C" b200_status b200_qweight_create(int32_t mode, int32_t n_experts, int3
             continue;  // zero nibbles, zero scale/bias (affine) -> zero weights
           }
           const size_t grow = (size_t)e * n + row;
+          if (mode == B200_Q_BF16) {
+            for (int cc = 0; cc < 8; ++cc)
+              std::memcpy(blk + r * 128 + ((cc ^ (r & 7)) << 4), (const uint16_t*)h_packed + grow * k + c * kChunkK + cc * 8, 16);
+            continue;
+          }
           for (int plane = 0; plane < 2; ++plane)
             for (int w = 0; w < 4; ++w) {
               uint32_t word = 0;
@@ -421,6 +447,54 @@ extern "C" b200_status b200_qweight_create(int32_t mode, int32_t n_experts, int3
   if (e != cudaSuccess) { b200_set_error("cudaMalloc(%zu) failed: %s", total, cudaGetErrorString(e)); delete w; return B200_ERR_CUDA; }
   e = cudaMemcpy(w->d_blocks, host.data(), total, cudaMemcpyHostToDevice);
   if (e != cudaSuccess) { b200_set_error("weight upload failed: %s", cudaGetErrorString(e)); cudaFree(w->d_blocks); delete w; return B200_ERR_CUDA; }
+  *out = w;
+  return B200_OK;
+}
+
+namespace {
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+  x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+  return x;
+}
+// Fills blocks with pseudo-random codes and plausible scales: affine weights land in about
+// [-0.04, 0.035], MXFP4 scales are 2^-6, dense weights are small bf16 values.
+__global__ void random_blocks_kernel(unsigned char* blocks, size_t n_blocks, int mode, uint32_t seed) {
+  const int bb = block_bytes(mode);
+  const size_t words = n_blocks * (size_t)(bb / 4);
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += (size_t)gridDim.x * blockDim.x) {
+    const int off = (int)(i % (size_t)(bb / 4)) * 4;
+    uint32_t v = mix32((uint32_t)i * 2654435761u + seed) ^ mix32((uint32_t)(i >> 32) + seed * 31u);
+    if (mode == B200_Q_AFFINE4_G64) {
+      if (off >= 2 * kPlaneBytes) v = off < 2 * kPlaneBytes + 256 ? 0x3BA43BA4u /* 0.005 x2 */ : 0xBD24BD24u /* -0.04 x2 */;
+    } else if (mode == B200_Q_MXFP4_G32) {
+      if (off >= 2 * kPlaneBytes) v = 0x79797979u;  // E8M0 121 -> 2^-6
+    } else {
+      v = (v & 0x807F807Fu) | 0x3C003C00u;  // bf16 with exponent 2^-7: |w| in [0.0078, 0.0156)
+    }
+    reinterpret_cast<uint32_t*>(blocks)[i] = v;
+  }
+}
+}  // namespace
+
+extern "C" b200_status b200_qweight_random(int32_t mode, int32_t n_experts, int32_t n, int32_t k, uint32_t seed,
+                                           b200_qweight** out) {
+  *out = nullptr;
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (mode < 0 || mode > B200_Q_BF16) { b200_set_error("unknown quantisation mode %d", mode); return B200_ERR_INVALID_QUANT_BITS; }
+  if (n_experts <= 0 || n <= 0 || k <= 0 || k % kChunkK != 0 || n % kTileN != 0) {
+    b200_set_error("random weights: N must be a multiple of 128 and K of 64");
+    return B200_ERR_INVALID_ARGUMENT;
+  }
+  auto* w = new b200_qweight();
+  w->mode = mode; w->n_experts = n_experts; w->n = n; w->k = k; w->nt = n / kTileN; w->kc = k / kChunkK;
+  w->block_bytes = block_bytes(mode);
+  const size_t n_blocks = (size_t)n_experts * w->nt * w->kc;
+  cudaError_t e = cudaMalloc((void**)&w->d_blocks, n_blocks * w->block_bytes);
+  if (e != cudaSuccess) { b200_set_error("cudaMalloc failed: %s", cudaGetErrorString(e)); delete w; return B200_ERR_CUDA; }
+  random_blocks_kernel<<<1184, 256>>>(w->d_blocks, n_blocks, mode, seed);
+  e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) { b200_set_error("random init failed: %s", cudaGetErrorString(e)); cudaFree(w->d_blocks); delete w; return B200_ERR_CUDA; }
   *out = w;
   return B200_OK;
 }
@@ -464,7 +538,7 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
   if (st != B200_OK) return st;
   a.ws = g_ws; a.counters = g_counters; a.err = g_err;
   const int stage_stride = kTileN * 128 + tn * 128 + kRawStride;
-  static int smem_budget[2] = {0, 0};  // opt-in dynamic shared memory available to this kernel
+  static int smem_budget[3] = {0, 0, 0};  // opt-in dynamic shared memory available to this kernel
   if (smem_budget[MODE] == 0) {
     int dev = 0, optin = 0;
     B200_CUDA_TRY(cudaGetDevice(&dev));
@@ -505,9 +579,14 @@ extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t 
   a.residual = (const __nv_bfloat16*)d_residual;
   a.rows = rows; a.n = w->n; a.k = w->k; a.nt = w->nt; a.kc = w->kc; a.epilogue = epilogue; a.swiglu_limit = swiglu_limit;
   cudaStream_t s = (cudaStream_t)stream;
-  if (path == B200_QMM_SIMT)
-    return w->mode == B200_Q_AFFINE4_G64 ? launch_simt<B200_Q_AFFINE4_G64>(a, rows, s) : launch_simt<B200_Q_MXFP4_G32>(a, rows, s);
-  return w->mode == B200_Q_AFFINE4_G64 ? launch_tc<B200_Q_AFFINE4_G64>(a, rows, s) : launch_tc<B200_Q_MXFP4_G32>(a, rows, s);
+  if (path == B200_QMM_SIMT) {
+    if (w->mode == B200_Q_AFFINE4_G64) return launch_simt<B200_Q_AFFINE4_G64>(a, rows, s);
+    if (w->mode == B200_Q_MXFP4_G32) return launch_simt<B200_Q_MXFP4_G32>(a, rows, s);
+    return launch_simt<B200_Q_BF16>(a, rows, s);
+  }
+  if (w->mode == B200_Q_AFFINE4_G64) return launch_tc<B200_Q_AFFINE4_G64>(a, rows, s);
+  if (w->mode == B200_Q_MXFP4_G32) return launch_tc<B200_Q_MXFP4_G32>(a, rows, s);
+  return launch_tc<B200_Q_BF16>(a, rows, s);
 }
 
 // Reads and clears the matmul kernels' error word (a bounded wait that ran out).
@@ -516,5 +595,13 @@ extern "C" b200_status b200_qmm_error_word(int32_t* out) {
   if (!g_err) return B200_OK;
   B200_CUDA_TRY(cudaMemcpy(out, g_err, sizeof(int), cudaMemcpyDeviceToHost));
   if (*out != 0) B200_CUDA_TRY(cudaMemset(g_err, 0, sizeof(int)));
+  return B200_OK;
+}
+
+// Queues a copy of the error word into pinned host memory on `stream` (no synchronisation).
+extern "C" b200_status b200_qmm_error_word_async(int32_t* h_out, void* stream) {
+  *h_out = 0;
+  if (!g_err) return B200_OK;
+  B200_CUDA_TRY(cudaMemcpyAsync(h_out, g_err, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
   return B200_OK;
 }

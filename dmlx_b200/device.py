@@ -257,3 +257,87 @@ def qmm_error_word() -> int:
     out = C.c_int32()
     _lib.check(lib.b200_qmm_error_word(C.byref(out)))
     return out.value
+
+
+Q_BF16 = 2
+W_Q, W_K, W_V, W_O, W_GATE, W_UP, W_DOWN, W_LM_HEAD = range(8)
+
+
+class LlamaModel:
+    """The LLaMA layer stack behind b200_llama_step (ModelVTable.forward + greedy sampling,
+    src/generation.zig:47-53,104-145)."""
+
+    def __init__(self, n_layers: int, hidden: int, n_heads: int, n_kv_heads: int, head_dim: int, ffn: int, vocab: int,
+                 max_rows: int, max_reqs: int, max_seqs: int, rms_eps: float = 1e-5, rope_theta: float = 10000.0):
+        self.cfg = _lib.LlamaConfig(n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab, max_rows, max_reqs,
+                                    max_seqs, rms_eps, rope_theta)
+        h = C.c_void_p()
+        _lib.check(lib.b200_llama_create(C.byref(self.cfg), C.byref(h)))
+        self._h = h.value
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib.b200_llama_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    def set_linear(self, layer: int, which: int, mode: int, packed: np.ndarray, scales: Optional[np.ndarray] = None,
+                   biases: Optional[np.ndarray] = None):
+        packed = np.ascontiguousarray(packed)
+        scales = np.ascontiguousarray(scales) if scales is not None else None
+        biases = np.ascontiguousarray(biases) if biases is not None else None
+        _lib.check(lib.b200_llama_set_linear(self._h, layer, which, mode, packed.ctypes.data,
+                                             scales.ctypes.data if scales is not None else None,
+                                             biases.ctypes.data if biases is not None else None))
+
+    def set_embedding(self, table_bf16_bits: np.ndarray):
+        t = np.ascontiguousarray(table_bf16_bits, np.uint16)
+        _lib.check(lib.b200_llama_set_embedding(self._h, t.ctypes.data))
+
+    def set_norm(self, layer: int, which: int, w_bf16_bits: np.ndarray):
+        t = np.ascontiguousarray(w_bf16_bits, np.uint16)
+        _lib.check(lib.b200_llama_set_norm(self._h, layer, which, t.ctypes.data))
+
+    def finalize(self):
+        _lib.check(lib.b200_llama_finalize(self._h))
+
+    def random_init(self, mode: int, seed: int = 1):
+        _lib.check(lib.b200_llama_random_init(self._h, mode, seed))
+
+    def step(self, kv: PagedKVCache, descs: Sequence[Sequence[int]], prefill_tokens: Sequence[int] = ()):
+        """b200_llama_step with host buffers.  Returns (next token per request, free pages)."""
+        n = len(descs)
+        d = (PackDesc * max(n, 1))()
+        for i, (slot, count, base, src) in enumerate(descs):
+            d[i].seq_slot, d[i].count, d[i].base_pos, d[i].src_offset = slot, count, base, src
+        pt = (C.c_uint32 * max(len(prefill_tokens), 1))(*[int(t) for t in prefill_tokens])
+        out = (C.c_uint32 * max(n, 1))()
+        free = C.c_int32()
+        _lib.check(lib.b200_llama_step(self._h, kv._h, d, n, pt, len(prefill_tokens), out, C.byref(free), _stream()))
+        return np.array([out[i] for i in range(n)], np.uint32), free.value
+
+    def forward_device(self, kv: PagedKVCache, d_desc: torch.Tensor, total_rows: int,
+                       d_prefill: Optional[torch.Tensor] = None):
+        """b200_llama_forward on device-resident descriptors (asynchronous)."""
+        _lib.check(lib.b200_llama_forward(self._h, kv._h, _ptr(d_desc), d_desc.shape[0], total_rows, _ptr(d_prefill),
+                                          _stream()))
+
+    def last_logits(self, n_req: int) -> np.ndarray:
+        out = np.zeros((n_req, self.cfg.vocab), np.uint16)
+        _lib.check(lib.b200_llama_last_logits(self._h, out.ctypes.data, n_req))
+        return (out.astype(np.uint32) << 16).view(np.float32)
+
+    def launch_count(self) -> int:
+        return int(lib.b200_llama_launch_count(self._h))
+
+    def profile_enable(self, on: bool = True):
+        lib.b200_llama_profile_enable(self._h, int(on))
+
+    def profile_collect(self):
+        """{category: (milliseconds, calls)} for attention / matmul / rope+append / other."""
+        ms, calls = (C.c_double * 4)(), (C.c_int64 * 4)()
+        _lib.check(lib.b200_llama_profile_collect(self._h, ms, calls))
+        names = ("attention", "matmul", "rope_append", "other")
+        return {n: (ms[i], calls[i]) for i, n in enumerate(names)}

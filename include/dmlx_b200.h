@@ -268,15 +268,21 @@ b200_status b200_argmax(const void* d_logits, int32_t rows, int32_t vocab, uint3
 /* y[T,N] = x[T,K] . dequant(W[N,K])^T  (quantizedMatmul call sites src/models/llama.zig:127,367,596;
  * gatherQmm src/models/deepseek_v4.zig:976).  Weights are repacked once into a tile-major device
  * layout; the handle owns that memory. */
-enum { B200_Q_AFFINE4_G64 = 0, B200_Q_MXFP4_G32 = 1 };
+enum { B200_Q_AFFINE4_G64 = 0, B200_Q_MXFP4_G32 = 1, B200_Q_BF16 = 2 };
 typedef struct b200_qweight b200_qweight;
 /* affine: packed uint32 [N, K/8] (8 nibbles per word, least significant first), scales and biases
  * bf16 [N, K/64]  (src/kvcache/paged.zig:358,1199-1208; src/models/llama_loader.zig:262-279).
  * mxfp4: packed uint8 [N, K/2] (low nibble = even element), E8M0 scales uint8 [N, K/32], no
  * biases (src/models/deepseek_v4_loader.zig:121-122,839-920).  Host pointers.
+ * bf16  : dense bf16 [N, K] in h_packed, no scales (the unquantised branch of `linear`,
+ *         src/models/llama.zig:129).
  * n_experts > 1 stacks [E, N, K] for grouped use. */
 b200_status b200_qweight_create(int32_t mode, int32_t n_experts, int32_t n, int32_t k,
                                 const void* h_packed, const void* h_scales, const void* h_biases,
+                                b200_qweight** out);
+/* Synthetic weights generated on the device (benchmarks with random-init models): uniform random
+ * codes with fixed plausible scales.  N a multiple of 128, K of 64. */
+b200_status b200_qweight_random(int32_t mode, int32_t n_experts, int32_t n, int32_t k, uint32_t seed,
                                 b200_qweight** out);
 void b200_qweight_destroy(b200_qweight* w);
 enum { B200_EPI_NONE = 0, B200_EPI_RESIDUAL = 1, B200_EPI_SWIGLU = 2 };
@@ -290,6 +296,53 @@ b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void*
 
 /* Reads and clears the matmul kernels' error word (set when a bounded wait ran out). */
 b200_status b200_qmm_error_word(int32_t* out);
+
+/* ---- LLaMA-architecture decode step over a packed ragged batch --------------------------------- */
+/* Stands in for ModelVTable.forward + the greedy branch of generateBatchStep
+ * (src/generation.zig:47-53,104-145) with LlamaModel.forward underneath
+ * (src/models/llama.zig:556-609). */
+typedef struct b200_llama_config {
+  int32_t n_layers, hidden, n_heads, n_kv_heads, head_dim, ffn, vocab; /* LlamaConfig, src/models/llama.zig:40-70 */
+  int32_t max_rows;  /* largest packed batch (rows) */
+  int32_t max_reqs;  /* most requests in one step */
+  int32_t max_seqs;  /* sequence slots of the page pool it will run on */
+  float rms_eps;
+  float rope_theta;
+} b200_llama_config;
+typedef struct b200_llama b200_llama;
+enum { B200_W_Q = 0, B200_W_K = 1, B200_W_V = 2, B200_W_O = 3, B200_W_GATE = 4, B200_W_UP = 5, B200_W_DOWN = 6,
+       B200_W_LM_HEAD = 7 };
+b200_status b200_llama_create(const b200_llama_config* cfg, b200_llama** out);
+void b200_llama_destroy(b200_llama* m);
+/* One projection matrix in the reference's layout ([out, in]; quantised triples as produced by the
+ * loader, src/models/llama_loader.zig:245-279).  q/k/v and gate/up are fused at finalize. */
+b200_status b200_llama_set_linear(b200_llama* m, int32_t layer, int32_t which, int32_t mode,
+                                  const void* h_packed, const void* h_scales, const void* h_biases);
+b200_status b200_llama_set_embedding(b200_llama* m, const void* h_bf16);          /* [vocab, hidden] */
+/* layer < 0: final norm; which: 0 = attention norm, 1 = ffn norm.  bf16 [hidden]. */
+b200_status b200_llama_set_norm(b200_llama* m, int32_t layer, int32_t which, const void* h_bf16);
+b200_status b200_llama_finalize(b200_llama* m);
+/* Synthetic random-init model generated on the device (benchmarks). */
+b200_status b200_llama_random_init(b200_llama* m, int32_t mode, uint32_t seed);
+/* One engine step with host buffers: descriptors and prefill tokens in, one greedy token per
+ * request out (first strict max, src/sampling.zig:22-39).  Copies, runs the whole stack, copies
+ * back and synchronises the stream.  out_free_pages (optional) receives the pool's free count. */
+b200_status b200_llama_step(b200_llama* m, b200_kv* kv, const b200_pack_desc* h_desc, int32_t n_req,
+                            const uint32_t* h_prefill_tokens, int32_t n_prefill_tokens,
+                            uint32_t* h_next_tokens, int32_t* out_free_pages, void* stream);
+/* The same step on device-resident inputs, asynchronous on `stream` (no copies, no sync). */
+b200_status b200_llama_forward(b200_llama* m, b200_kv* kv, const b200_pack_desc* d_desc, int32_t n_req,
+                               int32_t total_rows, const uint32_t* d_prefill_tokens, void* stream);
+void b200_llama_device_buffers(b200_llama* m, b200_pack_desc** d_desc, uint32_t** d_prefill,
+                               uint32_t** d_next);
+/* bf16 logits [n_req, vocab] of the last step's sampled rows (tests). */
+b200_status b200_llama_last_logits(b200_llama* m, void* h_bf16_out, int32_t n_req);
+int64_t b200_llama_launch_count(const b200_llama* m);
+/* CUDA-event timing of the step's kernels by category (0 attention, 1 matmuls, 2 rope + KV append,
+ * 3 the rest); collect() synchronises, fills ms[4] and calls[4], and clears the record.  Stands in
+ * for the reference's per-step timing logs (src/models/expert_stream.zig:36-51 TokenStepMetrics). */
+void b200_llama_profile_enable(b200_llama* m, int32_t on);
+b200_status b200_llama_profile_collect(b200_llama* m, double* ms, int64_t* calls);
 
 #ifdef __cplusplus
 }
