@@ -198,6 +198,9 @@ def run_llama(args, rank, world, local):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    # a stream of our own: decode steps are replayed as CUDA graphs, which the legacy default
+    # stream cannot capture
+    torch.cuda.set_stream(torch.cuda.Stream())
     c = dict(L8)
     if args.layers:
         c["n_layers"] = args.layers
@@ -249,14 +252,17 @@ def run_llama(args, rank, world, local):
         sampler.start()
     # ---- device-resident: descriptors already in HBM, no host copies in the timed region ----
     d = device_descs(W + K)
+    cur = torch.empty_like(d[0])  # fixed address: decode steps of one shape replay one CUDA graph
     for i in range(W):
-        model.forward_device(kv, d[i], n_req)
+        cur.copy_(d[i])
+        model.forward_device(kv, cur, n_req)
     barrier()
     launches0 = model.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for i in range(W, W + K):
-        model.forward_device(kv, d[i], n_req)
+        cur.copy_(d[i])
+        model.forward_device(kv, cur, n_req)
     e1.record()
     barrier()
     total_ms = e0.elapsed_time(e1)
@@ -268,7 +274,8 @@ def run_llama(args, rank, world, local):
     d = device_descs(P)
     model.profile_enable(True)
     for i in range(P):
-        model.forward_device(kv, d[i], n_req)
+        cur.copy_(d[i])
+        model.forward_device(kv, cur, n_req)
     prof = model.profile_collect()
     model.profile_enable(False)
     live_tokens = float(lens.sum() + n_req * (P + 1) / 2.0)

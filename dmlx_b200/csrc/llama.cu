@@ -10,6 +10,7 @@
 
 #include <cstring>
 #include <map>
+#include <tuple>
 #include <vector>
 
 #include "common.h"
@@ -52,6 +53,12 @@ struct b200_llama {
   int32_t* h_state = nullptr;  // [8] pool state words + [1] matmul error word
   int last_n_req = 0;
   long long launches = 0;  // kernels launched by forward calls so far
+  // CUDA graphs of decode-only steps, keyed by (requests, device descriptor pointer, stream): the
+  // first step of a shape runs eagerly (it may grow scratch buffers), the second is captured,
+  // later ones replay the graph.
+  bool graphs_on = true;
+  struct GraphEntry { int seen = 0; cudaGraphExec_t exec = nullptr; };
+  std::map<std::tuple<int, const void*, const void*, void*>, GraphEntry> graphs;
   // optional CUDA-event timing per category: 0 attention, 1 matmuls, 2 rope + KV append, 3 the rest
   bool prof_on = false;
   std::vector<cudaEvent_t> prof_events;  // pairs
@@ -157,6 +164,7 @@ void b200_llama_destroy(b200_llama* m) {
   if (m->h_next) cudaFreeHost(m->h_next);
   if (m->h_state) cudaFreeHost(m->h_state);
   for (cudaEvent_t e : m->prof_events) cudaEventDestroy(e);
+  for (auto& g : m->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
   delete m;
 }
 
@@ -284,8 +292,43 @@ b200_status b200_llama_random_init(b200_llama* m, int32_t mode, uint32_t seed) {
   return B200_OK;
 }
 
+static b200_status llama_forward_eager(b200_llama* m, b200_kv* kv, const b200_pack_desc* d_desc, int32_t n_req,
+                                       int32_t total_rows, const uint32_t* d_prefill_tokens, void* stream);
+
 b200_status b200_llama_forward(b200_llama* m, b200_kv* kv, const b200_pack_desc* d_desc, int32_t n_req, int32_t total_rows,
                                const uint32_t* d_prefill_tokens, void* stream) {
+  // Decode-only steps (one row per request) are launch-bound at small batch: replay them as a graph.
+  // (the legacy default stream cannot be captured)
+  if (!m->graphs_on || m->prof_on || total_rows != n_req || n_req <= 0 || !m->finalized || stream == nullptr)
+    return llama_forward_eager(m, kv, d_desc, n_req, total_rows, d_prefill_tokens, stream);
+  auto& ge = m->graphs[std::make_tuple((int)n_req, (const void*)d_desc, (const void*)kv, stream)];
+  ge.seen += 1;
+  if (ge.seen == 1) return llama_forward_eager(m, kv, d_desc, n_req, total_rows, d_prefill_tokens, stream);
+  cudaStream_t cs = (cudaStream_t)stream;
+  if (!ge.exec) {
+    if (m->graphs.size() > 64) {  // bounded cache: drop everything else
+      for (auto& kvp : m->graphs) if (kvp.second.exec && &kvp.second != &ge) { cudaGraphExecDestroy(kvp.second.exec); kvp.second.exec = nullptr; kvp.second.seen = 0; }
+    }
+    cudaGraph_t graph = nullptr;
+    B200_CUDA_TRY(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal));
+    const long long before = m->launches;
+    b200_status st = llama_forward_eager(m, kv, d_desc, n_req, total_rows, d_prefill_tokens, stream);
+    m->launches = before;
+    cudaError_t e = cudaStreamEndCapture(cs, &graph);
+    if (st != B200_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+    if (e != cudaSuccess) { b200_set_error("graph capture failed: %s", cudaGetErrorString(e)); cudaGetLastError(); return B200_ERR_CUDA; }
+    e = cudaGraphInstantiate(&ge.exec, graph, 0);
+    cudaGraphDestroy(graph);
+    if (e != cudaSuccess) { ge.exec = nullptr; b200_set_error("graph instantiate failed: %s", cudaGetErrorString(e)); return B200_ERR_CUDA; }
+  }
+  B200_CUDA_TRY(cudaGraphLaunch(ge.exec, cs));
+  m->last_n_req = n_req;
+  m->launches += 5 + 15LL * m->cfg.n_layers + 6;
+  return B200_OK;
+}
+
+static b200_status llama_forward_eager(b200_llama* m, b200_kv* kv, const b200_pack_desc* d_desc, int32_t n_req,
+                                       int32_t total_rows, const uint32_t* d_prefill_tokens, void* stream) {
   if (!m->finalized) { b200_set_error("llama: weights not finalized"); return B200_ERR_INVALID_ARGUMENT; }
   const b200_llama_config& c = m->cfg;
   if (n_req < 0 || n_req > c.max_reqs || total_rows < 0 || total_rows > c.max_rows) {
@@ -326,8 +369,9 @@ b200_status b200_llama_forward(b200_llama* m, b200_kv* kv, const b200_pack_desc*
   STEP(b200_scatter_tokens(m->d_next, d_desc, m->d_last_token, n_req, stream));
 #undef STEP
 #undef STEP_CAT
-  // pack 2, reserve 2, embed 1, per layer 11 (attention = plan + main + combine), tail 5
-  m->launches += 5 + 11LL * c.n_layers + 5;
+  // pack 2, reserve 2, embed 1; per layer 15 (each matmul = main + finish, attention = plan +
+  // main + combine); tail 6
+  m->launches += 5 + 15LL * c.n_layers + 6;
   return B200_OK;
 }
 
@@ -378,6 +422,7 @@ b200_status b200_llama_last_logits(b200_llama* m, void* h_bf16_out, int32_t n_re
 }
 
 int64_t b200_llama_launch_count(const b200_llama* m) { return m->launches; }
+void b200_llama_enable_graphs(b200_llama* m, int32_t on) { m->graphs_on = on != 0; }
 
 // CUDA-event timing of the step's kernels by category (0 attention, 1 matmuls, 2 rope + KV append,
 // 3 the rest).  collect() synchronises the device, adds the elapsed time of every recorded call

@@ -21,8 +21,8 @@
 //     block to bf16 into a 128B-swizzled K-major tile (1 row per thread); warp 5 issues 4
 //     tcgen05.mma (M128 x N x K16) accumulating in tensor memory and commits to free the stage.
 //     After the last chunk warps 0-3 read the accumulator with tcgen05.ld.
-// Split-K partials go to an f32 scratch; the last CTA to arrive for an output tile sums them in
-// split order (deterministic), applies the epilogue and writes bf16.  No CTA waits on another.
+// Split-K partials go to an f32 scratch; a finish kernel sums them in split order (deterministic),
+// applies the epilogue (residual add, SwiGLU) and writes bf16.  No CTA waits on another.
 #include <cuda.h>
 #include <cuda_bf16.h>
 
@@ -88,52 +88,55 @@ __device__ __forceinline__ void row_params(const unsigned char* blk, int r, int 
   }
 }
 
-// ---- split-K finish: the last CTA of a tile reduces, applies the epilogue, writes bf16 ----------
-__device__ void qmm_finish_tile(const QmmArgs& a, int tile_id, int nt, int t0, int split_count) {
-  __shared__ int s_last;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int prev = atomicAdd(&a.counters[tile_id], 1);
-    s_last = (prev == split_count - 1);
+// ---- split-K finish: sums the partial tiles in split order (deterministic), applies the epilogue,
+// writes bf16.  One thread per 4 consecutive output columns of one row, so the whole GPU takes
+// part and every thread has `splits` independent 16-byte loads in flight.
+__global__ void qmm_finish_kernel(QmmArgs a, int splits, int tts) {
+  const int n4 = a.nt * (kTileN / 4);
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)a.rows * n4) return;
+  const int token = (int)(idx / n4), c4 = (int)(idx % n4);
+  const int nt = c4 / (kTileN / 4), r = (c4 % (kTileN / 4)) * 4, n = nt * kTileN + r;
+  if (n >= a.n) return;
+  const int tt = token / a.tn, t = token - tt * a.tn;
+  const float4* p = reinterpret_cast<const float4*>(a.ws + (((size_t)(nt * tts + tt) * splits) * a.tn + t) * kTileN + r);
+  const size_t split_stride = (size_t)a.tn * kTileN / 4;  // in float4
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  int s = 0;
+  for (; s + 4 <= splits; s += 4) {
+    const float4 v0 = p[(size_t)s * split_stride], v1 = p[(size_t)(s + 1) * split_stride];
+    const float4 v2 = p[(size_t)(s + 2) * split_stride], v3 = p[(size_t)(s + 3) * split_stride];
+    acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
+    acc.x += v1.x; acc.y += v1.y; acc.z += v1.z; acc.w += v1.w;
+    acc.x += v2.x; acc.y += v2.y; acc.z += v2.z; acc.w += v2.w;
+    acc.x += v3.x; acc.y += v3.y; acc.z += v3.z; acc.w += v3.w;
   }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  const float* base = a.ws + (size_t)tile_id * split_count * a.tn * kTileN;
-  const int n0 = nt * kTileN;
+  for (; s < splits; ++s) {
+    const float4 v = p[(size_t)s * split_stride];
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  const float rs = a.row_scale(token);
   if (a.epilogue == B200_EPI_SWIGLU) {
-    const int n_out = a.n / 2;
-    for (int idx = threadIdx.x; idx < a.tn * (kTileN / 2); idx += blockDim.x) {
-      const int t = idx / (kTileN / 2), rp = idx % (kTileN / 2);
-      const int token = t0 + t, n = n0 + 2 * rp;
-      if (token >= a.rows || n >= a.n) continue;
-      float g = 0.f, u = 0.f;
-      for (int s = 0; s < split_count; ++s) {
-        const float* p = base + ((size_t)s * a.tn + t) * kTileN + 2 * rp;
-        g += p[0];
-        u += p[1];
-      }
-      if (a.swiglu_limit > 0.f) {
-        g = fminf(g, a.swiglu_limit);
-        u = fminf(fmaxf(u, -a.swiglu_limit), a.swiglu_limit);
-      }
-      const float act = g / (1.0f + __expf(-g)) * u;
-      a.y[(size_t)a.row_base_out(token) * n_out + n / 2] = __float2bfloat16(act * a.row_scale(token));
+    float g0 = acc.x, u0 = acc.y, g1 = acc.z, u1 = acc.w;
+    if (a.swiglu_limit > 0.f) {
+      const float L = a.swiglu_limit;
+      g0 = fminf(g0, L); g1 = fminf(g1, L);
+      u0 = fminf(fmaxf(u0, -L), L); u1 = fminf(fmaxf(u1, -L), L);
     }
+    const float y0 = g0 / (1.0f + __expf(-g0)) * u0 * rs, y1 = g1 / (1.0f + __expf(-g1)) * u1 * rs;
+    *reinterpret_cast<__nv_bfloat162*>(a.y + (size_t)a.row_base_out(token) * (a.n / 2) + n / 2) = __floats2bfloat162_rn(y0, y1);
   } else {
-    for (int idx = threadIdx.x; idx < a.tn * kTileN; idx += blockDim.x) {
-      const int t = idx / kTileN, r = idx % kTileN;
-      const int token = t0 + t, n = n0 + r;
-      if (token >= a.rows || n >= a.n) continue;
-      float acc = 0.f;
-      for (int s = 0; s < split_count; ++s) acc += base[((size_t)s * a.tn + t) * kTileN + r];
-      const size_t o = (size_t)a.row_base_out(token) * a.n + n;
-      if (a.epilogue == B200_EPI_RESIDUAL) acc += __bfloat162float(a.residual[o]);
-      a.y[o] = __float2bfloat16(acc * a.row_scale(token));
+    const size_t o = (size_t)a.row_base_out(token) * a.n + n;
+    if (a.epilogue == B200_EPI_RESIDUAL) {
+      const uint2 rv = *reinterpret_cast<const uint2*>(a.residual + o);
+      acc.x += ptx::bf16_lo(rv.x); acc.y += ptx::bf16_hi(rv.x); acc.z += ptx::bf16_lo(rv.y); acc.w += ptx::bf16_hi(rv.y);
     }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * rs, acc.y * rs), hi = __floats2bfloat162_rn(acc.z * rs, acc.w * rs);
+    uint2 ov;
+    ov.x = *reinterpret_cast<uint32_t*>(&lo);
+    ov.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(a.y + o) = ov;
   }
-  if (threadIdx.x == 0) a.counters[tile_id] = 0;
 }
 
 // ---- GEMV kernel ---------------------------------------------------------------------------------
@@ -202,7 +205,6 @@ __global__ void __launch_bounds__(kTileN) qmm_simt_kernel(QmmArgs a) {
   float* wsp = a.ws + ((size_t)tile_id * gridDim.y + split) * a.tn * kTileN;
 #pragma unroll
   for (int t = 0; t < TT; ++t) wsp[(size_t)t * kTileN + r] = acc[t];
-  qmm_finish_tile(a, tile_id, nt, t0, gridDim.y);
 }
 
 // ---- tcgen05 kernel ------------------------------------------------------------------------------
@@ -328,19 +330,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
   ptx::tc_fence_before_sync();
   const int any_bad = __syncthreads_or(!ok);
   if (warp == 5) ptx::tmem_dealloc(tmem_base, ncols);
-  if (any_bad) return;
-  qmm_finish_tile(a, nt * gridDim.z + tt, nt, t0, gridDim.y);
+  (void)any_bad;
 }
 
 // ---- host-side state -------------------------------------------------------------------------------
 float* g_ws = nullptr;
 size_t g_ws_bytes = 0;
-int* g_counters = nullptr;
-int g_counters_n = 0;
 int* g_err = nullptr;
 int g_sms = 0;
 
-b200_status ensure_state(size_t ws_bytes, int n_counters) {
+b200_status ensure_state(size_t ws_bytes) {
   if (!g_err) {
     B200_CUDA_TRY(cudaMalloc((void**)&g_err, sizeof(int)));
     B200_CUDA_TRY(cudaMemset(g_err, 0, sizeof(int)));
@@ -356,15 +355,6 @@ b200_status ensure_state(size_t ws_bytes, int n_counters) {
     B200_CUDA_TRY(cudaMalloc((void**)&g_ws, want));
     g_ws_bytes = want;
   }
-  if (n_counters > g_counters_n) {
-    B200_CUDA_TRY(cudaDeviceSynchronize());
-    if (g_counters) cudaFree(g_counters);
-    g_counters = nullptr;
-    int want = std::max(n_counters, 1 << 16);
-    B200_CUDA_TRY(cudaMalloc((void**)&g_counters, sizeof(int) * want));
-    B200_CUDA_TRY(cudaMemset(g_counters, 0, sizeof(int) * want));
-    g_counters_n = want;
-  }
   return B200_OK;
 }
 
@@ -375,11 +365,25 @@ b200_status make_x_map(CUtensorMap* map, const void* x, int rows, int k, int box
   return b200_make_tensor_map(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, dims, strides, box);
 }
 
-int pick_splits(int tiles, int kc, int sms) {
-  // Enough CTAs to fill the machine about twice, but at least 4 chunks per split.
-  int want = (2 * sms + tiles - 1) / tiles;
-  int max_s = std::max(1, kc / 4);
-  return std::max(1, std::min(want, max_s));
+// Number of K splits for `tiles` output tiles with `ctas_per_sm` resident CTAs per SM: the
+// smallest count whose grid comes closest to a whole number of waves, each split keeping at
+// least 4 chunks.
+int pick_splits(int tiles, int kc, int sms, int ctas_per_sm) {
+  const int slots = sms * ctas_per_sm;
+  const int max_s = std::max(1, std::min(16, kc / 4));
+  int best = 1;
+  double best_eff = 0.0;
+  for (int sp = 1; sp <= max_s; ++sp) {
+    const int cps = (kc + sp - 1) / sp;
+    const int real = (kc + cps - 1) / cps;
+    if (real != sp) continue;
+    const long long ctas = (long long)tiles * sp;
+    const long long waves = (ctas + slots - 1) / slots;
+    // useful work / occupied time, with a small penalty per split for its fixed cost
+    const double eff = (double)ctas / (double)(waves * slots) * (double)cps / (double)(cps + 2);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = sp; }
+  }
+  return best;
 }
 
 }  // namespace
@@ -506,21 +510,30 @@ extern "C" void b200_qweight_destroy(b200_qweight* w) {
 }
 
 // ---- launch -------------------------------------------------------------------------------------------
+static b200_status launch_finish(const QmmArgs& a, int splits, int tts, cudaStream_t s) {
+  const long long threads = (long long)a.rows * a.nt * (kTileN / 4);
+  qmm_finish_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(a, splits, tts);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
 template <int MODE>
 static b200_status launch_simt(QmmArgs& a, int rows, cudaStream_t s) {
   constexpr int TT = 4;
   a.tn = TT;
   const int tts = (rows + TT - 1) / TT;
   const int tiles = a.nt * tts;
-  const int splits0 = pick_splits(tiles, a.kc, g_sms ? g_sms : 148);
+  b200_status st = ensure_state(0);
+  if (st != B200_OK) return st;
+  const int splits0 = pick_splits(tiles, a.kc, g_sms, 8);
   a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
   const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
-  b200_status st = ensure_state((size_t)tiles * splits * TT * kTileN * sizeof(float), tiles);
+  st = ensure_state((size_t)tiles * splits * TT * kTileN * sizeof(float));
   if (st != B200_OK) return st;
-  a.ws = g_ws; a.counters = g_counters; a.err = g_err;
+  a.ws = g_ws; a.err = g_err;
   qmm_simt_kernel<MODE, TT><<<dim3(a.nt, splits, tts), kTileN, 0, s>>>(a);
   B200_LAUNCH_CHECK();
-  return B200_OK;
+  return launch_finish(a, splits, tts, s);
 }
 
 template <int MODE>
@@ -529,14 +542,8 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
   a.tn = tn;
   const int tts = (rows + tn - 1) / tn;
   const int tiles = a.nt * tts;
-  b200_status st = ensure_state(0, 0);
+  b200_status st = ensure_state(0);
   if (st != B200_OK) return st;
-  const int splits0 = pick_splits(tiles, a.kc, g_sms);
-  a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
-  const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
-  st = ensure_state((size_t)tiles * splits * tn * kTileN * sizeof(float), tiles);
-  if (st != B200_OK) return st;
-  a.ws = g_ws; a.counters = g_counters; a.err = g_err;
   const int stage_stride = kTileN * 128 + tn * 128 + kRawStride;
   static int smem_budget[3] = {0, 0, 0};  // opt-in dynamic shared memory available to this kernel
   if (smem_budget[MODE] == 0) {
@@ -550,19 +557,29 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
     smem_budget[MODE] = budget;
   }
   const int fixed = 1024 /*alignment slack*/ + 8 * (3 * 8 + 2) + 16;
-  a.stages = std::max(2, std::min(6, (std::min(smem_budget[MODE], 200 * 1024) - fixed) / stage_stride));
+  // Small token tiles leave room for two CTAs per SM (more weight bytes in flight); large ones
+  // take the whole SM.
+  const int per_cta = tn <= 64 ? 108 * 1024 : std::min(smem_budget[MODE], 220 * 1024);
+  a.stages = std::max(2, std::min(8, (per_cta - fixed) / stage_stride));
+  const int ctas_per_sm = tn <= 64 ? 2 : 1;
   const size_t smem = (size_t)a.stages * stage_stride + fixed;
   if ((int)smem > smem_budget[MODE]) {
     b200_set_error("qmm: %zu bytes of shared memory needed, %d available", smem, smem_budget[MODE]);
     return B200_ERR_CAPACITY;
   }
+  const int splits0 = pick_splits(tiles, a.kc, g_sms, ctas_per_sm);
+  a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
+  const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
+  st = ensure_state((size_t)tiles * splits * tn * kTileN * sizeof(float));
+  if (st != B200_OK) return st;
+  a.ws = g_ws; a.err = g_err;
   CUtensorMap xmap;
   st = make_x_map(&xmap, a.x, rows, a.k, tn);
   if (st != B200_OK) return st;
   a.x_row0 = 0;
   qmm_tc_kernel<MODE><<<dim3(a.nt, splits, tts), kTcThreads, smem, s>>>(xmap, a);
   B200_LAUNCH_CHECK();
-  return B200_OK;
+  return launch_finish(a, splits, tts, s);
 }
 
 extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,

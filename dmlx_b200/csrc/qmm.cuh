@@ -17,7 +17,6 @@ struct QmmArgs {
   const __nv_bfloat16* residual;
   const float* row_scales;      // optional per-row multiplier applied in the epilogue
   float* ws;                    // split-K scratch: [tile][split][tn][128] f32
-  int* counters;                // one arrival counter per output tile, zero between launches
   int* err;                     // device error word
   int rows, n, k, nt, kc;
   int chunks_per_split, tn, stages;

@@ -332,6 +332,9 @@ class LlamaModel:
     def launch_count(self) -> int:
         return int(lib.b200_llama_launch_count(self._h))
 
+    def enable_graphs(self, on: bool = True):
+        lib.b200_llama_enable_graphs(self._h, int(on))
+
     def profile_enable(self, on: bool = True):
         lib.b200_llama_profile_enable(self._h, int(on))
 

@@ -338,6 +338,8 @@ void b200_llama_device_buffers(b200_llama* m, b200_pack_desc** d_desc, uint32_t*
 /* bf16 logits [n_req, vocab] of the last step's sampled rows (tests). */
 b200_status b200_llama_last_logits(b200_llama* m, void* h_bf16_out, int32_t n_req);
 int64_t b200_llama_launch_count(const b200_llama* m);
+/* Decode-only steps are replayed as CUDA graphs by default (on = 0 turns that off). */
+void b200_llama_enable_graphs(b200_llama* m, int32_t on);
 /* CUDA-event timing of the step's kernels by category (0 attention, 1 matmuls, 2 rope + KV append,
  * 3 the rest); collect() synchronises, fills ms[4] and calls[4], and clears the record.  Stands in
  * for the reference's per-step timing logs (src/models/expert_stream.zig:36-51 TokenStepMetrics). */
