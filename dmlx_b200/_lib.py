@@ -184,6 +184,22 @@ _sig("b200_llama_enable_graphs", None, vp, i32)
 _sig("b200_llama_profile_collect", i32, vp, P(C.c_double), P(C.c_int64))
 
 
+class MoeConfig(C.Structure):
+    _fields_ = [(n, i32) for n in ("hidden", "n_experts", "inter", "top_k", "scoring", "tile_rows", "max_tokens")] + \
+               [("route_scale", f32), ("swiglu_limit", f32), ("shared_swiglu_limit", f32)]
+
+
+_sig("b200_moe_route", i32, vp, i32, vp, i32, i32, i32, i32, f32, vp, vp, vp, vp)
+_sig("b200_moe_group", i32, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp)
+_sig("b200_moe_gather", i32, vp, vp, vp, i32, i32, i32, vp, vp, vp)
+_sig("b200_moe_grouped_qmm", i32, vp, vp, i32, vp, i32, vp, f32, vp, vp, i32, i32, vp)
+_sig("b200_moe_combine", i32, vp, vp, i32, i32, i32, vp, vp, vp)
+_sig("b200_moe_create", i32, P(MoeConfig), vp, P(f32), vp, vp, vp, vp, P(vp))
+_sig("b200_moe_destroy", None, vp)
+_sig("b200_moe_forward", i32, vp, vp, i32, vp, vp)
+_sig("b200_moe_last_routing", i32, vp, i32, vp, vp, vp)
+
+
 class B200Error(RuntimeError):
     def __init__(self, status: int):
         self.status = status

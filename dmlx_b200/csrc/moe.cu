@@ -1,0 +1,387 @@
+// Mixture-of-experts routing and the ragged grouped matmul around it.
+//
+//   route   : per token, f32 scoring of the router logits (softmax / sigmoid / sqrt-softplus),
+//             + selection bias, top-k with the tie rule of an ascending stable argsort's last k
+//             (src/moe_router.zig:59-96, src/models/deepseek_v4.zig:383-396,555-681): among equal
+//             scores the larger expert index wins, output in ascending (score, index) order;
+//             weights come from the unbiased scores.  One warp per token, no sort.
+//   group   : stable counting sort of the N*k assignments by expert
+//             (the two argsorts of src/models/deepseek_v4.zig:747-784): expert_offsets[E+1],
+//             order[N*k], inv_order[N*k], and the work items of the grouped matmul.
+//   gather  : x_sorted[p] = x[order[p] / k], row_scales[p] = weights[order[p]].
+//   grouped matmul : b200_qmm_grouped (tcgen05, one work item per expert token tile).
+//   combine : out[t] = sum_j y_sorted[inv_order[t*k + j]] (+ shared expert)
+//             (src/models/deepseek_v4.zig:809-819,1051).
+#include <cuda_bf16.h>
+
+#include <vector>
+
+#include "common.h"
+#include "qmm.cuh"
+
+namespace {
+
+constexpr int kMaxExperts = 1024;
+constexpr int kMaxTopK = 16;
+
+__device__ __forceinline__ bool beats(float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia > ib); }
+
+// One warp per token.  E <= 1024 (32 experts per lane).
+template <typename LogitT>
+__global__ void route_kernel(const LogitT* __restrict__ logits, const float* __restrict__ bias, int n_tokens, int n_experts,
+                             int k, int scoring, float route_scale, uint32_t* __restrict__ out_idx,
+                             float* __restrict__ out_w, int* __restrict__ counts) {
+  const int token = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (token >= n_tokens) return;
+  constexpr int PER = kMaxExperts / 32;
+  float sc[PER];      // unbiased scores
+  float ch[PER];      // scores used for the choice
+  const int per = (n_experts + 31) / 32;
+  float mx = -INFINITY;
+  for (int i = 0; i < per; ++i) {
+    const int e = i * 32 + lane;
+    float v = -INFINITY;
+    if (e < n_experts) v = (float)logits[(size_t)token * n_experts + e];
+    sc[i] = v;
+    mx = fmaxf(mx, v);
+  }
+  if (scoring == 0) {  // softmax in f32 (deepseek_v4.zig:562-564)
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int i = 0; i < per; ++i) {
+      const float e = (i * 32 + lane < n_experts) ? expf(sc[i] - mx) : 0.f;
+      sc[i] = e;
+      sum += e;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    for (int i = 0; i < per; ++i) sc[i] = sc[i] / sum;
+  } else if (scoring == 1) {  // sigmoid
+    for (int i = 0; i < per; ++i) sc[i] = 1.0f / (1.0f + expf(-sc[i]));
+  } else {  // sqrt(softplus)
+    for (int i = 0; i < per; ++i) sc[i] = sqrtf(log1pf(expf(sc[i])));
+  }
+  for (int i = 0; i < per; ++i) {
+    const int e = i * 32 + lane;
+    ch[i] = e < n_experts ? sc[i] + (bias ? bias[e] : 0.f) : -INFINITY;
+  }
+  // k rounds of warp arg-max under (score, index) order; results come out descending.
+  float sel_w[kMaxTopK];
+  int sel_e[kMaxTopK];
+  for (int r = 0; r < k; ++r) {
+    float bv = -INFINITY;
+    int be = -1, bi = -1;
+    for (int i = 0; i < per; ++i) {
+      const int e = i * 32 + lane;
+      if (e < n_experts && beats(ch[i], e, bv, be)) { bv = ch[i]; be = e; bi = i; }
+    }
+    float wv = bv;
+    int we = be;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, wv, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, we, o);
+      if (beats(ov, oe, wv, we)) { wv = ov; we = oe; }
+    }
+    // the owning lane retires the winner and publishes its unbiased score
+    float w_unbiased = 0.f;
+    if (we == be && bi >= 0) { w_unbiased = sc[bi]; ch[bi] = -INFINITY; }
+    w_unbiased = __shfl_sync(0xffffffffu, w_unbiased, we & 31);
+    sel_w[r] = w_unbiased;
+    sel_e[r] = we;
+  }
+  if (lane == 0) {
+    float denom = 1.0f;
+    if (scoring != 0) {  // non-softmax scores are renormalised over the selection (deepseek_v4.zig:663-672)
+      float s = 0.f;
+      for (int r = k - 1; r >= 0; --r) s += sel_w[r];  // ascending order, as the reference sums
+      denom = s + 1e-20f;
+    }
+    for (int r = 0; r < k; ++r) {
+      const int src = k - 1 - r;  // ascending (score, index)
+      out_idx[(size_t)token * k + r] = (uint32_t)sel_e[src];
+      out_w[(size_t)token * k + r] = (scoring != 0 ? sel_w[src] / denom : sel_w[src]) * route_scale;
+      if (counts) atomicAdd(&counts[sel_e[src]], 1);
+    }
+  }
+}
+
+// offsets = exclusive scan of counts; work items {expert, first row, rows} for tiles of `tile_rows`.
+__global__ void offsets_items_kernel(const int* __restrict__ counts, int n_experts, int tile_rows, int* __restrict__ offsets,
+                                     int4* __restrict__ items, int* __restrict__ n_items) {
+  __shared__ int s_off[kMaxExperts + 1], s_item[kMaxExperts + 1];
+  if (threadIdx.x == 0) {
+    int o = 0, it = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      s_off[e] = o;
+      s_item[e] = it;
+      o += counts[e];
+      it += (counts[e] + tile_rows - 1) / tile_rows;
+    }
+    s_off[n_experts] = o;
+    s_item[n_experts] = it;
+    *n_items = it;
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e <= n_experts; e += blockDim.x) offsets[e] = s_off[e];
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) {
+    const int cnt = s_off[e + 1] - s_off[e];
+    for (int t = 0, i = s_item[e]; t < cnt; t += tile_rows, ++i) items[i] = make_int4(e, s_off[e] + t, min(tile_rows, cnt - t), 0);
+  }
+}
+
+// One CTA per expert: collects, in flat order, the assignments routed to it (stable).
+__global__ void __launch_bounds__(1024) place_kernel(const uint32_t* __restrict__ indices, int n_assign,
+                                                     const int* __restrict__ offsets, int* __restrict__ order,
+                                                     int* __restrict__ inv_order) {
+  __shared__ int warp_sums[32];
+  __shared__ int s_base;
+  const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  if (tid == 0) s_base = offsets[e];
+  __syncthreads();
+  for (int start = 0; start < n_assign; start += blockDim.x) {
+    const int a = start + tid;
+    const int flag = (a < n_assign && (int)indices[a] == e) ? 1 : 0;
+    const unsigned bal = __ballot_sync(0xffffffffu, flag);
+    const int within = __popc(bal & ((1u << lane) - 1));
+    if (lane == 0) warp_sums[warp] = __popc(bal);
+    __syncthreads();
+    int before = 0, total = 0;
+    for (int w = 0; w < 32; ++w) {
+      const int v = warp_sums[w];
+      if (w < warp) before += v;
+      total += v;
+    }
+    const int base = s_base;
+    if (flag) {
+      const int pos = base + before + within;
+      order[pos] = a;
+      inv_order[a] = pos;
+    }
+    __syncthreads();
+    if (tid == 0) s_base = base + total;
+    __syncthreads();
+  }
+}
+
+__global__ void gather_sorted_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ order,
+                                     const float* __restrict__ weights, int k, int hidden,
+                                     __nv_bfloat16* __restrict__ x_sorted, float* __restrict__ row_scales) {
+  const int p = blockIdx.x, a = order[p];
+  const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(a / k) * hidden);
+  uint4* dst = reinterpret_cast<uint4*>(x_sorted + (size_t)p * hidden);
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
+  if (threadIdx.x == 0 && row_scales) row_scales[p] = weights[a];
+}
+
+__global__ void combine_kernel(const __nv_bfloat16* __restrict__ y_sorted, const int* __restrict__ inv_order, int k, int hidden,
+                               const __nv_bfloat16* __restrict__ shared_out, __nv_bfloat16* __restrict__ out) {
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < hidden / 2; i += blockDim.x) {
+    float2 acc = make_float2(0.f, 0.f);
+    for (int j = 0; j < k; ++j) {
+      const float2 v = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(y_sorted + (size_t)inv_order[t * k + j] * hidden)[i]);
+      acc.x += v.x; acc.y += v.y;
+    }
+    if (shared_out) {
+      const float2 v = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(shared_out + (size_t)t * hidden)[i]);
+      acc.x += v.x; acc.y += v.y;
+    }
+    reinterpret_cast<__nv_bfloat162*>(out + (size_t)t * hidden)[i] = __floats2bfloat162_rn(acc.x, acc.y);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+b200_status b200_moe_route(const void* d_logits, int32_t logits_are_f32, const float* d_bias, int32_t n_tokens,
+                           int32_t n_experts, int32_t k, int32_t scoring, float route_scale, uint32_t* d_indices,
+                           float* d_weights, int32_t* d_counts, void* stream) {
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (n_experts <= 0 || n_experts > kMaxExperts || k <= 0 || k > kMaxTopK || k > n_experts || scoring < 0 || scoring > 2) {
+    b200_set_error("route: need 1 <= k <= min(%d, E), E <= %d, scoring in {0,1,2}", kMaxTopK, kMaxExperts);
+    return B200_ERR_INVALID_ARGUMENT;
+  }
+  if (n_tokens <= 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (d_counts) B200_CUDA_TRY(cudaMemsetAsync(d_counts, 0, sizeof(int) * n_experts, s));
+  const int blocks = (n_tokens * 32 + 255) / 256;
+  if (logits_are_f32)
+    route_kernel<float><<<blocks, 256, 0, s>>>((const float*)d_logits, d_bias, n_tokens, n_experts, k, scoring, route_scale,
+                                               d_indices, d_weights, d_counts);
+  else
+    route_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)d_logits, d_bias, n_tokens, n_experts, k, scoring,
+                                                       route_scale, d_indices, d_weights, d_counts);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+b200_status b200_moe_group(const uint32_t* d_indices, const int32_t* d_counts, int32_t n_tokens, int32_t k,
+                           int32_t n_experts, int32_t tile_rows, int32_t* d_offsets, int32_t* d_order,
+                           int32_t* d_inv_order, void* d_items, int32_t* d_n_items, void* stream) {
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (n_experts <= 0 || n_experts > kMaxExperts || tile_rows <= 0) { b200_set_error("group: bad expert count or tile"); return B200_ERR_INVALID_ARGUMENT; }
+  if (n_tokens <= 0) return B200_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  offsets_items_kernel<<<1, 256, 0, s>>>(d_counts, n_experts, tile_rows, d_offsets, (int4*)d_items, d_n_items);
+  B200_LAUNCH_CHECK();
+  place_kernel<<<n_experts, 1024, 0, s>>>(d_indices, n_tokens * k, d_offsets, d_order, d_inv_order);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+b200_status b200_moe_gather(const void* d_x, const int32_t* d_order, const float* d_weights, int32_t n_assign, int32_t k,
+                            int32_t hidden, void* d_x_sorted, float* d_row_scales, void* stream) {
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (hidden % 8) { b200_set_error("gather: hidden must be a multiple of 8"); return B200_ERR_INVALID_ARGUMENT; }
+  if (n_assign <= 0) return B200_OK;
+  gather_sorted_kernel<<<n_assign, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)d_x, d_order, d_weights, k, hidden,
+                                                                  (__nv_bfloat16*)d_x_sorted, d_row_scales);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+b200_status b200_moe_grouped_qmm(const b200_qweight* w, const void* d_x_sorted, int32_t rows, void* d_y_sorted,
+                                 int32_t epilogue, const float* d_row_scales, float swiglu_limit, const void* d_items,
+                                 const int32_t* d_n_items, int32_t max_items, int32_t tile_rows, void* stream) {
+  if (tile_rows % 16 != 0 || tile_rows < 16 || tile_rows > 256) { b200_set_error("grouped qmm: tile_rows must be a multiple of 16 in 16..256"); return B200_ERR_INVALID_ARGUMENT; }
+  return b200_qmm_grouped(w, d_x_sorted, rows, d_y_sorted, epilogue, d_row_scales, swiglu_limit, (const int4*)d_items,
+                          d_n_items, max_items, tile_rows, stream);
+}
+
+b200_status b200_moe_combine(const void* d_y_sorted, const int32_t* d_inv_order, int32_t n_tokens, int32_t k,
+                             int32_t hidden, const void* d_shared_out, void* d_out, void* stream) {
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (hidden % 2) { b200_set_error("combine: hidden must be even"); return B200_ERR_INVALID_ARGUMENT; }
+  if (n_tokens <= 0) return B200_OK;
+  combine_kernel<<<n_tokens, 256, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)d_y_sorted, d_inv_order, k, hidden,
+                                                             (const __nv_bfloat16*)d_shared_out, (__nv_bfloat16*)d_out);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// One MoE layer: DSV4MoE.forward (src/models/deepseek_v4.zig:1010-1056) =
+// shared expert + gate (route) + SwitchGLU over the routed experts (:721-848) + sum.
+// ---------------------------------------------------------------------------------------------
+struct b200_moe {
+  b200_moe_config cfg{};
+  const b200_qweight *gate = nullptr, *exp_gu = nullptr, *exp_down = nullptr, *sh_gu = nullptr, *sh_down = nullptr;
+  float* d_bias = nullptr;
+  __nv_bfloat16 *logits = nullptr, *x_sorted = nullptr, *act_sorted = nullptr, *y_sorted = nullptr, *sh_act = nullptr,
+                *sh_out = nullptr;
+  uint32_t* indices = nullptr;
+  float *weights = nullptr, *row_scales = nullptr;
+  int *counts = nullptr, *offsets = nullptr, *order = nullptr, *inv_order = nullptr, *n_items = nullptr;
+  int4* items = nullptr;
+  int max_items = 0;
+};
+
+extern "C" {
+
+void b200_moe_destroy(b200_moe* m) {
+  if (!m) return;
+  void* ptrs[] = {m->d_bias, m->logits, m->x_sorted, m->act_sorted, m->y_sorted, m->sh_act, m->sh_out, m->indices, m->weights,
+                  m->row_scales, m->counts, m->offsets, m->order, m->inv_order, m->n_items, m->items};
+  for (void* p : ptrs) if (p) cudaFree(p);
+  delete m;
+}
+
+b200_status b200_moe_create(const b200_moe_config* c, const b200_qweight* gate, const float* h_bias,
+                            const b200_qweight* experts_gate_up, const b200_qweight* experts_down,
+                            const b200_qweight* shared_gate_up, const b200_qweight* shared_down, b200_moe** out) {
+  *out = nullptr;
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (!gate || !experts_gate_up || !experts_down || gate->n != c->n_experts || gate->k != c->hidden ||
+      experts_gate_up->n_experts != c->n_experts || experts_gate_up->n != 2 * c->inter || experts_gate_up->k != c->hidden ||
+      experts_down->n_experts != c->n_experts || experts_down->n != c->hidden || experts_down->k != c->inter ||
+      c->tile_rows % 16 != 0 || c->tile_rows < 16 || c->tile_rows > 256 || c->max_tokens <= 0) {
+    b200_set_error("moe: weight shapes do not match the configuration");
+    return B200_ERR_INVALID_ARGUMENT;
+  }
+  auto* m = new b200_moe();
+  m->cfg = *c;
+  m->gate = gate; m->exp_gu = experts_gate_up; m->exp_down = experts_down; m->sh_gu = shared_gate_up; m->sh_down = shared_down;
+  const size_t N = c->max_tokens, A = N * c->top_k;
+  m->max_items = c->n_experts + (int)((A + c->tile_rows - 1) / c->tile_rows);
+#define M_ALLOC(ptr, bytes)                                                                  \
+  do {                                                                                       \
+    if (cudaMalloc((void**)&(ptr), (bytes)) != cudaSuccess) {                                \
+      b200_set_error("moe: cudaMalloc(%zu) failed", (size_t)(bytes));                        \
+      cudaGetLastError();                                                                    \
+      b200_moe_destroy(m);                                                                   \
+      return B200_ERR_CUDA;                                                                  \
+    }                                                                                        \
+  } while (0)
+  M_ALLOC(m->logits, N * c->n_experts * 2);
+  M_ALLOC(m->indices, A * 4);
+  M_ALLOC(m->weights, A * 4);
+  M_ALLOC(m->row_scales, A * 4);
+  M_ALLOC(m->counts, sizeof(int) * c->n_experts);
+  M_ALLOC(m->offsets, sizeof(int) * (c->n_experts + 1));
+  M_ALLOC(m->order, A * 4);
+  M_ALLOC(m->inv_order, A * 4);
+  M_ALLOC(m->n_items, sizeof(int));
+  M_ALLOC(m->items, sizeof(int4) * m->max_items);
+  M_ALLOC(m->x_sorted, A * c->hidden * 2);
+  M_ALLOC(m->act_sorted, A * c->inter * 2);
+  M_ALLOC(m->y_sorted, A * c->hidden * 2);
+  if (shared_gate_up && shared_down) {
+    M_ALLOC(m->sh_act, N * (shared_gate_up->n / 2) * 2);
+    M_ALLOC(m->sh_out, N * c->hidden * 2);
+  }
+  if (h_bias) {
+    M_ALLOC(m->d_bias, sizeof(float) * c->n_experts);
+    cudaMemcpy(m->d_bias, h_bias, sizeof(float) * c->n_experts, cudaMemcpyHostToDevice);
+  }
+#undef M_ALLOC
+  *out = m;
+  return B200_OK;
+}
+
+b200_status b200_moe_forward(b200_moe* m, const void* d_x, int32_t n_tokens, void* d_out, void* stream) {
+  const b200_moe_config& c = m->cfg;
+  if (n_tokens > c.max_tokens) { b200_set_error("moe: %d tokens > max_tokens %d", n_tokens, c.max_tokens); return B200_ERR_CAPACITY; }
+  if (n_tokens <= 0) return B200_OK;
+  const int A = n_tokens * c.top_k;
+  b200_status st;
+#define STEP(call) do { if ((st = (call)) != B200_OK) return st; } while (0)
+  if (m->sh_gu) {  // shared expert on every token (deepseek_v4.zig:1017-1022, 489-517)
+    STEP(b200_qmm(m->sh_gu, d_x, n_tokens, m->sh_act, B200_EPI_SWIGLU, nullptr, c.shared_swiglu_limit, B200_QMM_AUTO, stream));
+    STEP(b200_qmm(m->sh_down, m->sh_act, n_tokens, m->sh_out, B200_EPI_NONE, nullptr, 0.f, B200_QMM_AUTO, stream));
+  }
+  STEP(b200_qmm(m->gate, d_x, n_tokens, m->logits, B200_EPI_NONE, nullptr, 0.f, B200_QMM_AUTO, stream));
+  STEP(b200_moe_route(m->logits, 0, m->d_bias, n_tokens, c.n_experts, c.top_k, c.scoring, c.route_scale, m->indices,
+                      m->weights, m->counts, stream));
+  STEP(b200_moe_group(m->indices, m->counts, n_tokens, c.top_k, c.n_experts, c.tile_rows, m->offsets, m->order,
+                      m->inv_order, m->items, m->n_items, stream));
+  STEP(b200_moe_gather(d_x, m->order, m->weights, A, c.top_k, c.hidden, m->x_sorted, m->row_scales, stream));
+  // gate/up with clipped SwiGLU and the routing score folded in before the down projection (:787-805)
+  STEP(b200_qmm_grouped(m->exp_gu, m->x_sorted, A, m->act_sorted, B200_EPI_SWIGLU, m->row_scales, c.swiglu_limit, m->items,
+                        m->n_items, m->max_items, c.tile_rows, stream));
+  STEP(b200_qmm_grouped(m->exp_down, m->act_sorted, A, m->y_sorted, B200_EPI_NONE, nullptr, 0.f, m->items, m->n_items,
+                        m->max_items, c.tile_rows, stream));
+  STEP(b200_moe_combine(m->y_sorted, m->inv_order, n_tokens, c.top_k, c.hidden, m->sh_out, d_out, stream));
+#undef STEP
+  return B200_OK;
+}
+
+// Routing results of the last forward (tests): indices [N,k] u32, weights [N,k] f32, offsets [E+1].
+b200_status b200_moe_last_routing(b200_moe* m, int32_t n_tokens, uint32_t* h_indices, float* h_weights, int32_t* h_offsets) {
+  const size_t A = (size_t)n_tokens * m->cfg.top_k;
+  B200_CUDA_TRY(cudaMemcpy(h_indices, m->indices, A * 4, cudaMemcpyDeviceToHost));
+  B200_CUDA_TRY(cudaMemcpy(h_weights, m->weights, A * 4, cudaMemcpyDeviceToHost));
+  B200_CUDA_TRY(cudaMemcpy(h_offsets, m->offsets, sizeof(int) * (m->cfg.n_experts + 1), cudaMemcpyDeviceToHost));
+  return B200_OK;
+}
+
+}  // extern "C"

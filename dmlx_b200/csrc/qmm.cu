@@ -91,16 +91,16 @@ __device__ __forceinline__ void row_params(const unsigned char* blk, int r, int 
 // ---- split-K finish: sums the partial tiles in split order (deterministic), applies the epilogue,
 // writes bf16.  One thread per 4 consecutive output columns of one row, so the whole GPU takes
 // part and every thread has `splits` independent 16-byte loads in flight.
-__global__ void qmm_finish_kernel(QmmArgs a, int splits, int tts) {
+__global__ void qmm_finish_kernel(QmmArgs a, int splits) {
   const int n4 = a.nt * (kTileN / 4);
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)a.rows * n4) return;
   const int token = (int)(idx / n4), c4 = (int)(idx % n4);
   const int nt = c4 / (kTileN / 4), r = (c4 % (kTileN / 4)) * 4, n = nt * kTileN + r;
   if (n >= a.n) return;
-  const int tt = token / a.tn, t = token - tt * a.tn;
-  const float4* p = reinterpret_cast<const float4*>(a.ws + (((size_t)(nt * tts + tt) * splits) * a.tn + t) * kTileN + r);
-  const size_t split_stride = (size_t)a.tn * kTileN / 4;  // in float4
+  const size_t n_pad = (size_t)a.nt * kTileN;
+  const float4* p = reinterpret_cast<const float4*>(a.ws + (size_t)token * n_pad + n);
+  const size_t split_stride = (size_t)a.rows * n_pad / 4;  // in float4
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   int s = 0;
   for (; s + 4 <= splits; s += 4) {
@@ -201,10 +201,10 @@ __global__ void __launch_bounds__(kTileN) qmm_simt_kernel(QmmArgs a) {
     }
     }
   }
-  const int tile_id = nt * gridDim.z + tt;
-  float* wsp = a.ws + ((size_t)tile_id * gridDim.y + split) * a.tn * kTileN;
+  const size_t n_pad = (size_t)a.nt * kTileN;
 #pragma unroll
-  for (int t = 0; t < TT; ++t) wsp[(size_t)t * kTileN + r] = acc[t];
+  for (int t = 0; t < TT; ++t)
+    if (t0 + t < a.rows) a.ws[((size_t)split * a.rows + t0 + t) * n_pad + nt * kTileN + r] = acc[t];
 }
 
 // ---- tcgen05 kernel ------------------------------------------------------------------------------
@@ -229,8 +229,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * stages + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int nt = blockIdx.x, split = blockIdx.y, tt = blockIdx.z;
-  const int t0 = tt * tn;
+  const int nt = blockIdx.x, split = blockIdx.y;
+  // Dense: blockIdx.z is a token tile.  Grouped: blockIdx.z is a work item {expert, first row,
+  // rows} of the expert-sorted batch; unused items leave before touching any barrier.
+  int t0 = blockIdx.z * tn, rows_here = min(tn, a.rows - t0);
+  const unsigned char* blocks = a.blocks;
+  if (a.items) {
+    if ((int)blockIdx.z >= *a.n_items) return;
+    const int4 it = a.items[blockIdx.z];
+    blocks += (size_t)it.x * a.expert_stride;
+    t0 = it.y;
+    rows_here = it.z;
+  }
   const int kc0 = split * a.chunks_per_split, kc1 = min(kc0 + a.chunks_per_split, a.kc);
   const int n_chunks = kc1 - kc0;
   constexpr int BB = block_bytes(MODE);
@@ -264,7 +274,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
         if (!ok) break;
         ptx::mbar_expect_tx(&loaded[s], BB + tn * 128);
         // dense bf16 blocks are stored in the swizzled K-major layout and land in the MMA tile directly
-        ptx::bulk_g2s(MODE == B200_Q_BF16 ? a_tile(s) : raw_blk(s), a.blocks + ((size_t)nt * a.kc + kc0 + i) * BB, BB,
+        ptx::bulk_g2s(MODE == B200_Q_BF16 ? a_tile(s) : raw_blk(s), blocks + ((size_t)nt * a.kc + kc0 + i) * BB, BB,
                       &loaded[s]);
         ptx::tma_load_2d(x_tile(s), &xmap, (kc0 + i) * kChunkK, a.x_row0 + t0, &loaded[s]);
       }
@@ -314,15 +324,15 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
     if (ok) ok = ptx::mbar_wait(accum_ready, 0);
     if (ok) {
       ptx::tc_fence_after_sync();
-      const int tile_id = nt * gridDim.z + tt;
-      float* wsp = a.ws + ((size_t)tile_id * gridDim.y + split) * tn * kTileN;
-      for (int c0 = 0; c0 < tn; c0 += 32) {
+      const size_t n_pad = (size_t)a.nt * kTileN;
+      float* wsp = a.ws + ((size_t)split * a.rows + t0) * n_pad + nt * kTileN;
+      for (int c0 = 0; c0 < rows_here; c0 += 32) {
         uint32_t v[32];
         ptx::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
         ptx::tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j)
-          if (c0 + j < tn) wsp[(size_t)(c0 + j) * kTileN + warp * 32 + lane] = __uint_as_float(v[j]);
+          if (c0 + j < rows_here) wsp[(size_t)(c0 + j) * n_pad + warp * 32 + lane] = __uint_as_float(v[j]);
       }
     }
   }
@@ -510,9 +520,9 @@ extern "C" void b200_qweight_destroy(b200_qweight* w) {
 }
 
 // ---- launch -------------------------------------------------------------------------------------------
-static b200_status launch_finish(const QmmArgs& a, int splits, int tts, cudaStream_t s) {
+static b200_status launch_finish(const QmmArgs& a, int splits, cudaStream_t s) {
   const long long threads = (long long)a.rows * a.nt * (kTileN / 4);
-  qmm_finish_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(a, splits, tts);
+  qmm_finish_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(a, splits);
   B200_LAUNCH_CHECK();
   return B200_OK;
 }
@@ -528,20 +538,22 @@ static b200_status launch_simt(QmmArgs& a, int rows, cudaStream_t s) {
   const int splits0 = pick_splits(tiles, a.kc, g_sms, 8);
   a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
   const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
-  st = ensure_state((size_t)tiles * splits * TT * kTileN * sizeof(float));
+  st = ensure_state((size_t)splits * rows * a.nt * kTileN * sizeof(float));
   if (st != B200_OK) return st;
   a.ws = g_ws; a.err = g_err;
   qmm_simt_kernel<MODE, TT><<<dim3(a.nt, splits, tts), kTileN, 0, s>>>(a);
   B200_LAUNCH_CHECK();
-  return launch_finish(a, splits, tts, s);
+  return launch_finish(a, splits, s);
 }
 
 template <int MODE>
 static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
-  const int tn = std::min(256, ((rows + 15) / 16) * 16);
+  // grouped launches fix the token tile (an expert's rows are cut into tiles of a.tn); dense ones
+  // take the whole batch up to 256 rows per tile
+  const int tn = a.items ? a.tn : std::min(256, ((rows + 15) / 16) * 16);
   a.tn = tn;
   const int tts = (rows + tn - 1) / tn;
-  const int tiles = a.nt * tts;
+  const int tiles = a.items ? a.nt * a.max_items : a.nt * tts;
   b200_status st = ensure_state(0);
   if (st != B200_OK) return st;
   const int stage_stride = kTileN * 128 + tn * 128 + kRawStride;
@@ -567,19 +579,19 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
     b200_set_error("qmm: %zu bytes of shared memory needed, %d available", smem, smem_budget[MODE]);
     return B200_ERR_CAPACITY;
   }
-  const int splits0 = pick_splits(tiles, a.kc, g_sms, ctas_per_sm);
+  const int splits0 = a.items ? 1 : pick_splits(tiles, a.kc, g_sms, ctas_per_sm);
   a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
   const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
-  st = ensure_state((size_t)tiles * splits * tn * kTileN * sizeof(float));
+  st = ensure_state((size_t)splits * rows * a.nt * kTileN * sizeof(float));
   if (st != B200_OK) return st;
   a.ws = g_ws; a.err = g_err;
   CUtensorMap xmap;
   st = make_x_map(&xmap, a.x, rows, a.k, tn);
   if (st != B200_OK) return st;
   a.x_row0 = 0;
-  qmm_tc_kernel<MODE><<<dim3(a.nt, splits, tts), kTcThreads, smem, s>>>(xmap, a);
+  qmm_tc_kernel<MODE><<<dim3(a.nt, splits, a.items ? a.max_items : tts), kTcThreads, smem, s>>>(xmap, a);
   B200_LAUNCH_CHECK();
-  return launch_finish(a, splits, tts, s);
+  return launch_finish(a, splits, s);
 }
 
 extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
@@ -601,6 +613,27 @@ extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t 
     if (w->mode == B200_Q_MXFP4_G32) return launch_simt<B200_Q_MXFP4_G32>(a, rows, s);
     return launch_simt<B200_Q_BF16>(a, rows, s);
   }
+  if (w->mode == B200_Q_AFFINE4_G64) return launch_tc<B200_Q_AFFINE4_G64>(a, rows, s);
+  if (w->mode == B200_Q_MXFP4_G32) return launch_tc<B200_Q_MXFP4_G32>(a, rows, s);
+  return launch_tc<B200_Q_BF16>(a, rows, s);
+}
+
+// Grouped matmul over an expert-sorted batch: work item i = {expert, first row, rows}; every
+// item multiplies its rows by its expert's weight.  d_items / d_n_items live on the device
+// (built by the grouping kernels); max_items bounds the grid.
+b200_status b200_qmm_grouped(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
+                             const float* d_row_scales, float swiglu_limit, const int4* d_items, const int* d_n_items,
+                             int32_t max_items, int32_t tile_rows, void* stream) {
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (rows <= 0) return B200_OK;
+  QmmArgs a{};
+  a.blocks = w->d_blocks; a.x = (const __nv_bfloat16*)d_x; a.y = (__nv_bfloat16*)d_y; a.residual = nullptr;
+  a.row_scales = d_row_scales;
+  a.rows = rows; a.n = w->n; a.k = w->k; a.nt = w->nt; a.kc = w->kc; a.epilogue = epilogue; a.swiglu_limit = swiglu_limit;
+  a.items = d_items; a.n_items = d_n_items; a.max_items = max_items; a.tn = tile_rows;
+  a.expert_stride = (size_t)w->nt * w->kc * w->block_bytes;
+  cudaStream_t s = (cudaStream_t)stream;
   if (w->mode == B200_Q_AFFINE4_G64) return launch_tc<B200_Q_AFFINE4_G64>(a, rows, s);
   if (w->mode == B200_Q_MXFP4_G32) return launch_tc<B200_Q_MXFP4_G32>(a, rows, s);
   return launch_tc<B200_Q_BF16>(a, rows, s);

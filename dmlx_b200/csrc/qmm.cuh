@@ -16,7 +16,11 @@ struct QmmArgs {
   __nv_bfloat16* y;             // [rows, n] (or [rows, n/2] with the SwiGLU epilogue)
   const __nv_bfloat16* residual;
   const float* row_scales;      // optional per-row multiplier applied in the epilogue
-  float* ws;                    // split-K scratch: [tile][split][tn][128] f32
+  float* ws;                    // split-K scratch: [split][row][nt*128] f32
+  const int4* items;            // grouped mode: {expert, first row, rows, -} per work item (device)
+  const int* n_items;           // grouped mode: number of valid items (device)
+  size_t expert_stride;         // grouped mode: bytes between consecutive experts' blocks
+  int max_items;
   int* err;                     // device error word
   int rows, n, k, nt, kc;
   int chunks_per_split, tn, stages;
@@ -27,3 +31,7 @@ struct QmmArgs {
   __device__ __forceinline__ int row_base_out(int token) const { return token; }
   __device__ __forceinline__ float row_scale(int token) const { return row_scales ? row_scales[token] : 1.0f; }
 };
+
+b200_status b200_qmm_grouped(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
+                             const float* d_row_scales, float swiglu_limit, const int4* d_items, const int* d_n_items,
+                             int32_t max_items, int32_t tile_rows, void* stream);

@@ -344,3 +344,79 @@ class LlamaModel:
         _lib.check(lib.b200_llama_profile_collect(self._h, ms, calls))
         names = ("attention", "matmul", "rope_append", "other")
         return {n: (ms[i], calls[i]) for i, n in enumerate(names)}
+
+
+# ---------------------------------------------------------------------------------------------
+# mixture of experts
+# ---------------------------------------------------------------------------------------------
+SCORE_SOFTMAX, SCORE_SIGMOID, SCORE_SQRTSOFTPLUS = 0, 1, 2
+
+
+def moe_route(logits: torch.Tensor, k: int, bias: Optional[torch.Tensor] = None, scoring: int = SCORE_SOFTMAX,
+              route_scale: float = 1.0):
+    """b200_moe_route.  logits [N,E] bf16 or f32 -> (indices i32 [N,k], weights f32 [N,k], counts i32 [E])."""
+    n, e = logits.shape
+    idx = torch.empty((n, k), dtype=torch.int32, device=logits.device)
+    w = torch.empty((n, k), dtype=torch.float32, device=logits.device)
+    counts = torch.empty(e, dtype=torch.int32, device=logits.device)
+    _lib.check(lib.b200_moe_route(_ptr(logits), int(logits.dtype == torch.float32), _ptr(bias), n, e, k, scoring,
+                                  route_scale, _ptr(idx), _ptr(w), _ptr(counts), _stream()))
+    return idx, w, counts
+
+
+def moe_group(indices: torch.Tensor, counts: torch.Tensor, tile_rows: int = 128):
+    """b200_moe_group -> (offsets [E+1], order [N*k], inv_order [N*k], items [cap,4], n_items [1])."""
+    n, k = indices.shape
+    e = counts.shape[0]
+    dev_ = indices.device
+    offsets = torch.empty(e + 1, dtype=torch.int32, device=dev_)
+    order = torch.empty(n * k, dtype=torch.int32, device=dev_)
+    inv = torch.empty(n * k, dtype=torch.int32, device=dev_)
+    cap = e + (n * k + tile_rows - 1) // tile_rows
+    items = torch.zeros((cap, 4), dtype=torch.int32, device=dev_)
+    n_items = torch.zeros(1, dtype=torch.int32, device=dev_)
+    _lib.check(lib.b200_moe_group(_ptr(indices), _ptr(counts), n, k, e, tile_rows, _ptr(offsets), _ptr(order), _ptr(inv),
+                                  _ptr(items), _ptr(n_items), _stream()))
+    return offsets, order, inv, items, n_items
+
+
+class MoELayer:
+    """DSV4MoE.forward (src/models/deepseek_v4.zig:1010-1056) on borrowed weight handles."""
+
+    def __init__(self, hidden: int, n_experts: int, inter: int, top_k: int, gate: QWeight, experts_gate_up: QWeight,
+                 experts_down: QWeight, shared_gate_up: Optional[QWeight] = None, shared_down: Optional[QWeight] = None,
+                 bias: Optional[np.ndarray] = None, scoring: int = SCORE_SOFTMAX, route_scale: float = 1.0,
+                 swiglu_limit: float = 10.0, shared_swiglu_limit: float = 0.0, tile_rows: int = 128,
+                 max_tokens: int = 4096):
+        self.cfg = _lib.MoeConfig(hidden, n_experts, inter, top_k, scoring, tile_rows, max_tokens, route_scale,
+                                  swiglu_limit, shared_swiglu_limit)
+        self._keep = (gate, experts_gate_up, experts_down, shared_gate_up, shared_down)
+        b = np.ascontiguousarray(bias, np.float32) if bias is not None else None
+        h = C.c_void_p()
+        _lib.check(lib.b200_moe_create(C.byref(self.cfg), gate._h,
+                                       b.ctypes.data_as(C.POINTER(C.c_float)) if b is not None else None,
+                                       experts_gate_up._h, experts_down._h,
+                                       shared_gate_up._h if shared_gate_up else None,
+                                       shared_down._h if shared_down else None, C.byref(h)))
+        self._h = h.value
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib.b200_moe_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        out = out if out is not None else torch.empty_like(x)
+        _lib.check(lib.b200_moe_forward(self._h, _ptr(x), x.shape[0], _ptr(out), _stream()))
+        return out
+
+    def last_routing(self, n_tokens: int):
+        k, e = self.cfg.top_k, self.cfg.n_experts
+        idx = np.zeros((n_tokens, k), np.uint32)
+        w = np.zeros((n_tokens, k), np.float32)
+        off = np.zeros(e + 1, np.int32)
+        _lib.check(lib.b200_moe_last_routing(self._h, n_tokens, idx.ctypes.data, w.ctypes.data, off.ctypes.data))
+        return idx, w, off

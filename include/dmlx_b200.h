@@ -346,6 +346,64 @@ void b200_llama_enable_graphs(b200_llama* m, int32_t on);
 void b200_llama_profile_enable(b200_llama* m, int32_t on);
 b200_status b200_llama_profile_collect(b200_llama* m, double* ms, int64_t* calls);
 
+/* ---- mixture of experts ------------------------------------------------------------------------ */
+/* Top-k routing (MoERouter.topkRoute, src/moe_router.zig:55-103; DSV4Gate.forward scoring, bias and
+ * weights, src/models/deepseek_v4.zig:555-681).  logits [N,E] bf16 (or f32); scoring 0 = softmax,
+ * 1 = sigmoid, 2 = sqrt(softplus); bias (optional, f32 [E]) steers the choice only; weights come
+ * from the unbiased scores, renormalised over the selection unless softmax, times route_scale.
+ * Output per token in ascending (score, expert index) order — the last k of an ascending stable
+ * argsort.  counts (optional, i32 [E]) receives the per-expert histogram. */
+b200_status b200_moe_route(const void* d_logits, int32_t logits_are_f32, const float* d_bias,
+                           int32_t n_tokens, int32_t n_experts, int32_t k, int32_t scoring,
+                           float route_scale, uint32_t* d_indices, float* d_weights,
+                           int32_t* d_counts, void* stream);
+/* Stable grouping of the N*k assignments by expert (argsort(flat indices), argsort(order),
+ * src/models/deepseek_v4.zig:747-784): offsets [E+1], order [N*k], inv_order [N*k], plus the work
+ * items ({expert, first row, rows, 0} as 4 x i32; capacity E + ceil(N*k / tile_rows)) that the
+ * grouped matmul consumes. */
+b200_status b200_moe_group(const uint32_t* d_indices, const int32_t* d_counts, int32_t n_tokens,
+                           int32_t k, int32_t n_experts, int32_t tile_rows, int32_t* d_offsets,
+                           int32_t* d_order, int32_t* d_inv_order, void* d_items,
+                           int32_t* d_n_items, void* stream);
+/* x_sorted[p] = x[order[p] / k]; row_scales[p] = weights[order[p]]  (expandTokens + the gathers of
+ * src/moe_router.zig:111-132, deepseek_v4.zig:760-784). */
+b200_status b200_moe_gather(const void* d_x, const int32_t* d_order, const float* d_weights,
+                            int32_t n_assign, int32_t k, int32_t hidden, void* d_x_sorted,
+                            float* d_row_scales, void* stream);
+/* Ragged grouped quantised matmul over the expert-sorted rows (gather_qmm with sorted indices,
+ * src/models/deepseek_v4.zig:787-805,968-979); w stacks n_experts matrices; row_scales (optional)
+ * multiplies each output row in the epilogue. */
+b200_status b200_moe_grouped_qmm(const b200_qweight* w, const void* d_x_sorted, int32_t rows,
+                                 void* d_y_sorted, int32_t epilogue, const float* d_row_scales,
+                                 float swiglu_limit, const void* d_items, const int32_t* d_n_items,
+                                 int32_t max_items, int32_t tile_rows, void* stream);
+/* out[t] = sum_j y_sorted[inv_order[t*k + j]] (+ shared_out[t])  (reduceExperts,
+ * src/moe_router.zig:139-164; deepseek_v4.zig:809-819,1051). */
+b200_status b200_moe_combine(const void* d_y_sorted, const int32_t* d_inv_order, int32_t n_tokens,
+                             int32_t k, int32_t hidden, const void* d_shared_out, void* d_out,
+                             void* stream);
+/* One MoE layer = DSV4MoE.forward (src/models/deepseek_v4.zig:1010-1056).  Weight handles are
+ * borrowed: gate dense bf16 [E, hidden]; experts_gate_up stacks E x [2*inter, hidden] with gate
+ * and up rows interleaved; experts_down E x [hidden, inter]; shared_* optional. */
+typedef struct b200_moe_config {
+  int32_t hidden, n_experts, inter, top_k;
+  int32_t scoring;       /* 0 softmax, 1 sigmoid, 2 sqrt-softplus */
+  int32_t tile_rows;     /* token tile of the grouped matmul: multiple of 16, 16..256 */
+  int32_t max_tokens;
+  float route_scale;
+  float swiglu_limit;        /* routed experts: 10 in the reference (deepseek_v4.zig:64) */
+  float shared_swiglu_limit; /* shared expert (0 = unclipped) */
+} b200_moe_config;
+typedef struct b200_moe b200_moe;
+b200_status b200_moe_create(const b200_moe_config* cfg, const b200_qweight* gate, const float* h_bias,
+                            const b200_qweight* experts_gate_up, const b200_qweight* experts_down,
+                            const b200_qweight* shared_gate_up, const b200_qweight* shared_down,
+                            b200_moe** out);
+void b200_moe_destroy(b200_moe* m);
+b200_status b200_moe_forward(b200_moe* m, const void* d_x, int32_t n_tokens, void* d_out, void* stream);
+b200_status b200_moe_last_routing(b200_moe* m, int32_t n_tokens, uint32_t* h_indices, float* h_weights,
+                                  int32_t* h_offsets);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,121 @@
+"""GPU parity of MoE routing, grouping, the ragged grouped matmul and the whole layer against the
+oracle (src/moe_router.zig:55-164, src/models/deepseek_v4.zig:546-681,721-848,1010-1056)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import ref_math
+
+pytestmark = pytest.mark.gpu
+
+
+def _bits(a):
+    return (ref_math.bf16_round(a).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def _close(got, want):
+    g, w = np.asarray(got, np.float64).reshape(-1), np.asarray(want, np.float64).reshape(-1)
+    return np.abs(g - w).max() / max(np.abs(w).max(), 1e-30), g @ w / (np.linalg.norm(g) * np.linalg.norm(w) + 1e-30)
+
+
+@pytest.mark.parametrize("scoring", ["softmax", "sigmoid", "sqrtsoftplus"])
+def test_route_matches_gate_forward(scoring):
+    """Expert indices equal the oracle's wherever its decision margin is above f32 rounding of the
+    scoring function; weights within 1e-5 relative."""
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(18)
+    n, e, k = 512, 256, 6
+    logits = rng.normal(0, 1, (n, e)).astype(np.float32)
+    bias = rng.normal(0, 0.02, e).astype(np.float32)
+    w_ref, i_ref = ref_math.gate_forward(logits, bias, k, route_scale=1.5, scoring=scoring)
+    sc = {"softmax": 0, "sigmoid": 1, "sqrtsoftplus": 2}[scoring]
+    idx, w, counts = dev.moe_route(torch.tensor(logits, device="cuda"), k, torch.tensor(bias, device="cuda"), sc, 1.5)
+    idx, w = idx.cpu().numpy().astype(np.uint32), w.cpu().numpy()
+    same = (idx == i_ref).all(axis=1)
+    assert same.mean() >= 0.99, same.mean()
+    assert np.allclose(w[same], w_ref[same], rtol=2e-5, atol=1e-9)
+    assert counts.cpu().numpy().sum() == n * k
+    assert np.array_equal(counts.cpu().numpy(), np.bincount(idx.reshape(-1), minlength=e))
+    for t in np.where(~same)[0]:  # a disagreement is a swap at a near-tie: same set, or one expert exchanged
+        assert len(set(idx[t].tolist()) ^ set(i_ref[t].tolist())) in (0, 2)
+
+
+def test_route_tie_rule():
+    """Equal scores: the larger expert index wins and comes last (ascending stable argsort, last k;
+    src/moe_router.zig:59-73)."""
+    from dmlx_b200 import device as dev
+
+    logits = torch.zeros((3, 8), dtype=torch.float32, device="cuda")
+    idx, w, _ = dev.moe_route(logits, 3)
+    assert idx.cpu().numpy().tolist() == [[5, 6, 7]] * 3
+    assert ref_math.topk_route(np.zeros((1, 8), np.float32), 3).tolist() == [[5, 6, 7]]
+    assert np.allclose(w.cpu().numpy(), 1.0 / 8)
+
+
+def test_group_bit_exact():
+    """order / inv_order / offsets equal a stable host sort (src/models/deepseek_v4.zig:747-784)."""
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(3)
+    for n, e, k, tile in ((4096, 256, 6, 128), (37, 8, 2, 16), (1, 4, 4, 64)):
+        p = rng.random(e) ** 3  # skewed load
+        idx = np.stack([rng.choice(e, k, replace=False, p=p / p.sum()) for _ in range(n)]).astype(np.int32)
+        counts = np.bincount(idx.reshape(-1), minlength=e).astype(np.int32)
+        off, order, inv, items, n_items = dev.moe_group(torch.tensor(idx, device="cuda"), torch.tensor(counts, device="cuda"), tile)
+        o_ref, i_ref, tok_ref, off_ref = ref_math.group_by_expert(idx, e)
+        assert np.array_equal(off.cpu().numpy(), off_ref)
+        assert np.array_equal(order.cpu().numpy(), o_ref) and np.array_equal(inv.cpu().numpy(), i_ref)
+        ni = int(n_items.cpu()[0])
+        it = items.cpu().numpy()[:ni]
+        assert ni == sum(-(-c // tile) for c in counts)
+        covered = np.zeros(n * k, np.int32)
+        for ex, r0, rows, _ in it:
+            assert off_ref[ex] <= r0 and r0 + rows <= off_ref[ex + 1] and 0 < rows <= tile
+            covered[r0:r0 + rows] += 1
+        assert (covered == 1).all()
+
+
+@pytest.mark.parametrize("mode_name", ["mxfp4", "affine4"])
+def test_moe_layer_matches_oracle(mode_name):
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(11)
+    n, d, e, inter, k = 70, 256, 8, 128, 2
+    x = ref_math.bf16_round(rng.normal(0, 1, (n, d)))
+    wg = ref_math.bf16_round(rng.normal(0, 0.3, (e, d)))
+    bias = rng.normal(0, 0.01, e).astype(np.float32)
+
+    def make(n_e, rows, cols):
+        """-> (QWeight, dequantised [n_e, rows, cols])"""
+        if mode_name == "mxfp4":
+            packed = rng.integers(0, 256, (n_e * rows, cols // 2), dtype=np.uint8)
+            scales = rng.integers(118, 122, (n_e * rows, cols // 32), dtype=np.uint8)
+            w = dev.QWeight(dev.Q_MXFP4_G32, packed, scales, None, rows, cols, n_experts=n_e)
+            return w, ref_math.dequantize_mxfp4(packed, scales).reshape(n_e, rows, cols)
+        wf = rng.normal(0, 0.05, (n_e * rows, cols)).astype(np.float32)
+        packed, s, b = ref_math.quantize_affine4(wf)
+        w = dev.QWeight(dev.Q_AFFINE4_G64, packed, _bits(s), _bits(b), rows, cols, n_experts=n_e)
+        return w, ref_math.dequantize_affine4(packed, s, b).reshape(n_e, rows, cols)
+
+    gu, gu_deq = make(e, 2 * inter, d)      # rows interleaved: 2i = gate_i, 2i+1 = up_i
+    down, down_deq = make(e, d, inter)
+    sgu, sgu_deq = make(1, 2 * inter, d)
+    sdown, sdown_deq = make(1, d, inter)
+    gate = dev.QWeight(dev.Q_BF16, _bits(wg), np.zeros(1, np.uint8), None, e, d)
+    layer = dev.MoELayer(d, e, inter, k, gate, gu, down, sgu, sdown, bias=bias, route_scale=1.5, swiglu_limit=10.0,
+                         tile_rows=32, max_tokens=128)
+    got = layer.forward(torch.tensor(x, device="cuda").bfloat16()).float().cpu().numpy()
+    assert dev.qmm_error_word() == 0
+    idx, wts, off = layer.last_routing(n)
+    # routing against the oracle on bf16 logits (the reference's matmul output dtype)
+    logits = ref_math.bf16_round(x.astype(np.float64) @ wg.astype(np.float64).T)
+    w_ref, i_ref = ref_math.gate_forward(logits, bias, k, route_scale=1.5)
+    same = (idx == i_ref).all(axis=1)
+    assert same.mean() >= 0.95
+    assert np.array_equal(off, ref_math.group_by_expert(idx, e)[3])
+    # layer output against the oracle evaluated with the routing the device chose
+    routed = ref_math.switch_glu(x, idx, wts, gu_deq[:, 0::2], gu_deq[:, 1::2], down_deq, limit=10.0)
+    shared = ref_math.expert_forward(x, sgu_deq[0, 0::2], sgu_deq[0, 1::2], sdown_deq[0], limit=0.0)
+    rel, cos = _close(got, routed + shared)
+    assert rel <= 2e-2 and cos >= 0.9995, (rel, cos)
