@@ -167,6 +167,7 @@ class LlamaConfig(C.Structure):
 
 
 _sig("b200_qmm_error_word", i32, P(i32))
+_sig("b200_qmm_static_scratch", i32, vp, vp, i32, vp, i32, vp, f32, vp)
 _sig("b200_llama_create", i32, P(LlamaConfig), P(vp))
 _sig("b200_llama_destroy", None, vp)
 _sig("b200_llama_set_linear", i32, vp, i32, i32, i32, vp, vp, vp)

@@ -655,3 +655,111 @@ extern "C" b200_status b200_qmm_error_word_async(int32_t* h_out, void* stream) {
   B200_CUDA_TRY(cudaMemcpyAsync(h_out, g_err, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
   return B200_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant of the tensor-core matmul.
+//
+// b200_qmm grows its split-K scratch with cudaMalloc the first time a shape needs more room.
+// Some hosts cannot take that: an engine that has handed every remaining byte of HBM to its KV
+// page pool (a late cudaMalloc then fails in the middle of serving), a step that is being
+// recorded into a CUDA graph or runs beside other streams (cudaMalloc synchronises the whole
+// device), or an embedding whose rules forbid allocating after start-up.  For them the scratch
+// lives in the library image: a fixed device array that every GPU loading the library holds
+// until the process exits.
+//
+//  * Limit: splits * rows * round_up(N,128) * 4 bytes must fit in kStaticScratchBytes (32 MiB);
+//    larger problems are refused with B200_ERR_CAPACITY, nothing is launched.
+//  * The first call on each device looks up the array's device address (cudaGetSymbolAddress);
+//    make that call before any stream capture.
+//  * All calls share the one array and it keeps whatever the previous call left there.  Every
+//    element a call reads it has written first, so nothing needs clearing, but two calls that
+//    overlap on the GPU (different streams, no ordering between them) race on it.
+// ---------------------------------------------------------------------------------------------
+namespace {
+constexpr size_t kStaticScratchBytes = (size_t)32 << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ __align__(256) int g_static_err[64];
+constexpr int kMaxDevices = 64;
+float* g_static_ws[kMaxDevices] = {nullptr};
+int* g_static_err_ptr[kMaxDevices] = {nullptr};
+int g_static_sms[kMaxDevices] = {0};
+
+template <int MODE>
+b200_status launch_tc_static(QmmArgs& a, int rows, int dev, cudaStream_t s) {
+  const int tn = std::min(256, ((rows + 15) / 16) * 16);
+  a.tn = tn;
+  const int tts = (rows + tn - 1) / tn;
+  const int tiles = a.nt * tts;
+  const int stage_stride = kTileN * 128 + tn * 128 + kRawStride;
+  static int budget[3] = {0, 0, 0};
+  if (budget[MODE] == 0) {
+    int optin = 0;
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    cudaFuncAttributes fa;
+    B200_CUDA_TRY(cudaFuncGetAttributes(&fa, qmm_tc_kernel<MODE>));
+    const int b = optin - (int)fa.sharedSizeBytes;
+    B200_CUDA_TRY(cudaFuncSetAttribute(qmm_tc_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, b));
+    budget[MODE] = b;
+  }
+  const int fixed = 1024 + 8 * (3 * 8 + 2) + 16;
+  const int per_cta = tn <= 64 ? 108 * 1024 : std::min(budget[MODE], 220 * 1024);
+  a.stages = std::max(2, std::min(8, (per_cta - fixed) / stage_stride));
+  const int ctas_per_sm = tn <= 64 ? 2 : 1;
+  const size_t smem = (size_t)a.stages * stage_stride + fixed;
+  if ((int)smem > budget[MODE]) {
+    b200_set_error("qmm (static scratch): %zu bytes of shared memory needed, %d available", smem, budget[MODE]);
+    return B200_ERR_CAPACITY;
+  }
+  const int splits0 = pick_splits(tiles, a.kc, g_static_sms[dev], ctas_per_sm);
+  a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
+  const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
+  const size_t need = (size_t)splits * rows * a.nt * kTileN * sizeof(float);
+  if (need > kStaticScratchBytes) {
+    b200_set_error("qmm (static scratch): %d rows x N=%d in %d K-splits need %zu bytes of scratch, the built-in array holds %zu",
+                   rows, a.n, splits, need, kStaticScratchBytes);
+    return B200_ERR_CAPACITY;
+  }
+  a.ws = g_static_ws[dev];
+  a.err = g_static_err_ptr[dev];
+  CUtensorMap xmap;
+  b200_status st = make_x_map(&xmap, a.x, rows, a.k, tn);
+  if (st != B200_OK) return st;
+  a.x_row0 = 0;
+  qmm_tc_kernel<MODE><<<dim3(a.nt, splits, tts), kTcThreads, smem, s>>>(xmap, a);
+  B200_LAUNCH_CHECK();
+  return launch_finish(a, splits, s);
+}
+}  // namespace
+
+extern "C" b200_status b200_qmm_static_scratch(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y,
+                                               int32_t epilogue, const void* d_residual, float swiglu_limit,
+                                               void* stream) {
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (rows <= 0) return B200_OK;
+  if (w->n_experts != 1) { b200_set_error("qmm (static scratch): single weights only"); return B200_ERR_INVALID_ARGUMENT; }
+  if (epilogue == B200_EPI_RESIDUAL && !d_residual) { b200_set_error("qmm (static scratch): residual epilogue without a residual"); return B200_ERR_INVALID_ARGUMENT; }
+  if (epilogue == B200_EPI_SWIGLU && (w->n % 2) != 0) { b200_set_error("qmm (static scratch): SwiGLU needs an even N"); return B200_ERR_INVALID_ARGUMENT; }
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) { b200_set_error("qmm (static scratch): device ordinal %d not supported", dev); return B200_ERR_INVALID_ARGUMENT; }
+  if (!g_static_ws[dev]) {
+    // Set-up, once per device, with that device current: the array's name is only a host-side
+    // handle here; the kernel needs the address the symbol has on this device.
+    void* p = nullptr;
+    B200_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+    void* e = nullptr;
+    B200_CUDA_TRY(cudaGetSymbolAddress(&e, g_static_err));
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&g_static_sms[dev], cudaDevAttrMultiProcessorCount, dev));
+    g_static_err_ptr[dev] = (int*)e;
+    g_static_ws[dev] = (float*)p;
+  }
+  QmmArgs a{};
+  a.blocks = w->d_blocks; a.x = (const __nv_bfloat16*)d_x; a.y = (__nv_bfloat16*)d_y;
+  a.residual = (const __nv_bfloat16*)d_residual;
+  a.rows = rows; a.n = w->n; a.k = w->k; a.nt = w->nt; a.kc = w->kc; a.epilogue = epilogue; a.swiglu_limit = swiglu_limit;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (w->mode == B200_Q_AFFINE4_G64) return launch_tc_static<B200_Q_AFFINE4_G64>(a, rows, dev, s);
+  if (w->mode == B200_Q_MXFP4_G32) return launch_tc_static<B200_Q_MXFP4_G32>(a, rows, dev, s);
+  return launch_tc_static<B200_Q_BF16>(a, rows, dev, s);
+}

@@ -296,6 +296,17 @@ b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void*
 
 /* Reads and clears the matmul kernels' error word (set when a bounded wait ran out). */
 b200_status b200_qmm_error_word(int32_t* out);
+/* No counterpart in the reference.  The tensor-core matmul of b200_qmm for hosts that must not
+ * allocate after start-up (all HBM already given to the KV pool, a step being captured into a CUDA
+ * graph or running beside other streams, where cudaMalloc would fail or stall the device): its
+ * split-K scratch is a fixed 32 MiB array inside the library instead of a buffer grown on demand,
+ * and the call allocates nothing.  Problems whose scratch (K-splits x rows x round_up(N,128) x 4
+ * bytes) exceeds the array are refused with B200_ERR_CAPACITY.  The first call on a device
+ * resolves the array's address and should come before any stream capture; all calls share the
+ * array, so calls that overlap on the GPU race. */
+b200_status b200_qmm_static_scratch(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y,
+                                    int32_t epilogue, const void* d_residual, float swiglu_limit,
+                                    void* stream);
 
 /* ---- LLaMA-architecture decode step over a packed ragged batch --------------------------------- */
 /* Stands in for ModelVTable.forward + the greedy branch of generateBatchStep
