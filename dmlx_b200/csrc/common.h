@@ -18,8 +18,11 @@ void b200_set_error(const char* fmt, ...);
       return B200_ERR_CUDA;                                                                 \
     }                                                                                       \
   } while (0)
+// Every kernel launch of the library passes through B200_LAUNCH_CHECK, which also counts it.
+extern long long g_b200_launch_counter;
 #define B200_LAUNCH_CHECK()                                                                 \
   do {                                                                                      \
+    ++g_b200_launch_counter;                                                                \
     cudaError_t _e = cudaGetLastError();                                                    \
     if (_e != cudaSuccess) {                                                                \
       b200_set_error("kernel launch failed: %s (%s:%d)", cudaGetErrorString(_e), __FILE__, __LINE__); \

@@ -16,6 +16,7 @@
 namespace {
 thread_local std::string g_last_error;
 }
+long long g_b200_launch_counter = 0;
 
 void b200_set_error(const char* fmt, ...) {
   char buf[512];

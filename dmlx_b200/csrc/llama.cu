@@ -57,7 +57,7 @@ struct b200_llama {
   // first step of a shape runs eagerly (it may grow scratch buffers), the second is captured,
   // later ones replay the graph.
   bool graphs_on = true;
-  struct GraphEntry { int seen = 0; cudaGraphExec_t exec = nullptr; };
+  struct GraphEntry { int seen = 0; cudaGraphExec_t exec = nullptr; long long kernels = 0; };
   std::map<std::tuple<int, const void*, const void*, void*>, GraphEntry> graphs;
   // optional CUDA-event timing per category: 0 attention, 1 matmuls, 2 rope + KV append, 3 the rest
   bool prof_on = false;
@@ -313,6 +313,7 @@ b200_status b200_llama_forward(b200_llama* m, b200_kv* kv, const b200_pack_desc*
     B200_CUDA_TRY(cudaStreamBeginCapture(cs, cudaStreamCaptureModeThreadLocal));
     const long long before = m->launches;
     b200_status st = llama_forward_eager(m, kv, d_desc, n_req, total_rows, d_prefill_tokens, stream);
+    ge.kernels = m->launches - before;  // nodes of the graph
     m->launches = before;
     cudaError_t e = cudaStreamEndCapture(cs, &graph);
     if (st != B200_OK) { if (graph) cudaGraphDestroy(graph); return st; }
@@ -323,7 +324,7 @@ b200_status b200_llama_forward(b200_llama* m, b200_kv* kv, const b200_pack_desc*
   }
   B200_CUDA_TRY(cudaGraphLaunch(ge.exec, cs));
   m->last_n_req = n_req;
-  m->launches += 5 + 15LL * m->cfg.n_layers + 6;
+  m->launches += ge.kernels;
   return B200_OK;
 }
 
@@ -342,6 +343,7 @@ static b200_status llama_forward_eager(b200_llama* m, b200_kv* kv, const b200_pa
   }
   m->last_n_req = n_req;
   if (n_req == 0 || total_rows == 0) return B200_OK;
+  const long long launches_before = g_b200_launch_counter;
   const int T = total_rows, qd = c.n_heads * c.head_dim, kd = c.n_kv_heads * c.head_dim, qkv_dim = qd + 2 * kd;
   b200_status st;
   cudaStream_t cs = (cudaStream_t)stream;
@@ -369,9 +371,7 @@ static b200_status llama_forward_eager(b200_llama* m, b200_kv* kv, const b200_pa
   STEP(b200_scatter_tokens(m->d_next, d_desc, m->d_last_token, n_req, stream));
 #undef STEP
 #undef STEP_CAT
-  // pack 2, reserve 2, embed 1; per layer 15 (each matmul = main + finish, attention = plan +
-  // main + combine); tail 6
-  m->launches += 5 + 15LL * c.n_layers + 6;
+  m->launches += g_b200_launch_counter - launches_before;
   return B200_OK;
 }
 

@@ -325,14 +325,42 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
     if (ok) {
       ptx::tc_fence_after_sync();
       const size_t n_pad = (size_t)a.nt * kTileN;
-      float* wsp = a.ws + ((size_t)split * a.rows + t0) * n_pad + nt * kTileN;
+      const int n = nt * kTileN + warp * 32 + lane;
+      const bool direct = gridDim.y == 1;  // one K split: apply the epilogue here, no finish kernel
+      float* wsp = a.ws + ((size_t)split * a.rows + t0) * n_pad + n;
       for (int c0 = 0; c0 < rows_here; c0 += 32) {
         uint32_t v[32];
         ptx::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
         ptx::tmem_ld_wait();
+        if (!direct) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j)
-          if (c0 + j < rows_here) wsp[(size_t)(c0 + j) * n_pad + warp * 32 + lane] = __uint_as_float(v[j]);
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < rows_here) wsp[(size_t)(c0 + j) * n_pad] = __uint_as_float(v[j]);
+        } else if (a.epilogue == B200_EPI_SWIGLU) {
+          // rows 2i / 2i+1 of the tile are gate_i / up_i: neighbouring lanes
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float mine = __uint_as_float(v[j]);
+            const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+            if ((lane & 1) == 0 && c0 + j < rows_here && n < a.n) {
+              float g = mine, u = other;
+              if (a.swiglu_limit > 0.f) { g = fminf(g, a.swiglu_limit); u = fminf(fmaxf(u, -a.swiglu_limit), a.swiglu_limit); }
+              const int token = t0 + c0 + j;
+              a.y[(size_t)token * (a.n / 2) + n / 2] = __float2bfloat16(g / (1.0f + __expf(-g)) * u * a.row_scale(token));
+            }
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (c0 + j < rows_here && n < a.n) {
+              const int token = t0 + c0 + j;
+              const size_t o = (size_t)token * a.n + n;
+              float acc = __uint_as_float(v[j]);
+              if (a.epilogue == B200_EPI_RESIDUAL) acc += __bfloat162float(a.residual[o]);
+              a.y[o] = __float2bfloat16(acc * a.row_scale(token));
+            }
+          }
+        }
       }
     }
   }
@@ -341,6 +369,139 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
   const int any_bad = __syncthreads_or(!ok);
   if (warp == 5) ptx::tmem_dealloc(tmem_base, ncols);
   (void)any_bad;
+}
+
+// ---- small-batch kernel: register dequantisation + mma.sync -------------------------------------
+// For a handful of rows the matmul is a weight-streaming problem, and the tcgen05 route above pays
+// a long dependent chain per chunk (dequantise into a 16 KiB shared tile -> MMA -> commit -> slot
+// free).  Here nothing but the raw 4-bit blocks passes through shared memory: a producer warp
+// keeps a deep ring of raw blocks in flight with bulk copies; each of 8 consumer warps owns one
+// 16-row slice of the 128-row tile, pulls its rows' nibbles into registers, releases the slot at
+// once, dequantises straight into mma.sync A fragments (m16n8k16, bf16) and multiplies with the
+// activations (B fragments read from global memory through L1: the batch is tiny and shared by
+// all CTAs).  Tokens are the MMA N dimension: NT8 tiles of 8.
+constexpr int kGemvConsumers = 8;
+constexpr int kGemvThreads = (kGemvConsumers + 1) * 32;
+constexpr int kGemvRawStages = 12;
+
+__device__ __forceinline__ void mma_bf16_full(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// One column pair (already shifted into the low nibble of each half) -> bf16x2.
+template <int MODE>
+__device__ __forceinline__ uint32_t dequant_pair(uint32_t shifted, __nv_bfloat162 s2, __nv_bfloat162 b2) {
+  const uint32_t t = shifted & 0x000F000Fu;
+  __nv_bfloat162 r;
+  if (MODE == B200_Q_AFFINE4_G64) {
+    uint32_t u = t | 0x43004300u;
+    const uint32_t c128 = 0x43004300u;
+    r = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), *reinterpret_cast<const __nv_bfloat162*>(&c128)), s2, b2);
+  } else {
+    uint32_t u = ((t & 0x00080008u) << 12) | ((t & 0x00070007u) << 6);
+    const uint32_t c64 = 0x5F805F80u;
+    r = __hmul2(__hmul2(*reinterpret_cast<__nv_bfloat162*>(&u), *reinterpret_cast<const __nv_bfloat162*>(&c64)), s2);
+  }
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+template <int MODE, int NT8>
+__global__ void __launch_bounds__(kGemvThreads, 2) qmm_mma_kernel(QmmArgs a) {
+  extern __shared__ __align__(128) unsigned char gsm[];
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(gsm + (size_t)kGemvRawStages * kRawStride);
+  uint64_t* raw_free = raw_full + kGemvRawStages;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int nt = blockIdx.x, split = blockIdx.y, t0 = blockIdx.z * (NT8 * 8);
+  const int kc0 = split * a.chunks_per_split, kc1 = min(kc0 + a.chunks_per_split, a.kc), n_chunks = kc1 - kc0;
+  constexpr int BB = block_bytes(MODE);
+  if (tid == 0) {
+    for (int s = 0; s < kGemvRawStages; ++s) {
+      ptx::mbar_init(&raw_full[s], 1);
+      ptx::mbar_init(&raw_free[s], kGemvConsumers);
+    }
+    ptx::mbar_fence_init();
+  }
+  __syncthreads();
+  bool ok = true;
+  if (warp == kGemvConsumers) {
+    if (lane == 0) {
+      for (int i = 0; i < n_chunks; ++i) {
+        const int s = i % kGemvRawStages;
+        ok = ptx::mbar_wait(&raw_free[s], ((i / kGemvRawStages) & 1) ^ 1);
+        if (!ok) break;
+        ptx::mbar_expect_tx(&raw_full[s], BB);
+        ptx::bulk_g2s(gsm + (size_t)s * kRawStride, a.blocks + ((size_t)nt * a.kc + kc0 + i) * BB, BB, &raw_full[s]);
+      }
+    }
+  } else {
+    const int rA = warp * 16 + g, rB = rA + 8;
+    float acc[NT8][4];
+#pragma unroll
+    for (int j = 0; j < NT8; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
+    // activation row pointers of this lane's tokens (token = t0 + 8j + g), null beyond the batch
+    const uint32_t* xrow[NT8];
+#pragma unroll
+    for (int j = 0; j < NT8; ++j) {
+      const int tok = t0 + j * 8 + g;
+      xrow[j] = tok < a.rows ? reinterpret_cast<const uint32_t*>(a.x + (size_t)tok * a.k) : nullptr;
+    }
+    for (int i = 0; i < n_chunks; ++i) {
+      const int s = i % kGemvRawStages;
+      // B fragments of the whole chunk first: they do not depend on the weights
+      uint32_t xb[NT8][8];
+      const int kw = (kc0 + i) * (kChunkK / 2);  // chunk start in 32-bit words
+#pragma unroll
+      for (int j = 0; j < NT8; ++j) {
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks) {
+          xb[j][2 * ks] = xrow[j] ? __ldg(xrow[j] + kw + ks * 8 + t) : 0u;
+          xb[j][2 * ks + 1] = xrow[j] ? __ldg(xrow[j] + kw + ks * 8 + 4 + t) : 0u;
+        }
+      }
+      ok = ptx::mbar_wait(&raw_full[s], (i / kGemvRawStages) & 1);
+      if (!ok) break;
+      const unsigned char* blk = gsm + (size_t)s * kRawStride;
+      uint4 wa[2], wb[2];
+      __nv_bfloat162 sA[2], bA[2], sB[2], bB[2];
+#pragma unroll
+      for (int plane = 0; plane < 2; ++plane) {
+        wa[plane] = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[rA];
+        wb[plane] = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[rB];
+        row_params<MODE>(blk, rA, plane, sA[plane], bA[plane]);
+        row_params<MODE>(blk, rB, plane, sB[plane], bB[plane]);
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&raw_free[s]);  // everything this warp needs is in registers
+#pragma unroll
+      for (int ks = 0; ks < 4; ++ks) {
+        const int plane = ks >> 1;
+        // words 2*(ks&1) and 2*(ks&1)+1 of the plane hold columns 16ks..16ks+15; lane t takes pair t
+        const uint32_t a_w0 = (ks & 1) ? wa[plane].z : wa[plane].x, a_w1 = (ks & 1) ? wa[plane].w : wa[plane].y;
+        const uint32_t b_w0 = (ks & 1) ? wb[plane].z : wb[plane].x, b_w1 = (ks & 1) ? wb[plane].w : wb[plane].y;
+        uint32_t af[4];
+        af[0] = dequant_pair<MODE>(a_w0 >> (4 * t), sA[plane], bA[plane]);
+        af[1] = dequant_pair<MODE>(b_w0 >> (4 * t), sB[plane], bB[plane]);
+        af[2] = dequant_pair<MODE>(a_w1 >> (4 * t), sA[plane], bA[plane]);
+        af[3] = dequant_pair<MODE>(b_w1 >> (4 * t), sB[plane], bB[plane]);
+#pragma unroll
+        for (int j = 0; j < NT8; ++j) mma_bf16_full(acc[j], af, xb[j][2 * ks], xb[j][2 * ks + 1]);
+      }
+    }
+    if (ok) {
+      const size_t n_pad = (size_t)a.nt * kTileN;
+#pragma unroll
+      for (int j = 0; j < NT8; ++j) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int tok = t0 + j * 8 + 2 * t + (e & 1), row = (e & 2) ? rB : rA;
+          if (tok < a.rows) a.ws[((size_t)split * a.rows + tok) * n_pad + nt * kTileN + row] = acc[j][e];
+        }
+      }
+    }
+  }
+  if (!ok) atomicExch(a.err, B200_ERR_DEVICE_FLAGGED);
 }
 
 // ---- host-side state -------------------------------------------------------------------------------
@@ -591,7 +752,38 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
   a.x_row0 = 0;
   qmm_tc_kernel<MODE><<<dim3(a.nt, splits, a.items ? a.max_items : tts), kTcThreads, smem, s>>>(xmap, a);
   B200_LAUNCH_CHECK();
+  return splits == 1 ? B200_OK : launch_finish(a, splits, s);  // one split writes its output itself
+}
+
+template <int MODE, int NT8>
+static b200_status launch_mma_nt(QmmArgs& a, int rows, cudaStream_t s) {
+  const int tile = NT8 * 8;
+  a.tn = tile;
+  const int tts = (rows + tile - 1) / tile;
+  b200_status st = ensure_state(0);
+  if (st != B200_OK) return st;
+  const int splits0 = pick_splits(a.nt * tts, a.kc, g_sms, 2);
+  a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
+  const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
+  st = ensure_state((size_t)splits * rows * a.nt * kTileN * sizeof(float));
+  if (st != B200_OK) return st;
+  a.ws = g_ws; a.err = g_err;
+  const size_t smem = (size_t)kGemvRawStages * kRawStride + 2 * kGemvRawStages * sizeof(uint64_t);
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(qmm_mma_kernel<MODE, NT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  qmm_mma_kernel<MODE, NT8><<<dim3(a.nt, splits, tts), kGemvThreads, smem, s>>>(a);
+  B200_LAUNCH_CHECK();
   return launch_finish(a, splits, s);
+}
+
+template <int MODE>
+static b200_status launch_mma(QmmArgs& a, int rows, cudaStream_t s) {
+  if (rows <= 8) return launch_mma_nt<MODE, 1>(a, rows, s);
+  if (rows <= 16) return launch_mma_nt<MODE, 2>(a, rows, s);
+  return launch_mma_nt<MODE, 4>(a, rows, s);
 }
 
 extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
@@ -602,12 +794,18 @@ extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t 
   if (w->n_experts != 1) { b200_set_error("qmm: stacked expert weights go through the grouped entry point"); return B200_ERR_INVALID_ARGUMENT; }
   if (epilogue == B200_EPI_RESIDUAL && !d_residual) { b200_set_error("qmm: residual epilogue without a residual"); return B200_ERR_INVALID_ARGUMENT; }
   if (epilogue == B200_EPI_SWIGLU && (w->n % 2) != 0) { b200_set_error("qmm: SwiGLU needs an even N"); return B200_ERR_INVALID_ARGUMENT; }
-  if (path == B200_QMM_AUTO) path = rows <= 2 ? B200_QMM_SIMT : B200_QMM_TCGEN05;
+  // Quantised weights, up to 8 rows: register-dequant mma.sync kernel (pure weight streaming,
+  // measured 1.5-2.9 TB/s against 0.8-1.4 TB/s for tcgen05 at these sizes); more rows, or dense
+  // weights: tcgen05.
+  if (path == B200_QMM_AUTO) path = (rows <= 8 && w->mode != B200_Q_BF16) ? B200_QMM_MMA : B200_QMM_TCGEN05;
+  if (path == B200_QMM_MMA && w->mode == B200_Q_BF16) path = B200_QMM_TCGEN05;
   QmmArgs a{};
   a.blocks = w->d_blocks; a.x = (const __nv_bfloat16*)d_x; a.y = (__nv_bfloat16*)d_y;
   a.residual = (const __nv_bfloat16*)d_residual;
   a.rows = rows; a.n = w->n; a.k = w->k; a.nt = w->nt; a.kc = w->kc; a.epilogue = epilogue; a.swiglu_limit = swiglu_limit;
   cudaStream_t s = (cudaStream_t)stream;
+  if (path == B200_QMM_MMA)
+    return w->mode == B200_Q_AFFINE4_G64 ? launch_mma<B200_Q_AFFINE4_G64>(a, rows, s) : launch_mma<B200_Q_MXFP4_G32>(a, rows, s);
   if (path == B200_QMM_SIMT) {
     if (w->mode == B200_Q_AFFINE4_G64) return launch_simt<B200_Q_AFFINE4_G64>(a, rows, s);
     if (w->mode == B200_Q_MXFP4_G32) return launch_simt<B200_Q_MXFP4_G32>(a, rows, s);
@@ -727,7 +925,7 @@ b200_status launch_tc_static(QmmArgs& a, int rows, int dev, cudaStream_t s) {
   a.x_row0 = 0;
   qmm_tc_kernel<MODE><<<dim3(a.nt, splits, tts), kTcThreads, smem, s>>>(xmap, a);
   B200_LAUNCH_CHECK();
-  return launch_finish(a, splits, s);
+  return splits == 1 ? B200_OK : launch_finish(a, splits, s);
 }
 }  // namespace
 
