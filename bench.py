@@ -399,6 +399,119 @@ def cpu_baseline_c3(c, n_req, sample_req: int = 16, seed: int = 4321):
                       f"extrapolated to {c['n_layers']} layers + lm_head; {t_layer:.2f} s measured"}
 
 
+# ---------------------------------------------------------------------------------------------
+# config 4: MXFP4 MoE layer stack (expert parallel across ranks)
+# ---------------------------------------------------------------------------------------------
+MOE = dict(hidden=4096, n_experts=256, inter=2048, top_k=6, layers=4, tokens=4096)
+
+
+def run_moe(args, rank, world, local):
+    import torch
+    import torch.distributed as dist
+
+    from dmlx_b200 import device as dev
+    from dmlx_b200 import expert_parallel as ep
+
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    c = dict(MOE)
+    if args.layers:
+        c["layers"] = args.layers
+    K, W = args.steps, max(args.warmup, 3)
+    n_tok = c["tokens"] // world  # the step decodes 4096 tokens in total: strong scaling
+    el = c["n_experts"] // world
+    rng = np.random.default_rng(77)
+    bias = torch.tensor(rng.normal(0, 0.004, c["n_experts"]).astype(np.float32), device="cuda")  # skewed load
+    layers = []
+    for l in range(c["layers"]):
+        gate = dev.QWeight.random(dev.Q_BF16, c["n_experts"], c["hidden"], 1, seed=1000 + l)
+        gu = dev.QWeight.random(dev.Q_MXFP4_G32, 2 * c["inter"], c["hidden"], el, seed=2000 + 97 * l + rank)
+        dn = dev.QWeight.random(dev.Q_MXFP4_G32, c["hidden"], c["inter"], el, seed=3000 + 97 * l + rank)
+        sgu = dev.QWeight.random(dev.Q_MXFP4_G32, 2 * c["inter"], c["hidden"], 1, seed=4000 + l)
+        sdn = dev.QWeight.random(dev.Q_MXFP4_G32, c["hidden"], c["inter"], 1, seed=5000 + l)
+        if world == 1:
+            layers.append(dev.MoELayer(c["hidden"], c["n_experts"], c["inter"], c["top_k"], gate, gu, dn, sgu, sdn,
+                                       bias=bias.cpu().numpy(), route_scale=1.5, tile_rows=128, max_tokens=n_tok))
+        else:
+            layers.append(ep.ExpertParallelMoE(c["hidden"], c["n_experts"], c["inter"], c["top_k"], gate, gu, dn, sgu, sdn,
+                                               bias=bias, route_scale=1.5, tile_rows=128))
+    g = torch.Generator(device="cuda").manual_seed(11 + rank)
+    x_host = torch.randn((n_tok, c["hidden"]), generator=torch.Generator().manual_seed(11 + rank)).bfloat16().pin_memory()
+    x = x_host.cuda()
+
+    def step(inp):
+        h = inp
+        for layer in layers:
+            h = layer.forward(h)
+        return h
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for _ in range(W):
+        step(x)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        step(x)
+    e1.record()
+    barrier()
+    total_ms = e0.elapsed_time(e1)
+    out_host = torch.empty_like(x_host).pin_memory()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    t0.record()
+    for _ in range(K):
+        x.copy_(x_host, non_blocking=True)
+        out_host.copy_(step(x), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+    t1.record()
+    barrier()
+    e2e_ms = t0.elapsed_time(t1)
+    clocks = sampler.stop() if rank == 0 else None
+    assert dev.qmm_error_word() == 0
+    if world > 1:
+        t = torch.tensor([total_ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms = t.tolist()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    ms = total_ms / K
+    per_expert_params = 3 * c["inter"] * c["hidden"]
+    flops = c["layers"] * c["tokens"] * (c["top_k"] + 1) * 2.0 * per_expert_params
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    peak = float(peaks.get("bf16_tflops_sustained", 1400.0)) * world
+    achieved = flops / (ms * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "decode tokens/sec (ragged continuous batch)", "value": c["tokens"] / (ms * 1e-3), "unit": "decode tokens/s",
+        "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "mxfp4 weights (E2M1 + E8M0/32), bf16 activations, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "moe_mxfp4 layer stack", "layers": c["layers"], "hidden": c["hidden"], "experts": c["n_experts"],
+                   "expert_inter": c["inter"], "shared_experts": 1, "top_k": c["top_k"], "tokens_per_step": c["tokens"],
+                   "routing": "softmax + seeded per-expert bias (skewed load)",
+                   "l2": f"inputs larger than L2 ({c['layers'] * 257 * per_expert_params * 0.53125 / 1e9:.1f} GB of expert weights)",
+                   "parallelism": f"ep{world}" if world > 1 else "single GPU, all experts local"},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                     "peak_kind": "of measured (sustained cuBLAS bf16)" if peaks else "of fallback", "traffic": None,
+                     "kernel": "qmm_tc_kernel<mxfp4> grouped (gate/up + down) and dense (shared expert)",
+                     "algorithmic_flops_per_step": flops},
+        "e2e": {"value": c["tokens"] / (e2e_ms / K * 1e-3), "unit": "decode tokens/s",
+                "h2d_bytes_per_step": int(x_host.numel() * 2 * world), "d2h_bytes_per_step": int(x_host.numel() * 2 * world)},
+        "gpu_launches": None, "clocks": clocks,
+    }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_reference(args, rank: int):
     """--impl reference: the reference's own algorithm for the path on the host cores.  The
     reference itself (Zig + MLX) cannot be built here, so the timed code is the oracle's C twin."""
@@ -473,7 +586,7 @@ def main():
     ap.add_argument("--seqs", type=int, default=64, help="sequences per GPU (64 = the configuration; fewer for profiling)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = 10 if args.impl == "reference" else (50 if args.workload.startswith("llama") else 500)
+        args.steps = 10 if args.impl == "reference" else (50 if args.workload.startswith("llama") else (20 if args.workload.startswith("moe") else 500))
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -490,6 +603,9 @@ def main():
         raise SystemExit("bench.py needs a CUDA device (the product has no CPU path)")
     if args.workload.startswith("llama"):
         run_llama(args, rank, world, local)
+        return
+    if args.workload.startswith("moe"):
+        run_moe(args, rank, world, local)
         return
     torch.cuda.set_device(local)
     if world > 1:
@@ -582,7 +698,7 @@ def main():
                    "page_tokens": PAGE, "pool": "random permutation over 1.25x pages in use",
                    "l2": f"inputs larger than L2 ({alg / 1e6:.0f} MB of KV per step)", "parallelism": f"dp{world}"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}", "traffic": None, "kernel": "paged_attn_kernel (+plan, +combine)",
+                     "peak_kind": f"of {peak_kind}", "traffic": None, "kernel": ("paged_attn_kernel" if fp8 else "paged_attn_mma_kernel") + " (+plan, +combine)",
                      "algorithmic_bytes_per_launch": alg, "kernel_ms": kern_ms, "frac_of_8TBs": achieved / 8000.0},
         "e2e": {"value": tokens_per_step / (e2e_ms / args.steps * 1e-3), "unit": "decode tokens/s",
                 "h2d_bytes_per_step": int(q_host.numel() * 2 + desc_host.numel() * 4),

@@ -194,6 +194,7 @@ _sig("b200_moe_route", i32, vp, i32, vp, i32, i32, i32, i32, f32, vp, vp, vp, vp
 _sig("b200_moe_group", i32, vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp)
 _sig("b200_moe_gather", i32, vp, vp, vp, i32, i32, i32, vp, vp, vp)
 _sig("b200_moe_grouped_qmm", i32, vp, vp, i32, vp, i32, vp, f32, vp, vp, i32, i32, vp)
+_sig("b200_moe_gather_rows", i32, vp, vp, vp, i32, i32, vp)
 _sig("b200_moe_combine", i32, vp, vp, i32, i32, i32, vp, vp, vp)
 _sig("b200_moe_create", i32, P(MoeConfig), vp, P(f32), vp, vp, vp, vp, P(vp))
 _sig("b200_moe_destroy", None, vp)

@@ -254,6 +254,16 @@ b200_status b200_moe_grouped_qmm(const b200_qweight* w, const void* d_x_sorted, 
                           d_n_items, max_items, tile_rows, stream);
 }
 
+b200_status b200_gather_rows(const void* d_src, const int32_t* d_idx, void* d_dst, int32_t rows, int32_t hidden, void* stream);
+
+b200_status b200_moe_gather_rows(const void* d_src, const int32_t* d_idx, void* d_dst, int32_t rows, int32_t hidden,
+                                 void* stream) {
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (hidden % 8) { b200_set_error("gather_rows: hidden must be a multiple of 8"); return B200_ERR_INVALID_ARGUMENT; }
+  return b200_gather_rows(d_src, d_idx, d_dst, rows, hidden, stream);
+}
+
 b200_status b200_moe_combine(const void* d_y_sorted, const int32_t* d_inv_order, int32_t n_tokens, int32_t k,
                              int32_t hidden, const void* d_shared_out, void* d_out, void* stream) {
   b200_status st = b200_require_device();

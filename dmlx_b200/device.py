@@ -237,8 +237,17 @@ class QWeight:
                                            biases.ctypes.data if biases is not None else None, C.byref(h)))
         self._h, self.mode, self.n, self.k, self.n_experts = h.value, mode, n, k, n_experts
 
+    @classmethod
+    def random(cls, mode: int, n: int, k: int, n_experts: int = 1, seed: int = 1) -> "QWeight":
+        """Synthetic weights generated on the device (b200_qweight_random)."""
+        h = C.c_void_p()
+        _lib.check(lib.b200_qweight_random(mode, n_experts, n, k, seed, C.byref(h)))
+        w = cls.__new__(cls)
+        w._h, w.mode, w.n, w.k, w.n_experts = h.value, mode, n, k, n_experts
+        return w
+
     def __del__(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:
             lib.b200_qweight_destroy(self._h)
             self._h = None
 
@@ -420,3 +429,38 @@ class MoELayer:
         off = np.zeros(e + 1, np.int32)
         _lib.check(lib.b200_moe_last_routing(self._h, n_tokens, idx.ctypes.data, w.ctypes.data, off.ctypes.data))
         return idx, w, off
+
+
+def moe_gather(x: torch.Tensor, order: torch.Tensor, weights: torch.Tensor, k: int):
+    """b200_moe_gather -> (x_sorted [N*k, D] bf16, row_scales [N*k] f32)."""
+    a, d = order.shape[0], x.shape[1]
+    xs = torch.empty((a, d), dtype=torch.bfloat16, device=x.device)
+    rs = torch.empty(a, dtype=torch.float32, device=x.device)
+    _lib.check(lib.b200_moe_gather(_ptr(x), _ptr(order), _ptr(weights), a, k, d, _ptr(xs), _ptr(rs), _stream()))
+    return xs, rs
+
+
+def gather_rows(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """b200_moe_gather_rows: dst[r] = src[idx[r]] (bf16 rows)."""
+    out = torch.empty((idx.shape[0], src.shape[1]), dtype=torch.bfloat16, device=src.device)
+    _lib.check(lib.b200_moe_gather_rows(_ptr(src), _ptr(idx), _ptr(out), idx.shape[0], src.shape[1], _stream()))
+    return out
+
+
+def moe_grouped_qmm(w: QWeight, x_sorted: torch.Tensor, items: torch.Tensor, n_items: torch.Tensor, tile_rows: int,
+                    epilogue: int = EPI_NONE, row_scales: Optional[torch.Tensor] = None, swiglu_limit: float = 0.0):
+    """b200_moe_grouped_qmm over work items {expert, first row, rows, 0}."""
+    rows = x_sorted.shape[0]
+    n_out = w.n // 2 if epilogue == EPI_SWIGLU else w.n
+    out = torch.empty((rows, n_out), dtype=torch.bfloat16, device=x_sorted.device)
+    _lib.check(lib.b200_moe_grouped_qmm(w._h, _ptr(x_sorted), rows, _ptr(out), epilogue, _ptr(row_scales), swiglu_limit,
+                                        _ptr(items), _ptr(n_items), items.shape[0], tile_rows, _stream()))
+    return out
+
+
+def moe_combine(y_sorted: torch.Tensor, inv_order: torch.Tensor, n_tokens: int, k: int,
+                shared_out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    out = torch.empty((n_tokens, y_sorted.shape[1]), dtype=torch.bfloat16, device=y_sorted.device)
+    _lib.check(lib.b200_moe_combine(_ptr(y_sorted), _ptr(inv_order), n_tokens, k, y_sorted.shape[1], _ptr(shared_out),
+                                    _ptr(out), _stream()))
+    return out

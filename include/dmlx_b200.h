@@ -381,6 +381,11 @@ b200_status b200_moe_group(const uint32_t* d_indices, const int32_t* d_counts, i
 b200_status b200_moe_gather(const void* d_x, const int32_t* d_order, const float* d_weights,
                             int32_t n_assign, int32_t k, int32_t hidden, void* d_x_sorted,
                             float* d_row_scales, void* stream);
+/* dst[r] = src[idx[r]] for bf16 rows (regrouping rows received from other ranks into expert-major
+ * order in the expert-parallel layout; no reference counterpart — the reference has no expert
+ * parallelism, src/models/expert_stream.zig streams experts from SSD instead). */
+b200_status b200_moe_gather_rows(const void* d_src, const int32_t* d_idx, void* d_dst, int32_t rows,
+                                 int32_t hidden, void* stream);
 /* Ragged grouped quantised matmul over the expert-sorted rows (gather_qmm with sorted indices,
  * src/models/deepseek_v4.zig:787-805,968-979); w stacks n_experts matrices; row_scales (optional)
  * multiplies each output row in the epilogue. */
