@@ -202,6 +202,17 @@ _sig("b200_moe_forward", i32, vp, vp, i32, vp, vp)
 _sig("b200_moe_last_routing", i32, vp, i32, vp, vp, vp)
 
 
+_sig("b200_request_prompt", u64, vp, P(u32), u64)
+_sig("b200_engine_create", vp, vp, vp, u64)
+_sig("b200_engine_destroy", None, vp)
+_sig("b200_engine_submit", i32, vp, u64, P(u32), u64, u64, P(u32), u64)
+_sig("b200_engine_step", i32, vp, P(TokenOutput), u64, P(u64), vp)
+_sig("b200_engine_active_count", u64, vp)
+_sig("b200_engine_result", i32, vp, u64, P(u32), u64, P(u64), P(i32))
+_sig("b200_engine_forget", None, vp, u64)
+_sig("b200_engine_free_pages", i32, vp)
+
+
 class B200Error(RuntimeError):
     def __init__(self, status: int):
         self.status = status

@@ -1,0 +1,132 @@
+// Engine step: the caller the reference's framework is missing (its scheduler and batch builder are
+// "not wired up" to a forward pass, docs/en/technical/continuous-batching-design.md:187).  One call
+// runs schedule() -> ragged batch descriptors -> b200_llama_step -> postprocess(), i.e. the
+// Engine_Step loop described at src/scheduler.zig:7-10, with the device page pool behind the
+// scheduler's BlockManager (admission takes one page, completion releases the sequence).
+//
+// Prefill is always chunked here (a prefilling request contributes its current chunk,
+// src/scheduler.zig:183-186): the reference's batch builder sends all remaining prompt tokens while
+// postprocess advances by one chunk (src/batch_builder.zig:50-66 vs src/scheduler.zig:335-336), which
+// would write the same tokens into the KV cache twice.
+#include <algorithm>
+#include <unordered_map>
+#include <vector>
+
+#include "common.h"
+
+struct b200_engine {
+  b200_llama* model = nullptr;
+  b200_kv* kv = nullptr;
+  b200_sched_bm* bm = nullptr;
+  b200_scheduler* sched = nullptr;
+  uint64_t max_prefill = 512;
+  std::unordered_map<uint64_t, b200_request*> requests;  // owned
+  std::vector<b200_request*> prefill, decode;
+  std::vector<b200_pack_desc> descs;
+  std::vector<uint32_t> flat, next;
+  std::vector<b200_token_output> outs;
+  std::vector<uint32_t> scratch;
+  int32_t last_free_pages = 0;
+};
+
+extern "C" {
+
+b200_engine* b200_engine_create(b200_llama* model, b200_kv* kv, uint64_t max_prefill_tokens) {
+  auto* e = new b200_engine();
+  e->model = model;
+  e->kv = kv;
+  e->max_prefill = std::max<uint64_t>(1, max_prefill_tokens);
+  e->bm = b200_sched_bm_create_with_kv(kv);
+  if (!e->bm) { delete e; return nullptr; }
+  e->sched = b200_scheduler_create(e->bm, e->max_prefill);
+  return e;
+}
+
+void b200_engine_destroy(b200_engine* e) {
+  if (!e) return;
+  b200_scheduler_destroy(e->sched);
+  b200_sched_bm_destroy(e->bm);
+  for (auto& kvp : e->requests) b200_request_destroy(kvp.second);
+  delete e;
+}
+
+b200_status b200_engine_submit(b200_engine* e, uint64_t id, const uint32_t* prompt, uint64_t n_prompt, uint64_t max_tokens,
+                               const uint32_t* stop_tokens, uint64_t n_stop) {
+  if (e->requests.count(id)) { b200_set_error("engine: request id %llu already exists", (unsigned long long)id); return B200_ERR_INVALID_ARGUMENT; }
+  if (n_prompt == 0 || max_tokens == 0) { b200_set_error("engine: empty prompt or max_tokens 0"); return B200_ERR_INVALID_ARGUMENT; }
+  b200_request* r = b200_request_create(id, prompt, n_prompt, max_tokens, stop_tokens, n_stop);
+  e->requests[id] = r;
+  return b200_scheduler_add_request(e->sched, r);
+}
+
+uint64_t b200_engine_active_count(const b200_engine* e) { return b200_scheduler_active_count(e->sched); }
+
+b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t cap, uint64_t* n_out, void* stream) {
+  *n_out = 0;
+  const uint64_t active = b200_scheduler_active_count(e->sched);
+  if (active == 0) return B200_OK;
+  e->prefill.resize(active);
+  e->decode.resize(active);
+  uint64_t np = 0, nd = 0, need = 0;
+  b200_status st = b200_scheduler_schedule(e->sched, e->prefill.data(), &np, e->decode.data(), &nd, active, &need);
+  if (st != B200_OK) return st;
+  if (np + nd == 0) return B200_OK;
+  e->descs.clear();
+  e->flat.clear();
+  for (uint64_t i = 0; i < np; ++i) {  // prefill requests first (src/batch_builder.zig:100-111)
+    b200_request* r = e->prefill[i];
+    const uint64_t off = b200_request_prefill_offset(r);
+    const uint64_t len = b200_request_current_prefill_chunk_len(r, e->max_prefill);
+    e->scratch.resize(b200_request_prompt_len(r));
+    b200_request_prompt(r, e->scratch.data(), e->scratch.size());
+    b200_pack_desc d{b200_request_kv_slot(r), (int32_t)len, (int32_t)off, (int32_t)e->flat.size()};
+    e->flat.insert(e->flat.end(), e->scratch.begin() + off, e->scratch.begin() + off + len);
+    e->descs.push_back(d);
+  }
+  for (uint64_t i = 0; i < nd; ++i) {  // decode rows take the token the device sampled last step
+    b200_request* r = e->decode[i];
+    e->descs.push_back(b200_pack_desc{b200_request_kv_slot(r), 1, (int32_t)(b200_request_seq_len(r) - 1), -1});
+  }
+  e->next.resize(e->descs.size());
+  st = b200_llama_step(e->model, e->kv, e->descs.data(), (int32_t)e->descs.size(), e->flat.data(), (int32_t)e->flat.size(),
+                       e->next.data(), &e->last_free_pages, stream);
+  if (st != B200_OK) return st;
+  e->outs.clear();
+  for (uint64_t i = 0; i < np + nd; ++i) {
+    b200_request* r = i < np ? e->prefill[i] : e->decode[i - np];
+    e->outs.push_back(b200_token_output{b200_request_id(r), e->next[i], 0});
+  }
+  // Tokens that become part of a request's output this step: every decode row, and a prefill row
+  // whose chunk was the last one (src/scheduler.zig:338-349).
+  for (uint64_t i = 0; i < np + nd; ++i) {
+    b200_request* r = i < np ? e->prefill[i] : e->decode[i - np];
+    const bool last_chunk = i < np && b200_request_prefill_offset(r) + b200_request_current_prefill_chunk_len(r, e->max_prefill) >=
+                                          b200_request_prompt_len(r);
+    if (i >= np || last_chunk) {
+      if (*n_out >= cap) { b200_set_error("engine step: output array holds %llu tokens", (unsigned long long)cap); return B200_ERR_CAPACITY; }
+      out[(*n_out)++] = e->outs[i];
+    }
+  }
+  return b200_scheduler_postprocess(e->sched, e->outs.data(), e->outs.size());
+}
+
+// Generated tokens of a request so far (and whether it has finished); finished requests stay
+// queryable until b200_engine_forget.
+b200_status b200_engine_result(const b200_engine* e, uint64_t id, uint32_t* out, uint64_t cap, uint64_t* n, int32_t* done) {
+  auto it = e->requests.find(id);
+  if (it == e->requests.end()) { b200_set_error("engine: unknown request %llu", (unsigned long long)id); return B200_ERR_INVALID_ARGUMENT; }
+  *n = b200_request_generated(it->second, out, cap);
+  *done = b200_request_state(it->second) == B200_REQ_DONE;
+  return B200_OK;
+}
+
+void b200_engine_forget(b200_engine* e, uint64_t id) {
+  auto it = e->requests.find(id);
+  if (it == e->requests.end() || b200_request_state(it->second) != B200_REQ_DONE) return;
+  b200_request_destroy(it->second);
+  e->requests.erase(it);
+}
+
+int32_t b200_engine_free_pages(const b200_engine* e) { return (int32_t)b200_sched_bm_free_count(e->bm); }
+
+}  // extern "C"

@@ -269,6 +269,10 @@ uint64_t b200_request_generated(const b200_request* r, uint32_t* out, uint64_t c
   for (uint64_t i = 0; i < r->generated.size() && i < cap; ++i) out[i] = r->generated[i];
   return r->generated.size();
 }
+uint64_t b200_request_prompt(const b200_request* r, uint32_t* out, uint64_t cap) {
+  for (uint64_t i = 0; i < r->prompt.size() && i < cap; ++i) out[i] = r->prompt[i];
+  return r->prompt.size();
+}
 uint64_t b200_request_block_ids(const b200_request* r, uint64_t* out, uint64_t cap) {
   for (uint64_t i = 0; i < r->block_ids.size() && i < cap; ++i) out[i] = r->block_ids[i];
   return r->block_ids.size();

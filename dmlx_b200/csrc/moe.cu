@@ -19,6 +19,8 @@
 #include "common.h"
 #include "qmm.cuh"
 
+b200_status b200_gather_rows(const void* d_src, const int32_t* d_idx, void* d_dst, int32_t rows, int32_t hidden, void* stream);
+
 namespace {
 
 constexpr int kMaxExperts = 1024;
@@ -253,8 +255,6 @@ b200_status b200_moe_grouped_qmm(const b200_qweight* w, const void* d_x_sorted, 
   return b200_qmm_grouped(w, d_x_sorted, rows, d_y_sorted, epilogue, d_row_scales, swiglu_limit, (const int4*)d_items,
                           d_n_items, max_items, tile_rows, stream);
 }
-
-b200_status b200_gather_rows(const void* d_src, const int32_t* d_idx, void* d_dst, int32_t rows, int32_t hidden, void* stream);
 
 b200_status b200_moe_gather_rows(const void* d_src, const int32_t* d_idx, void* d_dst, int32_t rows, int32_t hidden,
                                  void* stream) {

@@ -464,3 +464,44 @@ def moe_combine(y_sorted: torch.Tensor, inv_order: torch.Tensor, n_tokens: int, 
     _lib.check(lib.b200_moe_combine(_ptr(y_sorted), _ptr(inv_order), n_tokens, k, y_sorted.shape[1], _ptr(shared_out),
                                     _ptr(out), _stream()))
     return out
+
+
+class Engine:
+    """b200_engine_*: scheduler + device page pool + model step in one loop."""
+
+    def __init__(self, model: LlamaModel, kv: PagedKVCache, max_prefill_tokens: int = 512):
+        self._h = lib.b200_engine_create(model._h, kv._h, max_prefill_tokens)
+        if not self._h:
+            raise _lib.B200Error(_lib.ERR_CUDA)
+        self._keep = (model, kv)
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib.b200_engine_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        self.close()
+
+    def submit(self, rid: int, prompt: Sequence[int], max_tokens: int, stop_tokens: Sequence[int] = ()):
+        p = (C.c_uint32 * max(len(prompt), 1))(*[int(t) for t in prompt])
+        s = (C.c_uint32 * max(len(stop_tokens), 1))(*[int(t) for t in stop_tokens])
+        _lib.check(lib.b200_engine_submit(self._h, rid, p, len(prompt), max_tokens, s, len(stop_tokens)))
+
+    def step(self, cap: int = 4096):
+        out = (_lib.TokenOutput * cap)()
+        n = C.c_uint64()
+        _lib.check(lib.b200_engine_step(self._h, out, cap, C.byref(n), _stream()))
+        return [(int(out[i].request_id), int(out[i].token)) for i in range(n.value)]
+
+    def active_count(self) -> int:
+        return int(lib.b200_engine_active_count(self._h))
+
+    def result(self, rid: int, cap: int = 8192):
+        out = (C.c_uint32 * cap)()
+        n, done = C.c_uint64(), C.c_int32()
+        _lib.check(lib.b200_engine_result(self._h, rid, out, cap, C.byref(n), C.byref(done)))
+        return [int(out[i]) for i in range(min(n.value, cap))], bool(done.value)
+
+    def free_pages(self) -> int:
+        return int(lib.b200_engine_free_pages(self._h))

@@ -101,6 +101,7 @@ int32_t b200_request_has_pending_prefill(const b200_request* r);                
 uint64_t b200_request_current_prefill_chunk_len(const b200_request* r, uint64_t max_prefill_tokens); /* :183-186 */
 uint64_t b200_request_generated(const b200_request* r, uint32_t* out, uint64_t cap); /* :111 */
 uint64_t b200_request_block_ids(const b200_request* r, uint64_t* out, uint64_t cap); /* :113 */
+uint64_t b200_request_prompt(const b200_request* r, uint32_t* out, uint64_t cap);     /* :110 */
 /* The reference's tests construct mid-flight requests by writing the fields. */
 void b200_request_force_state(b200_request* r, int32_t state, uint64_t prefill_offset,
                               const uint32_t* generated, uint64_t n_generated);
@@ -356,6 +357,25 @@ void b200_llama_enable_graphs(b200_llama* m, int32_t on);
  * for the reference's per-step timing logs (src/models/expert_stream.zig:36-51 TokenStepMetrics). */
 void b200_llama_profile_enable(b200_llama* m, int32_t on);
 b200_status b200_llama_profile_collect(b200_llama* m, double* ms, int64_t* calls);
+
+/* ---- engine step: schedule -> pack -> model step -> postprocess ------------------------------- */
+/* The Engine_Step loop of src/scheduler.zig:7-10 wired to a forward pass (the reference leaves
+ * it unwired, docs/en/technical/continuous-batching-design.md:187; its production loop is
+ * src/engine/engine_loop.zig:225-281,532-682).  The scheduler's BlockManager is the device pool.
+ * Prefill is chunked by max_prefill_tokens (src/scheduler.zig:183-186). */
+typedef struct b200_engine b200_engine;
+b200_engine* b200_engine_create(b200_llama* model, b200_kv* kv, uint64_t max_prefill_tokens);
+void b200_engine_destroy(b200_engine* e);
+b200_status b200_engine_submit(b200_engine* e, uint64_t id, const uint32_t* prompt, uint64_t n_prompt,
+                               uint64_t max_tokens, const uint32_t* stop_tokens, uint64_t n_stop);
+/* One step; `out` receives the tokens that joined a request's output this step. */
+b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t cap, uint64_t* n_out,
+                             void* stream);
+uint64_t b200_engine_active_count(const b200_engine* e);
+b200_status b200_engine_result(const b200_engine* e, uint64_t id, uint32_t* out, uint64_t cap,
+                               uint64_t* n, int32_t* done);
+void b200_engine_forget(b200_engine* e, uint64_t id);
+int32_t b200_engine_free_pages(const b200_engine* e);
 
 /* ---- mixture of experts ------------------------------------------------------------------------ */
 /* Top-k routing (MoERouter.topkRoute, src/moe_router.zig:55-103; DSV4Gate.forward scoring, bias and
