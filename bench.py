@@ -432,10 +432,10 @@ def run_moe(args, rank, world, local):
         sdn = dev.QWeight.random(dev.Q_MXFP4_G32, c["hidden"], c["inter"], 1, seed=5000 + l)
         if world == 1:
             layers.append(dev.MoELayer(c["hidden"], c["n_experts"], c["inter"], c["top_k"], gate, gu, dn, sgu, sdn,
-                                       bias=bias.cpu().numpy(), route_scale=1.5, tile_rows=128, max_tokens=n_tok))
+                                       bias=bias.cpu().numpy(), route_scale=1.5, tile_rows=args.moe_tile, max_tokens=n_tok))
         else:
             layers.append(ep.ExpertParallelMoE(c["hidden"], c["n_experts"], c["inter"], c["top_k"], gate, gu, dn, sgu, sdn,
-                                               bias=bias, route_scale=1.5, tile_rows=128))
+                                               bias=bias, route_scale=1.5, tile_rows=args.moe_tile))
     g = torch.Generator(device="cuda").manual_seed(11 + rank)
     x_host = torch.randn((n_tok, c["hidden"]), generator=torch.Generator().manual_seed(11 + rank)).bfloat16().pin_memory()
     x = x_host.cuda()
@@ -581,6 +581,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="llama8b_int4")
+    ap.add_argument("--moe-tile", type=int, default=128, help="moe_mxfp4 only: token tile of the grouped matmul")
     ap.add_argument("--layers", type=int, default=0, help="llama8b_int4 only: fewer layers (profiling / smoke runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--seqs", type=int, default=64, help="sequences per GPU (64 = the configuration; fewer for profiling)")

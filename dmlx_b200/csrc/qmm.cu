@@ -98,9 +98,19 @@ __global__ void qmm_finish_kernel(QmmArgs a, int splits) {
   const int token = (int)(idx / n4), c4 = (int)(idx % n4);
   const int nt = c4 / (kTileN / 4), r = (c4 % (kTileN / 4)) * 4, n = nt * kTileN + r;
   if (n >= a.n) return;
-  const size_t n_pad = (size_t)a.nt * kTileN;
-  const float4* p = reinterpret_cast<const float4*>(a.ws + (size_t)token * n_pad + n);
-  const size_t split_stride = (size_t)a.rows * n_pad / 4;  // in float4
+  // Dense launches keep each CTA's partial tile contiguous ([tile][split][tn][128]); grouped
+  // launches index by sorted row ([split][row][round_up(N,128)]).
+  const float4* p;
+  size_t split_stride;  // in float4
+  if (a.items) {
+    const size_t n_pad = (size_t)a.nt * kTileN;
+    p = reinterpret_cast<const float4*>(a.ws + (size_t)token * n_pad + n);
+    split_stride = (size_t)a.rows * n_pad / 4;
+  } else {
+    const int tts = (a.rows + a.tn - 1) / a.tn, tt = token / a.tn, t = token - tt * a.tn;
+    p = reinterpret_cast<const float4*>(a.ws + (((size_t)(nt * tts + tt) * splits) * a.tn + t) * kTileN + r);
+    split_stride = (size_t)a.tn * kTileN / 4;
+  }
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   int s = 0;
   for (; s + 4 <= splits; s += 4) {
@@ -201,14 +211,13 @@ __global__ void __launch_bounds__(kTileN) qmm_simt_kernel(QmmArgs a) {
     }
     }
   }
-  const size_t n_pad = (size_t)a.nt * kTileN;
+  float* wsp = a.ws + (((size_t)(nt * gridDim.z + tt) * gridDim.y + split) * a.tn) * kTileN;
 #pragma unroll
-  for (int t = 0; t < TT; ++t)
-    if (t0 + t < a.rows) a.ws[((size_t)split * a.rows + t0 + t) * n_pad + nt * kTileN + r] = acc[t];
+  for (int t = 0; t < TT; ++t) wsp[(size_t)t * kTileN + r] = acc[t];
 }
 
 // ---- tcgen05 kernel ------------------------------------------------------------------------------
-constexpr int kTcThreads = 192;
+constexpr int kTcThreads = 320;  // warps 0-7 dequantise (0-3 also run the epilogue), 8 loads, 9 issues MMAs
 constexpr int kRawStride = 5120;  // weight block padded to a multiple of 1024
 
 template <int MODE>
@@ -250,13 +259,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(&loaded[s], 1);
-      ptx::mbar_init(&a_ready[s], kTileN);
+      ptx::mbar_init(&a_ready[s], 2 * kTileN);
       ptx::mbar_init(&mma_done[s], 1);
     }
     ptx::mbar_init(accum_ready, 1);
     ptx::mbar_fence_init();
   }
-  if (warp == 5) {
+  if (warp == 9) {
     ptx::tmem_alloc(tmem_slot, ncols);
     ptx::tmem_relinquish();
   }
@@ -266,7 +275,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
   const uint32_t tmem_base = *tmem_slot;
   bool ok = true;
 
-  if (warp == 4) {
+  if (warp == 8) {
     if (lane == 0) {
       for (int i = 0; i < n_chunks && ok; ++i) {
         const int s = i % stages;
@@ -279,7 +288,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
         ptx::tma_load_2d(x_tile(s), &xmap, (kc0 + i) * kChunkK, a.x_row0 + t0, &loaded[s]);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     if (lane == 0) {
       const uint32_t idesc = ptx::umma_idesc_bf16(kTileN, tn);
       for (int i = 0; i < n_chunks && ok; ++i) {
@@ -297,16 +306,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
       if (ok) ptx::umma_commit(accum_ready);
     }
   } else {
-    // ---- dequantise: thread r owns weight row r of the tile ----
-    const int r = tid;
+    // ---- dequantise: thread (r, plane) owns one 32-column half of weight row r ----
+    const int r = tid & (kTileN - 1), my_plane = tid >> 7;
     for (int i = 0; i < n_chunks && ok; ++i) {
       const int s = i % stages;
       ok = ptx::mbar_wait(&loaded[s], (i / stages) & 1);
       if (!ok) break;
       const unsigned char* blk = raw_blk(s);
       unsigned char* arow = a_tile(s) + r * 128;
-#pragma unroll
-      for (int plane = 0; plane < (MODE == B200_Q_BF16 ? 0 : 2); ++plane) {
+      if (MODE != B200_Q_BF16) {
+        const int plane = my_plane;
         const uint4 raw = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[r];
         __nv_bfloat162 s2, b2;
         row_params<MODE>(blk, r, plane, s2, b2);
@@ -321,13 +330,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
       ptx::mbar_arrive(&a_ready[s]);
     }
     // ---- accumulator -> f32 partial tile in scratch ----
-    if (ok) ok = ptx::mbar_wait(accum_ready, 0);
-    if (ok) {
+    if (ok && warp < 4) ok = ptx::mbar_wait(accum_ready, 0);
+    if (ok && warp < 4) {
       ptx::tc_fence_after_sync();
-      const size_t n_pad = (size_t)a.nt * kTileN;
       const int n = nt * kTileN + warp * 32 + lane;
-      const bool direct = gridDim.y == 1;  // one K split: apply the epilogue here, no finish kernel
-      float* wsp = a.ws + ((size_t)split * a.rows + t0) * n_pad + n;
+      // One K split and a small token tile: apply the epilogue here and skip the finish kernel.  With
+      // large token tiles the strided 64-byte row stores cost more than the extra pass.
+      const bool direct = gridDim.y == 1 && tn <= 64;
+      const size_t n_pad = a.items ? (size_t)a.nt * kTileN : (size_t)kTileN;  // stride between token rows
+      float* wsp = a.items ? a.ws + ((size_t)split * a.rows + t0) * n_pad + n
+                           : a.ws + (((size_t)(nt * gridDim.z + blockIdx.z) * gridDim.y + split) * tn) * kTileN + warp * 32 + lane;
       for (int c0 = 0; c0 < rows_here; c0 += 32) {
         uint32_t v[32];
         ptx::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
@@ -367,7 +379,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
   if (!ok) atomicExch(a.err, B200_ERR_DEVICE_FLAGGED);
   ptx::tc_fence_before_sync();
   const int any_bad = __syncthreads_or(!ok);
-  if (warp == 5) ptx::tmem_dealloc(tmem_base, ncols);
+  if (warp == 9) ptx::tmem_dealloc(tmem_base, ncols);
   (void)any_bad;
 }
 
@@ -490,13 +502,13 @@ __global__ void __launch_bounds__(kGemvThreads, 2) qmm_mma_kernel(QmmArgs a) {
       }
     }
     if (ok) {
-      const size_t n_pad = (size_t)a.nt * kTileN;
+      float* wsp = a.ws + (((size_t)(nt * gridDim.z + blockIdx.z) * gridDim.y + split) * a.tn) * kTileN;
 #pragma unroll
       for (int j = 0; j < NT8; ++j) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const int tok = t0 + j * 8 + 2 * t + (e & 1), row = (e & 2) ? rB : rA;
-          if (tok < a.rows) a.ws[((size_t)split * a.rows + tok) * n_pad + nt * kTileN + row] = acc[j][e];
+          const int tl = j * 8 + 2 * t + (e & 1), row = (e & 2) ? rB : rA;
+          if (t0 + tl < a.rows) wsp[(size_t)tl * kTileN + row] = acc[j][e];
         }
       }
     }
@@ -699,7 +711,7 @@ static b200_status launch_simt(QmmArgs& a, int rows, cudaStream_t s) {
   const int splits0 = pick_splits(tiles, a.kc, g_sms, 8);
   a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
   const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
-  st = ensure_state((size_t)splits * rows * a.nt * kTileN * sizeof(float));
+  st = ensure_state((size_t)splits * (size_t)tts * TT * a.nt * kTileN * sizeof(float));
   if (st != B200_OK) return st;
   a.ws = g_ws; a.err = g_err;
   qmm_simt_kernel<MODE, TT><<<dim3(a.nt, splits, tts), kTileN, 0, s>>>(a);
@@ -732,9 +744,9 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
   const int fixed = 1024 /*alignment slack*/ + 8 * (3 * 8 + 2) + 16;
   // Small token tiles leave room for two CTAs per SM (more weight bytes in flight); large ones
   // take the whole SM.
-  const int per_cta = tn <= 64 ? 108 * 1024 : std::min(smem_budget[MODE], 220 * 1024);
+  const int per_cta = tn <= 128 ? 110 * 1024 : std::min(smem_budget[MODE], 220 * 1024);
   a.stages = std::max(2, std::min(8, (per_cta - fixed) / stage_stride));
-  const int ctas_per_sm = tn <= 64 ? 2 : 1;
+  const int ctas_per_sm = tn <= 128 ? 2 : 1;
   const size_t smem = (size_t)a.stages * stage_stride + fixed;
   if ((int)smem > smem_budget[MODE]) {
     b200_set_error("qmm: %zu bytes of shared memory needed, %d available", smem, smem_budget[MODE]);
@@ -743,7 +755,7 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
   const int splits0 = a.items ? 1 : pick_splits(tiles, a.kc, g_sms, ctas_per_sm);
   a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
   const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
-  st = ensure_state((size_t)splits * rows * a.nt * kTileN * sizeof(float));
+  st = ensure_state((size_t)splits * (a.items ? (size_t)rows : (size_t)tts * tn) * a.nt * kTileN * sizeof(float));
   if (st != B200_OK) return st;
   a.ws = g_ws; a.err = g_err;
   CUtensorMap xmap;
@@ -752,7 +764,7 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
   a.x_row0 = 0;
   qmm_tc_kernel<MODE><<<dim3(a.nt, splits, a.items ? a.max_items : tts), kTcThreads, smem, s>>>(xmap, a);
   B200_LAUNCH_CHECK();
-  return splits == 1 ? B200_OK : launch_finish(a, splits, s);  // one split writes its output itself
+  return (splits == 1 && tn <= 64) ? B200_OK : launch_finish(a, splits, s);  // a single small split writes its output itself
 }
 
 template <int MODE, int NT8>
@@ -765,7 +777,7 @@ static b200_status launch_mma_nt(QmmArgs& a, int rows, cudaStream_t s) {
   const int splits0 = pick_splits(a.nt * tts, a.kc, g_sms, 2);
   a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
   const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
-  st = ensure_state((size_t)splits * rows * a.nt * kTileN * sizeof(float));
+  st = ensure_state((size_t)splits * (size_t)tts * tile * a.nt * kTileN * sizeof(float));
   if (st != B200_OK) return st;
   a.ws = g_ws; a.err = g_err;
   const size_t smem = (size_t)kGemvRawStages * kRawStride + 2 * kGemvRawStages * sizeof(uint64_t);
@@ -900,9 +912,9 @@ b200_status launch_tc_static(QmmArgs& a, int rows, int dev, cudaStream_t s) {
     budget[MODE] = b;
   }
   const int fixed = 1024 + 8 * (3 * 8 + 2) + 16;
-  const int per_cta = tn <= 64 ? 108 * 1024 : std::min(budget[MODE], 220 * 1024);
+  const int per_cta = tn <= 128 ? 110 * 1024 : std::min(budget[MODE], 220 * 1024);
   a.stages = std::max(2, std::min(8, (per_cta - fixed) / stage_stride));
-  const int ctas_per_sm = tn <= 64 ? 2 : 1;
+  const int ctas_per_sm = tn <= 128 ? 2 : 1;
   const size_t smem = (size_t)a.stages * stage_stride + fixed;
   if ((int)smem > budget[MODE]) {
     b200_set_error("qmm (static scratch): %zu bytes of shared memory needed, %d available", smem, budget[MODE]);
@@ -911,7 +923,7 @@ b200_status launch_tc_static(QmmArgs& a, int rows, int dev, cudaStream_t s) {
   const int splits0 = pick_splits(tiles, a.kc, g_static_sms[dev], ctas_per_sm);
   a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
   const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
-  const size_t need = (size_t)splits * rows * a.nt * kTileN * sizeof(float);
+  const size_t need = (size_t)splits * tts * tn * a.nt * kTileN * sizeof(float);  // token tiles are padded to tn rows
   if (need > kStaticScratchBytes) {
     b200_set_error("qmm (static scratch): %d rows x N=%d in %d K-splits need %zu bytes of scratch, the built-in array holds %zu",
                    rows, a.n, splits, need, kStaticScratchBytes);
@@ -925,7 +937,7 @@ b200_status launch_tc_static(QmmArgs& a, int rows, int dev, cudaStream_t s) {
   a.x_row0 = 0;
   qmm_tc_kernel<MODE><<<dim3(a.nt, splits, tts), kTcThreads, smem, s>>>(xmap, a);
   B200_LAUNCH_CHECK();
-  return splits == 1 ? B200_OK : launch_finish(a, splits, s);
+  return (splits == 1 && tn <= 64) ? B200_OK : launch_finish(a, splits, s);
 }
 }  // namespace
 
