@@ -424,6 +424,9 @@ __global__ void __launch_bounds__(kGemvThreads, 2) qmm_mma_kernel(QmmArgs a) {
   extern __shared__ __align__(128) unsigned char gsm[];
   uint64_t* raw_full = reinterpret_cast<uint64_t*>(gsm + (size_t)kGemvRawStages * kRawStride);
   uint64_t* raw_free = raw_full + kGemvRawStages;
+  // Activation slab of this CTA's K range: NT8*8 token rows, row stride = chunks*128 + 16 bytes so
+  // that the 32 lanes of a B-fragment load hit 32 different banks.  Used when it fits (x_slab).
+  unsigned char* slab = reinterpret_cast<unsigned char*>(raw_free + kGemvRawStages);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
   const int nt = blockIdx.x, split = blockIdx.y, t0 = blockIdx.z * (NT8 * 8);
   const int kc0 = split * a.chunks_per_split, kc1 = min(kc0 + a.chunks_per_split, a.kc), n_chunks = kc1 - kc0;
@@ -434,6 +437,16 @@ __global__ void __launch_bounds__(kGemvThreads, 2) qmm_mma_kernel(QmmArgs a) {
       ptx::mbar_init(&raw_free[s], kGemvConsumers);
     }
     ptx::mbar_fence_init();
+  }
+  const int slab_stride = n_chunks * (kChunkK * 2) + 16;
+  if (a.x_slab) {
+    const int vec_per_row = n_chunks * (kChunkK * 2 / 16);
+    for (int idx = tid; idx < NT8 * 8 * vec_per_row; idx += kGemvThreads) {
+      const int row = idx / vec_per_row, v = idx - row * vec_per_row;
+      uint4 val = make_uint4(0u, 0u, 0u, 0u);
+      if (t0 + row < a.rows) val = *reinterpret_cast<const uint4*>(a.x + (size_t)(t0 + row) * a.k + (size_t)kc0 * kChunkK + v * 8);
+      *reinterpret_cast<uint4*>(slab + (size_t)row * slab_stride + v * 16) = val;
+    }
   }
   __syncthreads();
   bool ok = true;
@@ -466,10 +479,16 @@ __global__ void __launch_bounds__(kGemvThreads, 2) qmm_mma_kernel(QmmArgs a) {
       const int kw = (kc0 + i) * (kChunkK / 2);  // chunk start in 32-bit words
 #pragma unroll
       for (int j = 0; j < NT8; ++j) {
+        const uint32_t* srow = reinterpret_cast<const uint32_t*>(slab + (size_t)(j * 8 + g) * slab_stride) + i * (kChunkK / 2);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) {
-          xb[j][2 * ks] = xrow[j] ? __ldg(xrow[j] + kw + ks * 8 + t) : 0u;
-          xb[j][2 * ks + 1] = xrow[j] ? __ldg(xrow[j] + kw + ks * 8 + 4 + t) : 0u;
+          if (a.x_slab) {
+            xb[j][2 * ks] = srow[ks * 8 + t];
+            xb[j][2 * ks + 1] = srow[ks * 8 + 4 + t];
+          } else {
+            xb[j][2 * ks] = xrow[j] ? __ldg(xrow[j] + kw + ks * 8 + t) : 0u;
+            xb[j][2 * ks + 1] = xrow[j] ? __ldg(xrow[j] + kw + ks * 8 + 4 + t) : 0u;
+          }
         }
       }
       ok = ptx::mbar_wait(&raw_full[s], (i / kGemvRawStages) & 1);
@@ -774,16 +793,22 @@ static b200_status launch_mma_nt(QmmArgs& a, int rows, cudaStream_t s) {
   const int tts = (rows + tile - 1) / tile;
   b200_status st = ensure_state(0);
   if (st != B200_OK) return st;
-  const int splits0 = pick_splits(a.nt * tts, a.kc, g_sms, 2);
+  // enough K splits for the activation slab of a split (tile rows x chunks x 128 B) to fit 48 KiB
+  const int max_cps = std::max(1, ((48 * 1024) / tile - 16) / (kChunkK * 2));
+  const int splits0 = std::max(pick_splits(a.nt * tts, a.kc, g_sms, 2), (a.kc + max_cps - 1) / max_cps);
   a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
   const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
   st = ensure_state((size_t)splits * (size_t)tts * tile * a.nt * kTileN * sizeof(float));
   if (st != B200_OK) return st;
   a.ws = g_ws; a.err = g_err;
-  const size_t smem = (size_t)kGemvRawStages * kRawStride + 2 * kGemvRawStages * sizeof(uint64_t);
+  const size_t base_smem = (size_t)kGemvRawStages * kRawStride + 2 * kGemvRawStages * sizeof(uint64_t);
+  const size_t slab = (size_t)tile * ((size_t)a.chunks_per_split * kChunkK * 2 + 16);
+  a.x_slab = slab <= 48 * 1024 ? 1 : 0;  // keeps two CTAs per SM
+  const size_t smem = base_smem + (a.x_slab ? slab : 0);
   static bool configured = false;
   if (!configured) {
-    B200_CUDA_TRY(cudaFuncSetAttribute(qmm_mma_kernel<MODE, NT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200_CUDA_TRY(cudaFuncSetAttribute(qmm_mma_kernel<MODE, NT8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(base_smem + 48 * 1024)));
     configured = true;
   }
   qmm_mma_kernel<MODE, NT8><<<dim3(a.nt, splits, tts), kGemvThreads, smem, s>>>(a);
@@ -806,10 +831,10 @@ extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t 
   if (w->n_experts != 1) { b200_set_error("qmm: stacked expert weights go through the grouped entry point"); return B200_ERR_INVALID_ARGUMENT; }
   if (epilogue == B200_EPI_RESIDUAL && !d_residual) { b200_set_error("qmm: residual epilogue without a residual"); return B200_ERR_INVALID_ARGUMENT; }
   if (epilogue == B200_EPI_SWIGLU && (w->n % 2) != 0) { b200_set_error("qmm: SwiGLU needs an even N"); return B200_ERR_INVALID_ARGUMENT; }
-  // Quantised weights, up to 8 rows: register-dequant mma.sync kernel (pure weight streaming,
-  // measured 1.5-2.9 TB/s against 0.8-1.4 TB/s for tcgen05 at these sizes); more rows, or dense
+  // Quantised weights, up to 16 rows: register-dequant mma.sync kernel (pure weight streaming,
+  // measured 1.1-2.7 TB/s against 0.7-1.6 TB/s for tcgen05 at these sizes); more rows, or dense
   // weights: tcgen05.
-  if (path == B200_QMM_AUTO) path = (rows <= 8 && w->mode != B200_Q_BF16) ? B200_QMM_MMA : B200_QMM_TCGEN05;
+  if (path == B200_QMM_AUTO) path = (rows <= 16 && w->mode != B200_Q_BF16) ? B200_QMM_MMA : B200_QMM_TCGEN05;
   if (path == B200_QMM_MMA && w->mode == B200_Q_BF16) path = B200_QMM_TCGEN05;
   QmmArgs a{};
   a.blocks = w->d_blocks; a.x = (const __nv_bfloat16*)d_x; a.y = (__nv_bfloat16*)d_y;

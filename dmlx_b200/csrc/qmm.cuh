@@ -25,6 +25,7 @@ struct QmmArgs {
   int rows, n, k, nt, kc;
   int chunks_per_split, tn, stages;
   int epilogue;
+  int x_slab;                   // small-batch kernel: activations staged in shared memory
   int x_row0;                   // first row of this launch within the tensor map
   float swiglu_limit;
 
