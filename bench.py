@@ -140,6 +140,7 @@ def cpu_baseline_c2(ctxs, kv, k_rows, v_rows, q, sample: int = 8, min_time: floa
 
     from oracle import ref_c
 
+    ref_c.use_all_cores()
     idx = np.arange(min(sample, len(ctxs)))
     # a compact pool holding just the sampled sequences, pages in order
     off = np.concatenate([[0], np.cumsum(ctxs)])
@@ -353,7 +354,7 @@ def run_llama(args, rank, world, local):
     if tr:
         result["roofline"]["traffic"] = tr * kv_bytes_per_call
         result["roofline"]["traffic_note"] = "ncu capture of a 16-sequence case scaled by cached tokens"
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:
         result["cpu_baseline"] = cpu_baseline_c3(c, n_req)
     print(json.dumps(result))
     if world > 1:
@@ -366,6 +367,7 @@ def cpu_baseline_c3(c, n_req, sample_req: int = 16, seed: int = 4321):
     matmuls of the layer), extrapolated to 32 layers + lm_head by parameter count."""
     from oracle import ref_c
 
+    ref_c.use_all_cores()
     ctxs = c3_snapshot(seed, n_req)[:sample_req]
     rng = np.random.default_rng(0)
     hq, hkv, d, hid, ffn = c["n_heads"], c["n_kv_heads"], c["head_dim"], c["hidden"], c["ffn"]
@@ -517,6 +519,9 @@ def run_reference(args, rank: int):
     reference itself (Zig + MLX) cannot be built here, so the timed code is the oracle's C twin."""
     if rank != 0:
         return
+    from oracle import ref_c
+
+    ref_c.use_all_cores()  # torchrun exports OMP_NUM_THREADS=1
     if args.workload.startswith("llama"):
         times, cb = [], None
         for i in range(args.warmup + args.steps):
@@ -711,7 +716,7 @@ def main():
     if tr and not fp8:
         result["roofline"]["traffic"] = tr * alg
         result["roofline"]["traffic_note"] = "ncu capture of a 16-sequence case scaled by cached tokens"
-    if not args.no_cpu_baseline:
+    if not args.no_cpu_baseline and world == 1:
         cb, _ = cpu_baseline_c2(ctxs, kv, k_rows, v_rows, q)
         result["cpu_baseline"] = cb
     print(json.dumps(result))

@@ -27,6 +27,13 @@ def num_threads() -> int:
     return int(lib().ref_num_threads())
 
 
+def use_all_cores() -> int:
+    """Run the C twin on every core this process may use, whatever OMP_NUM_THREADS says."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    lib().ref_set_threads(C.c_int(n))
+    return num_threads()
+
+
 def paged_attention_decode(k_pool_bf16: np.ndarray, v_pool_bf16: np.ndarray, block_table: np.ndarray, ctx: np.ndarray,
                            hq: int, hkv: int, d: int, q: np.ndarray) -> np.ndarray:
     """k/v pool: uint16 [pages, hkv, 32, d]; block_table int32 [n_seq, max_pages]; q f32 [n_seq, hq, d]."""

@@ -134,6 +134,15 @@ void ref_qmm_mxfp4(const uint8_t* packed, const uint8_t* scales, int32_t n, int3
   }
 }
 
+/* Use `n` OpenMP threads from now on (launchers such as torchrun export OMP_NUM_THREADS=1). */
+void ref_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 int ref_num_threads(void) {
   int n = 1;
 #pragma omp parallel
