@@ -383,6 +383,179 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
   (void)any_bad;
 }
 
+// ---- tcgen05 kernel for large batches: two weight tiles per CTA ---------------------------------
+// With 129..256 rows per token tile the kernel above moves a 32 KiB activation tile through
+// shared memory for every 4.6 KiB weight block, and at one CTA per SM only four such stages fit:
+// the load -> dequantise -> MMA -> release chain of a stage is longer than the work the other
+// stages hold, and the tensor pipe idles.  Here a CTA owns TWO adjacent 128-row weight tiles and
+// multiplies both with the same activation tile (two accumulators, 2 x 256 tensor-memory columns):
+// a stage carries twice the MMA work per activation byte, so the same shared memory hides twice
+// the latency and the L2 -> SM activation traffic per flop halves.  16 dequant warps (one thread
+// per weight row and 32-column plane of either tile), one loader warp, one MMA warp.
+constexpr int kTc2Threads = 18 * 32;
+constexpr int kTc2DequantThreads = 16 * 32;
+
+// One 32-token batch of accumulators (v[j] = token c0+j, weight row n) to scratch or to the output.
+__device__ __forceinline__ void tile_epilogue_store(const QmmArgs& a, const uint32_t (&v)[32], int c0, int rows_here, int t0,
+                                                    int n, int lane, bool direct, float* wsp, size_t n_pad) {
+  if (!direct) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (c0 + j < rows_here) wsp[(size_t)(c0 + j) * n_pad] = __uint_as_float(v[j]);
+  } else if (a.epilogue == B200_EPI_SWIGLU) {
+    // rows 2i / 2i+1 of the tile are gate_i / up_i: neighbouring lanes
+    const float L = a.swiglu_limit;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float mine = __uint_as_float(v[j]);
+      const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+      if ((lane & 1) == 0 && c0 + j < rows_here && n < a.n) {
+        float g = mine, u = other;
+        if (L > 0.f) { g = fminf(g, L); u = fminf(fmaxf(u, -L), L); }
+        const int token = t0 + c0 + j;
+        a.y[(size_t)token * (a.n / 2) + n / 2] = __float2bfloat16(g / (1.0f + __expf(-g)) * u * a.row_scale(token));
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      if (c0 + j < rows_here && n < a.n) {
+        const int token = t0 + c0 + j;
+        const size_t o = (size_t)token * a.n + n;
+        float acc = __uint_as_float(v[j]);
+        if (a.epilogue == B200_EPI_RESIDUAL) acc += __bfloat162float(a.residual[o]);
+        a.y[o] = __float2bfloat16(acc * a.row_scale(token));
+      }
+    }
+  }
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kTc2Threads, 1) qmm_tc2_kernel(const __grid_constant__ CUtensorMap xmap, QmmArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int BB = block_bytes(MODE);
+  constexpr int kRaw = MODE == B200_Q_BF16 ? 0 : ((BB + 1023) / 1024) * 1024;  // dense blocks land in the MMA tile itself
+  const int tn = a.tn, stages = a.stages;
+  const int stage_stride = 2 * kTileN * 128 + tn * 128 + 2 * kRaw;
+  auto a_tile = [&](int s, int tile) { return smem + (size_t)s * stage_stride + tile * (kTileN * 128); };
+  auto x_tile = [&](int s) { return smem + (size_t)s * stage_stride + 2 * kTileN * 128; };
+  auto raw_blk = [&](int s, int tile) { return smem + (size_t)s * stage_stride + 2 * kTileN * 128 + tn * 128 + tile * kRaw; };
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_stride);
+  uint64_t* loaded = bars;
+  uint64_t* a_ready = bars + stages;
+  uint64_t* mma_done = bars + 2 * stages;
+  uint64_t* accum_ready = bars + 3 * stages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * stages + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int pair = blockIdx.x, split = blockIdx.y, tt = blockIdx.z;
+  const int t0 = tt * tn, rows_here = min(tn, a.rows - t0);
+  const int nt0 = 2 * pair;
+  const int n_tiles = min(2, a.nt - nt0);  // an odd tile count leaves the last CTA one tile
+  const int kc0 = split * a.chunks_per_split, kc1 = min(kc0 + a.chunks_per_split, a.kc);
+  const int n_chunks = kc1 - kc0;
+  constexpr uint32_t kCols = 512;  // accumulator of tile 0 at column 0, of tile 1 at column 256
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(&loaded[s], 1);
+      ptx::mbar_init(&a_ready[s], kTc2DequantThreads);
+      ptx::mbar_init(&mma_done[s], 1);
+    }
+    ptx::mbar_init(accum_ready, 1);
+    ptx::mbar_fence_init();
+  }
+  if (warp == 17) {
+    ptx::tmem_alloc(tmem_slot, kCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 16) {
+    if (lane == 0) {
+      for (int i = 0; i < n_chunks && ok; ++i) {
+        const int s = i % stages;
+        ok = ptx::mbar_wait(&mma_done[s], ((i / stages) & 1) ^ 1);
+        if (!ok) break;
+        ptx::mbar_expect_tx(&loaded[s], n_tiles * BB + tn * 128);
+        for (int tile = 0; tile < n_tiles; ++tile)
+          ptx::bulk_g2s(MODE == B200_Q_BF16 ? a_tile(s, tile) : raw_blk(s, tile),
+                        a.blocks + ((size_t)(nt0 + tile) * a.kc + kc0 + i) * BB, BB, &loaded[s]);
+        ptx::tma_load_2d(x_tile(s), &xmap, (kc0 + i) * kChunkK, a.x_row0 + t0, &loaded[s]);
+      }
+    }
+  } else if (warp == 17) {
+    if (lane == 0) {
+      const uint32_t idesc = ptx::umma_idesc_bf16(kTileN, tn);
+      for (int i = 0; i < n_chunks && ok; ++i) {
+        const int s = i % stages;
+        ok = ptx::mbar_wait(&loaded[s], (i / stages) & 1) && ptx::mbar_wait(&a_ready[s], (i / stages) & 1);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint64_t db = ptx::umma_desc_k_sw128(ptx::smem_u32(x_tile(s)));
+        for (int tile = 0; tile < n_tiles; ++tile) {
+          const uint64_t da = ptx::umma_desc_k_sw128(ptx::smem_u32(a_tile(s, tile)));
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4)
+            ptx::umma_bf16(tmem_base + tile * 256, da + 2 * k4, db + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+        }
+        ptx::umma_commit(&mma_done[s]);
+      }
+      if (ok) ptx::umma_commit(accum_ready);
+    }
+  } else {
+    // ---- dequantise: thread (r, plane, tile) owns one 32-column half of weight row r of a tile ----
+    const int r = tid & (kTileN - 1), plane = (tid >> 7) & 1, tile = tid >> 8;
+    for (int i = 0; i < n_chunks && ok; ++i) {
+      const int s = i % stages;
+      ok = ptx::mbar_wait(&loaded[s], (i / stages) & 1);
+      if (!ok) break;
+      if (MODE != B200_Q_BF16 && tile < n_tiles) {
+        const unsigned char* blk = raw_blk(s, tile);
+        unsigned char* arow = a_tile(s, tile) + r * 128;
+        const uint4 raw = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[r];
+        __nv_bfloat162 s2, b2;
+        row_params<MODE>(blk, r, plane, s2, b2);
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const int chunk16 = plane * 4 + w;
+          *reinterpret_cast<uint4*>(arow + ((chunk16 ^ (r & 7)) << 4)) = dequant_word<MODE>(words[w], s2, b2);
+        }
+      }
+      ptx::fence_proxy_async_smem();
+      ptx::mbar_arrive(&a_ready[s]);
+    }
+    // ---- accumulators: warp w reads lanes 32*(w%4); warps 4g..4g+3 take tile g/2, column half g%2 ----
+    if (ok) ok = ptx::mbar_wait(accum_ready, 0);
+    const int grp = warp >> 2, etile = grp >> 1, half = grp & 1;
+    if (ok && etile < n_tiles) {
+      ptx::tc_fence_after_sync();
+      const int lq = warp & 3;
+      const int nt = nt0 + etile, n = nt * kTileN + lq * 32 + lane;
+      const bool direct = gridDim.y == 1;
+      float* wsp = a.ws + (((size_t)(nt * gridDim.z + tt) * gridDim.y + split) * tn) * kTileN + lq * 32 + lane;
+      const int ch = ((tn / 2 + 31) / 32) * 32;
+      const int c_end = min(rows_here, (half + 1) * ch);
+      for (int c0 = half * ch; c0 < c_end; c0 += 32) {
+        uint32_t v[32];
+        ptx::tmem_ld32(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(etile * 256 + c0), v);
+        ptx::tmem_ld_wait();
+        tile_epilogue_store(a, v, c0, rows_here, t0, n, lane, direct, wsp, (size_t)kTileN);
+      }
+    }
+  }
+  if (!ok) atomicExch(a.err, B200_ERR_DEVICE_FLAGGED);
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 17) ptx::tmem_dealloc(tmem_base, kCols);
+}
+
 // ---- small-batch kernel: register dequantisation + mma.sync -------------------------------------
 // For a handful of rows the matmul is a weight-streaming problem, and the tcgen05 route above pays
 // a long dependent chain per chunk (dequantise into a 16 KiB shared tile -> MMA -> commit -> slot
@@ -570,7 +743,7 @@ b200_status make_x_map(CUtensorMap* map, const void* x, int rows, int k, int box
 // Number of K splits for `tiles` output tiles with `ctas_per_sm` resident CTAs per SM: the
 // smallest count whose grid comes closest to a whole number of waves, each split keeping at
 // least 4 chunks.
-int pick_splits(int tiles, int kc, int sms, int ctas_per_sm) {
+int pick_splits(int tiles, int kc, int sms, int ctas_per_sm, int fixed_cost = 2) {
   const int slots = sms * ctas_per_sm;
   const int max_s = std::max(1, std::min(16, kc / 4));
   int best = 1;
@@ -582,7 +755,7 @@ int pick_splits(int tiles, int kc, int sms, int ctas_per_sm) {
     const long long ctas = (long long)tiles * sp;
     const long long waves = (ctas + slots - 1) / slots;
     // useful work / occupied time, with a small penalty per split for its fixed cost
-    const double eff = (double)ctas / (double)(waves * slots) * (double)cps / (double)(cps + 2);
+    const double eff = (double)ctas / (double)(waves * slots) * (double)cps / (double)(cps + fixed_cost);
     if (eff > best_eff + 1e-9) { best_eff = eff; best = sp; }
   }
   return best;
@@ -786,6 +959,52 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
   return (splits == 1 && tn <= 64) ? B200_OK : launch_finish(a, splits, s);  // a single small split writes its output itself
 }
 
+// Large batches (129..256 rows per token tile): two weight tiles per CTA.
+template <int MODE>
+static b200_status launch_tc2(QmmArgs& a, int rows, cudaStream_t s) {
+  const int tn = std::min(256, ((rows + 15) / 16) * 16);
+  a.tn = tn;
+  const int tts = (rows + tn - 1) / tn;
+  const int pairs = (a.nt + 1) / 2;
+  b200_status st = ensure_state(0);
+  if (st != B200_OK) return st;
+  constexpr int BB = block_bytes(MODE);
+  constexpr int kRaw = MODE == B200_Q_BF16 ? 0 : ((BB + 1023) / 1024) * 1024;
+  const int stage_stride = 2 * kTileN * 128 + tn * 128 + 2 * kRaw;
+  static int smem_budget[3] = {0, 0, 0};
+  if (smem_budget[MODE] == 0) {
+    int dev = 0, optin = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    cudaFuncAttributes fa;
+    B200_CUDA_TRY(cudaFuncGetAttributes(&fa, qmm_tc2_kernel<MODE>));
+    const int budget = optin - (int)fa.sharedSizeBytes;
+    B200_CUDA_TRY(cudaFuncSetAttribute(qmm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget));
+    smem_budget[MODE] = budget;
+  }
+  const int fixed = 1024 /*alignment slack*/ + 8 * (3 * 8 + 2) + 16;
+  a.stages = std::min(6, (smem_budget[MODE] - fixed) / stage_stride);
+  if (a.stages < 2) {
+    b200_set_error("qmm: %d bytes of shared memory per stage, %d available", stage_stride, smem_budget[MODE]);
+    return B200_ERR_CAPACITY;
+  }
+  const size_t smem = (size_t)a.stages * stage_stride + fixed;
+  // a K split costs a 128 x tn f32 tile written and read back per weight tile: weigh it as chunks
+  const int splits0 = pick_splits(pairs * tts, a.kc, g_sms, 1, 2 + tn / 32);
+  a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
+  const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
+  st = ensure_state(splits > 1 ? (size_t)splits * (size_t)tts * tn * a.nt * kTileN * sizeof(float) : 0);
+  if (st != B200_OK) return st;
+  a.ws = g_ws; a.err = g_err;
+  CUtensorMap xmap;
+  st = make_x_map(&xmap, a.x, rows, a.k, tn);
+  if (st != B200_OK) return st;
+  a.x_row0 = 0;
+  qmm_tc2_kernel<MODE><<<dim3(pairs, splits, tts), kTc2Threads, smem, s>>>(xmap, a);
+  B200_LAUNCH_CHECK();
+  return splits == 1 ? B200_OK : launch_finish(a, splits, s);
+}
+
 template <int MODE, int NT8>
 static b200_status launch_mma_nt(QmmArgs& a, int rows, cudaStream_t s) {
   const int tile = NT8 * 8;
@@ -833,8 +1052,9 @@ extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t 
   if (epilogue == B200_EPI_SWIGLU && (w->n % 2) != 0) { b200_set_error("qmm: SwiGLU needs an even N"); return B200_ERR_INVALID_ARGUMENT; }
   // Quantised weights, up to 16 rows: register-dequant mma.sync kernel (pure weight streaming,
   // measured 1.1-2.7 TB/s against 0.7-1.6 TB/s for tcgen05 at these sizes); more rows, or dense
-  // weights: tcgen05.
-  if (path == B200_QMM_AUTO) path = (rows <= 16 && w->mode != B200_Q_BF16) ? B200_QMM_MMA : B200_QMM_TCGEN05;
+  // weights: tcgen05, with two weight tiles per CTA once a token tile exceeds 128 rows.
+  if (path == B200_QMM_AUTO)
+    path = (rows <= 16 && w->mode != B200_Q_BF16) ? B200_QMM_MMA : (rows > 128 ? B200_QMM_TCGEN05_X2 : B200_QMM_TCGEN05);
   if (path == B200_QMM_MMA && w->mode == B200_Q_BF16) path = B200_QMM_TCGEN05;
   QmmArgs a{};
   a.blocks = w->d_blocks; a.x = (const __nv_bfloat16*)d_x; a.y = (__nv_bfloat16*)d_y;
@@ -847,6 +1067,11 @@ extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t 
     if (w->mode == B200_Q_AFFINE4_G64) return launch_simt<B200_Q_AFFINE4_G64>(a, rows, s);
     if (w->mode == B200_Q_MXFP4_G32) return launch_simt<B200_Q_MXFP4_G32>(a, rows, s);
     return launch_simt<B200_Q_BF16>(a, rows, s);
+  }
+  if (path == B200_QMM_TCGEN05_X2) {
+    if (w->mode == B200_Q_AFFINE4_G64) return launch_tc2<B200_Q_AFFINE4_G64>(a, rows, s);
+    if (w->mode == B200_Q_MXFP4_G32) return launch_tc2<B200_Q_MXFP4_G32>(a, rows, s);
+    return launch_tc2<B200_Q_BF16>(a, rows, s);
   }
   if (w->mode == B200_Q_AFFINE4_G64) return launch_tc<B200_Q_AFFINE4_G64>(a, rows, s);
   if (w->mode == B200_Q_MXFP4_G32) return launch_tc<B200_Q_MXFP4_G32>(a, rows, s);
