@@ -88,6 +88,33 @@ __device__ __forceinline__ void row_params(const unsigned char* blk, int r, int 
   }
 }
 
+// Epilogue of one output quad: columns n..n+3 of row `token` (residual add, SwiGLU over
+// interleaved gate/up rows, per-row scale), written as bf16.
+__device__ __forceinline__ void finish_store(const QmmArgs& a, int token, int n, float4 acc) {
+  const float rs = a.row_scale(token);
+  if (a.epilogue == B200_EPI_SWIGLU) {
+    float g0 = acc.x, u0 = acc.y, g1 = acc.z, u1 = acc.w;
+    if (a.swiglu_limit > 0.f) {
+      const float L = a.swiglu_limit;
+      g0 = fminf(g0, L); g1 = fminf(g1, L);
+      u0 = fminf(fmaxf(u0, -L), L); u1 = fminf(fmaxf(u1, -L), L);
+    }
+    const float y0 = g0 / (1.0f + __expf(-g0)) * u0 * rs, y1 = g1 / (1.0f + __expf(-g1)) * u1 * rs;
+    *reinterpret_cast<__nv_bfloat162*>(a.y + (size_t)a.row_base_out(token) * (a.n / 2) + n / 2) = __floats2bfloat162_rn(y0, y1);
+  } else {
+    const size_t o = (size_t)a.row_base_out(token) * a.n + n;
+    if (a.epilogue == B200_EPI_RESIDUAL) {
+      const uint2 rv = *reinterpret_cast<const uint2*>(a.residual + o);
+      acc.x += ptx::bf16_lo(rv.x); acc.y += ptx::bf16_hi(rv.x); acc.z += ptx::bf16_lo(rv.y); acc.w += ptx::bf16_hi(rv.y);
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * rs, acc.y * rs), hi = __floats2bfloat162_rn(acc.z * rs, acc.w * rs);
+    uint2 ov;
+    ov.x = *reinterpret_cast<uint32_t*>(&lo);
+    ov.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(a.y + o) = ov;
+  }
+}
+
 // ---- split-K finish: sums the partial tiles in split order (deterministic), applies the epilogue,
 // writes bf16.  One thread per 4 consecutive output columns of one row, so the whole GPU takes
 // part and every thread has `splits` independent 16-byte loads in flight.
@@ -125,28 +152,7 @@ __global__ void qmm_finish_kernel(QmmArgs a, int splits) {
     const float4 v = p[(size_t)s * split_stride];
     acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
   }
-  const float rs = a.row_scale(token);
-  if (a.epilogue == B200_EPI_SWIGLU) {
-    float g0 = acc.x, u0 = acc.y, g1 = acc.z, u1 = acc.w;
-    if (a.swiglu_limit > 0.f) {
-      const float L = a.swiglu_limit;
-      g0 = fminf(g0, L); g1 = fminf(g1, L);
-      u0 = fminf(fmaxf(u0, -L), L); u1 = fminf(fmaxf(u1, -L), L);
-    }
-    const float y0 = g0 / (1.0f + __expf(-g0)) * u0 * rs, y1 = g1 / (1.0f + __expf(-g1)) * u1 * rs;
-    *reinterpret_cast<__nv_bfloat162*>(a.y + (size_t)a.row_base_out(token) * (a.n / 2) + n / 2) = __floats2bfloat162_rn(y0, y1);
-  } else {
-    const size_t o = (size_t)a.row_base_out(token) * a.n + n;
-    if (a.epilogue == B200_EPI_RESIDUAL) {
-      const uint2 rv = *reinterpret_cast<const uint2*>(a.residual + o);
-      acc.x += ptx::bf16_lo(rv.x); acc.y += ptx::bf16_hi(rv.x); acc.z += ptx::bf16_lo(rv.y); acc.w += ptx::bf16_hi(rv.y);
-    }
-    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * rs, acc.y * rs), hi = __floats2bfloat162_rn(acc.z * rs, acc.w * rs);
-    uint2 ov;
-    ov.x = *reinterpret_cast<uint32_t*>(&lo);
-    ov.y = *reinterpret_cast<uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(a.y + o) = ov;
-  }
+  finish_store(a, token, n, acc);
 }
 
 // ---- GEMV kernel ---------------------------------------------------------------------------------
@@ -561,13 +567,21 @@ __global__ void __launch_bounds__(kTc2Threads, 1) qmm_tc2_kernel(const __grid_co
 // a long dependent chain per chunk (dequantise into a 16 KiB shared tile -> MMA -> commit -> slot
 // free).  Here nothing but the raw 4-bit blocks passes through shared memory: a producer warp
 // keeps a deep ring of raw blocks in flight with bulk copies; each of 8 consumer warps owns one
-// 16-row slice of the 128-row tile, pulls its rows' nibbles into registers, releases the slot at
-// once, dequantises straight into mma.sync A fragments (m16n8k16, bf16) and multiplies with the
-// activations (B fragments read from global memory through L1: the batch is tiny and shared by
-// all CTAs).  Tokens are the MMA N dimension: NT8 tiles of 8.
+// 16-row slice of the 128-row tile and feeds mma.sync (m16n8k16, bf16) from registers.  Tokens are
+// the MMA N dimension: NT8 tiles of 8.  The kernel is bound by instruction issue, so the work per
+// block is kept minimal:
+//   * The MMA's K slots are a free permutation as long as both operands agree.  Lane t of a quad
+//     takes the 8 columns of word t of each plane (columns 8t..8t+7 and 32+8t..32+8t+7): one
+//     32-bit load per row and plane yields all four column pairs the lane needs for two K steps,
+//     and the matching activations are 16 contiguous bytes of the staged slab.
+//   * Affine weights are not dequantised at all: 0x4300 | q is the bf16 value 128 + q, which goes
+//     into the MMA as it is.  One block is one quantisation group, so per block
+//         y += s * (acc - 128 * sum_x) + b * sum_x = s * acc + (b - 128 s) * sum_x
+//     with sum_x (per token and group) computed once per CTA while the slab is staged.
 constexpr int kGemvConsumers = 8;
 constexpr int kGemvThreads = (kGemvConsumers + 1) * 32;
-constexpr int kGemvRawStages = 12;
+constexpr int kGemvRawStages = 6;  // ring slots of two blocks each
+constexpr int kSlabPad = 64;  // row stride = chunks*128 + 64: the 8 lanes of a 16-byte load phase hit 8 bank groups
 
 __device__ __forceinline__ void mma_bf16_full(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -575,132 +589,219 @@ __device__ __forceinline__ void mma_bf16_full(float (&d)[4], const uint32_t (&a)
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// One column pair (already shifted into the low nibble of each half) -> bf16x2.
+// The same with a zero accumulator input (first K step of a block).
+__device__ __forceinline__ void mma_bf16_zero(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+               : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+// Column pair i of a word -> MMA operand.  Affine: the raw code as bf16 128+q.  MXFP4: dequantised.
 template <int MODE>
-__device__ __forceinline__ uint32_t dequant_pair(uint32_t shifted, __nv_bfloat162 s2, __nv_bfloat162 b2) {
-  const uint32_t t = shifted & 0x000F000Fu;
-  __nv_bfloat162 r;
-  if (MODE == B200_Q_AFFINE4_G64) {
-    uint32_t u = t | 0x43004300u;
-    const uint32_t c128 = 0x43004300u;
-    r = __hfma2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&u), *reinterpret_cast<const __nv_bfloat162*>(&c128)), s2, b2);
-  } else {
-    uint32_t u = ((t & 0x00080008u) << 12) | ((t & 0x00070007u) << 6);
-    const uint32_t c64 = 0x5F805F80u;
-    r = __hmul2(__hmul2(*reinterpret_cast<__nv_bfloat162*>(&u), *reinterpret_cast<const __nv_bfloat162*>(&c64)), s2);
-  }
+__device__ __forceinline__ uint32_t operand_pair(uint32_t word, int i, __nv_bfloat162 s2) {
+  const uint32_t t = (word >> (4 * i)) & 0x000F000Fu;
+  if (MODE == B200_Q_AFFINE4_G64) return t | 0x43004300u;
+  uint32_t u = ((t & 0x00080008u) << 12) | ((t & 0x00070007u) << 6);
+  const uint32_t c64 = 0x5F805F80u;  // 2^64
+  __nv_bfloat162 r = __hmul2(__hmul2(*reinterpret_cast<__nv_bfloat162*>(&u), *reinterpret_cast<const __nv_bfloat162*>(&c64)), s2);
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
 template <int MODE, int NT8>
-__global__ void __launch_bounds__(kGemvThreads, 2) qmm_mma_kernel(QmmArgs a) {
+__global__ void __launch_bounds__(kGemvThreads, NT8 >= 4 ? 1 : 2) qmm_mma_kernel(QmmArgs a) {
   extern __shared__ __align__(128) unsigned char gsm[];
-  uint64_t* raw_full = reinterpret_cast<uint64_t*>(gsm + (size_t)kGemvRawStages * kRawStride);
-  uint64_t* raw_free = raw_full + kGemvRawStages;
-  // Activation slab of this CTA's K range: NT8*8 token rows, row stride = chunks*128 + 16 bytes so
-  // that the 32 lanes of a B-fragment load hit 32 different banks.  Used when it fits (x_slab).
-  unsigned char* slab = reinterpret_cast<unsigned char*>(raw_free + kGemvRawStages);
+  const int stages = a.stages;
+  constexpr int kSlotBytes = 2 * kRawStride;  // a ring slot holds the blocks of two adjacent weight tiles
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(gsm + (size_t)stages * kSlotBytes);
+  uint64_t* raw_free = raw_full + stages;
+  // Activation slab of this CTA's K range (NT8*8 token rows), then sum_x [chunk][token] (affine).
+  unsigned char* slab = reinterpret_cast<unsigned char*>(raw_free + stages);
+  constexpr int TILE = NT8 * 8;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  const int nt = blockIdx.x, split = blockIdx.y, t0 = blockIdx.z * (NT8 * 8);
+  // Persistent CTA: a fixed K split, and every `groups`-th pair of weight tiles starting at pair
+  // `grp`.  The activation slab is staged once; the weight ring never drains between pairs.  Both
+  // tiles of a pair share the wait, the activation loads and the loop bookkeeping of a chunk.
+  const int split = blockIdx.x % a.splits, grp = blockIdx.x / a.splits, groups = gridDim.x / a.splits;
+  const int tt = blockIdx.y, t0 = tt * TILE;
   const int kc0 = split * a.chunks_per_split, kc1 = min(kc0 + a.chunks_per_split, a.kc), n_chunks = kc1 - kc0;
+  const int n_pairs = (a.nt + 1) / 2;
+  const int n_items = grp < n_pairs ? (n_pairs - grp + groups - 1) / groups : 0;
   constexpr int BB = block_bytes(MODE);
   if (tid == 0) {
-    for (int s = 0; s < kGemvRawStages; ++s) {
+    for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(&raw_full[s], 1);
       ptx::mbar_init(&raw_free[s], kGemvConsumers);
     }
     ptx::mbar_fence_init();
   }
-  const int slab_stride = n_chunks * (kChunkK * 2) + 16;
-  if (a.x_slab) {
+  __syncthreads();
+  const int slab_stride = a.chunks_per_split * (kChunkK * 2) + kSlabPad;
+  float* sum_x = reinterpret_cast<float*>(slab + (size_t)TILE * slab_stride);
+  bool ok = true;
+  // The producer starts the weight stream at once; the consumer warps meanwhile stage the
+  // activations (they meet on named barrier 1, which the producer warp is not part of).
+  if (warp == kGemvConsumers) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 1;
+      for (int item = 0; item < n_items && ok; ++item) {
+        const int nt0 = 2 * (grp + item * groups);
+        const int tiles = min(2, a.nt - nt0);
+        const unsigned char* src = a.blocks + ((size_t)nt0 * a.kc + kc0) * BB;
+        for (int i = 0; i < n_chunks; ++i) {
+          ok = ptx::mbar_wait(&raw_free[s], phase);
+          if (!ok) break;
+          ptx::mbar_expect_tx(&raw_full[s], tiles * BB);
+          for (int u = 0; u < tiles; ++u)
+            ptx::bulk_g2s(gsm + (size_t)s * kSlotBytes + u * kRawStride, src + ((size_t)u * a.kc + i) * BB, BB, &raw_full[s]);
+          if (++s == stages) { s = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else {
     const int vec_per_row = n_chunks * (kChunkK * 2 / 16);
-    for (int idx = tid; idx < NT8 * 8 * vec_per_row; idx += kGemvThreads) {
+    for (int idx = tid; idx < TILE * vec_per_row; idx += kGemvConsumers * 32) {
       const int row = idx / vec_per_row, v = idx - row * vec_per_row;
       uint4 val = make_uint4(0u, 0u, 0u, 0u);
       if (t0 + row < a.rows) val = *reinterpret_cast<const uint4*>(a.x + (size_t)(t0 + row) * a.k + (size_t)kc0 * kChunkK + v * 8);
       *reinterpret_cast<uint4*>(slab + (size_t)row * slab_stride + v * 16) = val;
     }
-  }
-  __syncthreads();
-  bool ok = true;
-  if (warp == kGemvConsumers) {
-    if (lane == 0) {
-      for (int i = 0; i < n_chunks; ++i) {
-        const int s = i % kGemvRawStages;
-        ok = ptx::mbar_wait(&raw_free[s], ((i / kGemvRawStages) & 1) ^ 1);
-        if (!ok) break;
-        ptx::mbar_expect_tx(&raw_full[s], BB);
-        ptx::bulk_g2s(gsm + (size_t)s * kRawStride, a.blocks + ((size_t)nt * a.kc + kc0 + i) * BB, BB, &raw_full[s]);
+    asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumers * 32) : "memory");
+    if (MODE == B200_Q_AFFINE4_G64) {
+      for (int idx = tid; idx < TILE * n_chunks; idx += kGemvConsumers * 32) {
+        const int c = idx / TILE, row = idx - c * TILE;
+        const uint4* src = reinterpret_cast<const uint4*>(slab + (size_t)row * slab_stride + c * (kChunkK * 2));
+        float sum = 0.f;
+#pragma unroll
+        for (int v = 0; v < 8; ++v) {
+          const uint4 q = src[v];
+          sum += ptx::bf16_lo(q.x) + ptx::bf16_hi(q.x) + ptx::bf16_lo(q.y) + ptx::bf16_hi(q.y);
+          sum += ptx::bf16_lo(q.z) + ptx::bf16_hi(q.z) + ptx::bf16_lo(q.w) + ptx::bf16_hi(q.w);
+        }
+        sum_x[idx] = sum;
       }
+      asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumers * 32) : "memory");
     }
-  } else {
     const int rA = warp * 16 + g, rB = rA + 8;
-    float acc[NT8][4];
+    const unsigned char* xlane = slab + (size_t)g * slab_stride + 16 * t;  // token g of tile j: + j*8*slab_stride
+    // Loop state is kept incremental (slot, phase, pointers): the loop is bound by instruction issue.
+    const uint32_t full0 = ptx::smem_u32(raw_full), free0 = ptx::smem_u32(raw_free);
+    const uint32_t lane_ofs = (uint32_t)(rA * 16 + 4 * t);
+    uint32_t slot = 0, phase = 0;
+    for (int item = 0; item < n_items && ok; ++item) {
+      const int nt0 = 2 * (grp + item * groups);
+      const bool two = nt0 + 1 < a.nt;
+      float y[2][NT8][4];
 #pragma unroll
-    for (int j = 0; j < NT8; ++j) { acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f; }
-    // activation row pointers of this lane's tokens (token = t0 + 8j + g), null beyond the batch
-    const uint32_t* xrow[NT8];
+      for (int u = 0; u < 2; ++u)
 #pragma unroll
-    for (int j = 0; j < NT8; ++j) {
-      const int tok = t0 + j * 8 + g;
-      xrow[j] = tok < a.rows ? reinterpret_cast<const uint32_t*>(a.x + (size_t)tok * a.k) : nullptr;
-    }
-    for (int i = 0; i < n_chunks; ++i) {
-      const int s = i % kGemvRawStages;
-      // B fragments of the whole chunk first: they do not depend on the weights
-      uint32_t xb[NT8][8];
-      const int kw = (kc0 + i) * (kChunkK / 2);  // chunk start in 32-bit words
+        for (int j = 0; j < NT8; ++j) { y[u][j][0] = y[u][j][1] = y[u][j][2] = y[u][j][3] = 0.f; }
+      const unsigned char* px = xlane;
+      const float* psx = sum_x + 2 * t;
+      for (int i = 0; i < n_chunks; ++i) {
+        // activations of the chunk first: they do not depend on the weights
+        uint4 xv[NT8][2];
 #pragma unroll
-      for (int j = 0; j < NT8; ++j) {
-        const uint32_t* srow = reinterpret_cast<const uint32_t*>(slab + (size_t)(j * 8 + g) * slab_stride) + i * (kChunkK / 2);
+        for (int j = 0; j < NT8; ++j) {
+          xv[j][0] = *reinterpret_cast<const uint4*>(px + (size_t)(j * 8) * slab_stride);
+          xv[j][1] = *reinterpret_cast<const uint4*>(px + (size_t)(j * 8) * slab_stride + 64);
+        }
+        float2 sx[NT8];
+        if (MODE == B200_Q_AFFINE4_G64) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks) {
-          if (a.x_slab) {
-            xb[j][2 * ks] = srow[ks * 8 + t];
-            xb[j][2 * ks + 1] = srow[ks * 8 + 4 + t];
+          for (int j = 0; j < NT8; ++j) sx[j] = *reinterpret_cast<const float2*>(psx + j * 8);
+        }
+        ok = ptx::mbar_wait_addr(full0 + 8 * slot, phase);
+        if (!ok) break;
+        const unsigned char* slot_base = gsm + slot * kSlotBytes;
+        uint32_t wa[2][2], wb[2][2];
+        float sA[2], bA[2], sB[2], bB[2];
+        __nv_bfloat162 mA[2][2], mB[2][2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (u == 1 && !two) break;
+          const unsigned char* blk = slot_base + u * kRawStride;
+#pragma unroll
+          for (int plane = 0; plane < 2; ++plane) {
+            wa[u][plane] = *reinterpret_cast<const uint32_t*>(blk + lane_ofs + plane * kPlaneBytes);
+            wb[u][plane] = *reinterpret_cast<const uint32_t*>(blk + lane_ofs + plane * kPlaneBytes + 8 * 16);
+          }
+          if (MODE == B200_Q_AFFINE4_G64) {
+            const uint16_t* sc = reinterpret_cast<const uint16_t*>(blk + 2 * kPlaneBytes) + rA;
+            sA[u] = __uint_as_float((uint32_t)sc[0] << 16); bA[u] = __uint_as_float((uint32_t)sc[kTileN] << 16);
+            sB[u] = __uint_as_float((uint32_t)sc[8] << 16); bB[u] = __uint_as_float((uint32_t)sc[kTileN + 8] << 16);
           } else {
-            xb[j][2 * ks] = xrow[j] ? __ldg(xrow[j] + kw + ks * 8 + t) : 0u;
-            xb[j][2 * ks + 1] = xrow[j] ? __ldg(xrow[j] + kw + ks * 8 + 4 + t) : 0u;
+            __nv_bfloat162 dummy;
+#pragma unroll
+            for (int plane = 0; plane < 2; ++plane) {
+              row_params<MODE>(blk, rA, plane, mA[u][plane], dummy);
+              row_params<MODE>(blk, rB, plane, mB[u][plane], dummy);
+            }
           }
         }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_addr(free0 + 8 * slot);  // everything this warp needs is in registers
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (u == 1 && !two) break;
+          if (MODE == B200_Q_AFFINE4_G64) {
+            const float cA = fmaf(-128.f, sA[u], bA[u]), cB = fmaf(-128.f, sB[u], bB[u]);
+            float acc[NT8][4];
+            const __nv_bfloat162 unused = __nv_bfloat162();
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              const int plane = ks >> 1, p0 = 2 * (ks & 1);
+              uint32_t af[4];
+              af[0] = operand_pair<MODE>(wa[u][plane], p0, unused);
+              af[1] = operand_pair<MODE>(wb[u][plane], p0, unused);
+              af[2] = operand_pair<MODE>(wa[u][plane], p0 + 1, unused);
+              af[3] = operand_pair<MODE>(wb[u][plane], p0 + 1, unused);
+#pragma unroll
+              for (int j = 0; j < NT8; ++j) {
+                const uint32_t b0 = (ks & 1) ? xv[j][plane].z : xv[j][plane].x, b1 = (ks & 1) ? xv[j][plane].w : xv[j][plane].y;
+                if (ks == 0) mma_bf16_zero(acc[j], af, b0, b1);
+                else mma_bf16_full(acc[j], af, b0, b1);
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < NT8; ++j) {
+              y[u][j][0] = fmaf(sA[u], acc[j][0], fmaf(cA, sx[j].x, y[u][j][0]));
+              y[u][j][1] = fmaf(sA[u], acc[j][1], fmaf(cA, sx[j].y, y[u][j][1]));
+              y[u][j][2] = fmaf(sB[u], acc[j][2], fmaf(cB, sx[j].x, y[u][j][2]));
+              y[u][j][3] = fmaf(sB[u], acc[j][3], fmaf(cB, sx[j].y, y[u][j][3]));
+            }
+          } else {
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks) {
+              const int plane = ks >> 1, p0 = 2 * (ks & 1);
+              uint32_t af[4];
+              af[0] = operand_pair<MODE>(wa[u][plane], p0, mA[u][plane]);
+              af[1] = operand_pair<MODE>(wb[u][plane], p0, mB[u][plane]);
+              af[2] = operand_pair<MODE>(wa[u][plane], p0 + 1, mA[u][plane]);
+              af[3] = operand_pair<MODE>(wb[u][plane], p0 + 1, mB[u][plane]);
+#pragma unroll
+              for (int j = 0; j < NT8; ++j)
+                mma_bf16_full(y[u][j], af, (ks & 1) ? xv[j][plane].z : xv[j][plane].x, (ks & 1) ? xv[j][plane].w : xv[j][plane].y);
+            }
+          }
+        }
+        px += kChunkK * 2;
+        psx += TILE;
+        if (++slot == (uint32_t)stages) { slot = 0; phase ^= 1u; }
       }
-      ok = ptx::mbar_wait(&raw_full[s], (i / kGemvRawStages) & 1);
-      if (!ok) break;
-      const unsigned char* blk = gsm + (size_t)s * kRawStride;
-      uint4 wa[2], wb[2];
-      __nv_bfloat162 sA[2], bA[2], sB[2], bB[2];
+      if (ok) {
 #pragma unroll
-      for (int plane = 0; plane < 2; ++plane) {
-        wa[plane] = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[rA];
-        wb[plane] = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[rB];
-        row_params<MODE>(blk, rA, plane, sA[plane], bA[plane]);
-        row_params<MODE>(blk, rB, plane, sB[plane], bB[plane]);
-      }
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(&raw_free[s]);  // everything this warp needs is in registers
+        for (int u = 0; u < 2; ++u) {
+          if (u == 1 && !two) break;
+          float* wsp = a.ws + (((size_t)((nt0 + u) * gridDim.y + tt) * a.splits + split) * a.tn) * kTileN;
 #pragma unroll
-      for (int ks = 0; ks < 4; ++ks) {
-        const int plane = ks >> 1;
-        // words 2*(ks&1) and 2*(ks&1)+1 of the plane hold columns 16ks..16ks+15; lane t takes pair t
-        const uint32_t a_w0 = (ks & 1) ? wa[plane].z : wa[plane].x, a_w1 = (ks & 1) ? wa[plane].w : wa[plane].y;
-        const uint32_t b_w0 = (ks & 1) ? wb[plane].z : wb[plane].x, b_w1 = (ks & 1) ? wb[plane].w : wb[plane].y;
-        uint32_t af[4];
-        af[0] = dequant_pair<MODE>(a_w0 >> (4 * t), sA[plane], bA[plane]);
-        af[1] = dequant_pair<MODE>(b_w0 >> (4 * t), sB[plane], bB[plane]);
-        af[2] = dequant_pair<MODE>(a_w1 >> (4 * t), sA[plane], bA[plane]);
-        af[3] = dequant_pair<MODE>(b_w1 >> (4 * t), sB[plane], bB[plane]);
+          for (int j = 0; j < NT8; ++j) {
 #pragma unroll
-        for (int j = 0; j < NT8; ++j) mma_bf16_full(acc[j], af, xb[j][2 * ks], xb[j][2 * ks + 1]);
-      }
-    }
-    if (ok) {
-      float* wsp = a.ws + (((size_t)(nt * gridDim.z + blockIdx.z) * gridDim.y + split) * a.tn) * kTileN;
-#pragma unroll
-      for (int j = 0; j < NT8; ++j) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int tl = j * 8 + 2 * t + (e & 1), row = (e & 2) ? rB : rA;
-          if (t0 + tl < a.rows) wsp[(size_t)tl * kTileN + row] = acc[j][e];
+            for (int e = 0; e < 4; ++e) {
+              const int tl = j * 8 + 2 * t + (e & 1), row = (e & 2) ? rB : rA;
+              if (t0 + tl < a.rows) wsp[(size_t)tl * kTileN + row] = y[u][j][e];
+            }
+          }
         }
       }
     }
@@ -1012,25 +1113,40 @@ static b200_status launch_mma_nt(QmmArgs& a, int rows, cudaStream_t s) {
   const int tts = (rows + tile - 1) / tile;
   b200_status st = ensure_state(0);
   if (st != B200_OK) return st;
-  // enough K splits for the activation slab of a split (tile rows x chunks x 128 B) to fit 48 KiB
-  const int max_cps = std::max(1, ((48 * 1024) / tile - 16) / (kChunkK * 2));
-  const int splits0 = std::max(pick_splits(a.nt * tts, a.kc, g_sms, 2), (a.kc + max_cps - 1) / max_cps);
-  a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
-  const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
+  // Persistent grid: `groups` CTAs per K split, each walking every groups-th weight tile.  Pick the
+  // split count whose slab fits 48 KiB and whose critical path (tiles per CTA x (chunks + 1) plus a
+  // fixed start-up worth ~8 chunks) is shortest at two CTAs per SM.
+  a.stages = kGemvRawStages;
+  const size_t base_smem = (size_t)a.stages * 2 * kRawStride + 2 * a.stages * sizeof(uint64_t);
+  auto slab_bytes = [&](int cps) { return (size_t)tile * ((size_t)cps * kChunkK * 2 + kSlabPad) + (size_t)tile * cps * sizeof(float); };
+  const int slots = std::max(1, g_sms * 2 / tts);
+  int best = 0, best_groups = 1;
+  long long best_cost = 0;
+  for (int sp = 1; sp <= std::min(a.kc, slots); ++sp) {
+    const int cps = (a.kc + sp - 1) / sp;
+    if ((a.kc + cps - 1) / cps != sp || slab_bytes(cps) > 48 * 1024) continue;
+    if (best && cps < 2) break;
+    const int pairs = (a.nt + 1) / 2;
+    const int groups = std::max(1, std::min(pairs, slots / sp));
+    const long long cost = (long long)((pairs + groups - 1) / groups) * (2 * cps + 1) + 8;
+    if (!best || cost < best_cost) { best = sp; best_cost = cost; best_groups = groups; }
+  }
+  if (!best) { b200_set_error("qmm: no K split fits the activation slab"); return B200_ERR_CAPACITY; }
+  const int splits = best;
+  a.splits = splits;
+  a.chunks_per_split = (a.kc + splits - 1) / splits;
   st = ensure_state((size_t)splits * (size_t)tts * tile * a.nt * kTileN * sizeof(float));
   if (st != B200_OK) return st;
   a.ws = g_ws; a.err = g_err;
-  const size_t base_smem = (size_t)kGemvRawStages * kRawStride + 2 * kGemvRawStages * sizeof(uint64_t);
-  const size_t slab = (size_t)tile * ((size_t)a.chunks_per_split * kChunkK * 2 + 16);
-  a.x_slab = slab <= 48 * 1024 ? 1 : 0;  // keeps two CTAs per SM
-  const size_t smem = base_smem + (a.x_slab ? slab : 0);
+  a.x_slab = 1;
+  const size_t smem = base_smem + slab_bytes(a.chunks_per_split);
   static bool configured = false;
   if (!configured) {
     B200_CUDA_TRY(cudaFuncSetAttribute(qmm_mma_kernel<MODE, NT8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)(base_smem + 48 * 1024)));
     configured = true;
   }
-  qmm_mma_kernel<MODE, NT8><<<dim3(a.nt, splits, tts), kGemvThreads, smem, s>>>(a);
+  qmm_mma_kernel<MODE, NT8><<<dim3(best_groups * splits, tts), kGemvThreads, smem, s>>>(a);
   B200_LAUNCH_CHECK();
   return launch_finish(a, splits, s);
 }

@@ -24,6 +24,7 @@ struct QmmArgs {
   int* err;                     // device error word
   int rows, n, k, nt, kc;
   int chunks_per_split, tn, stages;
+  int splits;                   // small-batch kernel: number of K splits (the grid is persistent)
   int epilogue;
   int x_slab;                   // small-batch kernel: activations staged in shared memory
   int x_row0;                   // first row of this launch within the tensor map
