@@ -514,6 +514,15 @@ b200_status b200_kv_create(const b200_kv_config* c, b200_kv** out) {
     st = b200_make_tensor_map(&kv->kmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d.k_pool, dims, strides, box);
     if (st == B200_OK) st = b200_make_tensor_map(&kv->vmap, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, d.v_pool, dims, strides, box);
     if (st != B200_OK) { b200_kv_destroy(kv); return st; }
+  } else if (c->head_dim == 128) {
+    // FP8 pools: a token row of one head is 128 bytes, a page tile one 128 x 32 box
+    const uint64_t rows_per_layer = (uint64_t)c->n_pages * c->n_kv_heads * c->page_size;
+    const uint64_t dims[3] = {128, rows_per_layer, (uint64_t)c->n_layers};
+    const uint64_t strides[2] = {128, rows_per_layer * 128};
+    const uint32_t box[3] = {128, 32, 1};
+    st = b200_make_tensor_map(&kv->kmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.k_pool, dims, strides, box);
+    if (st == B200_OK) st = b200_make_tensor_map(&kv->vmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, d.v_pool, dims, strides, box);
+    if (st != B200_OK) { b200_kv_destroy(kv); return st; }
   }
   st = b200_kv_reset(kv);
   if (st != B200_OK) { b200_kv_destroy(kv); return st; }

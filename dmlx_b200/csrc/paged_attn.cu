@@ -602,6 +602,224 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1)
   if (!alive && lane == 0) atomicExch(a.d.state + ST_ATTN_ERR, B200_ERR_DEVICE_FLAGGED);
 }
 
+// ---------------------------------------------------------------------------------------------
+// FP8-E4M3 pools (head_dim 128): tensor-core variant.
+//
+// Same worker structure as above; a page's K or V tile is 32 tokens x 128 bytes = one 4 KiB TMA box
+// (128B swizzle).  The E4M3 codes are widened to f16 in registers (exact) and the products run on
+// mma.sync m16n8k16 f16 -> f32, with Q converted bf16 -> f16 once per item.
+//   * The MMA's K slots are a free permutation as long as both operands agree: ldmatrix on the
+//     byte tile hands lane (g, t) the four consecutive dims 16c+4t..16c+4t+3 of token g, which
+//     become the lane's four K slots of step c; Q is loaded with the same dim -> slot map.
+//   * For P V, ldmatrix.trans hands the lane two tokens x two adjacent dims; a byte permute sorts
+//     them into the B operands of an "even dims" and an "odd dims" output tile.
+//   * The per-(page, kv head) scales stay out of the MMAs: the K scale multiplies the f32 scores;
+//     the V scale, divided by the largest V scale of the item (so the factor is <= 1), multiplies
+//     P before it is rounded to f16, and the item's output is multiplied by that largest scale.
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  const uint32_t z = 0u;
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(z), "r"(a2), "r"(z), "r"(b0), "r"(b1));
+}
+// two E4M3 codes (low 16 bits: first code in the low byte) -> f16x2
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t lo16) {
+  uint32_t d;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(d) : "h"((unsigned short)lo16));
+  return d;
+}
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(kMmaWarps * 32, 2)
+    paged_attn_mma_fp8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, AttnArgs a) {
+  constexpr int D = 128;
+  constexpr int TILE = 32 * D;  // bytes of one K or V tile
+  constexpr int KS = D / 16;    // k-steps of Q K^T = 16-byte chunks of a row
+  constexpr int NO = D / 8;     // n-tiles of the output
+
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  unsigned char* my_tiles = smem + (size_t)warp * kMmaStages * 2 * TILE;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kMmaWarps * kMmaStages * 2 * TILE) + warp * kMmaStages;
+  const int H = a.d.n_kv_heads, G = a.n_q_heads / H;
+  const int n_items = a.chunk_start[a.total_rows] * H;
+  const int worker = blockIdx.x * kMmaWarps + warp, n_workers = gridDim.x * kMmaWarps;
+
+  if (lane == 0) {
+    for (int s = 0; s < kMmaStages; ++s) ptx::mbar_init(&full_bar[s], 1);
+    ptx::mbar_fence_init();
+  }
+  __syncwarp();
+
+  int p_item = worker, p_page = 0, p_end = 0, p_begin = 0, p_head = 0, p_pid = 0;
+  uint32_t prod_n = 0;
+  auto producer_enter_item = [&]() {
+    if (p_item < n_items) {
+      const Item it = decode_item(a, p_item);
+      p_begin = it.page_begin; p_page = it.page_begin; p_end = it.page_end; p_head = it.head;
+      const int pg = it.page_begin + lane;
+      if (pg < it.page_end) p_pid = a.d.block_table[(size_t)it.seq * a.d.max_pages_per_seq + pg];
+    }
+  };
+  auto produce_one = [&]() {
+    if (p_item >= n_items) return;
+    const int pid = __shfl_sync(0xffffffffu, p_pid, p_page - p_begin);
+    const uint32_t s = prod_n % kMmaStages;
+    if (lane == 0) {
+      ptx::fence_proxy_async_smem();
+      unsigned char* kd = my_tiles + (size_t)s * 2 * TILE;
+      const int row0 = (pid * H + p_head) * 32;
+      ptx::mbar_expect_tx(&full_bar[s], 2 * TILE);
+      ptx::tma_load_3d(kd, &kmap, 0, row0, a.layer, &full_bar[s]);
+      ptx::tma_load_3d(kd + TILE, &vmap, 0, row0, a.layer, &full_bar[s]);
+    }
+    prod_n += 1;
+    p_page += 1;
+    if (p_page >= p_end) {
+      p_item += n_workers;
+      producer_enter_item();
+    }
+  };
+  producer_enter_item();
+  for (int i = 0; i < kMmaStages; ++i) produce_one();
+
+  bool alive = true;
+  uint32_t cons_n = 0;
+  const int ld_r = lane & 7, ld_m = lane >> 3;
+  for (int item = worker; item < n_items && alive; item += n_workers) {
+    const Item it = decode_item(a, item);
+    // Q fragments (f16): k-step c, slots (2t,2t+1) <- dims 16c+4t+{0,1}; slots (2t+8,2t+9) <- dims 16c+4t+{2,3}
+    uint32_t qa0[KS], qa2[KS];
+    {
+      const __nv_bfloat16* qrow = a.q + (size_t)it.row * a.q_stride + (it.head * G + (g < G ? g : 0)) * D;
+#pragma unroll
+      for (int c = 0; c < KS; ++c) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(qrow + 16 * c + 4 * t);
+        qa0[c] = g < G ? pack_f16(ptx::bf16_lo(raw.x), ptx::bf16_hi(raw.x)) : 0u;
+        qa2[c] = g < G ? pack_f16(ptx::bf16_lo(raw.y), ptx::bf16_hi(raw.y)) : 0u;
+      }
+    }
+    // scales of this item's pages: lane i holds page page_begin + i
+    float my_ks = 0.f, my_vs = 0.f;
+    {
+      const int pg = it.page_begin + lane;
+      if (pg < it.page_end) {
+        const int pid = a.d.block_table[(size_t)it.seq * a.d.max_pages_per_seq + pg];
+        const size_t si = ((size_t)a.layer * a.d.n_pages + pid) * H + it.head;
+        my_ks = a.d.k_scale[si];
+        my_vs = a.d.v_scale[si];
+      }
+    }
+    float v_ref = my_vs;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v_ref = fmaxf(v_ref, __shfl_xor_sync(0xffffffffu, v_ref, o));
+    const float my_vr = v_ref > 0.f ? my_vs / v_ref : 0.f;
+
+    float o[NO][4];
+#pragma unroll
+    for (int j = 0; j < NO; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float m_run = -1e30f, l_run = 0.f;
+
+    for (int pg = it.page_begin; pg < it.page_end; ++pg) {
+      const uint32_t s = cons_n % kMmaStages;
+      alive = ptx::mbar_wait(&full_bar[s], (cons_n / kMmaStages) & 1u);
+      if (!alive) break;
+      const float ks = __shfl_sync(0xffffffffu, my_ks, pg - it.page_begin) * a.scale_log2;
+      const float vr = __shfl_sync(0xffffffffu, my_vr, pg - it.page_begin);
+      const uint32_t kbase = ptx::smem_u32(my_tiles + (size_t)s * 2 * TILE), vbase = kbase + TILE;
+      // ---- S = Q K^T : 4 n-tiles of 8 tokens; one ldmatrix.x4 = 4 chunks = 4 k-steps ----
+      float sc[4][4];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+#pragma unroll
+      for (int kk = 0; kk < KS / 4; ++kk) {
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          const int row = nt * 8 + ld_r, cc = 4 * kk + ld_m;
+          uint32_t b[4];
+          ldsm_x4(kbase + row * 128 + ((cc ^ (row & 7)) << 4), b);
+#pragma unroll
+          for (int m = 0; m < 4; ++m)
+            mma_f16_16816(sc[nt], qa0[4 * kk + m], qa2[4 * kk + m], e4m3x2_to_f16x2(b[m]), e4m3x2_to_f16x2(b[m] >> 16));
+        }
+      }
+      // ---- online softmax on row g ----
+      const int tok0 = pg * 32;
+      float mx = -1e30f;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const bool valid = tok0 + nt * 8 + 2 * t + e < it.ctx;
+          sc[nt][e] = valid ? sc[nt][e] * ks : -1e30f;
+          mx = fmaxf(mx, sc[nt][e]);
+        }
+      }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float m_new = fmaxf(m_run, mx);
+      const float corr = exp2f(m_run - m_new);
+      float psum = 0.f;
+      uint32_t pa0[2], pa2[2];
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt) {
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float sv = sc[2 * kt + (e >> 1)][e & 1];
+          pv[e] = sv > -1e29f ? exp2f(sv - m_new) : 0.f;
+          psum += pv[e];
+        }
+        pa0[kt] = pack_f16(pv[0] * vr, pv[1] * vr);
+        pa2[kt] = pack_f16(pv[2] * vr, pv[3] * vr);
+      }
+      l_run = l_run * corr + psum;
+      m_run = m_new;
+      if (__any_sync(0xffffffffu, corr != 1.f)) {
+#pragma unroll
+        for (int j = 0; j < NO; ++j) { o[j][0] *= corr; o[j][1] *= corr; }
+      }
+      // ---- O += P V : output tile 2c holds the even dims of chunk c, tile 2c+1 the odd dims ----
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt) {
+#pragma unroll
+        for (int jj = 0; jj < KS / 2; ++jj) {
+          const int row = kt * 16 + (ld_m & 1) * 8 + ld_r, cc = 2 * jj + (ld_m >> 1);
+          uint32_t b[4];
+          ldsm_x4_trans(vbase + row * 128 + ((cc ^ (row & 7)) << 4), b);
+          // bytes (tok 2t, dim 2g), (2t, 2g+1), (2t+1, 2g), (2t+1, 2g+1) -> (even dim pair | odd dim pair)
+          const uint32_t p0 = __byte_perm(b[0], 0u, 0x3120), p1 = __byte_perm(b[1], 0u, 0x3120);
+          const uint32_t p2 = __byte_perm(b[2], 0u, 0x3120), p3 = __byte_perm(b[3], 0u, 0x3120);
+          mma_f16_16816(o[4 * jj], pa0[kt], pa2[kt], e4m3x2_to_f16x2(p0), e4m3x2_to_f16x2(p1));
+          mma_f16_16816(o[4 * jj + 1], pa0[kt], pa2[kt], e4m3x2_to_f16x2(p0 >> 16), e4m3x2_to_f16x2(p1 >> 16));
+          mma_f16_16816(o[4 * jj + 2], pa0[kt], pa2[kt], e4m3x2_to_f16x2(p2), e4m3x2_to_f16x2(p3));
+          mma_f16_16816(o[4 * jj + 3], pa0[kt], pa2[kt], e4m3x2_to_f16x2(p2 >> 16), e4m3x2_to_f16x2(p3 >> 16));
+        }
+      }
+      __syncwarp();
+      cons_n += 1;
+      produce_one();
+    }
+    if (!alive) break;
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (g < G) {
+      const size_t pidx = (size_t)it.chunk * a.n_q_heads + it.head * G + g;
+      // chunk c of the row: dims 16c+4t+{0,1,2,3} = (tile 2c col 2t, tile 2c+1 col 2t, tile 2c col 2t+1, tile 2c+1 col 2t+1)
+#pragma unroll
+      for (int c = 0; c < KS; ++c)
+        *reinterpret_cast<float4*>(a.part_o + pidx * D + 16 * c + 4 * t) =
+            make_float4(o[2 * c][0] * v_ref, o[2 * c + 1][0] * v_ref, o[2 * c][1] * v_ref, o[2 * c + 1][1] * v_ref);
+      if (t == 0) { a.part_ml[pidx * 2] = m_run; a.part_ml[pidx * 2 + 1] = l_run; }
+    }
+  }
+  if (!alive && lane == 0) atomicExch(a.d.state + ST_ATTN_ERR, B200_ERR_DEVICE_FLAGGED);
+}
+
 // D threads per (row, query head): merge the row's chunks and write bf16.
 template <int D>
 __global__ void __launch_bounds__(D) attn_combine_kernel(AttnArgs a, __nv_bfloat16* __restrict__ out) {
@@ -659,6 +877,21 @@ b200_status launch_attn_mma(const b200_kv* kv, const AttnArgs& a, void* d_out, i
   return B200_OK;
 }
 
+b200_status launch_attn_mma_fp8(const b200_kv* kv, const AttnArgs& a, void* d_out, int sms, cudaStream_t s) {
+  constexpr int TILE = 32 * 128;
+  const size_t smem = (size_t)kMmaWarps * kMmaStages * 2 * TILE + 1024 + sizeof(uint64_t) * kMmaWarps * kMmaStages;
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(paged_attn_mma_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  paged_attn_mma_fp8_kernel<<<sms * 2, kMmaWarps * 32, smem, s>>>(kv->kmap, kv->vmap, a);
+  B200_LAUNCH_CHECK();
+  attn_combine_kernel<128><<<a.total_rows * a.n_q_heads, 128, 0, s>>>(a, (__nv_bfloat16*)d_out);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
 int g_sm_count = 0;
 
 }  // namespace
@@ -685,7 +918,8 @@ b200_status b200_paged_attn_decode_strided(b200_kv* kv, int32_t layer, const voi
   const b200_kv_config& c = kv->cfg;
   if (layer < 0 || layer >= c.n_layers) { b200_set_error("attention: layer %d out of range", layer); return B200_ERR_INVALID_ARGUMENT; }
   const bool fp8 = c.kv_dtype == B200_KV_FP8_E4M3;
-  const bool use_mma = !fp8 && b200_attn_path != 1 && c.n_q_heads / c.n_kv_heads <= 8;  // MMA rows 0..7 carry the group's heads
+  // MMA rows 0..7 carry the group's heads; the FP8 tensor-core kernel is built for head_dim 128
+  const bool use_mma = b200_attn_path != 1 && c.n_q_heads / c.n_kv_heads <= 8 && (!fp8 || c.head_dim == 128);
   if (!use_mma && c.n_q_heads != c.n_kv_heads * kGroup) {
     b200_set_error("attention: the CUDA-core kernel is built for a GQA group of %d query heads per kv head (got %d/%d)", kGroup, c.n_q_heads, c.n_kv_heads);
     return B200_ERR_UNSUPPORTED;
@@ -709,6 +943,7 @@ b200_status b200_paged_attn_decode_strided(b200_kv* kv, int32_t layer, const voi
   attn_plan_kernel<<<1, 1024, 0, s>>>(d_row_ctx, total_rows, c.page_size, ppc, kv->d_chunk_start, kv->max_chunks,
                                       kv->dev.state + ST_ATTN_ERR);
   B200_LAUNCH_CHECK();
+  if (use_mma && fp8) return launch_attn_mma_fp8(kv, a, d_out, g_sm_count, s);
   if (use_mma) return c.head_dim == 128 ? launch_attn_mma<128>(kv, a, d_out, g_sm_count, s) : launch_attn_mma<64>(kv, a, d_out, g_sm_count, s);
   const int grid = g_sm_count * 3;
   if (c.head_dim == 128) return fp8 ? launch_attn<128, true>(a, d_out, grid, s) : launch_attn<128, false>(a, d_out, grid, s);

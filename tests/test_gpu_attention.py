@@ -68,7 +68,7 @@ def _run_case(ctxs, hq, hkv, d, kv_dtype, seed, scatter=True, pages_per_chunk=8,
 
 
 @pytest.mark.parametrize("d", [64, 128])
-@pytest.mark.parametrize("kv_dtype,path", [(0, 0), (0, 1), (1, 0)])  # bf16 tensor-core, bf16 CUDA-core, FP8
+@pytest.mark.parametrize("kv_dtype,path", [(0, 0), (0, 1), (1, 0), (1, 1)])  # bf16 tensor-core, bf16 CUDA-core, FP8 tensor-core (head_dim 128), FP8 CUDA-core
 def test_ragged_contexts(d, kv_dtype, path):
     ctxs = [1, 31, 32, 33, 64, 65, 200, 257, 700, 5, 1023, 96]
     hq, hkv = (8, 2) if d == 64 else (32, 8)
