@@ -704,7 +704,7 @@ def main():
                    "page_tokens": PAGE, "pool": "random permutation over 1.25x pages in use",
                    "l2": f"inputs larger than L2 ({alg / 1e6:.0f} MB of KV per step)", "parallelism": f"dp{world}"},
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                     "peak_kind": f"of {peak_kind}", "traffic": None, "kernel": ("paged_attn_kernel" if fp8 else "paged_attn_mma_kernel") + " (+plan, +combine)",
+                     "peak_kind": f"of {peak_kind}", "traffic": None, "kernel": ("paged_attn_mma_fp8_kernel" if fp8 else "paged_attn_mma_kernel") + " (+plan, +combine)",
                      "algorithmic_bytes_per_launch": alg, "kernel_ms": kern_ms, "frac_of_8TBs": achieved / 8000.0},
         "e2e": {"value": tokens_per_step / (e2e_ms / args.steps * 1e-3), "unit": "decode tokens/s",
                 "h2d_bytes_per_step": int(q_host.numel() * 2 + desc_host.numel() * 4),

@@ -632,7 +632,8 @@ __device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(kMmaWarps * 32, 2)
+template <int STAGES, int MINB>
+__global__ void __launch_bounds__(kMmaWarps * 32, MINB)
     paged_attn_mma_fp8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, AttnArgs a) {
   constexpr int D = 128;
   constexpr int TILE = 32 * D;  // bytes of one K or V tile
@@ -643,14 +644,14 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2)
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
-  unsigned char* my_tiles = smem + (size_t)warp * kMmaStages * 2 * TILE;
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kMmaWarps * kMmaStages * 2 * TILE) + warp * kMmaStages;
+  unsigned char* my_tiles = smem + (size_t)warp * STAGES * 2 * TILE;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kMmaWarps * STAGES * 2 * TILE) + warp * STAGES;
   const int H = a.d.n_kv_heads, G = a.n_q_heads / H;
   const int n_items = a.chunk_start[a.total_rows] * H;
   const int worker = blockIdx.x * kMmaWarps + warp, n_workers = gridDim.x * kMmaWarps;
 
   if (lane == 0) {
-    for (int s = 0; s < kMmaStages; ++s) ptx::mbar_init(&full_bar[s], 1);
+    for (int s = 0; s < STAGES; ++s) ptx::mbar_init(&full_bar[s], 1);
     ptx::mbar_fence_init();
   }
   __syncwarp();
@@ -668,7 +669,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2)
   auto produce_one = [&]() {
     if (p_item >= n_items) return;
     const int pid = __shfl_sync(0xffffffffu, p_pid, p_page - p_begin);
-    const uint32_t s = prod_n % kMmaStages;
+    const uint32_t s = prod_n % STAGES;
     if (lane == 0) {
       ptx::fence_proxy_async_smem();
       unsigned char* kd = my_tiles + (size_t)s * 2 * TILE;
@@ -685,7 +686,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2)
     }
   };
   producer_enter_item();
-  for (int i = 0; i < kMmaStages; ++i) produce_one();
+  for (int i = 0; i < STAGES; ++i) produce_one();
 
   bool alive = true;
   uint32_t cons_n = 0;
@@ -725,8 +726,8 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2)
     float m_run = -1e30f, l_run = 0.f;
 
     for (int pg = it.page_begin; pg < it.page_end; ++pg) {
-      const uint32_t s = cons_n % kMmaStages;
-      alive = ptx::mbar_wait(&full_bar[s], (cons_n / kMmaStages) & 1u);
+      const uint32_t s = cons_n % STAGES;
+      alive = ptx::mbar_wait(&full_bar[s], (cons_n / STAGES) & 1u);
       if (!alive) break;
       const float ks = __shfl_sync(0xffffffffu, my_ks, pg - it.page_begin) * a.scale_log2;
       const float vr = __shfl_sync(0xffffffffu, my_vr, pg - it.page_begin);
@@ -877,19 +878,26 @@ b200_status launch_attn_mma(const b200_kv* kv, const AttnArgs& a, void* d_out, i
   return B200_OK;
 }
 
-b200_status launch_attn_mma_fp8(const b200_kv* kv, const AttnArgs& a, void* d_out, int sms, cudaStream_t s) {
+template <int STAGES, int MINB>
+b200_status launch_attn_mma_fp8_cfg(const b200_kv* kv, const AttnArgs& a, void* d_out, int sms, cudaStream_t s) {
   constexpr int TILE = 32 * 128;
-  const size_t smem = (size_t)kMmaWarps * kMmaStages * 2 * TILE + 1024 + sizeof(uint64_t) * kMmaWarps * kMmaStages;
+  const size_t smem = (size_t)kMmaWarps * STAGES * 2 * TILE + 1024 + sizeof(uint64_t) * kMmaWarps * STAGES;
   static bool configured = false;
   if (!configured) {
-    B200_CUDA_TRY(cudaFuncSetAttribute(paged_attn_mma_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    B200_CUDA_TRY((cudaFuncSetAttribute(paged_attn_mma_fp8_kernel<STAGES, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)));
     configured = true;
   }
-  paged_attn_mma_fp8_kernel<<<sms * 2, kMmaWarps * 32, smem, s>>>(kv->kmap, kv->vmap, a);
+  paged_attn_mma_fp8_kernel<STAGES, MINB><<<sms * MINB, kMmaWarps * 32, smem, s>>>(kv->kmap, kv->vmap, a);
   B200_LAUNCH_CHECK();
   attn_combine_kernel<128><<<a.total_rows * a.n_q_heads, 128, 0, s>>>(a, (__nv_bfloat16*)d_out);
   B200_LAUNCH_CHECK();
   return B200_OK;
+}
+
+// Two stages and two CTAs per SM: the kernel is bound by instruction issue (the code widening), not
+// by loads in flight; measured 4.22 TB/s against 4.05 (3 stages x 2 CTAs), 4.17 (2 x 3), 2.99 (4 x 1).
+b200_status launch_attn_mma_fp8(const b200_kv* kv, const AttnArgs& a, void* d_out, int sms, cudaStream_t s) {
+  return launch_attn_mma_fp8_cfg<2, 2>(kv, a, d_out, sms, s);
 }
 
 int g_sm_count = 0;
