@@ -225,6 +225,7 @@ __global__ void __launch_bounds__(kTileN) qmm_simt_kernel(QmmArgs a) {
 // ---- tcgen05 kernel ------------------------------------------------------------------------------
 constexpr int kTcThreads = 320;  // warps 0-7 dequantise (0-3 also run the epilogue), 8 loads, 9 issues MMAs
 constexpr int kRawStride = 5120;  // weight block padded to a multiple of 1024
+constexpr int kPrefetchAhead = 12;  // weight blocks requested into L2 ahead of the copy
 
 template <int MODE>
 __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_constant__ CUtensorMap xmap, QmmArgs a) {
@@ -232,11 +233,14 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
   // 1024-byte alignment: the 128B swizzle pattern is a function of the shared-memory address.
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int tn = a.tn, stages = a.stages;
-  const int stage_stride = kTileN * 128 + tn * 128 + kRawStride;
+  // [stage][A tile 16 KiB | X tile tn x 128 B] (1024-byte aligned for the 128B swizzle), then the raw
+  // weight blocks of all stages (only 16-byte alignment needed), then the barriers.
+  constexpr int kRaw = MODE == B200_Q_BF16 ? 0 : ((block_bytes(MODE) + 127) / 128) * 128;
+  const int stage_stride = kTileN * 128 + tn * 128;
   auto a_tile = [&](int s) { return smem + (size_t)s * stage_stride; };
   auto x_tile = [&](int s) { return smem + (size_t)s * stage_stride + kTileN * 128; };
-  auto raw_blk = [&](int s) { return smem + (size_t)s * stage_stride + kTileN * 128 + tn * 128; };
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_stride);
+  auto raw_blk = [&](int s) { return smem + (size_t)stages * stage_stride + (size_t)s * kRaw; };
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)stages * (stage_stride + kRaw));
   uint64_t* loaded = bars;
   uint64_t* a_ready = bars + stages;
   uint64_t* mma_done = bars + 2 * stages;
@@ -283,8 +287,13 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
 
   if (warp == 8) {
     if (lane == 0) {
+      // The weight blocks of this CTA are contiguous in HBM: ask for them in L2 well ahead of the
+      // stage that will copy them, so that a stage's refill waits for L2, not for HBM.
+      const unsigned char* wsrc = blocks + ((size_t)nt * a.kc + kc0) * BB;
+      for (int i = 0; i < min(n_chunks, kPrefetchAhead); ++i) ptx::bulk_prefetch_l2(wsrc + (size_t)i * BB, BB);
       for (int i = 0; i < n_chunks && ok; ++i) {
         const int s = i % stages;
+        if (i + kPrefetchAhead < n_chunks) ptx::bulk_prefetch_l2(wsrc + (size_t)(i + kPrefetchAhead) * BB, BB);
         ok = ptx::mbar_wait(&mma_done[s], ((i / stages) & 1) ^ 1);
         if (!ok) break;
         ptx::mbar_expect_tx(&loaded[s], BB + tn * 128);
@@ -1022,7 +1031,8 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
   const int tiles = a.items ? a.nt * a.max_items : a.nt * tts;
   b200_status st = ensure_state(0);
   if (st != B200_OK) return st;
-  const int stage_stride = kTileN * 128 + tn * 128 + kRawStride;
+  constexpr int kRaw = MODE == B200_Q_BF16 ? 0 : ((block_bytes(MODE) + 127) / 128) * 128;
+  const int stage_stride = kTileN * 128 + tn * 128 + kRaw;
   static int smem_budget[3] = {0, 0, 0};  // opt-in dynamic shared memory available to this kernel
   if (smem_budget[MODE] == 0) {
     int dev = 0, optin = 0;
@@ -1037,7 +1047,7 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
   const int fixed = 1024 /*alignment slack*/ + 8 * (3 * 8 + 2) + 16;
   // Small token tiles leave room for two CTAs per SM (more weight bytes in flight); large ones
   // take the whole SM.
-  const int per_cta = tn <= 128 ? 110 * 1024 : std::min(smem_budget[MODE], 220 * 1024);
+  const int per_cta = tn <= 128 ? 113 * 1024 : std::min(smem_budget[MODE], 220 * 1024);
   a.stages = std::max(2, std::min(8, (per_cta - fixed) / stage_stride));
   const int ctas_per_sm = tn <= 128 ? 2 : 1;
   const size_t smem = (size_t)a.stages * stage_stride + fixed;
@@ -1266,7 +1276,8 @@ b200_status launch_tc_static(QmmArgs& a, int rows, int dev, cudaStream_t s) {
   a.tn = tn;
   const int tts = (rows + tn - 1) / tn;
   const int tiles = a.nt * tts;
-  const int stage_stride = kTileN * 128 + tn * 128 + kRawStride;
+  constexpr int kRaw = MODE == B200_Q_BF16 ? 0 : ((block_bytes(MODE) + 127) / 128) * 128;
+  const int stage_stride = kTileN * 128 + tn * 128 + kRaw;
   static int budget[3] = {0, 0, 0};
   if (budget[MODE] == 0) {
     int optin = 0;
