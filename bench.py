@@ -460,11 +460,13 @@ def run_moe(args, rank, world, local):
         step(x)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = dev.launch_count()
     e0.record()
     for _ in range(K):
         step(x)
     e1.record()
     barrier()
+    launches = dev.launch_count() - launches0
     total_ms = e0.elapsed_time(e1)
     out_host = torch.empty_like(x_host).pin_memory()
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -508,7 +510,7 @@ def run_moe(args, rank, world, local):
                      "algorithmic_flops_per_step": flops},
         "e2e": {"value": c["tokens"] / (e2e_ms / K * 1e-3), "unit": "decode tokens/s",
                 "h2d_bytes_per_step": int(x_host.numel() * 2 * world), "d2h_bytes_per_step": int(x_host.numel() * 2 * world)},
-        "gpu_launches": None, "clocks": clocks,
+        "gpu_launches": int(launches), "clocks": clocks,
     }))
     if world > 1:
         dist.destroy_process_group()

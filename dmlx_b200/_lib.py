@@ -149,6 +149,7 @@ _sig("b200_kv_error_word", i32, vp, P(i32))
 _sig("b200_kv_gather", i32, vp, i32, i32, vp, vp, i32, vp)
 _sig("b200_kv_page_raw", i32, vp, i32, i32, vp, vp, P(f32), P(f32))
 _sig("b200_paged_attn_decode", i32, vp, i32, vp, vp, vp, i32, vp, vp)
+_sig("b200_paged_attn_prefill", i32, vp, i32, vp, vp, vp, i32, vp, vp)
 _sig("b200_set_attn_pages_per_chunk", None, i32)
 _sig("b200_set_attn_path", None, i32)
 _sig("b200_rmsnorm", i32, vp, vp, vp, i32, i32, f32, vp)
@@ -180,6 +181,7 @@ _sig("b200_llama_forward", i32, vp, vp, vp, i32, i32, vp, vp)
 _sig("b200_llama_device_buffers", None, vp, P(vp), P(vp), P(vp))
 _sig("b200_llama_last_logits", i32, vp, vp, i32)
 _sig("b200_llama_launch_count", C.c_int64, vp)
+_sig("b200_launch_count", C.c_int64)
 _sig("b200_llama_profile_enable", None, vp, i32)
 _sig("b200_llama_enable_graphs", None, vp, i32)
 _sig("b200_llama_profile_collect", i32, vp, P(C.c_double), P(C.c_int64))

@@ -17,6 +17,7 @@ namespace {
 thread_local std::string g_last_error;
 }
 long long g_b200_launch_counter = 0;
+extern "C" int64_t b200_launch_count(void) { return (int64_t)g_b200_launch_counter; }
 
 void b200_set_error(const char* fmt, ...) {
   char buf[512];

@@ -498,6 +498,7 @@ b200_status b200_kv_create(const b200_kv_config* c, b200_kv** out) {
   // split-K scratch for the attention kernel
   kv->max_chunks = c->attn_scratch_chunks > 0 ? c->attn_scratch_chunks : c->n_pages / 4 + c->max_rows + 8;
   KV_ALLOC(kv->d_chunk_start, sizeof(int) * (c->max_rows + 2));
+  KV_ALLOC(kv->d_groups, sizeof(int) * 3 * (c->max_rows + 2));
   KV_ALLOC(kv->d_part_o, sizeof(float) * (size_t)kv->max_chunks * c->n_q_heads * c->head_dim);
   KV_ALLOC(kv->d_part_ml, sizeof(float) * (size_t)kv->max_chunks * c->n_q_heads * 2);
 #undef KV_ALLOC
@@ -535,7 +536,7 @@ void b200_kv_destroy(b200_kv* kv) {
   KvDev& d = kv->dev;
   void* ptrs[] = {d.k_pool, d.v_pool, d.k_scale, d.v_scale, d.free_stack, d.ref_count, d.tokens_used, d.block_table,
                   d.seq_pages, d.seq_len, d.state, d.touch_list, d.cow_list, kv->d_admin_in, kv->d_admin_out,
-                  kv->d_chunk_start, kv->d_part_o, kv->d_part_ml};
+                  kv->d_chunk_start, kv->d_part_o, kv->d_part_ml, kv->d_groups};
   for (void* p : ptrs) if (p) cudaFree(p);
   delete kv;
 }

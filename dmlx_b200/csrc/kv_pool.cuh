@@ -39,6 +39,8 @@ struct b200_kv {
   float* d_part_o = nullptr;     // [max_chunks][n_q_heads][head_dim]
   float* d_part_ml = nullptr;    // [max_chunks][n_q_heads][2]  (running max in log2 units, sum)
   int max_chunks = 0;
+  // row-group plan of the prefill attention path: [3][max_rows + 2] = group_first | part_base | row_group
+  int* d_groups = nullptr;
   // 3-D tensor maps over the bf16 pools: [layer][page*kv_head*32 rows][head_dim], box 64 x 32 x 1
   CUtensorMap kmap, vmap;
 };
@@ -50,3 +52,6 @@ b200_status b200_kv_append_strided(b200_kv* kv, int32_t layer, const void* d_k_r
 b200_status b200_paged_attn_decode_strided(b200_kv* kv, int32_t layer, const void* d_q, int32_t q_stride,
                                            const int32_t* d_row_seq, const int32_t* d_row_ctx, int32_t total_rows,
                                            void* d_out, void* stream);
+b200_status b200_paged_attn_prefill_strided(b200_kv* kv, int32_t layer, const void* d_q, int32_t q_stride,
+                                            const int32_t* d_row_seq, const int32_t* d_row_ctx, int32_t total_rows,
+                                            void* d_out, void* stream);

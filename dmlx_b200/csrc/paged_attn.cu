@@ -45,6 +45,12 @@ struct AttnArgs {
   float* part_o;
   float* part_ml;
   float scale_log2;
+  // prefill path: rows grouped into runs of consecutive tokens of one sequence
+  const int* group_first = nullptr;  // [n_groups + 1] first row of each group
+  const int* part_base = nullptr;    // [n_groups] first partial slot of each group (a chunk holds one slot per row)
+  const int* row_group = nullptr;    // [T]
+  const int* n_groups = nullptr;
+  int q_tokens = 1;                  // rows per group at most (16 / GQA group size)
 };
 
 __global__ void attn_plan_kernel(const int* __restrict__ row_ctx, int total_rows, int page_size, int pages_per_chunk,
@@ -821,6 +827,339 @@ __global__ void __launch_bounds__(kMmaWarps * 32, MINB)
   if (!alive && lane == 0) atomicExch(a.d.state + ST_ATTN_ERR, B200_ERR_DEVICE_FLAGGED);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Prefill rows (bf16 pools): ragged causal attention of a chunk of new tokens over the paged cache.
+//
+// Semantics are those of the decode kernels (row r attends to the first row_ctx[r] cached tokens of
+// its slot; the rows' own K/V have been appended already), but rows are grouped: up to 16/G
+// consecutive rows of one sequence whose contexts grow by one token form a group, and a work item
+// is (group, chunk of pages, kv head).  The 16 MMA rows carry (token of the group) x (query head
+// of the kv head's GQA group), so a staged K/V page serves every token of the group at once and
+// the cache is read once per group instead of once per row.  Causality is a per-MMA-row context
+// length.  Groups are found on the device from the row arrays (one CTA, prefix scans).
+template <bool MAX>
+__device__ __forceinline__ int block_scan_inclusive(int v, int* warp_buf) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc = MAX ? max(inc, t) : inc + t;
+  }
+  if (lane == 31) warp_buf[warp] = inc;
+  __syncthreads();
+  if (warp == 0) {
+    int w = warp_buf[lane];
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, w, o);
+      if (lane >= o) w = MAX ? max(w, t) : w + t;
+    }
+    const int ex = __shfl_up_sync(0xffffffffu, w, 1);  // exclusive prefix over the warps
+    warp_buf[lane] = lane == 0 ? (MAX ? -1 : 0) : ex;
+  }
+  __syncthreads();
+  const int r = MAX ? max(warp_buf[warp], inc) : warp_buf[warp] + inc;
+  __syncthreads();
+  return r;
+}
+
+__global__ void __launch_bounds__(1024) attn_plan_groups_kernel(const int* __restrict__ row_seq, const int* __restrict__ row_ctx,
+                                                                int total_rows, int page_size, int pages_per_chunk, int q_tokens,
+                                                                int* __restrict__ chunk_start, int* __restrict__ group_first,
+                                                                int* __restrict__ part_base, int* __restrict__ row_group,
+                                                                int* __restrict__ n_groups_out, int max_slots, int* __restrict__ err) {
+  __shared__ int warp_buf[32];
+  __shared__ int carry_start, carry_groups, carry_chunks, carry_slots;
+  const int tid = threadIdx.x;
+  if (tid == 0) { carry_start = -1; carry_groups = 0; carry_chunks = 0; carry_slots = 0; }
+  __syncthreads();
+  // pass 1: runs of joinable rows, cut into groups of q_tokens
+  for (int base = 0; base < total_rows; base += blockDim.x) {
+    const int i = base + tid;
+    const bool valid = i < total_rows;
+    const bool joinable = valid && i > 0 && row_seq[i] == row_seq[i - 1] && row_ctx[i] == row_ctx[i - 1] + 1;
+    const int run_start = max(block_scan_inclusive<true>(valid && !joinable ? i : -1, warp_buf), carry_start);
+    const int head = valid && ((i - run_start) % q_tokens == 0) ? 1 : 0;
+    const int heads_incl = block_scan_inclusive<false>(head, warp_buf);
+    const int gid = carry_groups + heads_incl - 1;
+    if (valid) {
+      row_group[i] = gid;
+      if (head) group_first[gid] = i;
+    }
+    __syncthreads();
+    if (tid == blockDim.x - 1) { carry_start = run_start; carry_groups += heads_incl; }
+    __syncthreads();
+  }
+  const int n_groups = carry_groups;
+  if (tid == 0) { group_first[n_groups] = total_rows; *n_groups_out = n_groups; }
+  __syncthreads();
+  // pass 2: chunks and partial slots per group
+  for (int base = 0; base < n_groups; base += blockDim.x) {
+    const int gidx = base + tid;
+    int chunks = 0, slots = 0;
+    if (gidx < n_groups) {
+      const int first = group_first[gidx], next = group_first[gidx + 1];
+      const int pages = (max(row_ctx[next - 1], 0) + page_size - 1) / page_size;
+      chunks = (pages + pages_per_chunk - 1) / pages_per_chunk;
+      slots = chunks * (next - first);
+    }
+    const int c_incl = block_scan_inclusive<false>(chunks, warp_buf);
+    const int s_incl = block_scan_inclusive<false>(slots, warp_buf);
+    if (gidx < n_groups) {
+      chunk_start[gidx] = carry_chunks + c_incl - chunks;
+      part_base[gidx] = carry_slots + s_incl - slots;
+    }
+    __syncthreads();
+    if (tid == blockDim.x - 1) { carry_chunks += c_incl; carry_slots += s_incl; }
+    __syncthreads();
+  }
+  if (tid == 0) {
+    if (carry_slots > max_slots) { *err = B200_ERR_CAPACITY; chunk_start[n_groups] = 0; }
+    else chunk_start[n_groups] = carry_chunks;
+  }
+}
+
+struct GroupItem {
+  int head, seq, first_row, n_rows, ctx0, page_begin, page_end, slot0;
+};
+
+__device__ __forceinline__ GroupItem decode_group_item(const AttnArgs& a, int item, int n_groups) {
+  GroupItem it;
+  const int H = a.d.n_kv_heads;
+  const int chunk = item / H;
+  it.head = item - chunk * H;
+  int lo = 0, hi = n_groups - 1;  // last group with chunk_start[group] <= chunk
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (a.chunk_start[mid] <= chunk) lo = mid; else hi = mid - 1;
+  }
+  it.first_row = a.group_first[lo];
+  it.n_rows = a.group_first[lo + 1] - it.first_row;
+  it.seq = a.row_seq[it.first_row];
+  it.ctx0 = a.row_ctx[it.first_row];
+  const int c = chunk - a.chunk_start[lo];
+  const int npages = (it.ctx0 + it.n_rows - 1 + a.d.page_size - 1) / a.d.page_size;
+  it.page_begin = c * a.pages_per_chunk;
+  it.page_end = min(it.page_begin + a.pages_per_chunk, npages);
+  it.slot0 = a.part_base[lo] + c * it.n_rows;
+  return it;
+}
+
+__device__ __forceinline__ void mma_bf16_16816_full(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                                    uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int D>
+__global__ void __launch_bounds__(kMmaWarps * 32, 1)
+    paged_attn_prefill_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, AttnArgs a) {
+  constexpr int BOXES = D / 64;
+  constexpr int TILE = 32 * D * 2;
+  constexpr int KS = D / 16;
+  constexpr int NO = D / 8;
+
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  unsigned char* my_tiles = smem + (size_t)warp * kMmaStages * 2 * TILE;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kMmaWarps * kMmaStages * 2 * TILE) + warp * kMmaStages;
+  const int H = a.d.n_kv_heads, G = a.n_q_heads / H;
+  const int n_groups = *a.n_groups;
+  const int n_items = a.chunk_start[n_groups] * H;
+  const int worker = blockIdx.x * kMmaWarps + warp, n_workers = gridDim.x * kMmaWarps;
+
+  if (lane == 0) {
+    for (int s = 0; s < kMmaStages; ++s) ptx::mbar_init(&full_bar[s], 1);
+    ptx::mbar_fence_init();
+  }
+  __syncwarp();
+
+  int p_item = worker, p_page = 0, p_end = 0, p_begin = 0, p_head = 0, p_pid = 0;
+  uint32_t prod_n = 0;
+  auto producer_enter_item = [&]() {
+    if (p_item < n_items) {
+      const GroupItem it = decode_group_item(a, p_item, n_groups);
+      p_begin = it.page_begin; p_page = it.page_begin; p_end = it.page_end; p_head = it.head;
+      const int pg = it.page_begin + lane;
+      if (pg < it.page_end) p_pid = a.d.block_table[(size_t)it.seq * a.d.max_pages_per_seq + pg];
+    }
+  };
+  auto produce_one = [&]() {
+    if (p_item >= n_items) return;
+    const int pid = __shfl_sync(0xffffffffu, p_pid, p_page - p_begin);
+    const uint32_t s = prod_n % kMmaStages;
+    if (lane == 0) {
+      ptx::fence_proxy_async_smem();
+      unsigned char* kd = my_tiles + (size_t)s * 2 * TILE;
+      const int row0 = (pid * H + p_head) * 32;
+      ptx::mbar_expect_tx(&full_bar[s], 2 * TILE);
+#pragma unroll
+      for (int b = 0; b < BOXES; ++b) {
+        ptx::tma_load_3d(kd + b * 4096, &kmap, b * 64, row0, a.layer, &full_bar[s]);
+        ptx::tma_load_3d(kd + TILE + b * 4096, &vmap, b * 64, row0, a.layer, &full_bar[s]);
+      }
+    }
+    prod_n += 1;
+    p_page += 1;
+    if (p_page >= p_end) {
+      p_item += n_workers;
+      producer_enter_item();
+    }
+  };
+  producer_enter_item();
+  for (int i = 0; i < kMmaStages; ++i) produce_one();
+
+  bool alive = true;
+  uint32_t cons_n = 0;
+  const int ld_r = lane & 7, ld_m = lane >> 3;
+  // MMA rows g and g+8 of this lane: (token of the group, query head within the GQA group)
+  const int tokA = g / G, headA = g - tokA * G, tokB = (g + 8) / G, headB = (g + 8) - tokB * G;
+  for (int item = worker; item < n_items && alive; item += n_workers) {
+    const GroupItem it = decode_group_item(a, item, n_groups);
+    const bool onA = tokA < it.n_rows, onB = tokB < it.n_rows;
+    const int ctxA = onA ? it.ctx0 + tokA : 0, ctxB = onB ? it.ctx0 + tokB : 0;
+    uint32_t qa0[KS], qa1[KS], qa2[KS], qa3[KS];
+    {
+      const uint32_t* qA = reinterpret_cast<const uint32_t*>(a.q + (size_t)(it.first_row + (onA ? tokA : 0)) * a.q_stride + (it.head * G + headA) * D);
+      const uint32_t* qB = reinterpret_cast<const uint32_t*>(a.q + (size_t)(it.first_row + (onB ? tokB : 0)) * a.q_stride + (it.head * G + headB) * D);
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+        qa0[ks] = onA ? qA[ks * 8 + t] : 0u;
+        qa2[ks] = onA ? qA[ks * 8 + 4 + t] : 0u;
+        qa1[ks] = onB ? qB[ks * 8 + t] : 0u;
+        qa3[ks] = onB ? qB[ks * 8 + 4 + t] : 0u;
+      }
+    }
+    float o[NO][4];
+#pragma unroll
+    for (int j = 0; j < NO; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float mA = -1e30f, lA = 0.f, mB = -1e30f, lB = 0.f;
+
+    for (int pg = it.page_begin; pg < it.page_end; ++pg) {
+      const uint32_t s = cons_n % kMmaStages;
+      alive = ptx::mbar_wait(&full_bar[s], (cons_n / kMmaStages) & 1u);
+      if (!alive) break;
+      const uint32_t kbase = ptx::smem_u32(my_tiles + (size_t)s * 2 * TILE), vbase = kbase + TILE;
+      float sc[4][4];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+#pragma unroll
+      for (int kk = 0; kk < KS / 2; ++kk) {
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          const int row = nt * 8 + ld_r, cc = 4 * kk + ld_m;
+          uint32_t b[4];
+          ldsm_x4(kbase + (cc >> 3) * 4096 + row * 128 + (((cc & 7) ^ (row & 7)) << 4), b);
+          mma_bf16_16816_full(sc[nt], qa0[2 * kk], qa1[2 * kk], qa2[2 * kk], qa3[2 * kk], b[0], b[1]);
+          mma_bf16_16816_full(sc[nt], qa0[2 * kk + 1], qa1[2 * kk + 1], qa2[2 * kk + 1], qa3[2 * kk + 1], b[2], b[3]);
+        }
+      }
+      // ---- online softmax on rows g (A) and g+8 (B), each with its own causal context ----
+      const int tok0 = pg * 32;
+      float mxA = -1e30f, mxB = -1e30f;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int tok = tok0 + nt * 8 + 2 * t + e;
+          sc[nt][e] = tok < ctxA ? sc[nt][e] * a.scale_log2 : -1e30f;
+          sc[nt][2 + e] = tok < ctxB ? sc[nt][2 + e] * a.scale_log2 : -1e30f;
+          mxA = fmaxf(mxA, sc[nt][e]);
+          mxB = fmaxf(mxB, sc[nt][2 + e]);
+        }
+      }
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+      const float mA_new = fmaxf(mA, mxA), mB_new = fmaxf(mB, mxB);
+      const float corrA = exp2f(mA - mA_new), corrB = exp2f(mB - mB_new);
+      float psA = 0.f, psB = 0.f;
+      uint32_t pa0[2], pa1[2], pa2[2], pa3[2];
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt) {
+        float pA[4], pB[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float sa = sc[2 * kt + (e >> 1)][e & 1], sb = sc[2 * kt + (e >> 1)][2 + (e & 1)];
+          pA[e] = sa > -1e29f ? exp2f(sa - mA_new) : 0.f;
+          pB[e] = sb > -1e29f ? exp2f(sb - mB_new) : 0.f;
+          psA += pA[e];
+          psB += pB[e];
+        }
+        pa0[kt] = pack_bf16(pA[0], pA[1]);
+        pa2[kt] = pack_bf16(pA[2], pA[3]);
+        pa1[kt] = pack_bf16(pB[0], pB[1]);
+        pa3[kt] = pack_bf16(pB[2], pB[3]);
+      }
+      lA = lA * corrA + psA; mA = mA_new;
+      lB = lB * corrB + psB; mB = mB_new;
+      if (__any_sync(0xffffffffu, corrA != 1.f || corrB != 1.f)) {
+#pragma unroll
+        for (int j = 0; j < NO; ++j) { o[j][0] *= corrA; o[j][1] *= corrA; o[j][2] *= corrB; o[j][3] *= corrB; }
+      }
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt) {
+#pragma unroll
+        for (int jj = 0; jj < NO / 2; ++jj) {
+          const int row = kt * 16 + (ld_m & 1) * 8 + ld_r, cc = 2 * jj + (ld_m >> 1);
+          uint32_t b[4];
+          ldsm_x4_trans(vbase + (cc >> 3) * 4096 + row * 128 + (((cc & 7) ^ (row & 7)) << 4), b);
+          mma_bf16_16816_full(o[2 * jj], pa0[kt], pa1[kt], pa2[kt], pa3[kt], b[0], b[1]);
+          mma_bf16_16816_full(o[2 * jj + 1], pa0[kt], pa1[kt], pa2[kt], pa3[kt], b[2], b[3]);
+        }
+      }
+      __syncwarp();
+      cons_n += 1;
+      produce_one();
+    }
+    if (!alive) break;
+    lA += __shfl_xor_sync(0xffffffffu, lA, 1);
+    lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    if (onA) {
+      const size_t pidx = (size_t)(it.slot0 + tokA) * a.n_q_heads + it.head * G + headA;
+#pragma unroll
+      for (int j = 0; j < NO; ++j)
+        *reinterpret_cast<float2*>(a.part_o + pidx * D + j * 8 + 2 * t) = make_float2(o[j][0], o[j][1]);
+      if (t == 0) { a.part_ml[pidx * 2] = mA; a.part_ml[pidx * 2 + 1] = lA; }
+    }
+    if (onB) {
+      const size_t pidx = (size_t)(it.slot0 + tokB) * a.n_q_heads + it.head * G + headB;
+#pragma unroll
+      for (int j = 0; j < NO; ++j)
+        *reinterpret_cast<float2*>(a.part_o + pidx * D + j * 8 + 2 * t) = make_float2(o[j][2], o[j][3]);
+      if (t == 0) { a.part_ml[pidx * 2] = mB; a.part_ml[pidx * 2 + 1] = lB; }
+    }
+  }
+  if (!alive && lane == 0) atomicExch(a.d.state + ST_ATTN_ERR, B200_ERR_DEVICE_FLAGGED);
+}
+
+// D threads per (row, query head): merge the partials of the row's group chunks and write bf16.
+template <int D>
+__global__ void __launch_bounds__(D) attn_combine_groups_kernel(AttnArgs a, __nv_bfloat16* __restrict__ out) {
+  const int row = blockIdx.x / a.n_q_heads, qh = blockIdx.x - row * a.n_q_heads, d = threadIdx.x;
+  if (a.d.state[ST_ATTN_ERR] != 0) return;
+  const int grp = a.row_group[row], first = a.group_first[grp], size = a.group_first[grp + 1] - first;
+  const int n_chunks = a.chunk_start[grp + 1] - a.chunk_start[grp];
+  const size_t slot0 = (size_t)a.part_base[grp] + (row - first);
+  float mm = -1e30f;
+  for (int c = 0; c < n_chunks; ++c) mm = fmaxf(mm, a.part_ml[((slot0 + (size_t)c * size) * a.n_q_heads + qh) * 2]);
+  float ll = 0.f, acc = 0.f;
+#pragma unroll 4
+  for (int c = 0; c < n_chunks; ++c) {
+    const size_t pidx = (slot0 + (size_t)c * size) * a.n_q_heads + qh;
+    const float w = exp2f(a.part_ml[pidx * 2] - mm);
+    ll += a.part_ml[pidx * 2 + 1] * w;
+    acc += a.part_o[pidx * D + d] * w;
+  }
+  out[((size_t)row * a.n_q_heads + qh) * D + d] = __float2bfloat16(ll > 0.f ? acc / ll : 0.f);
+}
+
 // D threads per (row, query head): merge the row's chunks and write bf16.
 template <int D>
 __global__ void __launch_bounds__(D) attn_combine_kernel(AttnArgs a, __nv_bfloat16* __restrict__ out) {
@@ -900,6 +1239,23 @@ b200_status launch_attn_mma_fp8(const b200_kv* kv, const AttnArgs& a, void* d_ou
   return launch_attn_mma_fp8_cfg<2, 2>(kv, a, d_out, sms, s);
 }
 
+template <int D>
+b200_status launch_attn_prefill(const b200_kv* kv, const AttnArgs& a, void* d_out, int sms, cudaStream_t s) {
+  constexpr int TILE = 32 * D * 2;
+  const size_t smem = (size_t)kMmaWarps * kMmaStages * 2 * TILE + 1024 + sizeof(uint64_t) * kMmaWarps * kMmaStages;
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(paged_attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  const int ctas_per_sm = smem <= 100 * 1024 ? 2 : 1;
+  paged_attn_prefill_kernel<D><<<sms * ctas_per_sm, kMmaWarps * 32, smem, s>>>(kv->kmap, kv->vmap, a);
+  B200_LAUNCH_CHECK();
+  attn_combine_groups_kernel<D><<<a.total_rows * a.n_q_heads, D, 0, s>>>(a, (__nv_bfloat16*)d_out);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
 int g_sm_count = 0;
 
 }  // namespace
@@ -956,6 +1312,49 @@ b200_status b200_paged_attn_decode_strided(b200_kv* kv, int32_t layer, const voi
   const int grid = g_sm_count * 3;
   if (c.head_dim == 128) return fp8 ? launch_attn<128, true>(a, d_out, grid, s) : launch_attn<128, false>(a, d_out, grid, s);
   return fp8 ? launch_attn<64, true>(a, d_out, grid, s) : launch_attn<64, false>(a, d_out, grid, s);
+}
+
+extern "C" b200_status b200_paged_attn_prefill(b200_kv* kv, int32_t layer, const void* d_q, const int32_t* d_row_seq,
+                                               const int32_t* d_row_ctx, int32_t total_rows, void* d_out, void* stream) {
+  return b200_paged_attn_prefill_strided(kv, layer, d_q, kv->cfg.n_q_heads * kv->cfg.head_dim, d_row_seq, d_row_ctx,
+                                         total_rows, d_out, stream);
+}
+
+b200_status b200_paged_attn_prefill_strided(b200_kv* kv, int32_t layer, const void* d_q, int32_t q_stride,
+                                            const int32_t* d_row_seq, const int32_t* d_row_ctx, int32_t total_rows,
+                                            void* d_out, void* stream) {
+  const b200_kv_config& c = kv->cfg;
+  const int G = c.n_kv_heads > 0 ? c.n_q_heads / c.n_kv_heads : 0;
+  // Grouping needs the GQA group to divide the 16 MMA rows and a bf16 pool; anything else takes the
+  // per-row kernels (same results).
+  if (c.kv_dtype != B200_KV_BF16 || !(G == 1 || G == 2 || G == 4 || G == 8) || b200_attn_path == 1)
+    return b200_paged_attn_decode_strided(kv, layer, d_q, q_stride, d_row_seq, d_row_ctx, total_rows, d_out, stream);
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (layer < 0 || layer >= c.n_layers) { b200_set_error("attention: layer %d out of range", layer); return B200_ERR_INVALID_ARGUMENT; }
+  if (total_rows <= 0) return B200_OK;
+  if (total_rows > c.max_rows) { b200_set_error("attention: %d rows > max_rows %d", total_rows, c.max_rows); return B200_ERR_CAPACITY; }
+  cudaStream_t s = (cudaStream_t)stream;
+  if (g_sm_count == 0) {
+    int dev = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
+  }
+  const int ppc = std::min(std::max(b200_attn_pages_per_chunk, 4), kMaxChunkPages);
+  const int stride = c.max_rows + 2;
+  AttnArgs a;
+  a.d = kv->dev; a.layer = layer; a.q = (const __nv_bfloat16*)d_q; a.q_stride = q_stride; a.row_seq = d_row_seq; a.row_ctx = d_row_ctx;
+  a.chunk_start = kv->d_chunk_start; a.total_rows = total_rows; a.n_q_heads = c.n_q_heads; a.pages_per_chunk = ppc;
+  a.part_o = kv->d_part_o; a.part_ml = kv->d_part_ml;
+  a.scale_log2 = 1.4426950408889634f / sqrtf((float)c.head_dim);
+  a.group_first = kv->d_groups; a.part_base = kv->d_groups + stride; a.row_group = kv->d_groups + 2 * stride;
+  a.n_groups = kv->d_groups + 3 * stride - 1;  // last word of the row_group array (never a row index)
+  a.q_tokens = 16 / G;
+  attn_plan_groups_kernel<<<1, 1024, 0, s>>>(d_row_seq, d_row_ctx, total_rows, c.page_size, ppc, a.q_tokens, kv->d_chunk_start,
+                                             kv->d_groups, kv->d_groups + stride, kv->d_groups + 2 * stride,
+                                             kv->d_groups + 3 * stride - 1, kv->max_chunks, kv->dev.state + ST_ATTN_ERR);
+  B200_LAUNCH_CHECK();
+  return c.head_dim == 128 ? launch_attn_prefill<128>(kv, a, d_out, g_sm_count, s) : launch_attn_prefill<64>(kv, a, d_out, g_sm_count, s);
 }
 
 // Tuning hook (not part of the reference surface): pages per split-K chunk, 4..32.

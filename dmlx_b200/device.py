@@ -129,11 +129,12 @@ class PagedKVCache:
         _lib.check(lib.b200_kv_append(self._h, layer, _ptr(k_rows), _ptr(v_rows), k_rows.shape[0], _stream()))
 
     def attention(self, layer: int, q: torch.Tensor, row_seq: torch.Tensor, row_ctx: torch.Tensor,
-                  out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """b200_paged_attn_decode. q: [T, Hq, D] bf16."""
+                  out: Optional[torch.Tensor] = None, prefill: bool = False) -> torch.Tensor:
+        """b200_paged_attn_decode (or b200_paged_attn_prefill: same results, rows of a prefill chunk
+        served in groups). q: [T, Hq, D] bf16."""
         out = out if out is not None else torch.empty_like(q)
-        _lib.check(lib.b200_paged_attn_decode(self._h, layer, _ptr(q), _ptr(row_seq), _ptr(row_ctx), q.shape[0],
-                                              _ptr(out), _stream()))
+        fn = lib.b200_paged_attn_prefill if prefill else lib.b200_paged_attn_decode
+        _lib.check(fn(self._h, layer, _ptr(q), _ptr(row_seq), _ptr(row_ctx), q.shape[0], _ptr(out), _stream()))
         return out
 
     # -- introspection --
@@ -188,6 +189,11 @@ class PagedKVCache:
 
 def set_attn_pages_per_chunk(n: int):
     lib.b200_set_attn_pages_per_chunk(n)
+
+
+def launch_count() -> int:
+    """Kernels launched by the library in this process so far."""
+    return int(lib.b200_launch_count())
 
 
 def set_attn_path(path: int):

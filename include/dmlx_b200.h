@@ -50,6 +50,9 @@ const char* b200_last_error(void);
 /* Library version, and 1 if a CUDA device is usable by this process. */
 int32_t b200_version(void);
 int32_t b200_device_available(void);
+/* Kernels this library has launched in this process so far (benchmarks report the difference
+ * over their timed region; no reference counterpart). */
+int64_t b200_launch_count(void);
 
 /* ========================================================================================== */
 /* HOST LAYER (no GPU needed)                                                                  */
@@ -246,6 +249,13 @@ b200_status b200_kv_page_raw(b200_kv* kv, int32_t layer, int32_t page, void* h_k
 b200_status b200_paged_attn_decode(b200_kv* kv, int32_t layer, const void* d_q,
                                    const int32_t* d_row_seq, const int32_t* d_row_ctx,
                                    int32_t total_rows, void* d_out, void* stream);
+/* Same contract and results, for batches that hold prefill chunks (the block-diagonal causal mask
+ * of src/batch_builder.zig:138-177 expressed as one context length per row, the chunk cursor of
+ * src/scheduler.zig:183-186): consecutive rows of one sequence whose contexts grow by one token are
+ * served together, so the cache is read once per group of rows instead of once per row. */
+b200_status b200_paged_attn_prefill(b200_kv* kv, int32_t layer, const void* d_q,
+                                    const int32_t* d_row_seq, const int32_t* d_row_ctx,
+                                    int32_t total_rows, void* d_out, void* stream);
 
 /* Tuning hook with no reference counterpart: pages per split-K chunk (4..32, default 8). */
 void b200_set_attn_pages_per_chunk(int32_t n);
