@@ -95,6 +95,10 @@ class ExpertParallelMoE:
         assert n_experts % self.world == 0 and local_gate_up.n_experts == n_experts // self.world
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """One host synchronisation per layer (the split sizes the all-to-all needs as integers);
+        everything else, including the regrouping of received rows by local expert, runs on the
+        device: rows travel with their local expert id and routing weight, and the receiver sorts
+        them with the same stable counting sort the single-GPU layer uses."""
         from . import device as dev
 
         n, k, w = x.shape[0], self.k, self.world
@@ -103,31 +107,32 @@ class ExpertParallelMoE:
             shared = dev.qmm(self.sdown, dev.qmm(self.sgu, x, dev.EPI_SWIGLU))
         logits = dev.qmm(self.gate, x)
         idx, wts, counts = dev.moe_route(logits, k, self.bias, dev.SCORE_SOFTMAX, self.route_scale)
-        _, order, inv, _, _ = dev.moe_group(idx, counts, self.tile)
+        _, order, inv, items, n_items = dev.moe_group(idx, counts, self.tile)
         x_sorted, scales = dev.moe_gather(x, order, wts, k)
         if w == 1:
-            recv_counts = counts.view(1, -1)
-            rows, row_scales = x_sorted, scales
-            send = recv = [n * k]
-        else:
-            recv_counts = exchange_counts(counts, w, self.group)
-            send = send_splits(counts.cpu(), w)  # host integers: the one synchronisation of the layer
-            recv = recv_counts.sum(1).tolist()
-            rows = all_to_all_rows(x_sorted, send, recv, self.group)
-            row_scales = all_to_all_rows(scales, send, recv, self.group)
-        index, offsets = regroup_index(recv_counts)
-        index_d = index.to(x.device)
-        items = work_items(offsets, self.tile).to(x.device)
-        n_items = torch.tensor([items.shape[0] if offsets[-1] > 0 else 0], dtype=torch.int32, device=x.device)
-        if rows.shape[0] > 0:
-            xe = dev.gather_rows(rows, index_d)
-            se = row_scales[index_d.long()].contiguous()
-            act = dev.moe_grouped_qmm(self.gu, xe, items, n_items, self.tile, dev.EPI_SWIGLU, se, self.limit)
-            ye = dev.moe_grouped_qmm(self.down, act, items, n_items, self.tile)
-            inverse = torch.empty_like(index_d)
-            inverse[index_d.long()] = torch.arange(index_d.shape[0], dtype=torch.int32, device=x.device)
-            y_recv_order = dev.gather_rows(ye, inverse)
+            act = dev.moe_grouped_qmm(self.gu, x_sorted, items, n_items, self.tile, dev.EPI_SWIGLU, scales, self.limit)
+            y_sorted = dev.moe_grouped_qmm(self.down, act, items, n_items, self.tile)
+            return dev.moe_combine(y_sorted, inv, n, k, shared)
+        el = self.n_experts // w
+        recv_counts = exchange_counts(counts, w, self.group)  # [W, E_local] on the device
+        splits = torch.stack([counts.view(w, el).sum(1), recv_counts.sum(1)]).to("cpu")  # the layer's one sync
+        send, recv = splits[0].tolist(), splits[1].tolist()
+        # per sorted row: (local expert id, routing weight bits)
+        eid = torch.remainder(idx.view(-1)[order.long()], el).to(torch.int32)
+        meta = torch.stack([eid, scales.view(torch.int32)], 1).contiguous()
+        rows = all_to_all_rows(x_sorted, send, recv, self.group)
+        rmeta = all_to_all_rows(meta, send, recv, self.group)
+        m = rows.shape[0]
+        if m > 0:
+            ids = rmeta[:, 0].contiguous().view(m, 1)
+            lcounts = recv_counts.sum(0).to(torch.int32)
+            _, lorder, linv, litems, ln_items = dev.moe_group(ids, lcounts, self.tile)
+            xe = dev.gather_rows(rows, lorder)
+            se = rmeta[:, 1].contiguous().view(torch.float32)[lorder.long()].contiguous()
+            act = dev.moe_grouped_qmm(self.gu, xe, litems, ln_items, self.tile, dev.EPI_SWIGLU, se, self.limit)
+            ye = dev.moe_grouped_qmm(self.down, act, litems, ln_items, self.tile)
+            y_recv_order = dev.gather_rows(ye, linv)
         else:
             y_recv_order = torch.empty((0, self.hidden), dtype=torch.bfloat16, device=x.device)
-        y_sorted = y_recv_order if w == 1 else all_to_all_rows(y_recv_order, recv, send, self.group)
+        y_sorted = all_to_all_rows(y_recv_order, recv, send, self.group)
         return dev.moe_combine(y_sorted, inv, n, k, shared)
