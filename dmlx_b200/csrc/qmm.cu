@@ -291,10 +291,11 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
       // stage that will copy them, so that a stage's refill waits for L2, not for HBM.
       const unsigned char* wsrc = blocks + ((size_t)nt * a.kc + kc0) * BB;
       for (int i = 0; i < min(n_chunks, kPrefetchAhead); ++i) ptx::bulk_prefetch_l2(wsrc + (size_t)i * BB, BB);
-      for (int i = 0; i < n_chunks && ok; ++i) {
-        const int s = i % stages;
+      int s = 0;
+      uint32_t ph = 0;  // stage cursor kept incrementally: no division by the runtime stage count
+      for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == stages), s = (s + 1 == stages) ? 0 : s + 1) {
         if (i + kPrefetchAhead < n_chunks) ptx::bulk_prefetch_l2(wsrc + (size_t)(i + kPrefetchAhead) * BB, BB);
-        ok = ptx::mbar_wait(&mma_done[s], ((i / stages) & 1) ^ 1);
+        ok = ptx::mbar_wait(&mma_done[s], ph ^ 1u);
         if (!ok) break;
         ptx::mbar_expect_tx(&loaded[s], BB + tn * 128);
         // dense bf16 blocks are stored in the swizzled K-major layout and land in the MMA tile directly
@@ -306,9 +307,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
   } else if (warp == 9) {
     if (lane == 0) {
       const uint32_t idesc = ptx::umma_idesc_bf16(kTileN, tn);
-      for (int i = 0; i < n_chunks && ok; ++i) {
-        const int s = i % stages;
-        ok = ptx::mbar_wait(&loaded[s], (i / stages) & 1) && ptx::mbar_wait(&a_ready[s], (i / stages) & 1);
+      int s = 0;
+      uint32_t ph = 0;  // stage cursor kept incrementally: no division by the runtime stage count
+      for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == stages), s = (s + 1 == stages) ? 0 : s + 1) {
+        ok = ptx::mbar_wait(&loaded[s], ph) && ptx::mbar_wait(&a_ready[s], ph);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint64_t da = ptx::umma_desc_k_sw128(ptx::smem_u32(a_tile(s)));
@@ -323,9 +325,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
   } else {
     // ---- dequantise: thread (r, plane) owns one 32-column half of weight row r ----
     const int r = tid & (kTileN - 1), my_plane = tid >> 7;
-    for (int i = 0; i < n_chunks && ok; ++i) {
-      const int s = i % stages;
-      ok = ptx::mbar_wait(&loaded[s], (i / stages) & 1);
+    int s = 0;
+    uint32_t ph = 0;  // stage cursor kept incrementally: no division by the runtime stage count
+    for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == stages), s = (s + 1 == stages) ? 0 : s + 1) {
+      ok = ptx::mbar_wait(&loaded[s], ph);
       if (!ok) break;
       const unsigned char* blk = raw_blk(s);
       unsigned char* arow = a_tile(s) + r * 128;
@@ -493,9 +496,10 @@ __global__ void __launch_bounds__(kTc2Threads, 1) qmm_tc2_kernel(const __grid_co
 
   if (warp == 16) {
     if (lane == 0) {
-      for (int i = 0; i < n_chunks && ok; ++i) {
-        const int s = i % stages;
-        ok = ptx::mbar_wait(&mma_done[s], ((i / stages) & 1) ^ 1);
+      int s = 0;
+      uint32_t ph = 0;  // stage cursor kept incrementally: no division by the runtime stage count
+      for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == stages), s = (s + 1 == stages) ? 0 : s + 1) {
+        ok = ptx::mbar_wait(&mma_done[s], ph ^ 1u);
         if (!ok) break;
         ptx::mbar_expect_tx(&loaded[s], n_tiles * BB + tn * 128);
         for (int tile = 0; tile < n_tiles; ++tile)
@@ -507,9 +511,10 @@ __global__ void __launch_bounds__(kTc2Threads, 1) qmm_tc2_kernel(const __grid_co
   } else if (warp == 17) {
     if (lane == 0) {
       const uint32_t idesc = ptx::umma_idesc_bf16(kTileN, tn);
-      for (int i = 0; i < n_chunks && ok; ++i) {
-        const int s = i % stages;
-        ok = ptx::mbar_wait(&loaded[s], (i / stages) & 1) && ptx::mbar_wait(&a_ready[s], (i / stages) & 1);
+      int s = 0;
+      uint32_t ph = 0;  // stage cursor kept incrementally: no division by the runtime stage count
+      for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == stages), s = (s + 1 == stages) ? 0 : s + 1) {
+        ok = ptx::mbar_wait(&loaded[s], ph) && ptx::mbar_wait(&a_ready[s], ph);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint64_t db = ptx::umma_desc_k_sw128(ptx::smem_u32(x_tile(s)));
@@ -526,9 +531,10 @@ __global__ void __launch_bounds__(kTc2Threads, 1) qmm_tc2_kernel(const __grid_co
   } else {
     // ---- dequantise: thread (r, plane, tile) owns one 32-column half of weight row r of a tile ----
     const int r = tid & (kTileN - 1), plane = (tid >> 7) & 1, tile = tid >> 8;
-    for (int i = 0; i < n_chunks && ok; ++i) {
-      const int s = i % stages;
-      ok = ptx::mbar_wait(&loaded[s], (i / stages) & 1);
+    int s = 0;
+    uint32_t ph = 0;  // stage cursor kept incrementally: no division by the runtime stage count
+    for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == stages), s = (s + 1 == stages) ? 0 : s + 1) {
+      ok = ptx::mbar_wait(&loaded[s], ph);
       if (!ok) break;
       if (MODE != B200_Q_BF16 && tile < n_tiles) {
         const unsigned char* blk = raw_blk(s, tile);
