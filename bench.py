@@ -516,6 +516,91 @@ def run_moe(args, rank, world, local):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------------------------
+# quantised matmul microbench: the Llama-3-8B layer shapes at a given number of packed rows
+# ---------------------------------------------------------------------------------------------
+QMM_SHAPES = {"qkv": (6144, 4096), "o": (4096, 4096), "gate_up": (28672, 4096), "down": (4096, 14336),
+              "lm_head": (128256, 4096)}
+
+
+def run_qmm(args, local):
+    """One step = every selected shape once (weights rotated so that nothing is served from L2).
+    Up to 16 rows the path is a weight stream (HBM roofline on the weight bytes); from 64 rows it is
+    a dense contraction (tensor roofline)."""
+    import torch
+
+    from dmlx_b200 import device as dev
+
+    torch.cuda.set_device(local)
+    mxfp4 = args.workload.endswith("mxfp4")
+    mode = dev.Q_MXFP4_G32 if mxfp4 else dev.Q_AFFINE4_G64
+    bytes_per_weight = 0.53125 if mxfp4 else 0.5625
+    rows = args.rows
+    names = list(QMM_SHAPES) if args.shape == "all" else [args.shape]
+    stream = torch.cuda.Stream()
+    per_shape, launches = {}, 0
+    sampler = ClockSampler(local)
+    sampler.start()
+    with torch.cuda.stream(stream):
+        for name in names:
+            n, k = QMM_SHAPES[name]
+            copies = 2 if n > 100000 else 8  # more weight bytes than the 126 MB L2 between reuses
+            ws = [dev.QWeight.random(mode, n, k, 1, seed=17 + i) for i in range(copies)]
+            x = torch.randn((rows, k), device="cuda").bfloat16()
+            epi = dev.EPI_SWIGLU if name == "gate_up" else dev.EPI_NONE
+            out = torch.empty((rows, n // 2 if epi else n), device="cuda", dtype=torch.bfloat16)
+            for _ in range(max(args.warmup, 3)):
+                for w in ws:
+                    dev.qmm(w, x, epi, out=out, path=args.path)
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for w in ws:
+                    dev.qmm(w, x, epi, out=out, path=args.path)
+            g.replay()
+            stream.synchronize()
+            l0 = dev.launch_count()
+            for w in ws:  # counted outside the graph: launches per pass over the copies
+                dev.qmm(w, x, epi, out=out, path=args.path)
+            per_call = (dev.launch_count() - l0) / copies
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(args.steps):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+            us = e0.elapsed_time(e1) / args.steps / copies * 1e3
+            launches += per_call * args.steps * copies
+            per_shape[name] = {"us": us, "weight_GBs": bytes_per_weight * n * k / us / 1e3,
+                               "tflops": 2.0 * rows * n * k / us / 1e6, "kernels_per_call": per_call}
+            del ws, g
+    clocks = sampler.stop()
+    assert dev.qmm_error_word() == 0
+    hbm_peak, peak_kind = load_peaks()
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    total_us = sum(v["us"] for v in per_shape.values())
+    total_w = sum(bytes_per_weight * QMM_SHAPES[nm][0] * QMM_SHAPES[nm][1] for nm in names)
+    top = max(names, key=lambda nm: QMM_SHAPES[nm][0] * QMM_SHAPES[nm][1])
+    if rows <= 58:  # below the ridge (208 flop/B over 3.56 flop/B per row): weight streaming
+        roof = {"bound": "hbm", "achieved": per_shape[top]["weight_GBs"], "peak": hbm_peak, "unit": "GB/s",
+                "frac": per_shape[top]["weight_GBs"] / hbm_peak, "peak_kind": f"of {peak_kind}", "traffic": None,
+                "frac_of_8TBs": per_shape[top]["weight_GBs"] / 8000.0}
+    else:
+        tpeak = float(peaks.get("bf16_tflops", 1590.0))
+        roof = {"bound": "tensor", "achieved": per_shape[top]["tflops"], "peak": tpeak, "unit": "TFLOP/s",
+                "frac": per_shape[top]["tflops"] / tpeak, "peak_kind": "of measured (burst cuBLAS bf16)" if peaks else "of fallback",
+                "traffic": None}
+    roof["kernel"] = f"{top}: " + ("qmm_mma_kernel" if rows <= 16 and args.path in (0, 3) else "qmm_tc2_kernel" if rows > 128 else "qmm_tc_kernel")
+    print(json.dumps({
+        "metric": "quantised matmul weight bytes per second", "value": total_w / total_us / 1e3, "unit": "GB/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_us / 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": ("mxfp4" if mxfp4 else "int4 affine g64") + " weights, bf16 activations, f32 accumulate",
+        "data": "synthetic", "config": {"workload": args.workload, "rows": rows, "shapes": {nm: QMM_SHAPES[nm] for nm in names},
+                                        "path": args.path, "l2": "weights rotated over more than L2 between reuses"},
+        "roofline": roof, "per_shape": per_shape, "e2e": None, "gpu_launches": int(launches), "clocks": clocks,
+    }))
+
+
 def run_reference(args, rank: int):
     """--impl reference: the reference's own algorithm for the path on the host cores.  The
     reference itself (Zig + MLX) cannot be built here, so the timed code is the oracle's C twin."""
@@ -591,10 +676,13 @@ def main():
     ap.add_argument("--moe-tile", type=int, default=128, help="moe_mxfp4 only: token tile of the grouped matmul")
     ap.add_argument("--layers", type=int, default=0, help="llama8b_int4 only: fewer layers (profiling / smoke runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--rows", type=int, default=1, help="qmm_* only: packed rows")
+    ap.add_argument("--shape", default="all", help="qmm_* only: qkv | o | gate_up | down | lm_head | all")
+    ap.add_argument("--path", type=int, default=0, help="qmm_* only: kernel path (0 = automatic)")
     ap.add_argument("--seqs", type=int, default=64, help="sequences per GPU (64 = the configuration; fewer for profiling)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = 10 if args.impl == "reference" else (50 if args.workload.startswith("llama") else (20 if args.workload.startswith("moe") else 500))
+        args.steps = 10 if args.impl == "reference" else (50 if args.workload.startswith("llama") else (20 if args.workload.startswith(("moe", "qmm")) else 500))
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -614,6 +702,10 @@ def main():
         return
     if args.workload.startswith("moe"):
         run_moe(args, rank, world, local)
+        return
+    if args.workload.startswith("qmm"):
+        if rank == 0:
+            run_qmm(args, local)
         return
     torch.cuda.set_device(local)
     if world > 1:
