@@ -35,11 +35,11 @@ sys.path.insert(0, ROOT)
 HQ, HKV, D, PAGE = 32, 8, 128, 32
 
 
-def traffic_ratio():
+def traffic_ratio(fp8: bool = False):
     """DRAM traffic / algorithmic bytes of the attention kernel, from the committed ncu summary
     (captured on a 16-sequence case; traffic grows in proportion to cached tokens)."""
     import re
-    p = os.path.join(ROOT, "profiles", "paged_attn_mma_bf16_config2_16seq.md")
+    p = os.path.join(ROOT, "profiles", "paged_attn_mma_fp8_config2_16seq.md" if fp8 else "paged_attn_mma_bf16_config2_16seq.md")
     if not os.path.exists(p):
         return None
     m = re.search(r"traffic_ratio:\s*([0-9.]+)", open(p).read())
@@ -806,8 +806,8 @@ def main():
         "gpu_launches": 3 * args.steps,
         "clocks": clocks,
     }
-    tr = traffic_ratio()
-    if tr and not fp8:
+    tr = traffic_ratio(fp8)
+    if tr:
         result["roofline"]["traffic"] = tr * alg
         result["roofline"]["traffic_note"] = "ncu capture of a 16-sequence case scaled by cached tokens"
     if not args.no_cpu_baseline and world == 1:

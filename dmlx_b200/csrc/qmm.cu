@@ -12,15 +12,20 @@
 // position p stores column 2p (p < 4) or 2(p-4)+1, so that (word >> 4i) & 0x000F000F yields the
 // adjacent column pair (2i, 2i+1) in the two halves of a bf16x2 register.
 //
-// Two kernels share the layout, the split-K scratch and the epilogue:
-//   * qmm_simt_kernel : bandwidth-bound GEMV for a handful of rows, f32 FMAs on CUDA cores.
-//   * qmm_tc_kernel   : "swap-AB" tcgen05 GEMM.  The 128 weight rows are the MMA M dimension, the
-//     packed tokens (16..256 per tile) the N dimension, so small and large batches both map to
-//     dense tensor-core tiles.  Per 64-column chunk: warp 4 issues one bulk copy for the weight
-//     block and one 2-D TMA load (128B swizzle) for the activation tile; warps 0-3 dequantise the
-//     block to bf16 into a 128B-swizzled K-major tile (1 row per thread); warp 5 issues 4
-//     tcgen05.mma (M128 x N x K16) accumulating in tensor memory and commits to free the stage.
-//     After the last chunk warps 0-3 read the accumulator with tcgen05.ld.
+// The kernels share the layout, the split-K scratch and the epilogue:
+//   * qmm_mma_kernel  (up to 16 rows): weight streaming.  Persistent CTAs, a producer warp keeping a
+//     ring of raw 4-bit blocks in flight, 8 consumer warps feeding mma.sync from registers.
+//   * qmm_tc_kernel   (17..128 rows per token tile, and the grouped MoE launches): "swap-AB" tcgen05
+//     GEMM.  The 128 weight rows are the MMA M dimension, the packed tokens (16..256 per tile) the N
+//     dimension, so small and large batches both map to dense tensor-core tiles.  Per 64-column
+//     chunk: warp 8 issues one bulk copy for the weight block and one 2-D TMA load (128B swizzle)
+//     for the activation tile; warps 0-7 dequantise the block to bf16 into a 128B-swizzled K-major
+//     tile (one row and one 32-column plane per thread); warp 9 issues 4 tcgen05.mma (M128 x N x
+//     K16) accumulating in tensor memory and commits to free the stage.  After the last chunk warps
+//     0-3 read the accumulator with tcgen05.ld.
+//   * qmm_tc2_kernel  (129..256 rows per token tile): the same with two weight tiles per CTA
+//     sharing one activation tile.
+//   * qmm_simt_kernel : CUDA-core GEMV kept as a forced path for tests.
 // Split-K partials go to an f32 scratch; a finish kernel sums them in split order (deterministic),
 // applies the epilogue (residual add, SwiGLU) and writes bf16.  No CTA waits on another.
 #include <cuda.h>
