@@ -9,6 +9,7 @@
 // postprocess advances by one chunk (src/batch_builder.zig:50-66 vs src/scheduler.zig:335-336), which
 // would write the same tokens into the KV cache twice.
 #include <algorithm>
+#include <iterator>
 #include <unordered_map>
 #include <vector>
 
@@ -27,7 +28,63 @@ struct b200_engine {
   std::vector<b200_token_output> outs;
   std::vector<uint32_t> scratch;
   int32_t last_free_pages = 0;
+  // Prefix sharing (paged.BlockManager.findCachedPrefix, src/kvcache/paged.zig:234-265, applied when a
+  // request starts its prefill): live sequence slots with the chained hashes of their prompt blocks.
+  bool share_prefix = false;
+  struct Live { b200_request* req; std::vector<uint64_t> chain; };
+  std::unordered_map<int32_t, Live> live;               // by sequence slot
+  std::unordered_map<uint64_t, uint64_t> shared_tokens;  // request id -> tokens taken over from a donor
 };
+
+namespace {
+constexpr uint64_t kPageTokens = 32;
+
+// Chained hashes of the full 32-token blocks of a prompt (hashBlock, src/kvcache/paged.zig:224-230).
+std::vector<uint64_t> prompt_chain(const std::vector<uint32_t>& prompt) {
+  std::vector<uint64_t> chain;
+  uint64_t h = 0;
+  for (uint64_t b = 0; (b + 1) * kPageTokens <= prompt.size(); ++b) {
+    h = b200_hash_block(h, prompt.data() + b * kPageTokens, kPageTokens);
+    chain.push_back(h);
+  }
+  return chain;
+}
+
+// Tokens of a request whose K/V are in the pool.
+uint64_t cached_tokens(const b200_request* r) {
+  return b200_request_state(r) == B200_REQ_PREFILLING ? b200_request_prefill_offset(r) : b200_request_prompt_len(r);
+}
+
+// A request about to run its first prefill chunk takes over the longest run of full prompt blocks
+// that a live sequence already holds (same chained hashes, already prefilled): the pages are shared
+// by reference count and the request's prefill cursor starts behind them.  At least one prompt
+// token is always left to compute (its logits give the first output token).
+b200_status try_share_prefix(b200_engine* e, b200_request* r) {
+  const int32_t slot = b200_request_kv_slot(r);
+  std::vector<uint32_t> prompt(b200_request_prompt_len(r));
+  b200_request_prompt(r, prompt.data(), prompt.size());
+  b200_engine::Live me{r, prompt_chain(prompt)};
+  uint64_t best = 0;
+  int32_t donor = -1;
+  for (const auto& kvp : e->live) {
+    if (kvp.first == slot) continue;
+    const auto& other = kvp.second;
+    const uint64_t have = cached_tokens(other.req) / kPageTokens;
+    uint64_t j = 0;
+    while (j < me.chain.size() && j < other.chain.size() && j < have && me.chain[j] == other.chain[j]) ++j;
+    if (j > best) { best = j; donor = kvp.first; }
+  }
+  while (best > 0 && best * kPageTokens >= prompt.size()) --best;
+  e->live[slot] = std::move(me);
+  if (best == 0) return B200_OK;
+  b200_status st = b200_kv_rollback(e->kv, slot, 0);  // give back the page taken at admission
+  if (st == B200_OK) st = b200_kv_fork(e->kv, donor, slot, (int32_t)(best * kPageTokens));
+  if (st != B200_OK) return st;
+  b200_request_force_state(r, B200_REQ_PREFILLING, best * kPageTokens, nullptr, 0);
+  e->shared_tokens[b200_request_id(r)] = best * kPageTokens;
+  return B200_OK;
+}
+}  // namespace
 
 extern "C" {
 
@@ -71,6 +128,18 @@ b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t ca
   b200_status st = b200_scheduler_schedule(e->sched, e->prefill.data(), &np, e->decode.data(), &nd, active, &need);
   if (st != B200_OK) return st;
   if (np + nd == 0) return B200_OK;
+  if (e->share_prefix) {
+    for (uint64_t i = 0; i < np; ++i) {
+      b200_request* r = e->prefill[i];
+      const int32_t slot = b200_request_kv_slot(r);
+      auto it = e->live.find(slot);
+      if (it != e->live.end() && it->second.req == r) continue;  // already running
+      if (b200_request_prefill_offset(r) == 0) {
+        st = try_share_prefix(e, r);
+        if (st != B200_OK) return st;
+      }
+    }
+  }
   e->descs.clear();
   e->flat.clear();
   for (uint64_t i = 0; i < np; ++i) {  // prefill requests first (src/batch_builder.zig:100-111)
@@ -107,7 +176,19 @@ b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t ca
       out[(*n_out)++] = e->outs[i];
     }
   }
-  return b200_scheduler_postprocess(e->sched, e->outs.data(), e->outs.size());
+  st = b200_scheduler_postprocess(e->sched, e->outs.data(), e->outs.size());
+  if (e->share_prefix) {  // finished requests have given their slot back
+    for (auto it = e->live.begin(); it != e->live.end();)
+      it = b200_request_state(it->second.req) == B200_REQ_DONE ? e->live.erase(it) : std::next(it);
+  }
+  return st;
+}
+
+void b200_engine_set_prefix_sharing(b200_engine* e, int32_t on) { e->share_prefix = on != 0; }
+
+uint64_t b200_engine_shared_tokens(const b200_engine* e, uint64_t id) {
+  auto it = e->shared_tokens.find(id);
+  return it == e->shared_tokens.end() ? 0 : it->second;
 }
 
 // Generated tokens of a request so far (and whether it has finished); finished requests stay

@@ -511,3 +511,9 @@ class Engine:
 
     def free_pages(self) -> int:
         return int(lib.b200_engine_free_pages(self._h))
+
+    def set_prefix_sharing(self, on: bool = True):
+        lib.b200_engine_set_prefix_sharing(self._h, int(on))
+
+    def shared_tokens(self, rid: int) -> int:
+        return int(lib.b200_engine_shared_tokens(self._h, rid))

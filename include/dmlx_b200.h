@@ -386,6 +386,12 @@ b200_status b200_engine_result(const b200_engine* e, uint64_t id, uint32_t* out,
                                uint64_t* n, int32_t* done);
 void b200_engine_forget(b200_engine* e, uint64_t id);
 int32_t b200_engine_free_pages(const b200_engine* e);
+/* Prefix sharing (off by default): a request about to start its prefill takes over, by reference
+ * count, the full 32-token prompt blocks that a live request with the same chained block hashes has
+ * already prefilled (findCachedPrefix, src/kvcache/paged.zig:234-265); its own appends copy a shared
+ * page on write (:167-206).  shared_tokens reports how many prompt tokens a request took over. */
+void b200_engine_set_prefix_sharing(b200_engine* e, int32_t on);
+uint64_t b200_engine_shared_tokens(const b200_engine* e, uint64_t id);
 
 /* ---- mixture of experts ------------------------------------------------------------------------ */
 /* Top-k routing (MoERouter.topkRoute, src/moe_router.zig:55-103; DSV4Gate.forward scoring, bias and

@@ -22,11 +22,7 @@ def _bits(a):
     return (ref_math.bf16_round(a).view(np.uint32) >> 16).astype(np.uint16)
 
 
-def test_config1_greedy_decode_matches_oracle():
-    from dmlx_b200 import device as dev
-
-    cfg = CFG
-    weights = ref_math.random_llama_weights(cfg, seed=2026)
+def _build_model(dev, cfg, weights):
     model = dev.LlamaModel(cfg.n_layers, cfg.hidden, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab,
                            max_rows=1024, max_reqs=16, max_seqs=16, rms_eps=cfg.eps, rope_theta=cfg.theta)
     names = {"wq": 0, "wk": 1, "wv": 2, "wo": 3, "gate": 4, "up": 5, "down": 6}
@@ -39,6 +35,30 @@ def test_config1_greedy_decode_matches_oracle():
     model.set_norm(-1, 0, _bits(weights["final_norm"]))
     model.set_embedding(_bits(weights["embed"]))
     model.finalize()
+    return model
+
+
+def _check_against_oracle(cfg, weights, prompt, got, tag):
+    """Greedy ids equal the fp32 oracle up to the first near-tie; a divergence is the runner-up."""
+    o = ref_math.LlamaB1(cfg, weights)
+    logits = o.forward(prompt)
+    for j, g in enumerate(got):
+        tok = ref_host.greedy(logits)
+        if g != tok:
+            top2 = np.sort(logits)[-2:]
+            assert top2[1] - top2[0] < 2e-2 * np.abs(logits).max(), (tag, j, float(top2[1] - top2[0]))
+            assert g == int(np.argsort(logits)[-2]), (tag, j)
+            return False
+        logits = o.forward([tok])
+    return True
+
+
+def test_config1_greedy_decode_matches_oracle():
+    from dmlx_b200 import device as dev
+
+    cfg = CFG
+    weights = ref_math.random_llama_weights(cfg, seed=2026)
+    model = _build_model(dev, cfg, weights)
     kv = dev.PagedKVCache(cfg.n_layers, cfg.n_kv_heads, cfg.head_dim, 128, 16, 16, cfg.n_heads, max_rows=1024,
                           attn_scratch_chunks=8192)
     eng = dev.Engine(model, kv, max_prefill_tokens=96)  # prompts above 96 tokens prefill in chunks
@@ -71,6 +91,54 @@ def test_config1_greedy_decode_matches_oracle():
         else:
             identical += 1
     assert identical >= 1, identical  # every divergence above was checked to be a near-tie with the runner-up token
+    eng.close()
+    model.close()
+    kv.close()
+
+
+def test_prefix_sharing_through_engine():
+    """Config 5 in small: requests that share a prompt prefix take over the donor's full pages by
+    reference count when they start their prefill (findCachedPrefix, src/kvcache/paged.zig:234-265),
+    prefill only their own suffix in chunks, copy a shared page on write, and still decode what the
+    oracle decodes for the whole prompt.  Integer state is checked exactly: tokens taken over,
+    reference counts of the shared pages, every page returned at the end."""
+    from dmlx_b200 import device as dev
+
+    cfg = CFG
+    weights = ref_math.random_llama_weights(cfg, seed=2026)
+    model = _build_model(dev, cfg, weights)
+    kv = dev.PagedKVCache(cfg.n_layers, cfg.n_kv_heads, cfg.head_dim, 96, 16, 16, cfg.n_heads, max_rows=1024,
+                          attn_scratch_chunks=8192)
+    eng = dev.Engine(model, kv, max_prefill_tokens=64)
+    eng.set_prefix_sharing(True)
+    rng = np.random.default_rng(9)
+    prefix = rng.integers(0, cfg.vocab, 100).tolist()  # 3 full pages + 4 tokens
+    suffix_lens = [20, 5, 70, 33, 1, 64]
+    prompts = [prefix + rng.integers(0, cfg.vocab, n).tolist() for n in suffix_lens]
+    prompts.append(rng.integers(0, cfg.vocab, 50).tolist())  # unrelated prompt
+    n_new = 12
+    eng.submit(1, prompts[0], n_new)  # the donor prefills 120 tokens in two chunks
+    for _ in range(3):
+        eng.step()
+    for i in range(1, len(prompts)):
+        eng.submit(i + 1, prompts[i], n_new)
+    eng.step()  # the sharers start: 96 tokens each come from the donor's pages
+    donor_pages = kv.block_table(0)[:3]
+    refs = kv.ref_counts()
+    assert [eng.shared_tokens(i + 1) for i in range(len(prompts))] == [0, 96, 96, 96, 96, 96, 0]
+    assert [refs[p] for p in donor_pages] == [6, 6, 6]
+    steps = 0
+    while eng.active_count() > 0 and steps < 200:
+        eng.step()
+        steps += 1
+    assert eng.active_count() == 0 and kv.error_word() == 0
+    assert eng.free_pages() == 96 and sum(kv.ref_counts()) == 0
+    exact = 0
+    for i, p in enumerate(prompts):
+        got, done = eng.result(i + 1)
+        assert done and len(got) == n_new
+        exact += _check_against_oracle(cfg, weights, p, got, i)
+    assert exact >= 1
     eng.close()
     model.close()
     kv.close()
