@@ -270,6 +270,61 @@ __global__ void append_bf16_kernel(KvDev d, int layer, const __nv_bfloat16* __re
   }
 }
 
+// bf16 pools inside the model step: RoPE on q (in place) and k, and the append of the rotated k and
+// of v into their pages, in one pass over the fused projection output.  CTA (row, y) takes heads
+// 8y..8y+7 of a packed row, one per warp; lane l the rotation pairs (2l, 2l+1) of a head (non-traditional RoPE:
+// pair (i, i + D/2) rotates by pos * theta^(-2i/D)), so sin/cos are computed once per thread.
+// The page comes from the block table that b200_kv_reserve has just grown.
+__global__ void __launch_bounds__(256) rope_append_bf16_kernel(KvDev d, int layer, __nv_bfloat16* __restrict__ q,
+                                                               const __nv_bfloat16* __restrict__ k, const __nv_bfloat16* __restrict__ v,
+                                                               int q_stride, int k_stride, int v_stride,
+                                                               const int* __restrict__ positions, const int* __restrict__ row_seq, int hq,
+                                                               float log2_theta) {
+  const int row = blockIdx.x, D = d.head_dim, H = d.n_kv_heads, half = D / 2;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pos = positions[row], seq = row_seq[row];
+  const int page_idx = pos / d.page_size, slot = pos - page_idx * d.page_size;
+  // a step whose reservation failed has no page for this row: nothing is written (the error word is set)
+  const bool have_page = seq >= 0 && seq < d.max_seqs && page_idx < d.seq_pages[seq];
+  const int page = have_page ? d.block_table[(size_t)seq * d.max_pages_per_seq + page_idx] : 0;
+  const int ppt = half / 32;  // rotation pairs per lane: 1 (D = 64) or 2 (D = 128)
+  float sn[2], cs[2];
+  for (int j = 0; j < ppt; ++j) {
+    const int i = lane * ppt + j;
+    sincosf((float)pos * exp2f(-log2_theta * (2.0f * i) / (float)D), &sn[j], &cs[j]);
+  }
+  for (int h = blockIdx.y * 8 + warp; h < hq + H; h += 8 * gridDim.y) {
+    const bool is_q = h < hq;
+    const __nv_bfloat16* src = is_q ? q + (size_t)row * q_stride + (size_t)h * D : k + (size_t)row * k_stride + (size_t)(h - hq) * D;
+    __nv_bfloat16* dst = nullptr;
+    if (is_q) dst = q + (size_t)row * q_stride + (size_t)h * D;
+    else if (have_page)
+      dst = (__nv_bfloat16*)d.k_pool + ((((size_t)layer * d.n_pages + page) * H + (h - hq)) * d.page_size + slot) * (size_t)D;
+    float lo[2], hi[2];
+    for (int j = 0; j < ppt; ++j) {
+      const int i = lane * ppt + j;
+      const float x1 = __bfloat162float(src[i]), x2 = __bfloat162float(src[i + half]);
+      lo[j] = x1 * cs[j] - x2 * sn[j];
+      hi[j] = x1 * sn[j] + x2 * cs[j];
+    }
+    if (dst) {
+      for (int j = 0; j < ppt; ++j) {
+        const int i = lane * ppt + j;
+        dst[i] = __float2bfloat16(lo[j]);
+        dst[i + half] = __float2bfloat16(hi[j]);
+      }
+    }
+  }
+  if (have_page && blockIdx.y == 0) {
+    const int vec_per_head = D / 8;
+    for (int i = threadIdx.x; i < H * vec_per_head; i += blockDim.x) {
+      const int head = i / vec_per_head, c = i - head * vec_per_head;
+      uint4* vd = (uint4*)((__nv_bfloat16*)d.v_pool + ((((size_t)layer * d.n_pages + page) * H + head) * d.page_size + slot) * (size_t)D);
+      vd[c] = ((const uint4*)(v + (size_t)row * v_stride + (size_t)head * D))[c];
+    }
+  }
+}
+
 __device__ __forceinline__ unsigned char to_e4m3(float x) {
   return (unsigned char)__nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3);
 }
@@ -626,6 +681,26 @@ b200_status b200_kv_append_strided(b200_kv* kv, int32_t layer, const void* d_k_r
     append_fp8_kernel<<<dim3(gx, kv->cfg.n_kv_heads, 2), 128, 0, s>>>(kv->dev, layer, (const __nv_bfloat16*)d_k_rows,
                                                                       (const __nv_bfloat16*)d_v_rows, k_stride, v_stride);
   }
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+// RoPE + append for a bf16 pool in one launch (model step); other pools take the two-kernel route.
+b200_status b200_kv_rope_append_strided(b200_kv* kv, int32_t layer, void* d_q, const void* d_k_rows, const void* d_v_rows,
+                                        int32_t q_stride, int32_t k_stride, int32_t v_stride, const int32_t* d_positions,
+                                        const int32_t* d_row_seq, int32_t total_rows, int32_t n_q_heads, float theta, void* stream) {
+  const b200_kv_config& c = kv->cfg;
+  if (c.kv_dtype != B200_KV_BF16 || (c.head_dim != 64 && c.head_dim != 128)) {
+    b200_status st = b200_rope(d_q, const_cast<void*>(d_k_rows), d_positions, total_rows, n_q_heads, c.n_kv_heads, c.head_dim, q_stride,
+                               k_stride, theta, stream);
+    if (st != B200_OK) return st;
+    return b200_kv_append_strided(kv, layer, d_k_rows, d_v_rows, k_stride, v_stride, total_rows, stream);
+  }
+  if (layer < 0 || layer >= c.n_layers) { b200_set_error("append: layer %d out of range", layer); return B200_ERR_INVALID_ARGUMENT; }
+  if (total_rows <= 0) return B200_OK;
+  rope_append_bf16_kernel<<<dim3(total_rows, (n_q_heads + c.n_kv_heads + 7) / 8), 256, 0, (cudaStream_t)stream>>>(kv->dev, layer, (__nv_bfloat16*)d_q, (const __nv_bfloat16*)d_k_rows,
+                                                                         (const __nv_bfloat16*)d_v_rows, q_stride, k_stride, v_stride,
+                                                                         d_positions, d_row_seq, n_q_heads, log2f(theta));
   B200_LAUNCH_CHECK();
   return B200_OK;
 }

@@ -49,6 +49,9 @@ struct b200_kv {
 // projection output.
 b200_status b200_kv_append_strided(b200_kv* kv, int32_t layer, const void* d_k_rows, const void* d_v_rows,
                                    int32_t k_stride, int32_t v_stride, int32_t total_rows, void* stream);
+b200_status b200_kv_rope_append_strided(b200_kv* kv, int32_t layer, void* d_q, const void* d_k_rows, const void* d_v_rows,
+                                        int32_t q_stride, int32_t k_stride, int32_t v_stride, const int32_t* d_positions,
+                                        const int32_t* d_row_seq, int32_t total_rows, int32_t n_q_heads, float theta, void* stream);
 b200_status b200_paged_attn_decode_strided(b200_kv* kv, int32_t layer, const void* d_q, int32_t q_stride,
                                            const int32_t* d_row_seq, const int32_t* d_row_ctx, int32_t total_rows,
                                            void* d_out, void* stream);
