@@ -93,9 +93,26 @@ __global__ void argmax_kernel(const __nv_bfloat16* __restrict__ logits, int voca
   const __nv_bfloat16* lr = logits + (size_t)row * vocab;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-    float v = __bfloat162float(lr[i]);
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  // 16-byte loads where the row allows it (row start and length multiples of 8 elements); a thread
+  // meets its elements in increasing index order, so a strict > keeps the first maximum it saw.
+  const bool vec = (vocab % 8 == 0) && ((reinterpret_cast<uintptr_t>(lr) & 15) == 0);
+  if (vec) {
+    const uint4* lv = reinterpret_cast<const uint4*>(lr);
+    for (int c = threadIdx.x; c < vocab / 8; c += blockDim.x) {
+      const uint4 q = lv[c];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xFFFF0000u);
+        if (lo > best) { best = lo; bi = c * 8 + 2 * j; }
+        if (hi > best) { best = hi; bi = c * 8 + 2 * j + 1; }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      float v = __bfloat162float(lr[i]);
+      if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
   }
   auto better = [](float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); };
 #pragma unroll

@@ -46,7 +46,8 @@ struct b200_kv {
 };
 
 // Internal variants with explicit row strides (elements), used when q/k/v live inside a fused
-// projection output.
+// projection output.  reuse_plan = 1 skips the split-K planning kernel: the caller guarantees that the
+// previous attention call on this pool used the same row arrays (the layers of one model step).
 b200_status b200_kv_append_strided(b200_kv* kv, int32_t layer, const void* d_k_rows, const void* d_v_rows,
                                    int32_t k_stride, int32_t v_stride, int32_t total_rows, void* stream);
 b200_status b200_kv_rope_append_strided(b200_kv* kv, int32_t layer, void* d_q, const void* d_k_rows, const void* d_v_rows,
@@ -54,7 +55,7 @@ b200_status b200_kv_rope_append_strided(b200_kv* kv, int32_t layer, void* d_q, c
                                         const int32_t* d_row_seq, int32_t total_rows, int32_t n_q_heads, float theta, void* stream);
 b200_status b200_paged_attn_decode_strided(b200_kv* kv, int32_t layer, const void* d_q, int32_t q_stride,
                                            const int32_t* d_row_seq, const int32_t* d_row_ctx, int32_t total_rows,
-                                           void* d_out, void* stream);
+                                           void* d_out, void* stream, int32_t reuse_plan);
 b200_status b200_paged_attn_prefill_strided(b200_kv* kv, int32_t layer, const void* d_q, int32_t q_stride,
                                             const int32_t* d_row_seq, const int32_t* d_row_ctx, int32_t total_rows,
-                                            void* d_out, void* stream);
+                                            void* d_out, void* stream, int32_t reuse_plan);

@@ -359,8 +359,8 @@ static b200_status llama_forward_eager(b200_llama* m, b200_kv* kv, const b200_pa
     STEP_CAT(2, b200_kv_rope_append_strided(kv, l, m->qkv, m->qkv + qd, m->qkv + qd + kd, qkv_dim, qkv_dim, qkv_dim, m->d_pos,
                                             m->d_row_seq, T, c.n_heads, c.rope_theta, stream));
     // batches that hold prefill chunks (more rows than requests) take the grouped kernel
-    if (T > n_req) { STEP_CAT(0, b200_paged_attn_prefill_strided(kv, l, m->qkv, qkv_dim, m->d_row_seq, m->d_row_ctx, T, m->attn, stream)); }
-    else { STEP_CAT(0, b200_paged_attn_decode_strided(kv, l, m->qkv, qkv_dim, m->d_row_seq, m->d_row_ctx, T, m->attn, stream)); }
+    if (T > n_req) { STEP_CAT(0, b200_paged_attn_prefill_strided(kv, l, m->qkv, qkv_dim, m->d_row_seq, m->d_row_ctx, T, m->attn, stream, l > 0)); }
+    else { STEP_CAT(0, b200_paged_attn_decode_strided(kv, l, m->qkv, qkv_dim, m->d_row_seq, m->d_row_ctx, T, m->attn, stream, l > 0)); }
     STEP_CAT(1, b200_qmm(m->wo[l], m->attn, T, m->x, B200_EPI_RESIDUAL, m->x, 0.f, B200_QMM_AUTO, stream));
     STEP(b200_rmsnorm(m->x, m->ffn_norm[l], m->h, T, c.hidden, c.rms_eps, stream));
     STEP_CAT(1, b200_qmm(m->wgu[l], m->h, T, m->act, B200_EPI_SWIGLU, nullptr, 0.f, B200_QMM_AUTO, stream));

@@ -1271,12 +1271,12 @@ int b200_attn_path = 0;  // 0 = automatic, 1 = CUDA-core kernel, 2 = tensor-core
 extern "C" b200_status b200_paged_attn_decode(b200_kv* kv, int32_t layer, const void* d_q, const int32_t* d_row_seq,
                                               const int32_t* d_row_ctx, int32_t total_rows, void* d_out, void* stream) {
   return b200_paged_attn_decode_strided(kv, layer, d_q, kv->cfg.n_q_heads * kv->cfg.head_dim, d_row_seq, d_row_ctx,
-                                        total_rows, d_out, stream);
+                                        total_rows, d_out, stream, 0);
 }
 
 b200_status b200_paged_attn_decode_strided(b200_kv* kv, int32_t layer, const void* d_q, int32_t q_stride,
                                            const int32_t* d_row_seq, const int32_t* d_row_ctx, int32_t total_rows,
-                                           void* d_out, void* stream) {
+                                           void* d_out, void* stream, int32_t reuse_plan) {
   b200_status st = b200_require_device();
   if (st != B200_OK) return st;
   const b200_kv_config& c = kv->cfg;
@@ -1304,9 +1304,11 @@ b200_status b200_paged_attn_decode_strided(b200_kv* kv, int32_t layer, const voi
   a.chunk_start = kv->d_chunk_start; a.total_rows = total_rows; a.n_q_heads = c.n_q_heads; a.pages_per_chunk = ppc;
   a.part_o = kv->d_part_o; a.part_ml = kv->d_part_ml;
   a.scale_log2 = 1.4426950408889634f / sqrtf((float)c.head_dim);
-  attn_plan_kernel<<<1, 1024, 0, s>>>(d_row_ctx, total_rows, c.page_size, ppc, kv->d_chunk_start, kv->max_chunks,
-                                      kv->dev.state + ST_ATTN_ERR);
-  B200_LAUNCH_CHECK();
+  if (!reuse_plan) {  // the chunk plan depends on the row arrays only: the layers of one step share it
+    attn_plan_kernel<<<1, 1024, 0, s>>>(d_row_ctx, total_rows, c.page_size, ppc, kv->d_chunk_start, kv->max_chunks,
+                                        kv->dev.state + ST_ATTN_ERR);
+    B200_LAUNCH_CHECK();
+  }
   if (use_mma && fp8) return launch_attn_mma_fp8(kv, a, d_out, g_sm_count, s);
   if (use_mma) return c.head_dim == 128 ? launch_attn_mma<128>(kv, a, d_out, g_sm_count, s) : launch_attn_mma<64>(kv, a, d_out, g_sm_count, s);
   const int grid = g_sm_count * 3;
@@ -1317,18 +1319,18 @@ b200_status b200_paged_attn_decode_strided(b200_kv* kv, int32_t layer, const voi
 extern "C" b200_status b200_paged_attn_prefill(b200_kv* kv, int32_t layer, const void* d_q, const int32_t* d_row_seq,
                                                const int32_t* d_row_ctx, int32_t total_rows, void* d_out, void* stream) {
   return b200_paged_attn_prefill_strided(kv, layer, d_q, kv->cfg.n_q_heads * kv->cfg.head_dim, d_row_seq, d_row_ctx,
-                                         total_rows, d_out, stream);
+                                         total_rows, d_out, stream, 0);
 }
 
 b200_status b200_paged_attn_prefill_strided(b200_kv* kv, int32_t layer, const void* d_q, int32_t q_stride,
                                             const int32_t* d_row_seq, const int32_t* d_row_ctx, int32_t total_rows,
-                                            void* d_out, void* stream) {
+                                            void* d_out, void* stream, int32_t reuse_plan) {
   const b200_kv_config& c = kv->cfg;
   const int G = c.n_kv_heads > 0 ? c.n_q_heads / c.n_kv_heads : 0;
   // Grouping needs the GQA group to divide the 16 MMA rows and a bf16 pool; anything else takes the
   // per-row kernels (same results).
   if (c.kv_dtype != B200_KV_BF16 || !(G == 1 || G == 2 || G == 4 || G == 8) || b200_attn_path == 1)
-    return b200_paged_attn_decode_strided(kv, layer, d_q, q_stride, d_row_seq, d_row_ctx, total_rows, d_out, stream);
+    return b200_paged_attn_decode_strided(kv, layer, d_q, q_stride, d_row_seq, d_row_ctx, total_rows, d_out, stream, reuse_plan);
   b200_status st = b200_require_device();
   if (st != B200_OK) return st;
   if (layer < 0 || layer >= c.n_layers) { b200_set_error("attention: layer %d out of range", layer); return B200_ERR_INVALID_ARGUMENT; }
@@ -1350,10 +1352,12 @@ b200_status b200_paged_attn_prefill_strided(b200_kv* kv, int32_t layer, const vo
   a.group_first = kv->d_groups; a.part_base = kv->d_groups + stride; a.row_group = kv->d_groups + 2 * stride;
   a.n_groups = kv->d_groups + 3 * stride - 1;  // last word of the row_group array (never a row index)
   a.q_tokens = 16 / G;
-  attn_plan_groups_kernel<<<1, 1024, 0, s>>>(d_row_seq, d_row_ctx, total_rows, c.page_size, ppc, a.q_tokens, kv->d_chunk_start,
-                                             kv->d_groups, kv->d_groups + stride, kv->d_groups + 2 * stride,
-                                             kv->d_groups + 3 * stride - 1, kv->max_chunks, kv->dev.state + ST_ATTN_ERR);
-  B200_LAUNCH_CHECK();
+  if (!reuse_plan) {
+    attn_plan_groups_kernel<<<1, 1024, 0, s>>>(d_row_seq, d_row_ctx, total_rows, c.page_size, ppc, a.q_tokens, kv->d_chunk_start,
+                                               kv->d_groups, kv->d_groups + stride, kv->d_groups + 2 * stride,
+                                               kv->d_groups + 3 * stride - 1, kv->max_chunks, kv->dev.state + ST_ATTN_ERR);
+    B200_LAUNCH_CHECK();
+  }
   return c.head_dim == 128 ? launch_attn_prefill<128>(kv, a, d_out, g_sm_count, s) : launch_attn_prefill<64>(kv, a, d_out, g_sm_count, s);
 }
 
