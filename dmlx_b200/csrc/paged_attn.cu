@@ -1139,6 +1139,218 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1)
   if (!alive && lane == 0) atomicExch(a.d.state + ST_ATTN_ERR, B200_ERR_DEVICE_FLAGGED);
 }
 
+__device__ __forceinline__ void mma_f16_16816_full(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                                   uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Prefill rows over an FP8-E4M3 pool (head_dim 128): the row grouping of paged_attn_prefill_kernel
+// with the operand handling of paged_attn_mma_fp8_kernel (codes widened to f16 in registers, MMA K
+// slots permuted to match ldmatrix on byte tiles, K scale on the scores, relative V scale on P).
+__global__ void __launch_bounds__(kMmaWarps * 32, 1)
+    paged_attn_prefill_fp8_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap, AttnArgs a) {
+  constexpr int D = 128, TILE = 32 * D, KS = D / 16, NO = D / 8, STAGES = kMmaStages;
+  extern __shared__ unsigned char smem_dyn[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  unsigned char* my_tiles = smem + (size_t)warp * STAGES * 2 * TILE;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)kMmaWarps * STAGES * 2 * TILE) + warp * STAGES;
+  const int H = a.d.n_kv_heads, G = a.n_q_heads / H;
+  const int n_groups = *a.n_groups;
+  const int n_items = a.chunk_start[n_groups] * H;
+  const int worker = blockIdx.x * kMmaWarps + warp, n_workers = gridDim.x * kMmaWarps;
+
+  if (lane == 0) {
+    for (int s = 0; s < STAGES; ++s) ptx::mbar_init(&full_bar[s], 1);
+    ptx::mbar_fence_init();
+  }
+  __syncwarp();
+
+  int p_item = worker, p_page = 0, p_end = 0, p_begin = 0, p_head = 0, p_pid = 0;
+  uint32_t prod_n = 0;
+  auto producer_enter_item = [&]() {
+    if (p_item < n_items) {
+      const GroupItem it = decode_group_item(a, p_item, n_groups);
+      p_begin = it.page_begin; p_page = it.page_begin; p_end = it.page_end; p_head = it.head;
+      const int pg = it.page_begin + lane;
+      if (pg < it.page_end) p_pid = a.d.block_table[(size_t)it.seq * a.d.max_pages_per_seq + pg];
+    }
+  };
+  auto produce_one = [&]() {
+    if (p_item >= n_items) return;
+    const int pid = __shfl_sync(0xffffffffu, p_pid, p_page - p_begin);
+    const uint32_t s = prod_n % STAGES;
+    if (lane == 0) {
+      ptx::fence_proxy_async_smem();
+      unsigned char* kd = my_tiles + (size_t)s * 2 * TILE;
+      const int row0 = (pid * H + p_head) * 32;
+      ptx::mbar_expect_tx(&full_bar[s], 2 * TILE);
+      ptx::tma_load_3d(kd, &kmap, 0, row0, a.layer, &full_bar[s]);
+      ptx::tma_load_3d(kd + TILE, &vmap, 0, row0, a.layer, &full_bar[s]);
+    }
+    prod_n += 1;
+    p_page += 1;
+    if (p_page >= p_end) {
+      p_item += n_workers;
+      producer_enter_item();
+    }
+  };
+  producer_enter_item();
+  for (int i = 0; i < STAGES; ++i) produce_one();
+
+  bool alive = true;
+  uint32_t cons_n = 0;
+  const int ld_r = lane & 7, ld_m = lane >> 3;
+  const int tokA = g / G, headA = g - tokA * G, tokB = (g + 8) / G, headB = (g + 8) - tokB * G;
+  for (int item = worker; item < n_items && alive; item += n_workers) {
+    const GroupItem it = decode_group_item(a, item, n_groups);
+    const bool onA = tokA < it.n_rows, onB = tokB < it.n_rows;
+    const int ctxA = onA ? it.ctx0 + tokA : 0, ctxB = onB ? it.ctx0 + tokB : 0;
+    uint32_t qa0[KS], qa1[KS], qa2[KS], qa3[KS];
+    {
+      const __nv_bfloat16* qA = a.q + (size_t)(it.first_row + (onA ? tokA : 0)) * a.q_stride + (it.head * G + headA) * D;
+      const __nv_bfloat16* qB = a.q + (size_t)(it.first_row + (onB ? tokB : 0)) * a.q_stride + (it.head * G + headB) * D;
+#pragma unroll
+      for (int c = 0; c < KS; ++c) {
+        const uint2 ra = *reinterpret_cast<const uint2*>(qA + 16 * c + 4 * t), rb = *reinterpret_cast<const uint2*>(qB + 16 * c + 4 * t);
+        qa0[c] = onA ? pack_f16(ptx::bf16_lo(ra.x), ptx::bf16_hi(ra.x)) : 0u;
+        qa2[c] = onA ? pack_f16(ptx::bf16_lo(ra.y), ptx::bf16_hi(ra.y)) : 0u;
+        qa1[c] = onB ? pack_f16(ptx::bf16_lo(rb.x), ptx::bf16_hi(rb.x)) : 0u;
+        qa3[c] = onB ? pack_f16(ptx::bf16_lo(rb.y), ptx::bf16_hi(rb.y)) : 0u;
+      }
+    }
+    float my_ks = 0.f, my_vs = 0.f;
+    {
+      const int pg = it.page_begin + lane;
+      if (pg < it.page_end) {
+        const int pid = a.d.block_table[(size_t)it.seq * a.d.max_pages_per_seq + pg];
+        const size_t si = ((size_t)a.layer * a.d.n_pages + pid) * H + it.head;
+        my_ks = a.d.k_scale[si];
+        my_vs = a.d.v_scale[si];
+      }
+    }
+    float v_ref = my_vs;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v_ref = fmaxf(v_ref, __shfl_xor_sync(0xffffffffu, v_ref, o));
+    const float my_vr = v_ref > 0.f ? my_vs / v_ref : 0.f;
+
+    float o[NO][4];
+#pragma unroll
+    for (int j = 0; j < NO; ++j) { o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.f; }
+    float mA = -1e30f, lA = 0.f, mB = -1e30f, lB = 0.f;
+
+    for (int pg = it.page_begin; pg < it.page_end; ++pg) {
+      const uint32_t s = cons_n % STAGES;
+      alive = ptx::mbar_wait(&full_bar[s], (cons_n / STAGES) & 1u);
+      if (!alive) break;
+      const float ks = __shfl_sync(0xffffffffu, my_ks, pg - it.page_begin) * a.scale_log2;
+      const float vr = __shfl_sync(0xffffffffu, my_vr, pg - it.page_begin);
+      const uint32_t kbase = ptx::smem_u32(my_tiles + (size_t)s * 2 * TILE), vbase = kbase + TILE;
+      float sc[4][4];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) { sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f; }
+#pragma unroll
+      for (int kk = 0; kk < KS / 4; ++kk) {
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+          const int row = nt * 8 + ld_r, cc = 4 * kk + ld_m;
+          uint32_t b[4];
+          ldsm_x4(kbase + row * 128 + ((cc ^ (row & 7)) << 4), b);
+#pragma unroll
+          for (int m = 0; m < 4; ++m)
+            mma_f16_16816_full(sc[nt], qa0[4 * kk + m], qa1[4 * kk + m], qa2[4 * kk + m], qa3[4 * kk + m], e4m3x2_to_f16x2(b[m]),
+                               e4m3x2_to_f16x2(b[m] >> 16));
+        }
+      }
+      const int tok0 = pg * 32;
+      float mxA = -1e30f, mxB = -1e30f;
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int tok = tok0 + nt * 8 + 2 * t + e;
+          sc[nt][e] = tok < ctxA ? sc[nt][e] * ks : -1e30f;
+          sc[nt][2 + e] = tok < ctxB ? sc[nt][2 + e] * ks : -1e30f;
+          mxA = fmaxf(mxA, sc[nt][e]);
+          mxB = fmaxf(mxB, sc[nt][2 + e]);
+        }
+      }
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+      mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+      mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+      const float mA_new = fmaxf(mA, mxA), mB_new = fmaxf(mB, mxB);
+      const float corrA = exp2f(mA - mA_new), corrB = exp2f(mB - mB_new);
+      float psA = 0.f, psB = 0.f;
+      uint32_t pa0[2], pa1[2], pa2[2], pa3[2];
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt) {
+        float pA[4], pB[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float sa = sc[2 * kt + (e >> 1)][e & 1], sb = sc[2 * kt + (e >> 1)][2 + (e & 1)];
+          pA[e] = sa > -1e29f ? exp2f(sa - mA_new) : 0.f;
+          pB[e] = sb > -1e29f ? exp2f(sb - mB_new) : 0.f;
+          psA += pA[e];
+          psB += pB[e];
+        }
+        pa0[kt] = pack_f16(pA[0] * vr, pA[1] * vr);
+        pa2[kt] = pack_f16(pA[2] * vr, pA[3] * vr);
+        pa1[kt] = pack_f16(pB[0] * vr, pB[1] * vr);
+        pa3[kt] = pack_f16(pB[2] * vr, pB[3] * vr);
+      }
+      lA = lA * corrA + psA; mA = mA_new;
+      lB = lB * corrB + psB; mB = mB_new;
+      if (__any_sync(0xffffffffu, corrA != 1.f || corrB != 1.f)) {
+#pragma unroll
+        for (int j = 0; j < NO; ++j) { o[j][0] *= corrA; o[j][1] *= corrA; o[j][2] *= corrB; o[j][3] *= corrB; }
+      }
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt) {
+#pragma unroll
+        for (int jj = 0; jj < KS / 2; ++jj) {
+          const int row = kt * 16 + (ld_m & 1) * 8 + ld_r, cc = 2 * jj + (ld_m >> 1);
+          uint32_t b[4];
+          ldsm_x4_trans(vbase + row * 128 + ((cc ^ (row & 7)) << 4), b);
+          const uint32_t p0 = __byte_perm(b[0], 0u, 0x3120), p1 = __byte_perm(b[1], 0u, 0x3120);
+          const uint32_t p2 = __byte_perm(b[2], 0u, 0x3120), p3 = __byte_perm(b[3], 0u, 0x3120);
+          mma_f16_16816_full(o[4 * jj], pa0[kt], pa1[kt], pa2[kt], pa3[kt], e4m3x2_to_f16x2(p0), e4m3x2_to_f16x2(p1));
+          mma_f16_16816_full(o[4 * jj + 1], pa0[kt], pa1[kt], pa2[kt], pa3[kt], e4m3x2_to_f16x2(p0 >> 16), e4m3x2_to_f16x2(p1 >> 16));
+          mma_f16_16816_full(o[4 * jj + 2], pa0[kt], pa1[kt], pa2[kt], pa3[kt], e4m3x2_to_f16x2(p2), e4m3x2_to_f16x2(p3));
+          mma_f16_16816_full(o[4 * jj + 3], pa0[kt], pa1[kt], pa2[kt], pa3[kt], e4m3x2_to_f16x2(p2 >> 16), e4m3x2_to_f16x2(p3 >> 16));
+        }
+      }
+      __syncwarp();
+      cons_n += 1;
+      produce_one();
+    }
+    if (!alive) break;
+    lA += __shfl_xor_sync(0xffffffffu, lA, 1);
+    lA += __shfl_xor_sync(0xffffffffu, lA, 2);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+    lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    if (onA) {
+      const size_t pidx = (size_t)(it.slot0 + tokA) * a.n_q_heads + it.head * G + headA;
+#pragma unroll
+      for (int c = 0; c < KS; ++c)
+        *reinterpret_cast<float4*>(a.part_o + pidx * D + 16 * c + 4 * t) =
+            make_float4(o[2 * c][0] * v_ref, o[2 * c + 1][0] * v_ref, o[2 * c][1] * v_ref, o[2 * c + 1][1] * v_ref);
+      if (t == 0) { a.part_ml[pidx * 2] = mA; a.part_ml[pidx * 2 + 1] = lA; }
+    }
+    if (onB) {
+      const size_t pidx = (size_t)(it.slot0 + tokB) * a.n_q_heads + it.head * G + headB;
+#pragma unroll
+      for (int c = 0; c < KS; ++c)
+        *reinterpret_cast<float4*>(a.part_o + pidx * D + 16 * c + 4 * t) =
+            make_float4(o[2 * c][2] * v_ref, o[2 * c + 1][2] * v_ref, o[2 * c][3] * v_ref, o[2 * c + 1][3] * v_ref);
+      if (t == 0) { a.part_ml[pidx * 2] = mB; a.part_ml[pidx * 2 + 1] = lB; }
+    }
+  }
+  if (!alive && lane == 0) atomicExch(a.d.state + ST_ATTN_ERR, B200_ERR_DEVICE_FLAGGED);
+}
+
 // D threads per (row, query head): merge the partials of the row's group chunks and write bf16.
 template <int D>
 __global__ void __launch_bounds__(D) attn_combine_groups_kernel(AttnArgs a, __nv_bfloat16* __restrict__ out) {
@@ -1256,6 +1468,21 @@ b200_status launch_attn_prefill(const b200_kv* kv, const AttnArgs& a, void* d_ou
   return B200_OK;
 }
 
+b200_status launch_attn_prefill_fp8(const b200_kv* kv, const AttnArgs& a, void* d_out, int sms, cudaStream_t s) {
+  constexpr int TILE = 32 * 128;
+  const size_t smem = (size_t)kMmaWarps * kMmaStages * 2 * TILE + 1024 + sizeof(uint64_t) * kMmaWarps * kMmaStages;
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(paged_attn_prefill_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    configured = true;
+  }
+  paged_attn_prefill_fp8_kernel<<<sms * 2, kMmaWarps * 32, smem, s>>>(kv->kmap, kv->vmap, a);
+  B200_LAUNCH_CHECK();
+  attn_combine_groups_kernel<128><<<a.total_rows * a.n_q_heads, 128, 0, s>>>(a, (__nv_bfloat16*)d_out);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
 int g_sm_count = 0;
 
 }  // namespace
@@ -1327,9 +1554,10 @@ b200_status b200_paged_attn_prefill_strided(b200_kv* kv, int32_t layer, const vo
                                             void* d_out, void* stream, int32_t reuse_plan) {
   const b200_kv_config& c = kv->cfg;
   const int G = c.n_kv_heads > 0 ? c.n_q_heads / c.n_kv_heads : 0;
-  // Grouping needs the GQA group to divide the 16 MMA rows and a bf16 pool; anything else takes the
-  // per-row kernels (same results).
-  if (c.kv_dtype != B200_KV_BF16 || !(G == 1 || G == 2 || G == 4 || G == 8) || b200_attn_path == 1)
+  // Grouping needs the GQA group to divide the 16 MMA rows, and head_dim 128 for FP8 pools; anything
+  // else takes the per-row kernels (same results).
+  const bool fp8 = c.kv_dtype == B200_KV_FP8_E4M3;
+  if ((fp8 && c.head_dim != 128) || !(G == 1 || G == 2 || G == 4 || G == 8) || b200_attn_path == 1)
     return b200_paged_attn_decode_strided(kv, layer, d_q, q_stride, d_row_seq, d_row_ctx, total_rows, d_out, stream, reuse_plan);
   b200_status st = b200_require_device();
   if (st != B200_OK) return st;
@@ -1358,6 +1586,7 @@ b200_status b200_paged_attn_prefill_strided(b200_kv* kv, int32_t layer, const vo
                                                kv->d_groups + 3 * stride - 1, kv->max_chunks, kv->dev.state + ST_ATTN_ERR);
     B200_LAUNCH_CHECK();
   }
+  if (fp8) return launch_attn_prefill_fp8(kv, a, d_out, g_sm_count, s);
   return c.head_dim == 128 ? launch_attn_prefill<128>(kv, a, d_out, g_sm_count, s) : launch_attn_prefill<64>(kv, a, d_out, g_sm_count, s);
 }
 

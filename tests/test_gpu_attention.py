@@ -142,8 +142,9 @@ def test_prefill_rows_as_causal_decode_rows():
         assert rel <= REL_TOL and cos >= COS_TOL, (r, rel, cos)
 
 
-@pytest.mark.parametrize("hq,hkv,d", [(8, 2, 64), (32, 8, 128), (16, 2, 128), (4, 4, 64)])
-def test_prefill_groups_match_oracle_and_row_kernel(hq, hkv, d):
+@pytest.mark.parametrize("hq,hkv,d,kv_dtype", [(8, 2, 64, 0), (32, 8, 128, 0), (16, 2, 128, 0), (4, 4, 64, 0),
+                                                (32, 8, 128, 1), (16, 2, 128, 1)])
+def test_prefill_groups_match_oracle_and_row_kernel(hq, hkv, d, kv_dtype):
     """b200_paged_attn_prefill on a mixed batch: prefill chunks that start in the middle of a cached
     prefix (src/scheduler.zig:183-186 chunk cursor), chunks of 1..70 rows, and plain decode rows.
     Every row equals the oracle on its causal prefix, and the per-row kernel on the same inputs."""
@@ -156,12 +157,16 @@ def test_prefill_groups_match_oracle_and_row_kernel(hq, hkv, d):
     n_pages = sum(-(-t // 32) for t in totals) + 4
     n_rows = sum(n for _, n in reqs)
     kv = dev.PagedKVCache(1, hkv, d, n_pages, len(reqs), max(-(-max(totals) // 32), 1), hq, max_rows=max(totals) + n_rows,
-                          attn_scratch_chunks=4096)
+                          attn_scratch_chunks=4096, kv_dtype=kv_dtype)
     kv.set_free_order(rng.permutation(n_pages).tolist())
     ks = [ref_math.bf16_round(rng.normal(0, 1, (t, hkv, d)).astype(np.float32)) for t in totals]
     vs = [ref_math.bf16_round(rng.normal(0, 1, (t, hkv, d)).astype(np.float32)) for t in totals]
     kv.reserve(dev.pack_desc_array([(s, t, 0, -1) for s, t in enumerate(totals)]).cuda())
     kv.append(0, torch.tensor(np.concatenate(ks), device="cuda").bfloat16(), torch.tensor(np.concatenate(vs), device="cuda").bfloat16())
+    if kv_dtype != 0:  # the oracle for FP8 pools reads what the pool holds: decode(codes) * scale
+        eff = [kv.gather(0, s) for s in range(len(reqs))]
+        ks = [a.float().cpu().numpy() for a, _ in eff]
+        vs = [b.float().cpu().numpy() for _, b in eff]
     q = ref_math.bf16_round(rng.normal(0, 1, (n_rows, hq, d)).astype(np.float32))
     row_seq = np.concatenate([np.full(n, s, np.int32) for s, (_, n) in enumerate(reqs)])
     row_ctx = np.concatenate([np.arange(c + 1, c + n + 1, dtype=np.int32) for c, n in reqs])
@@ -174,5 +179,5 @@ def test_prefill_groups_match_oracle_and_row_kernel(hq, hkv, d):
         want = ref_math.gqa_attention_decode(q[r], ks[s][:c], vs[s][:c])
         rel, cos = _close(got[r], want)
         assert rel <= REL_TOL and cos >= COS_TOL, (r, s, c, rel, cos)
-    assert np.abs(got - per_row).max() <= 2e-2 * np.abs(per_row).max()
+    assert np.abs(got - per_row).max() <= 2e-2 * np.abs(per_row).max()  # both kernels read the same pool
     kv.close()
