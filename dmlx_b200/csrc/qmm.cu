@@ -1066,7 +1066,8 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
     b200_set_error("qmm: %zu bytes of shared memory needed, %d available", smem, smem_budget[MODE]);
     return B200_ERR_CAPACITY;
   }
-  const int splits0 = a.items ? 1 : pick_splits(tiles, a.kc, g_sms, ctas_per_sm);
+  // A CTA pays its first load (about 2.3 us measured), set-up and epilogue once: about 12 chunks' worth.
+  const int splits0 = a.items ? 1 : pick_splits(tiles, a.kc, g_sms, ctas_per_sm, 12);
   a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
   const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
   st = ensure_state((size_t)splits * (a.items ? (size_t)rows : (size_t)tts * tn) * a.nt * kTileN * sizeof(float));
