@@ -631,6 +631,50 @@ def run_reference(args, rank: int):
             "e2e": {"value": val, "unit": "decode tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         }))
         return
+    if args.workload.startswith(("qmm", "moe")):
+        # dequantise + matmul in the C twin on a bounded sample of weight rows, extrapolated linearly
+        mxfp4 = args.workload.endswith("mxfp4")
+        rng = np.random.default_rng(0)
+        if args.workload.startswith("qmm"):
+            names = list(QMM_SHAPES) if args.shape == "all" else [args.shape]
+            shapes, rows, scale_to = [QMM_SHAPES[nm] for nm in names], args.rows, 1.0
+        else:  # one expert's gate/up and down matmuls at the mean rows per expert, times 257 experts and the layers
+            shapes = [(2 * MOE["inter"], MOE["hidden"]), (MOE["hidden"], MOE["inter"])]
+            rows = MOE["tokens"] * MOE["top_k"] // MOE["n_experts"]
+            scale_to = float((MOE["n_experts"] + MOE["tokens"] / rows) * MOE["layers"])
+        times = []
+        for i in range(args.warmup + args.steps):
+            t_step = 0.0
+            for n, k in shapes:
+                ns = min(n, 4096)
+                x = rng.normal(0, 1, (rows, k)).astype(np.float32)
+                if mxfp4:
+                    w = (rng.integers(0, 256, (ns, k // 2), dtype=np.uint8), rng.integers(118, 124, (ns, k // 32), dtype=np.uint8))
+                    t0 = time.perf_counter()
+                    ref_c.qmm_mxfp4(w[0], w[1], x)
+                else:
+                    w = (rng.integers(0, 2 ** 32, (ns, k // 8), dtype=np.uint32), np.full((ns, k // 64), 0.005, np.float32),
+                         np.full((ns, k // 64), -0.04, np.float32))
+                    t0 = time.perf_counter()
+                    ref_c.qmm_affine4(w[0], w[1], w[2], x)
+                t_step += (time.perf_counter() - t0) * n / ns
+            if i >= args.warmup:
+                times.append(t_step * scale_to)
+        ms = float(np.mean(times) * 1e3)
+        bpw = 0.53125 if mxfp4 else 0.5625
+        if args.workload.startswith("qmm"):
+            metric, unit, val = "quantised matmul weight bytes per second", "GB/s", sum(bpw * n * k for n, k in shapes) / (ms * 1e-3) / 1e9
+        else:
+            metric, unit, val = "decode tokens/sec (ragged continuous batch)", "decode tokens/s", MOE["tokens"] / (ms * 1e-3)
+        cb = {"value": val, "unit": unit, "cores": ref_c.num_threads(), "kind": "port",
+              "sample": f"first 4096 weight rows of every matrix at {rows} rows, extrapolated linearly"}
+        print(json.dumps({
+            "impl": "reference", "metric": metric, "value": val, "unit": unit, "n_gpus": args.gpus, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": {"workload": args.workload, "rows": rows}, "cpu_baseline": cb,
+            "e2e": {"value": val, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }))
+        return
     import torch
 
     seed = 1234
