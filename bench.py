@@ -420,6 +420,8 @@ def run_moe(args, rank, world, local):
     c = dict(MOE)
     if args.layers:
         c["layers"] = args.layers
+    if args.moe_tmem_a >= 0:
+        dev.set_qmm_grouped_tmem_a(bool(args.moe_tmem_a))
     K, W = args.steps, max(args.warmup, 3)
     n_tok = c["tokens"] // world  # the step decodes 4096 tokens in total: strong scaling
     el = c["n_experts"] // world
@@ -506,7 +508,7 @@ def run_moe(args, rank, world, local):
                    "parallelism": f"ep{world}" if world > 1 else "single GPU, all experts local"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "peak_kind": "of measured (sustained cuBLAS bf16)" if peaks else "of fallback", "traffic": None,
-                     "kernel": "qmm_tc_kernel<mxfp4> grouped (gate/up + down) and dense (shared expert)",
+                     "kernel": "qmm_tca_kernel<mxfp4> grouped (gate/up + down) and dense (shared expert)",
                      "algorithmic_flops_per_step": flops},
         "e2e": {"value": c["tokens"] / (e2e_ms / K * 1e-3), "unit": "decode tokens/s",
                 "h2d_bytes_per_step": int(x_host.numel() * 2 * world), "d2h_bytes_per_step": int(x_host.numel() * 2 * world)},
@@ -590,7 +592,7 @@ def run_qmm(args, local):
         roof = {"bound": "tensor", "achieved": per_shape[top]["tflops"], "peak": tpeak, "unit": "TFLOP/s",
                 "frac": per_shape[top]["tflops"] / tpeak, "peak_kind": "of measured (burst cuBLAS bf16)" if peaks else "of fallback",
                 "traffic": None}
-    roof["kernel"] = f"{top}: " + ("qmm_mma_kernel" if rows <= 16 and args.path in (0, 3) else "qmm_tc2_kernel" if rows > 128 else "qmm_tc_kernel")
+    roof["kernel"] = f"{top}: " + ("qmm_mma_kernel" if rows <= 16 and args.path in (0, 3) else "automatic choice between qmm_tca_kernel and qmm_tc2_kernel" if args.path == 0 else f"path {args.path}")
     print(json.dumps({
         "metric": "quantised matmul weight bytes per second", "value": total_w / total_us / 1e3, "unit": "GB/s", "n_gpus": 1,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": total_us / 1e3, "higher_is_better": True,
@@ -718,6 +720,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="llama8b_int4")
     ap.add_argument("--moe-tile", type=int, default=128, help="moe_mxfp4 only: token tile of the grouped matmul")
+    ap.add_argument("--moe-tmem-a", type=int, default=-1, help="moe_mxfp4 only: 0/1 forces the grouped matmul kernel (default: library choice)")
     ap.add_argument("--layers", type=int, default=0, help="llama8b_int4 only: fewer layers (profiling / smoke runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--rows", type=int, default=1, help="qmm_* only: packed rows")

@@ -182,6 +182,7 @@ _sig("b200_llama_device_buffers", None, vp, P(vp), P(vp), P(vp))
 _sig("b200_llama_last_logits", i32, vp, vp, i32)
 _sig("b200_llama_launch_count", C.c_int64, vp)
 _sig("b200_launch_count", C.c_int64)
+_sig("b200_set_qmm_grouped_tmem_a", None, i32)
 _sig("b200_llama_profile_enable", None, vp, i32)
 _sig("b200_llama_enable_graphs", None, vp, i32)
 _sig("b200_llama_profile_collect", i32, vp, P(C.c_double), P(C.c_int64))

@@ -406,18 +406,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
   (void)any_bad;
 }
 
-// ---- tcgen05 kernel for large batches: two weight tiles per CTA ---------------------------------
-// With 129..256 rows per token tile the kernel above moves a 32 KiB activation tile through
-// shared memory for every 4.6 KiB weight block, and at one CTA per SM only four such stages fit:
-// the load -> dequantise -> MMA -> release chain of a stage is longer than the work the other
-// stages hold, and the tensor pipe idles.  Here a CTA owns TWO adjacent 128-row weight tiles and
-// multiplies both with the same activation tile (two accumulators, 2 x 256 tensor-memory columns):
-// a stage carries twice the MMA work per activation byte, so the same shared memory hides twice
-// the latency and the L2 -> SM activation traffic per flop halves.  16 dequant warps (one thread
-// per weight row and 32-column plane of either tile), one loader warp, one MMA warp.
-constexpr int kTc2Threads = 18 * 32;
-constexpr int kTc2DequantThreads = 16 * 32;
-
 // One 32-token batch of accumulators (v[j] = token c0+j, weight row n) to scratch or to the output.
 __device__ __forceinline__ void tile_epilogue_store(const QmmArgs& a, const uint32_t (&v)[32], int c0, int rows_here, int t0,
                                                     int n, int lane, bool direct, float* wsp, size_t n_pad) {
@@ -452,6 +440,177 @@ __device__ __forceinline__ void tile_epilogue_store(const QmmArgs& a, const uint
     }
   }
 }
+
+// ---- tcgen05 kernel with the weight operand in tensor memory -----------------------------------
+// In qmm_tc_kernel a stage is one unit: weight block + activation tile + the 16 KiB dequantised
+// tile travel together, a stage lives for load + dequantise + MMA (about 3000 cycles measured with
+// timestamps) and only three of them fit a CTA.  Here the two lifetimes are separated and the
+// dequantised tile leaves shared memory:
+//   * loads: a ring of P slots (raw 4-bit block + activation tile, 13-21 KiB each) runs ahead by
+//     the load latency;
+//   * dequantised weights: warps 0-7 write them straight into tensor memory (tcgen05.st; thread r
+//     owns lane r = weight row r, a 64-column chunk is 32 columns of packed bf16 pairs), into a ring
+//     of Q slots behind the accumulator, and tcgen05.mma takes its A operand from there.  No swizzled
+//     shared-memory tile, no proxy fence, and the MMA reads only the activation tile from shared
+//     memory.
+// An MMA's completion releases both its load slot and its tensor-memory slot (two commits).
+constexpr int kTcaThreads = 320;
+
+template <int MODE>
+__global__ void __launch_bounds__(kTcaThreads, 2) qmm_tca_kernel(const __grid_constant__ CUtensorMap xmap, QmmArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  constexpr int BB = block_bytes(MODE);
+  constexpr int kRaw = ((BB + 127) / 128) * 128;
+  const int tn = a.tn, P = a.stages, Q = a.a_slots;
+  auto x_tile = [&](int s) { return smem + (size_t)s * tn * 128; };
+  auto raw_blk = [&](int s) { return smem + (size_t)P * tn * 128 + (size_t)s * kRaw; };
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)P * (tn * 128 + kRaw));
+  uint64_t* full = bars;                 // [P] raw block + activation tile have landed
+  uint64_t* slot_free = bars + P;        // [P] the MMAs reading the activation tile are done
+  uint64_t* a_ready = bars + 2 * P;      // [Q] dequantised chunk is in tensor memory
+  uint64_t* a_free = bars + 2 * P + Q;   // [Q] the MMAs reading it are done
+  uint64_t* accum_ready = bars + 2 * P + 2 * Q;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_ready + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nt = blockIdx.x, split = blockIdx.y;
+  int t0 = blockIdx.z * tn, rows_here = min(tn, a.rows - t0);
+  const unsigned char* blocks = a.blocks;
+  if (a.items) {
+    if ((int)blockIdx.z >= *a.n_items) return;
+    const int4 it = a.items[blockIdx.z];
+    blocks += (size_t)it.x * a.expert_stride;
+    t0 = it.y;
+    rows_here = it.z;
+  }
+  const int kc0 = split * a.chunks_per_split, kc1 = min(kc0 + a.chunks_per_split, a.kc);
+  const int n_chunks = kc1 - kc0;
+  uint32_t acc_cols = 32;
+  while (acc_cols < (uint32_t)tn) acc_cols <<= 1;
+  uint32_t ncols = 32;
+  while (ncols < acc_cols + 32u * (uint32_t)Q) ncols <<= 1;
+
+  if (tid == 0) {
+    for (int s = 0; s < P; ++s) {
+      ptx::mbar_init(&full[s], 1);
+      ptx::mbar_init(&slot_free[s], 1);
+    }
+    for (int q = 0; q < Q; ++q) {
+      ptx::mbar_init(&a_ready[q], 2 * kTileN);
+      ptx::mbar_init(&a_free[q], 1);
+    }
+    ptx::mbar_init(accum_ready, 1);
+    ptx::mbar_fence_init();
+  }
+  if (warp == 9) {
+    ptx::tmem_alloc(tmem_slot, ncols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t a_col0 = tmem_base + acc_cols;
+  bool ok = true;
+
+  if (warp == 8) {
+    if (lane == 0) {
+      const unsigned char* wsrc = blocks + ((size_t)nt * a.kc + kc0) * BB;
+      for (int i = 0; i < min(n_chunks, kPrefetchAhead); ++i) ptx::bulk_prefetch_l2(wsrc + (size_t)i * BB, BB);
+      int s = 0;
+      uint32_t ph = 0;
+      for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1) {
+        if (i + kPrefetchAhead < n_chunks) ptx::bulk_prefetch_l2(wsrc + (size_t)(i + kPrefetchAhead) * BB, BB);
+        ok = ptx::mbar_wait(&slot_free[s], ph ^ 1u);
+        if (!ok) break;
+        ptx::mbar_expect_tx(&full[s], BB + tn * 128);
+        ptx::bulk_g2s(raw_blk(s), wsrc + (size_t)i * BB, BB, &full[s]);
+        ptx::tma_load_2d(x_tile(s), &xmap, (kc0 + i) * kChunkK, a.x_row0 + t0, &full[s]);
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0) {
+      const uint32_t idesc = ptx::umma_idesc_bf16(kTileN, tn);
+      int s = 0, q = 0;
+      uint32_t ph = 0, qh = 0;
+      for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1, qh ^= (q + 1 == Q),
+               q = (q + 1 == Q) ? 0 : q + 1) {
+        ok = ptx::mbar_wait(&full[s], ph) && ptx::mbar_wait(&a_ready[q], qh);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint64_t db = ptx::umma_desc_k_sw128(ptx::smem_u32(x_tile(s)));
+#pragma unroll
+        for (int k4 = 0; k4 < 4; ++k4)
+          ptx::umma_bf16_tmem_a(tmem_base, a_col0 + (uint32_t)(q * 32 + k4 * 8), db + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
+        ptx::umma_commit(&slot_free[s]);
+        ptx::umma_commit(&a_free[q]);
+      }
+      if (ok) ptx::umma_commit(accum_ready);
+    }
+  } else {
+    // ---- dequantise: thread (r, plane) owns one 32-column half of weight row r = tensor-memory lane r ----
+    const int r = tid & (kTileN - 1), plane = tid >> 7;
+    const uint32_t my_taddr = a_col0 + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(plane * 16);
+    int s = 0, q = 0;
+    uint32_t ph = 0, qh = 0;
+    for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1, qh ^= (q + 1 == Q),
+             q = (q + 1 == Q) ? 0 : q + 1) {
+      ok = ptx::mbar_wait(&full[s], ph);
+      if (!ok) break;
+      const unsigned char* blk = raw_blk(s);
+      const uint4 raw = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[r];
+      __nv_bfloat162 s2, b2;
+      row_params<MODE>(blk, r, plane, s2, b2);
+      const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+      uint32_t v[16];
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint4 d = dequant_word<MODE>(words[w], s2, b2);
+        v[4 * w] = d.x; v[4 * w + 1] = d.y; v[4 * w + 2] = d.z; v[4 * w + 3] = d.w;
+      }
+      ok = ptx::mbar_wait(&a_free[q], qh ^ 1u);
+      if (!ok) break;
+      ptx::tc_fence_after_sync();
+      ptx::tmem_st16(my_taddr + (uint32_t)(q * 32), v);
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(&a_ready[q]);
+    }
+    // ---- accumulator -> f32 partial tile in scratch ----
+    if (ok && warp < 4) ok = ptx::mbar_wait(accum_ready, 0);
+    if (ok && warp < 4) {
+      ptx::tc_fence_after_sync();
+      const int n = nt * kTileN + warp * 32 + lane;
+      const bool direct = gridDim.y == 1 && tn <= 64;
+      const size_t n_pad = a.items ? (size_t)a.nt * kTileN : (size_t)kTileN;
+      float* wsp = a.items ? a.ws + ((size_t)split * a.rows + t0) * n_pad + n
+                           : a.ws + (((size_t)(nt * gridDim.z + blockIdx.z) * gridDim.y + split) * tn) * kTileN + warp * 32 + lane;
+      for (int c0 = 0; c0 < rows_here; c0 += 32) {
+        uint32_t v[32];
+        ptx::tmem_ld32(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, v);
+        ptx::tmem_ld_wait();
+        tile_epilogue_store(a, v, c0, rows_here, t0, n, lane, direct, wsp, n_pad);
+      }
+    }
+  }
+  if (!ok) atomicExch(a.err, B200_ERR_DEVICE_FLAGGED);
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 9) ptx::tmem_dealloc(tmem_base, ncols);
+}
+
+// ---- tcgen05 kernel for large batches: two weight tiles per CTA ---------------------------------
+// With 129..256 rows per token tile the kernel above moves a 32 KiB activation tile through
+// shared memory for every 4.6 KiB weight block, and at one CTA per SM only four such stages fit:
+// the load -> dequantise -> MMA -> release chain of a stage is longer than the work the other
+// stages hold, and the tensor pipe idles.  Here a CTA owns TWO adjacent 128-row weight tiles and
+// multiplies both with the same activation tile (two accumulators, 2 x 256 tensor-memory columns):
+// a stage carries twice the MMA work per activation byte, so the same shared memory hides twice
+// the latency and the L2 -> SM activation traffic per flop halves.  16 dequant warps (one thread
+// per weight row and 32-column plane of either tile), one loader warp, one MMA warp.
+constexpr int kTc2Threads = 18 * 32;
+constexpr int kTc2DequantThreads = 16 * 32;
 
 template <int MODE>
 __global__ void __launch_bounds__(kTc2Threads, 1) qmm_tc2_kernel(const __grid_constant__ CUtensorMap xmap, QmmArgs a) {
@@ -1082,6 +1241,58 @@ static b200_status launch_tc(QmmArgs& a, int rows, cudaStream_t s) {
   return (splits == 1 && tn <= 64) ? B200_OK : launch_finish(a, splits, s);  // a single small split writes its output itself
 }
 
+// Quantised weights, up to 128 rows per token tile (dense) or grouped work items: dequantised weights
+// in tensor memory.
+template <int MODE>
+static b200_status launch_tca(QmmArgs& a, int rows, cudaStream_t s) {
+  const int tn = a.items ? a.tn : std::min(256, ((rows + 15) / 16) * 16);
+  a.tn = tn;
+  const int tts = (rows + tn - 1) / tn;
+  const int tiles = a.items ? a.nt * a.max_items : a.nt * tts;
+  b200_status st = ensure_state(0);
+  if (st != B200_OK) return st;
+  constexpr int kRaw = ((block_bytes(MODE) + 127) / 128) * 128;
+  const int slot_bytes = tn * 128 + kRaw;
+  static int smem_budget[3] = {0, 0, 0};
+  if (smem_budget[MODE] == 0) {
+    int dev = 0, optin = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    cudaFuncAttributes fa;
+    B200_CUDA_TRY(cudaFuncGetAttributes(&fa, qmm_tca_kernel<MODE>));
+    const int budget = optin - (int)fa.sharedSizeBytes;
+    B200_CUDA_TRY(cudaFuncSetAttribute(qmm_tca_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget));
+    smem_budget[MODE] = budget;
+  }
+  // Two CTAs per SM share the 512 tensor-memory columns: accumulator (tn rounded up to a power of
+  // two) + 32 columns per slot of dequantised weights, 256 columns per CTA (all 512 above 128 rows).
+  const int ctas_per_sm = tn <= 128 ? 2 : 1;
+  int acc_cols = 32;
+  while (acc_cols < tn) acc_cols <<= 1;
+  a.a_slots = std::min(8, ((ctas_per_sm == 2 ? 256 : 512) - acc_cols) / 32);
+  const int fixed = 1024 /*alignment slack*/ + 8 * (2 * 8 + 2 * 8 + 2) + 16;
+  const int per_cta = ctas_per_sm == 2 ? 113 * 1024 : std::min(smem_budget[MODE], 220 * 1024);
+  a.stages = std::max(2, std::min(8, (per_cta - fixed) / slot_bytes));
+  const size_t smem = (size_t)a.stages * slot_bytes + fixed;
+  if ((int)smem > smem_budget[MODE] || a.a_slots < 2) {
+    b200_set_error("qmm: %zu bytes of shared memory needed, %d available", smem, smem_budget[MODE]);
+    return B200_ERR_CAPACITY;
+  }
+  const int splits0 = a.items ? 1 : pick_splits(tiles, a.kc, g_sms, ctas_per_sm, 12);
+  a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
+  const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
+  st = ensure_state((size_t)splits * (a.items ? (size_t)rows : (size_t)tts * tn) * a.nt * kTileN * sizeof(float));
+  if (st != B200_OK) return st;
+  a.ws = g_ws; a.err = g_err;
+  CUtensorMap xmap;
+  st = make_x_map(&xmap, a.x, rows, a.k, tn);
+  if (st != B200_OK) return st;
+  a.x_row0 = 0;
+  qmm_tca_kernel<MODE><<<dim3(a.nt, splits, a.items ? a.max_items : tts), kTcaThreads, smem, s>>>(xmap, a);
+  B200_LAUNCH_CHECK();
+  return (splits == 1 && tn <= 64) ? B200_OK : launch_finish(a, splits, s);
+}
+
 // Large batches (129..256 rows per token tile): two weight tiles per CTA.
 template <int MODE>
 static b200_status launch_tc2(QmmArgs& a, int rows, cudaStream_t s) {
@@ -1180,6 +1391,9 @@ static b200_status launch_mma(QmmArgs& a, int rows, cudaStream_t s) {
   return launch_mma_nt<MODE, 4>(a, rows, s);
 }
 
+int b200_qmm_grouped_tmem_a = 1;  // measured 15.1 vs 15.8 ms on the 4-layer MoE stack
+extern "C" void b200_set_qmm_grouped_tmem_a(int32_t on) { b200_qmm_grouped_tmem_a = on; }
+
 extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
                                 const void* d_residual, float swiglu_limit, int32_t path, void* stream) {
   b200_status st = b200_require_device();
@@ -1188,11 +1402,22 @@ extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t 
   if (w->n_experts != 1) { b200_set_error("qmm: stacked expert weights go through the grouped entry point"); return B200_ERR_INVALID_ARGUMENT; }
   if (epilogue == B200_EPI_RESIDUAL && !d_residual) { b200_set_error("qmm: residual epilogue without a residual"); return B200_ERR_INVALID_ARGUMENT; }
   if (epilogue == B200_EPI_SWIGLU && (w->n % 2) != 0) { b200_set_error("qmm: SwiGLU needs an even N"); return B200_ERR_INVALID_ARGUMENT; }
-  // Quantised weights, up to 16 rows: register-dequant mma.sync kernel (pure weight streaming,
-  // measured 1.1-2.7 TB/s against 0.7-1.6 TB/s for tcgen05 at these sizes); more rows, or dense
-  // weights: tcgen05, with two weight tiles per CTA once a token tile exceeds 128 rows.
-  if (path == B200_QMM_AUTO)
-    path = (rows <= 16 && w->mode != B200_Q_BF16) ? B200_QMM_MMA : (rows > 128 ? B200_QMM_TCGEN05_X2 : B200_QMM_TCGEN05);
+  // Quantised weights, up to 16 rows: register-dequant mma.sync kernel (pure weight streaming).  More
+  // rows: tcgen05 with the dequantised weights in tensor memory; above 128 rows the tile-pair kernel
+  // where its grid is one well-filled wave without a K split (gate/up-sized matrices: 74 vs 85 us at
+  // 256 rows; elsewhere the tensor-memory kernel measured 3-8 % faster).  Dense bf16 weights: the
+  // shared-memory-operand kernels.
+  if (path == B200_QMM_AUTO) {
+    if (rows <= 16 && w->mode != B200_Q_BF16) path = B200_QMM_MMA;
+    else if (rows > 128) {
+      const int tn = std::min(256, ((rows + 15) / 16) * 16), pair_ctas = ((w->nt + 1) / 2) * ((rows + tn - 1) / tn);
+      if (ensure_state(0) != B200_OK) return B200_ERR_CUDA;
+      const bool one_wave = pair_ctas <= g_sms && pair_ctas * 2 >= g_sms;
+      path = (one_wave || w->mode == B200_Q_BF16) ? B200_QMM_TCGEN05_X2 : B200_QMM_TCGEN05_TMEM_A;
+    } else {
+      path = w->mode == B200_Q_BF16 ? B200_QMM_TCGEN05 : B200_QMM_TCGEN05_TMEM_A;
+    }
+  }
   if (path == B200_QMM_MMA && w->mode == B200_Q_BF16) path = B200_QMM_TCGEN05;
   QmmArgs a{};
   a.blocks = w->d_blocks; a.x = (const __nv_bfloat16*)d_x; a.y = (__nv_bfloat16*)d_y;
@@ -1206,6 +1431,8 @@ extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t 
     if (w->mode == B200_Q_MXFP4_G32) return launch_simt<B200_Q_MXFP4_G32>(a, rows, s);
     return launch_simt<B200_Q_BF16>(a, rows, s);
   }
+  if (path == B200_QMM_TCGEN05_TMEM_A && w->mode != B200_Q_BF16)
+    return w->mode == B200_Q_AFFINE4_G64 ? launch_tca<B200_Q_AFFINE4_G64>(a, rows, s) : launch_tca<B200_Q_MXFP4_G32>(a, rows, s);
   if (path == B200_QMM_TCGEN05_X2) {
     if (w->mode == B200_Q_AFFINE4_G64) return launch_tc2<B200_Q_AFFINE4_G64>(a, rows, s);
     if (w->mode == B200_Q_MXFP4_G32) return launch_tc2<B200_Q_MXFP4_G32>(a, rows, s);
@@ -1232,6 +1459,8 @@ b200_status b200_qmm_grouped(const b200_qweight* w, const void* d_x, int32_t row
   a.items = d_items; a.n_items = d_n_items; a.max_items = max_items; a.tn = tile_rows;
   a.expert_stride = (size_t)w->nt * w->kc * w->block_bytes;
   cudaStream_t s = (cudaStream_t)stream;
+  if (b200_qmm_grouped_tmem_a && w->mode != B200_Q_BF16)
+    return w->mode == B200_Q_AFFINE4_G64 ? launch_tca<B200_Q_AFFINE4_G64>(a, rows, s) : launch_tca<B200_Q_MXFP4_G32>(a, rows, s);
   if (w->mode == B200_Q_AFFINE4_G64) return launch_tc<B200_Q_AFFINE4_G64>(a, rows, s);
   if (w->mode == B200_Q_MXFP4_G32) return launch_tc<B200_Q_MXFP4_G32>(a, rows, s);
   return launch_tc<B200_Q_BF16>(a, rows, s);

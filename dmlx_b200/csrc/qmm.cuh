@@ -24,6 +24,7 @@ struct QmmArgs {
   int* err;                     // device error word
   int rows, n, k, nt, kc;
   int chunks_per_split, tn, stages;
+  int a_slots;                  // tensor-memory-operand kernel: slots of dequantised weights in tensor memory
   int splits;                   // small-batch kernel: number of K splits (the grid is persistent)
   int epilogue;
   int x_slab;                   // small-batch kernel: activations staged in shared memory

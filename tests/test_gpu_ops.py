@@ -109,7 +109,7 @@ def _mxfp4_weight(rng, n, k):
     return packed, scales
 
 
-@pytest.mark.parametrize("path", [1, 2, 3, 4])  # CUDA-core GEMV, tcgen05, register-dequant mma.sync, tcgen05 with tile pairs
+@pytest.mark.parametrize("path", [1, 2, 3, 4, 5])  # CUDA-core GEMV, tcgen05, register-dequant mma.sync, tcgen05 with tile pairs, tcgen05 with weights in tensor memory
 @pytest.mark.parametrize("rows,n,k", [(1, 256, 512), (3, 384, 1408), (16, 768, 512), (33, 128, 4096), (130, 512, 1024),
                                       (256, 384, 1024), (300, 256, 4096)])
 def test_qmm_affine4(path, rows, n, k):
@@ -128,7 +128,7 @@ def test_qmm_affine4(path, rows, n, k):
     assert rel <= 2e-2 and cos >= 0.9995, (rel, cos)
 
 
-@pytest.mark.parametrize("path", [1, 2, 3, 4])
+@pytest.mark.parametrize("path", [1, 2, 3, 4, 5])
 @pytest.mark.parametrize("rows,n,k", [(2, 256, 512), (24, 384, 2048), (100, 256, 4096), (200, 640, 2048)])
 def test_qmm_mxfp4(path, rows, n, k):
     from dmlx_b200 import device as dev
@@ -146,7 +146,7 @@ def test_qmm_mxfp4(path, rows, n, k):
     assert rel <= 2e-2 and cos >= 0.9995, (rel, cos)
 
 
-@pytest.mark.parametrize("path", [1, 2, 3, 4])
+@pytest.mark.parametrize("path", [1, 2, 3, 4, 5])
 def test_qmm_epilogues(path):
     """Residual add (src/models/llama.zig:466,477) and SwiGLU over interleaved gate/up rows
     (src/models/llama.zig:396-415; clipped form src/models/deepseek_v4.zig:947-966)."""
