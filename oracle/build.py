@@ -1,8 +1,8 @@
 """Builds the C twin of the oracle (oracle/ref_kernels.c) into oracle/_build/libref_kernels.so.
 
 TEST / BENCH INFRASTRUCTURE: only tests/, the smoke check and bench.py's CPU-baseline leg load it.
-The reference itself cannot be compiled here (Zig + MLX, neither present), so there is no
-oracle/_ref build; see DESIGN.md.
+The reference itself (Zig on MLX) needs a Zig toolchain and the MLX libraries, so no build of its
+own sources exists next to this twin.
 """
 import os
 import subprocess
