@@ -181,3 +181,24 @@ def test_qmm_paths_agree_and_are_deterministic():
     assert torch.equal(a1, a2)  # split-K partials are summed in a fixed order
     rel, cos = _close(dev.qmm(w, x, path=1).float().cpu().numpy(), a1.float().cpu().numpy())
     assert rel <= 1e-2 and cos >= 0.9999
+
+
+@pytest.mark.parametrize("path", [2, 3, 4, 5])
+def test_qmm_mxfp4_large_scales(path):
+    """E8M0 scales on both sides of 2^0, up to 2^12: value * 2^(scale-127) does not fit one bf16
+    multiply from the code's bit pattern, so the decode goes through 2^64 first.  Against the oracle
+    (src/models/deepseek_v4_loader.zig:839-920)."""
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(123)
+    rows, n, k = 20, 256, 1024
+    packed = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    for lo, hi in ((100, 129), (126, 140)):
+        scales = rng.integers(lo, hi, (n, k // 32), dtype=np.uint8)
+        w = dev.QWeight(dev.Q_MXFP4_G32, packed, scales, None, n, k)
+        x = ref_math.bf16_round(rng.normal(0, 1, (rows, k)))
+        got = dev.qmm(w, _bf(x), path=path).float().cpu().numpy()
+        assert dev.qmm_error_word() == 0
+        want = ref_math.qmm(x, ref_math.dequantize_mxfp4(packed, scales))
+        rel, cos = _close(got, want)
+        assert rel <= 2e-2 and cos >= 0.9995, (lo, hi, rel, cos)
