@@ -102,9 +102,10 @@ class ExpertParallelMoE:
         from . import device as dev
 
         n, k, w = x.shape[0], self.k, self.world
-        shared = None
-        if self.sgu is not None:
-            shared = dev.qmm(self.sdown, dev.qmm(self.sgu, x, dev.EPI_SWIGLU))
+
+        def shared_expert():
+            return dev.qmm(self.sdown, dev.qmm(self.sgu, x, dev.EPI_SWIGLU)) if self.sgu is not None else None
+
         logits = dev.qmm(self.gate, x)
         idx, wts, counts = dev.moe_route(logits, k, self.bias, dev.SCORE_SOFTMAX, self.route_scale)
         _, order, inv, items, n_items = dev.moe_group(idx, counts, self.tile)
@@ -112,7 +113,7 @@ class ExpertParallelMoE:
         if w == 1:
             act = dev.moe_grouped_qmm(self.gu, x_sorted, items, n_items, self.tile, dev.EPI_SWIGLU, scales, self.limit)
             y_sorted = dev.moe_grouped_qmm(self.down, act, items, n_items, self.tile)
-            return dev.moe_combine(y_sorted, inv, n, k, shared)
+            return dev.moe_combine(y_sorted, inv, n, k, shared_expert())
         el = self.n_experts // w
         recv_counts = exchange_counts(counts, w, self.group)  # [W, E_local] on the device
         splits = torch.stack([counts.view(w, el).sum(1), recv_counts.sum(1)]).to("cpu")  # the layer's one sync
@@ -120,8 +121,13 @@ class ExpertParallelMoE:
         # per sorted row: (local expert id, routing weight bits)
         eid = torch.remainder(idx.view(-1)[order.long()], el).to(torch.int32)
         meta = torch.stack([eid, scales.view(torch.int32)], 1).contiguous()
-        rows = all_to_all_rows(x_sorted, send, recv, self.group)
-        rmeta = all_to_all_rows(meta, send, recv, self.group)
+        rows = torch.empty((sum(recv), x.shape[1]), dtype=x_sorted.dtype, device=x.device)
+        rmeta = torch.empty((sum(recv), 2), dtype=torch.int32, device=x.device)
+        pending = [dist.all_to_all_single(rows, x_sorted, recv, send, group=self.group, async_op=True),
+                   dist.all_to_all_single(rmeta, meta, recv, send, group=self.group, async_op=True)]
+        shared = shared_expert()  # runs while the rows travel
+        for work in pending:
+            work.wait()
         m = rows.shape[0]
         if m > 0:
             ids = rmeta[:, 0].contiguous().view(m, 1)
