@@ -603,6 +603,125 @@ def run_qmm(args, local):
     }))
 
 
+# ---------------------------------------------------------------------------------------------
+# config 5: chunked prefill + decode with a shared prompt prefix (copy-on-write pages), FP8 KV
+# ---------------------------------------------------------------------------------------------
+C5 = dict(prefix=2048, suffix_lo=64, suffix_hi=1024, chunk=512, requests=512, new_tokens=32, step_tokens=8192)
+
+
+def run_prefix_prefill(args, rank, world, local):
+    """The per-GPU share of config 5 (512 requests over 8 GPUs = 64 per GPU unless --seqs says
+    otherwise) through the engine step: the first request prefills the 2048-token prefix, the others
+    take its pages over by reference count when they start, prefill only their own suffix in
+    512-token chunks (a step carries at most 8192 tokens) interleaved with the decode of the
+    requests that are already generating.  Host descriptors in, host tokens out, every step."""
+    import torch
+    import torch.distributed as dist
+
+    from dmlx_b200 import device as dev
+
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    c, w = dict(L8), dict(C5)
+    if args.layers:
+        c["layers"] = c["n_layers"] = args.layers
+    n_req = args.seqs if args.seqs != 64 else w["requests"] // 8
+    rows_cap = w["step_tokens"] + n_req
+    rng = np.random.default_rng(515 + rank)
+    prefix = rng.integers(0, c["vocab"], w["prefix"]).tolist()
+    suffixes = [rng.integers(0, c["vocab"], int(rng.integers(w["suffix_lo"], w["suffix_hi"] + 1))).tolist() for _ in range(n_req)]
+    per_req_pages = -(-(w["suffix_hi"] + w["new_tokens"]) // PAGE) + 2
+    n_pages = w["prefix"] // PAGE + n_req * per_req_pages + 64
+    kv = dev.PagedKVCache(c["n_layers"], c["n_kv_heads"], c["head_dim"], n_pages, n_req,
+                          -(-(w["prefix"] + w["suffix_hi"] + w["new_tokens"]) // PAGE) + 2, c["n_heads"], max_rows=rows_cap,
+                          kv_dtype=dev.KV_FP8_E4M3, attn_scratch_chunks=4 * rows_cap + 1024)
+    model = dev.LlamaModel(c["n_layers"], c["hidden"], c["n_heads"], c["n_kv_heads"], c["head_dim"], c["ffn"], c["vocab"],
+                           max_rows=rows_cap, max_reqs=n_req, max_seqs=n_req, rms_eps=1e-5, rope_theta=500000.0)
+    model.random_init(dev.Q_AFFINE4_G64, seed=7 + rank)
+
+    def scenario(n):
+        kv.reset()
+        eng = dev.Engine(model, kv, max_prefill_tokens=w["chunk"])
+        eng.set_prefix_sharing(True)
+        eng.set_max_step_tokens(w["step_tokens"])
+        eng.submit(1, prefix + suffixes[0], w["new_tokens"])
+        steps = 0
+        for _ in range(w["prefix"] // w["chunk"]):  # the prefix is in the pool before the others arrive
+            eng.step()
+            steps += 1
+        for i in range(1, n):
+            eng.submit(i + 1, prefix + suffixes[i], w["new_tokens"])
+        while eng.active_count() > 0 and steps < 100000:
+            eng.step()
+            steps += 1
+        shared = sum(eng.shared_tokens(i + 1) for i in range(n))
+        gen = sum(len(eng.result(i + 1)[0]) for i in range(n))
+        free = eng.free_pages()
+        eng.close()
+        return steps, shared, gen, free
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    for _ in range(max(1, min(args.warmup, 2))):
+        scenario(min(n_req, 6))  # warm-up: lazy set-up, scratch growth
+    K = max(1, min(args.steps, 3))
+    barrier()
+    l0 = dev.launch_count()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(K):
+        steps, shared, gen, free = scenario(n_req)
+    e1.record()
+    barrier()
+    launches = dev.launch_count() - l0
+    total_ms = e0.elapsed_time(e1)
+    assert kv.error_word() == 0 and dev.qmm_error_word() == 0
+    assert gen == n_req * w["new_tokens"] and free == n_pages, (gen, free)
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    ms = total_ms / K
+    prompt_tokens = sum(w["prefix"] + len(sfx) for sfx in suffixes)
+    computed = prompt_tokens - shared + gen - n_req  # every generated token but each request's first comes from a decode row
+    params = llama_weight_bytes(c) / 0.5625
+    peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    tpeak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+    tflops = 2.0 * params * computed / (ms * 1e-3) / 1e12
+    val = gen * world / (ms * 1e-3)
+    print(json.dumps({
+        "metric": "decode tokens/sec (ragged continuous batch)", "value": val, "unit": "decode tokens/s", "n_gpus": world,
+        "steps": K, "warmup": max(1, min(args.warmup, 2)), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int4 affine g64 weights, bf16 activations, FP8-E4M3 KV, f32 accumulate", "data": "synthetic",
+        "config": {"workload": "prefix_prefill: chunked prefill + decode with a shared prompt prefix", "requests_per_gpu": n_req,
+                   "layers": c["n_layers"], "prefix_tokens": w["prefix"], "suffix_tokens": [w["suffix_lo"], w["suffix_hi"]],
+                   "prefill_chunk": w["chunk"], "step_token_budget": w["step_tokens"], "new_tokens_per_request": w["new_tokens"],
+                   "engine_steps": steps, "prompt_tokens": prompt_tokens, "prompt_tokens_shared": shared,
+                   "tokens_computed": computed, "a_step_is": "one whole scenario (all requests prefilled and decoded)",
+                   "l2": "weights (4.5 GB) are read every engine step", "parallelism": f"dp{world}"},
+        "roofline": {"bound": "tensor", "achieved": tflops, "peak": tpeak, "unit": "TFLOP/s", "frac": tflops / tpeak,
+                     "peak_kind": "of measured (sustained cuBLAS bf16)" if peaks else "of fallback", "traffic": None,
+                     "kernel": "whole scenario: dense flops of the tokens computed over its duration"},
+        "e2e": {"value": val, "unit": "decode tokens/s", "h2d_bytes_per_step": int(4 * (prompt_tokens - shared) + 16 * steps * n_req),
+                "d2h_bytes_per_step": int(4 * gen)},
+        "gpu_launches": int(launches), "clocks": clocks,
+    }))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_reference(args, rank: int):
     """--impl reference: the reference's own algorithm for the path on the host cores.  The
     reference itself (Zig + MLX) cannot be built here, so the timed code is the oracle's C twin."""
@@ -729,7 +848,7 @@ def main():
     ap.add_argument("--seqs", type=int, default=64, help="sequences per GPU (64 = the configuration; fewer for profiling)")
     args = ap.parse_args()
     if args.steps is None:
-        args.steps = 10 if args.impl == "reference" else (50 if args.workload.startswith("llama") else (20 if args.workload.startswith(("moe", "qmm")) else 500))
+        args.steps = 10 if args.impl == "reference" else (50 if args.workload.startswith("llama") else (20 if args.workload.startswith(("moe", "qmm")) else (2 if args.workload.startswith("prefix") else 500)))
     if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
         os.environ["NCCL_DEBUG"] = "WARN"  # the version banner goes to stdout, ahead of the JSON line
     rank = int(os.environ.get("RANK", "0"))
@@ -755,6 +874,9 @@ def main():
     if args.workload.startswith("qmm"):
         if rank == 0:
             run_qmm(args, local)
+        return
+    if args.workload.startswith("prefix"):
+        run_prefix_prefill(args, rank, world, local)
         return
     torch.cuda.set_device(local)
     if world > 1:

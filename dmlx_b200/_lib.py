@@ -215,6 +215,7 @@ _sig("b200_engine_result", i32, vp, u64, P(u32), u64, P(u64), P(i32))
 _sig("b200_engine_forget", None, vp, u64)
 _sig("b200_engine_free_pages", i32, vp)
 _sig("b200_engine_set_prefix_sharing", None, vp, i32)
+_sig("b200_engine_set_max_step_tokens", None, vp, u64)
 _sig("b200_engine_shared_tokens", u64, vp, u64)
 
 

@@ -31,6 +31,7 @@ struct b200_engine {
   // Prefix sharing (paged.BlockManager.findCachedPrefix, src/kvcache/paged.zig:234-265, applied when a
   // request starts its prefill): live sequence slots with the chained hashes of their prompt blocks.
   bool share_prefix = false;
+  uint64_t max_step_tokens = 0;  // 0 = no cap; else prefill chunks beyond the budget wait for a later step
   struct Live { b200_request* req; std::vector<uint64_t> chain; };
   std::unordered_map<int32_t, Live> live;               // by sequence slot
   std::unordered_map<uint64_t, uint64_t> shared_tokens;  // request id -> tokens taken over from a donor
@@ -59,7 +60,8 @@ uint64_t cached_tokens(const b200_request* r) {
 // that a live sequence already holds (same chained hashes, already prefilled): the pages are shared
 // by reference count and the request's prefill cursor starts behind them.  At least one prompt
 // token is always left to compute (its logits give the first output token).
-b200_status try_share_prefix(b200_engine* e, b200_request* r) {
+b200_status try_share_prefix(b200_engine* e, b200_request* r, b200_engine::Live* self, bool* shared) {
+  *shared = false;
   const int32_t slot = b200_request_kv_slot(r);
   std::vector<uint32_t> prompt(b200_request_prompt_len(r));
   b200_request_prompt(r, prompt.data(), prompt.size());
@@ -75,13 +77,14 @@ b200_status try_share_prefix(b200_engine* e, b200_request* r) {
     if (j > best) { best = j; donor = kvp.first; }
   }
   while (best > 0 && best * kPageTokens >= prompt.size()) --best;
-  e->live[slot] = std::move(me);
+  *self = std::move(me);
   if (best == 0) return B200_OK;
   b200_status st = b200_kv_rollback(e->kv, slot, 0);  // give back the page taken at admission
   if (st == B200_OK) st = b200_kv_fork(e->kv, donor, slot, (int32_t)(best * kPageTokens));
   if (st != B200_OK) return st;
   b200_request_force_state(r, B200_REQ_PREFILLING, best * kPageTokens, nullptr, 0);
   e->shared_tokens[b200_request_id(r)] = best * kPageTokens;
+  *shared = true;
   return B200_OK;
 }
 }  // namespace
@@ -128,18 +131,33 @@ b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t ca
   b200_status st = b200_scheduler_schedule(e->sched, e->prefill.data(), &np, e->decode.data(), &nd, active, &need);
   if (st != B200_OK) return st;
   if (np + nd == 0) return B200_OK;
-  if (e->share_prefix) {
+  // Prefill requests take part in this step in scheduler order while the step's token budget lasts
+  // (decode rows always do; at least one prefill chunk is taken so that the loop makes progress).  A
+  // request left out keeps its cursor: postprocess only advances requests it gets an output for.
+  {
+    uint64_t used = nd, kept = 0;
     for (uint64_t i = 0; i < np; ++i) {
       b200_request* r = e->prefill[i];
-      const int32_t slot = b200_request_kv_slot(r);
-      auto it = e->live.find(slot);
-      if (it != e->live.end() && it->second.req == r) continue;  // already running
-      if (b200_request_prefill_offset(r) == 0) {
-        st = try_share_prefix(e, r);
-        if (st != B200_OK) return st;
+      b200_engine::Live self;
+      bool fresh = false, shared = false;
+      if (e->share_prefix) {
+        auto it = e->live.find(b200_request_kv_slot(r));
+        fresh = !(it != e->live.end() && it->second.req == r) && b200_request_prefill_offset(r) == 0;
+        if (fresh) {
+          st = try_share_prefix(e, r, &self, &shared);
+          if (st != B200_OK) return st;
+          if (shared) e->live[b200_request_kv_slot(r)] = self;  // it holds pages now, whether or not it runs this step
+        }
       }
+      const uint64_t len = b200_request_current_prefill_chunk_len(r, e->max_prefill);
+      if (e->max_step_tokens > 0 && used + len > e->max_step_tokens && (kept > 0 || nd > 0)) continue;  // tries again next step
+      if (fresh && !shared) e->live[b200_request_kv_slot(r)] = std::move(self);
+      used += len;
+      e->prefill[kept++] = r;
     }
+    np = kept;
   }
+  if (np + nd == 0) return B200_OK;
   e->descs.clear();
   e->flat.clear();
   for (uint64_t i = 0; i < np; ++i) {  // prefill requests first (src/batch_builder.zig:100-111)
@@ -185,6 +203,7 @@ b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t ca
 }
 
 void b200_engine_set_prefix_sharing(b200_engine* e, int32_t on) { e->share_prefix = on != 0; }
+void b200_engine_set_max_step_tokens(b200_engine* e, uint64_t n) { e->max_step_tokens = n; }
 
 uint64_t b200_engine_shared_tokens(const b200_engine* e, uint64_t id) {
   auto it = e->shared_tokens.find(id);

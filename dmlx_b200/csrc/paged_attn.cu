@@ -1570,7 +1570,8 @@ b200_status b200_paged_attn_prefill_strided(b200_kv* kv, int32_t layer, const vo
     B200_CUDA_TRY(cudaGetDevice(&dev));
     B200_CUDA_TRY(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
-  const int ppc = std::min(std::max(b200_attn_pages_per_chunk, 4), kMaxChunkPages);
+  // prefill batches have rows to spare for parallelism: long chunks keep the split-K partials small
+  const int ppc = total_rows >= 2048 ? kMaxChunkPages : std::min(std::max(b200_attn_pages_per_chunk, 4), kMaxChunkPages);
   const int stride = c.max_rows + 2;
   AttnArgs a;
   a.d = kv->dev; a.layer = layer; a.q = (const __nv_bfloat16*)d_q; a.q_stride = q_stride; a.row_seq = d_row_seq; a.row_ctx = d_row_ctx;

@@ -582,7 +582,7 @@ __global__ void __launch_bounds__(kTcaThreads, 2) qmm_tca_kernel(const __grid_co
     if (ok && warp < 4) {
       ptx::tc_fence_after_sync();
       const int n = nt * kTileN + warp * 32 + lane;
-      const bool direct = gridDim.y == 1 && tn <= 64;
+      const bool direct = gridDim.y == 1 && (tn <= 64 || a.direct_large);
       const size_t n_pad = a.items ? (size_t)a.nt * kTileN : (size_t)kTileN;
       float* wsp = a.items ? a.ws + ((size_t)split * a.rows + t0) * n_pad + n
                            : a.ws + (((size_t)(nt * gridDim.z + blockIdx.z) * gridDim.y + split) * tn) * kTileN + warp * 32 + lane;
@@ -1281,7 +1281,11 @@ static b200_status launch_tca(QmmArgs& a, int rows, cudaStream_t s) {
   const int splits0 = a.items ? 1 : pick_splits(tiles, a.kc, g_sms, ctas_per_sm, 12);
   a.chunks_per_split = (a.kc + splits0 - 1) / splits0;
   const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
-  st = ensure_state((size_t)splits * (a.items ? (size_t)rows : (size_t)tts * tn) * a.nt * kTileN * sizeof(float));
+  // Prefill-sized batches (several token tiles, one K split) would need rows x N x 4 bytes of scratch:
+  // the kernel writes its output itself instead.
+  a.direct_large = (!a.items && splits == 1 && tts >= 4) ? 1 : 0;
+  const bool direct = splits == 1 && (tn <= 64 || a.direct_large);
+  st = ensure_state(direct ? 0 : (size_t)splits * (a.items ? (size_t)rows : (size_t)tts * tn) * a.nt * kTileN * sizeof(float));
   if (st != B200_OK) return st;
   a.ws = g_ws; a.err = g_err;
   CUtensorMap xmap;
@@ -1290,7 +1294,7 @@ static b200_status launch_tca(QmmArgs& a, int rows, cudaStream_t s) {
   a.x_row0 = 0;
   qmm_tca_kernel<MODE><<<dim3(a.nt, splits, a.items ? a.max_items : tts), kTcaThreads, smem, s>>>(xmap, a);
   B200_LAUNCH_CHECK();
-  return (splits == 1 && tn <= 64) ? B200_OK : launch_finish(a, splits, s);
+  return direct ? B200_OK : launch_finish(a, splits, s);
 }
 
 // Large batches (129..256 rows per token tile): two weight tiles per CTA.

@@ -519,5 +519,8 @@ class Engine:
     def set_prefix_sharing(self, on: bool = True):
         lib.b200_engine_set_prefix_sharing(self._h, int(on))
 
+    def set_max_step_tokens(self, n: int):
+        lib.b200_engine_set_max_step_tokens(self._h, int(n))
+
     def shared_tokens(self, rid: int) -> int:
         return int(lib.b200_engine_shared_tokens(self._h, rid))

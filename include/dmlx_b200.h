@@ -395,6 +395,9 @@ int32_t b200_engine_free_pages(const b200_engine* e);
  * already prefilled (findCachedPrefix, src/kvcache/paged.zig:234-265); its own appends copy a shared
  * page on write (:167-206).  shared_tokens reports how many prompt tokens a request took over. */
 void b200_engine_set_prefix_sharing(b200_engine* e, int32_t on);
+/* Cap on the tokens of one step (0 = none, as in the reference scheduler, which sends a chunk of every
+ * prefilling request): prefill chunks beyond the budget wait for a later step; decode rows always run. */
+void b200_engine_set_max_step_tokens(b200_engine* e, uint64_t n);
 uint64_t b200_engine_shared_tokens(const b200_engine* e, uint64_t id);
 
 /* ---- mixture of experts ------------------------------------------------------------------------ */
