@@ -142,3 +142,39 @@ def test_prefix_sharing_through_engine():
     eng.close()
     model.close()
     kv.close()
+
+
+def test_step_token_budget_defers_prefill_chunks():
+    """b200_engine_set_max_step_tokens: with a budget smaller than the prompts waiting, prefill chunks
+    queue up over several steps (a request left out of a step keeps its cursor,
+    src/scheduler.zig:335-349 advances only requests it gets an output for); decode rows never wait.
+    Results still equal the oracle, every page comes back."""
+    from dmlx_b200 import device as dev
+
+    cfg = CFG
+    weights = ref_math.random_llama_weights(cfg, seed=2026)
+    model = _build_model(dev, cfg, weights)
+    kv = dev.PagedKVCache(cfg.n_layers, cfg.n_kv_heads, cfg.head_dim, 64, 16, 16, cfg.n_heads, max_rows=1024,
+                          attn_scratch_chunks=8192)
+    eng = dev.Engine(model, kv, max_prefill_tokens=64)
+    eng.set_max_step_tokens(100)
+    rng = np.random.default_rng(77)
+    prompts = [rng.integers(0, cfg.vocab, n).tolist() for n in (150, 40, 90, 64, 200)]
+    for i, p in enumerate(prompts):
+        eng.submit(i + 1, p, 10)
+    steps, max_rows_seen = 0, 0
+    while eng.active_count() > 0 and steps < 300:
+        eng.step()
+        steps += 1
+    assert eng.active_count() == 0 and kv.error_word() == 0 and eng.free_pages() == 64
+    # 544 prompt tokens at <= 100 per step cannot finish in fewer steps than this
+    assert steps >= 6 + 9
+    exact = 0
+    for i, p in enumerate(prompts):
+        got, done = eng.result(i + 1)
+        assert done and len(got) == 10
+        exact += _check_against_oracle(cfg, weights, p, got, i)
+    assert exact >= 1
+    eng.close()
+    model.close()
+    kv.close()
