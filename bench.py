@@ -849,8 +849,6 @@ def main():
     args = ap.parse_args()
     if args.steps is None:
         args.steps = 10 if args.impl == "reference" else (50 if args.workload.startswith("llama") else (20 if args.workload.startswith(("moe", "qmm")) else (2 if args.workload.startswith("prefix") else 500)))
-    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
-        os.environ["NCCL_DEBUG"] = "WARN"  # the version banner goes to stdout, ahead of the JSON line
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
