@@ -32,6 +32,11 @@ class TokenOutput(C.Structure):
     _fields_ = [("request_id", u64), ("token", u32), ("_pad", u32)]
 
 
+class SampleParams(C.Structure):
+    _fields_ = [("temperature", f32), ("top_p", f32), ("repetition_penalty", f32), ("uniform", f32), ("top_k", i32),
+                ("_pad", i32)]
+
+
 class KvConfig(C.Structure):
     _fields_ = [(n, i32) for n in (
         "n_layers", "n_kv_heads", "head_dim", "page_size", "n_pages", "max_seqs", "max_pages_per_seq",
@@ -148,6 +153,8 @@ _sig("b200_kv_ref_counts", i32, vp, P(i32), i32)
 _sig("b200_kv_error_word", i32, vp, P(i32))
 _sig("b200_kv_gather", i32, vp, i32, i32, vp, vp, i32, vp)
 _sig("b200_kv_page_raw", i32, vp, i32, i32, vp, vp, P(f32), P(f32))
+_sig("b200_kv_page_load", i32, vp, i32, i32, vp, vp, P(f32), P(f32))
+_sig("b200_kv_set_len", i32, vp, i32, i32)
 _sig("b200_paged_attn_decode", i32, vp, i32, vp, vp, vp, i32, vp, vp)
 _sig("b200_paged_attn_prefill", i32, vp, i32, vp, vp, vp, i32, vp, vp)
 _sig("b200_set_attn_pages_per_chunk", None, i32)
@@ -156,6 +163,10 @@ _sig("b200_rmsnorm", i32, vp, vp, vp, i32, i32, f32, vp)
 _sig("b200_rope", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp)
 _sig("b200_embed_gather", i32, vp, vp, vp, i32, i32, vp)
 _sig("b200_argmax", i32, vp, i32, i32, vp, vp)
+_sig("b200_sample_rows", i32, vp, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp)
+_sig("b200_prng_seed", None, u64, P(u64))
+_sig("b200_prng_next_u64", u64, P(u64))
+_sig("b200_prng_next_f32", f32, P(u64))
 _sig("b200_qweight_create", i32, i32, i32, i32, i32, vp, vp, vp, P(vp))
 _sig("b200_qweight_random", i32, i32, i32, i32, i32, u32, P(vp))
 _sig("b200_qweight_destroy", None, vp)
@@ -180,6 +191,8 @@ _sig("b200_llama_step", i32, vp, vp, vp, i32, vp, i32, vp, P(i32), vp)
 _sig("b200_llama_forward", i32, vp, vp, vp, i32, i32, vp, vp)
 _sig("b200_llama_device_buffers", None, vp, P(vp), P(vp), P(vp))
 _sig("b200_llama_last_logits", i32, vp, vp, i32)
+_sig("b200_llama_set_samplers", i32, vp, P(SampleParams), i32)
+_sig("b200_llama_last_logprobs", i32, vp, P(f32), i32)
 _sig("b200_llama_launch_count", C.c_int64, vp)
 _sig("b200_launch_count", C.c_int64)
 _sig("b200_set_qmm_grouped_tmem_a", None, i32)
@@ -215,6 +228,7 @@ _sig("b200_engine_result", i32, vp, u64, P(u32), u64, P(u64), P(i32))
 _sig("b200_engine_forget", None, vp, u64)
 _sig("b200_engine_free_pages", i32, vp)
 _sig("b200_engine_set_prefix_sharing", None, vp, i32)
+_sig("b200_engine_set_sampler", i32, vp, u64, f32, i32, f32, u64)
 _sig("b200_engine_set_max_step_tokens", None, vp, u64)
 _sig("b200_engine_shared_tokens", u64, vp, u64)
 

@@ -35,6 +35,10 @@ struct b200_engine {
   struct Live { b200_request* req; std::vector<uint64_t> chain; };
   std::unordered_map<int32_t, Live> live;               // by sequence slot
   std::unordered_map<uint64_t, uint64_t> shared_tokens;  // request id -> tokens taken over from a donor
+  // Per-request samplers (SamplerConfig, src/sampling.zig:277-296); requests without one are greedy.
+  struct Sampler { float temperature; int32_t top_k; float top_p; uint64_t prng[4]; };
+  std::unordered_map<uint64_t, Sampler> samplers;
+  std::vector<b200_sample_params> samp_rows;
 };
 
 namespace {
@@ -175,6 +179,27 @@ b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t ca
     e->descs.push_back(b200_pack_desc{b200_request_kv_slot(r), 1, (int32_t)(b200_request_seq_len(r) - 1), -1});
   }
   e->next.resize(e->descs.size());
+  if (!e->samplers.empty()) {
+    // One uniform variate per token that will join a request's output (decode rows and last prefill
+    // chunks); the other rows' tokens are dropped, so they stay greedy and draw nothing.
+    e->samp_rows.assign(e->descs.size(), b200_sample_params{0.f, 1.f, 1.f, 0.f, 0, 0});
+    bool any = false;
+    for (uint64_t i = 0; i < np + nd; ++i) {
+      b200_request* r = i < np ? e->prefill[i] : e->decode[i - np];
+      auto it = e->samplers.find(b200_request_id(r));
+      if (it == e->samplers.end() || !(it->second.temperature > 0.f)) continue;
+      const bool counts = i >= np || b200_request_prefill_offset(r) + b200_request_current_prefill_chunk_len(r, e->max_prefill) >=
+                                         b200_request_prompt_len(r);
+      if (!counts) continue;
+      auto& sp = it->second;
+      e->samp_rows[i] = b200_sample_params{sp.temperature, sp.top_p, 1.f, b200_prng_next_f32(sp.prng), sp.top_k, 0};
+      any = true;
+    }
+    if (any) {
+      st = b200_llama_set_samplers(e->model, e->samp_rows.data(), (int32_t)e->samp_rows.size());
+      if (st != B200_OK) return st;
+    }
+  }
   st = b200_llama_step(e->model, e->kv, e->descs.data(), (int32_t)e->descs.size(), e->flat.data(), (int32_t)e->flat.size(),
                        e->next.data(), &e->last_free_pages, stream);
   if (st != B200_OK) return st;
@@ -202,6 +227,14 @@ b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t ca
   return st;
 }
 
+b200_status b200_engine_set_sampler(b200_engine* e, uint64_t id, float temperature, int32_t top_k, float top_p, uint64_t seed) {
+  if (!e->requests.count(id)) { b200_set_error("engine: unknown request %llu", (unsigned long long)id); return B200_ERR_INVALID_ARGUMENT; }
+  b200_engine::Sampler sp{temperature, top_k, top_p, {0, 0, 0, 0}};
+  b200_prng_seed(seed, sp.prng);
+  e->samplers[id] = sp;
+  return B200_OK;
+}
+
 void b200_engine_set_prefix_sharing(b200_engine* e, int32_t on) { e->share_prefix = on != 0; }
 void b200_engine_set_max_step_tokens(b200_engine* e, uint64_t n) { e->max_step_tokens = n; }
 
@@ -225,6 +258,7 @@ void b200_engine_forget(b200_engine* e, uint64_t id) {
   if (it == e->requests.end() || b200_request_state(it->second) != B200_REQ_DONE) return;
   b200_request_destroy(it->second);
   e->requests.erase(it);
+  e->samplers.erase(id);
 }
 
 int32_t b200_engine_free_pages(const b200_engine* e) { return (int32_t)b200_sched_bm_free_count(e->bm); }

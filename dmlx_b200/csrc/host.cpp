@@ -176,6 +176,46 @@ uint64_t b200_hash_block(uint64_t prev_hash, const uint32_t* token_ids, uint64_t
   return fnv1a64(prev_hash, token_ids, n);
 }
 
+// The generator behind SamplerConfig.prng (src/sampling.zig:284-296): Zig's std.Random.DefaultPrng,
+// i.e. xoshiro256++ with its four state words drawn from SplitMix64(seed).
+void b200_prng_seed(uint64_t seed, uint64_t state[4]) {
+  uint64_t sm = seed;
+  for (int i = 0; i < 4; ++i) {
+    sm += 0x9E3779B97F4A7C15ull;
+    uint64_t z = sm;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    state[i] = z ^ (z >> 31);
+  }
+}
+uint64_t b200_prng_next_u64(uint64_t s[4]) {
+  auto rotl = [](uint64_t x, int k) { return (x << k) | (x >> (64 - k)); };
+  const uint64_t r = rotl(s[0] + s[3], 23) + s[0];
+  const uint64_t t = s[1] << 17;
+  s[2] ^= s[0];
+  s[3] ^= s[1];
+  s[1] ^= s[2];
+  s[0] ^= s[3];
+  s[2] ^= t;
+  s[3] = rotl(s[3], 45);
+  return r;
+}
+// Random.float(f32): the low 23 bits are the mantissa, the number of leading zeros of the 64-bit draw
+// lowers the exponent from 2^-1, with more draws when the top 41 bits are all zero.
+float b200_prng_next_f32(uint64_t s[4]) {
+  auto clz64 = [](uint64_t x) { return x == 0 ? 64u : (uint32_t)__builtin_clzll(x); };
+  const uint64_t r = b200_prng_next_u64(s);
+  uint32_t lz = clz64(r);
+  if (lz >= 41) {
+    lz = 41 + clz64(b200_prng_next_u64(s));
+    if (lz == 41 + 64) lz += (uint32_t)__builtin_clz((uint32_t)b200_prng_next_u64(s) | 0x7FFu);
+  }
+  const uint32_t bits = ((126u - lz) << 23) | (uint32_t)(r & 0x7FFFFFu);
+  float f;
+  std::memcpy(&f, &bits, 4);
+  return f;
+}
+
 b200_status b200_bm_find_cached_prefix(b200_block_manager* bm, const uint32_t* token_ids, uint64_t n_tokens,
                                        uint64_t block_size, uint64_t* out_ids, uint64_t cap, uint64_t* out_n) {
   *out_n = 0;

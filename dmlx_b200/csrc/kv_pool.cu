@@ -405,7 +405,7 @@ __global__ void gather_kernel(KvDev d, int layer, int seq, __nv_bfloat16* k_out,
 }
 
 // ---- administrative operations: one thread, sequential semantics --------------------------------
-enum { OP_ALLOC = 0, OP_RELEASE = 1, OP_FORK = 2, OP_ROLLBACK = 3, OP_SET_FREE = 4 };
+enum { OP_ALLOC = 0, OP_RELEASE = 1, OP_FORK = 2, OP_ROLLBACK = 3, OP_SET_FREE = 4, OP_SET_LEN = 5 };
 
 __device__ void release_page(KvDev& d, int page) {
   if (d.ref_count[page] > 1) {
@@ -466,6 +466,18 @@ __global__ void admin_kernel(KvDev d, int op, int a0, int a1, int a2, const int*
       int need = (a1 + d.page_size - 1) / d.page_size;
       while (d.seq_pages[s] > need) release_page(d, d.block_table[(size_t)s * d.max_pages_per_seq + --d.seq_pages[s]]);
       if (d.seq_len[s] > a1) d.seq_len[s] = a1;
+      break;
+    }
+    case OP_SET_LEN: {  // a0 = seq, a1 = tokens now held by the sequence's pages (restored from outside)
+      int s = a0, n = a1;
+      if (s < 0 || s >= d.max_seqs) { out[0] = B200_ERR_INVALID_BATCH_INDEX; return; }
+      if (n < 0 || (n + d.page_size - 1) / d.page_size > d.seq_pages[s]) { out[0] = B200_ERR_INVALID_ARGUMENT; return; }
+      d.seq_len[s] = n;
+      for (int p = 0; p < d.seq_pages[s]; ++p) {
+        int page = d.block_table[(size_t)s * d.max_pages_per_seq + p];
+        int used = n - p * d.page_size;
+        d.tokens_used[page] = used < 0 ? 0 : (used > d.page_size ? d.page_size : used);
+      }
       break;
     }
     case OP_SET_FREE: {  // a0 = n ids in list, popped list[0] first; only on an untouched pool
@@ -628,6 +640,9 @@ b200_status b200_kv_release(b200_kv* kv, const int32_t* seqs, int32_t n) {
 b200_status b200_kv_fork(b200_kv* kv, int32_t src, int32_t dst, int32_t n_tokens) {
   return run_admin(kv, OP_FORK, src, dst, n_tokens, nullptr, 0, nullptr, 0);
 }
+b200_status b200_kv_set_len(b200_kv* kv, int32_t seq, int32_t n_tokens) {
+  return run_admin(kv, OP_SET_LEN, seq, n_tokens, 0, nullptr, 0, nullptr, 0);
+}
 b200_status b200_kv_rollback(b200_kv* kv, int32_t seq, int32_t to_len) {
   return run_admin(kv, OP_ROLLBACK, seq, to_len, 0, nullptr, 0, nullptr, 0);
 }
@@ -758,6 +773,26 @@ b200_status b200_kv_gather(b200_kv* kv, int32_t layer, int32_t seq, void* d_k_ou
   gather_kernel<<<296, 256, 0, (cudaStream_t)stream>>>(kv->dev, layer, seq, (__nv_bfloat16*)d_k_out,
                                                        (__nv_bfloat16*)d_v_out, cap_rows);
   B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+b200_status b200_kv_page_load(b200_kv* kv, int32_t layer, int32_t page, const void* h_k, const void* h_v,
+                              const float* h_k_scales, const float* h_v_scales) {
+  if (layer < 0 || layer >= kv->cfg.n_layers || page < 0 || page >= kv->cfg.n_pages) {
+    b200_set_error("page_load: layer/page out of range");
+    return B200_ERR_INVALID_BLOCK_ID;
+  }
+  const KvDev& d = kv->dev;
+  if (d.elem_bytes == 1 && (!h_k_scales || !h_v_scales)) { b200_set_error("page_load: FP8 pages need their scales"); return B200_ERR_INVALID_ARGUMENT; }
+  size_t page_bytes = (size_t)d.n_kv_heads * d.page_size * d.head_dim * d.elem_bytes;
+  size_t off = ((size_t)layer * d.n_pages + page) * page_bytes;
+  B200_CUDA_TRY(cudaMemcpy((char*)d.k_pool + off, h_k, page_bytes, cudaMemcpyHostToDevice));
+  B200_CUDA_TRY(cudaMemcpy((char*)d.v_pool + off, h_v, page_bytes, cudaMemcpyHostToDevice));
+  if (d.elem_bytes == 1) {
+    size_t so = ((size_t)layer * d.n_pages + page) * d.n_kv_heads;
+    B200_CUDA_TRY(cudaMemcpy(d.k_scale + so, h_k_scales, sizeof(float) * d.n_kv_heads, cudaMemcpyHostToDevice));
+    B200_CUDA_TRY(cudaMemcpy(d.v_scale + so, h_v_scales, sizeof(float) * d.n_kv_heads, cudaMemcpyHostToDevice));
+  }
   return B200_OK;
 }
 

@@ -51,6 +51,11 @@ struct b200_llama {
   b200_pack_desc* h_desc = nullptr;
   uint32_t *h_prefill = nullptr, *h_next = nullptr;
   int32_t* h_state = nullptr;  // [8] pool state words + [1] matmul error word
+  // per-request sampler rows of the coming step (set by b200_llama_set_samplers, used once)
+  b200_sample_params *d_samp = nullptr, *h_samp = nullptr;
+  float* d_logprobs = nullptr;
+  int samp_n = 0;
+  bool sampling = false;  // the step in flight samples with d_samp instead of taking the argmax
   int last_n_req = 0;
   long long launches = 0;  // kernels launched by forward calls so far
   // CUDA graphs of decode-only steps, keyed by (requests, device descriptor pointer, stream): the
@@ -58,7 +63,7 @@ struct b200_llama {
   // later ones replay the graph.
   bool graphs_on = true;
   struct GraphEntry { int seen = 0; cudaGraphExec_t exec = nullptr; long long kernels = 0; };
-  std::map<std::tuple<int, const void*, const void*, void*>, GraphEntry> graphs;
+  std::map<std::tuple<int, const void*, const void*, void*, bool>, GraphEntry> graphs;
   // optional CUDA-event timing per category: 0 attention, 1 matmuls, 2 rope + KV append, 3 the rest
   bool prof_on = false;
   std::vector<cudaEvent_t> prof_events;  // pairs
@@ -133,10 +138,13 @@ b200_status b200_llama_create(const b200_llama_config* c, b200_llama** out) {
   L_ALLOC(m->d_row_seq, sizeof(int32_t) * R);
   L_ALLOC(m->d_row_ctx, sizeof(int32_t) * R);
   L_ALLOC(m->d_last_row, sizeof(int32_t) * Q);
+  L_ALLOC(m->d_samp, sizeof(b200_sample_params) * Q);
+  L_ALLOC(m->d_logprobs, sizeof(float) * Q);
   cudaMemset(m->d_last_token, 0, sizeof(uint32_t) * c->max_seqs);
   if (cudaMallocHost((void**)&m->h_desc, sizeof(b200_pack_desc) * Q) != cudaSuccess ||
       cudaMallocHost((void**)&m->h_prefill, sizeof(uint32_t) * R) != cudaSuccess ||
       cudaMallocHost((void**)&m->h_next, sizeof(uint32_t) * Q) != cudaSuccess ||
+      cudaMallocHost((void**)&m->h_samp, sizeof(b200_sample_params) * Q) != cudaSuccess ||
       cudaMallocHost((void**)&m->h_state, sizeof(int32_t) * 16) != cudaSuccess) {
     b200_set_error("pinned host allocation failed");
     b200_llama_destroy(m);
@@ -150,7 +158,7 @@ void b200_llama_destroy(b200_llama* m) {
   if (!m) return;
   void* dev[] = {m->embed, m->final_norm, m->x, m->h, m->qkv, m->attn, m->act, m->last_h, m->last_hn, m->logits, m->d_desc,
                  m->d_prefill, m->d_tokens, m->d_next, m->d_last_token, m->d_cu, m->d_pos, m->d_row_to_req, m->d_row_seq,
-                 m->d_row_ctx, m->d_last_row};
+                 m->d_row_ctx, m->d_last_row, m->d_samp, m->d_logprobs};
   for (void* p : dev) if (p) cudaFree(p);
   for (auto* p : m->attn_norm) if (p) cudaFree(p);
   for (auto* p : m->ffn_norm) if (p) cudaFree(p);
@@ -162,6 +170,7 @@ void b200_llama_destroy(b200_llama* m) {
   if (m->h_desc) cudaFreeHost(m->h_desc);
   if (m->h_prefill) cudaFreeHost(m->h_prefill);
   if (m->h_next) cudaFreeHost(m->h_next);
+  if (m->h_samp) cudaFreeHost(m->h_samp);
   if (m->h_state) cudaFreeHost(m->h_state);
   for (cudaEvent_t e : m->prof_events) cudaEventDestroy(e);
   for (auto& g : m->graphs) if (g.second.exec) cudaGraphExecDestroy(g.second.exec);
@@ -301,7 +310,7 @@ b200_status b200_llama_forward(b200_llama* m, b200_kv* kv, const b200_pack_desc*
   // (the legacy default stream cannot be captured)
   if (!m->graphs_on || m->prof_on || total_rows != n_req || n_req <= 0 || !m->finalized || stream == nullptr)
     return llama_forward_eager(m, kv, d_desc, n_req, total_rows, d_prefill_tokens, stream);
-  auto& ge = m->graphs[std::make_tuple((int)n_req, (const void*)d_desc, (const void*)kv, stream)];
+  auto& ge = m->graphs[std::make_tuple((int)n_req, (const void*)d_desc, (const void*)kv, stream, m->sampling)];
   ge.seen += 1;
   if (ge.seen == 1) return llama_forward_eager(m, kv, d_desc, n_req, total_rows, d_prefill_tokens, stream);
   cudaStream_t cs = (cudaStream_t)stream;
@@ -369,7 +378,11 @@ static b200_status llama_forward_eager(b200_llama* m, b200_kv* kv, const b200_pa
   STEP(b200_gather_rows(m->x, m->d_last_row, m->last_h, n_req, c.hidden, stream));
   STEP(b200_rmsnorm(m->last_h, m->final_norm, m->last_hn, n_req, c.hidden, c.rms_eps, stream));
   STEP_CAT(1, b200_qmm(m->lm_head, m->last_hn, n_req, m->logits, B200_EPI_NONE, nullptr, 0.f, B200_QMM_AUTO, stream));
-  STEP(b200_argmax(m->logits, n_req, c.vocab, m->d_next, stream));
+  if (m->sampling) {
+    STEP(b200_sample_rows(m->logits, 0, n_req, c.vocab, m->d_samp, nullptr, nullptr, nullptr, m->d_next, m->d_logprobs, stream));
+  } else {
+    STEP(b200_argmax(m->logits, n_req, c.vocab, m->d_next, stream));
+  }
   STEP(b200_scatter_tokens(m->d_next, d_desc, m->d_last_token, n_req, stream));
 #undef STEP
 #undef STEP_CAT
@@ -396,7 +409,19 @@ b200_status b200_llama_step(b200_llama* m, b200_kv* kv, const b200_pack_desc* h_
   if (n_req > 0) B200_CUDA_TRY(cudaMemcpyAsync(m->d_desc, m->h_desc, sizeof(b200_pack_desc) * n_req, cudaMemcpyHostToDevice, s));
   if (n_prefill_tokens > 0)
     B200_CUDA_TRY(cudaMemcpyAsync(m->d_prefill, m->h_prefill, sizeof(uint32_t) * n_prefill_tokens, cudaMemcpyHostToDevice, s));
+  m->sampling = m->samp_n > 0;
+  if (m->sampling) {
+    if (m->samp_n != n_req) {
+      b200_set_error("llama step: %d sampler rows for %d requests", m->samp_n, n_req);
+      m->samp_n = 0;
+      m->sampling = false;
+      return B200_ERR_INVALID_ARGUMENT;
+    }
+    B200_CUDA_TRY(cudaMemcpyAsync(m->d_samp, m->h_samp, sizeof(b200_sample_params) * n_req, cudaMemcpyHostToDevice, s));
+  }
+  m->samp_n = 0;
   b200_status st = b200_llama_forward(m, kv, m->d_desc, n_req, (int)total, m->d_prefill, stream);
+  m->sampling = false;
   if (st != B200_OK) return st;
   if (n_req > 0) B200_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(uint32_t) * n_req, cudaMemcpyDeviceToHost, s));
   B200_CUDA_TRY(cudaMemcpyAsync(m->h_state, kv->dev.state, sizeof(int32_t) * 8, cudaMemcpyDeviceToHost, s));
@@ -414,6 +439,22 @@ b200_status b200_llama_step(b200_llama* m, b200_kv* kv, const b200_pack_desc* h_
     b200_set_error("llama step: a kernel flagged %s", b200_status_name(code));
     return code;
   }
+  return B200_OK;
+}
+
+b200_status b200_llama_set_samplers(b200_llama* m, const b200_sample_params* h_rows, int32_t n_req) {
+  if (n_req < 0 || n_req > m->cfg.max_reqs || (n_req > 0 && h_rows == nullptr)) {
+    b200_set_error("set_samplers: %d rows (the model holds %d requests)", n_req, m->cfg.max_reqs);
+    return B200_ERR_INVALID_ARGUMENT;
+  }
+  for (int i = 0; i < n_req; ++i) m->h_samp[i] = h_rows[i];
+  m->samp_n = n_req;
+  return B200_OK;
+}
+
+b200_status b200_llama_last_logprobs(b200_llama* m, float* h_out, int32_t n_req) {
+  if (n_req > m->last_n_req) { b200_set_error("last_logprobs: %d rows requested, last step had %d", n_req, m->last_n_req); return B200_ERR_CAPACITY; }
+  if (n_req > 0) B200_CUDA_TRY(cudaMemcpy(h_out, m->d_logprobs, sizeof(float) * n_req, cudaMemcpyDeviceToHost));
   return B200_OK;
 }
 

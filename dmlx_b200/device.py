@@ -186,6 +186,17 @@ class PagedKVCache:
             return k.view(np.uint16).reshape(shape), v.view(np.uint16).reshape(shape), ks, vs
         return k.reshape(shape), v.reshape(shape), ks, vs
 
+    def page_load(self, layer: int, page: int, k: np.ndarray, v: np.ndarray, k_scales=None, v_scales=None):
+        """Inverse of page_raw: host page bytes (and, for FP8 pools, per-head scales) into the pool."""
+        k, v = np.ascontiguousarray(k), np.ascontiguousarray(v)
+        fp = lambda a: None if a is None else np.ascontiguousarray(a, np.float32)
+        ks, vs = fp(k_scales), fp(v_scales)
+        pf = lambda a: None if a is None else a.ctypes.data_as(C.POINTER(C.c_float))
+        _lib.check(lib.b200_kv_page_load(self._h, layer, page, k.ctypes.data, v.ctypes.data, pf(ks), pf(vs)))
+
+    def set_len(self, seq: int, n_tokens: int):
+        _lib.check(lib.b200_kv_set_len(self._h, seq, n_tokens))
+
 
 def set_attn_pages_per_chunk(n: int):
     lib.b200_set_attn_pages_per_chunk(n)
@@ -232,6 +243,37 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     out = out if out is not None else torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
     _lib.check(lib.b200_argmax(_ptr(logits), logits.shape[0], logits.shape[1], _ptr(out), _stream()))
     return out
+
+
+def sample_params_array(rows) -> np.ndarray:
+    """rows of (temperature, top_k, top_p, uniform[, repetition_penalty]) -> the 24-byte records of
+    b200_sample_params as a [n, 6] float32 array (top_k stored by its bits)."""
+    out = np.zeros((len(rows), 6), np.float32)
+    for i, r in enumerate(rows):
+        out[i, 0], out[i, 1], out[i, 3] = r[0], r[2], r[3]
+        out[i, 2] = r[4] if len(r) > 4 else 1.0
+    out.view(np.int32)[:, 4] = [int(r[1]) for r in rows]
+    return out
+
+
+def sample_rows(logits: torch.Tensor, rows, context: Optional[Sequence[Sequence[int]]] = None, logprobs: bool = True):
+    """SamplerConfig.sample per row (src/sampling.zig:298-322) on bf16 or f32 logits [R, V].
+    Returns (tokens int32 [R], logprobs float32 [R] or None)."""
+    assert logits.dtype in (torch.bfloat16, torch.float32) and logits.is_contiguous()
+    n, v = logits.shape
+    d_params = torch.from_numpy(sample_params_array(rows)).to(logits.device)
+    tokens = torch.empty(n, dtype=torch.int32, device=logits.device)
+    lp = torch.empty(n, dtype=torch.float32, device=logits.device) if logprobs else None
+    d_ctx = d_off = scratch = None
+    if context is not None:
+        flat = [int(t) for c in context for t in c]
+        offs = np.concatenate([[0], np.cumsum([len(c) for c in context])]).astype(np.int32)
+        d_ctx = torch.tensor(flat + [0], dtype=torch.int64).to(torch.int32).to(logits.device)
+        d_off = torch.from_numpy(offs).to(logits.device)
+        scratch = torch.empty((n, v), dtype=torch.float32, device=logits.device)
+    _lib.check(lib.b200_sample_rows(_ptr(logits), int(logits.dtype == torch.float32), n, v, _ptr(d_params), _ptr(d_ctx),
+                                    _ptr(d_off), _ptr(scratch), _ptr(tokens), _ptr(lp), _stream()))
+    return tokens, lp
 
 
 class QWeight:
@@ -342,6 +384,16 @@ class LlamaModel:
         """b200_llama_forward on device-resident descriptors (asynchronous)."""
         _lib.check(lib.b200_llama_forward(self._h, kv._h, _ptr(d_desc), d_desc.shape[0], total_rows, _ptr(d_prefill),
                                           _stream()))
+
+    def set_samplers(self, rows):
+        """Sampler rows (temperature, top_k, top_p, uniform) for the requests of the next step()."""
+        arr = sample_params_array(rows)
+        _lib.check(lib.b200_llama_set_samplers(self._h, arr.ctypes.data_as(C.POINTER(_lib.SampleParams)), len(rows)))
+
+    def last_logprobs(self, n_req: int) -> np.ndarray:
+        out = np.zeros(n_req, np.float32)
+        _lib.check(lib.b200_llama_last_logprobs(self._h, out.ctypes.data_as(C.POINTER(C.c_float)), n_req))
+        return out
 
     def last_logits(self, n_req: int) -> np.ndarray:
         out = np.zeros((n_req, self.cfg.vocab), np.uint16)
@@ -515,6 +567,9 @@ class Engine:
 
     def free_pages(self) -> int:
         return int(lib.b200_engine_free_pages(self._h))
+
+    def set_sampler(self, rid: int, temperature: float, top_k: int = 50, top_p: float = 1.0, seed: int = 0):
+        _lib.check(lib.b200_engine_set_sampler(self._h, rid, temperature, top_k, top_p, seed))
 
     def set_prefix_sharing(self, on: bool = True):
         lib.b200_engine_set_prefix_sharing(self._h, int(on))

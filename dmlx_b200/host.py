@@ -29,6 +29,24 @@ def hash_block(prev_hash: int, token_ids: Sequence[int]) -> int:
     return int(lib.b200_hash_block(int(prev_hash) & 0xFFFFFFFFFFFFFFFF, arr, n))
 
 
+class Prng:
+    """std.Random.DefaultPrng as SamplerConfig.init(seed) creates it (src/sampling.zig:287-296)."""
+
+    def __init__(self, seed: int):
+        self._s = (C.c_uint64 * 4)()
+        lib.b200_prng_seed(int(seed) & 0xFFFFFFFFFFFFFFFF, self._s)
+
+    def set_state(self, words: Sequence[int]):
+        for i in range(4):
+            self._s[i] = int(words[i])
+
+    def next_u64(self) -> int:
+        return int(lib.b200_prng_next_u64(self._s))
+
+    def next_f32(self) -> float:
+        return float(lib.b200_prng_next_f32(self._s))
+
+
 class PagedBlockManager:
     """paged.BlockManager (src/kvcache/paged.zig:44-273)."""
 

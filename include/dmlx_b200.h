@@ -241,6 +241,12 @@ b200_status b200_kv_gather(b200_kv* kv, int32_t layer, int32_t seq, void* d_k_ou
 /* Raw E4M3 codes and scales of one page (FP8 pools; bit-exact checks). */
 b200_status b200_kv_page_raw(b200_kv* kv, int32_t layer, int32_t page, void* h_k, void* h_v,
                              float* h_k_scales, float* h_v_scales);
+/* Restoring pages saved elsewhere (PrefixDiskCache.loadBlock / restorePrefix,
+ * src/kvcache/prefix_disk.zig:177-293): write one layer of a page from host memory (the inverse of
+ * b200_kv_page_raw), and declare that the pages a slot holds (b200_kv_alloc) now carry n_tokens. */
+b200_status b200_kv_page_load(b200_kv* kv, int32_t layer, int32_t page, const void* h_k,
+                              const void* h_v, const float* h_k_scales, const float* h_v_scales);
+b200_status b200_kv_set_len(b200_kv* kv, int32_t seq, int32_t n_tokens);
 
 /* ---- split-K GQA paged-attention decode ----------------------------------------------------- */
 /* Replaces gather + repeatHeads + softmax(QK^T/sqrt(D))V (src/kvcache/paged.zig:705-802,
@@ -274,6 +280,39 @@ b200_status b200_embed_gather(const void* d_table, const uint32_t* d_ids, void* 
 /* Greedy: first strict maximum per row of bf16 logits [rows, vocab] (src/sampling.zig:22-39). */
 b200_status b200_argmax(const void* d_logits, int32_t rows, int32_t vocab, uint32_t* d_out,
                         void* stream);
+
+/* ---- sampling beyond greedy (src/sampling.zig:42-242, 277-322) ------------------------------- */
+/* One row of SamplerConfig (:277-285) plus the uniform variate in [0,1) that sampleFromProbs (:258-268)
+ * draws: the caller draws it from its own per-request PRNG, so the token is a pure function of the
+ * row.  temperature <= 0 is greedy (:313-314); top_p >= 1 with top_k >= vocab samples the full
+ * softmax in index order (temperatureSample, :42-72); everything else is topKTopPSampler (:175-242):
+ * scores = logit / temperature sorted descending (equal scores keep index order), softmax over the
+ * top k, cut after the first prefix whose cumulative probability exceeds top_p, renormalise, sample.
+ * top_k <= 0 means no limit (the reference indexes an empty slice there). */
+typedef struct b200_sample_params {
+  float temperature;
+  float top_p;
+  float repetition_penalty; /* applied when > 1 and the row has context tokens (:301-309, 328-354) */
+  float uniform;
+  int32_t top_k;
+  int32_t _pad;
+} b200_sample_params;
+/* d_logits [rows, vocab], bf16 (logits_f32 = 0) or f32 (1), widened to f32 like the reference's
+ * astype (src/generation.zig:124-141).  d_ctx_tokens / d_ctx_offsets[rows+1] (optional) give each row's
+ * token history for the repetition penalty, applied once per occurrence; d_scratch [rows, vocab] f32
+ * is required with them.  d_logprobs (optional) receives log softmax of the (penalised, unscaled)
+ * logits at the sampled token (computeLogprob, :355-375).  Sums over the whole vocabulary are
+ * parallel reductions; sums over the sorted top-k prefix run in the reference's order. */
+b200_status b200_sample_rows(const void* d_logits, int32_t logits_f32, int32_t rows, int32_t vocab,
+                             const b200_sample_params* d_params, const uint32_t* d_ctx_tokens,
+                             const int32_t* d_ctx_offsets, float* d_scratch, uint32_t* d_tokens,
+                             float* d_logprobs, void* stream);
+/* std.Random.DefaultPrng as SamplerConfig.init seeds it (:287-296): xoshiro256++ whose state comes
+ * from SplitMix64(seed), and Random.float(f32) (23 mantissa bits, exponent from the leading-zero
+ * count of the remaining bits).  Both belong to the Zig standard library, not to the reference. */
+void b200_prng_seed(uint64_t seed, uint64_t state[4]);
+uint64_t b200_prng_next_u64(uint64_t state[4]);
+float b200_prng_next_f32(uint64_t state[4]);
 
 /* ---- dequant-fused quantised matmul --------------------------------------------------------- */
 /* y[T,N] = x[T,K] . dequant(W[N,K])^T  (quantizedMatmul call sites src/models/llama.zig:127,367,596;
@@ -361,6 +400,11 @@ b200_status b200_llama_forward(b200_llama* m, b200_kv* kv, const b200_pack_desc*
                                int32_t total_rows, const uint32_t* d_prefill_tokens, void* stream);
 void b200_llama_device_buffers(b200_llama* m, b200_pack_desc** d_desc, uint32_t** d_prefill,
                                uint32_t** d_next);
+/* Sampler rows for the requests of the NEXT b200_llama_step, in descriptor order (one use): that
+ * step draws its tokens with b200_sample_rows instead of the argmax.  Rows with temperature <= 0
+ * stay greedy.  b200_llama_last_logprobs returns the log-probabilities of that step's tokens. */
+b200_status b200_llama_set_samplers(b200_llama* m, const b200_sample_params* h_rows, int32_t n_req);
+b200_status b200_llama_last_logprobs(b200_llama* m, float* h_out, int32_t n_req);
 /* bf16 logits [n_req, vocab] of the last step's sampled rows (tests). */
 b200_status b200_llama_last_logits(b200_llama* m, void* h_bf16_out, int32_t n_req);
 int64_t b200_llama_launch_count(const b200_llama* m);
@@ -390,6 +434,12 @@ b200_status b200_engine_result(const b200_engine* e, uint64_t id, uint32_t* out,
                                uint64_t* n, int32_t* done);
 void b200_engine_forget(b200_engine* e, uint64_t id);
 int32_t b200_engine_free_pages(const b200_engine* e);
+/* Sampler of one request (SamplerConfig, src/sampling.zig:277-296): temperature, top-k, top-p and a
+ * PRNG seeded like SamplerConfig.init.  A request without one is greedy.  One uniform variate is
+ * drawn per token that joins the request's output, so a request's variates do not depend on what
+ * it is batched with.  No repetition penalty on this path. */
+b200_status b200_engine_set_sampler(b200_engine* e, uint64_t id, float temperature, int32_t top_k,
+                                    float top_p, uint64_t seed);
 /* Prefix sharing (off by default): a request about to start its prefill takes over, by reference
  * count, the full 32-token prompt blocks that a live request with the same chained block hashes has
  * already prefilled (findCachedPrefix, src/kvcache/paged.zig:234-265); its own appends copy a shared
