@@ -6,10 +6,11 @@
 // log-sum-exp, the digit passes of a radix select, one gather pass); nothing of vocabulary size is
 // kept on chip.  Ordering follows the reference's stable descending sort: a candidate is the
 // 64-bit key (descending score bits << 32 | token id), so equal scores keep index order.  The
-// top-k candidates are selected kCap at a time by a most-significant-digit radix select over that
-// key, sorted in shared memory with a bitonic network, and the sums over the sorted prefix
-// (softmax denominator, nucleus cut, renormalised draw) run on one thread in the reference's order
-// in f32.  A top-k above kCap walks the sorted order chunk by chunk, once per pass.
+// candidates are taken from that order kChunk at a time: one pass over the row bounds the chunk
+// (the kChunk-th smallest per-thread minimum), a second gathers the few keys under the bound, a
+// bitonic network in shared memory sorts them; a radix select over the key backs this up for rows
+// that defeat the bound.  The sums over the sorted prefix (softmax denominator, nucleus cut,
+// renormalised draw) run on one thread in the reference's order in f32.
 #include <cuda_bf16.h>
 
 #include "common.h"
@@ -17,11 +18,12 @@
 namespace {
 
 constexpr int kThreads = 1024;
-constexpr int kCap = 2048;
+constexpr int kCap = 2048;    // keys held in shared memory
+constexpr int kChunk = 512;   // candidates taken from the sorted order at a time
 
 struct Shared {
   unsigned long long key[kCap];
-  float e[kCap];
+  float e[kChunk];
   int hist[256];
   float red_f[32];
   int red_i[32];
@@ -140,18 +142,37 @@ template <typename T> __device__ int block_first_max(const Row<T>& r, Shared& s,
   return s.red_i[0];
 }
 
-// The m smallest keys that are >= lo_bound, sorted ascending into s.key; returns how many there
-// were (fewer than m only when the row runs out).  m <= kCap.
+// Ascending bitonic sort of s.key[0, n2), n2 a power of two <= kCap.  All threads call.
+__device__ void sort_keys(Shared& s, int n2) {
+  for (int k = 2; k <= n2; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = threadIdx.x; i < n2; i += kThreads) {
+        const int x = i ^ j;
+        if (x > i) {
+          const unsigned long long a = s.key[i], c = s.key[x];
+          if ((a > c) == ((i & k) == 0)) { s.key[i] = c; s.key[x] = a; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// Largest key of the m smallest keys >= lo_bound (most-significant-digit radix select over the whole
+// row); *out_count = how many keys lie in [lo_bound, result] (m, or fewer when the row runs out).
+// This is the general path: every element takes part in the first digit passes.
 template <typename T>
-__device__ int select_chunk(const Row<T>& r, float temperature, unsigned long long lo_bound, int m, Shared& s) {
+__device__ unsigned long long radix_threshold(const Row<T>& r, float temperature, unsigned long long lo_bound, int m,
+                                              Shared& s, int* out_count) {
   const int tid = threadIdx.x, lane = tid & 31;
   unsigned long long prefix = 0, mask = 0, thr = 0;
-  int need = m;
+  int need = m, taken = 0;
   bool closed = false;
   for (int b = 7; b >= 0 && !closed; --b) {
     // digits of the token id that are zero for every element of the row
     if (b == 3 || (b == 2 && r.V <= (1 << 16)) || (b == 1 && r.V <= (1 << 8))) continue;
     const int shift = 8 * b;
+    __syncthreads();
     if (tid < 256) s.hist[tid] = 0;
     __syncthreads();
     for (int base = 0; base < r.V; base += kThreads * 8) {
@@ -166,11 +187,13 @@ __device__ int select_chunk(const Row<T>& r, float temperature, unsigned long lo
           c = cand_key(v[j], temperature, i0 + j);
           valid = c >= lo_bound && (c & mask) == prefix;
         }
-        const unsigned digit = (unsigned)(c >> shift) & 255u;
-        // one shared-memory atomic per distinct digit of the warp: the leading digits of a row's
-        // scores fall into a handful of bins
-        const unsigned peers = __match_any_sync(0xffffffffu, valid ? digit : 256u + lane);
-        if (valid && lane == __ffs(peers) - 1) atomicAdd(&s.hist[digit], __popc(peers));
+        if (__any_sync(0xffffffffu, valid)) {
+          const unsigned digit = (unsigned)(c >> shift) & 255u;
+          // one shared-memory atomic per distinct digit of the warp: the leading digits of a row's
+          // scores fall into a handful of bins
+          const unsigned peers = __match_any_sync(0xffffffffu, valid ? digit : 256u + lane);
+          if (valid && lane == __ffs(peers) - 1) atomicAdd(&s.hist[digit], __popc(peers));
+        }
       }
     }
     __syncthreads();
@@ -197,8 +220,9 @@ __device__ int select_chunk(const Row<T>& r, float temperature, unsigned long lo
       if (lane == 0) s.sel_total = total;
     }
     __syncthreads();
-    if (s.sel_total == 0) return 0;
+    if (s.sel_total == 0) { *out_count = 0; return 0; }
     need = min(need, s.sel_total) - s.sel_below;
+    taken += s.sel_below;
     prefix |= (unsigned long long)s.sel_digit << shift;
     mask |= 255ull << shift;
     if (s.sel_count == need) {  // the whole bin is taken: no need to look at lower digits
@@ -207,8 +231,46 @@ __device__ int select_chunk(const Row<T>& r, float temperature, unsigned long lo
     }
   }
   if (!closed) thr = prefix;
-  if (tid == 0) s.count = 0;
+  *out_count = taken + need;
+  return thr;
+}
+
+// Appends every key in [lo_bound, hi_bound] to s.key (unordered); returns how many there are, which
+// may exceed kCap (only the first kCap are stored).
+template <typename T>
+__device__ int gather_keys(const Row<T>& r, float temperature, unsigned long long lo_bound, unsigned long long hi_bound,
+                           Shared& s) {
   __syncthreads();
+  if (threadIdx.x == 0) s.count = 0;
+  __syncthreads();
+  for (int base = 0; base < r.V; base += kThreads * 8) {
+    const int i0 = base + threadIdx.x * 8;
+    float v[8];
+    const int n = load8(r, i0, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j < n) {
+        const unsigned long long c = cand_key(v[j], temperature, i0 + j);
+        if (c >= lo_bound && c <= hi_bound) {
+          const int pos = atomicAdd(&s.count, 1);
+          if (pos < kCap) s.key[pos] = c;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  return s.count;
+}
+
+// The m (<= kChunk) smallest keys >= lo_bound, sorted ascending into s.key[0, m); returns how many
+// there were.  Fast path: the m-th smallest of the 1024 per-thread minima bounds the m-th smallest of
+// the row from above, and for m <= kChunk only a few more than m keys lie under that bound, so one
+// pass finds the bound and a second gathers the candidates.  Rows that defeat the bound (a run of
+// equal scores longer than the buffer, or fewer eligible keys than threads) take the radix select.
+template <typename T>
+__device__ int next_chunk(const Row<T>& r, float temperature, unsigned long long lo_bound, int m, Shared& s) {
+  const int tid = threadIdx.x;
+  unsigned long long best = ~0ull;
   for (int base = 0; base < r.V; base += kThreads * 8) {
     const int i0 = base + tid * 8;
     float v[8];
@@ -217,32 +279,28 @@ __device__ int select_chunk(const Row<T>& r, float temperature, unsigned long lo
     for (int j = 0; j < 8; ++j) {
       if (j < n) {
         const unsigned long long c = cand_key(v[j], temperature, i0 + j);
-        if (c >= lo_bound && c <= thr) {
-          const int pos = atomicAdd(&s.count, 1);
-          if (pos < kCap) s.key[pos] = c;
-        }
+        if (c >= lo_bound && c < best) best = c;
       }
     }
   }
   __syncthreads();
-  const int cnt = min(s.count, kCap);
+  s.key[tid] = best;
+  __syncthreads();
+  sort_keys(s, kThreads);
+  const unsigned long long tau = s.key[m - 1];  // ~0 when fewer than m threads saw an eligible key
+  int count = gather_keys(r, temperature, lo_bound, tau, s);
+  if (count > kCap) {
+    int exact = 0;
+    const unsigned long long thr = radix_threshold(r, temperature, lo_bound, m, s, &exact);
+    count = exact > 0 ? gather_keys(r, temperature, lo_bound, thr, s) : 0;
+  }
+  if (count == 0) return 0;
   int n2 = 2;
-  while (n2 < cnt) n2 <<= 1;
-  for (int i = cnt + tid; i < n2; i += kThreads) s.key[i] = ~0ull;
+  while (n2 < count) n2 <<= 1;
+  for (int i = count + tid; i < n2; i += kThreads) s.key[i] = ~0ull;
   __syncthreads();
-  for (int k = 2; k <= n2; k <<= 1) {
-    for (int j = k >> 1; j > 0; j >>= 1) {
-      for (int i = tid; i < n2; i += kThreads) {
-        const int x = i ^ j;
-        if (x > i) {
-          const unsigned long long a = s.key[i], c = s.key[x];
-          if ((a > c) == ((i & k) == 0)) { s.key[i] = c; s.key[x] = a; }
-        }
-      }
-      __syncthreads();
-    }
-  }
-  return cnt;
+  sort_keys(s, n2);
+  return min(count, m);
 }
 
 // temperatureSample (src/sampling.zig:42-72): softmax of (logit - max) / T in index order, first
@@ -300,20 +358,54 @@ __device__ unsigned sample_full_softmax(const Row<T>& r, float temperature, floa
   return s.token;
 }
 
-// topKTopPSampler (src/sampling.zig:175-242).
+// Sum of exp(score - max_score) over every key <= hi_bound, as a parallel reduction.
 template <typename T>
-__device__ unsigned sample_top_k_top_p(const Row<T>& r, float temperature, int k_eff, float top_p, float u, Shared& s) {
+__device__ float sum_exp_below(const Row<T>& r, float temperature, unsigned long long hi_bound, float max_score, Shared& s) {
+  float part = 0.f;
+  for (int base = 0; base < r.V; base += kThreads * 8) {
+    const int i0 = base + threadIdx.x * 8;
+    float v[8];
+    const int n = load8(r, i0, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (j < n) {
+        const unsigned long long c = cand_key(v[j], temperature, i0 + j);
+        if (c <= hi_bound) part += expf(key_score(c) - max_score);
+      }
+    }
+  }
+  return block_sum(part, s);
+}
+
+// topKTopPSampler (src/sampling.zig:175-242).  The sorted order is walked kChunk candidates at a time.
+// Up to kChunk candidates (the usual top-k) everything, the softmax denominator included, is summed on
+// one thread in sorted order like the reference; above that the denominator is a parallel reduction
+// and only the nucleus cut and the draw walk the order, normally inside the first chunk.
+template <typename T>
+__device__ unsigned sample_top_k_top_p(const Row<T>& r, float temperature, int k_eff, float top_p, float u, float gmax,
+                                       Shared& s) {
   const int tid = threadIdx.x;
-  const bool single = k_eff <= kCap;
+  const bool single = k_eff <= kChunk;
   bool have_chunk = false;
   int chunk_cnt = 0;
-  float max_score = 0.f;
-  bool have_max = false;
-  for (int pass = 0; pass < 3; ++pass) {
+  // the largest score is the largest logit's: division by a positive temperature keeps the order
+  const float max_score = gmax / temperature + 0.0f;
+  if (!single) {
+    unsigned long long hi = ~0ull;
+    if (k_eff < r.V) {
+      int exact = 0;
+      hi = radix_threshold(r, temperature, 0ull, k_eff, s, &exact);
+    }
+    const float total = sum_exp_below(r, temperature, hi, max_score, s);
+    if (tid == 0) s.sum_exp = total;
+    __syncthreads();
+  }
+  for (int pass = single ? 0 : 1; pass < 3; ++pass) {
     // pass 0: softmax denominator over the top k; 1: nucleus cut; 2: the draw inside the nucleus
     unsigned long long lo = 0;
     int taken = 0;
     const int limit = pass == 2 ? s.cutoff : k_eff;
+    __syncthreads();
     if (tid == 0) { s.acc = 0.f; s.done = 0; }
     __syncthreads();
     while (taken < limit) {
@@ -321,9 +413,8 @@ __device__ unsigned sample_top_k_top_p(const Row<T>& r, float temperature, int k
       if (single && have_chunk) {
         cnt = chunk_cnt;
       } else {
-        cnt = select_chunk(r, temperature, lo, min(kCap, k_eff - taken), s);
+        cnt = next_chunk(r, temperature, lo, min(kChunk, k_eff - taken), s);
         if (cnt == 0) break;
-        if (!have_max) { max_score = key_score(s.key[0]); have_max = true; }
         for (int i = tid; i < cnt; i += kThreads) s.e[i] = expf(key_score(s.key[i]) - max_score);
         __syncthreads();
         have_chunk = true;
@@ -377,7 +468,7 @@ __device__ void sample_row(const Row<T>& r, const b200_sample_params& p, Shared&
     token = sample_full_softmax(r, p.temperature, gmax, p.uniform, s);
   } else {
     const int k_eff = (p.top_k <= 0 || p.top_k > r.V) ? r.V : p.top_k;
-    token = sample_top_k_top_p(r, p.temperature, k_eff, p.top_p, p.uniform, s);
+    token = sample_top_k_top_p(r, p.temperature, k_eff, p.top_p, p.uniform, gmax, s);
   }
   if (out_logprob != nullptr) {
     float part = 0.f;
