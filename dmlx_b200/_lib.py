@@ -228,6 +228,13 @@ _sig("b200_engine_result", i32, vp, u64, P(u32), u64, P(u64), P(i32))
 _sig("b200_engine_forget", None, vp, u64)
 _sig("b200_engine_free_pages", i32, vp)
 _sig("b200_engine_set_prefix_sharing", None, vp, i32)
+_sig("b200_engine_park_slot", i32, vp, P(i32))
+_sig("b200_engine_publish_prefix", i32, vp, i32, P(u32), u64)
+_sig("b200_engine_drop_prefix", i32, vp, i32)
+_sig("b200_engine_request_slot", i32, vp, u64)
+_sig("b200_sched_bm_park_slot", i32, vp, P(i32))
+_sig("b200_sched_bm_unpark_slot", i32, vp, i32)
+_sig("b200_sched_bm_sync", i32, vp)
 _sig("b200_engine_set_sampler", i32, vp, u64, f32, i32, f32, u64)
 _sig("b200_engine_set_max_step_tokens", None, vp, u64)
 _sig("b200_engine_shared_tokens", u64, vp, u64)

@@ -32,7 +32,7 @@ struct b200_engine {
   // request starts its prefill): live sequence slots with the chained hashes of their prompt blocks.
   bool share_prefix = false;
   uint64_t max_step_tokens = 0;  // 0 = no cap; else prefill chunks beyond the budget wait for a later step
-  struct Live { b200_request* req; std::vector<uint64_t> chain; };
+  struct Live { b200_request* req; std::vector<uint64_t> chain; uint64_t parked_tokens = 0; };  // req == nullptr: a parked prefix
   std::unordered_map<int32_t, Live> live;               // by sequence slot
   std::unordered_map<uint64_t, uint64_t> shared_tokens;  // request id -> tokens taken over from a donor
   // Per-request samplers (SamplerConfig, src/sampling.zig:277-296); requests without one are greedy.
@@ -75,7 +75,7 @@ b200_status try_share_prefix(b200_engine* e, b200_request* r, b200_engine::Live*
   for (const auto& kvp : e->live) {
     if (kvp.first == slot) continue;
     const auto& other = kvp.second;
-    const uint64_t have = cached_tokens(other.req) / kPageTokens;
+    const uint64_t have = (other.req ? cached_tokens(other.req) : other.parked_tokens) / kPageTokens;
     uint64_t j = 0;
     while (j < me.chain.size() && j < other.chain.size() && j < have && me.chain[j] == other.chain[j]) ++j;
     if (j > best) { best = j; donor = kvp.first; }
@@ -222,9 +222,36 @@ b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t ca
   st = b200_scheduler_postprocess(e->sched, e->outs.data(), e->outs.size());
   if (e->share_prefix) {  // finished requests have given their slot back
     for (auto it = e->live.begin(); it != e->live.end();)
-      it = b200_request_state(it->second.req) == B200_REQ_DONE ? e->live.erase(it) : std::next(it);
+      it = it->second.req && b200_request_state(it->second.req) == B200_REQ_DONE ? e->live.erase(it) : std::next(it);
   }
   return st;
+}
+
+b200_status b200_engine_park_slot(b200_engine* e, int32_t* out_slot) { return b200_sched_bm_park_slot(e->bm, out_slot); }
+
+b200_status b200_engine_publish_prefix(b200_engine* e, int32_t slot, const uint32_t* token_ids, uint64_t n_tokens) {
+  int32_t len = 0;
+  b200_status st = b200_kv_seq_len(e->kv, slot, &len);
+  if (st != B200_OK) return st;
+  if ((uint64_t)len < n_tokens) {
+    b200_set_error("publish_prefix: slot %d holds %d tokens, %llu announced", slot, len, (unsigned long long)n_tokens);
+    return B200_ERR_INVALID_ARGUMENT;
+  }
+  b200_engine::Live donor{nullptr, prompt_chain(std::vector<uint32_t>(token_ids, token_ids + n_tokens)), n_tokens};
+  e->live[slot] = std::move(donor);
+  return b200_sched_bm_sync(e->bm);
+}
+
+b200_status b200_engine_drop_prefix(b200_engine* e, int32_t slot) {
+  auto it = e->live.find(slot);
+  if (it == e->live.end() || it->second.req != nullptr) { b200_set_error("drop_prefix: slot %d holds no parked prefix", slot); return B200_ERR_INVALID_ARGUMENT; }
+  e->live.erase(it);
+  return b200_sched_bm_unpark_slot(e->bm, slot);
+}
+
+int32_t b200_engine_request_slot(const b200_engine* e, uint64_t id) {
+  auto it = e->requests.find(id);
+  return it == e->requests.end() ? -1 : b200_request_kv_slot(it->second);
 }
 
 b200_status b200_engine_set_sampler(b200_engine* e, uint64_t id, float temperature, int32_t top_k, float top_p, uint64_t seed) {

@@ -436,6 +436,26 @@ b200_sched_bm* b200_sched_bm_create_with_kv(b200_kv* kv) {
   return b;
 }
 void b200_sched_bm_destroy(b200_sched_bm* bm) { delete bm; }
+// A sequence slot of the device pool taken out of admission (for pages filled from outside, e.g. a
+// prefix restored from disk), and its return; sync re-reads the pool's free count after the caller
+// has allocated or released pages behind the scheduler's back.
+b200_status b200_sched_bm_park_slot(b200_sched_bm* bm, int32_t* out_slot) {
+  if (!bm->kv || bm->free_slots.empty()) {
+    b200_set_error("park_slot: no device pool behind this block manager, or no free sequence slot");
+    return B200_ERR_INSUFFICIENT_BLOCKS;
+  }
+  *out_slot = bm->free_slots.back();
+  bm->free_slots.pop_back();
+  return B200_OK;
+}
+b200_status b200_sched_bm_unpark_slot(b200_sched_bm* bm, int32_t slot) {
+  if (!bm->kv) { b200_set_error("unpark_slot: no device pool behind this block manager"); return B200_ERR_INVALID_ARGUMENT; }
+  b200_status st = b200_kv_release(bm->kv, &slot, 1);
+  if (st != B200_OK) return st;
+  bm->free_slots.push_back(slot);
+  return bm->refresh_kv();
+}
+b200_status b200_sched_bm_sync(b200_sched_bm* bm) { return bm->kv ? bm->refresh_kv() : B200_OK; }
 int32_t b200_sched_bm_can_allocate(const b200_sched_bm* bm, uint64_t n) { return bm->can_allocate(n); }
 uint64_t b200_sched_bm_free_count(const b200_sched_bm* bm) { return bm->free_count(); }
 uint64_t b200_sched_bm_total_blocks(const b200_sched_bm* bm) { return bm->total_blocks; }

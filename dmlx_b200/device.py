@@ -571,6 +571,21 @@ class Engine:
     def set_sampler(self, rid: int, temperature: float, top_k: int = 50, top_p: float = 1.0, seed: int = 0):
         _lib.check(lib.b200_engine_set_sampler(self._h, rid, temperature, top_k, top_p, seed))
 
+    def park_slot(self) -> int:
+        out = C.c_int32()
+        _lib.check(lib.b200_engine_park_slot(self._h, C.byref(out)))
+        return out.value
+
+    def publish_prefix(self, slot: int, token_ids: Sequence[int]):
+        arr = (C.c_uint32 * max(len(token_ids), 1))(*[int(t) for t in token_ids])
+        _lib.check(lib.b200_engine_publish_prefix(self._h, slot, arr, len(token_ids)))
+
+    def drop_prefix(self, slot: int):
+        _lib.check(lib.b200_engine_drop_prefix(self._h, slot))
+
+    def request_slot(self, rid: int) -> int:
+        return int(lib.b200_engine_request_slot(self._h, rid))
+
     def set_prefix_sharing(self, on: bool = True):
         lib.b200_engine_set_prefix_sharing(self._h, int(on))
 

@@ -120,6 +120,11 @@ b200_sched_bm* b200_sched_bm_create_with_real(b200_block_manager* real);        
  * sequence slot, completion releases the sequence. */
 b200_sched_bm* b200_sched_bm_create_with_kv(b200_kv* kv);
 void b200_sched_bm_destroy(b200_sched_bm* bm);
+/* Device-pool views only: take a sequence slot out of admission / give it back (releasing its pages);
+ * sync re-reads the pool's free count after pages were allocated outside the scheduler. */
+b200_status b200_sched_bm_park_slot(b200_sched_bm* bm, int32_t* out_slot);
+b200_status b200_sched_bm_unpark_slot(b200_sched_bm* bm, int32_t slot);
+b200_status b200_sched_bm_sync(b200_sched_bm* bm);
 int32_t b200_sched_bm_can_allocate(const b200_sched_bm* bm, uint64_t n);         /* :46-51 */
 uint64_t b200_sched_bm_free_count(const b200_sched_bm* bm);                      /* :89-94 */
 uint64_t b200_sched_bm_total_blocks(const b200_sched_bm* bm);
@@ -434,6 +439,18 @@ b200_status b200_engine_result(const b200_engine* e, uint64_t id, uint32_t* out,
                                uint64_t* n, int32_t* done);
 void b200_engine_forget(b200_engine* e, uint64_t id);
 int32_t b200_engine_free_pages(const b200_engine* e);
+/* Prefix pages that outlive requests (RestoredPrefix, src/kvcache/prefix_disk.zig:15-29, 246-293): the
+ * caller parks a sequence slot, fills it (b200_kv_alloc + b200_kv_page_load + b200_kv_set_len, e.g.
+ * from blocks restored from disk) and publishes it with the token ids its pages hold; with prefix
+ * sharing on, later requests take over its full blocks by reference count exactly as they do from a
+ * live request.  drop releases the slot and its pages (pages still shared stay alive through their
+ * reference counts).  b200_engine_request_slot gives the slot of a running request (-1 if none), so
+ * that its prompt blocks can be saved before it finishes. */
+b200_status b200_engine_park_slot(b200_engine* e, int32_t* out_slot);
+b200_status b200_engine_publish_prefix(b200_engine* e, int32_t slot, const uint32_t* token_ids,
+                                       uint64_t n_tokens);
+b200_status b200_engine_drop_prefix(b200_engine* e, int32_t slot);
+int32_t b200_engine_request_slot(const b200_engine* e, uint64_t id);
 /* Sampler of one request (SamplerConfig, src/sampling.zig:277-296): temperature, top-k, top-p and a
  * PRNG seeded like SamplerConfig.init.  A request without one is greedy.  One uniform variate is
  * drawn per token that joins the request's output, so a request's variates do not depend on what
