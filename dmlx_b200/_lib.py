@@ -142,6 +142,7 @@ _sig("b200_kv_free_count", i32, vp, P(i32))
 _sig("b200_kv_alloc", i32, vp, i32, i32, P(i32))
 _sig("b200_kv_release", i32, vp, P(i32), i32)
 _sig("b200_kv_fork", i32, vp, i32, i32, i32)
+_sig("b200_kv_extend", i32, vp, i32, vp, i32)
 _sig("b200_kv_rollback", i32, vp, i32, i32)
 _sig("b200_kv_filter", i32, vp, P(i32), i32)
 _sig("b200_kv_reserve", i32, vp, vp, i32, vp)

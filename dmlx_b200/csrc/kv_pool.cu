@@ -796,6 +796,67 @@ b200_status b200_kv_page_load(b200_kv* kv, int32_t layer, int32_t page, const vo
   return B200_OK;
 }
 
+// extend (src/kvcache/paged.zig:947-1109): a sequence of another pool of the same shape becomes a new
+// sequence of this one, with its own copies of the pages.  One launch copies every layer's K and V
+// page (and, for FP8 pools, the per-head scales); grid = (pages of the sequence, layers).
+__global__ void __launch_bounds__(256) copy_pages_kernel(KvDev src, KvDev dst, const int* __restrict__ src_table,
+                                                         const int* __restrict__ dst_table) {
+  const int layer = blockIdx.y, sp = src_table[blockIdx.x], dp = dst_table[blockIdx.x];
+  if (sp < 0 || sp >= src.n_pages || dp < 0 || dp >= dst.n_pages) return;
+  const size_t page_bytes = (size_t)src.n_kv_heads * src.page_size * src.head_dim * src.elem_bytes;  // multiple of 16
+  const size_t so = ((size_t)layer * src.n_pages + sp) * page_bytes, dof = ((size_t)layer * dst.n_pages + dp) * page_bytes;
+  const uint4* sk = reinterpret_cast<const uint4*>((const char*)src.k_pool + so);
+  const uint4* sv = reinterpret_cast<const uint4*>((const char*)src.v_pool + so);
+  uint4* dk = reinterpret_cast<uint4*>((char*)dst.k_pool + dof);
+  uint4* dv = reinterpret_cast<uint4*>((char*)dst.v_pool + dof);
+  for (size_t i = threadIdx.x; i < page_bytes / 16; i += blockDim.x) { dk[i] = sk[i]; dv[i] = sv[i]; }
+  if (src.elem_bytes == 1 && threadIdx.x < src.n_kv_heads) {
+    const size_t ss = ((size_t)layer * src.n_pages + sp) * src.n_kv_heads + threadIdx.x;
+    const size_t ds = ((size_t)layer * dst.n_pages + dp) * dst.n_kv_heads + threadIdx.x;
+    dst.k_scale[ds] = src.k_scale[ss];
+    dst.v_scale[ds] = src.v_scale[ss];
+  }
+}
+
+b200_status b200_kv_extend(b200_kv* kv, int32_t dst_seq, b200_kv* src, int32_t src_seq) {
+  const b200_kv_config &a = kv->cfg, &b = src->cfg;
+  if (a.n_layers != b.n_layers || a.n_kv_heads != b.n_kv_heads || a.head_dim != b.head_dim || a.page_size != b.page_size ||
+      a.kv_dtype != b.kv_dtype) {
+    b200_set_error("extend: the two pools differ in shape or element type");
+    return B200_ERR_INVALID_ARGUMENT;
+  }
+  if (dst_seq < 0 || dst_seq >= a.max_seqs || src_seq < 0 || src_seq >= b.max_seqs) {
+    b200_set_error("extend: slot out of range");
+    return B200_ERR_INVALID_BATCH_INDEX;
+  }
+  int32_t src_len = 0, dst_pages_held = 0, n_src = 0;
+  b200_status st = b200_kv_seq_len(src, src_seq, &src_len);
+  if (st != B200_OK) return st;
+  B200_CUDA_TRY(cudaMemcpy(&dst_pages_held, kv->dev.seq_pages + dst_seq, sizeof(int), cudaMemcpyDeviceToHost));
+  if (dst_pages_held != 0) { b200_set_error("extend: destination slot %d is not empty", dst_seq); return B200_ERR_INVALID_ARGUMENT; }
+  const int need = (src_len + a.page_size - 1) / a.page_size;
+  if (need == 0) return B200_OK;
+  if (need > a.max_pages_per_seq) { b200_set_error("extend: %d pages exceed max_pages_per_seq %d", need, a.max_pages_per_seq); return B200_ERR_CAPACITY; }
+  std::vector<int32_t> src_ids(b.max_pages_per_seq), dst_ids(need);
+  st = b200_kv_block_table(src, src_seq, src_ids.data(), (int32_t)src_ids.size(), &n_src);
+  if (st != B200_OK) return st;
+  if (n_src < need) { b200_set_error("extend: source holds %d pages for %d tokens", n_src, src_len); return B200_ERR_INVALID_ARGUMENT; }
+  st = b200_kv_alloc(kv, dst_seq, need, dst_ids.data());  // InsufficientBlocks when the pool cannot take them
+  if (st != B200_OK) return st;
+  int* d_ids = nullptr;
+  B200_CUDA_TRY(cudaMalloc((void**)&d_ids, sizeof(int) * 2 * need));
+  cudaError_t e = cudaMemcpy(d_ids, src_ids.data(), sizeof(int) * need, cudaMemcpyHostToDevice);
+  if (e == cudaSuccess) e = cudaMemcpy(d_ids + need, dst_ids.data(), sizeof(int) * need, cudaMemcpyHostToDevice);
+  if (e != cudaSuccess) { cudaFree(d_ids); b200_set_error("extend: %s", cudaGetErrorString(e)); return B200_ERR_CUDA; }
+  copy_pages_kernel<<<dim3(need, a.n_layers), 256>>>(src->dev, kv->dev, d_ids, d_ids + need);
+  ++g_b200_launch_counter;
+  e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  cudaFree(d_ids);
+  if (e != cudaSuccess) { b200_set_error("extend: %s", cudaGetErrorString(e)); return B200_ERR_CUDA; }
+  return b200_kv_set_len(kv, dst_seq, src_len);
+}
+
 b200_status b200_kv_page_raw(b200_kv* kv, int32_t layer, int32_t page, void* h_k, void* h_v, float* h_k_scales,
                              float* h_v_scales) {
   if (layer < 0 || layer >= kv->cfg.n_layers || page < 0 || page >= kv->cfg.n_pages) {

@@ -113,6 +113,10 @@ class PagedKVCache:
     def fork(self, src: int, dst: int, n_tokens: int):
         _lib.check(lib.b200_kv_fork(self._h, src, dst, n_tokens))
 
+    def extend(self, dst_seq: int, src: "PagedKVCache", src_seq: int):
+        """VTable.extend: copy sequence src_seq of another pool into the empty slot dst_seq."""
+        _lib.check(lib.b200_kv_extend(self._h, dst_seq, src._h, src_seq))
+
     def rollback(self, seq: int, to_len: int):
         _lib.check(lib.b200_kv_rollback(self._h, seq, to_len))
 

@@ -217,6 +217,11 @@ b200_status b200_kv_release(b200_kv* kv, const int32_t* seqs, int32_t n);       
 /* Share the pages covering the first n_tokens of `src` with the empty slot `dst` (ref_count += 1,
  * the effect of findCachedPrefix :247-256). */
 b200_status b200_kv_fork(b200_kv* kv, int32_t src, int32_t dst, int32_t n_tokens);
+/* extend (VTable.extend, src/kvcache/interface.zig:60-69; src/kvcache/paged.zig:947-1109): sequence
+ * src_seq of another pool of the same shape and element type becomes sequence dst_seq (an empty
+ * slot) of this pool, with its own copies of the pages (reference count 1) in every layer.
+ * Synchronous.  InsufficientBlocks when this pool cannot take the pages. */
+b200_status b200_kv_extend(b200_kv* kv, int32_t dst_seq, b200_kv* src, int32_t src_seq);
 b200_status b200_kv_rollback(b200_kv* kv, int32_t seq, int32_t to_len);          /* :864-877 */
 /* filter: keep only the listed slots, release the rest (:879-945). */
 b200_status b200_kv_filter(b200_kv* kv, const int32_t* keep, int32_t n_keep);

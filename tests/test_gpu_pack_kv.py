@@ -242,3 +242,57 @@ def test_pool_exhaustion_is_flagged_not_trapped():
         kv.alloc(1, 1)
     kv.reserve(_desc(dev, [(7, 1, 0, -1)]))  # bad slot
     assert kv.error_word() == 5
+
+
+@pytest.mark.parametrize("kv_dtype_name", ["KV_BF16", "KV_FP8_E4M3"])
+def test_extend_copies_a_sequence_between_pools(kv_dtype_name):
+    """VTable.extend (src/kvcache/paged.zig:947-1109): a sequence prefilled in its own pool joins a
+    running pool as a new sequence with its own page copies: same gathered rows and raw page bytes
+    in every layer, reference counts 1, pages drawn from the destination's free stack in order; the
+    two pools stay independent afterwards.  Errors: occupied slot, other shape, pool too small."""
+    dev = _dev()
+    kv_dtype = getattr(dev, kv_dtype_name)
+    rng = np.random.default_rng(404)
+    src = dev.PagedKVCache(2, 2, 128, 16, 2, 8, 8, kv_dtype=kv_dtype)
+    dst = dev.PagedKVCache(2, 2, 128, 32, 4, 8, 8, kv_dtype=kv_dtype)
+    src.set_free_order(rng.permutation(16).tolist())
+    order = rng.permutation(32).tolist()
+    dst.set_free_order(order)
+    n_tok = 32 * 3 + 7
+    src.reserve(_desc(dev, [(1, n_tok, 0, -1)]))
+    dst.reserve(_desc(dev, [(0, 40, 0, -1)]))  # the running pool already serves a sequence
+    for layer in range(2):
+        src.append(layer, torch.randn(n_tok, 2, 128, device="cuda").bfloat16() * (1 + layer),
+                   torch.randn(n_tok, 2, 128, device="cuda").bfloat16())
+        dst.append(layer, torch.randn(40, 2, 128, device="cuda").bfloat16(), torch.randn(40, 2, 128, device="cuda").bfloat16())
+    torch.cuda.synchronize()
+    held = dst.block_table(0)
+    free_before = dst.free_count()
+    dst.extend(2, src, 1)
+    assert dst.seq_len(2) == n_tok and dst.free_count() == free_before - 4
+    table = dst.block_table(2)
+    assert len(table) == 4 and not set(table) & set(held)
+    assert [dst.ref_counts()[p] for p in table] == [1, 1, 1, 1]
+    for layer in range(2):
+        ks, vs = src.gather(layer, 1)
+        kd, vd = dst.gather(layer, 2)
+        assert torch.equal(ks, kd) and torch.equal(vs, vd)
+        for ps, pd in zip(src.block_table(1), table):
+            for x, y in zip(src.page_raw(layer, ps), dst.page_raw(layer, pd)):
+                assert np.array_equal(x, y)
+    # the copy keeps living when the source goes away, and grows on its own
+    src.release([1])
+    dst.reserve(_desc(dev, [(2, 30, n_tok, -1)]))
+    torch.cuda.synchronize()
+    assert dst.seq_len(2) == n_tok + 30 and len(dst.block_table(2)) == 5 and dst.error_word() == 0
+    with pytest.raises(Exception):
+        dst.extend(0, dst, 2)  # slot 0 is in use
+    other = dev.PagedKVCache(2, 2, 64, 16, 2, 8, 8, kv_dtype=kv_dtype)
+    with pytest.raises(Exception):
+        other.extend(0, dst, 2)
+    small = dev.PagedKVCache(2, 2, 128, 3, 2, 8, 8, kv_dtype=kv_dtype)
+    with pytest.raises(Exception):
+        small.extend(0, dst, 2)  # 5 pages needed, 3 in the pool
+    assert small.free_count() == 3
+    for p in (src, dst, other, small):
+        p.close()
