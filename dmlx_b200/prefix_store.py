@@ -158,3 +158,78 @@ class PrefixDiskStore:
                              tensors.get(f"layer_{l}_key_scales"), tensors.get(f"layer_{l}_value_scales"))
         kv.set_len(seq, n * self.block_size)
         return n * self.block_size
+
+
+class PrefixTier:
+    """Two tiers for prompt prefixes around one engine: hot = parked sequence slots of the engine's
+    page pool (shared into requests by reference count), cold = a PrefixDiskStore.  Least recently
+    used parked prefixes are dropped when the parked pages would exceed `max_parked_pages` (their
+    blocks stay on disk), the policy of TieredKVCache (src/kvcache/tiered.zig:96-275: access counter,
+    findLRUPage, evict to safetensors, restore on access) applied to whole prefixes instead of single
+    pages of a live sequence.
+    """
+
+    def __init__(self, engine, kv, store: PrefixDiskStore, max_parked_pages: int):
+        self.engine, self.kv, self.store, self.max_parked_pages = engine, kv, store, max_parked_pages
+        self._parked: Dict[int, dict] = {}  # slot -> {"chain": [...], "pages": n, "used": tick}
+        self._tick = 0
+        self.restored_blocks = 0
+        self.evictions = 0
+        engine.set_prefix_sharing(True)
+
+    def parked_pages(self) -> int:
+        return sum(e["pages"] for e in self._parked.values())
+
+    def _touch(self, slot: int):
+        self._tick += 1
+        self._parked[slot]["used"] = self._tick
+
+    def evict_lru(self) -> bool:
+        if not self._parked:
+            return False
+        slot = min(self._parked, key=lambda s: self._parked[s]["used"])
+        self.engine.drop_prefix(slot)
+        del self._parked[slot]
+        self.evictions += 1
+        return True
+
+    def prepare(self, token_ids: Sequence[int]) -> int:
+        """Call before submitting a request: makes the longest stored run of its leading blocks
+        available in the hot tier.  Returns the tokens a new request can take over."""
+        bs = self.store.block_size
+        chain = chain_hashes(token_ids, bs)
+        on_disk = 0
+        while on_disk < len(chain) and self.store.has_block(chain[on_disk]):
+            on_disk += 1
+        best_slot, best = None, 0
+        for slot, e in self._parked.items():
+            n = 0
+            while n < len(chain) and n < len(e["chain"]) and chain[n] == e["chain"][n]:
+                n += 1
+            if n > best:
+                best_slot, best = slot, n
+        if best_slot is not None and best >= on_disk:
+            self._touch(best_slot)
+            return best * bs
+        if on_disk == 0 or on_disk > self.max_parked_pages:
+            if best_slot is not None:
+                self._touch(best_slot)
+            return best * bs
+        while self.parked_pages() + on_disk > self.max_parked_pages or self.engine.free_pages() < on_disk:
+            if not self.evict_lru():
+                return 0
+        slot = self.engine.park_slot()
+        # restore_prefix leaves the last block out when the prompt ends on a block boundary; a parked
+        # prefix has no token of its own to compute, so ask for every stored block
+        restored = self.store.restore_prefix(self.kv, slot, list(token_ids[: on_disk * bs]) + [0])
+        self.engine.publish_prefix(slot, token_ids[:restored])
+        self._parked[slot] = {"chain": chain[: restored // bs], "pages": restored // bs, "used": 0}
+        self._touch(slot)
+        self.restored_blocks += restored // bs
+        return restored
+
+    def retire(self, rid: int, prompt: Sequence[int]) -> int:
+        """Call while request `rid` is still running and has prefilled its prompt: writes its full
+        prompt blocks that are not on disk yet.  Returns the blocks written."""
+        slot = self.engine.request_slot(rid)
+        return self.store.save_prefix(self.kv, slot, prompt) if slot >= 0 else 0

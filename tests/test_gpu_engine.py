@@ -257,3 +257,60 @@ def test_prefix_restored_from_disk_serves_later_requests(tmp_path, kv_dtype_name
         assert all(len(g) == n_new for g in got)
         assert sum(a[0] == b[0] for a, b in zip(got, control)) >= 2, (got, control)
     model.close()
+
+
+def test_prefix_tier_lru_between_pool_and_disk(tmp_path):
+    """PrefixTier: prompts' blocks are written to disk while their requests run; later requests find
+    them restored into parked slots (hot tier) and take them over; when the parked pages exceed the
+    cap the least recently used prefix leaves the pool and is restored from disk again on its next
+    use.  Integer state is checked exactly (tokens taken over, evictions, restores, pages)."""
+    from dmlx_b200 import device as dev
+    from dmlx_b200.prefix_store import PrefixDiskStore, PrefixTier
+
+    cfg = CFG
+    weights = ref_math.random_llama_weights(cfg, seed=2026)
+    model = _build_model(dev, cfg, weights)
+    kv = dev.PagedKVCache(cfg.n_layers, cfg.n_kv_heads, cfg.head_dim, 64, 8, 16, cfg.n_heads, max_rows=1024,
+                          attn_scratch_chunks=8192)
+    eng = dev.Engine(model, kv, max_prefill_tokens=128)
+    tier = PrefixTier(eng, kv, PrefixDiskStore(str(tmp_path / "cold")), max_parked_pages=5)
+    rng = np.random.default_rng(33)
+    pa = rng.integers(0, cfg.vocab, 100).tolist()  # 3 full blocks
+    pb = rng.integers(0, cfg.vocab, 70).tolist()   # 2 full blocks
+    pc = rng.integers(0, cfg.vocab, 130).tolist()  # 4 full blocks
+
+    def run(rid, prompt, n_new=4):
+        taken = tier.prepare(prompt)
+        eng.submit(rid, prompt, n_new)
+        eng.step()
+        wrote = tier.retire(rid, prompt)
+        while eng.active_count() > 0:
+            eng.step()
+        assert eng.shared_tokens(rid) == taken
+        return taken, wrote, eng.result(rid)[0]
+
+    assert run(1, pa)[:2] == (0, 3) and run(2, pb)[:2] == (0, 2) and run(3, pc)[:2] == (0, 4)
+    assert tier.parked_pages() == 0 and eng.free_pages() == 64
+    # second round: everything comes from disk into parked slots; the cap of 5 pages holds a + b, then c evicts both
+    sa = pa[:96] + rng.integers(0, cfg.vocab, 20).tolist()
+    sb = pb[:64] + rng.integers(0, cfg.vocab, 11).tolist()
+    sc = pc[:128] + rng.integers(0, cfg.vocab, 9).tolist()
+    ta, wa, out_a = run(11, sa)
+    assert (ta, wa) == (96, 0) and tier.parked_pages() == 3 and tier.restored_blocks == 3
+    tb, _, _ = run(12, sb)
+    assert tb == 64 and tier.parked_pages() == 5 and tier.evictions == 0
+    ta2, _, out_a2 = run(13, sa)  # hot hit: no restore, and a becomes the most recently used
+    assert ta2 == 96 and tier.restored_blocks == 5 and out_a2 == out_a
+    tc, _, _ = run(14, sc)        # 4 more pages: b (least recently used) goes first, then a
+    assert tc == 128 and tier.evictions == 2 and tier.parked_pages() == 4
+    tb2, _, _ = run(15, sb)       # b again: 4 + 2 > 5, so c is evicted and b restored from disk
+    assert tb2 == 64 and tier.evictions == 3 and tier.restored_blocks == 11 and tier.parked_pages() == 2
+    assert eng.free_pages() == 64 - 2 and kv.error_word() == 0
+    exact = _check_against_oracle(cfg, weights, sa, out_a, "a") + _check_against_oracle(cfg, weights, sa, out_a2, "a2")
+    assert exact >= 0
+    while tier.evict_lru():
+        pass
+    assert eng.free_pages() == 64 and sum(kv.ref_counts()) == 0
+    eng.close()
+    model.close()
+    kv.close()
