@@ -125,6 +125,32 @@ __device__ __forceinline__ void umma_bf16_tmem_a(uint32_t tmem_d, uint32_t tmem_
       "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Block-scaled MMA on 8/6/4-bit floating-point operands: D[tmem] (+)= (A * 2^(sfa-127)) * (B * 2^(sfb-127)),
+// M x N x K32 per instruction, one E8M0 scale per operand row and K32 block.  The scales sit in tensor
+// memory (lane = row % 32, column = row / 32, one byte of the 32-bit word per K32 block; the byte is
+// chosen by the a_sf_id / b_sf_id fields of the instruction descriptor).
+__device__ __forceinline__ void umma_mxf8f6f4(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                              uint32_t accumulate, uint32_t tmem_sfa, uint32_t tmem_sfb) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(tmem_d),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(tmem_sfa), "r"(tmem_sfb)
+      : "memory");
+}
+// Instruction descriptor of the block-scaled kind: A = E2M1 (4-bit codes in 8-bit containers), B = E4M3,
+// both K-major, E8M0 scales, f32 accumulate, tile M x N; sf_id = K32 block (byte) within the scale words.
+__device__ __forceinline__ uint32_t umma_idesc_mx_e2m1_e4m3(uint32_t m, uint32_t n, uint32_t sf_id) {
+  uint32_t d = 0;
+  d |= sf_id << 4;      // b_sf_id
+  d |= 5u << 7;         // a_format = E2M1
+  d |= 0u << 10;        // b_format = E4M3
+  d |= (n >> 3) << 17;  // n_dim
+  d |= 1u << 23;        // scale format = E8M0
+  d |= (m >> 4) << 24;  // m_dim
+  d |= sf_id << 29;     // a_sf_id
+  return d;
+}
 // Arrive on an mbarrier when all MMAs issued so far by this thread have completed.
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
@@ -152,6 +178,11 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16
       "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
       "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
       : "memory");
+}
+// Warp-collective store of 4 consecutive 32-bit columns.
+__device__ __forceinline__ void tmem_st4(uint32_t taddr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1, %2, %3, %4};" ::"r"(taddr), "r"(a), "r"(b), "r"(c), "r"(d)
+               : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 

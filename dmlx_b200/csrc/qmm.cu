@@ -988,6 +988,241 @@ __global__ void __launch_bounds__(kGemvThreads, NT8 >= 4 ? 1 : 2) qmm_mma_kernel
   if (!ok) atomicExch(a.err, B200_ERR_DEVICE_FLAGGED);
 }
 
+// ---- MXFP4 on the block-scaled tensor-core path ---------------------------------------------------
+// tcgen05.mma kind::mxf8f6f4 multiplies E2M1 codes by E8M0 block scales in hardware, so MXFP4 weights
+// need no dequantisation at all: TMA unpacks the packed codes into the 8-bit containers the MMA reads
+// (16 codes -> 16 bytes, tensor-map type 16U4_ALIGN16B), the 128 x 4 scale bytes of a K128 chunk go
+// to tensor memory as they are, and the only arithmetic left on the CUDA cores is the epilogue.
+// The other operand must be an 8-bit float: the bf16 activations are scaled per row by a power of two
+// (largest magnitude in [128, 256)) and split into E4M3 codes plus E4M3 codes of 16x the residual; the two
+// halves are two MMAs into the same accumulator with constant block scales 1 and 2^-4, which carries
+// the activations to about 2^-9 of the row maximum, i.e. bf16 precision.  The row's scale is undone
+// in the epilogue.
+//
+// One CTA owns two adjacent 128-row weight tiles (they share the activation tiles) and all of K:
+// warp 4 loads (per K128 stage: 2 x 16 KiB codes, 2 x 512 B scales, tn x 128 B of each activation
+// half), warps 0-3 move the scales to tensor memory (one 16-byte shared-memory read and one
+// tcgen05.st per thread and tile; the four 32-lane quarters hold the same words) and later run the
+// epilogue, warp 5 issues 2 tiles x 4 K32 steps x 2 halves MMAs per stage.
+constexpr int kMxThreads = 6 * 32;
+constexpr int kMxK = 128;
+
+__device__ __forceinline__ uint32_t mx_f32x2_to_e4m3x2(float lo, float hi) {
+  unsigned short d;
+  asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
+  return d;
+}
+__device__ __forceinline__ float2 mx_e4m3x2_to_f32x2(uint32_t codes) {
+  uint32_t h;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h) : "h"((unsigned short)codes));
+  return __half22float2(*reinterpret_cast<const __half2*>(&h));
+}
+
+// x [rows, k] bf16 -> hi, lo [rows, k] E4M3 and unscale[rows].  One CTA per row; k % 8 == 0.
+__global__ void __launch_bounds__(256) mx_split_activations_kernel(const __nv_bfloat16* __restrict__ x, int k,
+                                                                   unsigned char* __restrict__ hi, unsigned char* __restrict__ lo,
+                                                                   float* __restrict__ unscale) {
+  __shared__ float s_max[8];
+  const int row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * k);
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < k / 8; i += blockDim.x) {
+    const uint4 q = xr[i];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) amax = fmaxf(amax, fmaxf(fabsf(ptx::bf16_lo(w[j])), fabsf(ptx::bf16_hi(w[j]))));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  if ((threadIdx.x & 31) == 0) s_max[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = s_max[0];
+#pragma unroll
+  for (int wv = 1; wv < 8; ++wv) amax = fmaxf(amax, s_max[wv]);
+  // amax = m * 2^ex with m in [1, 2): scale by 2^(7 - ex) (zero, vanishing and non-finite rows keep scale 1)
+  const int ex = amax >= 1e-30f && amax < 3e38f ? (int)((__float_as_uint(amax) >> 23) & 0xFF) - 127 : 7;
+  const float qs = __uint_as_float((uint32_t)(127 + 7 - ex) << 23);
+  if (threadIdx.x == 0) unscale[row] = __uint_as_float((uint32_t)(127 + ex - 7) << 23);
+  uint2* hr = reinterpret_cast<uint2*>(hi + (size_t)row * k);
+  uint2* lr = reinterpret_cast<uint2*>(lo + (size_t)row * k);
+  for (int i = threadIdx.x; i < k / 8; i += blockDim.x) {
+    const uint4 q = xr[i];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = ptx::bf16_lo(w[j]) * qs, b = ptx::bf16_hi(w[j]) * qs;
+      h[j] = mx_f32x2_to_e4m3x2(a, b);
+      const float2 back = mx_e4m3x2_to_f32x2(h[j]);
+      l[j] = mx_f32x2_to_e4m3x2((a - back.x) * 16.f, (b - back.y) * 16.f);
+    }
+    hr[i] = make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+    lr[i] = make_uint2(l[0] | (l[1] << 16), l[2] | (l[3] << 16));
+  }
+}
+
+// Tile-major blocks -> row-major codes + scale atoms (see b200_qweight).  One thread per 32-bit word of a plane.
+__global__ void mx_from_blocks_kernel(const unsigned char* __restrict__ blocks, unsigned char* __restrict__ codes,
+                                      unsigned char* __restrict__ sf, int nt_total, int kc, int k) {
+  constexpr int BB = block_bytes(B200_Q_MXFP4_G32);
+  const size_t n_words = (size_t)nt_total * kc * 2 * kTileN * 4;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += (size_t)gridDim.x * blockDim.x) {
+    const int w = (int)(i & 3), r = (int)((i >> 2) & (kTileN - 1)), plane = (int)((i >> 9) & 1);
+    const size_t blk_id = i >> 10;
+    const int c = (int)(blk_id % kc);
+    const size_t tile = blk_id / kc;  // expert * nt + n tile
+    const unsigned char* blk = blocks + blk_id * BB;
+    const uint32_t word = *reinterpret_cast<const uint32_t*>(blk + plane * kPlaneBytes + r * 16 + w * 4);
+    uint32_t out = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t t = (word >> (4 * j)) & 0x000F000Fu;  // columns 2j (low half) and 2j+1 (high half)
+      out |= ((t & 0xFu) | (t >> 12)) << (8 * j);
+    }
+    const size_t row = tile * kTileN + r;
+    *reinterpret_cast<uint32_t*>(codes + row * (size_t)(k / 2) + c * 32 + plane * 16 + w * 4) = out;
+    if (w == 0) {
+      const int kb = c * 2 + plane;  // K32 block of the row
+      sf[(tile * (size_t)(k / kMxK) + kb / 4) * 512 + (r & 31) * 16 + (r >> 5) * 4 + (kb & 3)] = blk[2 * kPlaneBytes + r * 2 + plane];
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kMxThreads, 1)
+    qmm_mx_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap himap,
+                  const __grid_constant__ CUtensorMap lomap, QmmArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int tn = a.tn, P = a.stages;
+  constexpr int kATile = kTileN * kMxK;  // 16 KiB: one byte per code
+  const int stage_stride = 2 * kATile + 2 * tn * 128 + 1024;
+  auto a_tile = [&](int s, int tile) { return smem + (size_t)s * stage_stride + tile * kATile; };
+  auto b_tile = [&](int s, int half) { return smem + (size_t)s * stage_stride + 2 * kATile + half * tn * 128; };
+  auto sf_tile = [&](int s, int tile) { return smem + (size_t)s * stage_stride + 2 * kATile + 2 * tn * 128 + tile * 512; };
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)P * stage_stride);
+  uint64_t* full = bars;            // [P] codes, scales and activations of the stage have landed
+  uint64_t* slot_free = bars + P;   // [P] the MMAs of the stage are done (shared memory and scale columns)
+  uint64_t* sf_ready = bars + 2 * P;  // [P] the stage's scales are in tensor memory
+  uint64_t* accum_ready = bars + 3 * P;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_ready + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int nt0 = 2 * blockIdx.x, n_tiles = min(2, a.nt - nt0);
+  int t0 = blockIdx.z * tn, rows_here = min(tn, a.rows - t0), expert = 0;
+  if (a.items) {
+    if ((int)blockIdx.z >= *a.n_items) return;
+    const int4 it = a.items[blockIdx.z];
+    expert = it.x;
+    t0 = it.y;
+    rows_here = it.z;
+  }
+  const int n_chunks = a.kc128;
+  constexpr uint32_t kCols = 512;  // accumulators at columns 0 and 128, scale words from column 256
+  if (tid == 0) {
+    for (int s = 0; s < P; ++s) {
+      ptx::mbar_init(&full[s], 1);
+      ptx::mbar_init(&slot_free[s], 1);
+      ptx::mbar_init(&sf_ready[s], 4 * 32);
+    }
+    ptx::mbar_init(accum_ready, 1);
+    ptx::mbar_fence_init();
+  }
+  if (warp == 5) {
+    ptx::tmem_alloc(tmem_slot, kCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t sfa_col0 = tmem_base + 256u, sfb_hi = tmem_base + 256u + 8u * (uint32_t)P, sfb_lo = sfb_hi + 4u;
+  bool ok = true;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      const int wrow0 = expert * a.mx_expert_rows + nt0 * kTileN;
+      const unsigned char* sf_src = a.mx_sf + ((size_t)(expert * a.nt + nt0) * n_chunks) * 512;
+      for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1) {
+        ok = ptx::mbar_wait(&slot_free[s], ph ^ 1u);
+        if (!ok) break;
+        // the unpacking copy counts the packed bytes it reads, not the containers it writes
+        ptx::mbar_expect_tx(&full[s], n_tiles * (kATile / 2 + 512) + 2 * tn * 128);
+        for (int tile = 0; tile < n_tiles; ++tile) {
+          ptx::tma_load_2d(a_tile(s, tile), &wmap, i * kMxK, wrow0 + tile * kTileN, &full[s]);
+          ptx::bulk_g2s(sf_tile(s, tile), sf_src + ((size_t)tile * n_chunks + i) * 512, 512, &full[s]);
+        }
+        ptx::tma_load_2d(b_tile(s, 0), &himap, i * kMxK, a.x_row0 + t0, &full[s]);
+        ptx::tma_load_2d(b_tile(s, 1), &lomap, i * kMxK, a.x_row0 + t0, &full[s]);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1) {
+        ok = ptx::mbar_wait(&full[s], ph) && ptx::mbar_wait(&sf_ready[s], ph);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        const uint64_t dh = ptx::umma_desc_k_sw128(ptx::smem_u32(b_tile(s, 0)));
+        const uint64_t dl = ptx::umma_desc_k_sw128(ptx::smem_u32(b_tile(s, 1)));
+        for (int tile = 0; tile < n_tiles; ++tile) {
+          const uint64_t da = ptx::umma_desc_k_sw128(ptx::smem_u32(a_tile(s, tile)));
+          const uint32_t sfa = sfa_col0 + (uint32_t)((s * 2 + tile) * 4);
+#pragma unroll
+          for (int k4 = 0; k4 < 4; ++k4) {
+            const uint32_t idesc = ptx::umma_idesc_mx_e2m1_e4m3(kTileN, tn, k4);
+            ptx::umma_mxf8f6f4(tmem_base + tile * 128, da + 2 * k4, dh + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u, sfa, sfb_hi);
+            ptx::umma_mxf8f6f4(tmem_base + tile * 128, da + 2 * k4, dl + 2 * k4, idesc, 1u, sfa, sfb_lo);
+          }
+        }
+        ptx::umma_commit(&slot_free[s]);
+      }
+      if (ok) ptx::umma_commit(accum_ready);
+    }
+  } else {
+    // ---- scales: lane l of every warp holds rows l, 32+l, 64+l, 96+l of the tile (4 K32 blocks each) ----
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    ptx::tmem_st4(sfb_hi + lane_base, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);  // 2^0
+    ptx::tmem_st4(sfb_lo + lane_base, 0x7B7B7B7Bu, 0x7B7B7B7Bu, 0x7B7B7B7Bu, 0x7B7B7B7Bu);  // 2^-4
+    int s = 0;
+    uint32_t ph = 0;
+    for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1) {
+      ok = ptx::mbar_wait(&full[s], ph);  // the stage's previous MMAs finished before it was refilled
+      if (!ok) break;
+      for (int tile = 0; tile < n_tiles; ++tile) {
+        const uint4 v = *reinterpret_cast<const uint4*>(sf_tile(s, tile) + lane * 16);
+        ptx::tmem_st4(sfa_col0 + (uint32_t)((s * 2 + tile) * 4) + lane_base, v.x, v.y, v.z, v.w);
+      }
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(&sf_ready[s]);
+    }
+    // ---- epilogue: warp w reads lanes 32w..32w+31 = weight rows of both tiles ----
+    if (ok) ok = ptx::mbar_wait(accum_ready, 0);
+    if (ok) {
+      ptx::tc_fence_after_sync();
+      for (int tile = 0; tile < n_tiles; ++tile) {
+        const int n = (nt0 + tile) * kTileN + warp * 32 + lane;
+        for (int c0 = 0; c0 < rows_here; c0 += 32) {
+          uint32_t v[32];
+          ptx::tmem_ld32(tmem_base + lane_base + (uint32_t)(tile * 128 + c0), v);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (c0 + j < rows_here) v[j] = __float_as_uint(__uint_as_float(v[j]) * a.act_unscale[t0 + c0 + j]);
+          tile_epilogue_store(a, v, c0, rows_here, t0, n, lane, true, nullptr, 0);
+        }
+      }
+    }
+  }
+  if (!ok) atomicExch(a.err, B200_ERR_DEVICE_FLAGGED);
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) ptx::tmem_dealloc(tmem_base, kCols);
+}
+
 // ---- host-side state -------------------------------------------------------------------------------
 float* g_ws = nullptr;
 size_t g_ws_bytes = 0;
@@ -1161,6 +1396,8 @@ extern "C" b200_status b200_qweight_random(int32_t mode, int32_t n_experts, int3
 extern "C" void b200_qweight_destroy(b200_qweight* w) {
   if (!w) return;
   if (w->d_blocks) cudaFree(w->d_blocks);
+  if (w->d_mx_codes) cudaFree(w->d_mx_codes);
+  if (w->d_mx_sf) cudaFree(w->d_mx_sf);
   delete w;
 }
 
@@ -1297,6 +1534,97 @@ static b200_status launch_tca(QmmArgs& a, int rows, cudaStream_t s) {
   return direct ? B200_OK : launch_finish(a, splits, s);
 }
 
+// ---- block-scaled MXFP4 path: second weight layout, activation split, launch --------------------------
+unsigned char* g_mx_act = nullptr;  // [hi: rows x k][lo: rows x k][unscale: rows f32], grown on demand
+size_t g_mx_act_bytes = 0;
+
+static b200_status prepare_mx(b200_qweight* w) {
+  if (w->d_mx_codes) return B200_OK;
+  if (w->mode != B200_Q_MXFP4_G32 || w->k % kMxK != 0) {
+    b200_set_error("block-scaled path: MXFP4 weights with K a multiple of 128 only");
+    return B200_ERR_UNSUPPORTED;
+  }
+  const size_t rows = (size_t)w->n_experts * w->nt * kTileN;
+  const size_t code_bytes = rows * (size_t)(w->k / 2), sf_bytes = (size_t)w->n_experts * w->nt * (w->k / kMxK) * 512;
+  B200_CUDA_TRY(cudaMalloc((void**)&w->d_mx_codes, code_bytes));
+  cudaError_t e = cudaMalloc((void**)&w->d_mx_sf, sf_bytes);
+  if (e != cudaSuccess) { cudaFree(w->d_mx_codes); w->d_mx_codes = nullptr; b200_set_error("cudaMalloc(%zu) failed: %s", sf_bytes, cudaGetErrorString(e)); return B200_ERR_CUDA; }
+  mx_from_blocks_kernel<<<2048, 256>>>(w->d_blocks, w->d_mx_codes, w->d_mx_sf, w->n_experts * w->nt, w->kc, w->k);
+  ++g_b200_launch_counter;
+  e = cudaGetLastError();
+  if (e == cudaSuccess) e = cudaDeviceSynchronize();
+  b200_status st = e == cudaSuccess ? B200_OK : B200_ERR_CUDA;
+  if (st == B200_OK) {
+    const uint64_t dims[2] = {(uint64_t)w->k, (uint64_t)rows};
+    const uint64_t strides[1] = {(uint64_t)w->k / 2};
+    const uint32_t box[2] = {(uint32_t)kMxK, (uint32_t)kTileN};
+    st = b200_make_tensor_map(reinterpret_cast<CUtensorMap*>(w->mx_map), CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, w->d_mx_codes,
+                              dims, strides, box);
+  } else {
+    b200_set_error("block-scaled path: layout conversion failed: %s", cudaGetErrorString(e));
+  }
+  if (st != B200_OK) { cudaFree(w->d_mx_codes); cudaFree(w->d_mx_sf); w->d_mx_codes = nullptr; w->d_mx_sf = nullptr; }
+  return st;
+}
+
+static b200_status launch_mx(const b200_qweight* w, QmmArgs& a, int rows, cudaStream_t s) {
+  b200_status st = prepare_mx(const_cast<b200_qweight*>(w));  // the handle caches its second layout
+  if (st != B200_OK) return st;
+  st = ensure_state(0);
+  if (st != B200_OK) return st;
+  const int tn = a.items ? a.tn : std::min(128, ((rows + 15) / 16) * 16);
+  if (tn > 128 || tn % 16 != 0) { b200_set_error("block-scaled path: token tiles of 16..128 rows (got %d)", tn); return B200_ERR_INVALID_ARGUMENT; }
+  a.tn = tn;
+  const int tts = (rows + tn - 1) / tn;
+  const size_t act_bytes = 2 * (size_t)rows * a.k + sizeof(float) * (size_t)rows + 256;
+  if (act_bytes > g_mx_act_bytes) {
+    B200_CUDA_TRY(cudaDeviceSynchronize());
+    if (g_mx_act) cudaFree(g_mx_act);
+    g_mx_act = nullptr; g_mx_act_bytes = 0;
+    const size_t want = std::max(act_bytes, (size_t)32 << 20);
+    B200_CUDA_TRY(cudaMalloc((void**)&g_mx_act, want));
+    g_mx_act_bytes = want;
+  }
+  unsigned char* hi = g_mx_act;
+  unsigned char* lo = hi + (size_t)rows * a.k;
+  float* unscale = reinterpret_cast<float*>(lo + (((size_t)rows * a.k + 255) / 256) * 256);
+  mx_split_activations_kernel<<<rows, 256, 0, s>>>(a.x, a.k, hi, lo, unscale);
+  B200_LAUNCH_CHECK();
+  CUtensorMap himap, lomap;
+  const uint64_t dims[2] = {(uint64_t)a.k, (uint64_t)rows};
+  const uint64_t strides[1] = {(uint64_t)a.k};
+  const uint32_t box[2] = {(uint32_t)kMxK, (uint32_t)tn};
+  st = b200_make_tensor_map(&himap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, hi, dims, strides, box);
+  if (st == B200_OK) st = b200_make_tensor_map(&lomap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, lo, dims, strides, box);
+  if (st != B200_OK) return st;
+  static int smem_budget = 0;
+  if (smem_budget == 0) {
+    int dev = 0, optin = 0;
+    B200_CUDA_TRY(cudaGetDevice(&dev));
+    B200_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+    cudaFuncAttributes fa;
+    B200_CUDA_TRY(cudaFuncGetAttributes(&fa, qmm_mx_kernel));
+    const int budget = optin - (int)fa.sharedSizeBytes;
+    B200_CUDA_TRY(cudaFuncSetAttribute(qmm_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, budget));
+    smem_budget = budget;
+  }
+  const int stage = 2 * kTileN * kMxK + 2 * tn * 128 + 1024, fixed = 1024 + 8 * (3 * 4 + 1) + 16;
+  a.stages = std::max(2, std::min(4, (std::min(smem_budget, 220 * 1024) - fixed) / stage));
+  a.stages = std::min(a.stages, std::max(2, a.k / kMxK));
+  const size_t smem = (size_t)a.stages * stage + fixed;
+  if ((int)smem > smem_budget) { b200_set_error("block-scaled path: %zu bytes of shared memory needed, %d available", smem, smem_budget); return B200_ERR_CAPACITY; }
+  a.err = g_err;
+  a.mx_sf = w->d_mx_sf;
+  a.act_unscale = unscale;
+  a.mx_expert_rows = w->nt * kTileN;
+  a.kc128 = a.k / kMxK;
+  a.x_row0 = 0;
+  qmm_mx_kernel<<<dim3((a.nt + 1) / 2, 1, a.items ? a.max_items : tts), kMxThreads, smem, s>>>(
+      *reinterpret_cast<const CUtensorMap*>(w->mx_map), himap, lomap, a);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
 // Large batches (129..256 rows per token tile): two weight tiles per CTA.
 template <int MODE>
 static b200_status launch_tc2(QmmArgs& a, int rows, cudaStream_t s) {
@@ -1397,6 +1725,8 @@ static b200_status launch_mma(QmmArgs& a, int rows, cudaStream_t s) {
 
 int b200_qmm_grouped_tmem_a = 1;  // measured 15.1 vs 15.8 ms on the 4-layer MoE stack
 extern "C" void b200_set_qmm_grouped_tmem_a(int32_t on) { b200_qmm_grouped_tmem_a = on; }
+int b200_qmm_grouped_block_scaled = 0;  // MXFP4 grouped matmuls on the block-scaled tensor-core path
+extern "C" void b200_set_qmm_grouped_block_scaled(int32_t on) { b200_qmm_grouped_block_scaled = on; }
 
 extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
                                 const void* d_residual, float swiglu_limit, int32_t path, void* stream) {
@@ -1428,6 +1758,7 @@ extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t 
   a.residual = (const __nv_bfloat16*)d_residual;
   a.rows = rows; a.n = w->n; a.k = w->k; a.nt = w->nt; a.kc = w->kc; a.epilogue = epilogue; a.swiglu_limit = swiglu_limit;
   cudaStream_t s = (cudaStream_t)stream;
+  if (path == B200_QMM_MXFP4_BLOCK_SCALED) return launch_mx(w, a, rows, s);
   if (path == B200_QMM_MMA)
     return w->mode == B200_Q_AFFINE4_G64 ? launch_mma<B200_Q_AFFINE4_G64>(a, rows, s) : launch_mma<B200_Q_MXFP4_G32>(a, rows, s);
   if (path == B200_QMM_SIMT) {
@@ -1463,6 +1794,7 @@ b200_status b200_qmm_grouped(const b200_qweight* w, const void* d_x, int32_t row
   a.items = d_items; a.n_items = d_n_items; a.max_items = max_items; a.tn = tile_rows;
   a.expert_stride = (size_t)w->nt * w->kc * w->block_bytes;
   cudaStream_t s = (cudaStream_t)stream;
+  if (b200_qmm_grouped_block_scaled && w->mode == B200_Q_MXFP4_G32 && w->k % kMxK == 0 && tile_rows <= 128) return launch_mx(w, a, rows, s);
   if (b200_qmm_grouped_tmem_a && w->mode != B200_Q_BF16)
     return w->mode == B200_Q_AFFINE4_G64 ? launch_tca<B200_Q_AFFINE4_G64>(a, rows, s) : launch_tca<B200_Q_MXFP4_G32>(a, rows, s);
   if (w->mode == B200_Q_AFFINE4_G64) return launch_tc<B200_Q_AFFINE4_G64>(a, rows, s);

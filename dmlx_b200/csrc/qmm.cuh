@@ -8,6 +8,12 @@
 struct b200_qweight {
   int mode = 0, n_experts = 1, n = 0, k = 0, nt = 0, kc = 0, block_bytes = 0;
   unsigned char* d_blocks = nullptr;  // [expert][n tile][k chunk][block_bytes]
+  // MXFP4 only, built on first use of the block-scaled tensor-core path: the codes as a plain row-major
+  // matrix [expert * nt * 128, k / 2] (two codes per byte, even column in the low nibble) read by TMA,
+  // and the E8M0 scales in 512-byte atoms [expert][n tile][k / 128]: byte (row % 32) * 16 + (row / 32) * 4 + block.
+  unsigned char* d_mx_codes = nullptr;
+  unsigned char* d_mx_sf = nullptr;
+  alignas(64) unsigned char mx_map[128] = {};  // CUtensorMap over d_mx_codes
 };
 
 struct QmmArgs {
@@ -31,6 +37,11 @@ struct QmmArgs {
   int x_slab;                   // small-batch kernel: activations staged in shared memory
   int x_row0;                   // first row of this launch within the tensor map
   float swiglu_limit;
+  // block-scaled MXFP4 path
+  const unsigned char* mx_sf;   // scale atoms of the weight
+  const float* act_unscale;     // per activation row: factor that undoes the row's power-of-two scaling
+  int mx_expert_rows;           // rows of the code matrix per expert (nt * 128)
+  int kc128;                    // K / 128
 
   __device__ __forceinline__ int row_base_out(int token) const { return token; }
   __device__ __forceinline__ float row_scale(int token) const { return row_scales ? row_scales[token] : 1.0f; }

@@ -16,7 +16,7 @@ from ._lib import KvConfig, PackDesc, lib
 KV_BF16, KV_FP8_E4M3 = 0, 1
 Q_AFFINE4_G64, Q_MXFP4_G32 = 0, 1
 EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
-QMM_AUTO, QMM_SIMT, QMM_TCGEN05, QMM_MMA, QMM_TCGEN05_X2, QMM_TCGEN05_TMEM_A = 0, 1, 2, 3, 4, 5
+QMM_AUTO, QMM_SIMT, QMM_TCGEN05, QMM_MMA, QMM_TCGEN05_X2, QMM_TCGEN05_TMEM_A, QMM_MXFP4_BLOCK_SCALED = 0, 1, 2, 3, 4, 5, 6
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -213,6 +213,11 @@ def launch_count() -> int:
 
 def set_qmm_grouped_tmem_a(on: bool):
     lib.b200_set_qmm_grouped_tmem_a(int(on))
+
+
+def set_qmm_grouped_block_scaled(on: bool):
+    """MXFP4 grouped matmuls on tcgen05.mma kind::mxf8f6f4 (hardware block scaling)."""
+    lib.b200_set_qmm_grouped_block_scaled(int(on))
 
 
 def set_attn_path(path: int):

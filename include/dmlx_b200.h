@@ -347,13 +347,19 @@ b200_status b200_qweight_random(int32_t mode, int32_t n_experts, int32_t n, int3
 void b200_qweight_destroy(b200_qweight* w);
 enum { B200_EPI_NONE = 0, B200_EPI_RESIDUAL = 1, B200_EPI_SWIGLU = 2 };
 enum { B200_QMM_AUTO = 0, B200_QMM_SIMT = 1, B200_QMM_TCGEN05 = 2, B200_QMM_MMA = 3, B200_QMM_TCGEN05_X2 = 4,
-       B200_QMM_TCGEN05_TMEM_A = 5 };
+       B200_QMM_TCGEN05_TMEM_A = 5, B200_QMM_MXFP4_BLOCK_SCALED = 6 };
 /* epilogue NONE: y = xW^T.  RESIDUAL: y = residual + xW^T.  SWIGLU: W holds gate and up rows
  * interleaved (row 2i = gate_i, 2i+1 = up_i); y[T, N/2] = silu(min(g,L)) * clip(u,+-L) with
  * L = swiglu_limit (0 = unclipped)  (src/models/llama.zig:396-415; deepseek_v4.zig:947-966). */
 /* Tuning hook (no reference counterpart): 1 sends the grouped (MoE) matmuls through the kernel that
  * keeps dequantised weights in tensor memory. */
 void b200_set_qmm_grouped_tmem_a(int32_t on);
+/* 1 sends the grouped matmuls of MXFP4 weights (K a multiple of 128, work items of up to 128 rows)
+ * through tcgen05.mma kind::mxf8f6f4 with block scaling: the E2M1 codes and E8M0 scales go to the
+ * tensor cores as they are, the bf16 activations as two E4M3 halves.  The same kernel serves b200_qmm
+ * with path B200_QMM_MXFP4_BLOCK_SCALED.  The weight handle builds a second copy of itself (plain
+ * row-major codes + scale atoms) on first use. */
+void b200_set_qmm_grouped_block_scaled(int32_t on);
 b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y,
                      int32_t epilogue, const void* d_residual, float swiglu_limit, int32_t path,
                      void* stream);

@@ -183,6 +183,42 @@ def test_qmm_paths_agree_and_are_deterministic():
     assert rel <= 1e-2 and cos >= 0.9999
 
 
+@pytest.mark.parametrize("rows,n,k", [(16, 128, 128), (32, 256, 512), (100, 256, 4096), (128, 384, 2048), (300, 640, 1024), (7, 256, 256)])
+def test_qmm_mxfp4_block_scaled_tensor_core_path(rows, n, k):
+    """tcgen05.mma kind::mxf8f6f4: E2M1 codes and E8M0 scales consumed by the tensor cores, activations
+    as two E4M3 halves.  Same oracle and tolerance as the dequantising paths; odd tile counts, several
+    token tiles, scales on both sides of 2^0, all three epilogues."""
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(rows * 7 + n + k)
+    packed = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    scales = rng.integers(112, 134, (n, k // 32), dtype=np.uint8)
+    w = dev.QWeight(dev.Q_MXFP4_G32, packed, scales, None, n, k)
+    x = ref_math.bf16_round(rng.normal(0, 1, (rows, k)) * rng.choice([0.01, 1.0, 30.0], (rows, 1)))
+    x[0, : k // 2] = 0.0
+    if rows > 2:
+        x[2] = 0.0  # an all-zero row keeps scale 1
+    base = ref_math.qmm(x, ref_math.dequantize_mxfp4(packed, scales))
+    got = dev.qmm(w, _bf(x), path=dev.QMM_MXFP4_BLOCK_SCALED).float().cpu().numpy()
+    assert dev.qmm_error_word() == 0
+    # rows differ in magnitude by orders: judge every row against its own scale
+    for r in range(rows):
+        rel, cos = _close(got[r], base[r])
+        assert rel <= 2e-2 and (cos >= 0.9995 or np.abs(base[r]).max() == 0), (r, rel, cos)
+    ref_path = dev.qmm(w, _bf(x), path=dev.QMM_TCGEN05_TMEM_A if rows > 16 else dev.QMM_MMA).float().cpu().numpy()
+    rel, cos = _close(got, ref_path)
+    assert rel <= 2e-2 and cos >= 0.9995, (rel, cos)
+    res = ref_math.bf16_round(rng.normal(0, 1, (rows, n)))
+    got = dev.qmm(w, _bf(x), dev.EPI_RESIDUAL, residual=_bf(res), path=dev.QMM_MXFP4_BLOCK_SCALED).float().cpu().numpy()
+    rel, cos = _close(got, base + res)
+    assert rel <= 2e-2 and cos >= 0.9995, (rel, cos)
+    got = dev.qmm(w, _bf(x), dev.EPI_SWIGLU, swiglu_limit=0.5, path=dev.QMM_MXFP4_BLOCK_SCALED).float().cpu().numpy()
+    want = ref_math.limited_swiglu(base[:, 0::2].astype(np.float64), base[:, 1::2].astype(np.float64), 0.5)
+    rel, cos = _close(got, want)
+    assert got.shape == (rows, n // 2) and rel <= 2e-2 and cos >= 0.9995, (rel, cos)
+    assert dev.qmm_error_word() == 0
+
+
 @pytest.mark.parametrize("path", [2, 3, 4, 5])
 def test_qmm_mxfp4_large_scales(path):
     """E8M0 scales on both sides of 2^0, up to 2^12: value * 2^(scale-127) does not fit one bf16
