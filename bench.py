@@ -422,6 +422,8 @@ def run_moe(args, rank, world, local):
         c["layers"] = args.layers
     if args.moe_tmem_a >= 0:
         dev.set_qmm_grouped_tmem_a(bool(args.moe_tmem_a))
+    if args.moe_block_scaled >= 0:
+        dev.set_qmm_grouped_block_scaled(bool(args.moe_block_scaled))
     K, W = args.steps, max(args.warmup, 3)
     n_tok = c["tokens"] // world  # the step decodes 4096 tokens in total: strong scaling
     el = c["n_experts"] // world
@@ -839,6 +841,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="llama8b_int4")
     ap.add_argument("--moe-tile", type=int, default=128, help="moe_mxfp4 only: token tile of the grouped matmul")
+    ap.add_argument("--moe-block-scaled", type=int, default=-1, help="moe_mxfp4 only: 1 runs the grouped matmuls on tcgen05.mma kind::mxf8f6f4 (hardware block scaling), 0 on the dequantising kernels (default: library choice)")
     ap.add_argument("--moe-tmem-a", type=int, default=-1, help="moe_mxfp4 only: 0/1 forces the grouped matmul kernel (default: library choice)")
     ap.add_argument("--layers", type=int, default=0, help="llama8b_int4 only: fewer layers (profiling / smoke runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")

@@ -1088,6 +1088,20 @@ __global__ void mx_from_blocks_kernel(const unsigned char* __restrict__ blocks, 
   }
 }
 
+// AND of a predicate over the 128 threads of warps 0-3 (named barrier 1; warps 4 and 5 are elsewhere).
+__device__ __forceinline__ bool __syncthreads_and_epi(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+
 __global__ void __launch_bounds__(kMxThreads, 1)
     qmm_mx_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap himap,
                   const __grid_constant__ CUtensorMap lomap, QmmArgs a) {
@@ -1199,20 +1213,69 @@ __global__ void __launch_bounds__(kMxThreads, 1)
       ptx::tc_fence_before_sync();
       ptx::mbar_arrive(&sf_ready[s]);
     }
-    // ---- epilogue: warp w reads lanes 32w..32w+31 = weight rows of both tiles ----
+    // ---- epilogue ----
+    // Warp w holds weight rows 32w..32w+31 of both tiles (one per lane) for every token.  A token's
+    // output row wants the 128 (or 64 after SwiGLU) values of a tile side by side, so the accumulators
+    // go through the (now idle) stage buffers as f32 [tile][token][128 rows] and leave as 16-byte
+    // stores: 64-byte stores straight from the accumulator layout took as long as the whole K loop.
     if (ok) ok = ptx::mbar_wait(accum_ready, 0);
-    if (ok) {
+    const bool all_ok = __syncthreads_and_epi(ok);
+    if (all_ok) {
       ptx::tc_fence_after_sync();
+      float* stage_f = reinterpret_cast<float*>(smem);
       for (int tile = 0; tile < n_tiles; ++tile) {
-        const int n = (nt0 + tile) * kTileN + warp * 32 + lane;
         for (int c0 = 0; c0 < rows_here; c0 += 32) {
           uint32_t v[32];
           ptx::tmem_ld32(tmem_base + lane_base + (uint32_t)(tile * 128 + c0), v);
+          const float us_mine = c0 + lane < rows_here ? a.act_unscale[t0 + c0 + lane] : 0.f;
           ptx::tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (c0 + j < rows_here) v[j] = __float_as_uint(__uint_as_float(v[j]) * a.act_unscale[t0 + c0 + j]);
-          tile_epilogue_store(a, v, c0, rows_here, t0, n, lane, true, nullptr, 0);
+          for (int j = 0; j < 32; ++j) {
+            const float us = __shfl_sync(0xffffffffu, us_mine, j);
+            stage_f[((size_t)tile * tn + c0 + j) * kTileN + warp * 32 + lane] = __uint_as_float(v[j]) * us;
+          }
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      const bool swiglu = a.epilogue == B200_EPI_SWIGLU;
+      const int out_per_tile = swiglu ? kTileN / 2 : kTileN, chunks = out_per_tile / 8;
+      const int n_out = swiglu ? a.n / 2 : a.n;
+      const float L = a.swiglu_limit;
+      for (int tile = 0; tile < n_tiles; ++tile) {
+        for (int idx = tid; idx < rows_here * chunks; idx += 128) {
+          const int tok = idx / chunks, ch = idx - tok * chunks;
+          const int token = t0 + tok, col = (nt0 + tile) * out_per_tile + ch * 8;
+          if (col >= n_out) continue;
+          const float* src = stage_f + ((size_t)tile * tn + tok) * kTileN + ch * (swiglu ? 16 : 8);
+          const float rs = a.row_scale(token);
+          float o[8];
+          if (swiglu) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float4 f = reinterpret_cast<const float4*>(src)[q];  // gate, up, gate, up
+              float g0 = f.x, u0 = f.y, g1 = f.z, u1 = f.w;
+              if (L > 0.f) { g0 = fminf(g0, L); u0 = fminf(fmaxf(u0, -L), L); g1 = fminf(g1, L); u1 = fminf(fmaxf(u1, -L), L); }
+              o[2 * q] = g0 / (1.0f + __expf(-g0)) * u0 * rs;
+              o[2 * q + 1] = g1 / (1.0f + __expf(-g1)) * u1 * rs;
+            }
+          } else {
+            const float4 f0 = reinterpret_cast<const float4*>(src)[0], f1 = reinterpret_cast<const float4*>(src)[1];
+            o[0] = f0.x; o[1] = f0.y; o[2] = f0.z; o[3] = f0.w; o[4] = f1.x; o[5] = f1.y; o[6] = f1.z; o[7] = f1.w;
+            if (a.epilogue == B200_EPI_RESIDUAL) {
+              const uint4 r = *reinterpret_cast<const uint4*>(a.residual + (size_t)token * n_out + col);
+              const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+              for (int q = 0; q < 4; ++q) { o[2 * q] += ptx::bf16_lo(rw[q]); o[2 * q + 1] += ptx::bf16_hi(rw[q]); }
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) o[q] *= rs;
+          }
+          uint4 out;
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(o[0], o[1]), p1 = __floats2bfloat162_rn(o[2], o[3]);
+          __nv_bfloat162 p2 = __floats2bfloat162_rn(o[4], o[5]), p3 = __floats2bfloat162_rn(o[6], o[7]);
+          out.x = *reinterpret_cast<uint32_t*>(&p0); out.y = *reinterpret_cast<uint32_t*>(&p1);
+          out.z = *reinterpret_cast<uint32_t*>(&p2); out.w = *reinterpret_cast<uint32_t*>(&p3);
+          *reinterpret_cast<uint4*>(a.y + (size_t)token * n_out + col) = out;
         }
       }
     }
@@ -1573,6 +1636,7 @@ static b200_status launch_mx(const b200_qweight* w, QmmArgs& a, int rows, cudaSt
   st = ensure_state(0);
   if (st != B200_OK) return st;
   const int tn = a.items ? a.tn : std::min(128, ((rows + 15) / 16) * 16);
+  if (a.n % 16 != 0) { b200_set_error("block-scaled path: N must be a multiple of 16 (16-byte output stores)"); return B200_ERR_UNSUPPORTED; }
   if (tn > 128 || tn % 16 != 0) { b200_set_error("block-scaled path: token tiles of 16..128 rows (got %d)", tn); return B200_ERR_INVALID_ARGUMENT; }
   a.tn = tn;
   const int tts = (rows + tn - 1) / tn;

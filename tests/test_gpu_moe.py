@@ -76,10 +76,21 @@ def test_group_bit_exact():
         assert (covered == 1).all()
 
 
-@pytest.mark.parametrize("mode_name", ["mxfp4", "affine4"])
-def test_moe_layer_matches_oracle(mode_name):
+@pytest.fixture
+def _restore_grouped_path():
+    yield
     from dmlx_b200 import device as dev
 
+    dev.set_qmm_grouped_block_scaled(False)
+
+
+@pytest.mark.parametrize("mode_name", ["mxfp4", "affine4", "mxfp4_block_scaled"])
+def test_moe_layer_matches_oracle(mode_name, _restore_grouped_path):
+    from dmlx_b200 import device as dev
+
+    # the third variant sends the routed experts' grouped matmuls through tcgen05.mma kind::mxf8f6f4
+    dev.set_qmm_grouped_block_scaled(mode_name == "mxfp4_block_scaled")
+    mode_name = "mxfp4" if mode_name == "mxfp4_block_scaled" else mode_name
     rng = np.random.default_rng(11)
     n, d, e, inter, k = 70, 256, 8, 128, 2
     x = ref_math.bf16_round(rng.normal(0, 1, (n, d)))
