@@ -1789,7 +1789,8 @@ static b200_status launch_mma(QmmArgs& a, int rows, cudaStream_t s) {
 
 int b200_qmm_grouped_tmem_a = 1;  // measured 15.1 vs 15.8 ms on the 4-layer MoE stack
 extern "C" void b200_set_qmm_grouped_tmem_a(int32_t on) { b200_qmm_grouped_tmem_a = on; }
-int b200_qmm_grouped_block_scaled = 0;  // MXFP4 grouped matmuls on the block-scaled tensor-core path
+// MXFP4 grouped matmuls on the block-scaled tensor-core path: 13.8 vs 15.3 ms on the 4-layer MoE stack
+int b200_qmm_grouped_block_scaled = 1;
 extern "C" void b200_set_qmm_grouped_block_scaled(int32_t on) { b200_qmm_grouped_block_scaled = on; }
 
 extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
@@ -1805,6 +1806,14 @@ extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t 
   // where its grid is one well-filled wave without a K split (gate/up-sized matrices: 74 vs 85 us at
   // 256 rows; elsewhere the tensor-memory kernel measured 3-8 % faster).  Dense bf16 weights: the
   // shared-memory-operand kernels.
+  if (path == B200_QMM_AUTO) {
+    // MXFP4 at prefill-sized batches: the block-scaled tensor-core path once its grid (tile pairs x
+    // 128-row token tiles, no K split) fills most of the GPU: 188 vs 261 us at 4096 x 4096 x 4096,
+    // 1.07 vs 1.62 ms at 4096 rows of a 28672 x 4096 matrix; below that the dequantising kernels win.
+    if (w->mode == B200_Q_MXFP4_G32 && rows >= 512 && w->k % kMxK == 0 && w->n % 16 == 0 &&
+        ((w->nt + 1) / 2) * ((rows + 127) / 128) >= 96)
+      path = B200_QMM_MXFP4_BLOCK_SCALED;
+  }
   if (path == B200_QMM_AUTO) {
     if (rows <= 16 && w->mode != B200_Q_BF16) path = B200_QMM_MMA;
     else if (rows > 128) {

@@ -81,14 +81,15 @@ def _restore_grouped_path():
     yield
     from dmlx_b200 import device as dev
 
-    dev.set_qmm_grouped_block_scaled(False)
+    dev.set_qmm_grouped_block_scaled(True)  # the library default
 
 
 @pytest.mark.parametrize("mode_name", ["mxfp4", "affine4", "mxfp4_block_scaled"])
 def test_moe_layer_matches_oracle(mode_name, _restore_grouped_path):
     from dmlx_b200 import device as dev
 
-    # the third variant sends the routed experts' grouped matmuls through tcgen05.mma kind::mxf8f6f4
+    # "mxfp4" runs the grouped matmuls on the dequantising kernel, the third variant on tcgen05.mma
+    # kind::mxf8f6f4 (the default for MXFP4 weights)
     dev.set_qmm_grouped_block_scaled(mode_name == "mxfp4_block_scaled")
     mode_name = "mxfp4" if mode_name == "mxfp4_block_scaled" else mode_name
     rng = np.random.default_rng(11)
