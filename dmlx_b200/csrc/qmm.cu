@@ -1102,9 +1102,16 @@ __device__ __forceinline__ bool __syncthreads_and_epi(bool pred) {
   return r != 0;
 }
 
+// Activation tensor maps with boxes of 32, 64, 96 and 128 rows: a work item loads (and multiplies) only
+// as many token rows as it has, rounded up to 32.  The activation tiles are re-read by every CTA of
+// an item and are two thirds of the bytes a stage moves.
+struct MxActMaps {
+  CUtensorMap hi[4];
+  CUtensorMap lo[4];
+};
+
 __global__ void __launch_bounds__(kMxThreads, 1)
-    qmm_mx_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap himap,
-                  const __grid_constant__ CUtensorMap lomap, QmmArgs a) {
+    qmm_mx_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ MxActMaps amaps, QmmArgs a) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int tn = a.tn, P = a.stages;
@@ -1131,6 +1138,7 @@ __global__ void __launch_bounds__(kMxThreads, 1)
     rows_here = it.z;
   }
   const int n_chunks = a.kc128;
+  const int tn_eff = min(tn, ((rows_here + 31) / 32) * 32), map_idx = (tn_eff + 31) / 32 - 1;  // rows loaded and multiplied
   constexpr uint32_t kCols = 512;  // accumulators at columns 0 and 128, scale words from column 256
   if (tid == 0) {
     for (int s = 0; s < P; ++s) {
@@ -1162,13 +1170,13 @@ __global__ void __launch_bounds__(kMxThreads, 1)
         ok = ptx::mbar_wait(&slot_free[s], ph ^ 1u);
         if (!ok) break;
         // the unpacking copy counts the packed bytes it reads, not the containers it writes
-        ptx::mbar_expect_tx(&full[s], n_tiles * (kATile / 2 + 512) + 2 * tn * 128);
+        ptx::mbar_expect_tx(&full[s], n_tiles * (kATile / 2 + 512) + 2 * tn_eff * 128);
         for (int tile = 0; tile < n_tiles; ++tile) {
           ptx::tma_load_2d(a_tile(s, tile), &wmap, i * kMxK, wrow0 + tile * kTileN, &full[s]);
           ptx::bulk_g2s(sf_tile(s, tile), sf_src + ((size_t)tile * n_chunks + i) * 512, 512, &full[s]);
         }
-        ptx::tma_load_2d(b_tile(s, 0), &himap, i * kMxK, a.x_row0 + t0, &full[s]);
-        ptx::tma_load_2d(b_tile(s, 1), &lomap, i * kMxK, a.x_row0 + t0, &full[s]);
+        ptx::tma_load_2d(b_tile(s, 0), &amaps.hi[map_idx], i * kMxK, a.x_row0 + t0, &full[s]);
+        ptx::tma_load_2d(b_tile(s, 1), &amaps.lo[map_idx], i * kMxK, a.x_row0 + t0, &full[s]);
       }
     }
   } else if (warp == 5) {
@@ -1186,7 +1194,7 @@ __global__ void __launch_bounds__(kMxThreads, 1)
           const uint32_t sfa = sfa_col0 + (uint32_t)((s * 2 + tile) * 4);
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
-            const uint32_t idesc = ptx::umma_idesc_mx_e2m1_e4m3(kTileN, tn, k4);
+            const uint32_t idesc = ptx::umma_idesc_mx_e2m1_e4m3(kTileN, tn_eff, k4);
             ptx::umma_mxf8f6f4(tmem_base + tile * 128, da + 2 * k4, dh + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u, sfa, sfb_hi);
             ptx::umma_mxf8f6f4(tmem_base + tile * 128, da + 2 * k4, dl + 2 * k4, idesc, 1u, sfa, sfb_lo);
           }
@@ -1654,13 +1662,16 @@ static b200_status launch_mx(const b200_qweight* w, QmmArgs& a, int rows, cudaSt
   float* unscale = reinterpret_cast<float*>(lo + (((size_t)rows * a.k + 255) / 256) * 256);
   mx_split_activations_kernel<<<rows, 256, 0, s>>>(a.x, a.k, hi, lo, unscale);
   B200_LAUNCH_CHECK();
-  CUtensorMap himap, lomap;
+  MxActMaps amaps;
+  std::memset(&amaps, 0, sizeof(amaps));
   const uint64_t dims[2] = {(uint64_t)a.k, (uint64_t)rows};
   const uint64_t strides[1] = {(uint64_t)a.k};
-  const uint32_t box[2] = {(uint32_t)kMxK, (uint32_t)tn};
-  st = b200_make_tensor_map(&himap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, hi, dims, strides, box);
-  if (st == B200_OK) st = b200_make_tensor_map(&lomap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, lo, dims, strides, box);
-  if (st != B200_OK) return st;
+  for (int i = 0; i < 4 && 32 * (i + 1) <= ((tn + 31) / 32) * 32; ++i) {
+    const uint32_t box[2] = {(uint32_t)kMxK, (uint32_t)std::min(tn, 32 * (i + 1))};
+    st = b200_make_tensor_map(&amaps.hi[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, hi, dims, strides, box);
+    if (st == B200_OK) st = b200_make_tensor_map(&amaps.lo[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, lo, dims, strides, box);
+    if (st != B200_OK) return st;
+  }
   static int smem_budget = 0;
   if (smem_budget == 0) {
     int dev = 0, optin = 0;
@@ -1684,7 +1695,7 @@ static b200_status launch_mx(const b200_qweight* w, QmmArgs& a, int rows, cudaSt
   a.kc128 = a.k / kMxK;
   a.x_row0 = 0;
   qmm_mx_kernel<<<dim3((a.nt + 1) / 2, 1, a.items ? a.max_items : tts), kMxThreads, smem, s>>>(
-      *reinterpret_cast<const CUtensorMap*>(w->mx_map), himap, lomap, a);
+      *reinterpret_cast<const CUtensorMap*>(w->mx_map), amaps, a);
   B200_LAUNCH_CHECK();
   return B200_OK;
 }
