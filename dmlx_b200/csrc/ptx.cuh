@@ -197,6 +197,22 @@ __device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t smem_addr) {
   d |= (uint64_t)2 << 61;                       // layout: SWIZZLE_128B
   return d;
 }
+// Shared-memory descriptor of an unswizzled K-major operand one 16-byte column wide: 8-row core
+// matrices of 128 contiguous bytes, 128 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc_k_noswizzle_16B(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+  d |= (uint64_t)1 << 16;           // leading byte offset (one column: unused)
+  d |= (uint64_t)(128 >> 4) << 32;  // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;           // descriptor version (Blackwell)
+  return d;
+}
+// Copies 32 rows x 16 bytes from shared memory into 4 tensor-memory columns of lanes 0-31 and repeats
+// them in the other three lane quarters (the layout block scales are read from).  Issued by one
+// thread; ordered before the tcgen05.mma instructions the same thread issues afterwards.
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
 // Instruction descriptor: bf16 A and B (both K-major), f32 accumulate, tile M x N.
 __device__ __forceinline__ uint32_t umma_idesc_bf16(uint32_t m, uint32_t n) {
   uint32_t d = 0;

@@ -1183,8 +1183,9 @@ __global__ void __launch_bounds__(kMxThreads, 1)
     if (lane == 0) {
       int s = 0;
       uint32_t ph = 0;
+      ok = ptx::mbar_wait(&sf_ready[0], 0);  // the constant activation scales are in tensor memory
       for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1) {
-        ok = ptx::mbar_wait(&full[s], ph) && ptx::mbar_wait(&sf_ready[s], ph);
+        ok = ptx::mbar_wait(&full[s], ph);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint64_t dh = ptx::umma_desc_k_sw128(ptx::smem_u32(b_tile(s, 0)));
@@ -1192,6 +1193,8 @@ __global__ void __launch_bounds__(kMxThreads, 1)
         for (int tile = 0; tile < n_tiles; ++tile) {
           const uint64_t da = ptx::umma_desc_k_sw128(ptx::smem_u32(a_tile(s, tile)));
           const uint32_t sfa = sfa_col0 + (uint32_t)((s * 2 + tile) * 4);
+          // the tile's 128 x 4 scale bytes: shared memory -> tensor memory, ahead of the MMAs that read them
+          ptx::tmem_cp_32x128b_warpx4(sfa, ptx::umma_desc_k_noswizzle_16B(ptx::smem_u32(sf_tile(s, tile))));
 #pragma unroll
           for (int k4 = 0; k4 < 4; ++k4) {
             const uint32_t idesc = ptx::umma_idesc_mx_e2m1_e4m3(kTileN, tn_eff, k4);
@@ -1208,19 +1211,9 @@ __global__ void __launch_bounds__(kMxThreads, 1)
     const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     ptx::tmem_st4(sfb_hi + lane_base, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);  // 2^0
     ptx::tmem_st4(sfb_lo + lane_base, 0x7B7B7B7Bu, 0x7B7B7B7Bu, 0x7B7B7B7Bu, 0x7B7B7B7Bu);  // 2^-4
-    int s = 0;
-    uint32_t ph = 0;
-    for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1) {
-      ok = ptx::mbar_wait(&full[s], ph);  // the stage's previous MMAs finished before it was refilled
-      if (!ok) break;
-      for (int tile = 0; tile < n_tiles; ++tile) {
-        const uint4 v = *reinterpret_cast<const uint4*>(sf_tile(s, tile) + lane * 16);
-        ptx::tmem_st4(sfa_col0 + (uint32_t)((s * 2 + tile) * 4) + lane_base, v.x, v.y, v.z, v.w);
-      }
-      ptx::tmem_st_wait();
-      ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(&sf_ready[s]);
-    }
+    ptx::tmem_st_wait();
+    ptx::tc_fence_before_sync();
+    ptx::mbar_arrive(&sf_ready[0]);
     // ---- epilogue ----
     // Warp w holds weight rows 32w..32w+31 of both tiles (one per lane) for every token.  A token's
     // output row wants the 128 (or 64 after SwiGLU) values of a tile side by side, so the accumulators
