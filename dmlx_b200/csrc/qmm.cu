@@ -719,7 +719,59 @@ __global__ void __launch_bounds__(kTc2Threads, 1) qmm_tc2_kernel(const __grid_co
     // ---- accumulators: warp w reads lanes 32*(w%4); warps 4g..4g+3 take tile g/2, column half g%2 ----
     if (ok) ok = ptx::mbar_wait(accum_ready, 0);
     const int grp = warp >> 2, etile = grp >> 1, half = grp & 1;
-    if (ok && etile < n_tiles) {
+    // SwiGLU written by this kernel (no K split): the outputs go through the idle stage buffers as
+    // bf16 [token][tile][64] and leave as 16-byte stores, 256 contiguous bytes per token for the tile
+    // pair.  Stores of 64 bytes per token straight from the accumulator layout (one instruction per
+    // token and warp) took a quarter of the kernel's time at 256 rows.
+    const bool staged = gridDim.y == 1 && a.epilogue == B200_EPI_SWIGLU && a.n % 16 == 0;
+    if (staged) {
+      uint32_t all_ok;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\t"
+          "setp.ne.b32 p, %1, 0;\n\t"
+          "bar.red.and.pred q, 1, 512, p;\n\t"
+          "selp.u32 %0, 1, 0, q;\n\t}"
+          : "=r"(all_ok)
+          : "r"((uint32_t)ok)
+          : "memory");
+      if (all_ok) {
+        ptx::tc_fence_after_sync();
+        __nv_bfloat16* stage_h = reinterpret_cast<__nv_bfloat16*>(smem);
+        const float L = a.swiglu_limit;
+        if (etile < n_tiles) {
+          const int lq = warp & 3;
+          const int ch = ((tn / 2 + 31) / 32) * 32;
+          const int c_end = min(rows_here, (half + 1) * ch);
+          for (int c0 = half * ch; c0 < c_end; c0 += 32) {
+            uint32_t v[32];
+            ptx::tmem_ld32(tmem_base + ((uint32_t)(lq * 32) << 16) + (uint32_t)(etile * 256 + c0), v);
+            const float rs_mine = c0 + lane < rows_here ? a.row_scale(t0 + c0 + lane) : 0.f;
+            ptx::tmem_ld_wait();
+            // lanes 2i / 2i+1 hold gate_i / up_i of every token: the even lane takes token j, the odd
+            // lane token j+1, one exchange per token pair and no idle lanes in the arithmetic
+            const bool odd = lane & 1;
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const float a0 = __uint_as_float(v[j]), a1 = __uint_as_float(v[j + 1]);
+              const float got = __shfl_xor_sync(0xffffffffu, odd ? a0 : a1, 1);
+              float g = odd ? got : a0, u = odd ? a1 : got;
+              const float rs = __shfl_sync(0xffffffffu, rs_mine, j + (int)odd);
+              if (L > 0.f) { g = fminf(g, L); u = fminf(fmaxf(u, -L), L); }
+              stage_h[((size_t)(c0 + j + (int)odd) * 2 + etile) * 64 + lq * 16 + (lane >> 1)] =
+                  __float2bfloat16(g / (1.0f + __expf(-g)) * u * rs);
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 512;" ::: "memory");
+        const int n_out = a.n / 2;
+        for (int idx = tid; idx < rows_here * 16; idx += kTc2DequantThreads) {
+          const int tok = idx >> 4, c16 = idx & 15, tile = c16 >> 3;
+          const int col = (nt0 + tile) * 64 + (c16 & 7) * 8;
+          if (tile < n_tiles && col < n_out)
+            *reinterpret_cast<uint4*>(a.y + (size_t)(t0 + tok) * n_out + col) = *reinterpret_cast<const uint4*>(stage_h + (size_t)idx * 8);
+        }
+      }
+    } else if (ok && etile < n_tiles) {
       ptx::tc_fence_after_sync();
       const int lq = warp & 3;
       const int nt = nt0 + etile, n = nt * kTileN + lq * 32 + lane;
