@@ -414,16 +414,19 @@ __device__ __forceinline__ void tile_epilogue_store(const QmmArgs& a, const uint
     for (int j = 0; j < 32; ++j)
       if (c0 + j < rows_here) wsp[(size_t)(c0 + j) * n_pad] = __uint_as_float(v[j]);
   } else if (a.epilogue == B200_EPI_SWIGLU) {
-    // rows 2i / 2i+1 of the tile are gate_i / up_i: neighbouring lanes
+    // rows 2i / 2i+1 of the tile are gate_i / up_i: neighbouring lanes.  The even lane takes token j,
+    // the odd lane token j+1 (one exchange per token pair, no lane idles in the arithmetic).
     const float L = a.swiglu_limit;
+    const bool odd = lane & 1;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      const float mine = __uint_as_float(v[j]);
-      const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
-      if ((lane & 1) == 0 && c0 + j < rows_here && n < a.n) {
-        float g = mine, u = other;
+    for (int j = 0; j < 32; j += 2) {
+      const float a0 = __uint_as_float(v[j]), a1 = __uint_as_float(v[j + 1]);
+      const float got = __shfl_xor_sync(0xffffffffu, odd ? a0 : a1, 1);
+      const int tok = c0 + j + (int)odd;
+      if (tok < rows_here && n < a.n) {
+        float g = odd ? got : a0, u = odd ? a1 : got;
         if (L > 0.f) { g = fminf(g, L); u = fminf(fmaxf(u, -L), L); }
-        const int token = t0 + c0 + j;
+        const int token = t0 + tok;
         a.y[(size_t)token * (a.n / 2) + n / 2] = __float2bfloat16(g / (1.0f + __expf(-g)) * u * a.row_scale(token));
       }
     }
