@@ -172,6 +172,7 @@ _sig("b200_qweight_create", i32, i32, i32, i32, i32, vp, vp, vp, P(vp))
 _sig("b200_qweight_random", i32, i32, i32, i32, i32, u32, P(vp))
 _sig("b200_qweight_destroy", None, vp)
 _sig("b200_qmm", i32, vp, vp, i32, vp, i32, vp, f32, i32, vp)
+_sig("b200_qmm_residual_norm", i32, vp, vp, i32, vp, vp, vp, f32, vp, vp)
 
 
 class LlamaConfig(C.Structure):

@@ -362,18 +362,23 @@ static b200_status llama_forward_eager(b200_llama* m, b200_kv* kv, const b200_pa
                        m->d_row_seq, m->d_row_ctx, m->d_last_row, T, stream));
   STEP(b200_kv_reserve(kv, d_desc, n_req, stream));
   STEP(b200_embed_gather(m->embed, m->d_tokens, m->x, T, c.hidden, stream));
+  // The o and down projections also write the RMSNorm their result feeds (fused into their split-K
+  // finish pass), so only the first layer normalises x on its own.
   for (int l = 0; l < c.n_layers; ++l) {
-    STEP(b200_rmsnorm(m->x, m->attn_norm[l], m->h, T, c.hidden, c.rms_eps, stream));
+    if (l == 0) STEP(b200_rmsnorm(m->x, m->attn_norm[l], m->h, T, c.hidden, c.rms_eps, stream));
     STEP_CAT(1, b200_qmm(m->wqkv[l], m->h, T, m->qkv, B200_EPI_NONE, nullptr, 0.f, B200_QMM_AUTO, stream));
     STEP_CAT(2, b200_kv_rope_append_strided(kv, l, m->qkv, m->qkv + qd, m->qkv + qd + kd, qkv_dim, qkv_dim, qkv_dim, m->d_pos,
                                             m->d_row_seq, T, c.n_heads, c.rope_theta, stream));
     // batches that hold prefill chunks (more rows than requests) take the grouped kernel
     if (T > n_req) { STEP_CAT(0, b200_paged_attn_prefill_strided(kv, l, m->qkv, qkv_dim, m->d_row_seq, m->d_row_ctx, T, m->attn, stream, l > 0)); }
     else { STEP_CAT(0, b200_paged_attn_decode_strided(kv, l, m->qkv, qkv_dim, m->d_row_seq, m->d_row_ctx, T, m->attn, stream, l > 0)); }
-    STEP_CAT(1, b200_qmm(m->wo[l], m->attn, T, m->x, B200_EPI_RESIDUAL, m->x, 0.f, B200_QMM_AUTO, stream));
-    STEP(b200_rmsnorm(m->x, m->ffn_norm[l], m->h, T, c.hidden, c.rms_eps, stream));
+    STEP_CAT(1, b200_qmm_residual_norm(m->wo[l], m->attn, T, m->x, m->x, m->ffn_norm[l], c.rms_eps, m->h, stream));
     STEP_CAT(1, b200_qmm(m->wgu[l], m->h, T, m->act, B200_EPI_SWIGLU, nullptr, 0.f, B200_QMM_AUTO, stream));
-    STEP_CAT(1, b200_qmm(m->wdown[l], m->act, T, m->x, B200_EPI_RESIDUAL, m->x, 0.f, B200_QMM_AUTO, stream));
+    if (l + 1 < c.n_layers) {
+      STEP_CAT(1, b200_qmm_residual_norm(m->wdown[l], m->act, T, m->x, m->x, m->attn_norm[l + 1], c.rms_eps, m->h, stream));
+    } else {
+      STEP_CAT(1, b200_qmm(m->wdown[l], m->act, T, m->x, B200_EPI_RESIDUAL, m->x, 0.f, B200_QMM_AUTO, stream));
+    }
   }
   STEP(b200_gather_rows(m->x, m->d_last_row, m->last_h, n_req, c.hidden, stream));
   STEP(b200_rmsnorm(m->last_h, m->final_norm, m->last_hn, n_req, c.hidden, c.rms_eps, stream));

@@ -160,6 +160,75 @@ __global__ void qmm_finish_kernel(QmmArgs a, int splits) {
   finish_store(a, token, n, acc);
 }
 
+// ---- split-K finish + RMSNorm ---------------------------------------------------------------------
+// The o and down projections end in y = residual + x W^T, and the very next kernel of the layer
+// stack normalises y.  One CTA per row sums the partials in split order (the same arithmetic as
+// qmm_finish_kernel, so y has the same bits), adds the residual, writes y, and from the bf16 values
+// it has just written forms the row's mean square and writes rmsnorm(y) * weight: one launch and one
+// pass over y less per projection.  N <= 4 * 4 * blockDim (each thread keeps up to 4 quads).
+__global__ void __launch_bounds__(1024) qmm_finish_rmsnorm_kernel(QmmArgs a, int splits) {
+  __shared__ float s_part[32];
+  const int token = blockIdx.x, n4 = a.n / 4;
+  const int tts = (a.rows + a.tn - 1) / a.tn, tt = token / a.tn, t = token - tt * a.tn;
+  const size_t split_stride = (size_t)a.tn * kTileN / 4;
+  float4 val[4];
+  float ss = 0.f;
+  int cnt = 0;
+  for (int q = threadIdx.x; q < n4; q += blockDim.x, ++cnt) {
+    const int n = 4 * q, nt = n / kTileN, r = n - nt * kTileN;
+    const float4* p = reinterpret_cast<const float4*>(a.ws + (((size_t)(nt * tts + tt) * splits) * a.tn + t) * kTileN + r);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    int s = 0;
+    for (; s + 4 <= splits; s += 4) {
+      const float4 v0 = p[(size_t)s * split_stride], v1 = p[(size_t)(s + 1) * split_stride];
+      const float4 v2 = p[(size_t)(s + 2) * split_stride], v3 = p[(size_t)(s + 3) * split_stride];
+      acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
+      acc.x += v1.x; acc.y += v1.y; acc.z += v1.z; acc.w += v1.w;
+      acc.x += v2.x; acc.y += v2.y; acc.z += v2.z; acc.w += v2.w;
+      acc.x += v3.x; acc.y += v3.y; acc.z += v3.z; acc.w += v3.w;
+    }
+    for (; s < splits; ++s) {
+      const float4 v = p[(size_t)s * split_stride];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const size_t o = (size_t)token * a.n + n;
+    const uint2 rv = *reinterpret_cast<const uint2*>(a.residual + o);
+    acc.x += ptx::bf16_lo(rv.x); acc.y += ptx::bf16_hi(rv.x); acc.z += ptx::bf16_lo(rv.y); acc.w += ptx::bf16_hi(rv.y);
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 ov;
+    ov.x = *reinterpret_cast<uint32_t*>(&lo);
+    ov.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(a.y + o) = ov;
+    const float4 rounded = make_float4(ptx::bf16_lo(ov.x), ptx::bf16_hi(ov.x), ptx::bf16_lo(ov.y), ptx::bf16_hi(ov.y));
+    val[cnt] = rounded;
+    ss += rounded.x * rounded.x + rounded.y * rounded.y + rounded.z * rounded.z + rounded.w * rounded.w;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if ((threadIdx.x & 31) == 0) s_part[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    float tsum = threadIdx.x < (blockDim.x >> 5) ? s_part[threadIdx.x] : 0.f;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) tsum += __shfl_xor_sync(0xffffffffu, tsum, o);
+    if (threadIdx.x == 0) s_part[0] = rsqrtf(tsum / (float)a.n + a.norm_eps);
+  }
+  __syncthreads();
+  const float rn = s_part[0];
+  cnt = 0;
+  for (int q = threadIdx.x; q < n4; q += blockDim.x, ++cnt) {
+    const int n = 4 * q;
+    const uint2 gw = *reinterpret_cast<const uint2*>(a.norm_w + n);
+    const float4 v = val[cnt];
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x * rn * ptx::bf16_lo(gw.x), v.y * rn * ptx::bf16_hi(gw.x));
+    __nv_bfloat162 hi = __floats2bfloat162_rn(v.z * rn * ptx::bf16_lo(gw.y), v.w * rn * ptx::bf16_hi(gw.y));
+    uint2 ov;
+    ov.x = *reinterpret_cast<uint32_t*>(&lo);
+    ov.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(a.norm_out + (size_t)token * a.n + n) = ov;
+  }
+}
+
 // ---- GEMV kernel ---------------------------------------------------------------------------------
 template <int MODE, int TT>
 __global__ void __launch_bounds__(kTileN) qmm_simt_kernel(QmmArgs a) {
@@ -1521,7 +1590,17 @@ extern "C" void b200_qweight_destroy(b200_qweight* w) {
 }
 
 // ---- launch -------------------------------------------------------------------------------------------
+bool g_finish_did_norm = false;  // set by launch_finish when it also wrote the requested RMSNorm
+
 static b200_status launch_finish(const QmmArgs& a, int splits, cudaStream_t s) {
+  if (a.norm_w && a.epilogue == B200_EPI_RESIDUAL && !a.items && !a.row_scales && a.n % 4 == 0 && a.n <= 16384) {
+    int threads = ((a.n / 4 + 31) / 32) * 32;
+    while (threads > 1024) threads = (((threads + 1) / 2 + 31) / 32) * 32;
+    qmm_finish_rmsnorm_kernel<<<a.rows, threads, 0, s>>>(a, splits);
+    B200_LAUNCH_CHECK();
+    g_finish_did_norm = true;
+    return B200_OK;
+  }
   const long long threads = (long long)a.rows * a.nt * (kTileN / 4);
   qmm_finish_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, s>>>(a, splits);
   B200_LAUNCH_CHECK();
@@ -1852,8 +1931,32 @@ extern "C" void b200_set_qmm_grouped_tmem_a(int32_t on) { b200_qmm_grouped_tmem_
 int b200_qmm_grouped_block_scaled = 1;
 extern "C" void b200_set_qmm_grouped_block_scaled(int32_t on) { b200_qmm_grouped_block_scaled = on; }
 
+static b200_status qmm_entry(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
+                             const void* d_residual, float swiglu_limit, int32_t path, void* stream, const void* d_norm_w,
+                             float norm_eps, void* d_norm_out);
+
 extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
                                 const void* d_residual, float swiglu_limit, int32_t path, void* stream) {
+  return qmm_entry(w, d_x, rows, d_y, epilogue, d_residual, swiglu_limit, path, stream, nullptr, 0.f, nullptr);
+}
+
+extern "C" b200_status b200_rmsnorm(const void* d_x, const void* d_weight, void* d_out, int32_t rows, int32_t hidden, float eps,
+                                    void* stream);
+
+extern "C" b200_status b200_qmm_residual_norm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y,
+                                              const void* d_residual, const void* d_norm_weight, float eps, void* d_normed,
+                                              void* stream) {
+  if (rows <= 0) return B200_OK;
+  g_finish_did_norm = false;
+  b200_status st = qmm_entry(w, d_x, rows, d_y, B200_EPI_RESIDUAL, d_residual, 0.f, B200_QMM_AUTO, stream, d_norm_weight, eps, d_normed);
+  if (st != B200_OK) return st;
+  // kernels that wrote y themselves (no K split) leave the normalisation to the row kernel
+  return g_finish_did_norm ? B200_OK : b200_rmsnorm(d_y, d_norm_weight, d_normed, rows, w->n, eps, stream);
+}
+
+static b200_status qmm_entry(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
+                             const void* d_residual, float swiglu_limit, int32_t path, void* stream, const void* d_norm_w,
+                             float norm_eps, void* d_norm_out) {
   b200_status st = b200_require_device();
   if (st != B200_OK) return st;
   if (rows <= 0) return B200_OK;
@@ -1889,6 +1992,7 @@ extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t 
   a.blocks = w->d_blocks; a.x = (const __nv_bfloat16*)d_x; a.y = (__nv_bfloat16*)d_y;
   a.residual = (const __nv_bfloat16*)d_residual;
   a.rows = rows; a.n = w->n; a.k = w->k; a.nt = w->nt; a.kc = w->kc; a.epilogue = epilogue; a.swiglu_limit = swiglu_limit;
+  a.norm_w = (const __nv_bfloat16*)d_norm_w; a.norm_out = (__nv_bfloat16*)d_norm_out; a.norm_eps = norm_eps;
   cudaStream_t s = (cudaStream_t)stream;
   if (path == B200_QMM_MXFP4_BLOCK_SCALED) return launch_mx(w, a, rows, s);
   if (path == B200_QMM_MMA)

@@ -37,6 +37,10 @@ struct QmmArgs {
   int x_slab;                   // small-batch kernel: activations staged in shared memory
   int x_row0;                   // first row of this launch within the tensor map
   float swiglu_limit;
+  // split-K finish fused with the RMSNorm that reads the result next (residual epilogue only)
+  const __nv_bfloat16* norm_w;  // non-null: the finish pass also writes norm_out = rmsnorm(y) * norm_w
+  __nv_bfloat16* norm_out;
+  float norm_eps;
   // block-scaled MXFP4 path
   const unsigned char* mx_sf;   // scale atoms of the weight
   const float* act_unscale;     // per activation row: factor that undoes the row's power-of-two scaling

@@ -323,6 +323,15 @@ def qmm(w: QWeight, x: torch.Tensor, epilogue: int = EPI_NONE, residual: Optiona
     return out
 
 
+def qmm_residual_norm(w: QWeight, x: torch.Tensor, residual: torch.Tensor, norm_weight: torch.Tensor, eps: float = 1e-5):
+    """b200_qmm_residual_norm: y = residual + x W^T and rmsnorm(y) * norm_weight.  Returns (y, normed)."""
+    y = torch.empty((x.shape[0], w.n), dtype=torch.bfloat16, device=x.device)
+    h = torch.empty_like(y)
+    _lib.check(lib.b200_qmm_residual_norm(w._h, _ptr(x), x.shape[0], _ptr(y), _ptr(residual), _ptr(norm_weight), eps, _ptr(h),
+                                          _stream()))
+    return y, h
+
+
 def qmm_error_word() -> int:
     out = C.c_int32()
     _lib.check(lib.b200_qmm_error_word(C.byref(out)))

@@ -364,6 +364,14 @@ b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void*
                      int32_t epilogue, const void* d_residual, float swiglu_limit, int32_t path,
                      void* stream);
 
+/* y = residual + x W^T and normed = rmsnorm(y) * norm_weight in one call: the pair that closes the
+ * attention and the FFN half of a block (src/models/llama.zig:466-477: residual add, then the next
+ * RMSNorm).  When the matmul splits K its finish pass writes both; otherwise the row kernel follows.
+ * d_y may alias d_residual. */
+b200_status b200_qmm_residual_norm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y,
+                                   const void* d_residual, const void* d_norm_weight, float eps,
+                                   void* d_normed, void* stream);
+
 /* Reads and clears the matmul kernels' error word (set when a bounded wait ran out). */
 b200_status b200_qmm_error_word(int32_t* out);
 /* No counterpart in the reference.  The tensor-core matmul of b200_qmm for hosts that must not

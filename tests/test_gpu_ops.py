@@ -169,6 +169,36 @@ def test_qmm_epilogues(path):
         assert got.shape == (rows, n // 2) and rel <= 2e-2 and cos >= 0.9995, (limit, rel, cos)
 
 
+@pytest.mark.parametrize("rows,n,k", [(1, 512, 2048), (8, 4096, 1024), (100, 1024, 4096), (256, 4096, 2048), (300, 1536, 1024), (40, 128, 256)])
+def test_qmm_residual_norm_equals_the_two_calls(rows, n, k):
+    """b200_qmm_residual_norm (split-K finish fused with the RMSNorm that follows, src/models/llama.zig:466-477)
+    gives the same y bit for bit as b200_qmm with the residual epilogue, and the RMSNorm of that y
+    (row sums of squares are added in another order: at most one bf16 step apart)."""
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(rows + n)
+    packed, s, b, sb, bb = _affine_weight(rng, n, k)
+    w = dev.QWeight(dev.Q_AFFINE4_G64, packed, sb, bb, n, k)
+    x = _bf(ref_math.bf16_round(rng.normal(0, 1, (rows, k))))
+    res = _bf(ref_math.bf16_round(rng.normal(0, 1, (rows, n))))
+    g = _bf(ref_math.bf16_round(rng.normal(1, 0.2, n)))
+    y_ref = dev.qmm(w, x, dev.EPI_RESIDUAL, residual=res)
+    h_ref = dev.rmsnorm(y_ref, g, 1e-5)
+    y, h = dev.qmm_residual_norm(w, x, res, g, 1e-5)
+    assert dev.qmm_error_word() == 0
+    assert torch.equal(y, y_ref)
+    hf, hr = h.float(), h_ref.float()
+    assert (hf - hr).abs().max() <= 2 ** -7 * hr.abs().max()
+    assert (hf != hr).float().mean() < 0.02
+    # in place: y may alias the residual
+    res2 = res.clone()
+    h2 = torch.empty_like(res2)
+    from dmlx_b200 import _lib
+    _lib.check(_lib.lib.b200_qmm_residual_norm(w._h, x.data_ptr(), rows, res2.data_ptr(), res2.data_ptr(), g.data_ptr(), 1e-5,
+                                               h2.data_ptr(), torch.cuda.current_stream().cuda_stream))
+    assert torch.equal(res2, y) and torch.equal(h2, h)
+
+
 def test_qmm_paths_agree_and_are_deterministic():
     from dmlx_b200 import device as dev
 
