@@ -133,7 +133,9 @@ __global__ void offsets_items_kernel(const int* __restrict__ counts, int n_exper
   }
 }
 
-// One CTA per expert: collects, in flat order, the assignments routed to it (stable).
+// One CTA per expert: collects, in flat order, the assignments routed to it (stable).  A thread looks
+// at 8 consecutive assignments per pass (two 16-byte loads), so a pass of the CTA covers 8192 of them
+// with one block scan.
 __global__ void __launch_bounds__(1024) place_kernel(const uint32_t* __restrict__ indices, int n_assign,
                                                      const int* __restrict__ offsets, int* __restrict__ order,
                                                      int* __restrict__ inv_order) {
@@ -142,29 +144,60 @@ __global__ void __launch_bounds__(1024) place_kernel(const uint32_t* __restrict_
   const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) s_base = offsets[e];
   __syncthreads();
-  for (int start = 0; start < n_assign; start += blockDim.x) {
-    const int a = start + tid;
-    const int flag = (a < n_assign && (int)indices[a] == e) ? 1 : 0;
-    const unsigned bal = __ballot_sync(0xffffffffu, flag);
-    const int within = __popc(bal & ((1u << lane) - 1));
-    if (lane == 0) warp_sums[warp] = __popc(bal);
+  const bool vec = (reinterpret_cast<uintptr_t>(indices) & 15) == 0;
+  for (int start = 0; start < n_assign; start += blockDim.x * 8) {
+    const int a0 = start + tid * 8;
+    uint32_t idx[8];
+    if (vec && a0 + 8 <= n_assign) {
+      const uint4 q0 = *reinterpret_cast<const uint4*>(indices + a0), q1 = *reinterpret_cast<const uint4*>(indices + a0 + 4);
+      idx[0] = q0.x; idx[1] = q0.y; idx[2] = q0.z; idx[3] = q0.w; idx[4] = q1.x; idx[5] = q1.y; idx[6] = q1.z; idx[7] = q1.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) idx[j] = a0 + j < n_assign ? indices[a0 + j] : 0xFFFFFFFFu;
+    }
+    unsigned mask = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mask |= ((int)idx[j] == e ? 1u : 0u) << j;
+    const int mine = __popc(mask);
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += t;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
     __syncthreads();
     int before = 0, total = 0;
-    for (int w = 0; w < 32; ++w) {
-      const int v = warp_sums[w];
-      if (w < warp) before += v;
-      total += v;
+    {
+      const int v = warp_sums[lane];  // 32 warps
+      int sc = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, sc, o);
+        if (lane >= o) sc += t;
+      }
+      total = __shfl_sync(0xffffffffu, sc, 31);
+      before = __shfl_sync(0xffffffffu, sc - v, warp);
     }
-    const int base = s_base;
-    if (flag) {
-      const int pos = base + before + within;
-      order[pos] = a;
-      inv_order[a] = pos;
+    int pos = s_base + before + incl - mine;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      if (mask & (1u << j)) {
+        order[pos] = a0 + j;
+        inv_order[a0 + j] = pos;
+        ++pos;
+      }
     }
     __syncthreads();
-    if (tid == 0) s_base = base + total;
+    if (tid == 0) s_base += total;
     __syncthreads();
   }
+}
+
+// row_scales[p] = weights[order[p]] alone (the rows themselves are read in place by the matmul).
+__global__ void row_scales_kernel(const int* __restrict__ order, const float* __restrict__ weights, int n, float* __restrict__ out) {
+  const int p = blockIdx.x * blockDim.x + threadIdx.x;
+  if (p < n) out[p] = weights[order[p]];
 }
 
 __global__ void gather_sorted_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ order,
@@ -180,6 +213,31 @@ __global__ void gather_sorted_kernel(const __nv_bfloat16* __restrict__ x, const 
 __global__ void combine_kernel(const __nv_bfloat16* __restrict__ y_sorted, const int* __restrict__ inv_order, int k, int hidden,
                                const __nv_bfloat16* __restrict__ shared_out, __nv_bfloat16* __restrict__ out) {
   const int t = blockIdx.x;
+  if (hidden % 8 == 0 && k <= 16) {  // 16-byte loads, the row indices read once
+    int rows[16];
+    for (int j = 0; j < k; ++j) rows[j] = inv_order[t * k + j];
+    for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j <= k; ++j) {
+        if (j == k && !shared_out) break;
+        const __nv_bfloat16* src = j < k ? y_sorted + (size_t)rows[j] * hidden : shared_out + (size_t)t * hidden;
+        const uint4 q = reinterpret_cast<const uint4*>(src)[i];
+        const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          acc[2 * e] += __uint_as_float(w[e] << 16);
+          acc[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+        }
+      }
+      uint4 o;
+      __nv_bfloat162 p0 = __floats2bfloat162_rn(acc[0], acc[1]), p1 = __floats2bfloat162_rn(acc[2], acc[3]);
+      __nv_bfloat162 p2 = __floats2bfloat162_rn(acc[4], acc[5]), p3 = __floats2bfloat162_rn(acc[6], acc[7]);
+      o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+      o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+      reinterpret_cast<uint4*>(out + (size_t)t * hidden)[i] = o;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < hidden / 2; i += blockDim.x) {
     float2 acc = make_float2(0.f, 0.f);
     for (int j = 0; j < k; ++j) {
@@ -374,10 +432,19 @@ b200_status b200_moe_forward(b200_moe* m, const void* d_x, int32_t n_tokens, voi
                       m->weights, m->counts, stream));
   STEP(b200_moe_group(m->indices, m->counts, n_tokens, c.top_k, c.n_experts, c.tile_rows, m->offsets, m->order,
                       m->inv_order, m->items, m->n_items, stream));
-  STEP(b200_moe_gather(d_x, m->order, m->weights, A, c.top_k, c.hidden, m->x_sorted, m->row_scales, stream));
   // gate/up with clipped SwiGLU and the routing score folded in before the down projection (:787-805)
-  STEP(b200_qmm_grouped(m->exp_gu, m->x_sorted, A, m->act_sorted, B200_EPI_SWIGLU, m->row_scales, c.swiglu_limit, m->items,
-                        m->n_items, m->max_items, c.tile_rows, stream));
+  if (b200_qmm_grouped_takes_tokens(m->exp_gu, c.tile_rows)) {
+    // the block-scaled path re-encodes every activation row anyway: it reads the rows from the token
+    // matrix through `order`, and no expert-sorted bf16 copy is made
+    row_scales_kernel<<<(A + 255) / 256, 256, 0, (cudaStream_t)stream>>>(m->order, m->weights, A, m->row_scales);
+    B200_LAUNCH_CHECK();
+    STEP(b200_qmm_grouped_from_tokens(m->exp_gu, d_x, m->order, c.top_k, A, m->act_sorted, B200_EPI_SWIGLU, m->row_scales,
+                                      c.swiglu_limit, m->items, m->n_items, m->max_items, c.tile_rows, stream));
+  } else {
+    STEP(b200_moe_gather(d_x, m->order, m->weights, A, c.top_k, c.hidden, m->x_sorted, m->row_scales, stream));
+    STEP(b200_qmm_grouped(m->exp_gu, m->x_sorted, A, m->act_sorted, B200_EPI_SWIGLU, m->row_scales, c.swiglu_limit, m->items,
+                          m->n_items, m->max_items, c.tile_rows, stream));
+  }
   STEP(b200_qmm_grouped(m->exp_down, m->act_sorted, A, m->y_sorted, B200_EPI_NONE, nullptr, 0.f, m->items, m->n_items,
                         m->max_items, c.tile_rows, stream));
   STEP(b200_moe_combine(m->y_sorted, m->inv_order, n_tokens, c.top_k, c.hidden, m->sh_out, d_out, stream));

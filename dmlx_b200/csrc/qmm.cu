@@ -1145,10 +1145,12 @@ __device__ __forceinline__ float2 mx_e4m3x2_to_f32x2(uint32_t codes) {
 // x [rows, k] bf16 -> hi, lo [rows, k] E4M3 and unscale[rows].  One CTA per row; k % 8 == 0.
 __global__ void __launch_bounds__(256) mx_split_activations_kernel(const __nv_bfloat16* __restrict__ x, int k,
                                                                    unsigned char* __restrict__ hi, unsigned char* __restrict__ lo,
-                                                                   float* __restrict__ unscale) {
+                                                                   float* __restrict__ unscale, const int* __restrict__ gather,
+                                                                   int gather_div) {
   __shared__ float s_max[8];
   const int row = blockIdx.x;
-  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * k);
+  const int src_row = gather ? gather[row] / gather_div : row;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)src_row * k);
   float amax = 0.f;
   for (int i = threadIdx.x; i < k / 8; i += blockDim.x) {
     const uint4 q = xr[i];
@@ -1787,7 +1789,7 @@ static b200_status launch_mx(const b200_qweight* w, QmmArgs& a, int rows, cudaSt
   unsigned char* hi = g_mx_act;
   unsigned char* lo = hi + (size_t)rows * a.k;
   float* unscale = reinterpret_cast<float*>(lo + (((size_t)rows * a.k + 255) / 256) * 256);
-  mx_split_activations_kernel<<<rows, 256, 0, s>>>(a.x, a.k, hi, lo, unscale);
+  mx_split_activations_kernel<<<rows, 256, 0, s>>>(a.x, a.k, hi, lo, unscale, a.x_gather, a.x_gather_div);
   B200_LAUNCH_CHECK();
   MxActMaps amaps;
   std::memset(&amaps, 0, sizeof(amaps));
@@ -2036,6 +2038,28 @@ b200_status b200_qmm_grouped(const b200_qweight* w, const void* d_x, int32_t row
   if (w->mode == B200_Q_AFFINE4_G64) return launch_tc<B200_Q_AFFINE4_G64>(a, rows, s);
   if (w->mode == B200_Q_MXFP4_G32) return launch_tc<B200_Q_MXFP4_G32>(a, rows, s);
   return launch_tc<B200_Q_BF16>(a, rows, s);
+}
+
+int b200_qmm_grouped_takes_tokens(const b200_qweight* w, int32_t tile_rows) {
+  return b200_qmm_grouped_block_scaled && w->mode == B200_Q_MXFP4_G32 && w->k % kMxK == 0 && w->n % 16 == 0 && tile_rows <= 128 &&
+         tile_rows % 16 == 0;
+}
+
+b200_status b200_qmm_grouped_from_tokens(const b200_qweight* w, const void* d_tokens, const int* d_order, int32_t top_k,
+                                         int32_t rows, void* d_y, int32_t epilogue, const float* d_row_scales,
+                                         float swiglu_limit, const int4* d_items, const int* d_n_items, int32_t max_items,
+                                         int32_t tile_rows, void* stream) {
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (rows <= 0) return B200_OK;
+  if (!b200_qmm_grouped_takes_tokens(w, tile_rows)) { b200_set_error("grouped matmul from tokens: block-scaled MXFP4 path only"); return B200_ERR_UNSUPPORTED; }
+  QmmArgs a{};
+  a.blocks = w->d_blocks; a.x = (const __nv_bfloat16*)d_tokens; a.y = (__nv_bfloat16*)d_y; a.residual = nullptr;
+  a.row_scales = d_row_scales;
+  a.rows = rows; a.n = w->n; a.k = w->k; a.nt = w->nt; a.kc = w->kc; a.epilogue = epilogue; a.swiglu_limit = swiglu_limit;
+  a.items = d_items; a.n_items = d_n_items; a.max_items = max_items; a.tn = tile_rows;
+  a.x_gather = d_order; a.x_gather_div = top_k;
+  return launch_mx(w, a, rows, (cudaStream_t)stream);
 }
 
 // Reads and clears the matmul kernels' error word (a bounded wait that ran out).

@@ -44,6 +44,8 @@ struct QmmArgs {
   // block-scaled MXFP4 path
   const unsigned char* mx_sf;   // scale atoms of the weight
   const float* act_unscale;     // per activation row: factor that undoes the row's power-of-two scaling
+  const int* x_gather;          // optional: activation row p is x[x_gather[p] / x_gather_div] (expert-sorted rows
+  int x_gather_div;             //   taken straight from the token matrix while they are split; no sorted copy)
   int mx_expert_rows;           // rows of the code matrix per expert (nt * 128)
   int kc128;                    // K / 128
 
@@ -54,3 +56,11 @@ struct QmmArgs {
 b200_status b200_qmm_grouped(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
                              const float* d_row_scales, float swiglu_limit, const int4* d_items, const int* d_n_items,
                              int32_t max_items, int32_t tile_rows, void* stream);
+// 1 if b200_qmm_grouped_from_tokens can serve this weight and tile size (block-scaled MXFP4 path).
+int b200_qmm_grouped_takes_tokens(const b200_qweight* w, int32_t tile_rows);
+// The same matmul with the expert-sorted activation rows read from the unsorted token matrix:
+// row p = d_tokens[d_order[p] / top_k].
+b200_status b200_qmm_grouped_from_tokens(const b200_qweight* w, const void* d_tokens, const int* d_order, int32_t top_k,
+                                         int32_t rows, void* d_y, int32_t epilogue, const float* d_row_scales,
+                                         float swiglu_limit, const int4* d_items, const int* d_n_items, int32_t max_items,
+                                         int32_t tile_rows, void* stream);
