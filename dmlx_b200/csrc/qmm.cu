@@ -1985,9 +1985,10 @@ static b200_status qmm_entry(const b200_qweight* w, const void* d_x, int32_t row
       const int tn = std::min(256, ((rows + 15) / 16) * 16), pair_ctas = ((w->nt + 1) / 2) * ((rows + tn - 1) / tn);
       if (ensure_state(0) != B200_OK) return B200_ERR_CUDA;
       const bool one_wave = pair_ctas <= g_sms && pair_ctas * 2 >= g_sms;
-      // prefill chunks (512 rows and more): the tile-pair kernel is ahead on every projection shape
-      // (gate/up 126 vs 172 us at 512 rows, 317 vs 337 us at 1024; down 113 vs 121 us at 1024)
-      path = (one_wave || rows >= 512 || w->mode == B200_Q_BF16) ? B200_QMM_TCGEN05_X2 : B200_QMM_TCGEN05_TMEM_A;
+      // more than one 256-row token tile (prefill chunks): the tile-pair kernel is ahead or level on
+      // every projection shape (gate/up 122 vs 158 us at 384 rows, 126 vs 172 us at 512, 317 vs 337 us
+      // at 1024; down 113 vs 121 us at 1024)
+      path = (one_wave || rows > 256 || w->mode == B200_Q_BF16) ? B200_QMM_TCGEN05_X2 : B200_QMM_TCGEN05_TMEM_A;
     } else {
       path = w->mode == B200_Q_BF16 ? B200_QMM_TCGEN05 : B200_QMM_TCGEN05_TMEM_A;
     }
