@@ -1950,6 +1950,8 @@ extern "C" b200_status b200_qmm_residual_norm(const b200_qweight* w, const void*
                                               const void* d_residual, const void* d_norm_weight, float eps, void* d_normed,
                                               void* stream) {
   if (rows <= 0) return B200_OK;
+  if (!d_residual || !d_norm_weight || !d_normed || !d_y) { b200_set_error("qmm_residual_norm: null argument"); return B200_ERR_INVALID_ARGUMENT; }
+  if (w->n % 8 != 0) { b200_set_error("qmm_residual_norm: N must be a multiple of 8"); return B200_ERR_INVALID_ARGUMENT; }
   g_finish_did_norm = false;
   b200_status st = qmm_entry(w, d_x, rows, d_y, B200_EPI_RESIDUAL, d_residual, 0.f, B200_QMM_AUTO, stream, d_norm_weight, eps, d_normed);
   if (st != B200_OK) return st;
