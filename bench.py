@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-Prints ONE JSON line (rank 0).  Workloads (BASELINE.json `configs`, synthetic seeded inputs):
+Prints ONE JSON line (rank 0).  Workloads (synthetic seeded inputs):
   llama8b_int4 (default) : config 3, the Llama-3-8B-shaped int4 continuous-batching decode step at a
       fixed live-batch snapshot — 256 requests in flight, each with its lognormal prompt
       (mean 1024, sigma 0.6, clipped 32..8192) plus a uniform share of its 128..1024 output tokens

@@ -56,6 +56,7 @@ ERR_NO_DEVICE = 8
 ERR_UNSUPPORTED = 9
 ERR_CAPACITY = 10
 ERR_DEVICE_FLAGGED = 11
+ERR_CANCELLED = 12
 
 
 def _sig(name, restype, *argtypes):
@@ -171,6 +172,7 @@ _sig("b200_prng_next_f32", f32, P(u64))
 _sig("b200_qweight_create", i32, i32, i32, i32, i32, vp, vp, vp, P(vp))
 _sig("b200_qweight_random", i32, i32, i32, i32, i32, u32, P(vp))
 _sig("b200_qweight_destroy", None, vp)
+_sig("b200_qweight_export", i32, vp, i32, vp, vp, vp)
 _sig("b200_qmm", i32, vp, vp, i32, vp, i32, vp, f32, i32, vp)
 _sig("b200_qmm_residual_norm", i32, vp, vp, i32, vp, vp, vp, f32, vp, vp)
 
@@ -241,6 +243,19 @@ _sig("b200_sched_bm_sync", i32, vp)
 _sig("b200_engine_set_sampler", i32, vp, u64, f32, i32, f32, u64)
 _sig("b200_engine_set_max_step_tokens", None, vp, u64)
 _sig("b200_engine_shared_tokens", u64, vp, u64)
+_sig("b200_engine_last_batch", u64, vp, P(u64), u64)
+_sig("b200_engine_cancel", i32, vp, u64)
+_sig("b200_engine_request_status", i32, vp, u64, P(i32))
+_sig("b200_engine_pressure_stats", None, vp, P(u64), P(u64), P(u64))
+_sig("b200_request_error", i32, vp)
+_sig("b200_sched_bm_note_free", None, vp, u64)
+_sig("b200_scheduler_remove", i32, vp, vp, i32)
+_sig("b200_scheduler_preempt", i32, vp, vp)
+_sig("b200_scheduler_hold_admission", None, vp, i32)
+_sig("b200_scheduler_running", u64, vp, P(vp), u64)
+_sig("b200_kv_limits", i32, vp, P(i32), P(i32))
+_sig("b200_qmm_debug_set_error_word", i32, i32, i32)
+_sig("b200_qmm_debug_wait_runs_out", i32, i32, vp)
 
 
 class B200Error(RuntimeError):

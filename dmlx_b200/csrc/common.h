@@ -29,6 +29,9 @@ extern long long g_b200_launch_counter;
       return B200_ERR_CUDA;                                                                 \
     }                                                                                       \
   } while (0)
-// Returns B200_ERR_NO_DEVICE (with a message) unless a CUDA device is usable.
+// Returns B200_ERR_NO_DEVICE (with a message) unless a CUDA device is usable, and B200_ERR_UNSUPPORTED
+// when the current device is not the one this process first used the library on.
 b200_status b200_require_device();
+// The same without binding the process to a device (entry points that keep per-device state).
+b200_status b200_require_any_device();
 #endif

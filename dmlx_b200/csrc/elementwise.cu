@@ -146,9 +146,14 @@ __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ src, const 
   for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dp[i] = sp[i];
 }
 
+// `flags` (optional) points at the pool's state words: a step whose page reservation or attention was
+// flagged has computed its tokens from stale pages, so the sequences keep the input token they had
+// and the step can be run again once the cause (an exhausted pool) is gone.
 __global__ void scatter_tokens_kernel(const uint32_t* __restrict__ next, const b200_pack_desc* __restrict__ desc,
-                                      uint32_t* __restrict__ last_token, int n_req) {
+                                      uint32_t* __restrict__ last_token, int n_req, const int* __restrict__ flags,
+                                      int flag_a, int flag_b) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (flags && (flags[flag_a] != 0 || flags[flag_b] != 0)) return;
   if (i < n_req && desc[i].count > 0) last_token[desc[i].seq_slot] = next[i];
 }
 
@@ -164,9 +169,10 @@ b200_status b200_gather_rows(const void* d_src, const int32_t* d_idx, void* d_ds
 
 // The sampled token of request i becomes the next decode input of its sequence slot.
 b200_status b200_scatter_tokens(const uint32_t* d_next, const b200_pack_desc* d_desc, uint32_t* d_last_token, int32_t n_req,
-                                void* stream) {
+                                const int* d_flags, int flag_a, int flag_b, void* stream) {
   if (n_req <= 0) return B200_OK;
-  scatter_tokens_kernel<<<(n_req + 127) / 128, 128, 0, (cudaStream_t)stream>>>(d_next, d_desc, d_last_token, n_req);
+  scatter_tokens_kernel<<<(n_req + 127) / 128, 128, 0, (cudaStream_t)stream>>>(d_next, d_desc, d_last_token, n_req, d_flags,
+                                                                              flag_a, flag_b);
   B200_LAUNCH_CHECK();
   return B200_OK;
 }

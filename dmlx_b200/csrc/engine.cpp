@@ -39,6 +39,12 @@ struct b200_engine {
   struct Sampler { float temperature; int32_t top_k; float top_p; uint64_t prng[4]; };
   std::unordered_map<uint64_t, Sampler> samplers;
   std::vector<b200_sample_params> samp_rows;
+  // Pool pressure: requests left out of a step because their page growth did not fit, and running
+  // requests sent back to the waiting queue to make room (their cache is recomputed later).
+  uint64_t n_deferred = 0, n_preempted = 0, n_failed = 0;
+  bool pressure = false;  // the previous step left a running request out or preempted one: admit nobody new
+  int32_t max_pages_per_seq = 0, pool_pages = 0;
+  std::vector<b200_request*> running_tmp;
 };
 
 namespace {
@@ -58,6 +64,15 @@ std::vector<uint64_t> prompt_chain(const std::vector<uint32_t>& prompt) {
 // Tokens of a request whose K/V are in the pool.
 uint64_t cached_tokens(const b200_request* r) {
   return b200_request_state(r) == B200_REQ_PREFILLING ? b200_request_prefill_offset(r) : b200_request_prompt_len(r);
+}
+
+// Pages a request holds before the step (one from admission, then ceil(len / 32), shared ones included)
+// and the pages its rows of this step add (page-table growth of src/kvcache/paged.zig:525-531).
+uint64_t pages_for(uint64_t tokens) { return (tokens + kPageTokens - 1) / kPageTokens; }
+uint64_t pages_held(uint64_t len) { return std::max<uint64_t>(1, pages_for(len)); }
+uint64_t pages_needed(uint64_t len, uint64_t count) {
+  const uint64_t after = pages_for(len + count), held = pages_held(len);
+  return after > held ? after - held : 0;
 }
 
 // A request about to run its first prefill chunk takes over the longest run of full prompt blocks
@@ -102,6 +117,9 @@ b200_engine* b200_engine_create(b200_llama* model, b200_kv* kv, uint64_t max_pre
   e->max_prefill = std::max<uint64_t>(1, max_prefill_tokens);
   e->bm = b200_sched_bm_create_with_kv(kv);
   if (!e->bm) { delete e; return nullptr; }
+  int32_t max_seqs = 0, page_size = 0;
+  b200_kv_dims(kv, &e->pool_pages, &max_seqs);
+  b200_kv_limits(kv, &e->max_pages_per_seq, &page_size);
   e->sched = b200_scheduler_create(e->bm, e->max_prefill);
   return e;
 }
@@ -118,6 +136,13 @@ b200_status b200_engine_submit(b200_engine* e, uint64_t id, const uint32_t* prom
                                const uint32_t* stop_tokens, uint64_t n_stop) {
   if (e->requests.count(id)) { b200_set_error("engine: request id %llu already exists", (unsigned long long)id); return B200_ERR_INVALID_ARGUMENT; }
   if (n_prompt == 0 || max_tokens == 0) { b200_set_error("engine: empty prompt or max_tokens 0"); return B200_ERR_INVALID_ARGUMENT; }
+  // A request whose prompt alone can never fit is refused here instead of blocking the queue for ever.
+  const uint64_t most = std::min<uint64_t>((uint64_t)e->max_pages_per_seq, (uint64_t)e->pool_pages) * kPageTokens;
+  if (n_prompt + 1 > most) {
+    b200_set_error("engine: a prompt of %llu tokens exceeds what one sequence can hold (%llu tokens)", (unsigned long long)n_prompt,
+                   (unsigned long long)most);
+    return B200_ERR_CAPACITY;
+  }
   b200_request* r = b200_request_create(id, prompt, n_prompt, max_tokens, stop_tokens, n_stop);
   e->requests[id] = r;
   return b200_scheduler_add_request(e->sched, r);
@@ -125,43 +150,136 @@ b200_status b200_engine_submit(b200_engine* e, uint64_t id, const uint32_t* prom
 
 uint64_t b200_engine_active_count(const b200_engine* e) { return b200_scheduler_active_count(e->sched); }
 
+namespace {
+// Ends one request on its own account: out of the scheduler, pages back to the pool, the reason kept
+// for b200_engine_request_status (per-request isolation, src/engine/engine_loop.zig:687-754).
+b200_status end_request(b200_engine* e, b200_request* r, int32_t reason) {
+  const int32_t slot = b200_request_kv_slot(r);
+  b200_status st = b200_scheduler_remove(e->sched, r, reason);
+  if (st != B200_OK) return st;
+  if (slot >= 0) {
+    auto it = e->live.find(slot);
+    if (it != e->live.end() && it->second.req == r) e->live.erase(it);
+  }
+  return B200_OK;
+}
+}  // namespace
+
 b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t cap, uint64_t* n_out, void* stream) {
   *n_out = 0;
-  const uint64_t active = b200_scheduler_active_count(e->sched);
-  if (active == 0) return B200_OK;
-  e->prefill.resize(active);
-  e->decode.resize(active);
-  uint64_t np = 0, nd = 0, need = 0;
-  b200_status st = b200_scheduler_schedule(e->sched, e->prefill.data(), &np, e->decode.data(), &nd, active, &need);
-  if (st != B200_OK) return st;
-  if (np + nd == 0) return B200_OK;
-  // Prefill requests take part in this step in scheduler order while the step's token budget lasts
-  // (decode rows always do; at least one prefill chunk is taken so that the loop makes progress).  A
-  // request left out keeps its cursor: postprocess only advances requests it gets an output for.
-  {
-    uint64_t used = nd, kept = 0;
-    for (uint64_t i = 0; i < np; ++i) {
-      b200_request* r = e->prefill[i];
-      b200_engine::Live self;
-      bool fresh = false, shared = false;
-      if (e->share_prefix) {
-        auto it = e->live.find(b200_request_kv_slot(r));
-        fresh = !(it != e->live.end() && it->second.req == r) && b200_request_prefill_offset(r) == 0;
-        if (fresh) {
-          st = try_share_prefix(e, r, &self, &shared);
-          if (st != B200_OK) return st;
-          if (shared) e->live[b200_request_kv_slot(r)] = self;  // it holds pages now, whether or not it runs this step
+  b200_status st = B200_OK;
+  uint64_t np = 0, nd = 0;
+  // Up to a few rounds: a round that finds every runnable request blocked on page growth sends the
+  // youngest running request back to the waiting queue and schedules again.
+  bool pressure_now = false;
+  for (int round = 0;; ++round) {
+    const uint64_t active = b200_scheduler_active_count(e->sched);
+    if (active == 0) return B200_OK;
+    // While running requests are short of pages nobody new is admitted: a newcomer would take the page
+    // an older request is waiting for (the reference admits on one free block, src/scheduler.zig:291).
+    b200_scheduler_hold_admission(e->sched, (e->pressure || pressure_now) && b200_scheduler_running_count(e->sched) > 0);
+    e->prefill.resize(active);
+    e->decode.resize(active);
+    uint64_t need = 0;
+    np = nd = 0;
+    st = b200_scheduler_schedule(e->sched, e->prefill.data(), &np, e->decode.data(), &nd, active, &need);
+    b200_scheduler_hold_admission(e->sched, 0);
+    if (st != B200_OK) return st;
+    if (np + nd == 0) { e->pressure = false; return B200_OK; }
+    // A sequence that has reached the length its page table can hold ends here, alone (CacheOverflow,
+    // src/kvcache/quantized.zig:135); the others go on.
+    {
+      const uint64_t most = (uint64_t)e->max_pages_per_seq * kPageTokens;
+      uint64_t kept = 0;
+      for (uint64_t i = 0; i < nd; ++i) {
+        b200_request* r = e->decode[i];
+        if (b200_request_seq_len(r) > most) {
+          if ((st = end_request(e, r, B200_ERR_CAPACITY)) != B200_OK) return st;
+          e->n_failed += 1;
+        } else {
+          e->decode[kept++] = r;
         }
       }
-      const uint64_t len = b200_request_current_prefill_chunk_len(r, e->max_prefill);
-      if (e->max_step_tokens > 0 && used + len > e->max_step_tokens && (kept > 0 || nd > 0)) continue;  // tries again next step
-      if (fresh && !shared) e->live[b200_request_kv_slot(r)] = std::move(self);
-      used += len;
-      e->prefill[kept++] = r;
+      nd = kept;
     }
-    np = kept;
+    // Page budget of the step.  Decode rows come first (oldest request first), then prefill chunks in
+    // scheduler order while the step's token budget lasts; a request whose growth does not fit is
+    // left out of this step and keeps its cursor (postprocess only advances requests it gets an
+    // output for).
+    uint64_t free_pages = b200_sched_bm_free_count(e->bm);
+    {
+      uint64_t kept = 0;
+      for (uint64_t i = 0; i < nd; ++i) {
+        b200_request* r = e->decode[i];
+        const uint64_t grow = pages_needed(b200_request_seq_len(r) - 1, 1);
+        if (grow > free_pages) { e->n_deferred += 1; pressure_now = true; continue; }
+        free_pages -= grow;
+        e->decode[kept++] = r;
+      }
+      nd = kept;
+    }
+    {
+      uint64_t used = nd, kept = 0;
+      for (uint64_t i = 0; i < np; ++i) {
+        b200_request* r = e->prefill[i];
+        b200_engine::Live self;
+        bool fresh = false, shared = false;
+        if (e->share_prefix) {
+          auto it = e->live.find(b200_request_kv_slot(r));
+          fresh = !(it != e->live.end() && it->second.req == r) && b200_request_prefill_offset(r) == 0;
+          if (fresh) {
+            st = try_share_prefix(e, r, &self, &shared);
+            if (st != B200_OK) return st;
+            if (shared) {
+              e->live[b200_request_kv_slot(r)] = self;  // it holds pages now, whether or not it runs this step
+              if ((st = b200_sched_bm_sync(e->bm)) != B200_OK) return st;
+              free_pages = std::min<uint64_t>(free_pages, b200_sched_bm_free_count(e->bm));
+            }
+          }
+        }
+        const uint64_t len = b200_request_current_prefill_chunk_len(r, e->max_prefill);
+        if (e->max_step_tokens > 0 && used + len > e->max_step_tokens && (kept > 0 || nd > 0)) continue;  // tries again next step
+        const uint64_t grow = pages_needed(b200_request_prefill_offset(r), len);
+        if (grow > free_pages) { e->n_deferred += 1; pressure_now = true; continue; }
+        free_pages -= grow;
+        if (fresh && !shared) e->live[b200_request_kv_slot(r)] = std::move(self);
+        used += len;
+        e->prefill[kept++] = r;
+      }
+      np = kept;
+    }
+    if (np + nd > 0) break;
+    pressure_now = true;
+    // Nothing fits: every running request waits for a page nobody will free.  The youngest running
+    // request gives its pages back and is prefilled again later; a request that is alone and still
+    // does not fit can never run in this pool and fails on its own.
+    e->running_tmp.resize(active);
+    const uint64_t n_run = b200_scheduler_running(e->sched, e->running_tmp.data(), active);
+    if (n_run == 0 || round >= 64) { e->pressure = true; return B200_OK; }
+    b200_request* victim = e->running_tmp[n_run - 1];
+    if (n_run == 1) {
+      if ((st = end_request(e, victim, B200_ERR_INSUFFICIENT_BLOCKS)) != B200_OK) return st;
+      e->n_failed += 1;
+    } else {
+      const int32_t slot = b200_request_kv_slot(victim);
+      if ((st = b200_scheduler_preempt(e->sched, victim)) != B200_OK) return st;
+      auto it = e->live.find(slot);
+      if (it != e->live.end() && it->second.req == victim) e->live.erase(it);
+      e->shared_tokens.erase(b200_request_id(victim));
+      e->n_preempted += 1;
+    }
   }
-  if (np + nd == 0) return B200_OK;
+  // Tokens that will join a request's output this step (every decode row, and a prefill row whose
+  // chunk is the last one, src/scheduler.zig:338-349) must fit the caller's array: checked before
+  // anything is written to the cache.
+  {
+    uint64_t joining = nd;
+    for (uint64_t i = 0; i < np; ++i) {
+      b200_request* r = e->prefill[i];
+      if (b200_request_prefill_offset(r) + b200_request_current_prefill_chunk_len(r, e->max_prefill) >= b200_request_prompt_len(r)) joining += 1;
+    }
+    if (joining > cap) { b200_set_error("engine step: output array holds %llu tokens, %llu needed", (unsigned long long)cap, (unsigned long long)joining); return B200_ERR_CAPACITY; }
+  }
   e->descs.clear();
   e->flat.clear();
   for (uint64_t i = 0; i < np; ++i) {  // prefill requests first (src/batch_builder.zig:100-111)
@@ -202,22 +320,21 @@ b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t ca
   }
   st = b200_llama_step(e->model, e->kv, e->descs.data(), (int32_t)e->descs.size(), e->flat.data(), (int32_t)e->flat.size(),
                        e->next.data(), &e->last_free_pages, stream);
+  // A flagged step has changed neither the pool (the reservation is all or nothing) nor any sequence's
+  // next input token: the scheduler state is left as it was and the caller may step again.
   if (st != B200_OK) return st;
+  b200_sched_bm_note_free(e->bm, (uint64_t)e->last_free_pages);
+  e->pressure = pressure_now;
   e->outs.clear();
   for (uint64_t i = 0; i < np + nd; ++i) {
     b200_request* r = i < np ? e->prefill[i] : e->decode[i - np];
     e->outs.push_back(b200_token_output{b200_request_id(r), e->next[i], 0});
   }
-  // Tokens that become part of a request's output this step: every decode row, and a prefill row
-  // whose chunk was the last one (src/scheduler.zig:338-349).
   for (uint64_t i = 0; i < np + nd; ++i) {
     b200_request* r = i < np ? e->prefill[i] : e->decode[i - np];
     const bool last_chunk = i < np && b200_request_prefill_offset(r) + b200_request_current_prefill_chunk_len(r, e->max_prefill) >=
                                           b200_request_prompt_len(r);
-    if (i >= np || last_chunk) {
-      if (*n_out >= cap) { b200_set_error("engine step: output array holds %llu tokens", (unsigned long long)cap); return B200_ERR_CAPACITY; }
-      out[(*n_out)++] = e->outs[i];
-    }
+    if (i >= np || last_chunk) out[(*n_out)++] = e->outs[i];
   }
   st = b200_scheduler_postprocess(e->sched, e->outs.data(), e->outs.size());
   if (e->share_prefix) {  // finished requests have given their slot back
@@ -225,6 +342,37 @@ b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t ca
       it = it->second.req && b200_request_state(it->second.req) == B200_REQ_DONE ? e->live.erase(it) : std::next(it);
   }
   return st;
+}
+
+// Cancels a request wherever it is (waiting, mid-prefill or decoding): it leaves the scheduler at once,
+// its pages return to the pool and the tokens it has produced stay readable
+// (RequestState.cancelled, src/engine/request_state.zig:118,182-189; checked by the engine thread at
+// src/engine/engine_loop.zig:240-243).  The engine is single-owner, so this is called between steps.
+b200_status b200_engine_cancel(b200_engine* e, uint64_t id) {
+  auto it = e->requests.find(id);
+  if (it == e->requests.end()) { b200_set_error("engine: unknown request %llu", (unsigned long long)id); return B200_ERR_INVALID_ARGUMENT; }
+  if (b200_request_state(it->second) == B200_REQ_DONE) return B200_OK;
+  return end_request(e, it->second, B200_ERR_CANCELLED);
+}
+
+b200_status b200_engine_request_status(const b200_engine* e, uint64_t id, int32_t* status) {
+  auto it = e->requests.find(id);
+  if (it == e->requests.end()) { b200_set_error("engine: unknown request %llu", (unsigned long long)id); return B200_ERR_INVALID_ARGUMENT; }
+  *status = b200_request_error(it->second);
+  return B200_OK;
+}
+
+// Request ids of the last step's batch in descriptor order (prefill chunks first, then decode rows):
+// row i of b200_llama_last_logits belongs to ids[i].
+uint64_t b200_engine_last_batch(const b200_engine* e, uint64_t* ids, uint64_t cap) {
+  for (uint64_t i = 0; i < e->outs.size() && i < cap; ++i) ids[i] = e->outs[i].request_id;
+  return e->outs.size();
+}
+
+void b200_engine_pressure_stats(const b200_engine* e, uint64_t* deferred, uint64_t* preempted, uint64_t* failed) {
+  if (deferred) *deferred = e->n_deferred;
+  if (preempted) *preempted = e->n_preempted;
+  if (failed) *failed = e->n_failed;
 }
 
 b200_status b200_engine_park_slot(b200_engine* e, int32_t* out_slot) { return b200_sched_bm_park_slot(e->bm, out_slot); }

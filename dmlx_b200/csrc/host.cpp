@@ -46,6 +46,7 @@ const char* b200_status_name(b200_status s) {
     case B200_ERR_UNSUPPORTED: return "Unsupported";
     case B200_ERR_CAPACITY: return "Capacity";
     case B200_ERR_DEVICE_FLAGGED: return "DeviceFlagged";
+    case B200_ERR_CANCELLED: return "Cancelled";
     default: return "Unknown";
   }
 }
@@ -280,6 +281,10 @@ struct b200_request {
   std::vector<uint32_t> stop;
   uint64_t prefill_offset = 0;
   int32_t kv_slot = -1;
+  // Tokens of `generated` that a preemption appended to `prompt` (their K/V are recomputed by the
+  // request's second prefill); they still count as output but no longer as decode positions.
+  uint64_t folded = 0;
+  int32_t error = B200_OK;  // why the request ended early (cancelled, or failed on its own)
 };
 
 extern "C" {
@@ -298,7 +303,8 @@ uint64_t b200_request_id(const b200_request* r) { return r->id; }
 int32_t b200_request_state(const b200_request* r) { return r->state; }
 uint64_t b200_request_prefill_offset(const b200_request* r) { return r->prefill_offset; }
 uint64_t b200_request_prompt_len(const b200_request* r) { return r->prompt.size(); }
-uint64_t b200_request_seq_len(const b200_request* r) { return r->prefill_offset + r->generated.size(); }
+uint64_t b200_request_seq_len(const b200_request* r) { return r->prefill_offset + r->generated.size() - r->folded; }
+int32_t b200_request_error(const b200_request* r) { return r->error; }
 int32_t b200_request_is_stop_token(const b200_request* r, uint32_t t) {
   return std::find(r->stop.begin(), r->stop.end(), t) != r->stop.end();
 }
@@ -374,7 +380,12 @@ struct b200_sched_bm {
       int32_t slot = free_slots.back();
       std::vector<int32_t> ids(n);
       b200_status st = b200_kv_alloc(kv, slot, (int32_t)n, ids.data());
-      if (st != B200_OK) return st;
+      if (st != B200_OK) {
+        // the cached free count was stale (pages taken by decode growth since it was read): refresh it
+        // so that the caller sees the pool as it is
+        if (st == B200_ERR_INSUFFICIENT_BLOCKS) refresh_kv();
+        return st;
+      }
       free_slots.pop_back();
       req->kv_slot = slot;
       for (int32_t id : ids) req->block_ids.push_back((uint64_t)id);
@@ -456,6 +467,13 @@ b200_status b200_sched_bm_unpark_slot(b200_sched_bm* bm, int32_t slot) {
   return bm->refresh_kv();
 }
 b200_status b200_sched_bm_sync(b200_sched_bm* bm) { return bm->kv ? bm->refresh_kv() : B200_OK; }
+// The same without reading the device: the caller already holds the pool's free count (a model step
+// returns it), e.g. after decode growth took pages behind the scheduler's back.
+void b200_sched_bm_note_free(b200_sched_bm* bm, uint64_t free_pages) {
+  if (!bm->kv) return;
+  bm->kv_free_cached = (int32_t)free_pages;
+  bm->used_blocks = bm->total_blocks - free_pages;
+}
 int32_t b200_sched_bm_can_allocate(const b200_sched_bm* bm, uint64_t n) { return bm->can_allocate(n); }
 uint64_t b200_sched_bm_free_count(const b200_sched_bm* bm) { return bm->free_count(); }
 uint64_t b200_sched_bm_total_blocks(const b200_sched_bm* bm) { return bm->total_blocks; }
@@ -471,6 +489,7 @@ struct b200_scheduler {
   b200_sched_bm* bm = nullptr;
   uint64_t max_prefill_tokens = 0;
   uint64_t blocks_per_request = 1;
+  bool hold_admission = false;  // waiting requests stay where they are (set by a caller under pool pressure)
 };
 
 extern "C" {
@@ -510,8 +529,15 @@ b200_status b200_scheduler_schedule(b200_scheduler* s, b200_request** prefill_ou
   size_t kept = 0;
   for (size_t i = 0; i < s->waiting.size(); ++i) {
     b200_request* r = s->waiting[i];
-    if (s->bm->can_allocate(s->blocks_per_request)) {
+    if (!s->hold_admission && s->bm->can_allocate(s->blocks_per_request)) {
       b200_status st = s->bm->allocate(r, s->blocks_per_request);
+      if (st == B200_ERR_INSUFFICIENT_BLOCKS && s->bm->kv) {
+        // The device pool turned out to be empty (its cached free count was stale): the request keeps
+        // waiting, exactly as if canAllocate had said no (src/scheduler.zig:291-293, 306-309).
+        *blocks_needed += s->blocks_per_request;
+        s->waiting[kept++] = r;
+        continue;
+      }
       if (st != B200_OK) {
         s->waiting.erase(s->waiting.begin() + kept, s->waiting.begin() + i);
         return st;
@@ -562,6 +588,56 @@ b200_status b200_scheduler_postprocess(b200_scheduler* s, const b200_token_outpu
   return B200_OK;
 }
 
+// Take a request out of the scheduler before it has finished (cancellation, or a failure that is its
+// own: src/engine/request_state.zig:118,182-189; src/engine/engine_loop.zig:687-754 handleBatchError):
+// its blocks go back to the pool, its state becomes done with `error` as the reason, everything else
+// keeps running.
+b200_status b200_scheduler_remove(b200_scheduler* s, b200_request* r, int32_t error) {
+  auto drop = [&](std::vector<b200_request*>& v) {
+    auto it = std::find(v.begin(), v.end(), r);
+    if (it == v.end()) return false;
+    v.erase(it);
+    return true;
+  };
+  const bool was_running = drop(s->running);
+  if (!was_running && !drop(s->waiting)) {
+    b200_set_error("scheduler: request %llu is not active", (unsigned long long)r->id);
+    return B200_ERR_INVALID_ARGUMENT;
+  }
+  if (was_running) s->bm->release(r);
+  r->state = B200_REQ_DONE;
+  r->error = error;
+  return B200_OK;
+}
+
+// Preemption by recomputation (no reference counterpart: the reference admits on one free block and
+// has no answer when decode growth finds the pool empty, src/scheduler.zig:242,291-293 vs
+// src/kvcache/paged.zig:525-531).  A running request gives all its blocks back and returns to the head
+// of the waiting queue; the tokens it has generated so far join its prompt, so that its next prefill
+// rebuilds the same cache and its output continues where it stopped.
+b200_status b200_scheduler_preempt(b200_scheduler* s, b200_request* r) {
+  auto it = std::find(s->running.begin(), s->running.end(), r);
+  if (it == s->running.end()) {
+    b200_set_error("scheduler: request %llu is not running", (unsigned long long)r->id);
+    return B200_ERR_INVALID_ARGUMENT;
+  }
+  s->running.erase(it);
+  s->bm->release(r);
+  r->prompt.insert(r->prompt.end(), r->generated.begin() + r->folded, r->generated.end());
+  r->folded = r->generated.size();
+  r->prefill_offset = 0;
+  r->state = B200_REQ_WAITING;
+  s->waiting.insert(s->waiting.begin(), r);
+  return B200_OK;
+}
+
+void b200_scheduler_hold_admission(b200_scheduler* s, int32_t on) { s->hold_admission = on != 0; }
+
+uint64_t b200_scheduler_running(const b200_scheduler* s, b200_request** out, uint64_t cap) {
+  for (uint64_t i = 0; i < s->running.size() && i < cap; ++i) out[i] = s->running[i];
+  return s->running.size();
+}
+
 uint64_t b200_scheduler_active_count(const b200_scheduler* s) { return s->running.size() + s->waiting.size(); }
 uint64_t b200_scheduler_waiting_count(const b200_scheduler* s) { return s->waiting.size(); }
 uint64_t b200_scheduler_running_count(const b200_scheduler* s) { return s->running.size(); }
@@ -605,7 +681,7 @@ static Span request_span(const b200_request* r, bool chunked, uint64_t max_prefi
       else
         return sp;
       sp.count = 1;
-      uint64_t sl = r->prefill_offset + r->generated.size();
+      uint64_t sl = r->prefill_offset + r->generated.size() - r->folded;
       sp.base_pos = sl > 0 ? sl - sp.count : 0;
       return sp;
     }

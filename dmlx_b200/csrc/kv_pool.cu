@@ -23,8 +23,9 @@
 #include "tma.cuh"
 
 static int g_device_state = -1;  // -1 unknown, 0 none, 1 ok
+static int g_bound_device = -1;  // the device this process first used the library on
 
-b200_status b200_require_device() {
+b200_status b200_require_any_device() {
   if (g_device_state < 0) {
     int n = 0;
     cudaError_t e = cudaGetDeviceCount(&n);
@@ -38,7 +39,24 @@ b200_status b200_require_device() {
   return B200_OK;
 }
 
-extern "C" int32_t b200_device_available(void) { return b200_require_device() == B200_OK; }
+// The library keeps per-process caches (scratch buffers, shared-memory opt-ins, SM count) that belong
+// to one device: the first device a compute entry point runs on is the process's device from then on,
+// and a call made with another device current is refused instead of running with the wrong pointers.
+b200_status b200_require_device() {
+  b200_status st = b200_require_any_device();
+  if (st != B200_OK) return st;
+  int dev = 0;
+  B200_CUDA_TRY(cudaGetDevice(&dev));
+  if (g_bound_device < 0) g_bound_device = dev;
+  if (dev != g_bound_device) {
+    b200_set_error("this process uses the library on device %d, the current device is %d (one device per process)",
+                   g_bound_device, dev);
+    return B200_ERR_UNSUPPORTED;
+  }
+  return B200_OK;
+}
+
+extern "C" int32_t b200_device_available(void) { return b200_require_any_device() == B200_OK; }
 
 // ---------------------------------------------------------------------------------------------
 // kernels
@@ -611,6 +629,12 @@ void b200_kv_destroy(b200_kv* kv) {
 b200_status b200_kv_dims(const b200_kv* kv, int32_t* n_pages, int32_t* max_seqs) {
   *n_pages = kv->cfg.n_pages;
   *max_seqs = kv->cfg.max_seqs;
+  return B200_OK;
+}
+
+b200_status b200_kv_limits(const b200_kv* kv, int32_t* max_pages_per_seq, int32_t* page_size) {
+  *max_pages_per_seq = kv->cfg.max_pages_per_seq;
+  *page_size = kv->cfg.page_size;
   return B200_OK;
 }
 

@@ -19,7 +19,7 @@
 
 b200_status b200_gather_rows(const void* d_src, const int32_t* d_idx, void* d_dst, int32_t rows, int32_t hidden, void* stream);
 b200_status b200_scatter_tokens(const uint32_t* d_next, const b200_pack_desc* d_desc, uint32_t* d_last_token, int32_t n_req,
-                                void* stream);
+                                const int* d_flags, int flag_a, int flag_b, void* stream);
 
 namespace {
 struct HostMat {
@@ -50,7 +50,7 @@ struct b200_llama {
   // pinned staging
   b200_pack_desc* h_desc = nullptr;
   uint32_t *h_prefill = nullptr, *h_next = nullptr;
-  int32_t* h_state = nullptr;  // [8] pool state words + [1] matmul error word
+  int32_t* h_state = nullptr;  // [8] pool state words + [2] matmul error words
   // per-request sampler rows of the coming step (set by b200_llama_set_samplers, used once)
   b200_sample_params *d_samp = nullptr, *h_samp = nullptr;
   float* d_logprobs = nullptr;
@@ -87,7 +87,6 @@ struct b200_llama {
   void prof_end(cudaEvent_t e, cudaStream_t s) { if (e) cudaEventRecord(e, s); }
 };
 
-extern "C" b200_status b200_qmm_error_word_async(int32_t* h_out, void* stream);
 
 #define L_ALLOC(ptr, bytes)                                                                            \
   do {                                                                                                 \
@@ -388,7 +387,7 @@ static b200_status llama_forward_eager(b200_llama* m, b200_kv* kv, const b200_pa
   } else {
     STEP(b200_argmax(m->logits, n_req, c.vocab, m->d_next, stream));
   }
-  STEP(b200_scatter_tokens(m->d_next, d_desc, m->d_last_token, n_req, stream));
+  STEP(b200_scatter_tokens(m->d_next, d_desc, m->d_last_token, n_req, kv->dev.state, ST_ERR, ST_ATTN_ERR, stream));
 #undef STEP
 #undef STEP_CAT
   m->launches += g_b200_launch_counter - launches_before;
@@ -430,11 +429,12 @@ b200_status b200_llama_step(b200_llama* m, b200_kv* kv, const b200_pack_desc* h_
   if (st != B200_OK) return st;
   if (n_req > 0) B200_CUDA_TRY(cudaMemcpyAsync(m->h_next, m->d_next, sizeof(uint32_t) * n_req, cudaMemcpyDeviceToHost, s));
   B200_CUDA_TRY(cudaMemcpyAsync(m->h_state, kv->dev.state, sizeof(int32_t) * 8, cudaMemcpyDeviceToHost, s));
-  st = b200_qmm_error_word_async(m->h_state + 8, stream);
+  st = b200_qmm_error_words_async(m->h_state + 8, stream);
   if (st != B200_OK) return st;
   B200_CUDA_TRY(cudaStreamSynchronize(s));
   for (int i = 0; i < n_req; ++i) h_next_tokens[i] = m->h_next[i];
   if (out_free_pages) *out_free_pages = m->h_state[ST_FREE_TOP];
+  if (m->h_state[8] == 0) m->h_state[8] = m->h_state[9];
   if (m->h_state[ST_ERR] != 0 || m->h_state[ST_ATTN_ERR] != 0 || m->h_state[8] != 0) {
     int32_t word = 0;
     b200_kv_error_word(kv, &word);  // clears the pool's words

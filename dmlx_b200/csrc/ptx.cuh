@@ -39,14 +39,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait for the phase with the given parity to complete.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+// Bounded wait for the phase with the given parity to complete: gives up after `limit` failed polls.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if (i > 64) __nanosleep(64);
   }
   return false;
 }
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) { return mbar_wait_limit(bar, parity, kSpinLimit); }
 
 // The same on a shared-space address (hot loops keep barrier addresses as 32-bit integers).
 __device__ __forceinline__ bool mbar_wait_addr(uint32_t bar, uint32_t parity) {

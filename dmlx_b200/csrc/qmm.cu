@@ -1414,10 +1414,18 @@ __global__ void __launch_bounds__(kMxThreads, 1)
 }
 
 // ---- host-side state -------------------------------------------------------------------------------
+// One calling thread and one device per process use the matmul entry points (the library as a whole
+// binds to the first device it is used on, see b200_require_device).  The split-K scratch and the
+// activation buffers of the block-scaled path grow on demand, but a buffer that has been handed to a
+// kernel is never freed: CUDA graphs captured earlier (the decode steps of b200_llama_forward) carry its
+// address in their kernel arguments and keep writing their partial sums there.  An outgrown buffer is
+// retired (kept until the process exits) and new launches use the larger one; no device-wide
+// synchronisation is needed for that.
 float* g_ws = nullptr;
 size_t g_ws_bytes = 0;
 int* g_err = nullptr;
 int g_sms = 0;
+std::vector<void*> g_retired;  // outgrown scratch buffers, still referenced by captured graphs
 
 b200_status ensure_state(size_t ws_bytes) {
   if (!g_err) {
@@ -1428,11 +1436,11 @@ b200_status ensure_state(size_t ws_bytes) {
     B200_CUDA_TRY(cudaDeviceGetAttribute(&g_sms, cudaDevAttrMultiProcessorCount, dev));
   }
   if (ws_bytes > g_ws_bytes) {
-    B200_CUDA_TRY(cudaDeviceSynchronize());
-    if (g_ws) cudaFree(g_ws);
-    g_ws = nullptr;
-    size_t want = std::max(ws_bytes, (size_t)64 << 20);
-    B200_CUDA_TRY(cudaMalloc((void**)&g_ws, want));
+    const size_t want = std::max(ws_bytes + ws_bytes / 4, (size_t)64 << 20);
+    float* grown = nullptr;
+    B200_CUDA_TRY(cudaMalloc((void**)&grown, want));
+    if (g_ws) g_retired.push_back(g_ws);
+    g_ws = grown;
     g_ws_bytes = want;
   }
   return B200_OK;
@@ -1583,6 +1591,52 @@ extern "C" b200_status b200_qweight_random(int32_t mode, int32_t n_experts, int3
   return B200_OK;
 }
 
+// Inverse of b200_qweight_create for one expert: the tile-major blocks go back to the reference's
+// layout on the host (checks of weights that were generated on the device).
+extern "C" b200_status b200_qweight_export(const b200_qweight* w, int32_t expert, void* h_packed, void* h_scales, void* h_biases) {
+  if (expert < 0 || expert >= w->n_experts) { b200_set_error("qweight export: expert %d of %d", expert, w->n_experts); return B200_ERR_INVALID_ARGUMENT; }
+  if (w->mode == B200_Q_AFFINE4_G64 && !h_biases) { b200_set_error("qweight export: affine weights have biases"); return B200_ERR_INVALID_ARGUMENT; }
+  const int nt = w->nt, kc = w->kc, bb = w->block_bytes, n = w->n, k = w->k;
+  const size_t bytes = (size_t)nt * kc * bb;
+  std::vector<unsigned char> host(bytes);
+  B200_CUDA_TRY(cudaMemcpy(host.data(), w->d_blocks + (size_t)expert * bytes, bytes, cudaMemcpyDeviceToHost));
+  const size_t packed_row = w->mode == B200_Q_BF16 ? (size_t)k * 2 : (size_t)k / 2;
+  std::memset(h_packed, 0, packed_row * n);
+  for (int t = 0; t < nt; ++t)
+    for (int c = 0; c < kc; ++c) {
+      const unsigned char* blk = host.data() + ((size_t)t * kc + c) * bb;
+      for (int r = 0; r < kTileN; ++r) {
+        const int row = t * kTileN + r;
+        if (row >= n) break;
+        if (w->mode == B200_Q_BF16) {
+          for (int cc = 0; cc < 8; ++cc)
+            std::memcpy((uint16_t*)h_packed + (size_t)row * k + c * kChunkK + cc * 8, blk + r * 128 + ((cc ^ (r & 7)) << 4), 16);
+          continue;
+        }
+        unsigned char* dst = (unsigned char*)h_packed + (size_t)row * (k / 2) + c * (kChunkK / 2);  // 32 bytes of this chunk
+        for (int plane = 0; plane < 2; ++plane)
+          for (int wd = 0; wd < 4; ++wd) {
+            uint32_t word;
+            std::memcpy(&word, blk + plane * kPlaneBytes + r * 16 + wd * 4, 4);
+            for (int p = 0; p < 8; ++p) {
+              const int col = plane * 32 + wd * 8 + nibble_pos_to_col(p);  // column within the chunk
+              const uint32_t nib = (word >> (4 * p)) & 0xF;
+              dst[col / 2] |= (unsigned char)((col & 1) ? nib << 4 : nib);  // both formats: even column = low nibble
+            }
+          }
+        if (w->mode == B200_Q_AFFINE4_G64) {
+          const uint16_t* sc = (const uint16_t*)(blk + 2 * kPlaneBytes);
+          ((uint16_t*)h_scales)[(size_t)row * (k / 64) + c] = sc[r];
+          ((uint16_t*)h_biases)[(size_t)row * (k / 64) + c] = sc[kTileN + r];
+        } else {
+          ((uint8_t*)h_scales)[(size_t)row * (k / 32) + c * 2] = blk[2 * kPlaneBytes + r * 2];
+          ((uint8_t*)h_scales)[(size_t)row * (k / 32) + c * 2 + 1] = blk[2 * kPlaneBytes + r * 2 + 1];
+        }
+      }
+    }
+  return B200_OK;
+}
+
 extern "C" void b200_qweight_destroy(b200_qweight* w) {
   if (!w) return;
   if (w->d_blocks) cudaFree(w->d_blocks);
@@ -1592,16 +1646,15 @@ extern "C" void b200_qweight_destroy(b200_qweight* w) {
 }
 
 // ---- launch -------------------------------------------------------------------------------------------
-bool g_finish_did_norm = false;  // set by launch_finish when it also wrote the requested RMSNorm
-
-static b200_status launch_finish(const QmmArgs& a, int splits, cudaStream_t s) {
+// Sets a.did_norm when the finish pass also wrote the requested RMSNorm.
+static b200_status launch_finish(QmmArgs& a, int splits, cudaStream_t s) {
   // (decode-sized batches only: one CTA per row does not beat the two separate kernels on prefill chunks)
   if (a.norm_w && a.rows <= 256 && a.epilogue == B200_EPI_RESIDUAL && !a.items && !a.row_scales && a.n % 4 == 0 && a.n <= 16384) {
     int threads = ((a.n / 4 + 31) / 32) * 32;
     while (threads > 1024) threads = (((threads + 1) / 2 + 31) / 32) * 32;
     qmm_finish_rmsnorm_kernel<<<a.rows, threads, 0, s>>>(a, splits);
     B200_LAUNCH_CHECK();
-    g_finish_did_norm = true;
+    a.did_norm = 1;
     return B200_OK;
   }
   const long long threads = (long long)a.rows * a.nt * (kTileN / 4);
@@ -1779,12 +1832,12 @@ static b200_status launch_mx(const b200_qweight* w, QmmArgs& a, int rows, cudaSt
   a.tn = tn;
   const int tts = (rows + tn - 1) / tn;
   const size_t act_bytes = 2 * (size_t)rows * a.k + sizeof(float) * (size_t)rows + 256;
-  if (act_bytes > g_mx_act_bytes) {
-    B200_CUDA_TRY(cudaDeviceSynchronize());
-    if (g_mx_act) cudaFree(g_mx_act);
-    g_mx_act = nullptr; g_mx_act_bytes = 0;
-    const size_t want = std::max(act_bytes, (size_t)32 << 20);
-    B200_CUDA_TRY(cudaMalloc((void**)&g_mx_act, want));
+  if (act_bytes > g_mx_act_bytes) {  // grown buffers replace, never free (see ensure_state)
+    const size_t want = std::max(act_bytes + act_bytes / 4, (size_t)32 << 20);
+    unsigned char* grown = nullptr;
+    B200_CUDA_TRY(cudaMalloc((void**)&grown, want));
+    if (g_mx_act) g_retired.push_back(g_mx_act);
+    g_mx_act = grown;
     g_mx_act_bytes = want;
   }
   unsigned char* hi = g_mx_act;
@@ -1936,11 +1989,11 @@ extern "C" void b200_set_qmm_grouped_block_scaled(int32_t on) { b200_qmm_grouped
 
 static b200_status qmm_entry(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
                              const void* d_residual, float swiglu_limit, int32_t path, void* stream, const void* d_norm_w,
-                             float norm_eps, void* d_norm_out);
+                             float norm_eps, void* d_norm_out, int* did_norm);
 
 extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
                                 const void* d_residual, float swiglu_limit, int32_t path, void* stream) {
-  return qmm_entry(w, d_x, rows, d_y, epilogue, d_residual, swiglu_limit, path, stream, nullptr, 0.f, nullptr);
+  return qmm_entry(w, d_x, rows, d_y, epilogue, d_residual, swiglu_limit, path, stream, nullptr, 0.f, nullptr, nullptr);
 }
 
 extern "C" b200_status b200_rmsnorm(const void* d_x, const void* d_weight, void* d_out, int32_t rows, int32_t hidden, float eps,
@@ -1952,16 +2005,17 @@ extern "C" b200_status b200_qmm_residual_norm(const b200_qweight* w, const void*
   if (rows <= 0) return B200_OK;
   if (!d_residual || !d_norm_weight || !d_normed || !d_y) { b200_set_error("qmm_residual_norm: null argument"); return B200_ERR_INVALID_ARGUMENT; }
   if (w->n % 8 != 0) { b200_set_error("qmm_residual_norm: N must be a multiple of 8"); return B200_ERR_INVALID_ARGUMENT; }
-  g_finish_did_norm = false;
-  b200_status st = qmm_entry(w, d_x, rows, d_y, B200_EPI_RESIDUAL, d_residual, 0.f, B200_QMM_AUTO, stream, d_norm_weight, eps, d_normed);
+  int did_norm = 0;
+  b200_status st = qmm_entry(w, d_x, rows, d_y, B200_EPI_RESIDUAL, d_residual, 0.f, B200_QMM_AUTO, stream, d_norm_weight, eps, d_normed,
+                             &did_norm);
   if (st != B200_OK) return st;
   // kernels that wrote y themselves (no K split) leave the normalisation to the row kernel
-  return g_finish_did_norm ? B200_OK : b200_rmsnorm(d_y, d_norm_weight, d_normed, rows, w->n, eps, stream);
+  return did_norm ? B200_OK : b200_rmsnorm(d_y, d_norm_weight, d_normed, rows, w->n, eps, stream);
 }
 
 static b200_status qmm_entry(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t epilogue,
                              const void* d_residual, float swiglu_limit, int32_t path, void* stream, const void* d_norm_w,
-                             float norm_eps, void* d_norm_out) {
+                             float norm_eps, void* d_norm_out, int* did_norm) {
   b200_status st = b200_require_device();
   if (st != B200_OK) return st;
   if (rows <= 0) return B200_OK;
@@ -2002,24 +2056,29 @@ static b200_status qmm_entry(const b200_qweight* w, const void* d_x, int32_t row
   a.rows = rows; a.n = w->n; a.k = w->k; a.nt = w->nt; a.kc = w->kc; a.epilogue = epilogue; a.swiglu_limit = swiglu_limit;
   a.norm_w = (const __nv_bfloat16*)d_norm_w; a.norm_out = (__nv_bfloat16*)d_norm_out; a.norm_eps = norm_eps;
   cudaStream_t s = (cudaStream_t)stream;
-  if (path == B200_QMM_MXFP4_BLOCK_SCALED) return launch_mx(w, a, rows, s);
-  if (path == B200_QMM_MMA)
-    return w->mode == B200_Q_AFFINE4_G64 ? launch_mma<B200_Q_AFFINE4_G64>(a, rows, s) : launch_mma<B200_Q_MXFP4_G32>(a, rows, s);
-  if (path == B200_QMM_SIMT) {
-    if (w->mode == B200_Q_AFFINE4_G64) return launch_simt<B200_Q_AFFINE4_G64>(a, rows, s);
-    if (w->mode == B200_Q_MXFP4_G32) return launch_simt<B200_Q_MXFP4_G32>(a, rows, s);
-    return launch_simt<B200_Q_BF16>(a, rows, s);
-  }
-  if (path == B200_QMM_TCGEN05_TMEM_A && w->mode != B200_Q_BF16)
-    return w->mode == B200_Q_AFFINE4_G64 ? launch_tca<B200_Q_AFFINE4_G64>(a, rows, s) : launch_tca<B200_Q_MXFP4_G32>(a, rows, s);
-  if (path == B200_QMM_TCGEN05_X2) {
-    if (w->mode == B200_Q_AFFINE4_G64) return launch_tc2<B200_Q_AFFINE4_G64>(a, rows, s);
-    if (w->mode == B200_Q_MXFP4_G32) return launch_tc2<B200_Q_MXFP4_G32>(a, rows, s);
-    return launch_tc2<B200_Q_BF16>(a, rows, s);
-  }
-  if (w->mode == B200_Q_AFFINE4_G64) return launch_tc<B200_Q_AFFINE4_G64>(a, rows, s);
-  if (w->mode == B200_Q_MXFP4_G32) return launch_tc<B200_Q_MXFP4_G32>(a, rows, s);
-  return launch_tc<B200_Q_BF16>(a, rows, s);
+  auto dispatch = [&]() -> b200_status {
+    if (path == B200_QMM_MXFP4_BLOCK_SCALED) return launch_mx(w, a, rows, s);
+    if (path == B200_QMM_MMA)
+      return w->mode == B200_Q_AFFINE4_G64 ? launch_mma<B200_Q_AFFINE4_G64>(a, rows, s) : launch_mma<B200_Q_MXFP4_G32>(a, rows, s);
+    if (path == B200_QMM_SIMT) {
+      if (w->mode == B200_Q_AFFINE4_G64) return launch_simt<B200_Q_AFFINE4_G64>(a, rows, s);
+      if (w->mode == B200_Q_MXFP4_G32) return launch_simt<B200_Q_MXFP4_G32>(a, rows, s);
+      return launch_simt<B200_Q_BF16>(a, rows, s);
+    }
+    if (path == B200_QMM_TCGEN05_TMEM_A && w->mode != B200_Q_BF16)
+      return w->mode == B200_Q_AFFINE4_G64 ? launch_tca<B200_Q_AFFINE4_G64>(a, rows, s) : launch_tca<B200_Q_MXFP4_G32>(a, rows, s);
+    if (path == B200_QMM_TCGEN05_X2) {
+      if (w->mode == B200_Q_AFFINE4_G64) return launch_tc2<B200_Q_AFFINE4_G64>(a, rows, s);
+      if (w->mode == B200_Q_MXFP4_G32) return launch_tc2<B200_Q_MXFP4_G32>(a, rows, s);
+      return launch_tc2<B200_Q_BF16>(a, rows, s);
+    }
+    if (w->mode == B200_Q_AFFINE4_G64) return launch_tc<B200_Q_AFFINE4_G64>(a, rows, s);
+    if (w->mode == B200_Q_MXFP4_G32) return launch_tc<B200_Q_MXFP4_G32>(a, rows, s);
+    return launch_tc<B200_Q_BF16>(a, rows, s);
+  };
+  st = dispatch();
+  if (did_norm) *did_norm = a.did_norm;
+  return st;
 }
 
 // Grouped matmul over an expert-sorted batch: work item i = {expert, first row, rows}; every
@@ -2068,20 +2127,82 @@ b200_status b200_qmm_grouped_from_tokens(const b200_qweight* w, const void* d_to
   return launch_mx(w, a, rows, (cudaStream_t)stream);
 }
 
-// Reads and clears the matmul kernels' error word (a bounded wait that ran out).
+namespace {
+constexpr int kMaxDevices = 64;
+// Error word of the allocation-free entry point, per device (resolved at that entry point's set-up).
+int* g_static_err_ptr[kMaxDevices] = {nullptr};
+
+int* static_err_of_current_device() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  return g_static_err_ptr[dev];
+}
+}  // namespace
+
+// Reads and clears the matmul kernels' error words (a bounded wait that ran out): the word of the
+// kernels launched by b200_qmm / the grouped entry points, and the word of b200_qmm_static_scratch on
+// the current device.
 extern "C" b200_status b200_qmm_error_word(int32_t* out) {
   *out = 0;
-  if (!g_err) return B200_OK;
-  B200_CUDA_TRY(cudaMemcpy(out, g_err, sizeof(int), cudaMemcpyDeviceToHost));
-  if (*out != 0) B200_CUDA_TRY(cudaMemset(g_err, 0, sizeof(int)));
+  int32_t dyn = 0, stat = 0;
+  if (g_err) {
+    B200_CUDA_TRY(cudaMemcpy(&dyn, g_err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (dyn != 0) B200_CUDA_TRY(cudaMemset(g_err, 0, sizeof(int)));
+  }
+  if (int* se = static_err_of_current_device()) {
+    B200_CUDA_TRY(cudaMemcpy(&stat, se, sizeof(int), cudaMemcpyDeviceToHost));
+    if (stat != 0) B200_CUDA_TRY(cudaMemset(se, 0, sizeof(int)));
+  }
+  *out = dyn != 0 ? dyn : stat;
   return B200_OK;
 }
 
-// Queues a copy of the error word into pinned host memory on `stream` (no synchronisation).
-extern "C" b200_status b200_qmm_error_word_async(int32_t* h_out, void* stream) {
-  *h_out = 0;
-  if (!g_err) return B200_OK;
-  B200_CUDA_TRY(cudaMemcpyAsync(h_out, g_err, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+// Queues copies of both error words into pinned host memory on `stream` (no synchronisation, nothing
+// cleared): h_out[0] = b200_qmm's word, h_out[1] = the allocation-free entry point's.
+b200_status b200_qmm_error_words_async(int32_t* h_out, void* stream) {
+  h_out[0] = h_out[1] = 0;
+  if (g_err) B200_CUDA_TRY(cudaMemcpyAsync(h_out, g_err, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  if (int* se = static_err_of_current_device())
+    B200_CUDA_TRY(cudaMemcpyAsync(h_out + 1, se, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  return B200_OK;
+}
+
+namespace {
+// One thread waits, with a short limit, on a barrier that nothing will ever complete: the wait runs
+// out, the thread records that in the error word exactly as the matmul kernels do, and the kernel
+// returns.  Nothing faults or spins for ever; the context stays usable.
+__global__ void wait_runs_out_kernel(int* err, uint32_t polls) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(&bar, 1);
+    ptx::mbar_fence_init();
+    const bool ok = ptx::mbar_wait_limit(&bar, 0, polls);
+    if (!ok) atomicExch(err, B200_ERR_DEVICE_FLAGGED);
+  }
+}
+}  // namespace
+
+// Test hook (no reference counterpart): runs the kernels' give-up path for real.  A kernel waits at
+// most `polls` polls (a fraction of a millisecond for a few thousand) for a barrier nobody arrives on,
+// sets the matmul error word and returns; the caller then reads B200_ERR_DEVICE_FLAGGED through
+// b200_qmm_error_word and goes on using the library.
+extern "C" b200_status b200_qmm_debug_wait_runs_out(int32_t polls, void* stream) {
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (polls <= 0 || polls > (1 << 20)) { b200_set_error("wait probe: 1..2^20 polls"); return B200_ERR_INVALID_ARGUMENT; }
+  st = ensure_state(0);
+  if (st != B200_OK) return st;
+  wait_runs_out_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(g_err, (uint32_t)polls);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+// Test hook (no reference counterpart): the error word a b200_qmm launch would report through, so that a
+// test can check the read-and-clear path without making a kernel time out.
+extern "C" b200_status b200_qmm_debug_set_error_word(int32_t value, int32_t static_scratch_word) {
+  int* dst = static_scratch_word ? static_err_of_current_device() : g_err;
+  if (!dst) { b200_set_error("error word not set up yet (no matmul has run)"); return B200_ERR_INVALID_ARGUMENT; }
+  B200_CUDA_TRY(cudaMemcpy(dst, &value, sizeof(int), cudaMemcpyHostToDevice));
   return B200_OK;
 }
 
@@ -2096,8 +2217,9 @@ extern "C" b200_status b200_qmm_error_word_async(int32_t* h_out, void* stream) {
 // lives in the library image: a fixed device array that every GPU loading the library holds
 // until the process exits.
 //
-//  * Limit: splits * rows * round_up(N,128) * 4 bytes must fit in kStaticScratchBytes (32 MiB);
-//    larger problems are refused with B200_ERR_CAPACITY, nothing is launched.
+//  * Limit: K-splits * round_up(rows, token tile) * round_up(N,128) * 4 bytes must fit in
+//    kStaticScratchBytes (32 MiB), the token tile being min(256, round_up(rows,16)) rows (257 rows
+//    count as 512); larger problems are refused with B200_ERR_CAPACITY, nothing is launched.
 //  * The first call on each device looks up the array's device address (cudaGetSymbolAddress);
 //    make that call before any stream capture.
 //  * All calls share the one array and it keeps whatever the previous call left there.  Every
@@ -2108,10 +2230,9 @@ namespace {
 constexpr size_t kStaticScratchBytes = (size_t)32 << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 static __device__ __align__(256) int g_static_err[64];
-constexpr int kMaxDevices = 64;
 float* g_static_ws[kMaxDevices] = {nullptr};
-int* g_static_err_ptr[kMaxDevices] = {nullptr};
 int g_static_sms[kMaxDevices] = {0};
+int g_static_budget[kMaxDevices][3] = {};  // opt-in dynamic shared memory: a per-device function attribute
 
 template <int MODE>
 b200_status launch_tc_static(QmmArgs& a, int rows, int dev, cudaStream_t s) {
@@ -2121,7 +2242,7 @@ b200_status launch_tc_static(QmmArgs& a, int rows, int dev, cudaStream_t s) {
   const int tiles = a.nt * tts;
   constexpr int kRaw = MODE == B200_Q_BF16 ? 0 : ((block_bytes(MODE) + 127) / 128) * 128;
   const int stage_stride = kTileN * 128 + tn * 128 + kRaw;
-  static int budget[3] = {0, 0, 0};
+  int* budget = g_static_budget[dev];
   if (budget[MODE] == 0) {
     int optin = 0;
     B200_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
@@ -2145,8 +2266,8 @@ b200_status launch_tc_static(QmmArgs& a, int rows, int dev, cudaStream_t s) {
   const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
   const size_t need = (size_t)splits * tts * tn * a.nt * kTileN * sizeof(float);  // token tiles are padded to tn rows
   if (need > kStaticScratchBytes) {
-    b200_set_error("qmm (static scratch): %d rows x N=%d in %d K-splits need %zu bytes of scratch, the built-in array holds %zu",
-                   rows, a.n, splits, need, kStaticScratchBytes);
+    b200_set_error("qmm (static scratch): %d rows (token tiles of %d) x N=%d in %d K-splits need %zu bytes of scratch, the built-in array holds %zu",
+                   rows, tn, a.n, splits, need, kStaticScratchBytes);
     return B200_ERR_CAPACITY;
   }
   a.ws = g_static_ws[dev];
@@ -2164,7 +2285,7 @@ b200_status launch_tc_static(QmmArgs& a, int rows, int dev, cudaStream_t s) {
 extern "C" b200_status b200_qmm_static_scratch(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y,
                                                int32_t epilogue, const void* d_residual, float swiglu_limit,
                                                void* stream) {
-  b200_status st = b200_require_device();
+  b200_status st = b200_require_any_device();
   if (st != B200_OK) return st;
   if (rows <= 0) return B200_OK;
   if (w->n_experts != 1) { b200_set_error("qmm (static scratch): single weights only"); return B200_ERR_INVALID_ARGUMENT; }

@@ -48,6 +48,7 @@ struct QmmArgs {
   int x_gather_div;             //   taken straight from the token matrix while they are split; no sorted copy)
   int mx_expert_rows;           // rows of the code matrix per expert (nt * 128)
   int kc128;                    // K / 128
+  int did_norm;                 // host only: the finish pass also wrote norm_out
 
   __device__ __forceinline__ int row_base_out(int token) const { return token; }
   __device__ __forceinline__ float row_scale(int token) const { return row_scales ? row_scales[token] : 1.0f; }
@@ -64,3 +65,7 @@ b200_status b200_qmm_grouped_from_tokens(const b200_qweight* w, const void* d_to
                                          int32_t rows, void* d_y, int32_t epilogue, const float* d_row_scales,
                                          float swiglu_limit, const int4* d_items, const int* d_n_items, int32_t max_items,
                                          int32_t tile_rows, void* stream);
+// Queues copies of the matmul error words into pinned host memory on `stream` (no synchronisation,
+// nothing cleared): h_out[0] = the word of b200_qmm and the grouped launches, h_out[1] = the word of
+// b200_qmm_static_scratch on the current device.
+b200_status b200_qmm_error_words_async(int32_t* h_out, void* stream);

@@ -307,6 +307,19 @@ class QWeight:
         w._h, w.mode, w.n, w.k, w.n_experts = h.value, mode, n, k, n_experts
         return w
 
+    def export(self, expert: int = 0):
+        """(packed, scales, biases) of one expert in the layouts the constructor takes (b200_qweight_export)."""
+        n, k = self.n, self.k
+        if self.mode == Q_AFFINE4_G64:
+            packed, scales, biases = np.zeros((n, k // 8), np.uint32), np.zeros((n, k // 64), np.uint16), np.zeros((n, k // 64), np.uint16)
+        elif self.mode == Q_MXFP4_G32:
+            packed, scales, biases = np.zeros((n, k // 2), np.uint8), np.zeros((n, k // 32), np.uint8), None
+        else:
+            packed, scales, biases = np.zeros((n, k), np.uint16), np.zeros(1, np.uint8), None
+        _lib.check(lib.b200_qweight_export(self._h, expert, packed.ctypes.data, scales.ctypes.data,
+                                           biases.ctypes.data if biases is not None else None))
+        return packed, scales, biases
+
     def __del__(self):
         if getattr(self, "_h", None) and lib is not None:
             lib.b200_qweight_destroy(self._h)
@@ -612,3 +625,26 @@ class Engine:
 
     def shared_tokens(self, rid: int) -> int:
         return int(lib.b200_engine_shared_tokens(self._h, rid))
+
+    def cancel(self, rid: int):
+        _lib.check(lib.b200_engine_cancel(self._h, rid))
+
+    def request_status(self, rid: int) -> int:
+        out = C.c_int32()
+        _lib.check(lib.b200_engine_request_status(self._h, rid, C.byref(out)))
+        return out.value
+
+    def pressure_stats(self):
+        """(deferred request-steps, preemptions, requests failed on their own)."""
+        d, p, f = C.c_uint64(), C.c_uint64(), C.c_uint64()
+        lib.b200_engine_pressure_stats(self._h, C.byref(d), C.byref(p), C.byref(f))
+        return int(d.value), int(p.value), int(f.value)
+
+    def forget(self, rid: int):
+        lib.b200_engine_forget(self._h, rid)
+
+    def last_batch(self, cap: int = 4096):
+        """Request ids of the last step's batch, in the row order of the model's last logits."""
+        ids = (C.c_uint64 * cap)()
+        n = int(lib.b200_engine_last_batch(self._h, ids, cap))
+        return [int(ids[i]) for i in range(min(n, cap))]

@@ -125,7 +125,6 @@ class Request:
         s, ns = _u32(stop_tokens)
         self._h = lib.b200_request_create(id, p, n, max_tokens, s, ns)
         self.id = id
-        self.prompt_tokens = list(prompt_tokens)
         self.max_tokens = max_tokens
         self.stop_tokens = list(stop_tokens)
 
@@ -159,6 +158,17 @@ class Request:
     @property
     def kv_slot(self) -> int:
         return int(lib.b200_request_kv_slot(self._h))
+
+    @property
+    def error(self) -> int:
+        return int(lib.b200_request_error(self._h))
+
+    @property
+    def prompt_tokens(self) -> List[int]:
+        n = int(lib.b200_request_prompt(self._h, None, 0))
+        out = (C.c_uint32 * max(n, 1))()
+        lib.b200_request_prompt(self._h, out, n)
+        return [int(out[i]) for i in range(n)]
 
     def seq_len(self) -> int:
         return int(lib.b200_request_seq_len(self._h))
@@ -263,6 +273,16 @@ class Scheduler:
 
     def active_count(self) -> int:
         return int(lib.b200_scheduler_active_count(self._h))
+
+    def remove(self, req: Request, error: int) -> None:
+        _lib.check(lib.b200_scheduler_remove(self._h, req._h, error))
+        self._by_handle.pop(req._h, None)
+
+    def preempt(self, req: Request) -> None:
+        _lib.check(lib.b200_scheduler_preempt(self._h, req._h))
+
+    def hold_admission(self, on: bool) -> None:
+        lib.b200_scheduler_hold_admission(self._h, int(on))
 
     def waiting_count(self) -> int:
         return int(lib.b200_scheduler_waiting_count(self._h))

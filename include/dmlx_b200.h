@@ -9,8 +9,12 @@
  * Conventions
  *  - Every function that can fail returns a b200_status; b200_last_error() gives a message for
  *    the calling thread's last failure.
- *  - A context (kv pool, model, scheduler ...) is single-owner and not thread-safe, one per GPU per
- *    process, like the reference's single engine thread.
+ *  - A context (kv pool, model, scheduler ...) is single-owner and not thread-safe, like the
+ *    reference's single engine thread.  One device and one calling thread per process: the library
+ *    keeps per-process caches (matmul scratch, shared-memory opt-ins) for the first device a compute
+ *    entry point runs on and refuses calls made with another device current (B200_ERR_UNSUPPORTED);
+ *    all matmuls of a process share one split-K scratch, so they belong on one stream (or on streams
+ *    ordered by events).  b200_qmm_static_scratch alone keeps its state per device.
  *  - Device pointers are plain `void*`/typed pointers to memory on the current CUDA device; streams
  *    are passed as `void*` (a cudaStream_t; NULL = the default stream).
  *  - Conditions detected inside a kernel (pool exhausted, bad index) are reported through an error
@@ -43,7 +47,8 @@ enum {
   B200_ERR_NO_DEVICE = 8,
   B200_ERR_UNSUPPORTED = 9,         /* src/kvcache/interface.zig:119,136 (FilterNotSupported ...) */
   B200_ERR_CAPACITY = 10,           /* out-array too small / src/kvcache/quantized.zig:135 CacheOverflow */
-  B200_ERR_DEVICE_FLAGGED = 11      /* a kernel set the error word; see b200_kv_error_word */
+  B200_ERR_DEVICE_FLAGGED = 11,     /* a kernel set the error word; see b200_kv_error_word */
+  B200_ERR_CANCELLED = 12           /* src/engine/request_state.zig:118,182-189 (cancelled flag) */
 };
 const char* b200_status_name(b200_status s);
 const char* b200_last_error(void);
@@ -110,6 +115,10 @@ void b200_request_force_state(b200_request* r, int32_t state, uint64_t prefill_o
                               const uint32_t* generated, uint64_t n_generated);
 /* Sequence slot in a device KV pool bound to this request (-1 when none). */
 int32_t b200_request_kv_slot(const b200_request* r);
+/* Why a request ended before its stop condition: B200_OK, B200_ERR_CANCELLED, or the failure that was
+ * its own (src/engine/engine_loop.zig:687-754 handleBatchError marks the request done and delivers the
+ * error to its client). */
+int32_t b200_request_error(const b200_request* r);
 
 /* ---- scheduler-side BlockManager: src/scheduler.zig:22-95 --------------------------------- */
 typedef struct b200_sched_bm b200_sched_bm;
@@ -125,6 +134,9 @@ void b200_sched_bm_destroy(b200_sched_bm* bm);
 b200_status b200_sched_bm_park_slot(b200_sched_bm* bm, int32_t* out_slot);
 b200_status b200_sched_bm_unpark_slot(b200_sched_bm* bm, int32_t slot);
 b200_status b200_sched_bm_sync(b200_sched_bm* bm);
+/* sync without a device read, for a caller that already holds the pool's free count (b200_llama_step
+ * returns it after decode growth has taken pages). */
+void b200_sched_bm_note_free(b200_sched_bm* bm, uint64_t free_pages);
 int32_t b200_sched_bm_can_allocate(const b200_sched_bm* bm, uint64_t n);         /* :46-51 */
 uint64_t b200_sched_bm_free_count(const b200_sched_bm* bm);                      /* :89-94 */
 uint64_t b200_sched_bm_total_blocks(const b200_sched_bm* bm);
@@ -142,6 +154,19 @@ b200_status b200_scheduler_schedule(b200_scheduler* s, b200_request** prefill_ou
                                     uint64_t* n_decode, uint64_t cap, uint64_t* blocks_needed);
 b200_status b200_scheduler_postprocess(b200_scheduler* s, const b200_token_output* outputs,
                                        uint64_t n);                              /* :328-381 */
+/* A request leaves the scheduler before it has finished (cancellation, or a failure of its own): blocks
+ * back to the pool, state done, `error` kept as the reason; the other requests are untouched
+ * (src/engine/request_state.zig:182-189; src/engine/engine_loop.zig:687-754). */
+b200_status b200_scheduler_remove(b200_scheduler* s, b200_request* r, int32_t error);
+/* No reference counterpart (the reference admits on one free block, :242,291-293, and has no answer when
+ * decode growth finds the pool empty): a running request returns all its blocks and goes back to the
+ * head of the waiting queue; the tokens generated so far join its prompt, so its next prefill rebuilds
+ * the same cache and its output continues where it stopped. */
+b200_status b200_scheduler_preempt(b200_scheduler* s, b200_request* r);
+/* While on, schedule() promotes no waiting request. */
+void b200_scheduler_hold_admission(b200_scheduler* s, int32_t on);
+/* Running requests in admission order. */
+uint64_t b200_scheduler_running(const b200_scheduler* s, b200_request** out, uint64_t cap);
 uint64_t b200_scheduler_active_count(const b200_scheduler* s);                   /* :384-386 */
 uint64_t b200_scheduler_waiting_count(const b200_scheduler* s);
 uint64_t b200_scheduler_running_count(const b200_scheduler* s);
@@ -206,6 +231,7 @@ b200_status b200_kv_create(const b200_kv_config* cfg, b200_kv** out);           
 void b200_kv_destroy(b200_kv* kv);                                               /* :1111-1138 deinit */
 /* Pool size and number of sequence slots of a pool. */
 b200_status b200_kv_dims(const b200_kv* kv, int32_t* n_pages, int32_t* max_seqs);
+b200_status b200_kv_limits(const b200_kv* kv, int32_t* max_pages_per_seq, int32_t* page_size);
 b200_status b200_kv_reset(b200_kv* kv);                                          /* :851-862 reset */
 /* Install the order in which free pages will be popped (ids[0] first).  Default: 0,1,2,... */
 b200_status b200_kv_set_free_order(b200_kv* kv, const int32_t* ids, int32_t n);
@@ -344,13 +370,14 @@ b200_status b200_qweight_create(int32_t mode, int32_t n_experts, int32_t n, int3
  * codes with fixed plausible scales.  N a multiple of 128, K of 64. */
 b200_status b200_qweight_random(int32_t mode, int32_t n_experts, int32_t n, int32_t k, uint32_t seed,
                                 b200_qweight** out);
+/* The inverse of b200_qweight_create for one expert of a handle: host buffers in the layouts
+ * b200_qweight_create takes (checks of weights that were generated on the device). */
+b200_status b200_qweight_export(const b200_qweight* w, int32_t expert, void* h_packed, void* h_scales,
+                                void* h_biases);
 void b200_qweight_destroy(b200_qweight* w);
 enum { B200_EPI_NONE = 0, B200_EPI_RESIDUAL = 1, B200_EPI_SWIGLU = 2 };
 enum { B200_QMM_AUTO = 0, B200_QMM_SIMT = 1, B200_QMM_TCGEN05 = 2, B200_QMM_MMA = 3, B200_QMM_TCGEN05_X2 = 4,
        B200_QMM_TCGEN05_TMEM_A = 5, B200_QMM_MXFP4_BLOCK_SCALED = 6 };
-/* epilogue NONE: y = xW^T.  RESIDUAL: y = residual + xW^T.  SWIGLU: W holds gate and up rows
- * interleaved (row 2i = gate_i, 2i+1 = up_i); y[T, N/2] = silu(min(g,L)) * clip(u,+-L) with
- * L = swiglu_limit (0 = unclipped)  (src/models/llama.zig:396-415; deepseek_v4.zig:947-966). */
 /* Tuning hook (no reference counterpart): 1 sends the grouped (MoE) matmuls through the kernel that
  * keeps dequantised weights in tensor memory. */
 void b200_set_qmm_grouped_tmem_a(int32_t on);
@@ -360,6 +387,9 @@ void b200_set_qmm_grouped_tmem_a(int32_t on);
  * with path B200_QMM_MXFP4_BLOCK_SCALED.  The weight handle builds a second copy of itself (plain
  * row-major codes + scale atoms) on first use. */
 void b200_set_qmm_grouped_block_scaled(int32_t on);
+/* epilogue NONE: y = xW^T.  RESIDUAL: y = residual + xW^T.  SWIGLU: W holds gate and up rows
+ * interleaved (row 2i = gate_i, 2i+1 = up_i); y[T, N/2] = silu(min(g,L)) * clip(u,+-L) with
+ * L = swiglu_limit (0 = unclipped)  (src/models/llama.zig:396-415; deepseek_v4.zig:947-966). */
 b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y,
                      int32_t epilogue, const void* d_residual, float swiglu_limit, int32_t path,
                      void* stream);
@@ -372,16 +402,28 @@ b200_status b200_qmm_residual_norm(const b200_qweight* w, const void* d_x, int32
                                    const void* d_residual, const void* d_norm_weight, float eps,
                                    void* d_normed, void* stream);
 
-/* Reads and clears the matmul kernels' error word (set when a bounded wait ran out). */
+/* Reads and clears the matmul kernels' error words (set when a bounded wait ran out): the word of
+ * b200_qmm and the grouped launches, and the word of b200_qmm_static_scratch on the current device. */
 b200_status b200_qmm_error_word(int32_t* out);
+/* Test hook: writes `value` into the error word of b200_qmm (static_scratch_word = 0) or of
+ * b200_qmm_static_scratch (1), so that the read-and-clear path can be checked without a kernel that
+ * times out. */
+b200_status b200_qmm_debug_set_error_word(int32_t value, int32_t static_scratch_word);
+/* Test hook: launches a kernel whose one bounded wait (at most `polls` polls, 1..2^20) is on a barrier
+ * that nothing completes.  The wait runs out, the kernel sets the matmul error word the way the matmul
+ * kernels do and returns normally; b200_qmm_error_word then reports B200_ERR_DEVICE_FLAGGED and the
+ * library stays usable. */
+b200_status b200_qmm_debug_wait_runs_out(int32_t polls, void* stream);
 /* No counterpart in the reference.  The tensor-core matmul of b200_qmm for hosts that must not
  * allocate after start-up (all HBM already given to the KV pool, a step being captured into a CUDA
  * graph or running beside other streams, where cudaMalloc would fail or stall the device): its
  * split-K scratch is a fixed 32 MiB array inside the library instead of a buffer grown on demand,
- * and the call allocates nothing.  Problems whose scratch (K-splits x rows x round_up(N,128) x 4
- * bytes) exceeds the array are refused with B200_ERR_CAPACITY.  The first call on a device
- * resolves the array's address and should come before any stream capture; all calls share the
- * array, so calls that overlap on the GPU race. */
+ * and the call allocates nothing.  Problems whose scratch (K-splits x round_up(rows, token tile) x
+ * round_up(N,128) x 4 bytes, the token tile being min(256, round_up(rows,16)) rows, so 257 rows count
+ * as 512) exceeds the array are refused with B200_ERR_CAPACITY.  The first call on a device resolves
+ * the array's address and opts the kernel into large shared memory there, and should come before any
+ * stream capture; all calls share the array, so calls that overlap on the GPU race.  A bounded wait
+ * that runs out inside its kernels is reported through b200_qmm_error_word. */
 b200_status b200_qmm_static_scratch(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y,
                                     int32_t epilogue, const void* d_residual, float swiglu_limit,
                                     void* stream);
@@ -450,14 +492,39 @@ b200_engine* b200_engine_create(b200_llama* model, b200_kv* kv, uint64_t max_pre
 void b200_engine_destroy(b200_engine* e);
 b200_status b200_engine_submit(b200_engine* e, uint64_t id, const uint32_t* prompt, uint64_t n_prompt,
                                uint64_t max_tokens, const uint32_t* stop_tokens, uint64_t n_stop);
-/* One step; `out` receives the tokens that joined a request's output this step. */
+/* One step; `out` receives the tokens that joined a request's output this step (checked to fit `cap`
+ * before anything is written to the cache).  Page-table growth is budgeted on the host against the
+ * pool's free count before the model step: decode rows first, then prefill chunks; a request whose
+ * growth does not fit is left out of the step and keeps its cursor; when nothing fits, the youngest
+ * running request is preempted (b200_scheduler_preempt) — or fails on its own if it is alone.  A step
+ * that a kernel flags all the same changes neither the pool nor any sequence's next input token, so
+ * the caller may step again. */
 b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t cap, uint64_t* n_out,
                              void* stream);
 uint64_t b200_engine_active_count(const b200_engine* e);
 b200_status b200_engine_result(const b200_engine* e, uint64_t id, uint32_t* out, uint64_t cap,
                                uint64_t* n, int32_t* done);
 void b200_engine_forget(b200_engine* e, uint64_t id);
+/* Cancels a request wherever it is (waiting, mid-prefill, decoding): it leaves the scheduler at once,
+ * its pages return to the pool, the tokens it has produced stay readable and its status becomes
+ * B200_ERR_CANCELLED (RequestState.cancelled, src/engine/request_state.zig:118,182-189, checked by the
+ * engine thread at src/engine/engine_loop.zig:240-243).  Called between steps. */
+b200_status b200_engine_cancel(b200_engine* e, uint64_t id);
+/* B200_OK, or why the request ended early: B200_ERR_CANCELLED, B200_ERR_CAPACITY (its sequence reached
+ * the length a page table holds) or B200_ERR_INSUFFICIENT_BLOCKS (it does not fit the pool even alone).
+ * A request that fails this way leaves the batch on its own; the others go on
+ * (src/engine/engine_loop.zig:687-754). */
+b200_status b200_engine_request_status(const b200_engine* e, uint64_t id, int32_t* status);
+/* Page-pool pressure so far: request-steps left out because their page growth did not fit, running
+ * requests sent back to the waiting queue to free pages (their cache is recomputed when they are
+ * admitted again), requests that failed on their own.  While running requests are short of pages no
+ * new request is admitted. */
+void b200_engine_pressure_stats(const b200_engine* e, uint64_t* deferred, uint64_t* preempted, uint64_t* failed);
 int32_t b200_engine_free_pages(const b200_engine* e);
+/* Request ids of the last step's batch in descriptor order (prefill chunks first, then decode rows,
+ * src/batch_builder.zig:100-111): row i of b200_llama_last_logits belongs to ids[i].  Returns the
+ * batch size. */
+uint64_t b200_engine_last_batch(const b200_engine* e, uint64_t* ids, uint64_t cap);
 /* Prefix pages that outlive requests (RestoredPrefix, src/kvcache/prefix_disk.zig:15-29, 246-293): the
  * caller parks a sequence slot, fills it (b200_kv_alloc + b200_kv_page_load + b200_kv_set_len, e.g.
  * from blocks restored from disk) and publishes it with the token ids its pages hold; with prefix

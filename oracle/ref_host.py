@@ -203,9 +203,11 @@ class Request:
     state: int = WAITING
     block_ids: List[int] = field(default_factory=list)
     prefill_offset: int = 0
+    folded: int = 0  # generated tokens a preemption appended to the prompt (extension, see Scheduler.preempt)
+    error: int = 0   # why the request ended early (extension, see Scheduler.remove)
 
-    def seq_len(self) -> int:  # :165-167
-        return self.prefill_offset + len(self.generated_tokens)
+    def seq_len(self) -> int:  # :165-167 (minus the generated tokens that now sit in the prompt)
+        return self.prefill_offset + len(self.generated_tokens) - self.folded
 
     def is_stop_token(self, t: int) -> bool:  # :170-175
         return t in self.stop_tokens
@@ -285,6 +287,7 @@ class Scheduler:
         self.block_manager = block_manager
         self.max_prefill_tokens = max_prefill_tokens
         self.blocks_per_request = 1  # :242
+        self.hold = False  # extension: schedule() promotes nobody while set
 
     def add_request(self, req: Request) -> None:  # :252-255
         req.state = WAITING
@@ -299,7 +302,7 @@ class Scheduler:
                 decode_list.append(req)
         still_waiting, blocks_needed = [], 0
         for req in self.waiting:
-            if self.block_manager.can_allocate(self.blocks_per_request):
+            if not self.hold and self.block_manager.can_allocate(self.blocks_per_request):
                 self.block_manager.allocate_blocks(req, self.blocks_per_request)
                 req.state = PREFILLING
                 prefill_list.append(req)
@@ -337,6 +340,31 @@ class Scheduler:
 
     def active_count(self) -> int:  # :384-386
         return len(self.running) + len(self.waiting)
+
+    # ---- extensions with no counterpart in scheduler.zig (the engine loop's handleBatchError and
+    # cancel flag, src/engine/engine_loop.zig:687-754, src/engine/request_state.zig:182-189, and a
+    # preemption rule for an exhausted pool) -----------------------------------------------------
+    def remove(self, req: Request, error: int) -> None:
+        if req in self.running:
+            self.running.remove(req)
+            self.block_manager.free_blocks(req)
+        elif req in self.waiting:
+            self.waiting.remove(req)
+        else:
+            raise ValueError("request is not active")
+        req.state, req.error = DONE, error
+
+    def preempt(self, req: Request) -> None:
+        self.running.remove(req)
+        self.block_manager.free_blocks(req)
+        req.prompt_tokens = list(req.prompt_tokens) + list(req.generated_tokens[req.folded:])
+        req.folded = len(req.generated_tokens)
+        req.prefill_offset = 0
+        req.state = WAITING
+        self.waiting.insert(0, req)
+
+    def hold_admission(self, on: bool) -> None:
+        self.hold = bool(on)
 
 
 # ---------------------------------------------------------------------------
@@ -541,6 +569,47 @@ class PagedKVTables:
 
     def current_len(self) -> int:  # paged.zig:842-849
         return max(self.lens) if self.lens else 0
+
+    def filter(self, keep: Sequence[int]) -> None:
+        """paged.zig:879-945: reference counts are derived afresh from the page tables of the
+        sequences that stay (:898-914); pages nobody references any more are free again (:939-944).
+        Sequence slots keep their numbers here (the reference compacts them to 0..n-1), and a freed
+        page returns to the LIFO stack at the (slot, table position) of the last dropped sequence that
+        listed it."""
+        for s in keep:
+            if s < 0 or s >= len(self.tables):
+                raise InvalidBatchIndex()  # :904
+        kept = set(keep)
+        new_ref = [0] * len(self.ref)
+        for s in kept:
+            for p in self.tables[s]:
+                new_ref[p] += 1
+        dropped = [s for s in range(len(self.tables)) if s not in kept]
+        holders = [0] * len(self.ref)  # dropped tables that still list the page
+        for s in dropped:
+            for p in self.tables[s]:
+                holders[p] += 1
+        for s in dropped:
+            for p in self.tables[s]:
+                holders[p] -= 1
+                if new_ref[p] == 0 and holders[p] == 0:  # freed where its last holder goes
+                    self.tokens_used[p] = 0
+                    self.free.append(p)
+            self.tables[s] = []
+            self.lens[s] = 0
+        for p in range(len(self.ref)):
+            if self.ref[p] > 0:
+                self.ref[p] = new_ref[p]
+
+    def reset(self) -> None:
+        """paged.zig:851-862: every page unused, every sequence empty.  The pool is as new: pages pop
+        in the order 0, 1, 2, ... again."""
+        n = len(self.ref)
+        self.free = [n - 1 - i for i in range(n)]
+        self.ref = [0] * n
+        self.tokens_used = [0] * n
+        self.tables = [[] for _ in self.tables]
+        self.lens = [0] * len(self.lens)
 
 
 def greedy(logits: np.ndarray) -> int:

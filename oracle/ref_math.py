@@ -124,14 +124,16 @@ E2M1_TABLE = np.array([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0,
                        0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0], np.float32)  # deepseek_v4_loader.zig:862
 
 
+_E2M1_PAIRS = np.stack([E2M1_TABLE[np.arange(256) & 0x0F], E2M1_TABLE[np.arange(256) >> 4]], axis=-1)  # byte -> two values
+
+
 def dequantize_mxfp4(packed: np.ndarray, scales_e8m0: np.ndarray, block: int = 32) -> np.ndarray:
     """src/models/deepseek_v4_loader.zig:858-920: each byte packs two E2M1 codes, low nibble = even
     element; one E8M0 scale 2^(s-127) per ``block`` elements (:839-856)."""
-    lo = E2M1_TABLE[packed & 0x0F]
-    hi = E2M1_TABLE[(packed >> 4) & 0x0F]
-    w = np.stack([lo, hi], axis=-1).reshape(packed.shape[0], packed.shape[1] * 2)
+    n, k = packed.shape[0], packed.shape[1] * 2
+    w = _E2M1_PAIRS[packed].reshape(n, k // block, block)  # one gather: byte -> (even element, odd element)
     sc = np.exp2(scales_e8m0.astype(np.float32) - 127.0)
-    return w * np.repeat(sc, block, axis=1)
+    return (w * sc[:, :, None]).reshape(n, k)
 
 
 def qmm(x: np.ndarray, w_deq: np.ndarray) -> np.ndarray:

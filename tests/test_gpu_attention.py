@@ -181,3 +181,16 @@ def test_prefill_groups_match_oracle_and_row_kernel(hq, hkv, d, kv_dtype):
         assert rel <= REL_TOL and cos >= COS_TOL, (r, s, c, rel, cos)
     assert np.abs(got - per_row).max() <= 2e-2 * np.abs(per_row).max()  # both kernels read the same pool
     kv.close()
+
+
+@pytest.mark.parametrize("kv_dtype", [0, 1])  # bf16 pool, FP8-E4M3 pool (tensor-core kernels, head_dim 128)
+def test_long_contexts_of_the_attention_microbench(kv_dtype):
+    """Three sequences drawn from the attention microbench's range (log-uniform 128..32768 tokens, 32
+    query / 8 KV heads, head_dim 128), one of them at the maximum of 32768 tokens = 1024 pages = 128
+    split-K chunks, pages scattered over a pool sized to the pages x 1.25.  Per row against the
+    per-request oracle; for the FP8 pool the oracle reads what the pool holds (codes x scale)."""
+    ctxs = [32768, 4127, 128]
+    got, want, _ = _run_case(ctxs, 32, 8, 128, kv_dtype, seed=2048 + kv_dtype)
+    for s in range(len(ctxs)):
+        r, c = _close(got[s], want[s])
+        assert r <= REL_TOL and c >= COS_TOL, (s, ctxs[s], r, c)

@@ -1,12 +1,11 @@
-"""BASELINE config 1 end to end through the engine step (b200_engine_*): tiny LLaMA (4 layers,
-hidden 512, 8 query / 2 KV heads, head_dim 64, FFN 1408, vocab 32000, N(0,0.02) weights), a
-continuous batch of 8 requests with seeded prompt lengths 16..256, greedy decode, 32-token pages,
-chunked prefill.  Each request's greedy ids are compared with the fp32 oracle running that request
-alone at B=1.
-
-bf16 tensor-core arithmetic against an fp32 oracle on a random-init model can flip an argmax at a
-near-tie (top-2 logit gap below the ~1e-2 logit noise); a sequence is therefore required to be
-identical up to its first near-tie, and any divergence must be at such a tie."""
+"""The tiny LLaMA configuration end to end through the engine step (b200_engine_*): 4 layers, hidden
+512, 8 query / 2 KV heads, head_dim 64, FFN 1408, vocab 32000, N(0,0.02) weights, a continuous batch
+of 8 requests with seeded prompt lengths 16..256, greedy decode for 64 steps, 32-token pages, chunked
+prefill.  Every token the engine emits is checked against the fp32 oracle running that request alone
+at B=1 on the same token history: it must be the oracle's argmax unless the oracle's top-2 gap is
+below twice the logit error measured on that very row, and then it must lie within that bound of the
+maximum.  The number of sequences that equal the free-running oracle from the first to the last token
+is printed and pinned."""
 import numpy as np
 import pytest
 
@@ -15,7 +14,10 @@ from oracle import ref_host, ref_math
 pytestmark = pytest.mark.gpu
 
 CFG = ref_math.LlamaConfig(n_layers=4, hidden=512, n_heads=8, n_kv_heads=2, head_dim=64, ffn=1408, vocab=32000)
-N_REQ, N_STEPS = 8, 32
+N_REQ, N_STEPS = 8, 64
+# Sequences (of 8) whose 64 greedy ids equal the free-running fp32 oracle on a B200; the others part
+# from it at a near-tie that the per-token check below accepts.
+IDENTICAL_PINNED = 5
 
 
 def _bits(a):
@@ -66,34 +68,288 @@ def test_config1_greedy_decode_matches_oracle():
     prompts = [rng.integers(0, cfg.vocab, int(rng.integers(16, 257))).tolist() for _ in range(N_REQ)]
     # requests arrive over the first steps: continuous batching with mixed prefill + decode steps
     arrivals = {0: [0, 1, 2], 1: [3], 2: [4, 5], 4: [6], 7: [7]}
+    # one oracle per request, fed the engine's own tokens (so every token is checked, also after a near-tie)
+    oracles = {i + 1: ref_math.LlamaB1(cfg, weights) for i in range(N_REQ)}
+    fed = {i + 1: 0 for i in range(N_REQ)}        # prompt tokens the oracle has consumed
+    emitted = {i + 1: [] for i in range(N_REQ)}
+    diverged = set()
+    rel_worst, near_ties, checked = 0.0, 0, 0
     step = 0
-    while (eng.active_count() > 0 or step <= max(arrivals)) and step < 200:
+    while (eng.active_count() > 0 or step <= max(arrivals)) and step < 400:
         for i in arrivals.get(step, []):
             eng.submit(i + 1, prompts[i], N_STEPS)
-        eng.step()
+        joined = dict(eng.step())
+        batch = eng.last_batch()
+        logits = model.last_logits(len(batch))
+        for row, rid in enumerate(batch):
+            o, prompt = oracles[rid], prompts[rid - 1]
+            if fed[rid] < len(prompt):      # a prefill chunk (the engine's chunking: 96 tokens)
+                n = min(96, len(prompt) - fed[rid])
+                want = o.forward(prompt[fed[rid]:fed[rid] + n])
+                fed[rid] += n
+            else:
+                want = o.forward([emitted[rid][-1]])
+            if rid not in joined:
+                continue                    # a chunk that is not the last one: its token is dropped
+            got = joined[rid]
+            err = float(np.abs(logits[row] - want).max())
+            rel_worst = max(rel_worst, err / float(np.abs(want).max()))
+            best = ref_host.greedy(want)
+            top2 = np.sort(want)[-2:]
+            checked += 1
+            if top2[1] - top2[0] > 2 * err:
+                assert got == best, (rid, len(emitted[rid]), float(top2[1] - top2[0]), err)
+            elif got != best:
+                assert want[best] - want[got] <= 2 * err, (rid, len(emitted[rid]), float(want[best] - want[got]), err)
+                near_ties += 1
+                diverged.add(rid)
+            emitted[rid].append(got)
         step += 1
     assert eng.active_count() == 0
     assert eng.free_pages() == 128  # every page returned (src/scheduler.zig:371-380)
-    identical = 0
+    assert rel_worst <= 2e-2, rel_worst
     for i in range(N_REQ):
         got, done = eng.result(i + 1)
-        assert done and len(got) == N_STEPS
-        o = ref_math.LlamaB1(cfg, weights)
-        logits = o.forward(prompts[i])
-        for j in range(N_STEPS):
-            tok = ref_host.greedy(logits)
-            if got[j] != tok:
-                top2 = np.sort(logits)[-2:]
-                assert top2[1] - top2[0] < 2e-2 * np.abs(logits).max(), (i, j, float(top2[1] - top2[0]))
-                assert got[j] == int(np.argsort(logits)[-2]), (i, j)  # the runner-up, not an unrelated token
-                break
-            logits = o.forward([tok])
-        else:
-            identical += 1
-    assert identical >= 1, identical  # every divergence above was checked to be a near-tie with the runner-up token
+        assert done and len(got) == N_STEPS and got == emitted[i + 1]
+    identical = N_REQ - len(diverged)
+    print(f"greedy ids: {identical} of {N_REQ} sequences identical to the fp32 oracle over {N_STEPS} steps; "
+          f"{near_ties} near-tie tokens of {checked}; worst logit error {rel_worst:.2e} of the row maximum")
+    assert identical >= IDENTICAL_PINNED, (identical, sorted(diverged))
     eng.close()
     model.close()
     kv.close()
+
+
+def _run_engine(dev, cfg, model, prompts, n_new, n_pages, max_pages_per_seq=16, chunk=64, hook=None):
+    kv = dev.PagedKVCache(cfg.n_layers, cfg.n_kv_heads, cfg.head_dim, n_pages, 16, max_pages_per_seq, cfg.n_heads,
+                          max_rows=1024, attn_scratch_chunks=8192)
+    eng = dev.Engine(model, kv, max_prefill_tokens=chunk)
+    for i, p in enumerate(prompts):
+        eng.submit(i + 1, p, n_new)
+    steps = 0
+    while eng.active_count() > 0 and steps < 2000:
+        eng.step()
+        steps += 1
+        if hook:
+            hook(eng, kv, steps)
+    out = {i + 1: eng.result(i + 1) for i in range(len(prompts))}
+    status = {i + 1: eng.request_status(i + 1) for i in range(len(prompts))}
+    stats = eng.pressure_stats()
+    free, err, active = eng.free_pages(), kv.error_word(), eng.active_count()
+    refs = sum(kv.ref_counts())
+    eng.close()
+    kv.close()
+    return out, status, stats, (free, err, active, refs, steps)
+
+
+def test_pool_too_small_defers_and_preempts_instead_of_failing():
+    """Six requests that need 30 pages between them in a pool of 20: admission takes one page each
+    (src/scheduler.zig:242,291-293), decode growth then finds the pool empty (src/kvcache/paged.zig:525-531).
+    The step must not fail: requests whose growth does not fit wait, and when all are blocked the
+    youngest gives its pages back and is prefilled again later.  Every request still delivers all its
+    tokens, equal to the oracle's (and to an unpressured run's, up to near-ties), and every page returns."""
+    from dmlx_b200 import device as dev
+    from dmlx_b200 import _lib
+
+    cfg = CFG
+    weights = ref_math.random_llama_weights(cfg, seed=2026)
+    model = _build_model(dev, cfg, weights)
+    rng = np.random.default_rng(5)
+    prompts = [rng.integers(0, cfg.vocab, n).tolist() for n in (100, 90, 110, 95, 120, 105)]
+    n_new = 40
+    roomy, st_r, stats_r, (free_r, err_r, act_r, refs_r, _) = _run_engine(dev, cfg, model, prompts, n_new, 64)
+    assert stats_r == (0, 0, 0) and (free_r, err_r, act_r, refs_r) == (64, 0, 0, 0)
+    tight, st_t, stats_t, (free_t, err_t, act_t, refs_t, steps_t) = _run_engine(dev, cfg, model, prompts, n_new, 20)
+    assert (free_t, err_t, act_t, refs_t) == (20, 0, 0, 0), (free_t, err_t, act_t, refs_t)
+    assert stats_t[0] > 0 and stats_t[1] > 0 and stats_t[2] == 0, stats_t  # waited, preempted, nobody failed
+    same = 0
+    for i, p in enumerate(prompts):
+        got, done = tight[i + 1]
+        assert done and len(got) == n_new and st_t[i + 1] == _lib.OK
+        _check_against_oracle(cfg, weights, p, got, i)
+        same += got == roomy[i + 1][0]
+    assert same >= 3, same  # a recomputed cache may flip a near-tie, most sequences do not meet one
+    model.close()
+
+
+def test_cancel_waiting_prefilling_and_decoding_requests():
+    """b200_engine_cancel (RequestState.cancelled, src/engine/request_state.zig:118,182-189): a request
+    leaves at once wherever it is, its pages return, what it produced stays readable, and the other
+    requests decode what they decode without it."""
+    from dmlx_b200 import device as dev
+    from dmlx_b200 import _lib
+
+    cfg = CFG
+    weights = ref_math.random_llama_weights(cfg, seed=2026)
+    model = _build_model(dev, cfg, weights)
+    rng = np.random.default_rng(6)
+    prompts = [rng.integers(0, cfg.vocab, n).tolist() for n in (40, 200, 50, 30)]
+    kv = dev.PagedKVCache(cfg.n_layers, cfg.n_kv_heads, cfg.head_dim, 32, 3, 16, cfg.n_heads, max_rows=1024,
+                          attn_scratch_chunks=8192)   # three sequence slots: the fourth request waits
+    eng = dev.Engine(model, kv, max_prefill_tokens=64)
+    for i, p in enumerate(prompts):
+        eng.submit(i + 1, p, 12)
+    eng.step()
+    eng.step()                      # 1 and 3 decode, 2 is in the middle of its prefill, 4 waits for a slot
+    assert eng.request_slot(4) == -1
+    held_before = 32 - eng.free_pages()
+    eng.cancel(2)                   # mid-prefill: 128 of 200 prompt tokens cached = 4 pages
+    assert eng.request_status(2) == _lib.ERR_CANCELLED and eng.result(2) == ([], True)
+    assert 32 - eng.free_pages() == held_before - 4
+    eng.cancel(4)                   # still waiting
+    assert eng.request_status(4) == _lib.ERR_CANCELLED and eng.active_count() == 2
+    for _ in range(3):
+        eng.step()
+    got3_before = eng.result(3)[0]
+    eng.cancel(3)                   # decoding
+    assert eng.request_status(3) == _lib.ERR_CANCELLED and eng.result(3) == (got3_before, True) and len(got3_before) == 5
+    with pytest.raises(_lib.B200Error):
+        eng.cancel(99)
+    steps = 0
+    while eng.active_count() > 0 and steps < 100:
+        eng.step()
+        steps += 1
+    got1, done1 = eng.result(1)
+    assert done1 and len(got1) == 12 and eng.request_status(1) == _lib.OK
+    _check_against_oracle(cfg, weights, prompts[0], got1, 1)
+    _check_against_oracle(cfg, weights, prompts[2], got3_before, 3)
+    assert eng.free_pages() == 32 and sum(kv.ref_counts()) == 0 and kv.error_word() == 0
+    eng.close()
+    model.close()
+    kv.close()
+
+
+def test_sequence_that_outgrows_its_page_table_fails_alone():
+    """Per-request isolation (handleBatchError, src/engine/engine_loop.zig:687-754): a sequence that
+    reaches the length its page table holds (3 pages = 96 tokens here) ends with CacheOverflow's code,
+    keeps the tokens it produced, and the rest of the batch finishes normally.  A prompt that can never
+    fit is refused at submission."""
+    from dmlx_b200 import device as dev
+    from dmlx_b200 import _lib
+
+    cfg = CFG
+    weights = ref_math.random_llama_weights(cfg, seed=2026)
+    model = _build_model(dev, cfg, weights)
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(0, cfg.vocab, n).tolist() for n in (80, 20, 33)]
+    out, status, stats, (free, err, active, refs, _) = _run_engine(dev, cfg, model, prompts, 40, 24, max_pages_per_seq=3)
+    assert (free, err, active, refs) == (24, 0, 0, 0)
+    got1, done1 = out[1]
+    assert done1 and status[1] == _lib.ERR_CAPACITY and len(got1) == 96 - 80 + 1 and stats[2] == 1
+    for rid in (2, 3):
+        got, done = out[rid]
+        assert done and status[rid] == _lib.OK and len(got) == 40
+        _check_against_oracle(cfg, weights, prompts[rid - 1], got, rid)
+    _check_against_oracle(cfg, weights, prompts[0], got1, 1)
+    kv = dev.PagedKVCache(cfg.n_layers, cfg.n_kv_heads, cfg.head_dim, 24, 4, 3, cfg.n_heads, max_rows=1024)
+    eng = dev.Engine(model, kv, max_prefill_tokens=64)
+    with pytest.raises(_lib.B200Error) as ei:
+        eng.submit(1, list(range(96)), 4)
+    assert ei.value.status == _lib.ERR_CAPACITY
+    eng.close()
+    kv.close()
+    model.close()
+
+
+@pytest.mark.parametrize("own_stream", [False, True])  # True: decode steps are replayed as CUDA graphs
+def test_flagged_step_leaves_state_intact_and_can_be_retried(own_stream):
+    """A model step whose page reservation is flagged (pool exhausted) must change nothing: not the
+    pool (the reservation is all or nothing) and not the sequences' next input tokens.  Once a page is
+    free the same step is run again and the token stream equals that of a run that never lacked pages."""
+    import contextlib
+
+    import torch
+
+    from dmlx_b200 import device as dev
+    from dmlx_b200 import _lib
+
+    cfg = CFG
+    weights = ref_math.random_llama_weights(cfg, seed=2026)
+    model = _build_model(dev, cfg, weights)
+    ctx = (lambda: torch.cuda.stream(torch.cuda.Stream())) if own_stream else contextlib.nullcontext
+    rng = np.random.default_rng(10)
+    prompts = [rng.integers(0, cfg.vocab, n).tolist() for n in (62, 40)]
+
+    def run(n_pages, starve):
+        kv = dev.PagedKVCache(cfg.n_layers, cfg.n_kv_heads, cfg.head_dim, n_pages, 4, 8, cfg.n_heads, max_rows=1024)
+        for s in (0, 1):
+            kv.alloc(s, 1)
+        if starve:
+            kv.alloc(2, n_pages - 4)  # a third slot holds every page the two sequences will not own after prefill
+        descs = [(0, len(prompts[0]), 0, 0), (1, len(prompts[1]), 0, len(prompts[0]))]
+        toks, _ = model.step(kv, descs, prompts[0] + prompts[1])
+        stream = [list(map(int, toks))]
+        flagged = 0
+        for _ in range(6):
+            d = [(0, 1, kv.seq_len(0), -1), (1, 1, kv.seq_len(1), -1)]
+            try:
+                toks, _ = model.step(kv, d, [])
+            except _lib.B200Error as e:
+                assert e.status == _lib.ERR_INSUFFICIENT_BLOCKS and starve
+                flagged += 1
+                kv.release([2])       # the pages come back; same step again
+                toks, _ = model.step(kv, d, [])
+            stream.append(list(map(int, toks)))
+        lens = (kv.seq_len(0), kv.seq_len(1))
+        kv.close()
+        return stream, flagged, lens
+
+    with ctx():
+        want, f0, lens0 = run(12, False)
+        got, f1, lens1 = run(12, True)
+    torch.cuda.synchronize()
+    assert f0 == 0 and f1 == 1          # sequence 0 needs its third page at 64 tokens and finds none
+    assert lens0 == lens1 == (62 + 6, 40 + 6)
+    assert got == want
+    model.close()
+
+
+def test_decode_graph_survives_growth_of_the_matmul_scratch():
+    """Captured decode steps carry the address of the split-K scratch.  A later, larger matmul makes the
+    library grow that scratch; the old buffer must stay alive for the graphs that still write to it.
+    Decode steps replayed after the growth must produce what the same steps produce without it."""
+    import torch
+
+    from dmlx_b200 import device as dev
+
+    cfg = CFG
+    weights = ref_math.random_llama_weights(cfg, seed=2026)
+    model = _build_model(dev, cfg, weights)
+    rng = np.random.default_rng(12)
+    prompts = [rng.integers(0, cfg.vocab, n).tolist() for n in (50, 70, 33)]
+    big = dev.QWeight.random(dev.Q_AFFINE4_G64, 8192, 256, seed=3)
+    xb = torch.zeros(4096, 256, dtype=torch.bfloat16, device="cuda")
+
+    def run(grow):
+        kv = dev.PagedKVCache(cfg.n_layers, cfg.n_kv_heads, cfg.head_dim, 32, 4, 8, cfg.n_heads, max_rows=1024)
+        off, descs, flat = 0, [], []
+        for s, p in enumerate(prompts):
+            kv.alloc(s, 1)
+            descs.append((s, len(p), 0, off))
+            flat += p
+            off += len(p)
+        toks, _ = model.step(kv, descs, flat)
+        stream = [list(map(int, toks))]
+        for j in range(8):
+            if grow and j == 4:
+                # 4096 rows x 8192 columns of f32 partials on the CUDA-core path: twice the initial scratch
+                dev.qmm(big, xb, path=dev.QMM_SIMT)
+                torch.cuda.synchronize()
+            d = [(s, 1, kv.seq_len(s), -1) for s in range(len(prompts))]
+            toks, _ = model.step(kv, d, [])
+            stream.append(list(map(int, toks)))
+        logits = model.last_logits(len(prompts)).copy()
+        kv.close()
+        return stream, logits
+
+    with torch.cuda.stream(torch.cuda.Stream()):  # the legacy default stream cannot be captured
+        s0, l0 = run(False)
+        s1, l1 = run(True)
+    torch.cuda.synchronize()
+    assert s0 == s1 and np.array_equal(l0, l1)
+    assert dev.qmm_error_word() == 0
+    del big
+    model.close()
 
 
 def test_prefix_sharing_through_engine():

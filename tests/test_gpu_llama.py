@@ -1,5 +1,4 @@
-"""GPU parity of the whole decode step on the tiny LLaMA configuration (BASELINE config 1 shape
-family): continuous batch of ragged requests through scheduler -> pack -> paged KV -> layer stack
+"""GPU parity of the whole decode step on the tiny LLaMA test model: continuous batch of ragged requests through scheduler -> pack -> paged KV -> layer stack
 -> greedy token, against each request evaluated alone at B=1 by the fp32 oracle.
 
 Logit tolerance (bf16 compute): max |diff| / max |ref| <= 2e-2, cosine >= 0.9995.

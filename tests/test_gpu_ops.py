@@ -268,3 +268,117 @@ def test_qmm_mxfp4_large_scales(path):
         want = ref_math.qmm(x, ref_math.dequantize_mxfp4(packed, scales))
         rel, cos = _close(got, want)
         assert rel <= 2e-2 and cos >= 0.9995, (lo, hi, rel, cos)
+
+
+def test_bounded_wait_that_runs_out_sets_the_error_word_and_returns():
+    """Every wait inside the kernels is bounded; when one runs out the kernel records it in the error
+    word and returns.  A probe kernel waits (a few thousand polls) on a barrier nothing ever completes:
+    the host must read DeviceFlagged once, the word must clear, and the next matmul must run normally."""
+    from dmlx_b200 import _lib
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(3)
+    packed, s, b, sb, bb = _affine_weight(rng, 256, 512)
+    w = dev.QWeight(dev.Q_AFFINE4_G64, packed, sb, bb, 256, 512)
+    x = ref_math.bf16_round(rng.normal(0, 1, (4, 512)))
+    want = ref_math.qmm(x, ref_math.dequantize_affine4(packed, s, b))
+    dev.qmm(w, _bf(x))
+    assert dev.qmm_error_word() == 0
+    _lib.check(_lib.lib.b200_qmm_debug_wait_runs_out(4096, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    assert dev.qmm_error_word() == _lib.ERR_DEVICE_FLAGGED
+    assert dev.qmm_error_word() == 0
+    got = dev.qmm(w, _bf(x)).float().cpu().numpy()
+    assert dev.qmm_error_word() == 0
+    rel, cos = _close(got, want)
+    assert rel <= 2e-2 and cos >= 0.9995
+
+
+def test_qweight_export_is_the_inverse_of_create():
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(31)
+    n, k = 200, 512  # N not a multiple of the 128-row tile
+    packed, s, b, sb, bb = _affine_weight(rng, n, k)
+    w = dev.QWeight(dev.Q_AFFINE4_G64, packed, sb, bb, n, k)
+    p2, s2, b2 = w.export()
+    assert np.array_equal(p2, packed) and np.array_equal(s2, sb) and np.array_equal(b2, bb)
+    mp = rng.integers(0, 256, (2 * n, k // 2), dtype=np.uint8)
+    ms = rng.integers(100, 140, (2 * n, k // 32), dtype=np.uint8)
+    w = dev.QWeight(dev.Q_MXFP4_G32, mp, ms, None, n, k, n_experts=2)
+    for e in range(2):
+        p2, s2, _ = w.export(e)
+        assert np.array_equal(p2, mp[e * n:(e + 1) * n]) and np.array_equal(s2, ms[e * n:(e + 1) * n])
+
+
+# ---- the Llama-3-8B-shaped int4 model's own matrix shapes, with quantised real weights --------------
+# down is the deepest K (14336 = 224 chunks, the deepest K split); gate/up and lm_head are checked on a
+# slice of their rows (4096 resp. 33 x 128 = 4224, an odd number of 128-row tiles) at their real K.
+_BIG = {}
+
+
+def _big_weight(dev, name):
+    if name not in _BIG:
+        n, k = {"down": (4096, 14336), "gate_up": (4096, 4096), "lm_head": (4224, 4096)}[name]
+        rng = np.random.default_rng(len(name) * 100 + n)
+        wf = rng.normal(0, 0.02, (n, k)).astype(np.float32)
+        packed, s, b = ref_math.quantize_affine4(wf)
+        bits = lambda a: (ref_math.bf16_round(a).view(np.uint32) >> 16).astype(np.uint16)
+        _BIG[name] = (dev.QWeight(dev.Q_AFFINE4_G64, packed, bits(s), bits(b), n, k), ref_math.dequantize_affine4(packed, s, b), n, k)
+    return _BIG[name]
+
+
+@pytest.mark.parametrize("rows", [1, 16, 64, 256, 512])
+@pytest.mark.parametrize("name", ["down", "gate_up", "lm_head"])
+def test_qmm_affine4_at_model_shapes(name, rows):
+    """The automatic path at 1 / 16 / 64 / 256 / 512 packed rows (weight-streaming kernel, tensor-memory
+    kernel, tile-pair kernel, several token tiles) against the oracle, every row judged on its own."""
+    from dmlx_b200 import device as dev
+
+    w, wd, n, k = _big_weight(dev, name)
+    rng = np.random.default_rng(rows + n)
+    x = ref_math.bf16_round(rng.normal(0, 1, (rows, k)))
+    want = ref_math.qmm(x, wd)
+    if name == "down":
+        res = ref_math.bf16_round(rng.normal(0, 1, (rows, n)))
+        got = dev.qmm(w, _bf(x), dev.EPI_RESIDUAL, residual=_bf(res)).float().cpu().numpy()
+        want = want + res
+    elif name == "gate_up":
+        got = dev.qmm(w, _bf(x), dev.EPI_SWIGLU).float().cpu().numpy()
+        g_, u_ = want[:, 0::2].astype(np.float64), want[:, 1::2].astype(np.float64)
+        want = g_ / (1.0 + np.exp(-g_)) * u_
+    else:
+        got = dev.qmm(w, _bf(x)).float().cpu().numpy()
+    assert dev.qmm_error_word() == 0
+    for r in range(rows):
+        rel, cos = _close(got[r], want[r])
+        assert rel <= 2e-2 and cos >= 0.9995, (name, rows, r, rel, cos)
+
+
+def test_qmm_mxfp4_block_scaled_outlier_inside_a_row():
+    """The block-scaled path scales each activation row by a power of two and carries it as two E4M3
+    halves.  A row whose largest element is 2^12 above the rest pushes the rest towards the bottom of
+    E4M3's range: the small elements' contribution must survive.  The outlier sits in a column whose
+    weights are zero for half of the outputs, so those outputs consist of the small elements only and
+    are judged on their own scale."""
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(77)
+    rows, n, k = 64, 256, 1024
+    packed = rng.integers(0, 256, (n, k // 2), dtype=np.uint8)
+    scales = rng.integers(118, 124, (n, k // 32), dtype=np.uint8)
+    col = 333
+    packed[: n // 2, col // 2] &= 0x0F if col % 2 else 0xF0  # E2M1 code 0 = +0 in the outlier's column
+    w = dev.QWeight(dev.Q_MXFP4_G32, packed, scales, None, n, k)
+    wd = ref_math.dequantize_mxfp4(packed, scales)
+    assert np.all(wd[: n // 2, col] == 0)
+    x = ref_math.bf16_round(rng.normal(0, 1, (rows, k)))
+    x[::2, col] = 4096.0 * np.sign(x[::2, col] + 1e-9)  # every other row has the outlier
+    want = ref_math.qmm(x, wd)
+    got = dev.qmm(w, _bf(x), path=dev.QMM_MXFP4_BLOCK_SCALED).float().cpu().numpy()
+    assert dev.qmm_error_word() == 0
+    for r in range(rows):
+        rel, cos = _close(got[r], want[r])                      # the whole row (the outlier dominates it)
+        assert rel <= 2e-2 and cos >= 0.9995, (r, rel, cos)
+        rel, cos = _close(got[r, : n // 2], want[r, : n // 2])  # outputs the outlier does not reach
+        assert rel <= 2e-2 and cos >= 0.9995, (r, "small elements", rel, cos)

@@ -296,3 +296,52 @@ def test_extend_copies_a_sequence_between_pools(kv_dtype_name):
     assert small.free_count() == 3
     for p in (src, dst, other, small):
         p.close()
+
+
+def test_filter_current_len_and_reset_match_the_page_table_oracle():
+    """Three members of the KVCacheStrategy vtable on the device pool: filter keeps the listed
+    sequences and frees what only the others held (src/kvcache/paged.zig:879-945), currentLen is the
+    longest sequence (:842-849), reset empties the pool (:851-862).  Tables, reference counts, free
+    count and the order in which freed pages come back are compared with the oracle after every call,
+    with shared (forked) pages in play; a slot outside the pool is InvalidBatchIndex (:904)."""
+    from dmlx_b200 import _lib
+
+    dev = _dev()
+    rng = np.random.default_rng(404)
+    n_pages, n_seqs = 96, 10
+    kv = dev.PagedKVCache(1, 2, 64, n_pages, n_seqs, 16, 8, max_rows=4096)
+    ref = ref_host.PagedKVTables(n_pages, n_seqs)
+    assert kv.current_len() == ref.current_len() == 0
+    for rnd in range(4):
+        seqs = list(range(0, 6))
+        counts = [int(rng.integers(1, 150)) for _ in seqs]
+        ref.reserve(seqs, counts)
+        kv.reserve(_desc(dev, [(s, c, 0, -1) for s, c in zip(seqs, counts)]))
+        assert kv.error_word() == 0
+        # slots 6..8 share prefixes of 0..2; a prefix of the whole source shares its partly filled last page too
+        for dst, src in ((6, 0), (7, 1), (8, 2)):
+            nt = ref.lens[src] if dst == 6 else int(rng.integers(1, ref.lens[src] + 1))
+            ref.fork(src, dst, nt)
+            kv.fork(src, dst, nt)
+        _check_tables(kv, ref, n_seqs)
+        assert kv.current_len() == ref.current_len() == max(ref.lens)
+        keep = [[1, 6, 8, 3], [0, 7], [], [9, 2, 4]][rnd]   # a donor without its sharer, a sharer without its donor, nobody, an empty slot
+        ref.filter(keep)
+        kv.filter(keep)
+        _check_tables(kv, ref, n_seqs)
+        assert kv.current_len() == ref.current_len()
+        # the pages that came back are handed out again in the same order
+        grow = [s for s in range(n_seqs) if s not in keep][:3]
+        ref.reserve(grow, [40, 33, 70][: len(grow)])
+        kv.reserve(_desc(dev, [(s, c, 0, -1) for s, c in zip(grow, [40, 33, 70])]))
+        assert kv.error_word() == 0
+        _check_tables(kv, ref, n_seqs)
+        ref.reset()
+        kv.reset()
+        _check_tables(kv, ref, n_seqs)
+        assert kv.current_len() == 0 and kv.free_count() == n_pages and sum(kv.ref_counts().tolist()) == 0
+    with pytest.raises(_lib.InvalidBatchIndex):
+        kv.filter([0, n_seqs])
+    with pytest.raises(ref_host.InvalidBatchIndex):
+        ref.filter([0, n_seqs])
+    kv.close()

@@ -358,3 +358,79 @@ def test_scheduler_with_real_block_manager(H):  # scheduler.zig:37-43 initWithRe
 def test_greedy_first_strict_max(H):  # sampling.zig:22-39
     assert H.greedy(np.array([1.0, 3.0, 3.0, 2.0], np.float32)) == 1
     assert H.greedy(np.array([5.0], np.float32)) == 0
+
+
+# ---- extensions: removal of one request, preemption by recomputation, admission hold ----------
+# (src/engine/engine_loop.zig:687-754 handleBatchError, src/engine/request_state.zig:182-189 cancel
+# flag; preemption has no reference counterpart).  Oracle and product must agree.
+
+
+def test_remove_running_request_frees_its_blocks_only(H):
+    bm = H.SchedBlockManager(4)
+    s = H.Scheduler(bm, 512)
+    a, b = H.Request(1, [1, 2, 3], 8, []), H.Request(2, [4, 5], 8, [])
+    s.add_request(a)
+    s.add_request(b)
+    s.schedule()
+    s.postprocess([(1, 10), (2, 11)])
+    assert bm.free_count() == 2
+    s.remove(a, 12)
+    assert a.state == H.DONE and a.error == 12 and list(a.generated_tokens) == [10]
+    assert bm.free_count() == 3 and s.active_count() == 1
+    r = s.schedule()
+    assert [q.id for q in r.decode_requests] == [2] and not r.prefill_requests
+    s.postprocess([(2, 12)])
+    assert list(b.generated_tokens) == [11, 12] and b.error == 0
+
+
+def test_remove_waiting_request(H):
+    s = H.Scheduler(H.SchedBlockManager(0), 512)
+    a = H.Request(1, [1, 2, 3], 8, [])
+    s.add_request(a)
+    assert s.schedule().is_empty()
+    s.remove(a, 12)
+    assert a.state == H.DONE and s.active_count() == 0
+
+
+def test_preempt_folds_output_into_prompt_and_resumes(H):
+    bm = H.SchedBlockManager(4)
+    s = H.Scheduler(bm, 2)
+    a = H.Request(1, [1, 2, 3], 5, [])
+    s.add_request(a)
+    s.schedule(); s.postprocess([(1, 0)])       # chunk [1, 2]
+    s.schedule(); s.postprocess([(1, 50)])      # chunk [3] -> first token
+    s.schedule(); s.postprocess([(1, 51)])      # decode
+    assert a.seq_len() == 5 and list(a.generated_tokens) == [50, 51]
+    s.preempt(a)
+    assert a.state == H.WAITING and a.prefill_offset == 0 and bm.free_count() == 4
+    assert list(a.prompt_tokens) == [1, 2, 3, 50, 51] and list(a.generated_tokens) == [50, 51]
+    assert a.seq_len() == 0
+    # second prefill: three chunks of two, the last one yields the next output token
+    for tok in (0, 0, 52):
+        r = s.schedule()
+        assert [q.id for q in r.prefill_requests] == [1]
+        s.postprocess([(1, tok)])
+    assert a.state == H.DECODING and list(a.generated_tokens) == [50, 51, 52] and a.seq_len() == 6
+    r = s.schedule()
+    assert [q.id for q in r.decode_requests] == [1]
+    s.postprocess([(1, 53)])
+    s.schedule(); s.postprocess([(1, 54)])
+    assert a.state == H.DONE and list(a.generated_tokens) == [50, 51, 52, 53, 54]  # max_tokens counts all five
+
+
+def test_preempted_request_waits_ahead_of_newcomers_and_hold_blocks_admission(H):
+    bm = H.SchedBlockManager(2)
+    s = H.Scheduler(bm, 512)
+    a, b, c = H.Request(1, [1], 4, []), H.Request(2, [2], 4, []), H.Request(3, [3], 4, [])
+    s.add_request(a)
+    s.add_request(b)
+    s.schedule(); s.postprocess([(1, 7), (2, 8)])
+    s.add_request(c)
+    s.preempt(b)
+    s.hold_admission(True)
+    r = s.schedule()
+    assert [q.id for q in r.decode_requests] == [1] and not r.prefill_requests and r.blocks_needed == 2
+    s.hold_admission(False)
+    r = s.schedule()
+    assert [q.id for q in r.prefill_requests] == [2]  # b first: one block free, c keeps waiting
+    assert r.blocks_needed == 1
