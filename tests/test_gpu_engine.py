@@ -17,7 +17,7 @@ CFG = ref_math.LlamaConfig(n_layers=4, hidden=512, n_heads=8, n_kv_heads=2, head
 N_REQ, N_STEPS = 8, 64
 # Sequences (of 8) whose 64 greedy ids equal the free-running fp32 oracle on a B200; the others part
 # from it at a near-tie that the per-token check below accepts.
-IDENTICAL_PINNED = 5
+IDENTICAL_PINNED = 1
 
 
 def _bits(a):

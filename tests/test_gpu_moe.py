@@ -161,7 +161,10 @@ def test_moe_layer_at_full_size_against_the_oracle_on_sampled_tokens(_restore_gr
     w_ref, i_ref = ref_math.gate_forward(logits, bias, k, route_scale=1.5)
     same = (idx == i_ref).all(axis=1)
     assert same.mean() >= 0.97, same.mean()   # the rest are swaps at near-ties of bf16 logits
-    assert np.allclose(wts[same], w_ref[same], rtol=1e-3, atol=1e-7)
+    # the device's gate matmul and the oracle may round a logit to neighbouring bf16 values (one ulp of a
+    # logit near 4 is 2^-6, i.e. 1.6 % of its softmax weight): most weights agree closely, all within 5 %
+    dev_rel = np.abs(wts[same] - w_ref[same]) / w_ref[same]
+    assert np.median(dev_rel) <= 1e-3 and dev_rel.max() <= 5e-2, (float(np.median(dev_rel)), float(dev_rel.max()))
     assert np.array_equal(off, ref_math.group_by_expert(idx, e)[3])
     counts = np.diff(off)
     assert counts.sum() == n * k and counts.max() > 2 * counts.mean()  # the bias skews the load
