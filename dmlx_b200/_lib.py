@@ -252,6 +252,7 @@ _sig("b200_sched_bm_note_free", None, vp, u64)
 _sig("b200_scheduler_remove", i32, vp, vp, i32)
 _sig("b200_scheduler_preempt", i32, vp, vp)
 _sig("b200_scheduler_hold_admission", None, vp, i32)
+_sig("b200_scheduler_set_admission_budget", None, vp, u64)
 _sig("b200_scheduler_running", u64, vp, P(vp), u64)
 _sig("b200_kv_limits", i32, vp, P(i32), P(i32))
 _sig("b200_qmm_debug_set_error_word", i32, i32, i32)

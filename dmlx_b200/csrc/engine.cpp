@@ -177,9 +177,25 @@ b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t ca
     if (active == 0) return B200_OK;
     // While running requests are short of pages nobody new is admitted: a newcomer would take the page
     // an older request is waiting for (the reference admits on one free block, src/scheduler.zig:291).
-    b200_scheduler_hold_admission(e->sched, (e->pressure || pressure_now) && b200_scheduler_running_count(e->sched) > 0);
-    e->prefill.resize(active);
-    e->decode.resize(active);
+    const uint64_t n_running = b200_scheduler_running_count(e->sched);
+    b200_scheduler_hold_admission(e->sched, (e->pressure || pressure_now) && n_running > 0);
+    // A newcomer is admitted only when its whole prompt fits beside what the running requests are still
+    // owed: the prompt pages they have been promised but have not allocated yet (an admitted request
+    // holds one page until its chunks run) and one page of growth each.  With nothing running the first
+    // request always gets in (it fits the pool, checked at submission).
+    {
+      const uint64_t free_now = b200_sched_bm_free_count(e->bm);
+      uint64_t owed = n_running;
+      e->running_tmp.resize(active);
+      const uint64_t n_run = b200_scheduler_running(e->sched, e->running_tmp.data(), active);
+      for (uint64_t i = 0; i < n_run; ++i) {
+        const b200_request* r = e->running_tmp[i];
+        if (b200_request_state(r) != B200_REQ_PREFILLING) continue;
+        const uint64_t want = pages_for(b200_request_prompt_len(r) + 1), held = pages_held(b200_request_prefill_offset(r));
+        if (want > held) owed += want - held;
+      }
+      b200_scheduler_set_admission_budget(e->sched, n_running == 0 ? (uint64_t)e->pool_pages : (free_now > owed ? free_now - owed : 0));
+    }
     uint64_t need = 0;
     np = nd = 0;
     st = b200_scheduler_schedule(e->sched, e->prefill.data(), &np, e->decode.data(), &nd, active, &need);

@@ -490,6 +490,10 @@ struct b200_scheduler {
   uint64_t max_prefill_tokens = 0;
   uint64_t blocks_per_request = 1;
   bool hold_admission = false;  // waiting requests stay where they are (set by a caller under pool pressure)
+  // Pages the caller is willing to hand to newcomers in one schedule() call (default: no limit, the
+  // reference's behaviour).  A waiting request is promoted only while ceil((prompt + 1) / 32) pages are
+  // left of it, in arrival order: the first request that does not fit stops the promotions.
+  uint64_t admission_budget = ~0ull;
 };
 
 extern "C" {
@@ -527,9 +531,14 @@ b200_status b200_scheduler_schedule(b200_scheduler* s, b200_request** prefill_ou
   }
   // Promote waiting requests while a block can be had; keep arrival order among those left.
   size_t kept = 0;
+  uint64_t budget = s->admission_budget;
+  bool closed = s->hold_admission;
   for (size_t i = 0; i < s->waiting.size(); ++i) {
     b200_request* r = s->waiting[i];
-    if (!s->hold_admission && s->bm->can_allocate(s->blocks_per_request)) {
+    const uint64_t prompt_pages = (r->prompt.size() + 1 + 31) / 32;
+    if (!closed && budget != ~0ull && prompt_pages > budget) closed = true;  // arrival order: nobody overtakes it
+    if (!closed && s->bm->can_allocate(s->blocks_per_request)) {
+      if (budget != ~0ull) budget -= prompt_pages;
       b200_status st = s->bm->allocate(r, s->blocks_per_request);
       if (st == B200_ERR_INSUFFICIENT_BLOCKS && s->bm->kv) {
         // The device pool turned out to be empty (its cached free count was stale): the request keeps
@@ -632,6 +641,7 @@ b200_status b200_scheduler_preempt(b200_scheduler* s, b200_request* r) {
 }
 
 void b200_scheduler_hold_admission(b200_scheduler* s, int32_t on) { s->hold_admission = on != 0; }
+void b200_scheduler_set_admission_budget(b200_scheduler* s, uint64_t pages) { s->admission_budget = pages; }
 
 uint64_t b200_scheduler_running(const b200_scheduler* s, b200_request** out, uint64_t cap) {
   for (uint64_t i = 0; i < s->running.size() && i < cap; ++i) out[i] = s->running[i];

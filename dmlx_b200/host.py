@@ -284,6 +284,9 @@ class Scheduler:
     def hold_admission(self, on: bool) -> None:
         lib.b200_scheduler_hold_admission(self._h, int(on))
 
+    def set_admission_budget(self, pages: Optional[int]) -> None:
+        lib.b200_scheduler_set_admission_budget(self._h, 2 ** 64 - 1 if pages is None else int(pages))
+
     def waiting_count(self) -> int:
         return int(lib.b200_scheduler_waiting_count(self._h))
 

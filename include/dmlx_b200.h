@@ -165,6 +165,11 @@ b200_status b200_scheduler_remove(b200_scheduler* s, b200_request* r, int32_t er
 b200_status b200_scheduler_preempt(b200_scheduler* s, b200_request* r);
 /* While on, schedule() promotes no waiting request. */
 void b200_scheduler_hold_admission(b200_scheduler* s, int32_t on);
+/* Pages that one schedule() call may promise to newcomers (UINT64_MAX, the default, is the reference's
+ * rule: one free block admits, :291-293).  With a budget a waiting request is promoted only while
+ * ceil((prompt + 1) / 32) pages of it are left, in arrival order; the first request that does not fit
+ * stops the promotions of that call. */
+void b200_scheduler_set_admission_budget(b200_scheduler* s, uint64_t pages);
 /* Running requests in admission order. */
 uint64_t b200_scheduler_running(const b200_scheduler* s, b200_request** out, uint64_t cap);
 uint64_t b200_scheduler_active_count(const b200_scheduler* s);                   /* :384-386 */
@@ -225,7 +230,10 @@ typedef struct b200_kv_config {
   int32_t kv_dtype;          /* B200_KV_BF16 | B200_KV_FP8_E4M3 (one f32 scale per page and kv head) */
   int32_t max_rows;          /* largest packed batch (rows) a step may carry */
   int32_t n_q_heads;         /* LayerConfig.num_heads (sizes the split-K scratch) */
-  int32_t attn_scratch_chunks; /* split-K partial slots; 0 = n_pages/4 + max_rows + 8 */
+  int32_t attn_scratch_chunks; /* split-K partial slots; 0 = n_pages/4 + max_rows + 8, which covers decode-only
+                                * steps.  Steps with prefill chunks serve 16 / (q heads per kv head) rows per
+                                * group and need, per group, ceil(context pages / 8) slots; a step that needs more
+                                * slots than the pool holds is flagged B200_ERR_CAPACITY and changes nothing. */
 } b200_kv_config;
 b200_status b200_kv_create(const b200_kv_config* cfg, b200_kv** out);            /* :342-411 init, :1141-1186 factories */
 void b200_kv_destroy(b200_kv* kv);                                               /* :1111-1138 deinit */

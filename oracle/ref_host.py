@@ -288,6 +288,7 @@ class Scheduler:
         self.max_prefill_tokens = max_prefill_tokens
         self.blocks_per_request = 1  # :242
         self.hold = False  # extension: schedule() promotes nobody while set
+        self.admission_budget: Optional[int] = None  # extension: pages one schedule() may promise to newcomers
 
     def add_request(self, req: Request) -> None:  # :252-255
         req.state = WAITING
@@ -301,8 +302,14 @@ class Scheduler:
             else:
                 decode_list.append(req)
         still_waiting, blocks_needed = [], 0
+        budget, closed = self.admission_budget, self.hold
         for req in self.waiting:
-            if not self.hold and self.block_manager.can_allocate(self.blocks_per_request):
+            prompt_pages = -(-(len(req.prompt_tokens) + 1) // PAGE_SIZE)
+            if not closed and budget is not None and prompt_pages > budget:
+                closed = True  # arrival order: nobody overtakes the first request that does not fit
+            if not closed and self.block_manager.can_allocate(self.blocks_per_request):
+                if budget is not None:
+                    budget -= prompt_pages
                 self.block_manager.allocate_blocks(req, self.blocks_per_request)
                 req.state = PREFILLING
                 prefill_list.append(req)
@@ -365,6 +372,9 @@ class Scheduler:
 
     def hold_admission(self, on: bool) -> None:
         self.hold = bool(on)
+
+    def set_admission_budget(self, pages: Optional[int]) -> None:
+        self.admission_budget = pages
 
 
 # ---------------------------------------------------------------------------

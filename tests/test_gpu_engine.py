@@ -161,7 +161,7 @@ def test_pool_too_small_defers_and_preempts_instead_of_failing():
     assert stats_r == (0, 0, 0) and (free_r, err_r, act_r, refs_r) == (64, 0, 0, 0)
     tight, st_t, stats_t, (free_t, err_t, act_t, refs_t, steps_t) = _run_engine(dev, cfg, model, prompts, n_new, 20)
     assert (free_t, err_t, act_t, refs_t) == (20, 0, 0, 0), (free_t, err_t, act_t, refs_t)
-    assert stats_t[0] > 0 and stats_t[1] > 0 and stats_t[2] == 0, stats_t  # waited, preempted, nobody failed
+    assert stats_t[0] > 0 and stats_t[2] == 0, stats_t  # requests waited for pages, nobody failed
     same = 0
     for i, p in enumerate(prompts):
         got, done = tight[i + 1]
@@ -169,6 +169,29 @@ def test_pool_too_small_defers_and_preempts_instead_of_failing():
         _check_against_oracle(cfg, weights, p, got, i)
         same += got == roomy[i + 1][0]
     assert same >= 3, same  # a recomputed cache may flip a near-tie, most sequences do not meet one
+    model.close()
+
+
+def test_two_requests_blocked_on_the_same_step_preempt_the_younger():
+    """Two requests of equal length in a pool that holds both prompts but not both outputs: at the step
+    where each needs its fifth page none is free and both are blocked.  The younger one gives its pages
+    back, waits (its whole prompt, now including what it has generated, must fit before it returns), is
+    prefilled again and finishes with the tokens the oracle decodes for it."""
+    from dmlx_b200 import device as dev
+    from dmlx_b200 import _lib
+
+    cfg = CFG
+    weights = ref_math.random_llama_weights(cfg, seed=2026)
+    model = _build_model(dev, cfg, weights)
+    rng = np.random.default_rng(15)
+    prompts = [rng.integers(0, cfg.vocab, 96).tolist() for _ in range(2)]
+    out, status, stats, (free, err, active, refs, steps) = _run_engine(dev, cfg, model, prompts, 40, 8)
+    assert (free, err, active, refs) == (8, 0, 0, 0)
+    assert stats[1] == 1 and stats[2] == 0, stats   # exactly one preemption, nobody failed
+    for rid in (1, 2):
+        got, done = out[rid]
+        assert done and len(got) == 40 and status[rid] == _lib.OK
+        _check_against_oracle(cfg, weights, prompts[rid - 1], got, rid)
     model.close()
 
 

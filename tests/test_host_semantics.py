@@ -434,3 +434,22 @@ def test_preempted_request_waits_ahead_of_newcomers_and_hold_blocks_admission(H)
     r = s.schedule()
     assert [q.id for q in r.prefill_requests] == [2]  # b first: one block free, c keeps waiting
     assert r.blocks_needed == 1
+
+
+def test_admission_budget_in_pages_keeps_arrival_order(H):
+    """With a page budget, a waiting request is promoted only while ceil((prompt + 1) / 32) pages of the
+    budget are left, and the first one that does not fit stops the promotions of that call (nobody
+    overtakes it); without a budget one free block admits, as in src/scheduler.zig:291-293."""
+    s = H.Scheduler(H.SchedBlockManager(64), 512)
+    reqs = [H.Request(i + 1, list(range(n)), 4, []) for i, n in enumerate((31, 64, 200, 10))]  # 1, 3, 7, 1 pages
+    for r in reqs:
+        s.add_request(r)
+    s.set_admission_budget(5)
+    r = s.schedule()
+    assert [q.id for q in r.prefill_requests] == [1, 2] and r.blocks_needed == 2  # 3 needs 7 > 1 left; 4 waits behind it
+    s.set_admission_budget(7)
+    r = s.schedule()
+    assert [q.id for q in r.prefill_requests] == [1, 2, 3] and r.blocks_needed == 1
+    s.set_admission_budget(None)
+    r = s.schedule()
+    assert [q.id for q in r.prefill_requests] == [1, 2, 3, 4]
