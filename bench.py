@@ -320,6 +320,13 @@ def run_llama(args, rank, world, local):
         launches_before = model.launch_count()
         kv.close()
         arrivals = run_arrivals(args, rank, world, local, model=model, c=c)
+    # on several GPUs: the one workload with an exchange step, the MoE layer stack under expert parallelism
+    expert_parallel = None
+    if world > 1 and not args.no_ep and not args.layers:
+        model.close()
+        torch.cuda.empty_cache()
+        mc, m_total, m_e2e, mK, _, _, _, _ = moe_measure(args, rank, world, torch, dist, dev, steps=20)
+        expert_parallel = moe_summary(mc, m_total, m_e2e, mK, world)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -365,6 +372,8 @@ def run_llama(args, rank, world, local):
     result["roofline"]["traffic_note"] = "dram bytes of an ncu capture of a 16-sequence case, scaled by cached tokens (ratio to algorithmic bytes 1.02)"
     if arrivals:
         result["arrivals"] = arrivals
+    if expert_parallel:
+        result["expert_parallel"] = expert_parallel
     if not args.no_cpu_baseline and world == 1:
         result["cpu_baseline"] = cpu_baseline_c3(c, n_req)
     print(json.dumps(result))
@@ -609,16 +618,11 @@ def run_arrivals(args, rank, world, local, model=None, c=None, quiet=False):
 MOE = dict(hidden=4096, n_experts=256, inter=2048, top_k=6, layers=4, tokens=4096)
 
 
-def run_moe(args, rank, world, local):
-    import torch
-    import torch.distributed as dist
-
-    from dmlx_b200 import device as dev
+def moe_measure(args, rank, world, torch, dist, dev, steps=None):
+    """The MoE layer stack on `world` ranks (experts sharded over the ranks when world > 1): device-timed
+    and end-to-end times of a step, max over ranks.  Returns (config, total_ms, e2e_ms, K, W, launches, clocks, bytes)."""
     from dmlx_b200 import expert_parallel as ep
 
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     c = dict(MOE)
     if args.layers:
         c["layers"] = args.layers
@@ -626,11 +630,12 @@ def run_moe(args, rank, world, local):
         dev.set_qmm_grouped_tmem_a(bool(args.moe_tmem_a))
     if args.moe_block_scaled >= 0:
         dev.set_qmm_grouped_block_scaled(bool(args.moe_block_scaled))
-    K, W = args.steps, max(args.warmup, 3)
+    K, W = steps or args.steps, max(args.warmup, 3)
     n_tok = c["tokens"] // world  # the step decodes 4096 tokens in total: strong scaling
     el = c["n_experts"] // world
     rng = np.random.default_rng(77)
-    bias = torch.tensor(rng.normal(0, 0.004, c["n_experts"]).astype(np.float32), device="cuda")  # skewed load
+    bias = rng.normal(0, 0.004, c["n_experts"]).astype(np.float32)  # skewed load
+    comm = ep.Communicator(rank, world) if world > 1 else None
     layers = []
     for l in range(c["layers"]):
         gate = dev.QWeight.random(dev.Q_BF16, c["n_experts"], c["hidden"], 1, seed=1000 + l)
@@ -640,18 +645,18 @@ def run_moe(args, rank, world, local):
         sdn = dev.QWeight.random(dev.Q_MXFP4_G32, c["hidden"], c["inter"], 1, seed=5000 + l)
         if world == 1:
             layers.append(dev.MoELayer(c["hidden"], c["n_experts"], c["inter"], c["top_k"], gate, gu, dn, sgu, sdn,
-                                       bias=bias.cpu().numpy(), route_scale=1.5, tile_rows=args.moe_tile, max_tokens=n_tok))
+                                       bias=bias, route_scale=1.5, tile_rows=args.moe_tile, max_tokens=n_tok))
         else:
-            layers.append(ep.ExpertParallelMoE(c["hidden"], c["n_experts"], c["inter"], c["top_k"], gate, gu, dn, sgu, sdn,
-                                               bias=bias, route_scale=1.5, tile_rows=args.moe_tile))
-    g = torch.Generator(device="cuda").manual_seed(11 + rank)
+            layers.append(ep.ExpertParallelMoE(comm, c["hidden"], c["n_experts"], c["inter"], c["top_k"], gate, gu, dn, sgu, sdn,
+                                               bias=bias, route_scale=1.5, tile_rows=args.moe_tile, max_tokens=n_tok))
     x_host = torch.randn((n_tok, c["hidden"]), generator=torch.Generator().manual_seed(11 + rank)).bfloat16().pin_memory()
     x = x_host.cuda()
+    bufs = [torch.empty_like(x) for _ in range(2)]
 
     def step(inp):
         h = inp
-        for layer in layers:
-            h = layer.forward(h)
+        for i, layer in enumerate(layers):
+            h = layer.forward(h, bufs[i & 1])
         return h
 
     def barrier():
@@ -659,7 +664,7 @@ def run_moe(args, rank, world, local):
             dist.barrier()
         torch.cuda.synchronize()
 
-    sampler = ClockSampler(local)
+    sampler = ClockSampler(torch.cuda.current_device())
     if rank == 0:
         sampler.start()
     for _ in range(W):
@@ -687,10 +692,41 @@ def run_moe(args, rank, world, local):
     e2e_ms = t0.elapsed_time(t1)
     clocks = sampler.stop() if rank == 0 else None
     assert dev.qmm_error_word() == 0
+    if comm is not None:
+        comm.wait(timeout_ms=20000)
     if world > 1:
         t = torch.tensor([total_ms, e2e_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         total_ms, e2e_ms = t.tolist()
+    for layer in layers:
+        layer.close()
+    if comm is not None:
+        comm.close()
+    return c, total_ms, e2e_ms, K, W, int(launches), clocks, int(x_host.numel() * 2 * world)
+
+
+def moe_summary(c, total_ms, e2e_ms, K, world):
+    """Short form of the MoE measurement (the default workload reports it when it runs on several GPUs)."""
+    ms = total_ms / K
+    per_expert_params = 3 * c["inter"] * c["hidden"]
+    flops = c["layers"] * c["tokens"] * (c["top_k"] + 1) * 2.0 * per_expert_params
+    return {"workload": f"moe_mxfp4 layer stack: {c['layers']} layers, hidden {c['hidden']}, {c['n_experts']} routed experts of "
+                        f"{c['inter']} + 1 shared, top-{c['top_k']}, {c['tokens']} tokens per step in total",
+            "parallelism": f"ep{world}: experts sharded over the ranks, all-gather dispatch + f32 reduce-scatter combine (NCCL)",
+            "scaling": "strong", "ms_per_step": ms, "tokens_per_s": c["tokens"] / (ms * 1e-3),
+            "e2e_tokens_per_s": c["tokens"] / (e2e_ms / K * 1e-3), "tflops_bf16_equivalent": flops / (ms * 1e-3) / 1e12}
+
+
+def run_moe(args, rank, world, local):
+    import torch
+    import torch.distributed as dist
+
+    from dmlx_b200 import device as dev
+
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    c, total_ms, e2e_ms, K, W, launches, clocks, io_bytes = moe_measure(args, rank, world, torch, dist, dev)
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -712,10 +748,10 @@ def run_moe(args, rank, world, local):
                    "parallelism": f"ep{world}" if world > 1 else "single GPU, all experts local"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                      "peak_kind": "of measured (sustained cuBLAS bf16)" if peaks else "of fallback", "traffic": None,
-                     "kernel": "qmm_tca_kernel<mxfp4> grouped (gate/up + down) and dense (shared expert)",
+                     "kernel": "qmm_mx_kernel grouped (gate/up + down, tcgen05 kind::mxf8f6f4 block-scaled) and dense (shared expert)",
                      "algorithmic_flops_per_step": flops},
         "e2e": {"value": c["tokens"] / (e2e_ms / K * 1e-3), "unit": "decode tokens/s",
-                "h2d_bytes_per_step": int(x_host.numel() * 2 * world), "d2h_bytes_per_step": int(x_host.numel() * 2 * world)},
+                "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes},
         "gpu_launches": int(launches), "clocks": clocks,
     }))
     if world > 1:
@@ -1058,6 +1094,7 @@ def main():
     ap.add_argument("--path", type=int, default=0, help="qmm_* only: kernel path (0 = automatic)")
     ap.add_argument("--seqs", type=int, default=64, help="sequences per GPU (64 = the configuration; fewer for profiling)")
     ap.add_argument("--no-arrivals", action="store_true", help="llama8b_int4 only: skip the arrival-process scenarios")
+    ap.add_argument("--no-ep", action="store_true", help="llama8b_int4 on several GPUs only: skip the expert-parallel MoE measurement")
     ap.add_argument("--arrival-scenarios", default="both", help="poisson_20rps | saturation | both")
     ap.add_argument("--pool-pages", type=int, default=3072, help="arrival scenarios: KV pages per replica (32 tokens x 32 layers x 4 KiB each)")
     ap.add_argument("--prefill-chunk", type=int, default=512, help="arrival scenarios: prefill chunk (tokens)")

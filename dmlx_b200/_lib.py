@@ -208,7 +208,15 @@ _sig("b200_llama_profile_collect", i32, vp, P(C.c_double), P(C.c_int64))
 
 class MoeConfig(C.Structure):
     _fields_ = [(n, i32) for n in ("hidden", "n_experts", "inter", "top_k", "scoring", "tile_rows", "max_tokens")] + \
-               [("route_scale", f32), ("swiglu_limit", f32), ("shared_swiglu_limit", f32)]
+               [("route_scale", f32), ("swiglu_limit", f32), ("shared_swiglu_limit", f32), ("ep_rank", i32), ("ep_world", i32)]
+
+
+EP_UNIQUE_ID_BYTES = 128
+
+
+class EpWatchOps(C.Structure):
+    _fields_ = [("done", C.CFUNCTYPE(C.c_int, vp)), ("async_error", C.CFUNCTYPE(C.c_int, vp)), ("abort", C.CFUNCTYPE(None, vp)),
+                ("ctx", vp)]
 
 
 _sig("b200_moe_route", i32, vp, i32, vp, i32, i32, i32, i32, f32, vp, vp, vp, vp)
@@ -221,6 +229,19 @@ _sig("b200_moe_create", i32, P(MoeConfig), vp, P(f32), vp, vp, vp, vp, P(vp))
 _sig("b200_moe_destroy", None, vp)
 _sig("b200_moe_forward", i32, vp, vp, i32, vp, vp)
 _sig("b200_moe_last_routing", i32, vp, i32, vp, vp, vp)
+_sig("b200_ep_unique_id", i32, P(C.c_uint8))
+_sig("b200_ep_create", i32, i32, i32, P(C.c_uint8), P(vp))
+_sig("b200_ep_destroy", None, vp)
+_sig("b200_ep_rank", i32, vp)
+_sig("b200_ep_world", i32, vp)
+_sig("b200_ep_nccl_version", i32)
+_sig("b200_ep_dispatch", i32, vp, vp, vp, i32, i32, vp)
+_sig("b200_ep_plan", i32, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, vp)
+_sig("b200_ep_combine", i32, vp, vp, vp, i32, i32, vp)
+_sig("b200_moe_forward_ep", i32, vp, vp, vp, i32, vp, vp)
+_sig("b200_ep_wait", i32, vp, vp, i32)
+_sig("b200_ep_abort", i32, vp)
+_sig("b200_ep_watch", i32, P(EpWatchOps), i32, i32)
 
 
 _sig("b200_request_prompt", u64, vp, P(u32), u64)

@@ -195,15 +195,76 @@ __global__ void __launch_bounds__(1024) place_kernel(const uint32_t* __restrict_
 }
 
 // row_scales[p] = weights[order[p]] alone (the rows themselves are read in place by the matmul).
-__global__ void row_scales_kernel(const int* __restrict__ order, const float* __restrict__ weights, int n, float* __restrict__ out) {
+// n_valid (optional, device): rows that exist when n is only the capacity.
+__global__ void row_scales_kernel(const int* __restrict__ order, const float* __restrict__ weights, int n, float* __restrict__ out,
+                                  const int* __restrict__ n_valid) {
   const int p = blockIdx.x * blockDim.x + threadIdx.x;
-  if (p < n) out[p] = weights[order[p]];
+  if (p < n && (!n_valid || p < *n_valid)) out[p] = weights[order[p]];
+}
+
+// Expert parallelism: global expert ids -> ids among this rank's experts, everything else marked as
+// "not mine" (a value no expert matches, so the counting sort leaves those assignments out).
+__global__ void localize_kernel(const uint32_t* __restrict__ idx, int n_assign, int first_expert, int n_local,
+                                uint32_t* __restrict__ local_idx) {
+  const int a = blockIdx.x * blockDim.x + threadIdx.x;
+  if (a >= n_assign) return;
+  const int e = (int)idx[a] - first_expert;
+  local_idx[a] = (e >= 0 && e < n_local) ? (uint32_t)e : 0xFFFFFFFFu;
+}
+
+// Expert parallelism: this rank's share of every token's sum over k (f32; zero where none of the
+// token's experts lives here).  inv_order[a] < 0 marks an assignment served by another rank.
+__global__ void combine_partial_kernel(const __nv_bfloat16* __restrict__ y_sorted, const int* __restrict__ inv_order, int k,
+                                       int hidden, float* __restrict__ out) {
+  const int t = blockIdx.x;
+  int rows[kMaxTopK];
+  for (int j = 0; j < k; ++j) rows[j] = inv_order[t * k + j];
+  for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < k; ++j) {
+      if (rows[j] < 0) continue;
+      const uint4 q = reinterpret_cast<const uint4*>(y_sorted + (size_t)rows[j] * hidden)[i];
+      const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[2 * e] += __uint_as_float(w[e] << 16);
+        acc[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+      }
+    }
+    float4* dst = reinterpret_cast<float4*>(out + (size_t)t * hidden) + 2 * i;
+    dst[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    dst[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+  }
+}
+
+// Expert parallelism: out = bf16(routed sum (f32, reduced over the ranks) + shared expert).
+__global__ void add_shared_kernel(const float* __restrict__ routed, const __nv_bfloat16* __restrict__ shared_out, size_t n8,
+                                  __nv_bfloat16* __restrict__ out) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n8) return;
+  const float4 a = reinterpret_cast<const float4*>(routed)[2 * i], b = reinterpret_cast<const float4*>(routed)[2 * i + 1];
+  float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  if (shared_out) {
+    const uint4 q = reinterpret_cast<const uint4*>(shared_out)[i];
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int e = 0; e < 4; ++e) { v[2 * e] += __uint_as_float(w[e] << 16); v[2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u); }
+  }
+  uint4 o;
+  __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+  __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
+  o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+  o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+  reinterpret_cast<uint4*>(out)[i] = o;
 }
 
 __global__ void gather_sorted_kernel(const __nv_bfloat16* __restrict__ x, const int* __restrict__ order,
                                      const float* __restrict__ weights, int k, int hidden,
-                                     __nv_bfloat16* __restrict__ x_sorted, float* __restrict__ row_scales) {
-  const int p = blockIdx.x, a = order[p];
+                                     __nv_bfloat16* __restrict__ x_sorted, float* __restrict__ row_scales,
+                                     const int* __restrict__ n_valid) {
+  const int p = blockIdx.x;
+  if (n_valid && p >= *n_valid) return;
+  const int a = order[p];
   const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(a / k) * hidden);
   uint4* dst = reinterpret_cast<uint4*>(x_sorted + (size_t)p * hidden);
   for (int i = threadIdx.x; i < hidden / 8; i += blockDim.x) dst[i] = src[i];
@@ -301,7 +362,7 @@ b200_status b200_moe_gather(const void* d_x, const int32_t* d_order, const float
   if (hidden % 8) { b200_set_error("gather: hidden must be a multiple of 8"); return B200_ERR_INVALID_ARGUMENT; }
   if (n_assign <= 0) return B200_OK;
   gather_sorted_kernel<<<n_assign, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)d_x, d_order, d_weights, k, hidden,
-                                                                  (__nv_bfloat16*)d_x_sorted, d_row_scales);
+                                                                  (__nv_bfloat16*)d_x_sorted, d_row_scales, nullptr);
   B200_LAUNCH_CHECK();
   return B200_OK;
 }
@@ -334,6 +395,34 @@ b200_status b200_moe_combine(const void* d_y_sorted, const int32_t* d_inv_order,
   return B200_OK;
 }
 
+// Expert parallelism, the plan of one rank (the grouping of src/models/deepseek_v4.zig:747-784 restricted
+// to the experts that live on `rank`): of the N*k assignments of all ranks' tokens, those whose expert is
+// one of this rank's n_experts / world are grouped by local expert (stable); offsets [E_local + 1],
+// order [<= N*k] (row p of the grouped matmul is assignment order[p]), inv_order [N*k] (-1 where the
+// assignment is served elsewhere), work items, and the local ids as scratch.  d_counts is the histogram
+// over the global experts that b200_moe_route produced.
+b200_status b200_ep_plan(const uint32_t* d_indices, const int32_t* d_counts, int32_t n_tokens, int32_t k, int32_t n_experts,
+                         int32_t rank, int32_t world, int32_t tile_rows, uint32_t* d_local_idx, int32_t* d_offsets,
+                         int32_t* d_order, int32_t* d_inv_order, void* d_items, int32_t* d_n_items, void* stream) {
+  b200_status st = b200_require_device();
+  if (st != B200_OK) return st;
+  if (world <= 0 || n_experts % world != 0 || rank < 0 || rank >= world || tile_rows <= 0 || n_experts / world > kMaxExperts) {
+    b200_set_error("ep plan: %d experts over %d ranks (rank %d)", n_experts, world, rank);
+    return B200_ERR_INVALID_ARGUMENT;
+  }
+  if (n_tokens <= 0) return B200_OK;
+  const int n_local = n_experts / world, A = n_tokens * k;
+  cudaStream_t s = (cudaStream_t)stream;
+  localize_kernel<<<(A + 255) / 256, 256, 0, s>>>(d_indices, A, rank * n_local, n_local, d_local_idx);
+  B200_LAUNCH_CHECK();
+  B200_CUDA_TRY(cudaMemsetAsync(d_inv_order, 0xFF, sizeof(int) * (size_t)A, s));
+  offsets_items_kernel<<<1, 256, 0, s>>>(d_counts + rank * n_local, n_local, tile_rows, d_offsets, (int4*)d_items, d_n_items);
+  B200_LAUNCH_CHECK();
+  place_kernel<<<n_local, 1024, 0, s>>>(d_local_idx, A, d_offsets, d_order, d_inv_order);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
 }  // extern "C"
 
 // ---------------------------------------------------------------------------------------------
@@ -351,6 +440,13 @@ struct b200_moe {
   int *counts = nullptr, *offsets = nullptr, *order = nullptr, *inv_order = nullptr, *n_items = nullptr;
   int4* items = nullptr;
   int max_items = 0;
+  // expert parallelism (cfg.ep_world > 1): the weights hold this rank's n_experts / ep_world experts; the
+  // buffers above are sized for the tokens of all ranks
+  int n_local = 0, first_expert = 0;
+  __nv_bfloat16* x_all = nullptr;   // [world * max_tokens, hidden]: every rank's tokens (all-gather)
+  uint32_t* local_idx = nullptr;    // [world * max_tokens * k]
+  float *partial = nullptr;         // [world * max_tokens, hidden] f32: this rank's share of every token's sum
+  float *reduced = nullptr;         // [max_tokens, hidden] f32: the sums of this rank's tokens (reduce-scatter)
 };
 
 extern "C" {
@@ -358,7 +454,8 @@ extern "C" {
 void b200_moe_destroy(b200_moe* m) {
   if (!m) return;
   void* ptrs[] = {m->d_bias, m->logits, m->x_sorted, m->act_sorted, m->y_sorted, m->sh_act, m->sh_out, m->indices, m->weights,
-                  m->row_scales, m->counts, m->offsets, m->order, m->inv_order, m->n_items, m->items};
+                  m->row_scales, m->counts, m->offsets, m->order, m->inv_order, m->n_items, m->items, m->x_all, m->local_idx,
+                  m->partial, m->reduced};
   for (void* p : ptrs) if (p) cudaFree(p);
   delete m;
 }
@@ -369,9 +466,16 @@ b200_status b200_moe_create(const b200_moe_config* c, const b200_qweight* gate, 
   *out = nullptr;
   b200_status st = b200_require_device();
   if (st != B200_OK) return st;
+  const bool ep_mode = c->ep_world >= 1;  // a group of one rank runs the same path (tests on one GPU)
+  const int world = ep_mode ? c->ep_world : 1;
+  if (ep_mode && (c->n_experts % world != 0 || c->ep_rank < 0 || c->ep_rank >= world || c->hidden % 8 != 0)) {
+    b200_set_error("moe: %d experts do not divide over %d ranks (rank %d)", c->n_experts, world, c->ep_rank);
+    return B200_ERR_INVALID_ARGUMENT;
+  }
+  const int n_local = c->n_experts / world;
   if (!gate || !experts_gate_up || !experts_down || gate->n != c->n_experts || gate->k != c->hidden ||
-      experts_gate_up->n_experts != c->n_experts || experts_gate_up->n != 2 * c->inter || experts_gate_up->k != c->hidden ||
-      experts_down->n_experts != c->n_experts || experts_down->n != c->hidden || experts_down->k != c->inter ||
+      experts_gate_up->n_experts != n_local || experts_gate_up->n != 2 * c->inter || experts_gate_up->k != c->hidden ||
+      experts_down->n_experts != n_local || experts_down->n != c->hidden || experts_down->k != c->inter ||
       c->tile_rows % 16 != 0 || c->tile_rows < 16 || c->tile_rows > 256 || c->max_tokens <= 0) {
     b200_set_error("moe: weight shapes do not match the configuration");
     return B200_ERR_INVALID_ARGUMENT;
@@ -379,8 +483,12 @@ b200_status b200_moe_create(const b200_moe_config* c, const b200_qweight* gate, 
   auto* m = new b200_moe();
   m->cfg = *c;
   m->gate = gate; m->exp_gu = experts_gate_up; m->exp_down = experts_down; m->sh_gu = shared_gate_up; m->sh_down = shared_down;
-  const size_t N = c->max_tokens, A = N * c->top_k;
-  m->max_items = c->n_experts + (int)((A + c->tile_rows - 1) / c->tile_rows);
+  m->n_local = n_local;
+  m->first_expert = ep_mode ? c->ep_rank * n_local : 0;
+  // with expert parallelism every rank routes the tokens of all ranks; a rank's matmul rows are the
+  // assignments that fall on its experts, at most all of them
+  const size_t N = (size_t)c->max_tokens * world, A = N * c->top_k;
+  m->max_items = n_local + (int)((A + c->tile_rows - 1) / c->tile_rows);
 #define M_ALLOC(ptr, bytes)                                                                  \
   do {                                                                                       \
     if (cudaMalloc((void**)&(ptr), (bytes)) != cudaSuccess) {                                \
@@ -407,6 +515,12 @@ b200_status b200_moe_create(const b200_moe_config* c, const b200_qweight* gate, 
     M_ALLOC(m->sh_act, N * (shared_gate_up->n / 2) * 2);
     M_ALLOC(m->sh_out, N * c->hidden * 2);
   }
+  if (ep_mode) {
+    M_ALLOC(m->x_all, N * c->hidden * 2);
+    M_ALLOC(m->local_idx, A * 4);
+    M_ALLOC(m->partial, N * c->hidden * 4);
+    M_ALLOC(m->reduced, (size_t)c->max_tokens * c->hidden * 4);
+  }
   if (h_bias) {
     M_ALLOC(m->d_bias, sizeof(float) * c->n_experts);
     cudaMemcpy(m->d_bias, h_bias, sizeof(float) * c->n_experts, cudaMemcpyHostToDevice);
@@ -418,6 +532,7 @@ b200_status b200_moe_create(const b200_moe_config* c, const b200_qweight* gate, 
 
 b200_status b200_moe_forward(b200_moe* m, const void* d_x, int32_t n_tokens, void* d_out, void* stream) {
   const b200_moe_config& c = m->cfg;
+  if (c.ep_world >= 1) { b200_set_error("moe: a layer built for expert parallelism runs through b200_moe_forward_ep"); return B200_ERR_INVALID_ARGUMENT; }
   if (n_tokens > c.max_tokens) { b200_set_error("moe: %d tokens > max_tokens %d", n_tokens, c.max_tokens); return B200_ERR_CAPACITY; }
   if (n_tokens <= 0) return B200_OK;
   const int A = n_tokens * c.top_k;
@@ -436,7 +551,7 @@ b200_status b200_moe_forward(b200_moe* m, const void* d_x, int32_t n_tokens, voi
   if (b200_qmm_grouped_takes_tokens(m->exp_gu, c.tile_rows)) {
     // the block-scaled path re-encodes every activation row anyway: it reads the rows from the token
     // matrix through `order`, and no expert-sorted bf16 copy is made
-    row_scales_kernel<<<(A + 255) / 256, 256, 0, (cudaStream_t)stream>>>(m->order, m->weights, A, m->row_scales);
+    row_scales_kernel<<<(A + 255) / 256, 256, 0, (cudaStream_t)stream>>>(m->order, m->weights, A, m->row_scales, nullptr);
     B200_LAUNCH_CHECK();
     STEP(b200_qmm_grouped_from_tokens(m->exp_gu, d_x, m->order, c.top_k, A, m->act_sorted, B200_EPI_SWIGLU, m->row_scales,
                                       c.swiglu_limit, m->items, m->n_items, m->max_items, c.tile_rows, stream));
@@ -452,12 +567,75 @@ b200_status b200_moe_forward(b200_moe* m, const void* d_x, int32_t n_tokens, voi
   return B200_OK;
 }
 
+// The same layer with the routed experts sharded over the ranks of `ep` (no reference counterpart: the
+// reference keeps every expert on one device and streams them from SSD, src/models/expert_stream.zig).
+// DSV4SwitchGLU is cut where its two argsorts sit (src/models/deepseek_v4.zig:747-784 sort by expert,
+// :809-819 unsort and sum over k):
+//   dispatch  all-gather of the token rows, so that every rank holds the tokens of all ranks; every rank
+//             routes all of them (the router is replicated and deterministic, so all ranks agree) and
+//             keeps the assignments that fall on its own experts.  With top-6 of 8 ranks a token is
+//             needed by most ranks anyway: the all-gather moves (W-1)/W of the rows, a selective
+//             exchange 1-(1-1/W)^k of them, and nothing has to be counted on the host first.
+//   experts   stable grouping by local expert, grouped gate/up (clipped SwiGLU x routing weight) and
+//             down matmuls on the rows that exist (the count stays on the device).
+//   combine   each rank sums, per token, the outputs of its own experts in f32; a reduce-scatter adds
+//             the ranks' shares and leaves every rank with the sums of its own tokens; the shared expert
+//             (computed on the rank's own tokens) is added last.
+// Two collectives per layer, no host synchronisation, every rank passes the same n_tokens.
+b200_status b200_moe_forward_ep(b200_moe* m, b200_ep* ep, const void* d_x, int32_t n_tokens, void* d_out, void* stream) {
+  const b200_moe_config& c = m->cfg;
+  const int world = c.ep_world;
+  if (world < 1 || !ep || b200_ep_world(ep) != world || b200_ep_rank(ep) != c.ep_rank) {
+    b200_set_error("moe: this layer was not built for expert parallelism on this communicator");
+    return B200_ERR_INVALID_ARGUMENT;
+  }
+  if (n_tokens > c.max_tokens) { b200_set_error("moe: %d tokens > max_tokens %d", n_tokens, c.max_tokens); return B200_ERR_CAPACITY; }
+  if (n_tokens <= 0) return B200_OK;
+  const int N = n_tokens * world, A = N * c.top_k;
+  cudaStream_t s = (cudaStream_t)stream;
+  b200_status st;
+#define STEP(call) do { if ((st = (call)) != B200_OK) return st; } while (0)
+  STEP(b200_ep_dispatch(ep, d_x, m->x_all, n_tokens, c.hidden, stream));
+  if (m->sh_gu) {  // shared expert on the rank's own tokens
+    STEP(b200_qmm(m->sh_gu, d_x, n_tokens, m->sh_act, B200_EPI_SWIGLU, nullptr, c.shared_swiglu_limit, B200_QMM_AUTO, stream));
+    STEP(b200_qmm(m->sh_down, m->sh_act, n_tokens, m->sh_out, B200_EPI_NONE, nullptr, 0.f, B200_QMM_AUTO, stream));
+  }
+  STEP(b200_qmm(m->gate, m->x_all, N, m->logits, B200_EPI_NONE, nullptr, 0.f, B200_QMM_AUTO, stream));
+  STEP(b200_moe_route(m->logits, 0, m->d_bias, N, c.n_experts, c.top_k, c.scoring, c.route_scale, m->indices, m->weights,
+                      m->counts, stream));
+  STEP(b200_ep_plan(m->indices, m->counts, N, c.top_k, c.n_experts, c.ep_rank, world, c.tile_rows, m->local_idx, m->offsets,
+                    m->order, m->inv_order, m->items, m->n_items, stream));
+  const int* rows_valid = m->offsets + m->n_local;  // assignments served here
+  row_scales_kernel<<<(A + 255) / 256, 256, 0, s>>>(m->order, m->weights, A, m->row_scales, rows_valid);
+  B200_LAUNCH_CHECK();
+  if (b200_qmm_grouped_takes_tokens(m->exp_gu, c.tile_rows)) {
+    STEP(b200_qmm_grouped_from_tokens(m->exp_gu, m->x_all, m->order, c.top_k, A, m->act_sorted, B200_EPI_SWIGLU, m->row_scales,
+                                      c.swiglu_limit, m->items, m->n_items, m->max_items, c.tile_rows, stream, rows_valid));
+  } else {
+    gather_sorted_kernel<<<A, 128, 0, s>>>(m->x_all, m->order, m->weights, c.top_k, c.hidden, m->x_sorted, nullptr, rows_valid);
+    B200_LAUNCH_CHECK();
+    STEP(b200_qmm_grouped(m->exp_gu, m->x_sorted, A, m->act_sorted, B200_EPI_SWIGLU, m->row_scales, c.swiglu_limit, m->items,
+                          m->n_items, m->max_items, c.tile_rows, stream));
+  }
+  STEP(b200_qmm_grouped(m->exp_down, m->act_sorted, A, m->y_sorted, B200_EPI_NONE, nullptr, 0.f, m->items, m->n_items,
+                        m->max_items, c.tile_rows, stream));
+  combine_partial_kernel<<<N, 256, 0, s>>>(m->y_sorted, m->inv_order, c.top_k, c.hidden, m->partial);
+  B200_LAUNCH_CHECK();
+  STEP(b200_ep_combine(ep, m->partial, m->reduced, n_tokens, c.hidden, stream));
+  const size_t n8 = (size_t)n_tokens * c.hidden / 8;
+  add_shared_kernel<<<(unsigned)((n8 + 255) / 256), 256, 0, s>>>(m->reduced, m->sh_out, n8, (__nv_bfloat16*)d_out);
+  B200_LAUNCH_CHECK();
+#undef STEP
+  return B200_OK;
+}
+
 // Routing results of the last forward (tests): indices [N,k] u32, weights [N,k] f32, offsets [E+1].
 b200_status b200_moe_last_routing(b200_moe* m, int32_t n_tokens, uint32_t* h_indices, float* h_weights, int32_t* h_offsets) {
   const size_t A = (size_t)n_tokens * m->cfg.top_k;
   B200_CUDA_TRY(cudaMemcpy(h_indices, m->indices, A * 4, cudaMemcpyDeviceToHost));
   B200_CUDA_TRY(cudaMemcpy(h_weights, m->weights, A * 4, cudaMemcpyDeviceToHost));
-  B200_CUDA_TRY(cudaMemcpy(h_offsets, m->offsets, sizeof(int) * (m->cfg.n_experts + 1), cudaMemcpyDeviceToHost));
+  const int n_off = (m->cfg.ep_world >= 1 ? m->n_local : m->cfg.n_experts) + 1;  // expert parallel: this rank's experts
+  B200_CUDA_TRY(cudaMemcpy(h_offsets, m->offsets, sizeof(int) * n_off, cudaMemcpyDeviceToHost));
   return B200_OK;
 }
 

@@ -1146,9 +1146,10 @@ __device__ __forceinline__ float2 mx_e4m3x2_to_f32x2(uint32_t codes) {
 __global__ void __launch_bounds__(256) mx_split_activations_kernel(const __nv_bfloat16* __restrict__ x, int k,
                                                                    unsigned char* __restrict__ hi, unsigned char* __restrict__ lo,
                                                                    float* __restrict__ unscale, const int* __restrict__ gather,
-                                                                   int gather_div) {
+                                                                   int gather_div, const int* __restrict__ rows_valid) {
   __shared__ float s_max[8];
   const int row = blockIdx.x;
+  if (rows_valid && row >= *rows_valid) return;  // capacity beyond the rows that exist: nothing to read
   const int src_row = gather ? gather[row] / gather_div : row;
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)src_row * k);
   float amax = 0.f;
@@ -1843,7 +1844,7 @@ static b200_status launch_mx(const b200_qweight* w, QmmArgs& a, int rows, cudaSt
   unsigned char* hi = g_mx_act;
   unsigned char* lo = hi + (size_t)rows * a.k;
   float* unscale = reinterpret_cast<float*>(lo + (((size_t)rows * a.k + 255) / 256) * 256);
-  mx_split_activations_kernel<<<rows, 256, 0, s>>>(a.x, a.k, hi, lo, unscale, a.x_gather, a.x_gather_div);
+  mx_split_activations_kernel<<<rows, 256, 0, s>>>(a.x, a.k, hi, lo, unscale, a.x_gather, a.x_gather_div, a.rows_valid);
   B200_LAUNCH_CHECK();
   MxActMaps amaps;
   std::memset(&amaps, 0, sizeof(amaps));
@@ -2113,7 +2114,7 @@ int b200_qmm_grouped_takes_tokens(const b200_qweight* w, int32_t tile_rows) {
 b200_status b200_qmm_grouped_from_tokens(const b200_qweight* w, const void* d_tokens, const int* d_order, int32_t top_k,
                                          int32_t rows, void* d_y, int32_t epilogue, const float* d_row_scales,
                                          float swiglu_limit, const int4* d_items, const int* d_n_items, int32_t max_items,
-                                         int32_t tile_rows, void* stream) {
+                                         int32_t tile_rows, void* stream, const int* d_rows_valid) {
   b200_status st = b200_require_device();
   if (st != B200_OK) return st;
   if (rows <= 0) return B200_OK;
@@ -2124,6 +2125,7 @@ b200_status b200_qmm_grouped_from_tokens(const b200_qweight* w, const void* d_to
   a.rows = rows; a.n = w->n; a.k = w->k; a.nt = w->nt; a.kc = w->kc; a.epilogue = epilogue; a.swiglu_limit = swiglu_limit;
   a.items = d_items; a.n_items = d_n_items; a.max_items = max_items; a.tn = tile_rows;
   a.x_gather = d_order; a.x_gather_div = top_k;
+  a.rows_valid = d_rows_valid;
   return launch_mx(w, a, rows, (cudaStream_t)stream);
 }
 

@@ -46,6 +46,7 @@ struct QmmArgs {
   const float* act_unscale;     // per activation row: factor that undoes the row's power-of-two scaling
   const int* x_gather;          // optional: activation row p is x[x_gather[p] / x_gather_div] (expert-sorted rows
   int x_gather_div;             //   taken straight from the token matrix while they are split; no sorted copy)
+  const int* rows_valid;        // optional (device): only the first *rows_valid rows exist; the rest of `rows` is capacity
   int mx_expert_rows;           // rows of the code matrix per expert (nt * 128)
   int kc128;                    // K / 128
   int did_norm;                 // host only: the finish pass also wrote norm_out
@@ -61,10 +62,11 @@ b200_status b200_qmm_grouped(const b200_qweight* w, const void* d_x, int32_t row
 int b200_qmm_grouped_takes_tokens(const b200_qweight* w, int32_t tile_rows);
 // The same matmul with the expert-sorted activation rows read from the unsorted token matrix:
 // row p = d_tokens[d_order[p] / top_k].
+// d_rows_valid (optional, device): the number of rows that exist; `rows` is then only the capacity of the buffers.
 b200_status b200_qmm_grouped_from_tokens(const b200_qweight* w, const void* d_tokens, const int* d_order, int32_t top_k,
                                          int32_t rows, void* d_y, int32_t epilogue, const float* d_row_scales,
                                          float swiglu_limit, const int4* d_items, const int* d_n_items, int32_t max_items,
-                                         int32_t tile_rows, void* stream);
+                                         int32_t tile_rows, void* stream, const int* d_rows_valid = nullptr);
 // Queues copies of the matmul error words into pinned host memory on `stream` (no synchronisation,
 // nothing cleared): h_out[0] = the word of b200_qmm and the grouped launches, h_out[1] = the word of
 // b200_qmm_static_scratch on the current device.

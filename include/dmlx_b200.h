@@ -613,6 +613,12 @@ typedef struct b200_moe_config {
   float route_scale;
   float swiglu_limit;        /* routed experts: 10 in the reference (deepseek_v4.zig:64) */
   float shared_swiglu_limit; /* shared expert (0 = unclipped) */
+  /* Expert parallelism (ep_world = 0: off, every expert is local; a group of one rank is allowed and runs
+   * the same code path).  n_experts stays the number of routed
+   * experts of the model; the expert weight handles then stack the n_experts / ep_world experts of this
+   * rank (global expert e lives on rank e / (n_experts / ep_world)), max_tokens is the most tokens ONE
+   * rank brings to a step, and the layer runs through b200_moe_forward_ep. */
+  int32_t ep_rank, ep_world;
 } b200_moe_config;
 typedef struct b200_moe b200_moe;
 b200_status b200_moe_create(const b200_moe_config* cfg, const b200_qweight* gate, const float* h_bias,
@@ -623,6 +629,61 @@ void b200_moe_destroy(b200_moe* m);
 b200_status b200_moe_forward(b200_moe* m, const void* d_x, int32_t n_tokens, void* d_out, void* stream);
 b200_status b200_moe_last_routing(b200_moe* m, int32_t n_tokens, uint32_t* h_indices, float* h_weights,
                                   int32_t* h_offsets);
+
+
+/* ---- expert parallelism ---------------------------------------------------------------------------- */
+/* No reference counterpart: the reference keeps all experts on one device and streams them from SSD
+ * (src/models/expert_stream.zig:400-613).  The routed experts are sharded over `world` ranks, one
+ * process per GPU; DSV4SwitchGLU is cut at its two argsorts (src/models/deepseek_v4.zig:747-784 sort by
+ * expert -> dispatch; :809-819 unsort and sum over k -> combine).  The communicator is NCCL, loaded at
+ * run time; rank 0 makes the 128-byte id and the host hands it to every rank by its own means. */
+enum { B200_EP_UNIQUE_ID_BYTES = 128 };
+typedef struct b200_ep b200_ep;
+b200_status b200_ep_unique_id(uint8_t* out_128_bytes);                   /* ncclGetUniqueId */
+b200_status b200_ep_create(int32_t rank, int32_t world, const uint8_t* unique_id, b200_ep** out); /* collective */
+void b200_ep_destroy(b200_ep* ep);
+int32_t b200_ep_rank(const b200_ep* ep);
+int32_t b200_ep_world(const b200_ep* ep);
+int32_t b200_ep_nccl_version(void);
+/* dispatch: every rank's n_rows token rows [n_rows, hidden] bf16 -> all ranks' rows, rank-major
+ * [world * n_rows, hidden] (an all-gather: with top-6 routing over 8 ranks nearly every rank needs
+ * nearly every token, and no per-destination count has to reach the host first).  Queued on `stream`. */
+b200_status b200_ep_dispatch(b200_ep* ep, const void* d_rows, void* d_rows_all, int32_t n_rows, int32_t hidden,
+                             void* stream);
+/* plan: the grouping of deepseek_v4.zig:747-784 restricted to this rank's experts.  d_indices [N, k] and
+ * d_counts [n_experts] come from b200_moe_route over the tokens of all ranks; outputs: offsets
+ * [E_local + 1], order (row p of the grouped matmul is assignment order[p]; offsets[E_local] rows exist),
+ * inv_order [N * k] (-1 where another rank serves the assignment), work items, d_local_idx [N * k] scratch. */
+b200_status b200_ep_plan(const uint32_t* d_indices, const int32_t* d_counts, int32_t n_tokens, int32_t k,
+                         int32_t n_experts, int32_t rank, int32_t world, int32_t tile_rows, uint32_t* d_local_idx,
+                         int32_t* d_offsets, int32_t* d_order, int32_t* d_inv_order, void* d_items,
+                         int32_t* d_n_items, void* stream);
+/* combine: d_partial_all [world * n_rows, hidden] f32 holds, for the tokens of all ranks, the sum of the
+ * outputs of THIS rank's experts; the reduce-scatter leaves in d_sum [n_rows, hidden] f32 the complete
+ * sums over k of this rank's own tokens (reduceExperts, src/moe_router.zig:139-164).  Queued on `stream`. */
+b200_status b200_ep_combine(b200_ep* ep, const float* d_partial_all, float* d_sum, int32_t n_rows, int32_t hidden,
+                            void* stream);
+/* DSV4MoE.forward (src/models/deepseek_v4.zig:1010-1056) for a layer created with ep_world > 1: dispatch,
+ * replicated routing, plan, grouped matmuls on the local experts, combine, shared expert.  Every rank
+ * calls it with the same n_tokens.  Two collectives, no host synchronisation. */
+b200_status b200_moe_forward_ep(b200_moe* m, b200_ep* ep, const void* d_x, int32_t n_tokens, void* d_out,
+                                void* stream);
+/* Host-side watchdog: waits until the work queued on `stream` so far has finished, at most timeout_ms
+ * (negative = no limit), polling ncclCommGetAsyncError; on an error or when the time is up the
+ * communicator is aborted (ncclCommAbort), the GPU comes back to the caller and B200_ERR_DEVICE_FLAGGED is
+ * returned.  After an abort the handle only accepts b200_ep_destroy. */
+b200_status b200_ep_wait(b200_ep* ep, void* stream, int32_t timeout_ms);
+b200_status b200_ep_abort(b200_ep* ep);
+/* The watchdog's loop on its own, over caller-supplied operations (each gets ctx): done() != 0 when the
+ * work has finished, async_error() != 0 when the communicator reports an error, abort() tears it down. */
+typedef struct b200_ep_watch_ops {
+  int (*done)(void* ctx);
+  int (*async_error)(void* ctx);
+  void (*abort)(void* ctx);
+  void* ctx;
+} b200_ep_watch_ops;
+enum { B200_EP_WATCH_DONE = 0, B200_EP_WATCH_ERROR = 1, B200_EP_WATCH_TIMEOUT = 2 };
+int32_t b200_ep_watch(const b200_ep_watch_ops* ops, int32_t timeout_ms, int32_t poll_us);
 
 #ifdef __cplusplus
 }

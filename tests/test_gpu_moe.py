@@ -185,3 +185,86 @@ def test_moe_layer_at_full_size_against_the_oracle_on_sampled_tokens(_restore_gr
             want = want + float(wts[tkn, j]) * expert_out(xt, gu, down, idx[tkn, j], 10.0)
         rel, cos = _close(got[tkn], want)
         assert rel <= 2e-2 and cos >= 0.9995, (int(tkn), rel, cos)
+
+
+def test_ep_plan_groups_only_the_local_experts():
+    """b200_ep_plan for every rank of a group of four, on one GPU: of the assignments of all tokens a rank
+    keeps those whose expert it holds, grouped by local expert in a stable order; the others are marked -1
+    in inv_order.  Against a stable host sort of the same subset (src/models/deepseek_v4.zig:747-784)."""
+    import ctypes as C
+
+    from dmlx_b200 import _lib
+
+    rng = np.random.default_rng(8)
+    n, e, k, world, tile = 1000, 64, 6, 4, 32
+    p = rng.random(e) ** 2
+    idx = np.stack([rng.choice(e, k, replace=False, p=p / p.sum()) for _ in range(n)]).astype(np.uint32)
+    counts = np.bincount(idx.reshape(-1), minlength=e).astype(np.int32)
+    d_idx, d_counts = torch.tensor(idx.astype(np.int64), device="cuda").to(torch.int32), torch.tensor(counts, device="cuda")
+    el, a = e // world, n * k
+    for rank in range(world):
+        local = torch.empty(a, dtype=torch.int32, device="cuda")
+        off = torch.empty(el + 1, dtype=torch.int32, device="cuda")
+        order = torch.full((a,), -7, dtype=torch.int32, device="cuda")
+        inv = torch.empty(a, dtype=torch.int32, device="cuda")
+        items = torch.empty((el + a // tile + 1, 4), dtype=torch.int32, device="cuda")
+        n_items = torch.zeros(1, dtype=torch.int32, device="cuda")
+        _lib.check(_lib.lib.b200_ep_plan(d_idx.data_ptr(), d_counts.data_ptr(), n, k, e, rank, world, tile, local.data_ptr(),
+                                         off.data_ptr(), order.data_ptr(), inv.data_ptr(), items.data_ptr(), n_items.data_ptr(),
+                                         torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        flat = idx.reshape(-1).astype(np.int64)
+        mine = np.nonzero((flat >= rank * el) & (flat < (rank + 1) * el))[0]
+        want_order = mine[np.argsort(flat[mine], kind="stable")]
+        want_off = np.concatenate([[0], np.cumsum(counts[rank * el:(rank + 1) * el])])
+        m = len(mine)
+        assert np.array_equal(off.cpu().numpy(), want_off) and want_off[-1] == m
+        assert np.array_equal(order.cpu().numpy()[:m], want_order)
+        want_inv = np.full(a, -1, np.int64)
+        want_inv[want_order] = np.arange(m)
+        assert np.array_equal(inv.cpu().numpy(), want_inv)
+        ni = int(n_items.cpu()[0])
+        covered = np.zeros(m, np.int32)
+        for ex, r0, rows, _ in items.cpu().numpy()[:ni]:
+            assert want_off[ex] <= r0 and r0 + rows <= want_off[ex + 1] and 0 < rows <= tile
+            covered[r0:r0 + rows] += 1
+        assert (covered == 1).all()
+
+
+@pytest.mark.parametrize("mode_name", ["mxfp4", "affine4"])
+def test_expert_parallel_layer_with_a_group_of_one_equals_the_plain_layer(mode_name, _restore_grouped_path):
+    """The expert-parallel code path (dispatch, replicated routing, plan, grouped matmuls on the rows that
+    exist, f32 partial sums, combine, shared expert) with a communicator of one rank, where both
+    collectives are identities: its output must equal the plain layer's on the same weights, and the
+    watchdog must see the stream finish."""
+    import torch.distributed as dist
+
+    from dmlx_b200 import device as dev
+    from dmlx_b200 import expert_parallel as ep
+
+    rng = np.random.default_rng(12)
+    n, d, e, inter, k = 90, 256, 8, 128, 2
+    x = torch.tensor(ref_math.bf16_round(rng.normal(0, 1, (n, d))), device="cuda").bfloat16()
+    wg = ref_math.bf16_round(rng.normal(0, 0.3, (e, d)))
+    bias = rng.normal(0, 0.01, e).astype(np.float32)
+    mode = dev.Q_MXFP4_G32 if mode_name == "mxfp4" else dev.Q_AFFINE4_G64
+    gate = dev.QWeight(dev.Q_BF16, _bits(wg), np.zeros(1, np.uint8), None, e, d)
+    gu = dev.QWeight.random(mode, 2 * inter, d, e, seed=1)
+    down = dev.QWeight.random(mode, d, inter, e, seed=2)
+    sgu = dev.QWeight.random(mode, 2 * inter, d, 1, seed=3)
+    sdown = dev.QWeight.random(mode, d, inter, 1, seed=4)
+    plain = dev.MoELayer(d, e, inter, k, gate, gu, down, sgu, sdown, bias=bias, route_scale=1.5, tile_rows=32, max_tokens=128)
+    want = plain.forward(x).float().cpu().numpy()
+    comm = ep.Communicator(0, 1)
+    layer = ep.ExpertParallelMoE(comm, d, e, inter, k, gate, gu, down, sgu, sdown, bias=bias, route_scale=1.5, tile_rows=32,
+                                 max_tokens=128)
+    got = layer.forward(x)
+    comm.wait(timeout_ms=5000)
+    got = got.float().cpu().numpy()
+    assert dev.qmm_error_word() == 0
+    rel, cos = _close(got, want)
+    # same kernels and the same rows; only the sum over k runs in f32 here (and is rounded once)
+    assert rel <= 1e-2 and cos >= 0.9999, (rel, cos)
+    layer.close()
+    comm.close()
+    plain.close()
