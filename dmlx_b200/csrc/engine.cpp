@@ -196,6 +196,8 @@ b200_status b200_engine_step(b200_engine* e, b200_token_output* out, uint64_t ca
       }
       b200_scheduler_set_admission_budget(e->sched, n_running == 0 ? (uint64_t)e->pool_pages : (free_now > owed ? free_now - owed : 0));
     }
+    e->prefill.resize(active);
+    e->decode.resize(active);
     uint64_t need = 0;
     np = nd = 0;
     st = b200_scheduler_schedule(e->sched, e->prefill.data(), &np, e->decode.data(), &nd, active, &need);

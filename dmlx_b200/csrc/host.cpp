@@ -13,8 +13,34 @@
 
 #include "common.h"
 
+#include <execinfo.h>
+#include <signal.h>
+#include <unistd.h>
+
 namespace {
 thread_local std::string g_last_error;
+
+// Debugging aid: with DMLX_B200_BACKTRACE=1 in the environment a fatal signal inside the process prints the
+// native call stack (module + offset per frame, resolvable with addr2line) before the default action.
+void fatal_signal(int sig) {
+  void* frames[64];
+  const int n = backtrace(frames, 64);
+  const char msg[] = "dmlx_b200: fatal signal, native stack:\n";
+  if (write(2, msg, sizeof(msg) - 1) < 0) {}
+  backtrace_symbols_fd(frames, n, 2);
+  signal(sig, SIG_DFL);
+  raise(sig);
+}
+struct BacktraceInstaller {
+  BacktraceInstaller() {
+    const char* e = getenv("DMLX_B200_BACKTRACE");
+    if (e && *e == '1') {
+      signal(SIGSEGV, fatal_signal);
+      signal(SIGBUS, fatal_signal);
+      signal(SIGABRT, fatal_signal);
+    }
+  }
+} g_backtrace_installer;
 }
 long long g_b200_launch_counter = 0;
 extern "C" int64_t b200_launch_count(void) { return (int64_t)g_b200_launch_counter; }
