@@ -1112,6 +1112,255 @@ __global__ void __launch_bounds__(kGemvThreads, NT8 >= 4 ? 1 : 2) qmm_mma_kernel
   if (!ok) atomicExch(a.err, B200_ERR_DEVICE_FLAGGED);
 }
 
+// ---- small-batch kernel, integer variant (affine int4) --------------------------------------------
+// The kernel above is bound by the integer pipe: turning a 32-bit word of eight 4-bit codes into four
+// bf16x2 MMA operands costs a shift and a logic operation per pair.  An 8-bit integer MMA takes the
+// codes almost as they lie: `w & 0x0F0F0F0F` is four operand bytes, `(w >> 4) & 0x0F0F0F0F` the other
+// four — three operations per word instead of seven, and m16n8k32 covers a 32-column plane per
+// instruction.  The activations of the CTA's K range are quantised once, while the slab is staged, to
+// 16-bit fixed point per token: x = sigma * (128 * hi + lo) with hi in [-127, 127] and lo in [-64, 64],
+// both int8 (sigma = amax / (127 * 128) over the CTA's K range).  Two integer MMAs per plane (hi, lo)
+// accumulate exactly in int32; one chunk is one quantisation group, so per chunk and output
+//     y += s * sigma * (128 * acc_hi + acc_lo) + b * sum_x,
+// with sum_x the group sum of the quantised activations (an integer times sigma).  The error of the
+// fixed-point activations is 2^-14 of the row's largest magnitude, well inside bf16's own rounding.
+// Byte j of a weight word holds columns (j<2 ? 4j : 4j-7) [low nibble] and that + 2 [high nibble] of the
+// word's eight columns, i.e. low nibbles are columns 0,4,1,5 and high nibbles 2,6,3,7: the activation
+// slab stores each group of eight columns in the order 0,4,1,5,2,6,3,7, so that a lane's operand is one
+// 8-byte load.
+__device__ __forceinline__ void mma_s8(int (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1, bool zero) {
+  if (zero) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+                 : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "r"(0));
+  } else {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+  }
+}
+
+// Row stride of the int8 slabs: 32 bytes past a multiple of 128, so that the four token rows a half-warp's
+// 8-byte loads touch (8 bytes x 4 lanes per row) fall into four disjoint groups of banks.
+__host__ __device__ constexpr int slab8_stride(int chunks) { return (chunks * kChunkK + 127) / 128 * 128 + 32; }
+
+template <int NT8>
+__global__ void __launch_bounds__(kGemvThreads, NT8 >= 4 ? 1 : 2) qmm_mma8_kernel(QmmArgs a) {
+  extern __shared__ __align__(128) unsigned char gsm[];
+  const int stages = a.stages;
+  constexpr int kSlotBytes = 2 * kRawStride;
+  constexpr int MODE = B200_Q_AFFINE4_G64;
+  constexpr int BB = block_bytes(MODE);
+  uint64_t* raw_full = reinterpret_cast<uint64_t*>(gsm + (size_t)stages * kSlotBytes);
+  uint64_t* raw_free = raw_full + stages;
+  constexpr int TILE = NT8 * 8;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  const int split = blockIdx.x % a.splits, grp = blockIdx.x / a.splits, groups = gridDim.x / a.splits;
+  const int tt = blockIdx.y, t0 = tt * TILE;
+  const int kc0 = split * a.chunks_per_split, kc1 = min(kc0 + a.chunks_per_split, a.kc), n_chunks = kc1 - kc0;
+  const int n_pairs = (a.nt + 1) / 2;
+  const int n_items = grp < n_pairs ? (n_pairs - grp + groups - 1) / groups : 0;
+  // [hi slab][lo slab] int8, [sum_x int32: chunk][token], [sigma f32: token], [amax scratch f32: warp][token]
+  const int slab_stride = slab8_stride(a.chunks_per_split);
+  unsigned char* slab_hi = reinterpret_cast<unsigned char*>(raw_free + stages);
+  unsigned char* slab_lo = slab_hi + (size_t)TILE * slab_stride;
+  int* sum_x = reinterpret_cast<int*>(slab_lo + (size_t)TILE * slab_stride);
+  float* sigma = reinterpret_cast<float*>(sum_x + (size_t)TILE * a.chunks_per_split);
+  float* amax_part = sigma + TILE;
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) {
+      ptx::mbar_init(&raw_full[s], 1);
+      ptx::mbar_init(&raw_free[s], kGemvConsumers);
+    }
+    ptx::mbar_fence_init();
+  }
+  __syncthreads();
+  bool ok = true;
+  if (warp == kGemvConsumers) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t phase = 1;
+      for (int item = 0; item < n_items && ok; ++item) {
+        const int nt0 = 2 * (grp + item * groups);
+        const int tiles = min(2, a.nt - nt0);
+        const unsigned char* src = a.blocks + ((size_t)nt0 * a.kc + kc0) * BB;
+        for (int i = 0; i < n_chunks; ++i) {
+          ok = ptx::mbar_wait(&raw_free[s], phase);
+          if (!ok) break;
+          ptx::mbar_expect_tx(&raw_full[s], tiles * BB);
+          for (int u = 0; u < tiles; ++u)
+            ptx::bulk_g2s(gsm + (size_t)s * kSlotBytes + u * kRawStride, src + ((size_t)u * a.kc + i) * BB, BB, &raw_full[s]);
+          if (++s == stages) { s = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else {
+    // ---- stage the activations: per-token scale over this CTA's K range, then 16-bit fixed point ----
+    const int vec_per_row = n_chunks * (kChunkK / 8);  // groups of 8 columns (16 bytes of bf16)
+    {
+      // warp w scans rows w, w+8, ... ; lanes stride over the row's 8-column groups
+      for (int row = warp; row < TILE; row += kGemvConsumers) {
+        float m = 0.f;
+        if (t0 + row < a.rows) {
+          const uint4* xr = reinterpret_cast<const uint4*>(a.x + (size_t)(t0 + row) * a.k + (size_t)kc0 * kChunkK);
+          for (int v = lane; v < vec_per_row; v += 32) {
+            const uint4 q = xr[v];
+            const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) m = fmaxf(m, fmaxf(fabsf(ptx::bf16_lo(w4[j])), fabsf(ptx::bf16_hi(w4[j]))));
+          }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) sigma[row] = (m > 0.f && m < 3e38f) ? m * (1.0f / (127.0f * 128.0f)) : 1.0f;
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumers * 32) : "memory");
+    for (int idx = tid; idx < TILE * vec_per_row; idx += kGemvConsumers * 32) {
+      const int row = idx / vec_per_row, v = idx - row * vec_per_row;
+      uint2 hi8 = make_uint2(0u, 0u), lo8 = make_uint2(0u, 0u);
+      if (t0 + row < a.rows) {
+        const uint4 q = *reinterpret_cast<const uint4*>(a.x + (size_t)(t0 + row) * a.k + (size_t)kc0 * kChunkK + v * 8);
+        const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+        const float inv = 1.0f / (sigma[row] * 128.0f);  // 1 / (step of the hi part)
+        int h[8], l[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float xv = (j & 1) ? ptx::bf16_hi(w4[j >> 1]) : ptx::bf16_lo(w4[j >> 1]);
+          const float hf = rintf(xv * inv);
+          h[j] = (int)hf;
+          l[j] = (int)rintf((xv * inv - hf) * 128.0f);
+        }
+        // byte order 0,4,1,5 | 2,6,3,7 (see above)
+        auto pack4 = [](int b0, int b1, int b2, int b3) {
+          return (uint32_t)(b0 & 0xFF) | ((uint32_t)(b1 & 0xFF) << 8) | ((uint32_t)(b2 & 0xFF) << 16) | ((uint32_t)(b3 & 0xFF) << 24);
+        };
+        hi8 = make_uint2(pack4(h[0], h[4], h[1], h[5]), pack4(h[2], h[6], h[3], h[7]));
+        lo8 = make_uint2(pack4(l[0], l[4], l[1], l[5]), pack4(l[2], l[6], l[3], l[7]));
+      }
+      *reinterpret_cast<uint2*>(slab_hi + (size_t)row * slab_stride + v * 8) = hi8;
+      *reinterpret_cast<uint2*>(slab_lo + (size_t)row * slab_stride + v * 8) = lo8;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumers * 32) : "memory");
+    for (int idx = tid; idx < TILE * n_chunks; idx += kGemvConsumers * 32) {
+      const int c = idx / TILE, row = idx - c * TILE;
+      const uint32_t* ph = reinterpret_cast<const uint32_t*>(slab_hi + (size_t)row * slab_stride + c * kChunkK);
+      const uint32_t* pl = reinterpret_cast<const uint32_t*>(slab_lo + (size_t)row * slab_stride + c * kChunkK);
+      int sh = 0, sl = 0;
+#pragma unroll
+      for (int v = 0; v < kChunkK / 4; ++v) {
+        sh = __dp4a((int)ph[v], 0x01010101, sh);
+        sl = __dp4a((int)pl[v], 0x01010101, sl);
+      }
+      sum_x[idx] = sh * 128 + sl;
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumers * 32) : "memory");
+
+    const int rA = warp * 16 + g;
+    const unsigned char* xh_lane = slab_hi + (size_t)g * slab_stride + 8 * t;  // token g of tile j: + j*8*slab_stride
+    const unsigned char* xl_lane = slab_lo + (size_t)g * slab_stride + 8 * t;
+    float sg[NT8][2];  // sigma of the lane's two tokens of every token tile
+#pragma unroll
+    for (int j = 0; j < NT8; ++j) { sg[j][0] = sigma[j * 8 + 2 * t]; sg[j][1] = sigma[j * 8 + 2 * t + 1]; }
+    const uint32_t full0 = ptx::smem_u32(raw_full), free0 = ptx::smem_u32(raw_free);
+    const uint32_t lane_ofs = (uint32_t)(rA * 16 + 4 * t);
+    uint32_t slot = 0, phase = 0;
+    for (int item = 0; item < n_items && ok; ++item) {
+      const int nt0 = 2 * (grp + item * groups);
+      const bool two = nt0 + 1 < a.nt;
+      float y[2][NT8][4];
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int j = 0; j < NT8; ++j) { y[u][j][0] = y[u][j][1] = y[u][j][2] = y[u][j][3] = 0.f; }
+      int xoff = 0;
+      const int* psx = sum_x + 2 * t;
+      for (int i = 0; i < n_chunks; ++i) {
+        // activations of the chunk first: they do not depend on the weights
+        uint2 xh[NT8][2], xl[NT8][2];
+        float2 sx[NT8];
+#pragma unroll
+        for (int j = 0; j < NT8; ++j) {
+#pragma unroll
+          for (int plane = 0; plane < 2; ++plane) {
+            xh[j][plane] = *reinterpret_cast<const uint2*>(xh_lane + (size_t)(j * 8) * slab_stride + xoff + plane * 32);
+            xl[j][plane] = *reinterpret_cast<const uint2*>(xl_lane + (size_t)(j * 8) * slab_stride + xoff + plane * 32);
+          }
+          const int2 si = *reinterpret_cast<const int2*>(psx + j * 8);
+          sx[j] = make_float2((float)si.x * sg[j][0], (float)si.y * sg[j][1]);
+        }
+        ok = ptx::mbar_wait_addr(full0 + 8 * slot, phase);
+        if (!ok) break;
+        const unsigned char* slot_base = gsm + slot * kSlotBytes;
+        uint32_t wa[2][2], wb[2][2];
+        float sA[2], bA[2], sB[2], bB[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (u == 1 && !two) break;
+          const unsigned char* blk = slot_base + u * kRawStride;
+#pragma unroll
+          for (int plane = 0; plane < 2; ++plane) {
+            wa[u][plane] = *reinterpret_cast<const uint32_t*>(blk + lane_ofs + plane * kPlaneBytes);
+            wb[u][plane] = *reinterpret_cast<const uint32_t*>(blk + lane_ofs + plane * kPlaneBytes + 8 * 16);
+          }
+          const uint16_t* sc = reinterpret_cast<const uint16_t*>(blk + 2 * kPlaneBytes) + rA;
+          sA[u] = __uint_as_float((uint32_t)sc[0] << 16); bA[u] = __uint_as_float((uint32_t)sc[kTileN] << 16);
+          sB[u] = __uint_as_float((uint32_t)sc[8] << 16); bB[u] = __uint_as_float((uint32_t)sc[kTileN + 8] << 16);
+        }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_addr(free0 + 8 * slot);  // everything this warp needs is in registers
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (u == 1 && !two) break;
+          int acc_h[NT8][4], acc_l[NT8][4];
+#pragma unroll
+          for (int plane = 0; plane < 2; ++plane) {
+            uint32_t af[4];
+            af[0] = wa[u][plane] & 0x0F0F0F0Fu;
+            af[1] = wb[u][plane] & 0x0F0F0F0Fu;
+            af[2] = (wa[u][plane] >> 4) & 0x0F0F0F0Fu;
+            af[3] = (wb[u][plane] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+            for (int j = 0; j < NT8; ++j) {
+              mma_s8(acc_h[j], af, xh[j][plane].x, xh[j][plane].y, plane == 0);
+              mma_s8(acc_l[j], af, xl[j][plane].x, xl[j][plane].y, plane == 0);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < NT8; ++j) {
+            const float f0 = (float)(acc_h[j][0] * 128 + acc_l[j][0]), f1 = (float)(acc_h[j][1] * 128 + acc_l[j][1]);
+            const float f2 = (float)(acc_h[j][2] * 128 + acc_l[j][2]), f3 = (float)(acc_h[j][3] * 128 + acc_l[j][3]);
+            y[u][j][0] = fmaf(sA[u] * sg[j][0], f0, fmaf(bA[u], sx[j].x, y[u][j][0]));
+            y[u][j][1] = fmaf(sA[u] * sg[j][1], f1, fmaf(bA[u], sx[j].y, y[u][j][1]));
+            y[u][j][2] = fmaf(sB[u] * sg[j][0], f2, fmaf(bB[u], sx[j].x, y[u][j][2]));
+            y[u][j][3] = fmaf(sB[u] * sg[j][1], f3, fmaf(bB[u], sx[j].y, y[u][j][3]));
+          }
+        }
+        xoff += kChunkK;
+        psx += TILE;
+        if (++slot == (uint32_t)stages) { slot = 0; phase ^= 1u; }
+      }
+      if (ok) {
+        const int rB = rA + 8;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          if (u == 1 && !two) break;
+          float* wsp = a.ws + (((size_t)((nt0 + u) * gridDim.y + tt) * a.splits + split) * a.tn) * kTileN;
+#pragma unroll
+          for (int j = 0; j < NT8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int tl = j * 8 + 2 * t + (e & 1), row = (e & 2) ? rB : rA;
+              if (t0 + tl < a.rows) wsp[(size_t)tl * kTileN + row] = y[u][j][e];
+            }
+          }
+        }
+      }
+    }
+  }
+  if (!ok) atomicExch(a.err, B200_ERR_DEVICE_FLAGGED);
+}
+
 // ---- MXFP4 on the block-scaled tensor-core path ---------------------------------------------------
 // tcgen05.mma kind::mxf8f6f4 multiplies E2M1 codes by E8M0 block scales in hardware, so MXFP4 weights
 // need no dequantisation at all: TMA unpacks the packed codes into the 8-bit containers the MMA reads
@@ -1975,6 +2224,56 @@ static b200_status launch_mma_nt(QmmArgs& a, int rows, cudaStream_t s) {
   return launch_finish(a, splits, s);
 }
 
+template <int NT8>
+static b200_status launch_mma8_nt(QmmArgs& a, int rows, cudaStream_t s) {
+  const int tile = NT8 * 8;
+  a.tn = tile;
+  const int tts = (rows + tile - 1) / tile;
+  b200_status st = ensure_state(0);
+  if (st != B200_OK) return st;
+  a.stages = kGemvRawStages;
+  const size_t base_smem = (size_t)a.stages * 2 * kRawStride + 2 * a.stages * sizeof(uint64_t);
+  // two int8 slabs, the group sums, the per-token scales and a little scratch
+  auto slab_bytes = [&](int cps) {
+    return 2 * (size_t)tile * slab8_stride(cps) + (size_t)tile * cps * sizeof(int) + (size_t)tile * 2 * sizeof(float) + 64;
+  };
+  const int slots = std::max(1, g_sms * 2 / tts);
+  int best = 0, best_groups = 1;
+  long long best_cost = 0;
+  for (int sp = 1; sp <= std::min(a.kc, slots); ++sp) {
+    const int cps = (a.kc + sp - 1) / sp;
+    if ((a.kc + cps - 1) / cps != sp || slab_bytes(cps) > 48 * 1024) continue;
+    if (best && cps < 2) break;
+    const int pairs = (a.nt + 1) / 2;
+    const int groups = std::max(1, std::min(pairs, slots / sp));
+    const long long cost = (long long)((pairs + groups - 1) / groups) * (2 * cps + 1) + 8;
+    if (!best || cost < best_cost) { best = sp; best_cost = cost; best_groups = groups; }
+  }
+  if (!best) { b200_set_error("qmm: no K split fits the activation slab"); return B200_ERR_CAPACITY; }
+  const int splits = best;
+  a.splits = splits;
+  a.chunks_per_split = (a.kc + splits - 1) / splits;
+  st = ensure_state((size_t)splits * (size_t)tts * tile * a.nt * kTileN * sizeof(float));
+  if (st != B200_OK) return st;
+  a.ws = g_ws; a.err = g_err;
+  a.x_slab = 1;
+  const size_t smem = base_smem + slab_bytes(a.chunks_per_split);
+  static bool configured = false;
+  if (!configured) {
+    B200_CUDA_TRY(cudaFuncSetAttribute(qmm_mma8_kernel<NT8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(base_smem + 48 * 1024)));
+    configured = true;
+  }
+  qmm_mma8_kernel<NT8><<<dim3(best_groups * splits, tts), kGemvThreads, smem, s>>>(a);
+  B200_LAUNCH_CHECK();
+  return launch_finish(a, splits, s);
+}
+
+static b200_status launch_mma8(QmmArgs& a, int rows, cudaStream_t s) {
+  if (rows <= 8) return launch_mma8_nt<1>(a, rows, s);
+  if (rows <= 16) return launch_mma8_nt<2>(a, rows, s);
+  return launch_mma8_nt<4>(a, rows, s);
+}
+
 template <int MODE>
 static b200_status launch_mma(QmmArgs& a, int rows, cudaStream_t s) {
   if (rows <= 8) return launch_mma_nt<MODE, 1>(a, rows, s);
@@ -2037,7 +2336,10 @@ static b200_status qmm_entry(const b200_qweight* w, const void* d_x, int32_t row
       path = B200_QMM_MXFP4_BLOCK_SCALED;
   }
   if (path == B200_QMM_AUTO) {
-    if (rows <= 16 && w->mode != B200_Q_BF16) path = B200_QMM_MMA;
+    // up to 8 rows of affine int4: the integer small-batch kernel (lm_head 59 vs 80 us, gate/up 20 vs 23 us at
+    // one row); 9..16 rows only on the largest matrices, where its longer activation staging is amortised
+    if (rows <= 16 && w->mode == B200_Q_AFFINE4_G64 && (rows <= 8 || w->n >= 32768)) path = B200_QMM_MMA_I8;
+    else if (rows <= 16 && w->mode != B200_Q_BF16) path = B200_QMM_MMA;
     else if (rows > 128) {
       const int tn = std::min(256, ((rows + 15) / 16) * 16), pair_ctas = ((w->nt + 1) / 2) * ((rows + tn - 1) / tn);
       if (ensure_state(0) != B200_OK) return B200_ERR_CUDA;
@@ -2059,6 +2361,10 @@ static b200_status qmm_entry(const b200_qweight* w, const void* d_x, int32_t row
   cudaStream_t s = (cudaStream_t)stream;
   auto dispatch = [&]() -> b200_status {
     if (path == B200_QMM_MXFP4_BLOCK_SCALED) return launch_mx(w, a, rows, s);
+    if (path == B200_QMM_MMA_I8) {
+      if (w->mode != B200_Q_AFFINE4_G64) { b200_set_error("qmm: the integer small-batch kernel serves affine int4 weights"); return B200_ERR_UNSUPPORTED; }
+      return launch_mma8(a, rows, s);
+    }
     if (path == B200_QMM_MMA)
       return w->mode == B200_Q_AFFINE4_G64 ? launch_mma<B200_Q_AFFINE4_G64>(a, rows, s) : launch_mma<B200_Q_MXFP4_G32>(a, rows, s);
     if (path == B200_QMM_SIMT) {

@@ -16,7 +16,7 @@ from ._lib import KvConfig, PackDesc, lib
 KV_BF16, KV_FP8_E4M3 = 0, 1
 Q_AFFINE4_G64, Q_MXFP4_G32 = 0, 1
 EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
-QMM_AUTO, QMM_SIMT, QMM_TCGEN05, QMM_MMA, QMM_TCGEN05_X2, QMM_TCGEN05_TMEM_A, QMM_MXFP4_BLOCK_SCALED = 0, 1, 2, 3, 4, 5, 6
+QMM_AUTO, QMM_SIMT, QMM_TCGEN05, QMM_MMA, QMM_TCGEN05_X2, QMM_TCGEN05_TMEM_A, QMM_MXFP4_BLOCK_SCALED, QMM_MMA_I8 = 0, 1, 2, 3, 4, 5, 6, 7
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:

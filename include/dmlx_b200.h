@@ -385,7 +385,7 @@ b200_status b200_qweight_export(const b200_qweight* w, int32_t expert, void* h_p
 void b200_qweight_destroy(b200_qweight* w);
 enum { B200_EPI_NONE = 0, B200_EPI_RESIDUAL = 1, B200_EPI_SWIGLU = 2 };
 enum { B200_QMM_AUTO = 0, B200_QMM_SIMT = 1, B200_QMM_TCGEN05 = 2, B200_QMM_MMA = 3, B200_QMM_TCGEN05_X2 = 4,
-       B200_QMM_TCGEN05_TMEM_A = 5, B200_QMM_MXFP4_BLOCK_SCALED = 6 };
+       B200_QMM_TCGEN05_TMEM_A = 5, B200_QMM_MXFP4_BLOCK_SCALED = 6, B200_QMM_MMA_I8 = 7 };
 /* Tuning hook (no reference counterpart): 1 sends the grouped (MoE) matmuls through the kernel that
  * keeps dequantised weights in tensor memory. */
 void b200_set_qmm_grouped_tmem_a(int32_t on);

@@ -109,7 +109,7 @@ def _mxfp4_weight(rng, n, k):
     return packed, scales
 
 
-@pytest.mark.parametrize("path", [1, 2, 3, 4, 5])  # CUDA-core GEMV, tcgen05, register-dequant mma.sync, tcgen05 with tile pairs, tcgen05 with weights in tensor memory
+@pytest.mark.parametrize("path", [1, 2, 3, 4, 5, 7])  # CUDA-core GEMV, tcgen05, register-dequant mma.sync, tcgen05 with tile pairs, tcgen05 with weights in tensor memory, int8 mma.sync on the raw codes
 @pytest.mark.parametrize("rows,n,k", [(1, 256, 512), (3, 384, 1408), (16, 768, 512), (33, 128, 4096), (130, 512, 1024),
                                       (256, 384, 1024), (300, 256, 4096)])
 def test_qmm_affine4(path, rows, n, k):
@@ -117,6 +117,8 @@ def test_qmm_affine4(path, rows, n, k):
 
     if path == 1 and rows > 16:
         pytest.skip("the GEMV kernel is the small-batch path")
+    if path == 7 and rows > 64:
+        pytest.skip("the integer kernel is a small-batch path")
     rng = np.random.default_rng(rows * 1000 + n + k)
     packed, s, b, sb, bb = _affine_weight(rng, n, k)
     w = dev.QWeight(dev.Q_AFFINE4_G64, packed, sb, bb, n, k)
@@ -146,7 +148,7 @@ def test_qmm_mxfp4(path, rows, n, k):
     assert rel <= 2e-2 and cos >= 0.9995, (rel, cos)
 
 
-@pytest.mark.parametrize("path", [1, 2, 3, 4, 5])
+@pytest.mark.parametrize("path", [1, 2, 3, 4, 5, 7])
 def test_qmm_epilogues(path):
     """Residual add (src/models/llama.zig:466,477) and SwiGLU over interleaved gate/up rows
     (src/models/llama.zig:396-415; clipped form src/models/deepseek_v4.zig:947-966)."""
@@ -381,4 +383,33 @@ def test_qmm_mxfp4_block_scaled_outlier_inside_a_row():
         rel, cos = _close(got[r], want[r])                      # the whole row (the outlier dominates it)
         assert rel <= 2e-2 and cos >= 0.9995, (r, rel, cos)
         rel, cos = _close(got[r, : n // 2], want[r, : n // 2])  # outputs the outlier does not reach
+        assert rel <= 2e-2 and cos >= 0.9995, (r, "small elements", rel, cos)
+
+
+def test_qmm_integer_small_batch_kernel_keeps_small_elements_beside_an_outlier():
+    """The integer small-batch kernel carries a token's activations as 16-bit fixed point relative to the
+    token's largest magnitude (within the K range of a CTA).  One element 2^12 above the rest must not
+    wipe out the others: outputs whose weights are zero in the outlier's column are judged on their own."""
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(41)
+    rows, n, k = 8, 256, 2048
+    wf = rng.normal(0, 0.02, (n, k)).astype(np.float32)
+    col = 777
+    g0 = (col // 64) * 64
+    wf[: n // 2, g0:g0 + 64] = 0.0   # the whole quantisation group: scale 1 (degenerate), bias 0, codes 0 -> exact zeros
+    packed, s, b, = ref_math.quantize_affine4(wf)
+    bits = lambda a: (ref_math.bf16_round(a).view(np.uint32) >> 16).astype(np.uint16)
+    w = dev.QWeight(dev.Q_AFFINE4_G64, packed, bits(s), bits(b), n, k)
+    wd = ref_math.dequantize_affine4(packed, s, b)
+    assert np.all(wd[: n // 2, col] == 0)
+    x = ref_math.bf16_round(rng.normal(0, 1, (rows, k)))
+    x[::2, col] = 4096.0
+    want = ref_math.qmm(x, wd)
+    got = dev.qmm(w, _bf(x), path=dev.QMM_MMA_I8).float().cpu().numpy()
+    assert dev.qmm_error_word() == 0
+    for r in range(rows):
+        rel, cos = _close(got[r], want[r])
+        assert rel <= 2e-2 and cos >= 0.9995, (r, rel, cos)
+        rel, cos = _close(got[r, : n // 2], want[r, : n // 2])
         assert rel <= 2e-2 and cos >= 0.9995, (r, "small elements", rel, cos)
