@@ -1118,12 +1118,13 @@ __global__ void __launch_bounds__(kGemvThreads, NT8 >= 4 ? 1 : 2) qmm_mma_kernel
 // codes almost as they lie: `w & 0x0F0F0F0F` is four operand bytes, `(w >> 4) & 0x0F0F0F0F` the other
 // four — three operations per word instead of seven, and m16n8k32 covers a 32-column plane per
 // instruction.  The activations of the CTA's K range are quantised once, while the slab is staged, to
-// 16-bit fixed point per token: x = sigma * (128 * hi + lo) with hi in [-127, 127] and lo in [-64, 64],
-// both int8 (sigma = amax / (127 * 128) over the CTA's K range).  Two integer MMAs per plane (hi, lo)
-// accumulate exactly in int32; one chunk is one quantisation group, so per chunk and output
+// 16-bit fixed point with one scale per token and 64-column group (the weights' quantisation group):
+// x = sigma * (128 * hi + lo) with hi in [-127, 127] and lo in [-64, 64], both int8, sigma =
+// (largest magnitude of the group) / (127 * 128).  Two integer MMAs per plane (hi, lo) accumulate exactly
+// in int32; one chunk is one group, so per chunk and output
 //     y += s * sigma * (128 * acc_hi + acc_lo) + b * sum_x,
-// with sum_x the group sum of the quantised activations (an integer times sigma).  The error of the
-// fixed-point activations is 2^-14 of the row's largest magnitude, well inside bf16's own rounding.
+// with sum_x the group sum of the quantised activations.  The fixed-point error is 2^-14 of the group's
+// largest magnitude: an outlier costs precision only among the 63 columns that share its group.
 // Byte j of a weight word holds columns (j<2 ? 4j : 4j-7) [low nibble] and that + 2 [high nibble] of the
 // word's eight columns, i.e. low nibbles are columns 0,4,1,5 and high nibbles 2,6,3,7: the activation
 // slab stores each group of eight columns in the order 0,4,1,5,2,6,3,7, so that a lane's operand is one
@@ -1160,13 +1161,12 @@ __global__ void __launch_bounds__(kGemvThreads, NT8 >= 4 ? 1 : 2) qmm_mma8_kerne
   const int kc0 = split * a.chunks_per_split, kc1 = min(kc0 + a.chunks_per_split, a.kc), n_chunks = kc1 - kc0;
   const int n_pairs = (a.nt + 1) / 2;
   const int n_items = grp < n_pairs ? (n_pairs - grp + groups - 1) / groups : 0;
-  // [hi slab][lo slab] int8, [sum_x int32: chunk][token], [sigma f32: token], [amax scratch f32: warp][token]
+  // [hi slab][lo slab] int8, then per chunk and token the group's scale and its sum of activations (f32)
   const int slab_stride = slab8_stride(a.chunks_per_split);
   unsigned char* slab_hi = reinterpret_cast<unsigned char*>(raw_free + stages);
   unsigned char* slab_lo = slab_hi + (size_t)TILE * slab_stride;
-  int* sum_x = reinterpret_cast<int*>(slab_lo + (size_t)TILE * slab_stride);
-  float* sigma = reinterpret_cast<float*>(sum_x + (size_t)TILE * a.chunks_per_split);
-  float* amax_part = sigma + TILE;
+  float* sum_x = reinterpret_cast<float*>(slab_lo + (size_t)TILE * slab_stride);
+  float* sigma = sum_x + (size_t)TILE * a.chunks_per_split;
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(&raw_full[s], 1);
@@ -1195,73 +1195,62 @@ __global__ void __launch_bounds__(kGemvThreads, NT8 >= 4 ? 1 : 2) qmm_mma8_kerne
       }
     }
   } else {
-    // ---- stage the activations: per-token scale over this CTA's K range, then 16-bit fixed point ----
-    const int vec_per_row = n_chunks * (kChunkK / 8);  // groups of 8 columns (16 bytes of bf16)
-    {
-      // warp w scans rows w, w+8, ... ; lanes stride over the row's 8-column groups
-      for (int row = warp; row < TILE; row += kGemvConsumers) {
-        float m = 0.f;
-        if (t0 + row < a.rows) {
-          const uint4* xr = reinterpret_cast<const uint4*>(a.x + (size_t)(t0 + row) * a.k + (size_t)kc0 * kChunkK);
-          for (int v = lane; v < vec_per_row; v += 32) {
-            const uint4 q = xr[v];
-            const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
+    // ---- stage the activations: 16-bit fixed point with one scale per token and 64-column group ----
+    // One thread per 8 columns; the 8 threads of a group (consecutive lanes) agree on the group's scale,
+    // quantise, and add up the group's integer sum.  A single pass, one barrier at the end.
+    const int vec_per_row = n_chunks * (kChunkK / 8);
+    const int total = TILE * vec_per_row;
+    for (int base = 0; base < total; base += kGemvConsumers * 32) {
+      const int idx = base + tid;
+      const bool valid = idx < total;
+      const int row = valid ? idx / vec_per_row : 0, v = valid ? idx - row * vec_per_row : 0;
+      float xv[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) m = fmaxf(m, fmaxf(fabsf(ptx::bf16_lo(w4[j])), fabsf(ptx::bf16_hi(w4[j]))));
-          }
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-        if (lane == 0) sigma[row] = (m > 0.f && m < 3e38f) ? m * (1.0f / (127.0f * 128.0f)) : 1.0f;
-      }
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumers * 32) : "memory");
-    for (int idx = tid; idx < TILE * vec_per_row; idx += kGemvConsumers * 32) {
-      const int row = idx / vec_per_row, v = idx - row * vec_per_row;
-      uint2 hi8 = make_uint2(0u, 0u), lo8 = make_uint2(0u, 0u);
-      if (t0 + row < a.rows) {
+      for (int j = 0; j < 8; ++j) xv[j] = 0.f;
+      if (valid && t0 + row < a.rows) {
         const uint4 q = *reinterpret_cast<const uint4*>(a.x + (size_t)(t0 + row) * a.k + (size_t)kc0 * kChunkK + v * 8);
         const uint32_t w4[4] = {q.x, q.y, q.z, q.w};
-        const float inv = 1.0f / (sigma[row] * 128.0f);  // 1 / (step of the hi part)
-        int h[8], l[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const float xv = (j & 1) ? ptx::bf16_hi(w4[j >> 1]) : ptx::bf16_lo(w4[j >> 1]);
-          const float hf = rintf(xv * inv);
-          h[j] = (int)hf;
-          l[j] = (int)rintf((xv * inv - hf) * 128.0f);
-        }
+        for (int j = 0; j < 4; ++j) { xv[2 * j] = ptx::bf16_lo(w4[j]); xv[2 * j + 1] = ptx::bf16_hi(w4[j]); }
+      }
+      float m = 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(xv[j]));
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      const float sig = (m > 0.f && m < 3e38f) ? m * (1.0f / (127.0f * 128.0f)) : 1.0f;
+      const float inv = 1.0f / (sig * 128.0f);  // 1 / (step of the hi part)
+      int h[8], l[8], part = 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float hf = rintf(xv[j] * inv);
+        h[j] = (int)hf;
+        l[j] = (int)rintf((xv[j] * inv - hf) * 128.0f);
+        part += h[j] * 128 + l[j];
+      }
+#pragma unroll
+      for (int o = 4; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+      if (valid) {
         // byte order 0,4,1,5 | 2,6,3,7 (see above)
         auto pack4 = [](int b0, int b1, int b2, int b3) {
           return (uint32_t)(b0 & 0xFF) | ((uint32_t)(b1 & 0xFF) << 8) | ((uint32_t)(b2 & 0xFF) << 16) | ((uint32_t)(b3 & 0xFF) << 24);
         };
-        hi8 = make_uint2(pack4(h[0], h[4], h[1], h[5]), pack4(h[2], h[6], h[3], h[7]));
-        lo8 = make_uint2(pack4(l[0], l[4], l[1], l[5]), pack4(l[2], l[6], l[3], l[7]));
+        *reinterpret_cast<uint2*>(slab_hi + (size_t)row * slab_stride + v * 8) =
+            make_uint2(pack4(h[0], h[4], h[1], h[5]), pack4(h[2], h[6], h[3], h[7]));
+        *reinterpret_cast<uint2*>(slab_lo + (size_t)row * slab_stride + v * 8) =
+            make_uint2(pack4(l[0], l[4], l[1], l[5]), pack4(l[2], l[6], l[3], l[7]));
+        if ((v & 7) == 0) {
+          const int c = v >> 3;
+          sigma[c * TILE + row] = sig;
+          sum_x[c * TILE + row] = (float)part * sig;
+        }
       }
-      *reinterpret_cast<uint2*>(slab_hi + (size_t)row * slab_stride + v * 8) = hi8;
-      *reinterpret_cast<uint2*>(slab_lo + (size_t)row * slab_stride + v * 8) = lo8;
-    }
-    asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumers * 32) : "memory");
-    for (int idx = tid; idx < TILE * n_chunks; idx += kGemvConsumers * 32) {
-      const int c = idx / TILE, row = idx - c * TILE;
-      const uint32_t* ph = reinterpret_cast<const uint32_t*>(slab_hi + (size_t)row * slab_stride + c * kChunkK);
-      const uint32_t* pl = reinterpret_cast<const uint32_t*>(slab_lo + (size_t)row * slab_stride + c * kChunkK);
-      int sh = 0, sl = 0;
-#pragma unroll
-      for (int v = 0; v < kChunkK / 4; ++v) {
-        sh = __dp4a((int)ph[v], 0x01010101, sh);
-        sl = __dp4a((int)pl[v], 0x01010101, sl);
-      }
-      sum_x[idx] = sh * 128 + sl;
     }
     asm volatile("bar.sync 1, %0;" ::"n"(kGemvConsumers * 32) : "memory");
 
     const int rA = warp * 16 + g;
     const unsigned char* xh_lane = slab_hi + (size_t)g * slab_stride + 8 * t;  // token g of tile j: + j*8*slab_stride
     const unsigned char* xl_lane = slab_lo + (size_t)g * slab_stride + 8 * t;
-    float sg[NT8][2];  // sigma of the lane's two tokens of every token tile
-#pragma unroll
-    for (int j = 0; j < NT8; ++j) { sg[j][0] = sigma[j * 8 + 2 * t]; sg[j][1] = sigma[j * 8 + 2 * t + 1]; }
     const uint32_t full0 = ptx::smem_u32(raw_full), free0 = ptx::smem_u32(raw_free);
     const uint32_t lane_ofs = (uint32_t)(rA * 16 + 4 * t);
     uint32_t slot = 0, phase = 0;
@@ -1274,11 +1263,12 @@ __global__ void __launch_bounds__(kGemvThreads, NT8 >= 4 ? 1 : 2) qmm_mma8_kerne
 #pragma unroll
         for (int j = 0; j < NT8; ++j) { y[u][j][0] = y[u][j][1] = y[u][j][2] = y[u][j][3] = 0.f; }
       int xoff = 0;
-      const int* psx = sum_x + 2 * t;
+      const float* psx = sum_x + 2 * t;
+      const float* psg = sigma + 2 * t;
       for (int i = 0; i < n_chunks; ++i) {
         // activations of the chunk first: they do not depend on the weights
         uint2 xh[NT8][2], xl[NT8][2];
-        float2 sx[NT8];
+        float2 sx[NT8], sg[NT8];
 #pragma unroll
         for (int j = 0; j < NT8; ++j) {
 #pragma unroll
@@ -1286,8 +1276,8 @@ __global__ void __launch_bounds__(kGemvThreads, NT8 >= 4 ? 1 : 2) qmm_mma8_kerne
             xh[j][plane] = *reinterpret_cast<const uint2*>(xh_lane + (size_t)(j * 8) * slab_stride + xoff + plane * 32);
             xl[j][plane] = *reinterpret_cast<const uint2*>(xl_lane + (size_t)(j * 8) * slab_stride + xoff + plane * 32);
           }
-          const int2 si = *reinterpret_cast<const int2*>(psx + j * 8);
-          sx[j] = make_float2((float)si.x * sg[j][0], (float)si.y * sg[j][1]);
+          sx[j] = *reinterpret_cast<const float2*>(psx + j * 8);
+          sg[j] = *reinterpret_cast<const float2*>(psg + j * 8);
         }
         ok = ptx::mbar_wait_addr(full0 + 8 * slot, phase);
         if (!ok) break;
@@ -1330,14 +1320,15 @@ __global__ void __launch_bounds__(kGemvThreads, NT8 >= 4 ? 1 : 2) qmm_mma8_kerne
           for (int j = 0; j < NT8; ++j) {
             const float f0 = (float)(acc_h[j][0] * 128 + acc_l[j][0]), f1 = (float)(acc_h[j][1] * 128 + acc_l[j][1]);
             const float f2 = (float)(acc_h[j][2] * 128 + acc_l[j][2]), f3 = (float)(acc_h[j][3] * 128 + acc_l[j][3]);
-            y[u][j][0] = fmaf(sA[u] * sg[j][0], f0, fmaf(bA[u], sx[j].x, y[u][j][0]));
-            y[u][j][1] = fmaf(sA[u] * sg[j][1], f1, fmaf(bA[u], sx[j].y, y[u][j][1]));
-            y[u][j][2] = fmaf(sB[u] * sg[j][0], f2, fmaf(bB[u], sx[j].x, y[u][j][2]));
-            y[u][j][3] = fmaf(sB[u] * sg[j][1], f3, fmaf(bB[u], sx[j].y, y[u][j][3]));
+            y[u][j][0] = fmaf(sA[u] * sg[j].x, f0, fmaf(bA[u], sx[j].x, y[u][j][0]));
+            y[u][j][1] = fmaf(sA[u] * sg[j].y, f1, fmaf(bA[u], sx[j].y, y[u][j][1]));
+            y[u][j][2] = fmaf(sB[u] * sg[j].x, f2, fmaf(bB[u], sx[j].x, y[u][j][2]));
+            y[u][j][3] = fmaf(sB[u] * sg[j].y, f3, fmaf(bB[u], sx[j].y, y[u][j][3]));
           }
         }
         xoff += kChunkK;
         psx += TILE;
+        psg += TILE;
         if (++slot == (uint32_t)stages) { slot = 0; phase ^= 1u; }
       }
       if (ok) {
@@ -2235,7 +2226,7 @@ static b200_status launch_mma8_nt(QmmArgs& a, int rows, cudaStream_t s) {
   const size_t base_smem = (size_t)a.stages * 2 * kRawStride + 2 * a.stages * sizeof(uint64_t);
   // two int8 slabs, the group sums, the per-token scales and a little scratch
   auto slab_bytes = [&](int cps) {
-    return 2 * (size_t)tile * slab8_stride(cps) + (size_t)tile * cps * sizeof(int) + (size_t)tile * 2 * sizeof(float) + 64;
+    return 2 * (size_t)tile * slab8_stride(cps) + 2 * (size_t)tile * cps * sizeof(float) + 64;
   };
   const int slots = std::max(1, g_sms * 2 / tts);
   int best = 0, best_groups = 1;
