@@ -343,7 +343,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(&loaded[s], 1);
-      ptx::mbar_init(&a_ready[s], 2 * kTileN);
+      ptx::mbar_init(&a_ready[s], 2 * kTileN / 32);  // one arrival per dequantising warp
       ptx::mbar_init(&mma_done[s], 1);
     }
     ptx::mbar_init(accum_ready, 1);
@@ -419,7 +419,8 @@ __global__ void __launch_bounds__(kTcThreads, 1) qmm_tc_kernel(const __grid_cons
         }
       }
       ptx::fence_proxy_async_smem();
-      ptx::mbar_arrive(&a_ready[s]);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&a_ready[s]);
     }
     // ---- accumulator -> f32 partial tile in scratch ----
     if (ok && warp < 4) ok = ptx::mbar_wait(accum_ready, 0);
@@ -569,7 +570,7 @@ __global__ void __launch_bounds__(kTcaThreads, 2) qmm_tca_kernel(const __grid_co
       ptx::mbar_init(&slot_free[s], 1);
     }
     for (int q = 0; q < Q; ++q) {
-      ptx::mbar_init(&a_ready[q], 2 * kTileN);
+      ptx::mbar_init(&a_ready[q], 2 * kTileN / 32);  // one arrival per dequantising warp (256 single arrivals cost ~500 cycles)
       ptx::mbar_init(&a_free[q], 1);
     }
     ptx::mbar_init(accum_ready, 1);
@@ -624,8 +625,10 @@ __global__ void __launch_bounds__(kTcaThreads, 2) qmm_tca_kernel(const __grid_co
     // ---- dequantise: thread (r, plane) owns one 32-column half of weight row r = tensor-memory lane r ----
     const int r = tid & (kTileN - 1), plane = tid >> 7;
     const uint32_t my_taddr = a_col0 + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(plane * 16);
-    int s = 0, q = 0;
+    int s = 0, q = 0, pending_q = -1;
     uint32_t ph = 0, qh = 0;
+    // The store of chunk i into tensor memory is left in flight while chunk i+1 is loaded and dequantised;
+    // it is waited for, and its slot announced, just before the next store is issued.
     for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1, qh ^= (q + 1 == Q),
              q = (q + 1 == Q) ? 0 : q + 1) {
       ok = ptx::mbar_wait(&full[s], ph);
@@ -641,13 +644,24 @@ __global__ void __launch_bounds__(kTcaThreads, 2) qmm_tca_kernel(const __grid_co
         const uint4 d = dequant_word<MODE>(words[w], s2, b2);
         v[4 * w] = d.x; v[4 * w + 1] = d.y; v[4 * w + 2] = d.z; v[4 * w + 3] = d.w;
       }
+      if (pending_q >= 0) {
+        ptx::tmem_st_wait();
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&a_ready[pending_q]);
+        pending_q = -1;
+      }
       ok = ptx::mbar_wait(&a_free[q], qh ^ 1u);
       if (!ok) break;
       ptx::tc_fence_after_sync();
       ptx::tmem_st16(my_taddr + (uint32_t)(q * 32), v);
+      pending_q = q;
+    }
+    if (pending_q >= 0) {
       ptx::tmem_st_wait();
       ptx::tc_fence_before_sync();
-      ptx::mbar_arrive(&a_ready[q]);
+      __syncwarp();
+      if (ok && lane == 0) ptx::mbar_arrive(&a_ready[pending_q]);
     }
     // ---- accumulator -> f32 partial tile in scratch ----
     if (ok && warp < 4) ok = ptx::mbar_wait(accum_ready, 0);
@@ -714,7 +728,7 @@ __global__ void __launch_bounds__(kTc2Threads, 1) qmm_tc2_kernel(const __grid_co
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
       ptx::mbar_init(&loaded[s], 1);
-      ptx::mbar_init(&a_ready[s], kTc2DequantThreads);
+      ptx::mbar_init(&a_ready[s], kTc2DequantThreads / 32);  // one arrival per dequantising warp
       ptx::mbar_init(&mma_done[s], 1);
     }
     ptx::mbar_init(accum_ready, 1);
@@ -786,7 +800,8 @@ __global__ void __launch_bounds__(kTc2Threads, 1) qmm_tc2_kernel(const __grid_co
         }
       }
       ptx::fence_proxy_async_smem();
-      ptx::mbar_arrive(&a_ready[s]);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&a_ready[s]);
     }
     // ---- accumulators: warp w reads lanes 32*(w%4); warps 4g..4g+3 take tile g/2, column half g%2 ----
     if (ok) ok = ptx::mbar_wait(accum_ready, 0);
