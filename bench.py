@@ -1093,6 +1093,7 @@ def main():
     ap.add_argument("--shape", default="all", help="qmm_* only: qkv | o | gate_up | down | lm_head | all")
     ap.add_argument("--path", type=int, default=0, help="qmm_* only: kernel path (0 = automatic)")
     ap.add_argument("--seqs", type=int, default=64, help="sequences per GPU (64 = the configuration; fewer for profiling)")
+    ap.add_argument("--mx-persistent", type=int, default=-1, help="block-scaled MXFP4 path: 1 persistent CTAs over work items, 0 one CTA per item (default: library choice)")
     ap.add_argument("--no-arrivals", action="store_true", help="llama8b_int4 only: skip the arrival-process scenarios")
     ap.add_argument("--no-ep", action="store_true", help="llama8b_int4 on several GPUs only: skip the expert-parallel MoE measurement")
     ap.add_argument("--arrival-scenarios", default="both", help="poisson_20rps | saturation | both")
@@ -1116,6 +1117,9 @@ def main():
 
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the product has no CPU path)")
+    if args.mx_persistent >= 0:
+        from dmlx_b200 import _lib
+        _lib.lib.b200_set_qmm_mx_persistent(args.mx_persistent)
     if args.workload == "llama8b_int4_arrivals":
         run_arrivals(args, rank, world, local)
         return

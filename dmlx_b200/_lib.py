@@ -201,6 +201,7 @@ _sig("b200_llama_launch_count", C.c_int64, vp)
 _sig("b200_launch_count", C.c_int64)
 _sig("b200_set_qmm_grouped_tmem_a", None, i32)
 _sig("b200_set_qmm_grouped_block_scaled", None, i32)
+_sig("b200_set_qmm_mx_persistent", None, i32)
 _sig("b200_llama_profile_enable", None, vp, i32)
 _sig("b200_llama_enable_graphs", None, vp, i32)
 _sig("b200_llama_profile_collect", i32, vp, P(C.c_double), P(C.c_int64))

@@ -1669,6 +1669,245 @@ __global__ void __launch_bounds__(kMxThreads, 1)
   if (warp == 5) ptx::tmem_dealloc(tmem_base, kCols);
 }
 
+// ---- block-scaled MXFP4, persistent form -----------------------------------------------------------
+// The kernel above runs one work item per CTA: a CTA's stage ring drains while its epilogue runs, the
+// next CTA starts with an empty ring, and short items (a MoE expert with a few dozen rows, a weight
+// stream for a handful of tokens) are mostly ramp-up and tail.  Here a CTA stays on its SM and walks a
+// list of work items; the loader warp runs ahead into the next item's weights while the epilogue
+// warps drain the accumulators of the current one, so the ring never empties between items.
+//   work item   = (tile pair, token tile or expert item, K range); item w of CTA b is b + i * gridDim.x,
+//                 tile pair fastest, so that neighbouring CTAs share an item's activation rows in L2.
+//   K splits    (dense launches with few tile pairs): partial sums go to the split-K scratch and the
+//                 finish kernel, as for the other kernels.
+//   epilogue    16 tokens at a time: tensor memory -> registers -> a dedicated 16 KiB f32 staging
+//                 tile -> 16-byte stores; the accumulators are handed back to the MMA warp as soon as
+//                 the last slab has been read, before it is stored.
+constexpr int kMxpStageTokens = 16;
+
+__global__ void __launch_bounds__(kMxThreads, 1)
+    qmm_mxp_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ MxActMaps amaps, QmmArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int tn = a.tn, P = a.stages;
+  constexpr int kATile = kTileN * kMxK;
+  const int stage_stride = 2 * kATile + 2 * tn * 128 + 1024;
+  auto a_tile = [&](int s, int tile) { return smem + (size_t)s * stage_stride + tile * kATile; };
+  auto b_tile = [&](int s, int half) { return smem + (size_t)s * stage_stride + 2 * kATile + half * tn * 128; };
+  auto sf_tile = [&](int s, int tile) { return smem + (size_t)s * stage_stride + 2 * kATile + 2 * tn * 128 + tile * 512; };
+  float* stage_f = reinterpret_cast<float*>(smem + (size_t)P * stage_stride);  // [2 tiles][16 tokens][128 rows]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)P * stage_stride + 2 * kMxpStageTokens * kTileN * sizeof(float));
+  uint64_t* full = bars;
+  uint64_t* slot_free = bars + P;
+  uint64_t* sf_ready = bars + 2 * P;     // the constant activation scales are in tensor memory (once)
+  uint64_t* accum_ready = bars + 2 * P + 1;
+  uint64_t* accum_free = bars + 2 * P + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P + 3);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_pairs = (a.nt + 1) / 2;
+  const int splits = a.items ? 1 : a.splits;
+  const int tts = a.items ? 0 : (a.rows + tn - 1) / tn;
+  const int n_work = a.items ? n_pairs * min(*a.n_items, a.max_items) : n_pairs * tts * splits;
+  constexpr uint32_t kCols = 512;
+
+  struct Work { int nt0, n_tiles, t0, rows_here, expert, kc0, n_chunks, tn_eff, map_idx, split, tt; };
+  auto decode = [&](int w) {
+    Work k;
+    const int pair = w % n_pairs, rest = w / n_pairs;
+    k.nt0 = 2 * pair;
+    k.n_tiles = min(2, a.nt - k.nt0);
+    k.expert = 0; k.split = 0; k.tt = 0;
+    if (a.items) {
+      const int4 it = a.items[rest];
+      k.expert = it.x; k.t0 = it.y; k.rows_here = it.z;
+      k.kc0 = 0; k.n_chunks = a.kc128;
+    } else {
+      k.tt = rest % tts;
+      k.split = rest / tts;
+      k.t0 = k.tt * tn;
+      k.rows_here = min(tn, a.rows - k.t0);
+      k.kc0 = k.split * a.chunks_per_split;
+      k.n_chunks = min(a.chunks_per_split, a.kc128 - k.kc0);
+    }
+    k.tn_eff = min(tn, ((k.rows_here + 31) / 32) * 32);
+    if (k.tn_eff < 16) k.tn_eff = 16;
+    k.map_idx = (k.tn_eff + 31) / 32 - 1;
+    return k;
+  };
+
+  if (tid == 0) {
+    for (int s = 0; s < P; ++s) {
+      ptx::mbar_init(&full[s], 1);
+      ptx::mbar_init(&slot_free[s], 1);
+    }
+    ptx::mbar_init(sf_ready, 4 * 32);
+    ptx::mbar_init(accum_ready, 1);
+    ptx::mbar_init(accum_free, 4);
+    ptx::mbar_fence_init();
+  }
+  if (warp == 5) {
+    ptx::tmem_alloc(tmem_slot, kCols);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t sfa_col0 = tmem_base + 256u, sfb_hi = tmem_base + 256u + 8u * (uint32_t)P, sfb_lo = sfb_hi + 4u;
+  bool ok = true;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0;
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x) {
+        const Work k = decode(w);
+        const int wrow0 = k.expert * a.mx_expert_rows + k.nt0 * kTileN;
+        const unsigned char* sf_src = a.mx_sf + ((size_t)(k.expert * a.nt + k.nt0) * a.kc128) * 512;
+        for (int i = 0; i < k.n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1) {
+          ok = ptx::mbar_wait(&slot_free[s], ph ^ 1u);
+          if (!ok) break;
+          const int kc = k.kc0 + i;
+          ptx::mbar_expect_tx(&full[s], k.n_tiles * (kATile / 2 + 512) + 2 * k.tn_eff * 128);
+          for (int tile = 0; tile < k.n_tiles; ++tile) {
+            ptx::tma_load_2d(a_tile(s, tile), &wmap, kc * kMxK, wrow0 + tile * kTileN, &full[s]);
+            ptx::bulk_g2s(sf_tile(s, tile), sf_src + ((size_t)tile * a.kc128 + kc) * 512, 512, &full[s]);
+          }
+          ptx::tma_load_2d(b_tile(s, 0), &amaps.hi[k.map_idx], kc * kMxK, a.x_row0 + k.t0, &full[s]);
+          ptx::tma_load_2d(b_tile(s, 1), &amaps.lo[k.map_idx], kc * kMxK, a.x_row0 + k.t0, &full[s]);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      int s = 0;
+      uint32_t ph = 0, n_done = 0;
+      ok = ptx::mbar_wait(sf_ready, 0);
+      for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++n_done) {
+        const Work k = decode(w);
+        // the epilogue of the previous item must have read the accumulators out before they are overwritten
+        if (n_done > 0) ok = ptx::mbar_wait(accum_free, (n_done - 1) & 1u);
+        if (!ok) break;
+        ptx::tc_fence_after_sync();
+        for (int i = 0; i < k.n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1) {
+          ok = ptx::mbar_wait(&full[s], ph);
+          if (!ok) break;
+          ptx::tc_fence_after_sync();
+          const uint64_t dh = ptx::umma_desc_k_sw128(ptx::smem_u32(b_tile(s, 0)));
+          const uint64_t dl = ptx::umma_desc_k_sw128(ptx::smem_u32(b_tile(s, 1)));
+          for (int tile = 0; tile < k.n_tiles; ++tile) {
+            const uint64_t da = ptx::umma_desc_k_sw128(ptx::smem_u32(a_tile(s, tile)));
+            const uint32_t sfa = sfa_col0 + (uint32_t)((s * 2 + tile) * 4);
+            ptx::tmem_cp_32x128b_warpx4(sfa, ptx::umma_desc_k_noswizzle_16B(ptx::smem_u32(sf_tile(s, tile))));
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4) {
+              const uint32_t idesc = ptx::umma_idesc_mx_e2m1_e4m3(kTileN, k.tn_eff, k4);
+              ptx::umma_mxf8f6f4(tmem_base + tile * 128, da + 2 * k4, dh + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u, sfa, sfb_hi);
+              ptx::umma_mxf8f6f4(tmem_base + tile * 128, da + 2 * k4, dl + 2 * k4, idesc, 1u, sfa, sfb_lo);
+            }
+          }
+          ptx::umma_commit(&slot_free[s]);
+        }
+        if (ok) ptx::umma_commit(accum_ready);
+      }
+    }
+  } else {
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+    ptx::tmem_st4(sfb_hi + lane_base, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);  // 2^0
+    ptx::tmem_st4(sfb_lo + lane_base, 0x7B7B7B7Bu, 0x7B7B7B7Bu, 0x7B7B7B7Bu, 0x7B7B7B7Bu);  // 2^-4
+    ptx::tmem_st_wait();
+    ptx::tc_fence_before_sync();
+    ptx::mbar_arrive(sf_ready);
+    const bool swiglu = a.epilogue == B200_EPI_SWIGLU;
+    const int out_per_tile = swiglu ? kTileN / 2 : kTileN, chunks = out_per_tile / 8;
+    const int n_out = swiglu ? a.n / 2 : a.n;
+    const float L = a.swiglu_limit;
+    uint32_t n_done = 0;
+    for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++n_done) {
+      const Work k = decode(w);
+      if (ok) ok = ptx::mbar_wait(accum_ready, n_done & 1u);
+      const bool all_ok = __syncthreads_and_epi(ok);
+      if (!all_ok) { ok = false; break; }
+      ptx::tc_fence_after_sync();
+      const bool partial = splits > 1;
+      for (int c0 = 0; c0 < k.rows_here; c0 += kMxpStageTokens) {
+        const bool last_slab = c0 + kMxpStageTokens >= k.rows_here;
+        const float us_mine = (lane < kMxpStageTokens && c0 + lane < k.rows_here) ? a.act_unscale[k.t0 + c0 + lane] : 0.f;
+        for (int tile = 0; tile < k.n_tiles; ++tile) {
+          uint32_t v[16];
+          ptx::tmem_ld16(tmem_base + lane_base + (uint32_t)(tile * 128 + c0), v);
+          ptx::tmem_ld_wait();
+          if (partial) {
+            // [weight tile][token tile][split][tn][128] f32, summed by the finish kernel
+            float* wsp = a.ws + (((size_t)((k.nt0 + tile) * tts + k.tt) * splits + k.split) * tn) * kTileN + warp * 32 + lane;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float us = __shfl_sync(0xffffffffu, us_mine, j);
+              if (c0 + j < k.rows_here) wsp[(size_t)(c0 + j) * kTileN] = __uint_as_float(v[j]) * us;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float us = __shfl_sync(0xffffffffu, us_mine, j);
+              stage_f[((size_t)tile * kMxpStageTokens + j) * kTileN + warp * 32 + lane] = __uint_as_float(v[j]) * us;
+            }
+          }
+        }
+        if (last_slab) {  // everything this item holds in tensor memory has been read
+          ptx::tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(accum_free);
+        }
+        if (partial) continue;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int slab_rows = min(kMxpStageTokens, k.rows_here - c0);
+        for (int tile = 0; tile < k.n_tiles; ++tile) {
+          for (int idx = tid; idx < slab_rows * chunks; idx += 128) {
+            const int tok = idx / chunks, ch = idx - tok * chunks;
+            const int token = k.t0 + c0 + tok, col = (k.nt0 + tile) * out_per_tile + ch * 8;
+            if (col >= n_out) continue;
+            const float* src = stage_f + ((size_t)tile * kMxpStageTokens + tok) * kTileN + ch * (swiglu ? 16 : 8);
+            const float rs = a.row_scale(token);
+            float o[8];
+            if (swiglu) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float4 f = reinterpret_cast<const float4*>(src)[q];  // gate, up, gate, up
+                float g0 = f.x, u0 = f.y, g1 = f.z, u1 = f.w;
+                if (L > 0.f) { g0 = fminf(g0, L); u0 = fminf(fmaxf(u0, -L), L); g1 = fminf(g1, L); u1 = fminf(fmaxf(u1, -L), L); }
+                o[2 * q] = g0 / (1.0f + __expf(-g0)) * u0 * rs;
+                o[2 * q + 1] = g1 / (1.0f + __expf(-g1)) * u1 * rs;
+              }
+            } else {
+              const float4 f0 = reinterpret_cast<const float4*>(src)[0], f1 = reinterpret_cast<const float4*>(src)[1];
+              o[0] = f0.x; o[1] = f0.y; o[2] = f0.z; o[3] = f0.w; o[4] = f1.x; o[5] = f1.y; o[6] = f1.z; o[7] = f1.w;
+              if (a.epilogue == B200_EPI_RESIDUAL) {
+                const uint4 r = *reinterpret_cast<const uint4*>(a.residual + (size_t)token * n_out + col);
+                const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+                for (int q = 0; q < 4; ++q) { o[2 * q] += ptx::bf16_lo(rw[q]); o[2 * q + 1] += ptx::bf16_hi(rw[q]); }
+              }
+#pragma unroll
+              for (int q = 0; q < 8; ++q) o[q] *= rs;
+            }
+            uint4 out;
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(o[0], o[1]), p1 = __floats2bfloat162_rn(o[2], o[3]);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(o[4], o[5]), p3 = __floats2bfloat162_rn(o[6], o[7]);
+            out.x = *reinterpret_cast<uint32_t*>(&p0); out.y = *reinterpret_cast<uint32_t*>(&p1);
+            out.z = *reinterpret_cast<uint32_t*>(&p2); out.w = *reinterpret_cast<uint32_t*>(&p3);
+            *reinterpret_cast<uint4*>(a.y + (size_t)token * n_out + col) = out;
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the staging tile is free for the next slab
+      }
+    }
+  }
+  if (!ok) atomicExch(a.err, B200_ERR_DEVICE_FLAGGED);
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) ptx::tmem_dealloc(tmem_base, kCols);
+}
+
 // ---- host-side state -------------------------------------------------------------------------------
 // One calling thread and one device per process use the matmul entry points (the library as a whole
 // binds to the first device it is used on, see b200_require_device).  The split-K scratch and the
@@ -2077,6 +2316,11 @@ static b200_status prepare_mx(b200_qweight* w) {
   return st;
 }
 
+int b200_qmm_mx_persistent = 1;
+extern "C" void b200_set_qmm_mx_persistent(int32_t on) { b200_qmm_mx_persistent = on; }
+
+static b200_status launch_finish(QmmArgs& a, int splits, cudaStream_t s);
+
 static b200_status launch_mx(const b200_qweight* w, QmmArgs& a, int rows, cudaStream_t s) {
   b200_status st = prepare_mx(const_cast<b200_qweight*>(w));  // the handle caches its second layout
   if (st != B200_OK) return st;
@@ -2116,23 +2360,54 @@ static b200_status launch_mx(const b200_qweight* w, QmmArgs& a, int rows, cudaSt
     int dev = 0, optin = 0;
     B200_CUDA_TRY(cudaGetDevice(&dev));
     B200_CUDA_TRY(cudaDeviceGetAttribute(&optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
-    cudaFuncAttributes fa;
+    cudaFuncAttributes fa, fb;
     B200_CUDA_TRY(cudaFuncGetAttributes(&fa, qmm_mx_kernel));
-    const int budget = optin - (int)fa.sharedSizeBytes;
+    B200_CUDA_TRY(cudaFuncGetAttributes(&fb, qmm_mxp_kernel));
+    const int budget = optin - (int)std::max(fa.sharedSizeBytes, fb.sharedSizeBytes);
     B200_CUDA_TRY(cudaFuncSetAttribute(qmm_mx_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, budget));
+    B200_CUDA_TRY(cudaFuncSetAttribute(qmm_mxp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, budget));
     smem_budget = budget;
   }
-  const int stage = 2 * kTileN * kMxK + 2 * tn * 128 + 1024, fixed = 1024 + 8 * (3 * 4 + 1) + 16;
-  a.stages = std::max(2, std::min(4, (std::min(smem_budget, 220 * 1024) - fixed) / stage));
-  a.stages = std::min(a.stages, std::max(2, a.k / kMxK));
-  const size_t smem = (size_t)a.stages * stage + fixed;
-  if ((int)smem > smem_budget) { b200_set_error("block-scaled path: %zu bytes of shared memory needed, %d available", smem, smem_budget); return B200_ERR_CAPACITY; }
   a.err = g_err;
   a.mx_sf = w->d_mx_sf;
   a.act_unscale = unscale;
   a.mx_expert_rows = w->nt * kTileN;
   a.kc128 = a.k / kMxK;
   a.x_row0 = 0;
+  const int stage = 2 * kTileN * kMxK + 2 * tn * 128 + 1024;
+  if (b200_qmm_mx_persistent) {
+    // persistent form: one CTA per SM walks the work items; dense launches with few tile pairs split K
+    const int fixed = 1024 + 2 * kMxpStageTokens * kTileN * (int)sizeof(float) + 8 * (2 * 8 + 4) + 16;
+    a.stages = std::max(2, std::min(6, (std::min(smem_budget, 224 * 1024) - fixed) / stage));
+    const size_t smem = (size_t)a.stages * stage + fixed;
+    if ((int)smem > smem_budget) { b200_set_error("block-scaled path: %zu bytes of shared memory needed, %d available", smem, smem_budget); return B200_ERR_CAPACITY; }
+    const int pairs = (a.nt + 1) / 2;
+    int splits = 1;
+    if (!a.items) {
+      // enough work items to give every SM a few chunks of K at a time; each split keeps >= 4 chunks of 128
+      const int base = pairs * tts;
+      while (base * splits < 2 * g_sms && a.kc128 / (splits * 2) >= 4 && splits < 16) splits *= 2;
+    }
+    a.splits = splits;
+    a.chunks_per_split = (a.kc128 + splits - 1) / splits;
+    const int real_splits = (a.kc128 + a.chunks_per_split - 1) / a.chunks_per_split;
+    a.splits = real_splits;
+    if (real_splits > 1) {
+      st = ensure_state((size_t)real_splits * (size_t)tts * tn * a.nt * kTileN * sizeof(float));
+      if (st != B200_OK) return st;
+      a.ws = g_ws;
+    }
+    const long long n_work = a.items ? (long long)pairs * a.max_items : (long long)pairs * tts * real_splits;
+    const int grid = (int)std::max<long long>(1, std::min<long long>(g_sms, n_work));
+    qmm_mxp_kernel<<<grid, kMxThreads, smem, s>>>(*reinterpret_cast<const CUtensorMap*>(w->mx_map), amaps, a);
+    B200_LAUNCH_CHECK();
+    return real_splits > 1 ? launch_finish(a, real_splits, s) : B200_OK;
+  }
+  const int fixed = 1024 + 8 * (3 * 4 + 1) + 16;
+  a.stages = std::max(2, std::min(4, (std::min(smem_budget, 220 * 1024) - fixed) / stage));
+  a.stages = std::min(a.stages, std::max(2, a.k / kMxK));
+  const size_t smem = (size_t)a.stages * stage + fixed;
+  if ((int)smem > smem_budget) { b200_set_error("block-scaled path: %zu bytes of shared memory needed, %d available", smem, smem_budget); return B200_ERR_CAPACITY; }
   qmm_mx_kernel<<<dim3((a.nt + 1) / 2, 1, a.items ? a.max_items : tts), kMxThreads, smem, s>>>(
       *reinterpret_cast<const CUtensorMap*>(w->mx_map), amaps, a);
   B200_LAUNCH_CHECK();
@@ -2339,6 +2614,11 @@ static b200_status qmm_entry(const b200_qweight* w, const void* d_x, int32_t row
     // 1.07 vs 1.62 ms at 4096 rows of a 28672 x 4096 matrix; below that the dequantising kernels win.
     if (w->mode == B200_Q_MXFP4_G32 && rows >= 512 && w->k % kMxK == 0 && w->n % 16 == 0 &&
         ((w->nt + 1) / 2) * ((rows + 127) / 128) >= 96)
+      path = B200_QMM_MXFP4_BLOCK_SCALED;
+    // 16..128 rows of a very wide matrix (lm_head): the persistent block-scaled kernel streams the weights
+    // without any conversion work (110 vs 124 us at 16 rows, 125 vs 162 us at 64 rows of 128256 x 4096)
+    if (w->mode == B200_Q_MXFP4_G32 && rows >= 16 && rows <= 128 && w->n >= 65536 && w->k % kMxK == 0 && w->n % 16 == 0 &&
+        b200_qmm_mx_persistent)
       path = B200_QMM_MXFP4_BLOCK_SCALED;
   }
   if (path == B200_QMM_AUTO) {

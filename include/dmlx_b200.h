@@ -395,6 +395,9 @@ void b200_set_qmm_grouped_tmem_a(int32_t on);
  * with path B200_QMM_MXFP4_BLOCK_SCALED.  The weight handle builds a second copy of itself (plain
  * row-major codes + scale atoms) on first use. */
 void b200_set_qmm_grouped_block_scaled(int32_t on);
+/* Tuning hook: 1 (default) runs the block-scaled MXFP4 path as persistent CTAs walking a list of work items
+ * (tile pair x token tile or expert item x K range), 0 as one CTA per work item. */
+void b200_set_qmm_mx_persistent(int32_t on);
 /* epilogue NONE: y = xW^T.  RESIDUAL: y = residual + xW^T.  SWIGLU: W holds gate and up rows
  * interleaved (row 2i = gate_i, 2i+1 = up_i); y[T, N/2] = silu(min(g,L)) * clip(u,+-L) with
  * L = swiglu_limit (0 = unclipped)  (src/models/llama.zig:396-415; deepseek_v4.zig:947-966). */
