@@ -148,6 +148,7 @@ _sig("b200_kv_rollback", i32, vp, i32, i32)
 _sig("b200_kv_filter", i32, vp, P(i32), i32)
 _sig("b200_kv_reserve", i32, vp, vp, i32, vp)
 _sig("b200_kv_append", i32, vp, i32, vp, vp, i32, vp)
+_sig("b200_kv_rope_append", i32, vp, i32, vp, vp, vp, vp, vp, i32, i32, f32, vp)
 _sig("b200_kv_seq_len", i32, vp, i32, P(i32))
 _sig("b200_kv_current_len", i32, vp, P(i32))
 _sig("b200_kv_block_table", i32, vp, i32, P(i32), i32, P(i32))

@@ -724,6 +724,15 @@ b200_status b200_kv_append_strided(b200_kv* kv, int32_t layer, const void* d_k_r
   return B200_OK;
 }
 
+// The same on contiguous q [T, n_q_heads, D] and k/v [T, n_kv_heads, D] rows (the exported form).
+extern "C" b200_status b200_kv_rope_append(b200_kv* kv, int32_t layer, void* d_q, void* d_k_rows, const void* d_v_rows,
+                                           const int32_t* d_positions, const int32_t* d_row_seq, int32_t total_rows,
+                                           int32_t n_q_heads, float theta, void* stream) {
+  const int q_stride = n_q_heads * kv->cfg.head_dim, kv_stride = kv->cfg.n_kv_heads * kv->cfg.head_dim;
+  return b200_kv_rope_append_strided(kv, layer, d_q, d_k_rows, d_v_rows, q_stride, kv_stride, kv_stride, d_positions, d_row_seq,
+                                     total_rows, n_q_heads, theta, stream);
+}
+
 // RoPE + append for a bf16 pool in one launch (model step); other pools take the two-kernel route.
 b200_status b200_kv_rope_append_strided(b200_kv* kv, int32_t layer, void* d_q, const void* d_k_rows, const void* d_v_rows,
                                         int32_t q_stride, int32_t k_stride, int32_t v_stride, const int32_t* d_positions,

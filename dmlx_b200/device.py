@@ -128,6 +128,12 @@ class PagedKVCache:
     def reserve(self, d_desc: torch.Tensor):
         _lib.check(lib.b200_kv_reserve(self._h, _ptr(d_desc), d_desc.shape[0], _stream()))
 
+    def rope_append(self, layer: int, q: torch.Tensor, k_rows: torch.Tensor, v_rows: torch.Tensor, positions: torch.Tensor,
+                    row_seq: torch.Tensor, theta: float = 10000.0):
+        """b200_kv_rope_append: rotate q and k in place, then append k and v to the pages reserved for this step."""
+        _lib.check(lib.b200_kv_rope_append(self._h, layer, _ptr(q), _ptr(k_rows), _ptr(v_rows), _ptr(positions), _ptr(row_seq),
+                                           q.shape[0], q.shape[1], theta, _stream()))
+
     def append(self, layer: int, k_rows: torch.Tensor, v_rows: torch.Tensor):
         assert k_rows.dtype == torch.bfloat16 and v_rows.dtype == torch.bfloat16
         _lib.check(lib.b200_kv_append(self._h, layer, _ptr(k_rows), _ptr(v_rows), k_rows.shape[0], _stream()))

@@ -270,6 +270,12 @@ b200_status b200_kv_reserve(b200_kv* kv, const b200_pack_desc* d_desc, int32_t n
  * (:533-637).  K rows are expected already rotated, as updateAndFetch receives them. */
 b200_status b200_kv_append(b200_kv* kv, int32_t layer, const void* d_k_rows, const void* d_v_rows,
                            int32_t total_rows, void* stream);
+/* RoPE on q and k (in place, non-traditional, per-row positions, src/models/llama.zig:213-215) and the
+ * append of the rotated K rows and the V rows in one launch: q [T, n_q_heads, head_dim], k and v
+ * [T, n_kv_heads, head_dim] bf16, d_row_seq the sequence slot of every row (b200_pack_batch). */
+b200_status b200_kv_rope_append(b200_kv* kv, int32_t layer, void* d_q, void* d_k_rows, const void* d_v_rows,
+                                const int32_t* d_positions, const int32_t* d_row_seq, int32_t total_rows,
+                                int32_t n_q_heads, float theta, void* stream);
 /* Introspection for bit-exact checks (synchronous). */
 b200_status b200_kv_seq_len(b200_kv* kv, int32_t seq, int32_t* out_len);         /* :485-488 */
 b200_status b200_kv_current_len(b200_kv* kv, int32_t* out_len);                  /* :842-849 currentLen */

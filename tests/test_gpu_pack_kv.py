@@ -345,3 +345,36 @@ def test_filter_current_len_and_reset_match_the_page_table_oracle():
     with pytest.raises(ref_host.InvalidBatchIndex):
         ref.filter([0, n_seqs])
     kv.close()
+
+
+def test_rope_append_in_one_call_matches_rope_then_append():
+    """b200_kv_rope_append: q and k rotated in place with per-row positions (non-traditional RoPE,
+    src/models/llama.zig:213-215) and the rotated K rows and V rows written to their pages, against the
+    oracle's rope followed by the gathered view of the pool."""
+    dev = _dev()
+    rng = np.random.default_rng(17)
+    hq, hkv, d = 8, 2, 64
+    ctxs = [37, 5, 64]
+    kv = dev.PagedKVCache(1, hkv, d, 16, 3, 4, hq, max_rows=256)
+    desc = dev.pack_desc_array([(s, c, 0, -1) for s, c in enumerate(ctxs)]).cuda()
+    kv.reserve(desc)
+    t = sum(ctxs)
+    q = ref_math.bf16_round(rng.normal(0, 1, (t, hq, d)))
+    k = ref_math.bf16_round(rng.normal(0, 1, (t, hkv, d)))
+    v = ref_math.bf16_round(rng.normal(0, 1, (t, hkv, d)))
+    pos = np.concatenate([np.arange(c) for c in ctxs]).astype(np.int32)
+    seq = np.concatenate([np.full(c, s) for s, c in enumerate(ctxs)]).astype(np.int32)
+    qd, kd, vd = (torch.tensor(a, device="cuda").bfloat16() for a in (q, k, v))
+    kv.rope_append(0, qd, kd, vd, torch.tensor(pos, device="cuda"), torch.tensor(seq, device="cuda"), theta=10000.0)
+    torch.cuda.synchronize()
+    assert kv.error_word() == 0
+    off = 0
+    for s, c in enumerate(ctxs):
+        want_q = ref_math.rope(q[off:off + c].transpose(1, 0, 2), np.arange(c)).transpose(1, 0, 2)
+        want_k = ref_math.rope(k[off:off + c].transpose(1, 0, 2), np.arange(c)).transpose(1, 0, 2)
+        got_k, got_v = kv.gather(0, s)
+        assert np.abs(qd[off:off + c].float().cpu().numpy() - want_q).max() <= 2e-2 * np.abs(want_q).max()
+        assert np.abs(got_k.float().cpu().numpy() - want_k).max() <= 2e-2 * np.abs(want_k).max()
+        assert np.array_equal(got_v.float().cpu().numpy(), v[off:off + c])
+        off += c
+    kv.close()
