@@ -582,17 +582,19 @@ def run_arrivals(args, rank, world, local, model=None, c=None, quiet=False):
         torch.cuda.synchronize()
 
     out = {}
-    for name, rate in (("poisson_20rps", 20.0), ("saturation", 0.0)):
+    # the two scenarios on a pool small enough that admission has to wait (--pool-pages), and the saturated one
+    # again on a pool that holds all 256 requests at once (4 MiB per page over 32 layers: 64 GiB)
+    for name, rate, pool in (("poisson_20rps", 20.0, args.pool_pages), ("saturation", 0.0, args.pool_pages),
+                             ("saturation_large_pool", 0.0, 16384)):
         if args.arrival_scenarios != "both" and args.arrival_scenarios != name:
             continue
-        part = run_arrival_scenario(dev, torch, model, c, rank, world, barrier, rate, args.pool_pages, args.prefill_chunk,
-                                    args.step_tokens)
+        part = run_arrival_scenario(dev, torch, model, c, rank, world, barrier, rate, pool, args.prefill_chunk, args.step_tokens)
         if world > 1:
             parts = [None] * world
             dist.all_gather_object(parts, part)
         else:
             parts = [part]
-        out[name] = summarise_arrivals(parts, rate, args.pool_pages, args.prefill_chunk, args.step_tokens, world)
+        out[name] = summarise_arrivals(parts, rate, pool, args.prefill_chunk, args.step_tokens, world)
     if own:
         if rank == 0 and not quiet:
             sat = out.get("saturation") or next(iter(out.values()))
@@ -1096,7 +1098,7 @@ def main():
     ap.add_argument("--mx-persistent", type=int, default=-1, help="block-scaled MXFP4 path: 1 persistent CTAs over work items, 0 one CTA per item (default: library choice)")
     ap.add_argument("--no-arrivals", action="store_true", help="llama8b_int4 only: skip the arrival-process scenarios")
     ap.add_argument("--no-ep", action="store_true", help="llama8b_int4 on several GPUs only: skip the expert-parallel MoE measurement")
-    ap.add_argument("--arrival-scenarios", default="both", help="poisson_20rps | saturation | both")
+    ap.add_argument("--arrival-scenarios", default="both", help="poisson_20rps | saturation | saturation_large_pool | both (= all three)")
     ap.add_argument("--pool-pages", type=int, default=3072, help="arrival scenarios: KV pages per replica (32 tokens x 32 layers x 4 KiB each)")
     ap.add_argument("--prefill-chunk", type=int, default=512, help="arrival scenarios: prefill chunk (tokens)")
     ap.add_argument("--step-tokens", type=int, default=2048, help="arrival scenarios: token budget of one engine step")
