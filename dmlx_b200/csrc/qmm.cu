@@ -516,34 +516,43 @@ __device__ __forceinline__ void tile_epilogue_store(const QmmArgs& a, const uint
 
 // ---- tcgen05 kernel with the weight operand in tensor memory -----------------------------------
 // In qmm_tc_kernel a stage is one unit: weight block + activation tile + the 16 KiB dequantised
-// tile travel together, a stage lives for load + dequantise + MMA (about 3000 cycles measured with
-// timestamps) and only three of them fit a CTA.  Here the two lifetimes are separated and the
-// dequantised tile leaves shared memory:
-//   * loads: a ring of P slots (raw 4-bit block + activation tile, 13-21 KiB each) runs ahead by
-//     the load latency;
+// tile travel together, a stage lives for load + dequantise + MMA and only three of them fit a CTA.
+// Here the lifetimes are separated and the dequantised tile leaves shared memory:
+//   * raw weight blocks: a ring of PW slots of two consecutive blocks (128 K columns, 9 KiB, one bulk
+//     copy).  A slot is released as soon as the dequantising warps hold its words in registers;
+//   * activation tiles (two of tn x 128 B per slot, re-read from L2 by every CTA): their own ring of
+//     PX slots, released by the MMAs that read them.  Sharing one ring with the weights, as an earlier
+//     form of this kernel did, let the activation tiles crowd out the weight bytes in flight;
 //   * dequantised weights: warps 0-7 write them straight into tensor memory (tcgen05.st; thread r
 //     owns lane r = weight row r, a 64-column chunk is 32 columns of packed bf16 pairs), into a ring
-//     of Q slots behind the accumulator, and tcgen05.mma takes its A operand from there.  No swizzled
-//     shared-memory tile, no proxy fence, and the MMA reads only the activation tile from shared
-//     memory.
-// An MMA's completion releases both its load slot and its tensor-memory slot (two commits).
-constexpr int kTcaThreads = 320;
+//     of Q slots of 64 columns behind the accumulator, and tcgen05.mma takes its A operand from there.
+//     No swizzled shared-memory tile, no proxy fence, and the MMA reads only the activation tile from
+//     shared memory.
+// Every handshake covers a pair of chunks: with one chunk per handshake a dequantising warp spent about
+// 120 of its 186 instructions per chunk on waits, arrivals and ring bookkeeping (instruction counters),
+// and the MMA thread 500 cycles per chunk of which the two commits took more than the four MMAs.
+constexpr int kTcaThreads = 352;  // warps 0-7 dequantise (0-3 also run the epilogue), 8 loads weights, 9 issues MMAs, 10 loads activations
+constexpr int kTcaMaxWeightSlots = 24;
 
 template <int MODE>
 __global__ void __launch_bounds__(kTcaThreads, 2) qmm_tca_kernel(const __grid_constant__ CUtensorMap xmap, QmmArgs a) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr int BB = block_bytes(MODE);
-  constexpr int kRaw = ((BB + 127) / 128) * 128;
-  const int tn = a.tn, P = a.stages, Q = a.a_slots;
-  auto x_tile = [&](int s) { return smem + (size_t)s * tn * 128; };
-  auto raw_blk = [&](int s) { return smem + (size_t)P * tn * 128 + (size_t)s * kRaw; };
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)P * (tn * 128 + kRaw));
-  uint64_t* full = bars;                 // [P] raw block + activation tile have landed
-  uint64_t* slot_free = bars + P;        // [P] the MMAs reading the activation tile are done
-  uint64_t* a_ready = bars + 2 * P;      // [Q] dequantised chunk is in tensor memory
-  uint64_t* a_free = bars + 2 * P + Q;   // [Q] the MMAs reading it are done
-  uint64_t* accum_ready = bars + 2 * P + 2 * Q;
+  static_assert(BB % 128 == 0, "two blocks are copied as one run");
+  const int tn = a.tn, PW = a.stages, PX = a.x_slots, Q = a.a_slots;
+  const uint32_t x_slot_bytes = 2u * (uint32_t)tn * 128u;
+  unsigned char* wring = smem + (size_t)PX * x_slot_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(wring + (size_t)PW * 2 * BB);
+  // barrier addresses in the shared window (the hot loops keep them as 32-bit integers)
+  const uint32_t smem_u = ptx::smem_u32(smem), wring_u = ptx::smem_u32(wring), bars_u = ptx::smem_u32(bars);
+  const uint32_t wfull = bars_u;                                  // [PW] a pair of raw blocks has landed
+  const uint32_t wfree = wfull + 8u * PW;                         // [PW] every dequantising warp has read it
+  const uint32_t xfull = wfree + 8u * PW;                         // [PX] a pair of activation tiles has landed
+  const uint32_t xfree = xfull + 8u * PX;                         // [PX] the MMAs reading it are done
+  const uint32_t a_ready = xfree + 8u * PX;                       // [Q] a dequantised pair is in tensor memory
+  const uint32_t a_free = a_ready + 8u * Q;                       // [Q] the MMAs reading it are done
+  uint64_t* accum_ready = bars + 2 * PW + 2 * PX + 2 * Q;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_ready + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -558,20 +567,24 @@ __global__ void __launch_bounds__(kTcaThreads, 2) qmm_tca_kernel(const __grid_co
     rows_here = it.z;
   }
   const int kc0 = split * a.chunks_per_split, kc1 = min(kc0 + a.chunks_per_split, a.kc);
-  const int n_chunks = kc1 - kc0;
+  const int n_chunks = kc1 - kc0, n_pairs = (n_chunks + 1) >> 1;
   uint32_t acc_cols = 32;
   while (acc_cols < (uint32_t)tn) acc_cols <<= 1;
   uint32_t ncols = 32;
-  while (ncols < acc_cols + 32u * (uint32_t)Q) ncols <<= 1;
+  while (ncols < acc_cols + 64u * (uint32_t)Q) ncols <<= 1;
 
   if (tid == 0) {
-    for (int s = 0; s < P; ++s) {
-      ptx::mbar_init(&full[s], 1);
-      ptx::mbar_init(&slot_free[s], 1);
+    for (int s = 0; s < PW; ++s) {
+      ptx::mbar_init(&bars[s], 1);
+      ptx::mbar_init(&bars[PW + s], 2 * kTileN / 32);  // one arrival per dequantising warp
+    }
+    for (int s = 0; s < PX; ++s) {
+      ptx::mbar_init(&bars[2 * PW + s], 1);
+      ptx::mbar_init(&bars[2 * PW + PX + s], 1);
     }
     for (int q = 0; q < Q; ++q) {
-      ptx::mbar_init(&a_ready[q], 2 * kTileN / 32);  // one arrival per dequantising warp (256 single arrivals cost ~500 cycles)
-      ptx::mbar_init(&a_free[q], 1);
+      ptx::mbar_init(&bars[2 * PW + 2 * PX + q], 2 * kTileN / 32);  // one arrival per dequantising warp (256 single arrivals cost ~500 cycles)
+      ptx::mbar_init(&bars[2 * PW + 2 * PX + Q + q], 1);
     }
     ptx::mbar_init(accum_ready, 1);
     ptx::mbar_fence_init();
@@ -588,18 +601,33 @@ __global__ void __launch_bounds__(kTcaThreads, 2) qmm_tca_kernel(const __grid_co
   bool ok = true;
 
   if (warp == 8) {
-    if (lane == 0) {
+    if (lane == 0) {  // the weight stream
       const unsigned char* wsrc = blocks + ((size_t)nt * a.kc + kc0) * BB;
-      for (int i = 0; i < min(n_chunks, kPrefetchAhead); ++i) ptx::bulk_prefetch_l2(wsrc + (size_t)i * BB, BB);
       int s = 0;
-      uint32_t ph = 0;
-      for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1) {
-        if (i + kPrefetchAhead < n_chunks) ptx::bulk_prefetch_l2(wsrc + (size_t)(i + kPrefetchAhead) * BB, BB);
-        ok = ptx::mbar_wait(&slot_free[s], ph ^ 1u);
+      uint32_t ph = 1;
+      for (int p = 0; p < n_pairs; ++p) {
+        ok = ptx::mbar_wait_addr(wfree + 8u * s, ph);
         if (!ok) break;
-        ptx::mbar_expect_tx(&full[s], BB + tn * 128);
-        ptx::bulk_g2s(raw_blk(s), wsrc + (size_t)i * BB, BB, &full[s]);
-        ptx::tma_load_2d(x_tile(s), &xmap, (kc0 + i) * kChunkK, a.x_row0 + t0, &full[s]);
+        const uint32_t bytes = (2 * p + 1 < n_chunks) ? 2u * BB : (uint32_t)BB;
+        ptx::mbar_expect_tx_addr(wfull + 8u * s, bytes);
+        ptx::bulk_g2s_addr(wring_u + (uint32_t)s * 2u * BB, wsrc + (size_t)p * 2 * BB, bytes, wfull + 8u * s);
+        if (++s == PW) { s = 0; ph ^= 1u; }
+      }
+    }
+  } else if (warp == 10) {
+    if (lane == 0) {  // the activation tiles
+      int s = 0;
+      uint32_t ph = 1;
+      for (int p = 0; p < n_pairs; ++p) {
+        ok = ptx::mbar_wait_addr(xfree + 8u * s, ph);
+        if (!ok) break;
+        const bool two = 2 * p + 1 < n_chunks;
+        uint64_t* bar = &bars[2 * PW + s];
+        ptx::mbar_expect_tx(bar, two ? x_slot_bytes : x_slot_bytes / 2);
+        unsigned char* dst = smem + (size_t)s * x_slot_bytes;
+        ptx::tma_load_2d(dst, &xmap, (kc0 + 2 * p) * kChunkK, a.x_row0 + t0, bar);
+        if (two) ptx::tma_load_2d(dst + x_slot_bytes / 2, &xmap, (kc0 + 2 * p + 1) * kChunkK, a.x_row0 + t0, bar);
+        if (++s == PX) { s = 0; ph ^= 1u; }
       }
     }
   } else if (warp == 9) {
@@ -607,17 +635,27 @@ __global__ void __launch_bounds__(kTcaThreads, 2) qmm_tca_kernel(const __grid_co
       const uint32_t idesc = ptx::umma_idesc_bf16(kTileN, tn);
       int s = 0, q = 0;
       uint32_t ph = 0, qh = 0;
-      for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1, qh ^= (q + 1 == Q),
-               q = (q + 1 == Q) ? 0 : q + 1) {
-        ok = ptx::mbar_wait(&full[s], ph) && ptx::mbar_wait(&a_ready[q], qh);
+      for (int p = 0; p < n_pairs; ++p) {
+        ok = ptx::mbar_wait_addr(xfull + 8u * s, ph) && ptx::mbar_wait_addr(a_ready + 8u * q, qh);
         if (!ok) break;
         ptx::tc_fence_after_sync();
-        const uint64_t db = ptx::umma_desc_k_sw128(ptx::smem_u32(x_tile(s)));
+        const uint64_t db = ptx::umma_desc_k_sw128(smem_u + (uint32_t)s * x_slot_bytes);
+        const uint64_t db_step = (uint64_t)(x_slot_bytes / 2) >> 4;  // second tile of the pair (descriptor addresses count 16 bytes)
+        const uint32_t acol = a_col0 + (uint32_t)(q * 64);
+        const int n_here = (2 * p + 1 < n_chunks) ? 2 : 1;
 #pragma unroll
-        for (int k4 = 0; k4 < 4; ++k4)
-          ptx::umma_bf16_tmem_a(tmem_base, a_col0 + (uint32_t)(q * 32 + k4 * 8), db + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
-        ptx::umma_commit(&slot_free[s]);
-        ptx::umma_commit(&a_free[q]);
+        for (int j = 0; j < 2; ++j) {
+          if (j < n_here) {
+#pragma unroll
+            for (int k4 = 0; k4 < 4; ++k4)
+              ptx::umma_bf16_tmem_a(tmem_base, acol + (uint32_t)(j * 32 + k4 * 8), db + j * db_step + 2 * k4, idesc,
+                                    (p > 0 || j > 0 || k4 > 0) ? 1u : 0u);
+          }
+        }
+        ptx::umma_commit(&bars[2 * PW + PX + s]);
+        ptx::umma_commit(&bars[2 * PW + 2 * PX + Q + q]);
+        if (++s == PX) { s = 0; ph ^= 1u; }
+        if (++q == Q) { q = 0; qh ^= 1u; }
       }
       if (ok) ptx::umma_commit(accum_ready);
     }
@@ -625,43 +663,65 @@ __global__ void __launch_bounds__(kTcaThreads, 2) qmm_tca_kernel(const __grid_co
     // ---- dequantise: thread (r, plane) owns one 32-column half of weight row r = tensor-memory lane r ----
     const int r = tid & (kTileN - 1), plane = tid >> 7;
     const uint32_t my_taddr = a_col0 + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(plane * 16);
+    const unsigned char* my_raw = wring + plane * kPlaneBytes + r * 16;
     int s = 0, q = 0, pending_q = -1;
-    uint32_t ph = 0, qh = 0;
-    // The store of chunk i into tensor memory is left in flight while chunk i+1 is loaded and dequantised;
-    // it is waited for, and its slot announced, just before the next store is issued.
-    for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1, qh ^= (q + 1 == Q),
-             q = (q + 1 == Q) ? 0 : q + 1) {
-      ok = ptx::mbar_wait(&full[s], ph);
+    uint32_t ph = 0, qh = 1;
+    // The stores of pair p into tensor memory are left in flight while pair p+1 is loaded and its first
+    // chunk dequantised; they are waited for, and their slot announced, just before the next store.
+    for (int p = 0; p < n_pairs; ++p) {
+      ok = ptx::mbar_wait_addr(wfull + 8u * s, ph);
       if (!ok) break;
-      const unsigned char* blk = raw_blk(s);
-      const uint4 raw = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[r];
-      __nv_bfloat162 s2, b2;
-      row_params<MODE>(blk, r, plane, s2, b2);
-      const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+      const bool two = 2 * p + 1 < n_chunks;
+      const unsigned char* blk = wring + (size_t)s * 2 * BB;
+      const uint4 raw0 = *reinterpret_cast<const uint4*>(my_raw + (size_t)s * 2 * BB);
+      uint4 raw1 = make_uint4(0u, 0u, 0u, 0u);
+      __nv_bfloat162 s20, b20, s21, b21;
+      row_params<MODE>(blk, r, plane, s20, b20);
+      s21 = s20; b21 = b20;
+      if (two) {
+        raw1 = *reinterpret_cast<const uint4*>(my_raw + (size_t)s * 2 * BB + BB);
+        row_params<MODE>(blk + BB, r, plane, s21, b21);
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_addr(wfree + 8u * s);  // this warp's share of the pair is in registers
       uint32_t v[16];
+      {
+        const uint32_t words[4] = {raw0.x, raw0.y, raw0.z, raw0.w};
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const uint4 d = dequant_word<MODE>(words[w], s2, b2);
-        v[4 * w] = d.x; v[4 * w + 1] = d.y; v[4 * w + 2] = d.z; v[4 * w + 3] = d.w;
+        for (int w = 0; w < 4; ++w) {
+          const uint4 d = dequant_word<MODE>(words[w], s20, b20);
+          v[4 * w] = d.x; v[4 * w + 1] = d.y; v[4 * w + 2] = d.z; v[4 * w + 3] = d.w;
+        }
       }
       if (pending_q >= 0) {
         ptx::tmem_st_wait();
         ptx::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&a_ready[pending_q]);
+        if (lane == 0) ptx::mbar_arrive_addr(a_ready + 8u * pending_q);
         pending_q = -1;
       }
-      ok = ptx::mbar_wait(&a_free[q], qh ^ 1u);
+      ok = ptx::mbar_wait_addr(a_free + 8u * q, qh);
       if (!ok) break;
       ptx::tc_fence_after_sync();
-      ptx::tmem_st16(my_taddr + (uint32_t)(q * 32), v);
+      ptx::tmem_st16(my_taddr + (uint32_t)(q * 64), v);
+      if (two) {
+        const uint32_t words[4] = {raw1.x, raw1.y, raw1.z, raw1.w};
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+          const uint4 d = dequant_word<MODE>(words[w], s21, b21);
+          v[4 * w] = d.x; v[4 * w + 1] = d.y; v[4 * w + 2] = d.z; v[4 * w + 3] = d.w;
+        }
+        ptx::tmem_st16(my_taddr + (uint32_t)(q * 64 + 32), v);
+      }
       pending_q = q;
+      if (++s == PW) { s = 0; ph ^= 1u; }
+      if (++q == Q) { q = 0; qh ^= 1u; }
     }
     if (pending_q >= 0) {
       ptx::tmem_st_wait();
       ptx::tc_fence_before_sync();
       __syncwarp();
-      if (ok && lane == 0) ptx::mbar_arrive(&a_ready[pending_q]);
+      if (ok && lane == 0) ptx::mbar_arrive_addr(a_ready + 8u * pending_q);
     }
     // ---- accumulator -> f32 partial tile in scratch ----
     if (ok && warp < 4) ok = ptx::mbar_wait(accum_ready, 0);
@@ -2237,8 +2297,6 @@ static b200_status launch_tca(QmmArgs& a, int rows, cudaStream_t s) {
   const int tiles = a.items ? a.nt * a.max_items : a.nt * tts;
   b200_status st = ensure_state(0);
   if (st != B200_OK) return st;
-  constexpr int kRaw = ((block_bytes(MODE) + 127) / 128) * 128;
-  const int slot_bytes = tn * 128 + kRaw;
   static int smem_budget[3] = {0, 0, 0};
   if (smem_budget[MODE] == 0) {
     int dev = 0, optin = 0;
@@ -2251,15 +2309,18 @@ static b200_status launch_tca(QmmArgs& a, int rows, cudaStream_t s) {
     smem_budget[MODE] = budget;
   }
   // Two CTAs per SM share the 512 tensor-memory columns: accumulator (tn rounded up to a power of
-  // two) + 32 columns per slot of dequantised weights, 256 columns per CTA (all 512 above 128 rows).
+  // two) + 64 columns per slot of dequantised weights (a pair of chunks), 256 columns per CTA (all
+  // 512 above 128 rows).
   const int ctas_per_sm = tn <= 128 ? 2 : 1;
   int acc_cols = 32;
   while (acc_cols < tn) acc_cols <<= 1;
-  a.a_slots = std::min(8, ((ctas_per_sm == 2 ? 256 : 512) - acc_cols) / 32);
-  const int fixed = 1024 /*alignment slack*/ + 8 * (2 * 8 + 2 * 8 + 2) + 16;
+  a.a_slots = std::min(4, ((ctas_per_sm == 2 ? 256 : 512) - acc_cols) / 64);
+  // shared memory: two slots of activation-tile pairs, the rest a ring of raw block pairs
   const int per_cta = ctas_per_sm == 2 ? 113 * 1024 : std::min(smem_budget[MODE], 220 * 1024);
-  a.stages = std::max(2, std::min(8, (per_cta - fixed) / slot_bytes));
-  const size_t smem = (size_t)a.stages * slot_bytes + fixed;
+  a.x_slots = 2;
+  const int fixed = 1024 /*alignment slack*/ + 8 * (2 * kTcaMaxWeightSlots + 2 * 2 + 2 * 4 + 2) + 16;
+  a.stages = std::max(2, std::min(kTcaMaxWeightSlots, (per_cta - fixed - a.x_slots * 2 * tn * 128) / (2 * block_bytes(MODE))));
+  const size_t smem = (size_t)a.x_slots * 2 * tn * 128 + (size_t)a.stages * 2 * block_bytes(MODE) + fixed;
   if ((int)smem > smem_budget[MODE] || a.a_slots < 2) {
     b200_set_error("qmm: %zu bytes of shared memory needed, %d available", smem, smem_budget[MODE]);
     return B200_ERR_CAPACITY;
