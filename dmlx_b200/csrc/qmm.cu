@@ -2330,7 +2330,9 @@ static b200_status launch_tca(QmmArgs& a, int rows, cudaStream_t s) {
   const int splits = (a.kc + a.chunks_per_split - 1) / a.chunks_per_split;
   // Prefill-sized batches (several token tiles, one K split) would need rows x N x 4 bytes of scratch:
   // the kernel writes its output itself instead.
-  a.direct_large = (!a.items && splits == 1 && tts >= 4) ? 1 : 0;
+  // ... and so does a single K split of up to 128-row tiles (gate/up at 128 rows 44.9 -> 42.9 us, lm_head 159 -> 147 us;
+  // with 256-row tiles at one CTA per SM the longer epilogue costs more than the finish pass: 290 -> 302 us)
+  a.direct_large = (!a.items && splits == 1 && (tts >= 4 || tn <= 128)) ? 1 : 0;
   const bool direct = splits == 1 && (tn <= 64 || a.direct_large);
   st = ensure_state(direct ? 0 : (size_t)splits * (a.items ? (size_t)rows : (size_t)tts * tn) * a.nt * kTileN * sizeof(float));
   if (st != B200_OK) return st;
