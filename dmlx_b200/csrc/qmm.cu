@@ -755,26 +755,35 @@ __global__ void __launch_bounds__(kTcaThreads, 2) qmm_tca_kernel(const __grid_co
 // a stage carries twice the MMA work per activation byte, so the same shared memory hides twice
 // the latency and the L2 -> SM activation traffic per flop halves.  16 dequant warps (one thread
 // per weight row and 32-column plane of either tile), one loader warp, one MMA warp.
-constexpr int kTc2Threads = 18 * 32;
+constexpr int kTc2Threads = 19 * 32;  // warps 0-15 dequantise, 16 streams the weights, 17 issues MMAs, 18 loads activation tiles
 constexpr int kTc2DequantThreads = 16 * 32;
 
+// Quantised weights: the raw 4-bit blocks have a ring of their own (SR slots of two blocks), released as
+// soon as the dequantising warps hold the words in registers, so the weight stream runs ahead of the
+// stages by the DRAM latency instead of starting when an MMA retires a stage (load 1500 cycles ->
+// dequantise 700 -> MMA 1024 per stage of three was longer than the MMAs of the other two stages).
+// A stage holds the two dequantised tiles and the activation tile, which comes from L2 while the
+// dequantisation runs.  Dense bf16 blocks land in the stage's MMA tiles directly (SR = stages there).
 template <int MODE>
 __global__ void __launch_bounds__(kTc2Threads, 1) qmm_tc2_kernel(const __grid_constant__ CUtensorMap xmap, QmmArgs a) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr int BB = block_bytes(MODE);
-  constexpr int kRaw = MODE == B200_Q_BF16 ? 0 : ((BB + 1023) / 1024) * 1024;  // dense blocks land in the MMA tile itself
-  const int tn = a.tn, stages = a.stages;
-  const int stage_stride = 2 * kTileN * 128 + tn * 128 + 2 * kRaw;
+  constexpr bool kDense = MODE == B200_Q_BF16;
+  constexpr int RB = kDense ? 0 : ((BB + 127) / 128) * 128;
+  const int tn = a.tn, stages = a.stages, SR = a.x_slots;
+  const int stage_stride = 2 * kTileN * 128 + tn * 128;
   auto a_tile = [&](int s, int tile) { return smem + (size_t)s * stage_stride + tile * (kTileN * 128); };
   auto x_tile = [&](int s) { return smem + (size_t)s * stage_stride + 2 * kTileN * 128; };
-  auto raw_blk = [&](int s, int tile) { return smem + (size_t)s * stage_stride + 2 * kTileN * 128 + tn * 128 + tile * kRaw; };
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_stride);
-  uint64_t* loaded = bars;
-  uint64_t* a_ready = bars + stages;
-  uint64_t* mma_done = bars + 2 * stages;
-  uint64_t* accum_ready = bars + 3 * stages;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * stages + 1);
+  auto raw_blk = [&](int sr, int tile) { return smem + (size_t)stages * stage_stride + (size_t)(sr * 2 + tile) * RB; };
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_stride + (size_t)(kDense ? 0 : SR) * 2 * RB);
+  uint64_t* x_loaded = bars;                   // [stages] activation tile has landed
+  uint64_t* a_ready = bars + stages;           // [stages] both MMA tiles are written (or, dense, have landed)
+  uint64_t* mma_done = bars + 2 * stages;      // [stages] the MMAs reading the stage are done
+  uint64_t* raw_full = bars + 3 * stages;      // [SR] raw blocks have landed
+  uint64_t* raw_free = bars + 3 * stages + SR; // [SR] every dequantising warp has read them
+  uint64_t* accum_ready = bars + 3 * stages + 2 * SR;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_ready + 1);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int pair = blockIdx.x, split = blockIdx.y, tt = blockIdx.z;
@@ -787,9 +796,13 @@ __global__ void __launch_bounds__(kTc2Threads, 1) qmm_tc2_kernel(const __grid_co
 
   if (tid == 0) {
     for (int s = 0; s < stages; ++s) {
-      ptx::mbar_init(&loaded[s], 1);
+      ptx::mbar_init(&x_loaded[s], 1);
       ptx::mbar_init(&a_ready[s], kTc2DequantThreads / 32);  // one arrival per dequantising warp
       ptx::mbar_init(&mma_done[s], 1);
+    }
+    for (int s = 0; s < SR; ++s) {
+      ptx::mbar_init(&raw_full[s], 1);
+      ptx::mbar_init(&raw_free[s], kTc2DequantThreads / 32);
     }
     ptx::mbar_init(accum_ready, 1);
     ptx::mbar_fence_init();
@@ -805,26 +818,39 @@ __global__ void __launch_bounds__(kTc2Threads, 1) qmm_tc2_kernel(const __grid_co
   bool ok = true;
 
   if (warp == 16) {
-    if (lane == 0) {
+    if (lane == 0) {  // the weight stream
       int s = 0;
-      uint32_t ph = 0;  // stage cursor kept incrementally: no division by the runtime stage count
-      for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == stages), s = (s + 1 == stages) ? 0 : s + 1) {
-        ok = ptx::mbar_wait(&mma_done[s], ph ^ 1u);
+      uint32_t ph = 1;
+      for (int i = 0; i < n_chunks; ++i) {
+        // dense blocks go into the stage's MMA tiles, so their slot is the stage and frees with its MMAs
+        ok = ptx::mbar_wait(kDense ? &mma_done[s] : &raw_free[s], ph);
         if (!ok) break;
-        ptx::mbar_expect_tx(&loaded[s], n_tiles * BB + tn * 128);
+        ptx::mbar_expect_tx(&raw_full[s], n_tiles * BB);
         for (int tile = 0; tile < n_tiles; ++tile)
-          ptx::bulk_g2s(MODE == B200_Q_BF16 ? a_tile(s, tile) : raw_blk(s, tile),
-                        a.blocks + ((size_t)(nt0 + tile) * a.kc + kc0 + i) * BB, BB, &loaded[s]);
-        ptx::tma_load_2d(x_tile(s), &xmap, (kc0 + i) * kChunkK, a.x_row0 + t0, &loaded[s]);
+          ptx::bulk_g2s(kDense ? a_tile(s, tile) : raw_blk(s, tile), a.blocks + ((size_t)(nt0 + tile) * a.kc + kc0 + i) * BB, BB,
+                        &raw_full[s]);
+        if (++s == SR) { s = 0; ph ^= 1u; }
+      }
+    }
+  } else if (warp == 18) {
+    if (lane == 0) {  // the activation tiles
+      int s = 0;
+      uint32_t ph = 1;
+      for (int i = 0; i < n_chunks; ++i) {
+        ok = ptx::mbar_wait(&mma_done[s], ph);
+        if (!ok) break;
+        ptx::mbar_expect_tx(&x_loaded[s], tn * 128);
+        ptx::tma_load_2d(x_tile(s), &xmap, (kc0 + i) * kChunkK, a.x_row0 + t0, &x_loaded[s]);
+        if (++s == stages) { s = 0; ph ^= 1u; }
       }
     }
   } else if (warp == 17) {
     if (lane == 0) {
       const uint32_t idesc = ptx::umma_idesc_bf16(kTileN, tn);
       int s = 0;
-      uint32_t ph = 0;  // stage cursor kept incrementally: no division by the runtime stage count
-      for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == stages), s = (s + 1 == stages) ? 0 : s + 1) {
-        ok = ptx::mbar_wait(&loaded[s], ph) && ptx::mbar_wait(&a_ready[s], ph);
+      uint32_t ph = 0;
+      for (int i = 0; i < n_chunks; ++i) {
+        ok = ptx::mbar_wait(&x_loaded[s], ph) && ptx::mbar_wait(&a_ready[s], ph);
         if (!ok) break;
         ptx::tc_fence_after_sync();
         const uint64_t db = ptx::umma_desc_k_sw128(ptx::smem_u32(x_tile(s)));
@@ -835,33 +861,45 @@ __global__ void __launch_bounds__(kTc2Threads, 1) qmm_tc2_kernel(const __grid_co
             ptx::umma_bf16(tmem_base + tile * 256, da + 2 * k4, db + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u);
         }
         ptx::umma_commit(&mma_done[s]);
+        if (++s == stages) { s = 0; ph ^= 1u; }
       }
       if (ok) ptx::umma_commit(accum_ready);
     }
   } else {
     // ---- dequantise: thread (r, plane, tile) owns one 32-column half of weight row r of a tile ----
     const int r = tid & (kTileN - 1), plane = (tid >> 7) & 1, tile = tid >> 8;
-    int s = 0;
-    uint32_t ph = 0;  // stage cursor kept incrementally: no division by the runtime stage count
-    for (int i = 0; i < n_chunks && ok; ++i, ph ^= (s + 1 == stages), s = (s + 1 == stages) ? 0 : s + 1) {
-      ok = ptx::mbar_wait(&loaded[s], ph);
+    int s = 0, sr = 0;
+    uint32_t ph = 0, phr = 0;
+    for (int i = 0; i < n_chunks; ++i) {
+      ok = ptx::mbar_wait(&raw_full[sr], phr);
       if (!ok) break;
-      if (MODE != B200_Q_BF16 && tile < n_tiles) {
-        const unsigned char* blk = raw_blk(s, tile);
-        unsigned char* arow = a_tile(s, tile) + r * 128;
-        const uint4 raw = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[r];
+      if (!kDense) {
+        uint4 raw = make_uint4(0u, 0u, 0u, 0u);
         __nv_bfloat162 s2, b2;
-        row_params<MODE>(blk, r, plane, s2, b2);
-        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-          const int chunk16 = plane * 4 + w;
-          *reinterpret_cast<uint4*>(arow + ((chunk16 ^ (r & 7)) << 4)) = dequant_word<MODE>(words[w], s2, b2);
+        if (tile < n_tiles) {
+          const unsigned char* blk = raw_blk(sr, tile);
+          raw = reinterpret_cast<const uint4*>(blk + plane * kPlaneBytes)[r];
+          row_params<MODE>(blk, r, plane, s2, b2);
         }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&raw_free[sr]);  // this warp's share of the blocks is in registers
+        ok = ptx::mbar_wait(&mma_done[s], ph ^ 1u);     // the stage's MMA tiles may be overwritten
+        if (!ok) break;
+        if (tile < n_tiles) {
+          unsigned char* arow = a_tile(s, tile) + r * 128;
+          const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+          for (int w = 0; w < 4; ++w) {
+            const int chunk16 = plane * 4 + w;
+            *reinterpret_cast<uint4*>(arow + ((chunk16 ^ (r & 7)) << 4)) = dequant_word<MODE>(words[w], s2, b2);
+          }
+        }
+        ptx::fence_proxy_async_smem();
       }
-      ptx::fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&a_ready[s]);
+      if (++s == stages) { s = 0; ph ^= 1u; }
+      if (++sr == SR) { sr = 0; phr ^= 1u; }
     }
     // ---- accumulators: warp w reads lanes 32*(w%4); warps 4g..4g+3 take tile g/2, column half g%2 ----
     if (ok) ok = ptx::mbar_wait(accum_ready, 0);
@@ -2487,8 +2525,8 @@ static b200_status launch_tc2(QmmArgs& a, int rows, cudaStream_t s) {
   b200_status st = ensure_state(0);
   if (st != B200_OK) return st;
   constexpr int BB = block_bytes(MODE);
-  constexpr int kRaw = MODE == B200_Q_BF16 ? 0 : ((BB + 1023) / 1024) * 1024;
-  const int stage_stride = 2 * kTileN * 128 + tn * 128 + 2 * kRaw;
+  constexpr int RB = MODE == B200_Q_BF16 ? 0 : ((BB + 127) / 128) * 128;
+  const int stage_stride = 2 * kTileN * 128 + tn * 128;
   static int smem_budget[3] = {0, 0, 0};
   if (smem_budget[MODE] == 0) {
     int dev = 0, optin = 0;
@@ -2500,13 +2538,17 @@ static b200_status launch_tc2(QmmArgs& a, int rows, cudaStream_t s) {
     B200_CUDA_TRY(cudaFuncSetAttribute(qmm_tc2_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, budget));
     smem_budget[MODE] = budget;
   }
-  const int fixed = 1024 /*alignment slack*/ + 8 * (3 * 8 + 2) + 16;
-  a.stages = std::min(6, (smem_budget[MODE] - fixed) / stage_stride);
+  // stages of two MMA tiles + one activation tile; quantised weights add a ring of raw block pairs: at least
+  // three slots, then whatever the stages leave over
+  const int fixed = 1024 /*alignment slack*/ + 8 * (3 * 6 + 2 * 8 + 2) + 16;
+  const int raw_min = MODE == B200_Q_BF16 ? 0 : 3 * 2 * RB;
+  a.stages = std::min(6, (smem_budget[MODE] - fixed - raw_min) / stage_stride);
   if (a.stages < 2) {
     b200_set_error("qmm: %d bytes of shared memory per stage, %d available", stage_stride, smem_budget[MODE]);
     return B200_ERR_CAPACITY;
   }
-  const size_t smem = (size_t)a.stages * stage_stride + fixed;
+  a.x_slots = MODE == B200_Q_BF16 ? a.stages : std::min(8, (smem_budget[MODE] - fixed - a.stages * stage_stride) / (2 * RB));
+  const size_t smem = (size_t)a.stages * stage_stride + (MODE == B200_Q_BF16 ? 0 : (size_t)a.x_slots * 2 * RB) + fixed;
   // a K split costs a 128 x tn f32 tile written and read back per weight tile: weigh it as chunks
   const int splits0 = pick_splits(pairs * tts, a.kc, g_sms, 1, 2 + tn / 32);
   a.chunks_per_split = (a.kc + splits0 - 1) / splits0;

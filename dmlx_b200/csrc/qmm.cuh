@@ -31,7 +31,7 @@ struct QmmArgs {
   int rows, n, k, nt, kc;
   int chunks_per_split, tn, stages;
   int a_slots;                  // tensor-memory-operand kernel: slots of dequantised weights in tensor memory
-  int x_slots;                  // tensor-memory-operand kernel: ring slots of activation tiles (the raw weight blocks have their own ring of `stages` slots)
+  int x_slots;                  // tensor-memory-operand kernel: ring slots of activation tiles (the raw weight blocks have their own ring of `stages` slots); tile-pair kernel: ring slots of raw block pairs
   int direct_large;             // one K split and many token tiles: write the output from the kernel, no scratch
   int splits;                   // small-batch kernel: number of K splits (the grid is persistent)
   int epilogue;
