@@ -161,6 +161,7 @@ _sig("b200_kv_set_len", i32, vp, i32, i32)
 _sig("b200_paged_attn_decode", i32, vp, i32, vp, vp, vp, i32, vp, vp)
 _sig("b200_paged_attn_prefill", i32, vp, i32, vp, vp, vp, i32, vp, vp)
 _sig("b200_set_attn_pages_per_chunk", None, i32)
+_sig("b200_set_attn_prefill_direct", None, i32)
 _sig("b200_set_attn_path", None, i32)
 _sig("b200_rmsnorm", i32, vp, vp, vp, i32, i32, f32, vp)
 _sig("b200_rope", i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, f32, vp)

@@ -51,6 +51,9 @@ struct AttnArgs {
   const int* row_group = nullptr;    // [T]
   const int* n_groups = nullptr;
   int q_tokens = 1;                  // rows per group at most (16 / GQA group size)
+  // prefill path with one chunk per group (a chunk long enough for any context): the kernel normalises and writes
+  // the rows itself, no partials and no combine pass
+  __nv_bfloat16* direct_out = nullptr;
 };
 
 __global__ void attn_plan_kernel(const int* __restrict__ row_ctx, int total_rows, int page_size, int pages_per_chunk,
@@ -977,19 +980,26 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1)
   }
   __syncwarp();
 
-  int p_item = worker, p_page = 0, p_end = 0, p_begin = 0, p_head = 0, p_pid = 0;
+  // the lanes hold the page ids of a window of 32 pages of the item's chunk (a chunk may be longer: one chunk per
+  // group in the direct mode), refilled every 32 pages
+  int p_item = worker, p_page = 0, p_end = 0, p_begin = 0, p_head = 0, p_pid = 0, p_seq = 0;
   uint32_t prod_n = 0;
   auto producer_enter_item = [&]() {
     if (p_item < n_items) {
       const GroupItem it = decode_group_item(a, p_item, n_groups);
-      p_begin = it.page_begin; p_page = it.page_begin; p_end = it.page_end; p_head = it.head;
+      p_begin = it.page_begin; p_page = it.page_begin; p_end = it.page_end; p_head = it.head; p_seq = it.seq;
       const int pg = it.page_begin + lane;
       if (pg < it.page_end) p_pid = a.d.block_table[(size_t)it.seq * a.d.max_pages_per_seq + pg];
     }
   };
   auto produce_one = [&]() {
     if (p_item >= n_items) return;
-    const int pid = __shfl_sync(0xffffffffu, p_pid, p_page - p_begin);
+    const int rel = p_page - p_begin;
+    if (rel > 0 && (rel & 31) == 0) {
+      const int pg = p_page + lane;
+      if (pg < p_end) p_pid = a.d.block_table[(size_t)p_seq * a.d.max_pages_per_seq + pg];
+    }
+    const int pid = __shfl_sync(0xffffffffu, p_pid, rel & 31);
     const uint32_t s = prod_n % kMmaStages;
     if (lane == 0) {
       ptx::fence_proxy_async_smem();
@@ -1121,6 +1131,21 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1)
     lA += __shfl_xor_sync(0xffffffffu, lA, 2);
     lB += __shfl_xor_sync(0xffffffffu, lB, 1);
     lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    if (a.direct_out) {
+      if (onA) {
+        const float inv = lA > 0.f ? 1.0f / lA : 0.f;
+        __nv_bfloat16* dst = a.direct_out + ((size_t)(it.first_row + tokA) * a.n_q_heads + it.head * G + headA) * D;
+#pragma unroll
+        for (int j = 0; j < NO; ++j) *reinterpret_cast<__nv_bfloat162*>(dst + j * 8 + 2 * t) = __floats2bfloat162_rn(o[j][0] * inv, o[j][1] * inv);
+      }
+      if (onB) {
+        const float inv = lB > 0.f ? 1.0f / lB : 0.f;
+        __nv_bfloat16* dst = a.direct_out + ((size_t)(it.first_row + tokB) * a.n_q_heads + it.head * G + headB) * D;
+#pragma unroll
+        for (int j = 0; j < NO; ++j) *reinterpret_cast<__nv_bfloat162*>(dst + j * 8 + 2 * t) = __floats2bfloat162_rn(o[j][2] * inv, o[j][3] * inv);
+      }
+      continue;
+    }
     if (onA) {
       const size_t pidx = (size_t)(it.slot0 + tokA) * a.n_q_heads + it.head * G + headA;
 #pragma unroll
@@ -1168,19 +1193,26 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1)
   }
   __syncwarp();
 
-  int p_item = worker, p_page = 0, p_end = 0, p_begin = 0, p_head = 0, p_pid = 0;
+  // the lanes hold the page ids of a window of 32 pages of the item's chunk (a chunk may be longer: one chunk per
+  // group in the direct mode), refilled every 32 pages
+  int p_item = worker, p_page = 0, p_end = 0, p_begin = 0, p_head = 0, p_pid = 0, p_seq = 0;
   uint32_t prod_n = 0;
   auto producer_enter_item = [&]() {
     if (p_item < n_items) {
       const GroupItem it = decode_group_item(a, p_item, n_groups);
-      p_begin = it.page_begin; p_page = it.page_begin; p_end = it.page_end; p_head = it.head;
+      p_begin = it.page_begin; p_page = it.page_begin; p_end = it.page_end; p_head = it.head; p_seq = it.seq;
       const int pg = it.page_begin + lane;
       if (pg < it.page_end) p_pid = a.d.block_table[(size_t)it.seq * a.d.max_pages_per_seq + pg];
     }
   };
   auto produce_one = [&]() {
     if (p_item >= n_items) return;
-    const int pid = __shfl_sync(0xffffffffu, p_pid, p_page - p_begin);
+    const int rel = p_page - p_begin;
+    if (rel > 0 && (rel & 31) == 0) {
+      const int pg = p_page + lane;
+      if (pg < p_end) p_pid = a.d.block_table[(size_t)p_seq * a.d.max_pages_per_seq + pg];
+    }
+    const int pid = __shfl_sync(0xffffffffu, p_pid, rel & 31);
     const uint32_t s = prod_n % STAGES;
     if (lane == 0) {
       ptx::fence_proxy_async_smem();
@@ -1221,20 +1253,21 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1)
         qa3[c] = onB ? pack_f16(ptx::bf16_lo(rb.y), ptx::bf16_hi(rb.y)) : 0u;
       }
     }
-    float my_ks = 0.f, my_vs = 0.f;
-    {
-      const int pg = it.page_begin + lane;
+    // per-page scales: the lanes hold a window of 32 pages; the reference V scale is the largest of the whole chunk
+    float my_ks = 0.f, my_vs = 0.f, v_ref = 0.f;
+    for (int base = it.page_begin; base < it.page_end; base += 32) {
+      const int pg = base + lane;
       if (pg < it.page_end) {
         const int pid = a.d.block_table[(size_t)it.seq * a.d.max_pages_per_seq + pg];
         const size_t si = ((size_t)a.layer * a.d.n_pages + pid) * H + it.head;
-        my_ks = a.d.k_scale[si];
-        my_vs = a.d.v_scale[si];
+        const float vsc = a.d.v_scale[si];
+        v_ref = fmaxf(v_ref, vsc);
+        if (base == it.page_begin) { my_ks = a.d.k_scale[si]; my_vs = vsc; }
       }
     }
-    float v_ref = my_vs;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v_ref = fmaxf(v_ref, __shfl_xor_sync(0xffffffffu, v_ref, o));
-    const float my_vr = v_ref > 0.f ? my_vs / v_ref : 0.f;
+    float my_vr = v_ref > 0.f ? my_vs / v_ref : 0.f;
 
     float o[NO][4];
 #pragma unroll
@@ -1245,8 +1278,18 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1)
       const uint32_t s = cons_n % STAGES;
       alive = ptx::mbar_wait(&full_bar[s], (cons_n / STAGES) & 1u);
       if (!alive) break;
-      const float ks = __shfl_sync(0xffffffffu, my_ks, pg - it.page_begin) * a.scale_log2;
-      const float vr = __shfl_sync(0xffffffffu, my_vr, pg - it.page_begin);
+      const int rel = pg - it.page_begin;
+      if (rel > 0 && (rel & 31) == 0) {  // next window of page scales
+        my_ks = 0.f; my_vr = 0.f;
+        if (pg + lane < it.page_end) {
+          const int pid = a.d.block_table[(size_t)it.seq * a.d.max_pages_per_seq + pg + lane];
+          const size_t si = ((size_t)a.layer * a.d.n_pages + pid) * H + it.head;
+          my_ks = a.d.k_scale[si];
+          my_vr = v_ref > 0.f ? a.d.v_scale[si] / v_ref : 0.f;
+        }
+      }
+      const float ks = __shfl_sync(0xffffffffu, my_ks, rel & 31) * a.scale_log2;
+      const float vr = __shfl_sync(0xffffffffu, my_vr, rel & 31);
       const uint32_t kbase = ptx::smem_u32(my_tiles + (size_t)s * 2 * TILE), vbase = kbase + TILE;
       float sc[4][4];
 #pragma unroll
@@ -1331,6 +1374,27 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 1)
     lA += __shfl_xor_sync(0xffffffffu, lA, 2);
     lB += __shfl_xor_sync(0xffffffffu, lB, 1);
     lB += __shfl_xor_sync(0xffffffffu, lB, 2);
+    if (a.direct_out) {
+      if (onA) {
+        const float f = lA > 0.f ? v_ref / lA : 0.f;
+        __nv_bfloat16* dst = a.direct_out + ((size_t)(it.first_row + tokA) * a.n_q_heads + it.head * G + headA) * D;
+#pragma unroll
+        for (int c = 0; c < KS; ++c) {
+          const __nv_bfloat162 p0 = __floats2bfloat162_rn(o[2 * c][0] * f, o[2 * c + 1][0] * f), p1 = __floats2bfloat162_rn(o[2 * c][1] * f, o[2 * c + 1][1] * f);
+          *reinterpret_cast<uint2*>(dst + 16 * c + 4 * t) = make_uint2(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1));
+        }
+      }
+      if (onB) {
+        const float f = lB > 0.f ? v_ref / lB : 0.f;
+        __nv_bfloat16* dst = a.direct_out + ((size_t)(it.first_row + tokB) * a.n_q_heads + it.head * G + headB) * D;
+#pragma unroll
+        for (int c = 0; c < KS; ++c) {
+          const __nv_bfloat162 p0 = __floats2bfloat162_rn(o[2 * c][2] * f, o[2 * c + 1][2] * f), p1 = __floats2bfloat162_rn(o[2 * c][3] * f, o[2 * c + 1][3] * f);
+          *reinterpret_cast<uint2*>(dst + 16 * c + 4 * t) = make_uint2(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1));
+        }
+      }
+      continue;
+    }
     if (onA) {
       const size_t pidx = (size_t)(it.slot0 + tokA) * a.n_q_heads + it.head * G + headA;
 #pragma unroll
@@ -1463,6 +1527,7 @@ b200_status launch_attn_prefill(const b200_kv* kv, const AttnArgs& a, void* d_ou
   const int ctas_per_sm = smem <= 100 * 1024 ? 2 : 1;
   paged_attn_prefill_kernel<D><<<sms * ctas_per_sm, kMmaWarps * 32, smem, s>>>(kv->kmap, kv->vmap, a);
   B200_LAUNCH_CHECK();
+  if (a.direct_out) return B200_OK;  // one chunk per group: the kernel wrote the rows itself
   attn_combine_groups_kernel<D><<<a.total_rows * a.n_q_heads, D, 0, s>>>(a, (__nv_bfloat16*)d_out);
   B200_LAUNCH_CHECK();
   return B200_OK;
@@ -1478,6 +1543,7 @@ b200_status launch_attn_prefill_fp8(const b200_kv* kv, const AttnArgs& a, void* 
   }
   paged_attn_prefill_fp8_kernel<<<sms * 2, kMmaWarps * 32, smem, s>>>(kv->kmap, kv->vmap, a);
   B200_LAUNCH_CHECK();
+  if (a.direct_out) return B200_OK;  // one chunk per group: the kernel wrote the rows itself
   attn_combine_groups_kernel<128><<<a.total_rows * a.n_q_heads, 128, 0, s>>>(a, (__nv_bfloat16*)d_out);
   B200_LAUNCH_CHECK();
   return B200_OK;
@@ -1488,11 +1554,13 @@ int g_sm_count = 0;
 }  // namespace
 
 extern int b200_attn_pages_per_chunk;
+extern int b200_attn_prefill_direct;
 extern int b200_attn_path;
 
 // Pages per chunk chosen so that the persistent grid sees several items per CTA without making
 // the per-item partials a visible share of the traffic.
 int b200_attn_pages_per_chunk = 8;
+int b200_attn_prefill_direct = 1;  // tuning hook for tests: 0 keeps the chunked prefill path at every size
 int b200_attn_path = 0;  // 0 = automatic, 1 = CUDA-core kernel, 2 = tensor-core kernel
 
 extern "C" b200_status b200_paged_attn_decode(b200_kv* kv, int32_t layer, const void* d_q, const int32_t* d_row_seq,
@@ -1570,8 +1638,11 @@ b200_status b200_paged_attn_prefill_strided(b200_kv* kv, int32_t layer, const vo
     B200_CUDA_TRY(cudaGetDevice(&dev));
     B200_CUDA_TRY(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
-  // prefill batches have rows to spare for parallelism: long chunks keep the split-K partials small
-  const int ppc = total_rows >= 2048 ? kMaxChunkPages : std::min(std::max(b200_attn_pages_per_chunk, 4), kMaxChunkPages);
+  // Prefill batches of 1024 rows and more have rows to spare for parallelism (256 groups x kv heads and up): one chunk
+  // per group, as long as its context, and the kernel writes the normalised rows itself: no f32 partials, no combine
+  // pass (at 8192 rows of config 5 the partials were 400 MB per layer and the combine pass 7 % of the scenario).
+  const bool single_chunk = total_rows >= 1024 && b200_attn_prefill_direct;
+  const int ppc = single_chunk ? std::max(c.max_pages_per_seq, 1) : std::min(std::max(b200_attn_pages_per_chunk, 4), kMaxChunkPages);
   const int stride = c.max_rows + 2;
   AttnArgs a;
   a.d = kv->dev; a.layer = layer; a.q = (const __nv_bfloat16*)d_q; a.q_stride = q_stride; a.row_seq = d_row_seq; a.row_ctx = d_row_ctx;
@@ -1581,6 +1652,7 @@ b200_status b200_paged_attn_prefill_strided(b200_kv* kv, int32_t layer, const vo
   a.group_first = kv->d_groups; a.part_base = kv->d_groups + stride; a.row_group = kv->d_groups + 2 * stride;
   a.n_groups = kv->d_groups + 3 * stride - 1;  // last word of the row_group array (never a row index)
   a.q_tokens = 16 / G;
+  a.direct_out = single_chunk ? (__nv_bfloat16*)d_out : nullptr;
   if (!reuse_plan) {
     attn_plan_groups_kernel<<<1, 1024, 0, s>>>(d_row_seq, d_row_ctx, total_rows, c.page_size, ppc, a.q_tokens, kv->d_chunk_start,
                                                kv->d_groups, kv->d_groups + stride, kv->d_groups + 2 * stride,
@@ -1593,5 +1665,6 @@ b200_status b200_paged_attn_prefill_strided(b200_kv* kv, int32_t layer, const vo
 
 // Tuning hook (not part of the reference surface): pages per split-K chunk, 4..32.
 extern "C" void b200_set_attn_pages_per_chunk(int32_t n) { b200_attn_pages_per_chunk = n; }
+extern "C" void b200_set_attn_prefill_direct(int32_t on) { b200_attn_prefill_direct = on; }
 // Tuning hook: 0 = automatic (tensor-core kernel for bf16 pools), 1 = force the CUDA-core kernel.
 extern "C" void b200_set_attn_path(int32_t p) { b200_attn_path = p; }

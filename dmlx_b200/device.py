@@ -212,6 +212,10 @@ def set_attn_pages_per_chunk(n: int):
     lib.b200_set_attn_pages_per_chunk(n)
 
 
+def set_attn_prefill_direct(on: bool):
+    lib.b200_set_attn_prefill_direct(1 if on else 0)
+
+
 def launch_count() -> int:
     """Kernels launched by the library in this process so far."""
     return int(lib.b200_launch_count())

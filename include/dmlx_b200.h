@@ -315,6 +315,10 @@ b200_status b200_paged_attn_prefill(b200_kv* kv, int32_t layer, const void* d_q,
 
 /* Tuning hook with no reference counterpart: pages per split-K chunk (4..32, default 8). */
 void b200_set_attn_pages_per_chunk(int32_t n);
+/* Tuning hook with no reference counterpart: b200_paged_attn_prefill serves batches of 1024 rows and more
+ * with one chunk per group of rows and writes the normalised rows itself (default, 1); 0 keeps the chunked
+ * path with f32 partials and a combine pass at every size (tests compare the two). */
+void b200_set_attn_prefill_direct(int32_t on);
 /* Tuning hook: 0 = automatic (tensor-core kernel for bf16 pools), 1 = force the CUDA-core kernel. */
 void b200_set_attn_path(int32_t path);
 

@@ -183,6 +183,56 @@ def test_prefill_groups_match_oracle_and_row_kernel(hq, hkv, d, kv_dtype):
     kv.close()
 
 
+@pytest.mark.parametrize("hq,hkv,d,kv_dtype", [(32, 8, 128, 0), (32, 8, 128, 1), (8, 2, 64, 0)])
+def test_prefill_batches_of_1024_rows_and_more_write_their_rows_directly(hq, hkv, d, kv_dtype):
+    """From 1024 rows on b200_paged_attn_prefill gives every group of rows one chunk as long as its context
+    and the kernel normalises and writes the rows itself.  Chunks that start inside a cached prefix, contexts
+    over more than 32 pages, plus decode rows in the same batch.  A sample of rows against the oracle, every
+    row against the chunked path (partials + combine pass) on the same pool."""
+    from dmlx_b200 import device as dev
+
+    rng = np.random.default_rng(91 + hq + d + kv_dtype)
+    reqs = [(0, 520), (700, 333), (1500, 1), (64, 200), (2100, 1), (31, 47)]   # 1102 rows
+    totals = [c + n for c, n in reqs]
+    n_pages = sum(-(-t // 32) for t in totals) + 4
+    n_rows = sum(n for _, n in reqs)
+    assert n_rows >= 1024
+    kv = dev.PagedKVCache(1, hkv, d, n_pages, len(reqs), -(-max(totals) // 32), hq, max_rows=max(totals) + n_rows,
+                          attn_scratch_chunks=8192, kv_dtype=kv_dtype)
+    kv.set_free_order(rng.permutation(n_pages).tolist())
+    ks = [ref_math.bf16_round(rng.normal(0, 1, (t, hkv, d)).astype(np.float32)) for t in totals]
+    vs = [ref_math.bf16_round(rng.normal(0, 1, (t, hkv, d)).astype(np.float32)) for t in totals]
+    kv.reserve(dev.pack_desc_array([(s, t, 0, -1) for s, t in enumerate(totals)]).cuda())
+    kv.append(0, torch.tensor(np.concatenate(ks), device="cuda").bfloat16(), torch.tensor(np.concatenate(vs), device="cuda").bfloat16())
+    if kv_dtype != 0:
+        eff = [kv.gather(0, s) for s in range(len(reqs))]
+        ks = [a.float().cpu().numpy() for a, _ in eff]
+        vs = [b.float().cpu().numpy() for _, b in eff]
+    q = ref_math.bf16_round(rng.normal(0, 1, (n_rows, hq, d)).astype(np.float32))
+    row_seq = np.concatenate([np.full(n, s, np.int32) for s, (_, n) in enumerate(reqs)])
+    row_ctx = np.concatenate([np.arange(c + 1, c + n + 1, dtype=np.int32) for c, n in reqs])
+    qd, rs, rc = torch.tensor(q, device="cuda").bfloat16(), torch.tensor(row_seq, device="cuda"), torch.tensor(row_ctx, device="cuda")
+    launches = dev.launch_count()
+    got = kv.attention(0, qd, rs, rc, prefill=True).float().cpu().numpy()
+    direct_launches = dev.launch_count() - launches
+    assert kv.error_word() == 0
+    try:
+        dev.set_attn_prefill_direct(False)
+        launches = dev.launch_count()
+        chunked = kv.attention(0, qd, rs, rc, prefill=True).float().cpu().numpy()
+        assert dev.launch_count() - launches == direct_launches + 1   # the combine pass
+    finally:
+        dev.set_attn_prefill_direct(True)
+    assert kv.error_word() == 0
+    assert np.abs(got - chunked).max() <= 1e-2 * np.abs(chunked).max()
+    for r in list(range(0, n_rows, 37)) + [519, 520, 852, 853, 854, 1053, 1054, n_rows - 1]:
+        s, c = int(row_seq[r]), int(row_ctx[r])
+        want = ref_math.gqa_attention_decode(q[r], ks[s][:c], vs[s][:c])
+        rel, cos = _close(got[r], want)
+        assert rel <= REL_TOL and cos >= COS_TOL, (r, s, c, rel, cos)
+    kv.close()
+
+
 @pytest.mark.parametrize("kv_dtype", [0, 1])  # bf16 pool, FP8-E4M3 pool (tensor-core kernels, head_dim 128)
 def test_long_contexts_of_the_attention_microbench(kv_dtype):
     """Three sequences drawn from the attention microbench's range (log-uniform 128..32768 tokens, 32
