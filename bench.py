@@ -230,6 +230,8 @@ def run_llama(args, rank, world, local):
                            max_rows=max(n_req, 16, (args.step_tokens + 256) if do_arrivals else 0), max_reqs=max(n_req, 256 if do_arrivals else 0),
                            max_seqs=max(n_req, 256 if do_arrivals else 0), rms_eps=1e-5, rope_theta=500000.0)
     model.random_init(dev.Q_AFFINE4_G64, seed=7 + rank)
+    if getattr(args, "unfused_qkv_rope", False):
+        model.set_fused_qkv_rope(False)
     # live-batch snapshot: every request already holds `ctx` cached tokens in every layer
     kv.reserve(dev.pack_desc_array([(s, int(n), 0, -1) for s, n in enumerate(ctxs)]).cuda())
     g = torch.Generator(device="cuda").manual_seed(5 + rank)
@@ -1097,6 +1099,8 @@ def main():
     ap.add_argument("--seqs", type=int, default=64, help="sequences per GPU (64 = the configuration; fewer for profiling)")
     ap.add_argument("--mx-persistent", type=int, default=-1, help="block-scaled MXFP4 path: 1 persistent CTAs over work items, 0 one CTA per item (default: library choice)")
     ap.add_argument("--no-arrivals", action="store_true", help="llama8b_int4 only: skip the arrival-process scenarios")
+    ap.add_argument("--unfused-qkv-rope", action="store_true",
+                    help="llama8b_int4 snapshot step only: keep the q/k/v projection's own finish pass (A/B of the fused RoPE + append)")
     ap.add_argument("--no-ep", action="store_true", help="llama8b_int4 on several GPUs only: skip the expert-parallel MoE measurement")
     ap.add_argument("--arrival-scenarios", default="both", help="poisson_20rps | saturation | saturation_large_pool | both (= all three)")
     ap.add_argument("--pool-pages", type=int, default=3072, help="arrival scenarios: KV pages per replica (32 tokens x 32 layers x 4 KiB each)")

@@ -209,6 +209,15 @@ _sig("b200_llama_enable_graphs", None, vp, i32)
 _sig("b200_llama_profile_collect", i32, vp, P(C.c_double), P(C.c_int64))
 
 
+class QmmPartials(C.Structure):
+    _fields_ = [("d_ws", vp)] + [(n, i32) for n in ("splits", "tn", "tts", "nt", "rows", "n", "pending")]
+
+
+_sig("b200_qmm_deferred", i32, vp, vp, i32, vp, i32, vp, P(QmmPartials))
+_sig("b200_kv_rope_append_partials", i32, vp, i32, P(QmmPartials), vp, i32, vp, vp, i32, i32, f32, vp)
+_sig("b200_llama_set_fused_qkv_rope", None, vp, i32)
+
+
 class MoeConfig(C.Structure):
     _fields_ = [(n, i32) for n in ("hidden", "n_experts", "inter", "top_k", "scoring", "tile_rows", "max_tokens")] + \
                [("route_scale", f32), ("swiglu_limit", f32), ("shared_swiglu_limit", f32), ("ep_rank", i32), ("ep_world", i32)]

@@ -733,6 +733,85 @@ extern "C" b200_status b200_kv_rope_append(b200_kv* kv, int32_t layer, void* d_q
                                      total_rows, n_q_heads, theta, stream);
 }
 
+// RoPE + append fed from the split-K partial sums of the fused q/k/v projection (head_dim 128 = one 128-row weight
+// tile per head).  One warp per (row, head): the lane's four columns (two rotation pairs) are summed over the splits
+// in split order and rounded to bf16 as the matmul's finish pass would have done, then rotated and stored: q into the
+// activation buffer, k and v into the row's page.
+__global__ void __launch_bounds__(256) rope_append_partials_bf16_kernel(KvDev d, int layer, b200_qmm_partials p, __nv_bfloat16* __restrict__ q,
+                                                                        int q_stride, const int* __restrict__ positions,
+                                                                        const int* __restrict__ row_seq, int hq, float log2_theta) {
+  constexpr int D = 128, half = 64;
+  const int row = blockIdx.x, H = d.n_kv_heads;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pos = positions[row], seq = row_seq[row];
+  const int page_idx = pos / d.page_size, slot = pos - page_idx * d.page_size;
+  // a step whose reservation failed has no page for this row: nothing is written (the error word is set)
+  const bool have_page = seq >= 0 && seq < d.max_seqs && page_idx < d.seq_pages[seq];
+  const int page = have_page ? d.block_table[(size_t)seq * d.max_pages_per_seq + page_idx] : 0;
+  const int tt = row / p.tn, tr = row - tt * p.tn;
+  const size_t split_stride = (size_t)p.tn * 128;
+  for (int h = blockIdx.y * 8 + warp; h < hq + 2 * H; h += 8 * gridDim.y) {
+    const float* base = p.d_ws + (((size_t)(h * p.tts + tt) * p.splits) * p.tn + tr) * 128;
+    if (h < hq + H) {
+      // columns 2*lane, 2*lane+1 and their partners 64 further on
+      float2 lo = make_float2(0.f, 0.f), hi = make_float2(0.f, 0.f);
+      for (int s = 0; s < p.splits; ++s) {
+        const float2 a = *reinterpret_cast<const float2*>(base + (size_t)s * split_stride + 2 * lane);
+        const float2 b = *reinterpret_cast<const float2*>(base + (size_t)s * split_stride + half + 2 * lane);
+        lo.x += a.x; lo.y += a.y; hi.x += b.x; hi.y += b.y;
+      }
+      const float x1[2] = {__bfloat162float(__float2bfloat16(lo.x)), __bfloat162float(__float2bfloat16(lo.y))};
+      const float x2[2] = {__bfloat162float(__float2bfloat16(hi.x)), __bfloat162float(__float2bfloat16(hi.y))};
+      __nv_bfloat16* dst = nullptr;
+      if (h < hq) dst = q + (size_t)row * q_stride + (size_t)h * D;
+      else if (have_page)
+        dst = (__nv_bfloat16*)d.k_pool + ((((size_t)layer * d.n_pages + page) * H + (h - hq)) * d.page_size + slot) * (size_t)D;
+      float o1[2], o2[2];
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int i = lane * 2 + j;
+        float sn, cs;
+        sincosf((float)pos * exp2f(-log2_theta * (2.0f * i) / (float)D), &sn, &cs);
+        o1[j] = x1[j] * cs - x2[j] * sn;
+        o2[j] = x1[j] * sn + x2[j] * cs;
+      }
+      if (dst) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + 2 * lane) = __floats2bfloat162_rn(o1[0], o1[1]);
+        *reinterpret_cast<__nv_bfloat162*>(dst + half + 2 * lane) = __floats2bfloat162_rn(o2[0], o2[1]);
+      }
+    } else {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < p.splits; ++s) {
+        const float4 a = *reinterpret_cast<const float4*>(base + (size_t)s * split_stride + 4 * lane);
+        acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+      }
+      if (have_page) {
+        __nv_bfloat16* dst = (__nv_bfloat16*)d.v_pool + ((((size_t)layer * d.n_pages + page) * H + (h - hq - H)) * d.page_size + slot) * (size_t)D;
+        const __nv_bfloat162 a0 = __floats2bfloat162_rn(acc.x, acc.y), a1 = __floats2bfloat162_rn(acc.z, acc.w);
+        *reinterpret_cast<uint2*>(dst + 4 * lane) = make_uint2(*reinterpret_cast<const uint32_t*>(&a0), *reinterpret_cast<const uint32_t*>(&a1));
+      }
+    }
+  }
+}
+
+extern "C" b200_status b200_kv_rope_append_partials(b200_kv* kv, int32_t layer, const b200_qmm_partials* parts, void* d_q, int32_t q_stride,
+                                                    const int32_t* d_positions, const int32_t* d_row_seq, int32_t total_rows,
+                                                    int32_t n_q_heads, float theta, void* stream) {
+  const b200_kv_config& c = kv->cfg;
+  if (c.kv_dtype != B200_KV_BF16 || c.head_dim != 128) { b200_set_error("rope+append from partial sums: bf16 pools with head_dim 128 only"); return B200_ERR_UNSUPPORTED; }
+  if (!parts || !parts->pending || !parts->d_ws || parts->rows != total_rows || parts->n != (n_q_heads + 2 * c.n_kv_heads) * 128 ||
+      parts->nt * 128 != parts->n || parts->tn <= 0 || parts->tts != (total_rows + parts->tn - 1) / parts->tn || parts->splits <= 0) {
+    b200_set_error("rope+append from partial sums: the partial sums do not describe a q/k/v projection of %d rows", total_rows);
+    return B200_ERR_INVALID_ARGUMENT;
+  }
+  if (layer < 0 || layer >= c.n_layers) { b200_set_error("append: layer %d out of range", layer); return B200_ERR_INVALID_ARGUMENT; }
+  if (total_rows <= 0) return B200_OK;
+  rope_append_partials_bf16_kernel<<<dim3(total_rows, (n_q_heads + 2 * c.n_kv_heads + 7) / 8), 256, 0, (cudaStream_t)stream>>>(
+      kv->dev, layer, *parts, (__nv_bfloat16*)d_q, q_stride, d_positions, d_row_seq, n_q_heads, log2f(theta));
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
 // RoPE + append for a bf16 pool in one launch (model step); other pools take the two-kernel route.
 b200_status b200_kv_rope_append_strided(b200_kv* kv, int32_t layer, void* d_q, const void* d_k_rows, const void* d_v_rows,
                                         int32_t q_stride, int32_t k_stride, int32_t v_stride, const int32_t* d_positions,

@@ -62,6 +62,7 @@ struct b200_llama {
   // first step of a shape runs eagerly (it may grow scratch buffers), the second is captured,
   // later ones replay the graph.
   bool graphs_on = true;
+  bool fuse_qkv_rope = true;  // b200_llama_set_fused_qkv_rope
   struct GraphEntry { int seen = 0; cudaGraphExec_t exec = nullptr; long long kernels = 0; };
   std::map<std::tuple<int, const void*, const void*, void*, bool>, GraphEntry> graphs;
   // optional CUDA-event timing per category: 0 attention, 1 matmuls, 2 rope + KV append, 3 the rest
@@ -361,13 +362,21 @@ static b200_status llama_forward_eager(b200_llama* m, b200_kv* kv, const b200_pa
                        m->d_row_seq, m->d_row_ctx, m->d_last_row, T, stream));
   STEP(b200_kv_reserve(kv, d_desc, n_req, stream));
   STEP(b200_embed_gather(m->embed, m->d_tokens, m->x, T, c.hidden, stream));
+  const int fuse_qkv = (m->fuse_qkv_rope && kv->cfg.kv_dtype == B200_KV_BF16 && c.head_dim == 128) ? 1 : 0;
   // The o and down projections also write the RMSNorm their result feeds (fused into their split-K
   // finish pass), so only the first layer normalises x on its own.
   for (int l = 0; l < c.n_layers; ++l) {
     if (l == 0) STEP(b200_rmsnorm(m->x, m->attn_norm[l], m->h, T, c.hidden, c.rms_eps, stream));
-    STEP_CAT(1, b200_qmm(m->wqkv[l], m->h, T, m->qkv, B200_EPI_NONE, nullptr, 0.f, B200_QMM_AUTO, stream));
-    STEP_CAT(2, b200_kv_rope_append_strided(kv, l, m->qkv, m->qkv + qd, m->qkv + qd + kd, qkv_dim, qkv_dim, qkv_dim, m->d_pos,
-                                            m->d_row_seq, T, c.n_heads, c.rope_theta, stream));
+    // When the q/k/v projection splits K, its partial sums go straight to RoPE + append (bf16 pools, head_dim 128):
+    // same bits, one launch and one pass over the projection's output less.
+    b200_qmm_partials parts;
+    STEP_CAT(1, b200_qmm_deferred(m->wqkv[l], m->h, T, m->qkv, fuse_qkv, stream, &parts));
+    if (parts.pending) {
+      STEP_CAT(2, b200_kv_rope_append_partials(kv, l, &parts, m->qkv, qkv_dim, m->d_pos, m->d_row_seq, T, c.n_heads, c.rope_theta, stream));
+    } else {
+      STEP_CAT(2, b200_kv_rope_append_strided(kv, l, m->qkv, m->qkv + qd, m->qkv + qd + kd, qkv_dim, qkv_dim, qkv_dim, m->d_pos,
+                                              m->d_row_seq, T, c.n_heads, c.rope_theta, stream));
+    }
     // batches that hold prefill chunks (more rows than requests) take the grouped kernel
     if (T > n_req) { STEP_CAT(0, b200_paged_attn_prefill_strided(kv, l, m->qkv, qkv_dim, m->d_row_seq, m->d_row_ctx, T, m->attn, stream, l > 0)); }
     else { STEP_CAT(0, b200_paged_attn_decode_strided(kv, l, m->qkv, qkv_dim, m->d_row_seq, m->d_row_ctx, T, m->attn, stream, l > 0)); }
@@ -471,6 +480,11 @@ b200_status b200_llama_last_logits(b200_llama* m, void* h_bf16_out, int32_t n_re
 
 int64_t b200_llama_launch_count(const b200_llama* m) { return m->launches; }
 void b200_llama_enable_graphs(b200_llama* m, int32_t on) { m->graphs_on = on != 0; }
+void b200_llama_set_fused_qkv_rope(b200_llama* m, int32_t on) {
+  m->fuse_qkv_rope = on != 0;
+  // graphs captured with the other setting hold the other kernels
+  for (auto& g : m->graphs) if (g.second.exec) { cudaGraphExecDestroy(g.second.exec); g.second.exec = nullptr; g.second.seen = 0; }
+}
 
 // CUDA-event timing of the step's kernels by category (0 attention, 1 matmuls, 2 rope + KV append,
 // 3 the rest).  collect() synchronises the device, adds the elapsed time of every recorded call

@@ -2241,6 +2241,12 @@ extern "C" void b200_qweight_destroy(b200_qweight* w) {
 // ---- launch -------------------------------------------------------------------------------------------
 // Sets a.did_norm when the finish pass also wrote the requested RMSNorm.
 static b200_status launch_finish(QmmArgs& a, int splits, cudaStream_t s) {
+  if (a.defer && a.epilogue == B200_EPI_NONE && !a.items && !a.row_scales && !a.norm_w) {
+    // the caller's next kernel sums the splits (b200_kv_rope_append_partials)
+    a.defer->d_ws = a.ws; a.defer->splits = splits; a.defer->tn = a.tn; a.defer->tts = (a.rows + a.tn - 1) / a.tn;
+    a.defer->nt = a.nt; a.defer->rows = a.rows; a.defer->n = a.n; a.defer->pending = 1;
+    return B200_OK;
+  }
   // (decode-sized batches only: one CTA per row does not beat the two separate kernels on prefill chunks)
   if (a.norm_w && a.rows <= 256 && a.epilogue == B200_EPI_RESIDUAL && !a.items && !a.row_scales && a.n % 4 == 0 && a.n <= 16384) {
     int threads = ((a.n / 4 + 31) / 32) * 32;
@@ -2682,6 +2688,18 @@ extern "C" b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t 
   return qmm_entry(w, d_x, rows, d_y, epilogue, d_residual, swiglu_limit, path, stream, nullptr, 0.f, nullptr, nullptr);
 }
 
+// Set by b200_qmm_deferred around its call of qmm_entry (one calling thread per process uses the matmul entry points).
+static b200_qmm_partials* g_defer_target = nullptr;
+
+extern "C" b200_status b200_qmm_deferred(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t defer, void* stream,
+                                         b200_qmm_partials* out) {
+  std::memset(out, 0, sizeof(*out));
+  g_defer_target = defer ? out : nullptr;
+  const b200_status st = qmm_entry(w, d_x, rows, d_y, B200_EPI_NONE, nullptr, 0.f, B200_QMM_AUTO, stream, nullptr, 0.f, nullptr, nullptr);
+  g_defer_target = nullptr;
+  return st;
+}
+
 extern "C" b200_status b200_rmsnorm(const void* d_x, const void* d_weight, void* d_out, int32_t rows, int32_t hidden, float eps,
                                     void* stream);
 
@@ -2749,6 +2767,7 @@ static b200_status qmm_entry(const b200_qweight* w, const void* d_x, int32_t row
   a.residual = (const __nv_bfloat16*)d_residual;
   a.rows = rows; a.n = w->n; a.k = w->k; a.nt = w->nt; a.kc = w->kc; a.epilogue = epilogue; a.swiglu_limit = swiglu_limit;
   a.norm_w = (const __nv_bfloat16*)d_norm_w; a.norm_out = (__nv_bfloat16*)d_norm_out; a.norm_eps = norm_eps;
+  a.defer = g_defer_target;
   cudaStream_t s = (cudaStream_t)stream;
   auto dispatch = [&]() -> b200_status {
     if (path == B200_QMM_MXFP4_BLOCK_SCALED) return launch_mx(w, a, rows, s);

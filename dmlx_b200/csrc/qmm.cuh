@@ -51,6 +51,7 @@ struct QmmArgs {
   int mx_expert_rows;           // rows of the code matrix per expert (nt * 128)
   int kc128;                    // K / 128
   int did_norm;                 // host only: the finish pass also wrote norm_out
+  b200_qmm_partials* defer = nullptr;  // when set, a dense launch with epilogue NONE leaves its finish pass to the caller
 
   __device__ __forceinline__ int row_base_out(int token) const { return token; }
   __device__ __forceinline__ float row_scale(int token) const { return row_scales ? row_scales[token] : 1.0f; }

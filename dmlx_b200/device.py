@@ -134,6 +134,12 @@ class PagedKVCache:
         _lib.check(lib.b200_kv_rope_append(self._h, layer, _ptr(q), _ptr(k_rows), _ptr(v_rows), _ptr(positions), _ptr(row_seq),
                                            q.shape[0], q.shape[1], theta, _stream()))
 
+    def rope_append_partials(self, layer: int, parts, q_buf: torch.Tensor, q_stride: int, positions: torch.Tensor, row_seq: torch.Tensor,
+                             n_q_heads: int, theta: float = 10000.0):
+        """b200_kv_rope_append_partials: RoPE + append fed from the split-K partial sums of the q/k/v projection."""
+        _lib.check(lib.b200_kv_rope_append_partials(self._h, layer, C.byref(parts), _ptr(q_buf), q_stride, _ptr(positions), _ptr(row_seq),
+                                                    positions.shape[0], n_q_heads, theta, _stream()))
+
     def append(self, layer: int, k_rows: torch.Tensor, v_rows: torch.Tensor):
         assert k_rows.dtype == torch.bfloat16 and v_rows.dtype == torch.bfloat16
         _lib.check(lib.b200_kv_append(self._h, layer, _ptr(k_rows), _ptr(v_rows), k_rows.shape[0], _stream()))
@@ -336,6 +342,13 @@ class QWeight:
             self._h = None
 
 
+def qmm_deferred(w: "QWeight", x: torch.Tensor, out: torch.Tensor, defer: bool = True):
+    """b200_qmm_deferred: the matmul with its split-K finish pass left to the caller; returns the partial-sum record."""
+    parts = _lib.QmmPartials()
+    _lib.check(lib.b200_qmm_deferred(w._h, _ptr(x), x.shape[0], _ptr(out), 1 if defer else 0, _stream(), C.byref(parts)))
+    return parts
+
+
 def qmm(w: QWeight, x: torch.Tensor, epilogue: int = EPI_NONE, residual: Optional[torch.Tensor] = None,
         swiglu_limit: float = 0.0, path: int = QMM_AUTO, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """b200_qmm: y = x . dequant(W)^T with a fused epilogue."""
@@ -446,6 +459,9 @@ class LlamaModel:
 
     def enable_graphs(self, on: bool = True):
         lib.b200_llama_enable_graphs(self._h, int(on))
+
+    def set_fused_qkv_rope(self, on: bool = True):
+        lib.b200_llama_set_fused_qkv_rope(self._h, int(on))
 
     def profile_enable(self, on: bool = True):
         lib.b200_llama_profile_enable(self._h, int(on))

@@ -276,6 +276,23 @@ b200_status b200_kv_append(b200_kv* kv, int32_t layer, const void* d_k_rows, con
 b200_status b200_kv_rope_append(b200_kv* kv, int32_t layer, void* d_q, void* d_k_rows, const void* d_v_rows,
                                 const int32_t* d_positions, const int32_t* d_row_seq, int32_t total_rows,
                                 int32_t n_q_heads, float theta, void* stream);
+/* The split-K partial sums of a matmul whose finish pass was left to the next kernel (b200_qmm_deferred):
+ * f32 tiles [weight tile of 128 rows][token tile][split][tn tokens][128] in the library's matmul scratch, valid
+ * until the next matmul on the stream.  pending = 0: nothing was deferred, y holds the result. */
+typedef struct b200_qmm_partials {
+  const float* d_ws;
+  int32_t splits, tn, tts, nt, rows, n, pending;
+} b200_qmm_partials;
+/* b200_kv_rope_append fed from the partial sums of the fused q/k/v projection (no reference counterpart: the
+ * seam between src/models/llama.zig:206-215 and the cache update, one launch less per layer): sums the K
+ * splits in split order, rounds to bf16 exactly as the matmul's own finish pass would, rotates q and k, writes q
+ * [T, n_q_heads, head_dim] into d_q (row stride q_stride elements) and the rotated k and v rows into their
+ * pages.  Same bits as b200_qmm followed by b200_kv_rope_append.  bf16 pools with head_dim 128, and a
+ * projection with n = (n_q_heads + 2 n_kv_heads) * 128 rows in q, k, v order; anything else returns
+ * B200_ERR_UNSUPPORTED. */
+b200_status b200_kv_rope_append_partials(b200_kv* kv, int32_t layer, const b200_qmm_partials* parts, void* d_q,
+                                         int32_t q_stride, const int32_t* d_positions, const int32_t* d_row_seq,
+                                         int32_t total_rows, int32_t n_q_heads, float theta, void* stream);
 /* Introspection for bit-exact checks (synchronous). */
 b200_status b200_kv_seq_len(b200_kv* kv, int32_t seq, int32_t* out_len);         /* :485-488 */
 b200_status b200_kv_current_len(b200_kv* kv, int32_t* out_len);                  /* :842-849 currentLen */
@@ -415,6 +432,13 @@ b200_status b200_qmm(const b200_qweight* w, const void* d_x, int32_t rows, void*
                      int32_t epilogue, const void* d_residual, float swiglu_limit, int32_t path,
                      void* stream);
 
+/* b200_qmm with epilogue NONE whose split-K finish pass may be left to the caller's next kernel (no reference
+ * counterpart).  defer = 0: exactly b200_qmm.  defer != 0: when the chosen kernel splits K, the finish pass is not
+ * launched, out->pending = 1 and out describes the partial sums (d_y is NOT written); when it does not split K,
+ * d_y is written and out->pending = 0. */
+b200_status b200_qmm_deferred(const b200_qweight* w, const void* d_x, int32_t rows, void* d_y, int32_t defer,
+                              void* stream, b200_qmm_partials* out);
+
 /* y = residual + x W^T and normed = rmsnorm(y) * norm_weight in one call: the pair that closes the
  * attention and the FFN half of a block (src/models/llama.zig:466-477: residual add, then the next
  * RMSNorm).  When the matmul splits K its finish pass writes both; otherwise the row kernel follows.
@@ -497,6 +521,10 @@ b200_status b200_llama_last_logits(b200_llama* m, void* h_bf16_out, int32_t n_re
 int64_t b200_llama_launch_count(const b200_llama* m);
 /* Decode-only steps are replayed as CUDA graphs by default (on = 0 turns that off). */
 void b200_llama_enable_graphs(b200_llama* m, int32_t on);
+/* The step feeds RoPE + KV append from the q/k/v projection's split-K partial sums where it can
+ * (b200_kv_rope_append_partials; default on).  0 keeps the projection's own finish pass and b200_kv_rope_append
+ * (tests compare the two: same tokens, same pages). */
+void b200_llama_set_fused_qkv_rope(b200_llama* m, int32_t on);
 /* CUDA-event timing of the step's kernels by category (0 attention, 1 matmuls, 2 rope + KV append,
  * 3 the rest); collect() synchronises, fills ms[4] and calls[4], and clears the record.  Stands in
  * for the reference's per-step timing logs (src/models/expert_stream.zig:36-51 TokenStepMetrics). */

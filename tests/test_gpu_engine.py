@@ -593,3 +593,55 @@ def test_prefix_tier_lru_between_pool_and_disk(tmp_path):
     eng.close()
     model.close()
     kv.close()
+
+
+def test_step_with_rope_and_append_fed_from_partial_sums_equals_the_two_kernel_step():
+    """With head_dim 128 and a bf16 pool the model step hands the q/k/v projection's split-K partial sums to
+    RoPE + append (b200_kv_rope_append_partials).  Prefill of three prompts and 12 decode steps, fused against
+    unfused on the same model: same tokens, bit-identical logits of the last step, bit-identical pages."""
+    import torch
+
+    from dmlx_b200 import device as dev
+
+    # int4 weights generated on the device, hidden 2048: the q/k/v projection (1024 x 2048) splits K at these row counts
+    cfg = ref_math.LlamaConfig(n_layers=3, hidden=2048, n_heads=4, n_kv_heads=2, head_dim=128, ffn=1408, vocab=32000)
+    model = dev.LlamaModel(cfg.n_layers, cfg.hidden, cfg.n_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.vocab,
+                           max_rows=1024, max_reqs=16, max_seqs=16, rms_eps=cfg.eps, rope_theta=cfg.theta)
+    model.random_init(dev.Q_AFFINE4_G64, seed=5)
+    rng = np.random.default_rng(3)
+    prompts = [rng.integers(0, cfg.vocab, n).tolist() for n in (45, 130, 7)]
+
+    def run(fused):
+        model.set_fused_qkv_rope(fused)
+        kv = dev.PagedKVCache(cfg.n_layers, cfg.n_kv_heads, cfg.head_dim, 32, 4, 8, cfg.n_heads, max_rows=1024)
+        kv.set_free_order(list(range(32)))
+        off, descs, flat = 0, [], []
+        for s, p in enumerate(prompts):
+            kv.alloc(s, 1)
+            descs.append((s, len(p), 0, off))
+            flat += p
+            off += len(p)
+        before = model.launch_count()
+        toks, _ = model.step(kv, descs, flat)
+        prefill_launches = model.launch_count() - before
+        stream = [list(map(int, toks))]
+        for _ in range(12):
+            d = [(s, 1, kv.seq_len(s), -1) for s in range(len(prompts))]
+            toks, _ = model.step(kv, d, [])
+            stream.append(list(map(int, toks)))
+        logits = model.last_logits(len(prompts)).copy()
+        pages = [[t.view(torch.int16).cpu().numpy() for t in kv.gather(l, s)] for l in range(cfg.n_layers) for s in range(len(prompts))]
+        assert kv.error_word() == 0
+        kv.close()
+        return stream, logits, pages, prefill_launches
+
+    with torch.cuda.stream(torch.cuda.Stream()):  # decode steps replay as graphs on a capturable stream
+        s0, l0, p0, n0 = run(False)
+        s1, l1, p1, n1 = run(True)
+    model.set_fused_qkv_rope(True)
+    assert s0 == s1
+    assert np.array_equal(l0, l1)
+    for (k0, v0), (k1, v1) in zip(p0, p1):
+        assert np.array_equal(k0, k1) and np.array_equal(v0, v1)
+    assert n1 == n0 - cfg.n_layers   # the prefill step: one launch less per layer (the projection's finish pass)
+

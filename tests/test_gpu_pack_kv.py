@@ -378,3 +378,59 @@ def test_rope_append_in_one_call_matches_rope_then_append():
         assert np.array_equal(got_v.float().cpu().numpy(), v[off:off + c])
         off += c
     kv.close()
+
+
+@pytest.mark.parametrize("rows_per_seq", [(5,), (1, 1, 1, 1, 1, 1, 1, 1), (40, 3), (200, 97, 3)])
+def test_rope_append_from_the_projection_partial_sums_gives_the_same_bits(rows_per_seq):
+    """b200_qmm_deferred + b200_kv_rope_append_partials against b200_qmm + b200_kv_rope_append on the same inputs:
+    the q rows and the K and V pages must be bit-identical (the fused kernel sums the K splits in split order and
+    rounds to bf16 where the finish pass would).  Row counts chosen to reach the small-batch kernel, the
+    tensor-memory kernel and a launch with several token tiles."""
+    dev = _dev()
+    rng = np.random.default_rng(5 + sum(rows_per_seq))
+    hq, hkv, d, k = 6, 2, 128, 1024
+    n = (hq + 2 * hkv) * d
+    w = dev.QWeight.random(dev.Q_AFFINE4_G64, n, k, seed=11)
+    t = sum(rows_per_seq)
+    x = torch.tensor(ref_math.bf16_round(rng.normal(0, 1, (t, k))), device="cuda").bfloat16()
+    starts = [int(rng.integers(0, 60)) for _ in rows_per_seq]   # rows continue sequences that already hold tokens
+    pos = np.concatenate([np.arange(s0, s0 + c) for s0, c in zip(starts, rows_per_seq)]).astype(np.int32)
+    seq = np.concatenate([np.full(c, s) for s, c in enumerate(rows_per_seq)]).astype(np.int32)
+    posd, seqd = torch.tensor(pos, device="cuda"), torch.tensor(seq, device="cuda")
+    results = []
+    for fused in (False, True):
+        kv = dev.PagedKVCache(1, hkv, d, 32, len(rows_per_seq), 12, hq, max_rows=512)
+        kv.set_free_order(list(range(32)))
+        for s, s0 in enumerate(starts):
+            if s0 > 0:
+                kv.reserve(dev.pack_desc_array([(s, s0, 0, -1)]).cuda())
+        kv.reserve(dev.pack_desc_array([(s, c, s0, -1) for s, (s0, c) in enumerate(zip(starts, rows_per_seq))]).cuda())
+        qkv = torch.zeros((t, n), dtype=torch.bfloat16, device="cuda")
+        if fused:
+            parts = dev.qmm_deferred(w, x, qkv)
+            assert parts.pending == 1, "this shape is expected to split K"
+            assert parts.rows == t and parts.n == n and parts.nt * 128 == n
+            kv.rope_append_partials(0, parts, qkv, n, posd, seqd, hq, theta=500000.0)
+        else:
+            parts = dev.qmm_deferred(w, x, qkv, defer=False)
+            assert parts.pending == 0
+            qc = qkv[:, : hq * d].contiguous().view(t, hq, d)
+            kc = qkv[:, hq * d: (hq + hkv) * d].contiguous().view(t, hkv, d)
+            vc = qkv[:, (hq + hkv) * d:].contiguous().view(t, hkv, d)
+            kv.rope_append(0, qc, kc, vc, posd, seqd, theta=500000.0)
+            qkv[:, : hq * d] = qc.view(t, hq * d)
+        torch.cuda.synchronize()
+        assert kv.error_word() == 0 and dev.qmm_error_word() == 0
+        q = qkv[:, : hq * d].clone().view(torch.int16).cpu().numpy()
+        pages = []
+        for s, (s0, c) in enumerate(zip(starts, rows_per_seq)):
+            gk, gv = kv.gather(0, s)
+            pages.append((gk[s0:s0 + c].view(torch.int16).cpu().numpy(), gv[s0:s0 + c].view(torch.int16).cpu().numpy()))
+        results.append((q, pages))
+        kv.close()
+    (q0, p0), (q1, p1) = results
+    assert np.array_equal(q0, q1)
+    for (k0, v0), (k1, v1) in zip(p0, p1):
+        assert np.array_equal(k0, k1) and np.array_equal(v0, v1)
+    assert np.abs(q0.astype(np.int32)).max() > 0
+
