@@ -1099,6 +1099,8 @@ def main():
     ap.add_argument("--seqs", type=int, default=64, help="sequences per GPU (64 = the configuration; fewer for profiling)")
     ap.add_argument("--mx-persistent", type=int, default=-1, help="block-scaled MXFP4 path: 1 persistent CTAs over work items, 0 one CTA per item (default: library choice)")
     ap.add_argument("--no-arrivals", action="store_true", help="llama8b_int4 only: skip the arrival-process scenarios")
+    ap.add_argument("--attn-pages-per-chunk", type=int, default=0,
+                    help="tuning: pages per split-K chunk of the decode attention (0 = the library's default)")
     ap.add_argument("--unfused-qkv-rope", action="store_true",
                     help="llama8b_int4 snapshot step only: keep the q/k/v projection's own finish pass (A/B of the fused RoPE + append)")
     ap.add_argument("--no-ep", action="store_true", help="llama8b_int4 on several GPUs only: skip the expert-parallel MoE measurement")
@@ -1107,6 +1109,9 @@ def main():
     ap.add_argument("--prefill-chunk", type=int, default=512, help="arrival scenarios: prefill chunk (tokens)")
     ap.add_argument("--step-tokens", type=int, default=2048, help="arrival scenarios: token budget of one engine step")
     args = ap.parse_args()
+    if args.attn_pages_per_chunk > 0:
+        from dmlx_b200 import device as _dev
+        _dev.set_attn_pages_per_chunk(args.attn_pages_per_chunk)
     if args.steps is None:
         args.steps = 10 if args.impl == "reference" else (150 if args.workload.startswith("llama") else (20 if args.workload.startswith(("moe", "qmm")) else (2 if args.workload.startswith("prefix") else 500)))
     rank = int(os.environ.get("RANK", "0"))

@@ -54,14 +54,43 @@ struct AttnArgs {
   // prefill path with one chunk per group (a chunk long enough for any context): the kernel normalises and writes
   // the rows itself, no partials and no combine pass
   __nv_bfloat16* direct_out = nullptr;
+  // decode path: pages per chunk as the plan kernel chose it for this batch (else pages_per_chunk holds it)
+  const int* ppc_dev = nullptr;
 };
 
+__device__ __forceinline__ int attn_pages_per_chunk(const AttnArgs& a) { return a.ppc_dev ? *a.ppc_dev : a.pages_per_chunk; }
+
+// pages_per_chunk <= 0: the kernel picks the chunk length from the batch's mean context, 8 pages below 96 pages per
+// row, 16 below 192, 32 above.  Short chunks give the persistent grid more items to balance; with long contexts the
+// partial sums and the combine pass's walk over a row's chunks cost more than the balance gains (256 requests of
+// ~47 pages: 12.8 ms per step at 8 pages per chunk against 13.1 at 16; 64 requests of ~250 pages: 0.338 ms per
+// launch at 32 against 0.377 at 8).  The choice is written to *ppc_out for the kernels that follow.
 __global__ void attn_plan_kernel(const int* __restrict__ row_ctx, int total_rows, int page_size, int pages_per_chunk,
-                                 int* __restrict__ chunk_start, int max_chunks, int* __restrict__ err) {
+                                 int* __restrict__ chunk_start, int max_chunks, int* __restrict__ err, int* __restrict__ ppc_out) {
   __shared__ int warp_sums[32];
   __shared__ int carry;
+  __shared__ int s_ppc;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) carry = 0;
+  if (pages_per_chunk <= 0) {
+    long long pages = 0;
+    for (int i = tid; i < total_rows; i += blockDim.x) pages += (max(row_ctx[i], 0) + page_size - 1) / page_size;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) pages += __shfl_xor_sync(0xffffffffu, pages, o);
+    if (lane == 0) warp_sums[warp] = (int)min(pages, (long long)0x7fffffff / 64);
+    __syncthreads();
+    if (tid == 0) {
+      long long total = 0;
+      for (int w = 0; w < (int)(blockDim.x >> 5); ++w) total += warp_sums[w];
+      const long long mean = total / max(total_rows, 1);
+      s_ppc = mean < 96 ? 8 : (mean < 192 ? 16 : 32);
+    }
+  } else if (tid == 0) {
+    s_ppc = pages_per_chunk;
+  }
+  __syncthreads();
+  pages_per_chunk = s_ppc;
+  if (tid == 0) *ppc_out = pages_per_chunk;
   __syncthreads();
   for (int base = 0; base < total_rows; base += blockDim.x) {
     int i = base + tid;
@@ -120,8 +149,9 @@ __device__ __forceinline__ Item decode_item(const AttnArgs& a, int item) {
   it.ctx = a.row_ctx[lo];
   int c = it.chunk - a.chunk_start[lo];
   int npages = (it.ctx + a.d.page_size - 1) / a.d.page_size;
-  it.page_begin = c * a.pages_per_chunk;
-  it.page_end = min(it.page_begin + a.pages_per_chunk, npages);
+  const int ppc = attn_pages_per_chunk(a);
+  it.page_begin = c * ppc;
+  it.page_end = min(it.page_begin + ppc, npages);
   return it;
 }
 
@@ -1557,9 +1587,10 @@ extern int b200_attn_pages_per_chunk;
 extern int b200_attn_prefill_direct;
 extern int b200_attn_path;
 
-// Pages per chunk chosen so that the persistent grid sees several items per CTA without making
-// the per-item partials a visible share of the traffic.
-int b200_attn_pages_per_chunk = 8;
+// Pages per chunk: 0 = chosen per batch by the plan kernel (decode rows; 8 for prefill groups below the direct mode),
+// so that the persistent grid sees several items per worker without making the per-item partials a visible share of
+// the traffic; 4..32 forces a value.
+int b200_attn_pages_per_chunk = 0;
 int b200_attn_prefill_direct = 1;  // tuning hook for tests: 0 keeps the chunked prefill path at every size
 int b200_attn_path = 0;  // 0 = automatic, 1 = CUDA-core kernel, 2 = tensor-core kernel
 
@@ -1591,17 +1622,18 @@ b200_status b200_paged_attn_decode_strided(b200_kv* kv, int32_t layer, const voi
     B200_CUDA_TRY(cudaGetDevice(&dev));
     B200_CUDA_TRY(cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, dev));
   }
-  int ppc = std::min(std::max(b200_attn_pages_per_chunk, 1), kMaxChunkPages);
-  // scratch bound: chunks <= pages/ppc + rows; kv->max_chunks was sized for ppc >= 4
-  if (ppc < 4) ppc = 4;
+  // 0 = the plan kernel picks 8, 16 or 32 from the batch's mean context; the tuning hook forces 4..32
+  // (scratch bound: chunks <= pages/ppc + rows; kv->max_chunks was sized for ppc >= 4)
+  const int ppc = b200_attn_pages_per_chunk <= 0 ? 0 : std::min(std::max(b200_attn_pages_per_chunk, 4), kMaxChunkPages);
   AttnArgs a;
   a.d = kv->dev; a.layer = layer; a.q = (const __nv_bfloat16*)d_q; a.q_stride = q_stride; a.row_seq = d_row_seq; a.row_ctx = d_row_ctx;
   a.chunk_start = kv->d_chunk_start; a.total_rows = total_rows; a.n_q_heads = c.n_q_heads; a.pages_per_chunk = ppc;
   a.part_o = kv->d_part_o; a.part_ml = kv->d_part_ml;
   a.scale_log2 = 1.4426950408889634f / sqrtf((float)c.head_dim);
+  a.ppc_dev = kv->d_chunk_start + c.max_rows + 1;  // the last word of the array: the plan kernel's choice
   if (!reuse_plan) {  // the chunk plan depends on the row arrays only: the layers of one step share it
     attn_plan_kernel<<<1, 1024, 0, s>>>(d_row_ctx, total_rows, c.page_size, ppc, kv->d_chunk_start, kv->max_chunks,
-                                        kv->dev.state + ST_ATTN_ERR);
+                                        kv->dev.state + ST_ATTN_ERR, kv->d_chunk_start + c.max_rows + 1);
     B200_LAUNCH_CHECK();
   }
   if (use_mma && fp8) return launch_attn_mma_fp8(kv, a, d_out, g_sm_count, s);
@@ -1642,7 +1674,8 @@ b200_status b200_paged_attn_prefill_strided(b200_kv* kv, int32_t layer, const vo
   // per group, as long as its context, and the kernel writes the normalised rows itself: no f32 partials, no combine
   // pass (at 8192 rows of config 5 the partials were 400 MB per layer and the combine pass 7 % of the scenario).
   const bool single_chunk = total_rows >= 1024 && b200_attn_prefill_direct;
-  const int ppc = single_chunk ? std::max(c.max_pages_per_seq, 1) : std::min(std::max(b200_attn_pages_per_chunk, 4), kMaxChunkPages);
+  const int ppc = single_chunk ? std::max(c.max_pages_per_seq, 1)
+                               : (b200_attn_pages_per_chunk <= 0 ? 8 : std::min(std::max(b200_attn_pages_per_chunk, 4), kMaxChunkPages));
   const int stride = c.max_rows + 2;
   AttnArgs a;
   a.d = kv->dev; a.layer = layer; a.q = (const __nv_bfloat16*)d_q; a.q_stride = q_stride; a.row_seq = d_row_seq; a.row_ctx = d_row_ctx;

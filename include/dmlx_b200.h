@@ -330,7 +330,8 @@ b200_status b200_paged_attn_prefill(b200_kv* kv, int32_t layer, const void* d_q,
                                     const int32_t* d_row_seq, const int32_t* d_row_ctx,
                                     int32_t total_rows, void* d_out, void* stream);
 
-/* Tuning hook with no reference counterpart: pages per split-K chunk (4..32, default 8). */
+/* Tuning hook with no reference counterpart: pages per split-K chunk, 4..32; 0 (default) = 8, 16 or 32 chosen on
+ * the device from the batch's mean context. */
 void b200_set_attn_pages_per_chunk(int32_t n);
 /* Tuning hook with no reference counterpart: b200_paged_attn_prefill serves batches of 1024 rows and more
  * with one chunk per group of rows and writes the normalised rows itself (default, 1); 0 keeps the chunked

@@ -20,7 +20,7 @@ def _close(got, want):
     return rel, cos
 
 
-def _run_case(ctxs, hq, hkv, d, kv_dtype, seed, scatter=True, pages_per_chunk=8, path=0):
+def _run_case(ctxs, hq, hkv, d, kv_dtype, seed, scatter=True, pages_per_chunk=0, path=0):
     from dmlx_b200 import device as dev
 
     rng = np.random.default_rng(seed)
@@ -63,7 +63,7 @@ def _run_case(ctxs, hq, hkv, d, kv_dtype, seed, scatter=True, pages_per_chunk=8,
         off += c
     kv.close()
     dev.set_attn_path(0)
-    dev.set_attn_pages_per_chunk(8)
+    dev.set_attn_pages_per_chunk(0)   # back to the automatic choice
     return got, want, (k, v, q)
 
 
@@ -231,6 +231,22 @@ def test_prefill_batches_of_1024_rows_and_more_write_their_rows_directly(hq, hkv
         rel, cos = _close(got[r], want)
         assert rel <= REL_TOL and cos >= COS_TOL, (r, s, c, rel, cos)
     kv.close()
+
+
+@pytest.mark.parametrize("ctxs,forced", [([300, 70, 1500, 33], 8), ([4100, 3900, 4200, 3500], 16), ([9000, 7000, 8100], 32)])
+@pytest.mark.parametrize("kv_dtype", [0, 1])
+def test_chunk_length_chosen_on_the_device_equals_the_forced_one(ctxs, forced, kv_dtype):
+    """With the tuning hook at 0 the plan kernel picks 8, 16 or 32 pages per chunk from the batch's mean context
+    (below 96 pages per row, below 192, above).  The outputs must be the bits of a run with that length forced,
+    and match the oracle."""
+    auto, want, _ = _run_case(ctxs, 32, 8, 128, kv_dtype, seed=7 + forced)
+    same, _, _ = _run_case(ctxs, 32, 8, 128, kv_dtype, seed=7 + forced, pages_per_chunk=forced)
+    assert np.array_equal(auto, same)
+    other, _, _ = _run_case(ctxs, 32, 8, 128, kv_dtype, seed=7 + forced, pages_per_chunk=4)
+    assert not np.array_equal(auto, other) or len(ctxs) == 0   # another split order rounds differently somewhere
+    for s in range(len(ctxs)):
+        r, c = _close(auto[s], want[s])
+        assert r <= REL_TOL and c >= COS_TOL, (s, ctxs[s], r, c)
 
 
 @pytest.mark.parametrize("kv_dtype", [0, 1])  # bf16 pool, FP8-E4M3 pool (tensor-core kernels, head_dim 128)
