@@ -318,17 +318,24 @@ def run_llama(args, rank, world, local):
         total_ms, e2e_ms = t.tolist()
     # the same model through the engine as an arrival process (all ranks take part: 256 requests in total)
     arrivals = None
+    # (a failure in these two additions is reported under their key; it does not cost the run its headline line)
     if do_arrivals:
         launches_before = model.launch_count()
         kv.close()
-        arrivals = run_arrivals(args, rank, world, local, model=model, c=c)
+        try:
+            arrivals = run_arrivals(args, rank, world, local, model=model, c=c)
+        except Exception as e:  # noqa: BLE001
+            arrivals = {"error": f"{type(e).__name__}: {e}"}
     # on several GPUs: the one workload with an exchange step, the MoE layer stack under expert parallelism
     expert_parallel = None
     if world > 1 and not args.no_ep and not args.layers:
-        model.close()
-        torch.cuda.empty_cache()
-        mc, m_total, m_e2e, mK, _, _, _, _ = moe_measure(args, rank, world, torch, dist, dev, steps=20)
-        expert_parallel = moe_summary(mc, m_total, m_e2e, mK, world)
+        try:
+            model.close()
+            torch.cuda.empty_cache()
+            mc, m_total, m_e2e, mK, _, _, _, _ = moe_measure(args, rank, world, torch, dist, dev, steps=20)
+            expert_parallel = moe_summary(mc, m_total, m_e2e, mK, world)
+        except Exception as e:  # noqa: BLE001
+            expert_parallel = {"error": f"{type(e).__name__}: {e}"}
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
