@@ -1095,7 +1095,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--workload", default="llama8b_int4")
-    ap.add_argument("--moe-tile", type=int, default=128, help="moe_mxfp4 only: token tile of the grouped matmul")
+    ap.add_argument("--moe-tile", type=int, default=112,
+                    help="moe_mxfp4 only: token tile of the grouped matmul (up to 112 rows the block-scaled kernel keeps two accumulator sets)")
     ap.add_argument("--moe-block-scaled", type=int, default=-1, help="moe_mxfp4 only: 1 runs the grouped matmuls on tcgen05.mma kind::mxf8f6f4 (hardware block scaling), 0 on the dequantising kernels (default: library choice)")
     ap.add_argument("--moe-tmem-a", type=int, default=-1, help="moe_mxfp4 only: 0/1 forces the grouped matmul kernel (default: library choice)")
     ap.add_argument("--layers", type=int, default=0, help="llama8b_int4 only: fewer layers (profiling / smoke runs)")

@@ -1797,9 +1797,9 @@ __global__ void __launch_bounds__(kMxThreads, 1)
   uint64_t* full = bars;
   uint64_t* slot_free = bars + P;
   uint64_t* sf_ready = bars + 2 * P;     // the constant activation scales are in tensor memory (once)
-  uint64_t* accum_ready = bars + 2 * P + 1;
-  uint64_t* accum_free = bars + 2 * P + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P + 3);
+  uint64_t* accum_ready = bars + 2 * P + 1;  // [2] one per accumulator set
+  uint64_t* accum_free = bars + 2 * P + 3;   // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * P + 5);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_pairs = (a.nt + 1) / 2;
@@ -1839,8 +1839,10 @@ __global__ void __launch_bounds__(kMxThreads, 1)
       ptx::mbar_init(&slot_free[s], 1);
     }
     ptx::mbar_init(sf_ready, 4 * 32);
-    ptx::mbar_init(accum_ready, 1);
-    ptx::mbar_init(accum_free, 4);
+    for (int q = 0; q < 2; ++q) {
+      ptx::mbar_init(&accum_ready[q], 1);
+      ptx::mbar_init(&accum_free[q], 4);
+    }
     ptx::mbar_fence_init();
   }
   if (warp == 5) {
@@ -1851,7 +1853,14 @@ __global__ void __launch_bounds__(kMxThreads, 1)
   __syncthreads();
   ptx::tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t sfa_col0 = tmem_base + 256u, sfb_hi = tmem_base + 256u + 8u * (uint32_t)P, sfb_lo = sfb_hi + 4u;
+  // Tensor-memory columns.  Token tiles of up to 112 rows leave room for TWO sets of accumulators (2 sets x 2 tiles x tn
+  // columns + the scales <= 512): work items alternate between them, so that the epilogue of one item drains its set
+  // while the MMAs of the next item fill the other.  With one set the next item's first MMA had to wait for the last
+  // slab of the epilogue: the MoE stack spent a quarter of its time there (10.7 ms -> 7.9 ms with the epilogue left
+  // out, timing only).  Wider tiles keep one set of two 128-column accumulators.
+  const bool dual = 4 * tn + 8 * P + 8 <= (int)kCols;
+  const uint32_t acc_stride = dual ? (uint32_t)tn : 128u, set_stride = 2u * acc_stride;
+  const uint32_t sfa_col0 = tmem_base + (dual ? 2u * set_stride : 256u), sfb_hi = sfa_col0 + 8u * (uint32_t)P, sfb_lo = sfb_hi + 4u;
   bool ok = true;
 
   if (warp == 4) {
@@ -1883,10 +1892,12 @@ __global__ void __launch_bounds__(kMxThreads, 1)
       ok = ptx::mbar_wait(sf_ready, 0);
       for (int w = blockIdx.x; w < n_work && ok; w += gridDim.x, ++n_done) {
         const Work k = decode(w);
-        // the epilogue of the previous item must have read the accumulators out before they are overwritten
-        if (n_done > 0) ok = ptx::mbar_wait(accum_free, (n_done - 1) & 1u);
+        // the epilogue of the set's previous item must have read the accumulators out before they are overwritten
+        const uint32_t set = dual ? (n_done & 1u) : 0u, uses = dual ? (n_done >> 1) : n_done;
+        if (uses > 0) ok = ptx::mbar_wait(&accum_free[set], (uses - 1) & 1u);
         if (!ok) break;
         ptx::tc_fence_after_sync();
+        const uint32_t acc0 = tmem_base + set * set_stride;
         for (int i = 0; i < k.n_chunks && ok; ++i, ph ^= (s + 1 == P), s = (s + 1 == P) ? 0 : s + 1) {
           ok = ptx::mbar_wait(&full[s], ph);
           if (!ok) break;
@@ -1900,13 +1911,13 @@ __global__ void __launch_bounds__(kMxThreads, 1)
 #pragma unroll
             for (int k4 = 0; k4 < 4; ++k4) {
               const uint32_t idesc = ptx::umma_idesc_mx_e2m1_e4m3(kTileN, k.tn_eff, k4);
-              ptx::umma_mxf8f6f4(tmem_base + tile * 128, da + 2 * k4, dh + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u, sfa, sfb_hi);
-              ptx::umma_mxf8f6f4(tmem_base + tile * 128, da + 2 * k4, dl + 2 * k4, idesc, 1u, sfa, sfb_lo);
+              ptx::umma_mxf8f6f4(acc0 + tile * acc_stride, da + 2 * k4, dh + 2 * k4, idesc, (i > 0 || k4 > 0) ? 1u : 0u, sfa, sfb_hi);
+              ptx::umma_mxf8f6f4(acc0 + tile * acc_stride, da + 2 * k4, dl + 2 * k4, idesc, 1u, sfa, sfb_lo);
             }
           }
           ptx::umma_commit(&slot_free[s]);
         }
-        if (ok) ptx::umma_commit(accum_ready);
+        if (ok) ptx::umma_commit(&accum_ready[set]);
       }
     }
   } else {
@@ -1923,7 +1934,9 @@ __global__ void __launch_bounds__(kMxThreads, 1)
     uint32_t n_done = 0;
     for (int w = blockIdx.x; w < n_work; w += gridDim.x, ++n_done) {
       const Work k = decode(w);
-      if (ok) ok = ptx::mbar_wait(accum_ready, n_done & 1u);
+      const uint32_t set = dual ? (n_done & 1u) : 0u, uses = dual ? (n_done >> 1) : n_done;
+      const uint32_t acc0 = tmem_base + set * set_stride;
+      if (ok) ok = ptx::mbar_wait(&accum_ready[set], uses & 1u);
       const bool all_ok = __syncthreads_and_epi(ok);
       if (!all_ok) { ok = false; break; }
       ptx::tc_fence_after_sync();
@@ -1933,7 +1946,7 @@ __global__ void __launch_bounds__(kMxThreads, 1)
         const float us_mine = (lane < kMxpStageTokens && c0 + lane < k.rows_here) ? a.act_unscale[k.t0 + c0 + lane] : 0.f;
         for (int tile = 0; tile < k.n_tiles; ++tile) {
           uint32_t v[16];
-          ptx::tmem_ld16(tmem_base + lane_base + (uint32_t)(tile * 128 + c0), v);
+          ptx::tmem_ld16(acc0 + lane_base + (uint32_t)tile * acc_stride + (uint32_t)c0, v);
           ptx::tmem_ld_wait();
           if (partial) {
             // [weight tile][token tile][split][tn][128] f32, summed by the finish kernel
@@ -1954,7 +1967,7 @@ __global__ void __launch_bounds__(kMxThreads, 1)
         if (last_slab) {  // everything this item holds in tensor memory has been read
           ptx::tc_fence_before_sync();
           __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(accum_free);
+          if (lane == 0) ptx::mbar_arrive(&accum_free[set]);
         }
         if (partial) continue;
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -2484,7 +2497,7 @@ static b200_status launch_mx(const b200_qweight* w, QmmArgs& a, int rows, cudaSt
   const int stage = 2 * kTileN * kMxK + 2 * tn * 128 + 1024;
   if (b200_qmm_mx_persistent) {
     // persistent form: one CTA per SM walks the work items; dense launches with few tile pairs split K
-    const int fixed = 1024 + 2 * kMxpStageTokens * kTileN * (int)sizeof(float) + 8 * (2 * 8 + 4) + 16;
+    const int fixed = 1024 + 2 * kMxpStageTokens * kTileN * (int)sizeof(float) + 8 * (2 * 8 + 6) + 16;
     a.stages = std::max(2, std::min(6, (std::min(smem_budget, 224 * 1024) - fixed) / stage));
     const size_t smem = (size_t)a.stages * stage + fixed;
     if ((int)smem > smem_budget) { b200_set_error("block-scaled path: %zu bytes of shared memory needed, %d available", smem, smem_budget); return B200_ERR_CAPACITY; }

@@ -133,7 +133,8 @@ def test_moe_layer_matches_oracle(mode_name, _restore_grouped_path):
     assert rel <= 2e-2 and cos >= 0.9995, (rel, cos)
 
 
-def test_moe_layer_at_full_size_against_the_oracle_on_sampled_tokens(_restore_grouped_path):
+@pytest.mark.parametrize("tile_rows", [128, 112])  # 112: two accumulator sets in tensor memory, work items alternate
+def test_moe_layer_at_full_size_against_the_oracle_on_sampled_tokens(tile_rows, _restore_grouped_path):
     """The MoE workload's own shape: hidden 4096, 256 routed experts of intermediate 2048 plus a shared
     expert, top-6 softmax routing with a skewed per-expert bias, 4096 tokens in one step, MXFP4 weights
     generated on the device.  Routing and grouping are checked for all tokens; the layer output of 10
@@ -153,7 +154,7 @@ def test_moe_layer_at_full_size_against_the_oracle_on_sampled_tokens(_restore_gr
     sgu = dev.QWeight.random(dev.Q_MXFP4_G32, 2 * inter, d, 1, seed=23)
     sdown = dev.QWeight.random(dev.Q_MXFP4_G32, d, inter, 1, seed=24)
     layer = dev.MoELayer(d, e, inter, k, gate, gu, down, sgu, sdown, bias=bias, route_scale=1.5, swiglu_limit=10.0,
-                         tile_rows=128, max_tokens=n)
+                         tile_rows=tile_rows, max_tokens=n)
     got = layer.forward(torch.tensor(x, device="cuda").bfloat16()).float().cpu().numpy()
     assert dev.qmm_error_word() == 0
     idx, wts, off = layer.last_routing(n)
