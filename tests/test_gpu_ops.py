@@ -215,7 +215,8 @@ def test_qmm_paths_agree_and_are_deterministic():
     assert rel <= 1e-2 and cos >= 0.9999
 
 
-@pytest.mark.parametrize("rows,n,k", [(16, 128, 128), (32, 256, 512), (100, 256, 4096), (128, 384, 2048), (300, 640, 1024), (7, 256, 256)])
+@pytest.mark.parametrize("rows,n,k", [(16, 128, 128), (32, 256, 512), (100, 256, 4096), (128, 384, 2048), (300, 640, 1024), (7, 256, 256),
+                                      (600, 384, 1024), (1024, 4096, 512)])  # the last two: 112-row tiles (two accumulator sets), 128-row tiles
 def test_qmm_mxfp4_block_scaled_tensor_core_path(rows, n, k):
     """tcgen05.mma kind::mxf8f6f4: E2M1 codes and E8M0 scales consumed by the tensor cores, activations
     as two E4M3 halves.  Same oracle and tolerance as the dequantising paths; odd tile counts, several
