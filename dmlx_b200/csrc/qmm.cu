@@ -1482,6 +1482,7 @@ __global__ void __launch_bounds__(kGemvThreads, NT8 >= 4 ? 1 : 2) qmm_mma8_kerne
 // tcgen05.st per thread and tile; the four 32-lane quarters hold the same words) and later run the
 // epilogue, warp 5 issues 2 tiles x 4 K32 steps x 2 halves MMAs per stage.
 constexpr int kMxThreads = 6 * 32;
+constexpr int kMxpThreads = 10 * 32;  // persistent form: warps 0-3 and 6-9 run the epilogue (one tile each), 4 loads, 5 issues MMAs
 constexpr int kMxK = 128;
 
 __device__ __forceinline__ uint32_t mx_f32x2_to_e4m3x2(float lo, float hi) {
@@ -1575,6 +1576,20 @@ __device__ __forceinline__ bool __syncthreads_and_epi(bool pred) {
       "{\n\t.reg .pred p, q;\n\t"
       "setp.ne.b32 p, %1, 0;\n\t"
       "bar.red.and.pred q, 1, 128, p;\n\t"
+      "selp.u32 %0, 1, 0, q;\n\t}"
+      : "=r"(r)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return r != 0;
+}
+
+// The same over the 256 epilogue threads of the persistent kernel (warps 0-3 and 6-9).
+__device__ __forceinline__ bool __syncthreads_and_epi8(bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %1, 0;\n\t"
+      "bar.red.and.pred q, 1, 256, p;\n\t"
       "selp.u32 %0, 1, 0, q;\n\t}"
       : "=r"(r)
       : "r"((uint32_t)pred)
@@ -1782,7 +1797,7 @@ __global__ void __launch_bounds__(kMxThreads, 1)
 //                 the last slab has been read, before it is stored.
 constexpr int kMxpStageTokens = 16;
 
-__global__ void __launch_bounds__(kMxThreads, 1)
+__global__ void __launch_bounds__(kMxpThreads, 1)
     qmm_mxp_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ MxActMaps amaps, QmmArgs a) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -1841,7 +1856,7 @@ __global__ void __launch_bounds__(kMxThreads, 1)
     ptx::mbar_init(sf_ready, 4 * 32);
     for (int q = 0; q < 2; ++q) {
       ptx::mbar_init(&accum_ready[q], 1);
-      ptx::mbar_init(&accum_free[q], 4);
+      ptx::mbar_init(&accum_free[q], 8);  // one arrival per epilogue warp
     }
     ptx::mbar_fence_init();
   }
@@ -1921,12 +1936,16 @@ __global__ void __launch_bounds__(kMxThreads, 1)
       }
     }
   } else {
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    ptx::tmem_st4(sfb_hi + lane_base, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);  // 2^0
-    ptx::tmem_st4(sfb_lo + lane_base, 0x7B7B7B7Bu, 0x7B7B7B7Bu, 0x7B7B7B7Bu, 0x7B7B7B7Bu);  // 2^-4
-    ptx::tmem_st_wait();
-    ptx::tc_fence_before_sync();
-    ptx::mbar_arrive(sf_ready);
+    // ---- epilogue: warps 0-3 drain tile 0, warps 6-9 tile 1 (a warp reads the tensor-memory lanes 32 * (warp % 4)) ----
+    const int etile = warp < 4 ? 0 : 1, etid = warp < 4 ? tid : tid - 64;  // dense index over the 256 epilogue threads
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    if (warp < 4) {
+      ptx::tmem_st4(sfb_hi + lane_base, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu);  // 2^0
+      ptx::tmem_st4(sfb_lo + lane_base, 0x7B7B7B7Bu, 0x7B7B7B7Bu, 0x7B7B7B7Bu, 0x7B7B7B7Bu);  // 2^-4
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before_sync();
+      ptx::mbar_arrive(sf_ready);
+    }
     const bool swiglu = a.epilogue == B200_EPI_SWIGLU;
     const int out_per_tile = swiglu ? kTileN / 2 : kTileN, chunks = out_per_tile / 8;
     const int n_out = swiglu ? a.n / 2 : a.n;
@@ -1937,20 +1956,21 @@ __global__ void __launch_bounds__(kMxThreads, 1)
       const uint32_t set = dual ? (n_done & 1u) : 0u, uses = dual ? (n_done >> 1) : n_done;
       const uint32_t acc0 = tmem_base + set * set_stride;
       if (ok) ok = ptx::mbar_wait(&accum_ready[set], uses & 1u);
-      const bool all_ok = __syncthreads_and_epi(ok);
+      const bool all_ok = __syncthreads_and_epi8(ok);
       if (!all_ok) { ok = false; break; }
       ptx::tc_fence_after_sync();
       const bool partial = splits > 1;
+      const bool mine = etile < k.n_tiles;
       for (int c0 = 0; c0 < k.rows_here; c0 += kMxpStageTokens) {
         const bool last_slab = c0 + kMxpStageTokens >= k.rows_here;
         const float us_mine = (lane < kMxpStageTokens && c0 + lane < k.rows_here) ? a.act_unscale[k.t0 + c0 + lane] : 0.f;
-        for (int tile = 0; tile < k.n_tiles; ++tile) {
+        if (mine) {
           uint32_t v[16];
-          ptx::tmem_ld16(acc0 + lane_base + (uint32_t)tile * acc_stride + (uint32_t)c0, v);
+          ptx::tmem_ld16(acc0 + lane_base + (uint32_t)etile * acc_stride + (uint32_t)c0, v);
           ptx::tmem_ld_wait();
           if (partial) {
             // [weight tile][token tile][split][tn][128] f32, summed by the finish kernel
-            float* wsp = a.ws + (((size_t)((k.nt0 + tile) * tts + k.tt) * splits + k.split) * tn) * kTileN + warp * 32 + lane;
+            float* wsp = a.ws + (((size_t)((k.nt0 + etile) * tts + k.tt) * splits + k.split) * tn) * kTileN + (warp & 3) * 32 + lane;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const float us = __shfl_sync(0xffffffffu, us_mine, j);
@@ -1960,56 +1980,56 @@ __global__ void __launch_bounds__(kMxThreads, 1)
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               const float us = __shfl_sync(0xffffffffu, us_mine, j);
-              stage_f[((size_t)tile * kMxpStageTokens + j) * kTileN + warp * 32 + lane] = __uint_as_float(v[j]) * us;
+              stage_f[((size_t)etile * kMxpStageTokens + j) * kTileN + (warp & 3) * 32 + lane] = __uint_as_float(v[j]) * us;
             }
           }
         }
-        if (last_slab) {  // everything this item holds in tensor memory has been read
+        if (last_slab) {  // everything this warp reads of the item's accumulators has been read
           ptx::tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(&accum_free[set]);
         }
         if (partial) continue;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         const int slab_rows = min(kMxpStageTokens, k.rows_here - c0);
-        for (int tile = 0; tile < k.n_tiles; ++tile) {
-          for (int idx = tid; idx < slab_rows * chunks; idx += 128) {
-            const int tok = idx / chunks, ch = idx - tok * chunks;
-            const int token = k.t0 + c0 + tok, col = (k.nt0 + tile) * out_per_tile + ch * 8;
-            if (col >= n_out) continue;
-            const float* src = stage_f + ((size_t)tile * kMxpStageTokens + tok) * kTileN + ch * (swiglu ? 16 : 8);
-            const float rs = a.row_scale(token);
-            float o[8];
-            if (swiglu) {
+        const int per_tile = slab_rows * chunks;
+        for (int idx = etid; idx < k.n_tiles * per_tile; idx += 256) {
+          const int tile = idx / per_tile, rest = idx - tile * per_tile;
+          const int tok = rest / chunks, ch = rest - tok * chunks;
+          const int token = k.t0 + c0 + tok, col = (k.nt0 + tile) * out_per_tile + ch * 8;
+          if (col >= n_out) continue;
+          const float* src = stage_f + ((size_t)tile * kMxpStageTokens + tok) * kTileN + ch * (swiglu ? 16 : 8);
+          const float rs = a.row_scale(token);
+          float o[8];
+          if (swiglu) {
 #pragma unroll
-              for (int q = 0; q < 4; ++q) {
-                const float4 f = reinterpret_cast<const float4*>(src)[q];  // gate, up, gate, up
-                float g0 = f.x, u0 = f.y, g1 = f.z, u1 = f.w;
-                if (L > 0.f) { g0 = fminf(g0, L); u0 = fminf(fmaxf(u0, -L), L); g1 = fminf(g1, L); u1 = fminf(fmaxf(u1, -L), L); }
-                o[2 * q] = g0 / (1.0f + __expf(-g0)) * u0 * rs;
-                o[2 * q + 1] = g1 / (1.0f + __expf(-g1)) * u1 * rs;
-              }
-            } else {
-              const float4 f0 = reinterpret_cast<const float4*>(src)[0], f1 = reinterpret_cast<const float4*>(src)[1];
-              o[0] = f0.x; o[1] = f0.y; o[2] = f0.z; o[3] = f0.w; o[4] = f1.x; o[5] = f1.y; o[6] = f1.z; o[7] = f1.w;
-              if (a.epilogue == B200_EPI_RESIDUAL) {
-                const uint4 r = *reinterpret_cast<const uint4*>(a.residual + (size_t)token * n_out + col);
-                const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
-#pragma unroll
-                for (int q = 0; q < 4; ++q) { o[2 * q] += ptx::bf16_lo(rw[q]); o[2 * q + 1] += ptx::bf16_hi(rw[q]); }
-              }
-#pragma unroll
-              for (int q = 0; q < 8; ++q) o[q] *= rs;
+            for (int q = 0; q < 4; ++q) {
+              const float4 f = reinterpret_cast<const float4*>(src)[q];  // gate, up, gate, up
+              float g0 = f.x, u0 = f.y, g1 = f.z, u1 = f.w;
+              if (L > 0.f) { g0 = fminf(g0, L); u0 = fminf(fmaxf(u0, -L), L); g1 = fminf(g1, L); u1 = fminf(fmaxf(u1, -L), L); }
+              o[2 * q] = g0 / (1.0f + __expf(-g0)) * u0 * rs;
+              o[2 * q + 1] = g1 / (1.0f + __expf(-g1)) * u1 * rs;
             }
-            uint4 out;
-            __nv_bfloat162 p0 = __floats2bfloat162_rn(o[0], o[1]), p1 = __floats2bfloat162_rn(o[2], o[3]);
-            __nv_bfloat162 p2 = __floats2bfloat162_rn(o[4], o[5]), p3 = __floats2bfloat162_rn(o[6], o[7]);
-            out.x = *reinterpret_cast<uint32_t*>(&p0); out.y = *reinterpret_cast<uint32_t*>(&p1);
-            out.z = *reinterpret_cast<uint32_t*>(&p2); out.w = *reinterpret_cast<uint32_t*>(&p3);
-            *reinterpret_cast<uint4*>(a.y + (size_t)token * n_out + col) = out;
+          } else {
+            const float4 f0 = reinterpret_cast<const float4*>(src)[0], f1 = reinterpret_cast<const float4*>(src)[1];
+            o[0] = f0.x; o[1] = f0.y; o[2] = f0.z; o[3] = f0.w; o[4] = f1.x; o[5] = f1.y; o[6] = f1.z; o[7] = f1.w;
+            if (a.epilogue == B200_EPI_RESIDUAL) {
+              const uint4 r = *reinterpret_cast<const uint4*>(a.residual + (size_t)token * n_out + col);
+              const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+              for (int q = 0; q < 4; ++q) { o[2 * q] += ptx::bf16_lo(rw[q]); o[2 * q + 1] += ptx::bf16_hi(rw[q]); }
+            }
+#pragma unroll
+            for (int q = 0; q < 8; ++q) o[q] *= rs;
           }
+          uint4 out;
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(o[0], o[1]), p1 = __floats2bfloat162_rn(o[2], o[3]);
+          __nv_bfloat162 p2 = __floats2bfloat162_rn(o[4], o[5]), p3 = __floats2bfloat162_rn(o[6], o[7]);
+          out.x = *reinterpret_cast<uint32_t*>(&p0); out.y = *reinterpret_cast<uint32_t*>(&p1);
+          out.z = *reinterpret_cast<uint32_t*>(&p2); out.w = *reinterpret_cast<uint32_t*>(&p3);
+          *reinterpret_cast<uint4*>(a.y + (size_t)token * n_out + col) = out;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");  // the staging tile is free for the next slab
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // the staging tile is free for the next slab
       }
     }
   }
@@ -2530,7 +2550,7 @@ static b200_status launch_mx(const b200_qweight* w, QmmArgs& a, int rows, cudaSt
     }
     const long long n_work = a.items ? (long long)pairs * a.max_items : (long long)pairs * tts * real_splits;
     const int grid = (int)std::max<long long>(1, std::min<long long>(g_sms, n_work));
-    qmm_mxp_kernel<<<grid, kMxThreads, smem, s>>>(*reinterpret_cast<const CUtensorMap*>(w->mx_map), amaps, a);
+    qmm_mxp_kernel<<<grid, kMxpThreads, smem, s>>>(*reinterpret_cast<const CUtensorMap*>(w->mx_map), amaps, a);
     B200_LAUNCH_CHECK();
     return real_splits > 1 ? launch_finish(a, real_splits, s) : B200_OK;
   }
