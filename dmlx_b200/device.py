@@ -514,7 +514,7 @@ class MoELayer:
     def __init__(self, hidden: int, n_experts: int, inter: int, top_k: int, gate: QWeight, experts_gate_up: QWeight,
                  experts_down: QWeight, shared_gate_up: Optional[QWeight] = None, shared_down: Optional[QWeight] = None,
                  bias: Optional[np.ndarray] = None, scoring: int = SCORE_SOFTMAX, route_scale: float = 1.0,
-                 swiglu_limit: float = 10.0, shared_swiglu_limit: float = 0.0, tile_rows: int = 128,
+                 swiglu_limit: float = 10.0, shared_swiglu_limit: float = 0.0, tile_rows: int = 112,
                  max_tokens: int = 4096):
         self.cfg = _lib.MoeConfig(hidden, n_experts, inter, top_k, scoring, tile_rows, max_tokens, route_scale,
                                   swiglu_limit, shared_swiglu_limit)

@@ -90,7 +90,7 @@ class ExpertParallelMoE:
 
     def __init__(self, comm: Communicator, hidden: int, n_experts: int, inter: int, top_k: int, gate, local_gate_up,
                  local_down, shared_gate_up=None, shared_down=None, bias: Optional[np.ndarray] = None, scoring: int = 0,
-                 route_scale: float = 1.0, swiglu_limit: float = 10.0, shared_swiglu_limit: float = 0.0, tile_rows: int = 128,
+                 route_scale: float = 1.0, swiglu_limit: float = 10.0, shared_swiglu_limit: float = 0.0, tile_rows: int = 112,
                  max_tokens: int = 4096):
         assert n_experts % comm.world == 0 and local_gate_up.n_experts == n_experts // comm.world
         self.comm = comm

@@ -650,7 +650,9 @@ b200_status b200_moe_combine(const void* d_y_sorted, const int32_t* d_inv_order,
 typedef struct b200_moe_config {
   int32_t hidden, n_experts, inter, top_k;
   int32_t scoring;       /* 0 softmax, 1 sigmoid, 2 sqrt-softplus */
-  int32_t tile_rows;     /* token tile of the grouped matmul: multiple of 16, 16..256 */
+  int32_t tile_rows;     /* token tile of the grouped matmul: multiple of 16, 16..256; up to 112 the block-scaled
+                          * MXFP4 kernel keeps two accumulator sets and overlaps an item's epilogue with the
+                          * next item's MMAs (112 measured best for experts of about a hundred rows) */
   int32_t max_tokens;
   float route_scale;
   float swiglu_limit;        /* routed experts: 10 in the reference (deepseek_v4.zig:64) */
